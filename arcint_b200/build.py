@@ -1,0 +1,105 @@
+"""Compile the CUDA library in-tree for sm_100a: arcint_b200/lib/libb200q.so.
+
+nvcc cross-compiles without a GPU. Objects are rebuilt only when a source or header is
+newer; `python -m arcint_b200.build --force` rebuilds everything, `--verbose` adds
+-Xptxas -v (registers, spills, shared memory per kernel).
+"""
+import argparse
+import concurrent.futures
+import glob
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIBDIR = os.path.join(HERE, "lib")
+OBJDIR = os.path.join(HERE, "build")
+LIB = os.path.join(LIBDIR, "libb200q.so")
+EMUL = os.path.join(LIBDIR, "libb200q_emul.so")
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]
+
+
+def nvcc():
+    p = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(p):
+        raise RuntimeError("nvcc not found")
+    return p
+
+
+def _deps():
+    return glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + \
+        [os.path.join(HERE, "..", "include", "b200q.h")]
+
+
+def _stale(dst, srcs):
+    return not os.path.exists(dst) or any(os.path.getmtime(s) > os.path.getmtime(dst) for s in srcs)
+
+
+def _compile(src, obj, verbose):
+    cmd = [nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    return src, r.returncode, r.stdout + r.stderr
+
+
+def build(force=False, verbose=False):
+    os.makedirs(LIBDIR, exist_ok=True)
+    os.makedirs(OBJDIR, exist_ok=True)
+    srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+    deps = _deps()
+    jobs, objs = [], []
+    for s in srcs:
+        o = os.path.join(OBJDIR, os.path.basename(s)[:-3] + ".o")
+        objs.append(o)
+        if force or verbose or _stale(o, [s] + deps):
+            jobs.append((s, o))
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
+        for src, rc, out in ex.map(lambda j: _compile(j[0], j[1], verbose), jobs):
+            if verbose or rc:
+                print(out)
+            if rc:
+                raise RuntimeError("nvcc failed on " + src)
+    if jobs or not os.path.exists(LIB):
+        cmd = [nvcc(), "-shared", "-o", LIB] + objs + ["-lcudart"] + _extra_link()
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode:
+            print(r.stdout + r.stderr)
+            raise RuntimeError("link failed")
+    build_emul(force)
+    return LIB
+
+
+def _extra_link():
+    return []
+
+
+def build_emul(force=False):
+    """Host build of the kernels' per-lane text (device-free tests): g++ on emul.cpp."""
+    src = os.path.join(CSRC, "emul.cpp")
+    if not os.path.exists(src):
+        return None
+    if not force and not _stale(EMUL, [src] + _deps()):
+        return EMUL
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(nvcc())), "include")
+    for cxx in ("/usr/bin/g++", os.environ.get("CXX", "g++"), "g++"):
+        cxx = cxx if os.path.isabs(cxx) else shutil.which(cxx)
+        if not cxx or not os.path.exists(cxx):
+            continue
+        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-I", cuda_inc, src, "-o", EMUL]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode == 0:
+            return EMUL
+        err = r.stderr
+    raise RuntimeError("emul build failed:\n" + err[-2000:])
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--verbose", action="store_true")
+    a = ap.parse_args()
+    print(build(force=a.force, verbose=a.verbose))
+    sys.exit(0)

@@ -1,0 +1,356 @@
+// api.cu -- the C ABI: context, scratch, shape gates and dispatch of MUL_MAT.
+//
+// Host side of the path, the counterpart of the reference's dispatch in ggml-opencl.cpp
+// (marfrit/arcint contrib/llama.cpp/patches/0000-01-kquant-integer-dpas.patch):
+// ggml_cl_kq_type_index / ggml_cl_kq_mul_mat_shape (:781-812), the per-graph activation
+// conversion cache (:670-715), ggml_cl_mul_mat (:1135-1158) and supports_op (:615-652).
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace b200q {
+
+b200q_status fail(b200q_ctx *ctx, b200q_status st, const char *fmt, ...) {
+    if (ctx) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof(buf), fmt, ap);
+        va_end(ap);
+        ctx->last_error = buf;
+    }
+    return st;
+}
+
+// grow-only scratch (the reference's prealloc_* buffers never shrink either)
+b200q_status ws_reserve(b200q_ctx *ctx, Workspace *ws, size_t bytes) {
+    if (bytes <= ws->cap) return B200Q_OK;
+    if (ws->ptr) {
+        // the old block may still be in use by work already enqueued on the stream
+        B200Q_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        B200Q_CUDA(ctx, cudaFree(ws->ptr));
+        ws->ptr = nullptr;
+        ws->cap = 0;
+    }
+    const size_t want = (bytes + (1u << 20) - 1) & ~(size_t)((1u << 20) - 1);
+    cudaError_t e = cudaMalloc(&ws->ptr, want);
+    if (e != cudaSuccess) {
+        ws->ptr = nullptr;
+        return fail(ctx, B200Q_NO_MEMORY, "cudaMalloc(%zu): %s", want, cudaGetErrorString(e));
+    }
+    ws->cap = want;
+    count(ctx, "workspace_grow");
+    return B200Q_OK;
+}
+
+static bool is_contiguous_f32(const b200q_tensor *t) {
+    return t->type == B200Q_TYPE_F32 && t->nb[0] == sizeof(float);
+}
+
+// The gate of ggml_cl_kq_mul_mat_shape plus what the kernels' loads need.
+static b200q_status check_mul_mat(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1,
+                                  const b200q_tensor *dst, bool id_form) {
+    if (!src0 || !src1 || !dst) return fail(ctx, B200Q_INVALID, "null tensor");
+    TypeInfo ti;
+    if (!type_info(src0->type, &ti)) return fail(ctx, B200Q_UNSUPPORTED, "weight type %d", src0->type);
+    const int64_t K = src0->ne[0], M = src0->ne[1];
+    if (K <= 0 || K % ti.block) return fail(ctx, B200Q_UNSUPPORTED, "K=%lld not a multiple of %d", (long long)K, ti.block);
+    const size_t row_bytes = (size_t)(K / ti.block) * ti.bytes;
+    if (src0->nb[0] != (size_t)ti.bytes) return fail(ctx, B200Q_UNSUPPORTED, "weight nb[0]=%zu", src0->nb[0]);
+    if (src0->nb[1] < row_bytes || src0->nb[1] % 2) return fail(ctx, B200Q_UNSUPPORTED, "weight row stride %zu", src0->nb[1]);
+    if (!id_form && (src0->ne[2] != 1 || src0->ne[3] != 1))
+        return fail(ctx, B200Q_UNSUPPORTED, "3-D weights for MUL_MAT");
+    if (src0->ne[3] != 1) return fail(ctx, B200Q_UNSUPPORTED, "4-D weights");
+    if ((uintptr_t)src0->data % 2) return fail(ctx, B200Q_UNSUPPORTED, "weight address not 2-byte aligned");
+    if (!is_contiguous_f32(src1)) return fail(ctx, B200Q_UNSUPPORTED, "src1 must be f32 with unit element stride");
+    if (!is_contiguous_f32(dst)) return fail(ctx, B200Q_UNSUPPORTED, "dst must be f32 with unit element stride");
+    if (src1->ne[0] != K) return fail(ctx, B200Q_INVALID, "src1 ne[0]=%lld, K=%lld", (long long)src1->ne[0], (long long)K);
+    if (dst->ne[0] != M) return fail(ctx, B200Q_INVALID, "dst ne[0]=%lld, M=%lld", (long long)dst->ne[0], (long long)M);
+    if ((uintptr_t)src1->data % 16 || src1->nb[1] % 16 || src1->nb[2] % 16 || src1->nb[3] % 16)
+        return fail(ctx, B200Q_UNSUPPORTED, "src1 columns must be 16-byte aligned");
+    if ((uintptr_t)dst->data % 4 || dst->nb[1] % 4 || dst->nb[2] % 4 || dst->nb[3] % 4)
+        return fail(ctx, B200Q_UNSUPPORTED, "dst columns must be 4-byte aligned");
+    if (!src0->data || !src1->data || !dst->data) {
+        const bool empty = M == 0 || src1->ne[1] * src1->ne[2] * src1->ne[3] == 0;
+        if (!empty) return fail(ctx, B200Q_INVALID, "null data pointer");
+    }
+    return B200Q_OK;
+}
+
+// Quantize src1 once per graph: q/k/v and gate/up share their input (P01:670-688).
+static b200q_status get_activation(b200q_ctx *ctx, int form, const b200q_tensor *src1, ActView *out) {
+    ActKey key;
+    key.data = src1->data;
+    key.form = form;
+    key.gen = ctx->generation;
+    for (int i = 0; i < 4; ++i) { key.ne[i] = src1->ne[i]; key.nb[i] = src1->nb[i]; }
+    ActEntry *hit = nullptr;
+    for (auto &e : ctx->act_cache)
+        if (e.valid && e.key == key) { hit = &e; break; }
+    const int64_t K = src1->ne[0], N = src1->ne[1] * src1->ne[2] * src1->ne[3];
+    if (!hit) {
+        if (ctx->act_cache.size() < 4) ctx->act_cache.resize(4);
+        ActEntry &e = ctx->act_cache[ctx->act_next];
+        ctx->act_next = (ctx->act_next + 1) % ctx->act_cache.size();
+        e.valid = false;
+        b200q_status st;
+        if ((st = ws_reserve(ctx, &e.codes, (size_t)(N * K) + 64)) != B200Q_OK) return st;
+        const size_t sbytes = form == ACT_Q8_0 ? sizeof(uint16_t) * (size_t)(N * (K / 32)) : sizeof(float) * (size_t)(N * (K / 256));
+        if ((st = ws_reserve(ctx, &e.scales, sbytes + 64)) != B200Q_OK) return st;
+        if (form == ACT_Q8_256 && (st = ws_reserve(ctx, &e.sums, sizeof(int16_t) * (size_t)(N * (K / 32)) + 64)) != B200Q_OK)
+            return st;
+        if ((st = launch_quantize_act(ctx, form, src1, (int8_t *)e.codes.ptr, e.scales.ptr, (int16_t *)e.sums.ptr)) != B200Q_OK)
+            return st;
+        e.key = key;
+        e.valid = true;
+        hit = &e;
+    } else {
+        count(ctx, "act_cache_hit");
+    }
+    out->codes = (const int8_t *)hit->codes.ptr;
+    out->d16 = form == ACT_Q8_0 ? (const uint16_t *)hit->scales.ptr : nullptr;
+    out->d32 = form == ACT_Q8_256 ? (const float *)hit->scales.ptr : nullptr;
+    out->bsums = form == ACT_Q8_256 ? (const int16_t *)hit->sums.ptr : nullptr;
+    out->form = form;
+    out->K = K;
+    out->N = N;
+    return B200Q_OK;
+}
+
+// dst column c (flattened like src1) -> element offset; the kernels take a single column
+// stride, so a dst whose flattened columns are not evenly spaced is walked in runs
+static bool dst_uniform(const b200q_tensor *dst, int64_t *ldd) {
+    const size_t s1 = dst->nb[1];
+    const bool ok2 = dst->ne[2] == 1 || dst->nb[2] == s1 * (size_t)dst->ne[1];
+    const bool ok3 = dst->ne[3] == 1 || dst->nb[3] == s1 * (size_t)dst->ne[1] * (size_t)dst->ne[2];
+    *ldd = (int64_t)(s1 / sizeof(float));
+    return ok2 && ok3;
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+const char *b200q_version(void) { return "b200q 0.1 (sm_100a)"; }
+
+b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
+    if (!out) return B200Q_INVALID;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) return B200Q_CUDA_ERROR;
+    if (cudaSetDevice(device) != cudaSuccess) return B200Q_CUDA_ERROR;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return B200Q_CUDA_ERROR;
+    if (prop.major != 10) return B200Q_UNSUPPORTED;            // sm_100a kernels only
+    b200q_ctx *ctx = new b200q_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (stream) {
+        ctx->stream = (cudaStream_t)stream;
+    } else {
+        if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+            delete ctx;
+            return B200Q_CUDA_ERROR;
+        }
+        ctx->own_stream = true;
+    }
+    cudaEventCreate(&ctx->ev0);
+    cudaEventCreate(&ctx->ev1);
+    *out = ctx;
+    return B200Q_OK;
+}
+
+void b200q_free(b200q_ctx *ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (auto &e : ctx->act_cache) {
+        if (e.codes.ptr) cudaFree(e.codes.ptr);
+        if (e.scales.ptr) cudaFree(e.scales.ptr);
+        if (e.sums.ptr) cudaFree(e.sums.ptr);
+    }
+    if (ctx->flush_buf.ptr) cudaFree(ctx->flush_buf.ptr);
+    for (auto &w : ctx->moe_ws)
+        if (w.ptr) cudaFree(w.ptr);
+    if (ctx->ev0) cudaEventDestroy(ctx->ev0);
+    if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+const char *b200q_last_error(const b200q_ctx *ctx) { return ctx ? ctx->last_error.c_str() : ""; }
+
+b200q_status b200q_supports(const b200q_ctx *ctx, int op, const b200q_tensor *src0, const b200q_tensor *src1,
+                            const b200q_tensor *ids, const b200q_tensor *dst) {
+    (void)ctx;
+    if (op == B200Q_OP_MUL_MAT) {
+        b200q_status st = check_mul_mat(nullptr, src0, src1, dst, false);
+        if (st != B200Q_OK) return st;
+        if (dst->ne[1] != src1->ne[1] || dst->ne[2] != src1->ne[2] || dst->ne[3] != src1->ne[3]) return B200Q_INVALID;
+        return B200Q_OK;
+    }
+    if (op == B200Q_OP_MUL_MAT_ID) {
+        if (!ids || ids->type != B200Q_TYPE_I32) return B200Q_UNSUPPORTED;
+        return check_mul_mat(nullptr, src0, src1, dst, true);
+    }
+    return B200Q_UNSUPPORTED;
+}
+
+b200q_status b200q_graph_begin(b200q_ctx *ctx) {
+    if (!ctx) return B200Q_INVALID;
+    ++ctx->generation;
+    return B200Q_OK;
+}
+
+b200q_status b200q_mul_mat(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1, b200q_tensor *dst) {
+    if (!ctx) return B200Q_INVALID;
+    b200q_status st = check_mul_mat(ctx, src0, src1, dst, false);
+    if (st != B200Q_OK) return st;
+    if (dst->ne[1] != src1->ne[1] || dst->ne[2] != src1->ne[2] || dst->ne[3] != src1->ne[3])
+        return fail(ctx, B200Q_INVALID, "dst shape does not match src1");
+    B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+    TypeInfo ti;
+    type_info(src0->type, &ti);
+    const int64_t K = src0->ne[0], M = src0->ne[1];
+    const int64_t N = src1->ne[1] * src1->ne[2] * src1->ne[3];
+    if (M == 0 || N == 0) return B200Q_OK;
+    ActView act;
+    if ((st = get_activation(ctx, ti.act_form, src1, &act)) != B200Q_OK) return st;
+    int64_t ldd;
+    const bool uniform = dst_uniform(dst, &ldd);
+    // decode widths go to the GEMV; wider products walk it in groups of eight columns
+    // until the tensor-core GEMM takes them
+    const int64_t run = uniform ? N : dst->ne[1];     // columns that share one stride
+    for (int64_t c0 = 0; c0 < N; c0 += run) {
+        const int64_t c23 = c0 / dst->ne[1], c2 = c23 % dst->ne[2], c3 = c23 / dst->ne[2];
+        float *base = uniform ? (float *)dst->data
+                              : (float *)((uint8_t *)dst->data + c2 * dst->nb[2] + c3 * dst->nb[3]);
+        if (N > 8) count(ctx, "mul_mat_gemv_chunks");
+        for (int64_t c = 0; c < run; c += 8) {
+            const int nc = (int)(run - c < 8 ? run - c : 8);
+            st = launch_gemv(ctx, src0->type, src0->data, src0->nb[1], M, K, act, c0 + c, nc, base + c * ldd, ldd);
+            if (st != B200Q_OK) return st;
+        }
+    }
+    return B200Q_OK;
+}
+
+b200q_status b200q_mul_mat_id(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1,
+                              const b200q_tensor *ids, b200q_tensor *dst) {
+    (void)src0; (void)src1; (void)ids; (void)dst;
+    return fail(ctx, B200Q_UNSUPPORTED, "MUL_MAT_ID not built yet");
+}
+
+// ---- buffers and copies --------------------------------------------------------------
+
+b200q_status b200q_buffer_alloc(b200q_ctx *ctx, size_t bytes, void **dev_ptr) {
+    if (!ctx || !dev_ptr) return B200Q_INVALID;
+    *dev_ptr = nullptr;
+    B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaError_t e = cudaMalloc(dev_ptr, bytes ? bytes : 1);
+    if (e != cudaSuccess) return fail(ctx, B200Q_NO_MEMORY, "cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+    return B200Q_OK;
+}
+
+b200q_status b200q_buffer_free(b200q_ctx *ctx, void *dev_ptr) {
+    if (!ctx) return B200Q_INVALID;
+    if (!dev_ptr) return B200Q_OK;
+    B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+    B200Q_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    B200Q_CUDA(ctx, cudaFree(dev_ptr));
+    return B200Q_OK;
+}
+
+b200q_status b200q_tensor_set(b200q_ctx *ctx, void *dev_dst, const void *host_src, size_t bytes) {
+    if (!ctx || (bytes && (!dev_dst || !host_src))) return B200Q_INVALID;
+    B200Q_CUDA(ctx, cudaMemcpyAsync(dev_dst, host_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return B200Q_OK;
+}
+
+b200q_status b200q_tensor_get(b200q_ctx *ctx, void *host_dst, const void *dev_src, size_t bytes) {
+    if (!ctx || (bytes && (!host_dst || !dev_src))) return B200Q_INVALID;
+    B200Q_CUDA(ctx, cudaMemcpyAsync(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return B200Q_OK;
+}
+
+b200q_status b200q_tensor_copy(b200q_ctx *ctx, void *dev_dst, const void *dev_src, size_t bytes) {
+    if (!ctx || (bytes && (!dev_dst || !dev_src))) return B200Q_INVALID;
+    B200Q_CUDA(ctx, cudaMemcpyAsync(dev_dst, dev_src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return B200Q_OK;
+}
+
+b200q_status b200q_synchronize(b200q_ctx *ctx) {
+    if (!ctx) return B200Q_INVALID;
+    B200Q_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return B200Q_OK;
+}
+
+b200q_status b200q_host_alloc(size_t bytes, void **host_ptr) {
+    if (!host_ptr) return B200Q_INVALID;
+    return cudaMallocHost(host_ptr, bytes ? bytes : 1) == cudaSuccess ? B200Q_OK : B200Q_NO_MEMORY;
+}
+
+b200q_status b200q_host_free(void *host_ptr) {
+    return (!host_ptr || cudaFreeHost(host_ptr) == cudaSuccess) ? B200Q_OK : B200Q_CUDA_ERROR;
+}
+
+// ---- stats, timing --------------------------------------------------------------------
+
+const char *b200q_stats(b200q_ctx *ctx) {
+    if (!ctx) return "";
+    ctx->stats_text.clear();
+    for (auto &kv : ctx->stats) ctx->stats_text += kv.first + "\t" + std::to_string(kv.second) + "\n";
+    return ctx->stats_text.c_str();
+}
+
+void b200q_stats_reset(b200q_ctx *ctx) {
+    if (ctx) ctx->stats.clear();
+}
+
+b200q_status b200q_timer_start(b200q_ctx *ctx) {
+    if (!ctx) return B200Q_INVALID;
+    B200Q_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+    return B200Q_OK;
+}
+
+b200q_status b200q_timer_stop(b200q_ctx *ctx, float *elapsed_ms) {
+    if (!ctx || !elapsed_ms) return B200Q_INVALID;
+    B200Q_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+    B200Q_CUDA(ctx, cudaEventSynchronize(ctx->ev1));
+    B200Q_CUDA(ctx, cudaEventElapsedTime(elapsed_ms, ctx->ev0, ctx->ev1));
+    return B200Q_OK;
+}
+
+b200q_status b200q_flush_l2(b200q_ctx *ctx) {
+    if (!ctx) return B200Q_INVALID;
+    const size_t bytes = 256u << 20;                     // twice the 126 MB L2
+    b200q_status st = ws_reserve(ctx, &ctx->flush_buf, bytes);
+    if (st != B200Q_OK) return st;
+    B200Q_CUDA(ctx, cudaMemsetAsync(ctx->flush_buf.ptr, 0, bytes, ctx->stream));
+    return B200Q_OK;
+}
+
+// ---- debug views ----------------------------------------------------------------------
+
+b200q_status b200q_debug_quantize_act(b200q_ctx *ctx, int weight_type, const b200q_tensor *src1, void *dev_codes,
+                                      void *dev_scales, void *dev_sums) {
+    if (!ctx || !src1 || !dev_codes || !dev_scales) return B200Q_INVALID;
+    TypeInfo ti;
+    if (!type_info(weight_type, &ti)) return fail(ctx, B200Q_UNSUPPORTED, "weight type %d", weight_type);
+    if (!is_contiguous_f32(src1) || src1->ne[0] % ti.block) return fail(ctx, B200Q_UNSUPPORTED, "src1 layout");
+    if (ti.act_form == ACT_Q8_256 && !dev_sums) return B200Q_INVALID;
+    return launch_quantize_act(ctx, ti.act_form, src1, (int8_t *)dev_codes, dev_scales, (int16_t *)dev_sums);
+}
+
+b200q_status b200q_debug_dequantize(b200q_ctx *ctx, const b200q_tensor *src0, float *dev_out) {
+    if (!ctx || !src0 || !dev_out) return B200Q_INVALID;
+    TypeInfo ti;
+    if (!type_info(src0->type, &ti) || src0->ne[0] % ti.block) return fail(ctx, B200Q_UNSUPPORTED, "weight layout");
+    return launch_dequantize(ctx, src0->type, src0->data, src0->ne[1] * src0->ne[2] * src0->ne[3], src0->ne[0],
+                             src0->nb[1], dev_out);
+}
+
+}  // extern "C"

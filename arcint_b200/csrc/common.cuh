@@ -1,0 +1,130 @@
+// common.cuh -- shared host/device declarations of the b200q library (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/b200q.h"
+
+#define QK   32
+#define QK_K 256
+
+namespace b200q {
+
+// ---- block formats ------------------------------------------------------------------
+
+struct TypeInfo {
+    int    block;        // weights per block
+    int    bytes;        // bytes per block
+    int    act_form;     // 0: per-32 activation (fp16 scale), 1: per-256 (f32 scale + sums)
+    const char *name;
+};
+
+__host__ __device__ inline bool type_info(int type, TypeInfo *ti) {
+    switch (type) {
+        case B200Q_TYPE_Q4_0:   *ti = { 32, 18, 0, "q4_0" };    return true;
+        case B200Q_TYPE_Q8_0:   *ti = { 32, 34, 0, "q8_0" };    return true;
+        case B200Q_TYPE_Q4_K:   *ti = { 256, 144, 1, "q4_K" };  return true;
+        case B200Q_TYPE_Q6_K:   *ti = { 256, 210, 1, "q6_K" };  return true;
+        case B200Q_TYPE_IQ4_XS: *ti = { 256, 136, 1, "iq4_xs" }; return true;
+        default: return false;
+    }
+}
+
+enum { ACT_Q8_0 = 0, ACT_Q8_256 = 1 };
+
+// Quantized activation as the kernels read it: column c of K values at
+//   codes  + c*K            int8
+//   d16    + c*(K/32)       fp16 bits, per-32 form
+//   d32    + c*(K/256)      f32,       per-256 form
+//   bsums  + c*(K/32)       int16 sums of each 32 codes, per-256 form
+struct ActView {
+    const int8_t   *codes;
+    const uint16_t *d16;
+    const float    *d32;
+    const int16_t  *bsums;
+    int             form;
+    int64_t         K;
+    int64_t         N;
+};
+
+// ---- context ------------------------------------------------------------------------
+
+struct Workspace {
+    void  *ptr = nullptr;
+    size_t cap = 0;
+};
+
+struct ActKey {
+    const void *data;
+    int64_t ne[4];
+    size_t  nb[4];
+    int     form;
+    uint64_t gen;
+    bool operator==(const ActKey &o) const {
+        if (data != o.data || form != o.form || gen != o.gen) return false;
+        for (int i = 0; i < 4; ++i) if (ne[i] != o.ne[i] || nb[i] != o.nb[i]) return false;
+        return true;
+    }
+};
+
+struct ActEntry {
+    ActKey    key;
+    Workspace codes, scales, sums;
+    bool      valid = false;
+};
+
+struct RouteEntry;
+
+}  // namespace b200q
+
+struct b200q_ctx {
+    int          device = 0;
+    cudaStream_t stream = nullptr;
+    bool         own_stream = false;
+    int          sm_count = 148;
+    uint64_t     generation = 1;
+    std::string  last_error;
+    std::string  stats_text;
+    std::map<std::string, uint64_t> stats;
+    // quantized-activation cache: a few entries, reused round-robin
+    std::vector<b200q::ActEntry> act_cache;
+    size_t       act_next = 0;
+    b200q::Workspace flush_buf;
+    b200q::Workspace moe_ws[8];
+    std::vector<b200q::RouteEntry *> routes;
+    cudaEvent_t  ev0 = nullptr, ev1 = nullptr;
+    void        *tp = nullptr;   // tensor/expert-parallel state (tp.cu)
+    void        *gemm = nullptr; // tcgen05 GEMM state (gemm_tc.cu)
+};
+
+namespace b200q {
+
+b200q_status fail(b200q_ctx *ctx, b200q_status st, const char *fmt, ...);
+b200q_status ws_reserve(b200q_ctx *ctx, Workspace *ws, size_t bytes);
+inline void  count(b200q_ctx *ctx, const std::string &key) { ++ctx->stats[key]; }
+
+#define B200Q_CUDA(ctx, expr)                                                                       \
+    do {                                                                                            \
+        cudaError_t e_ = (expr);                                                                    \
+        if (e_ != cudaSuccess)                                                                      \
+            return b200q::fail((ctx), B200Q_CUDA_ERROR, "%s: %s (%s:%d)", #expr, cudaGetErrorString(e_), \
+                               __FILE__, __LINE__);                                                 \
+    } while (0)
+
+// quantize.cu
+b200q_status launch_quantize_act(b200q_ctx *ctx, int form, const b200q_tensor *src1, int8_t *codes, void *scales,
+                                 int16_t *bsums);
+b200q_status launch_dequantize(b200q_ctx *ctx, int type, const void *w, int64_t M, int64_t K, size_t row_stride,
+                               float *out);
+
+// gemv.cu: dst[m + c*ldd] for c < ncols (<= 8), rows [0, M)
+b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
+                         const ActView &act, int64_t col0, int ncols, float *dst, int64_t ldd);
+
+}  // namespace b200q

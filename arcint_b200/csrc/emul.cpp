@@ -1,0 +1,100 @@
+// emul.cpp -- host build of the kernels' per-lane text, for device-free tests.
+//
+// The GEMV's lane code (gemv_core.cuh), the block decoders and the bit tricks
+// (formats.cuh) are written once as host+device text. This file compiles them with g++
+// and replays the kernel's loop structure (row groups, stages, 32 lanes) on the CPU, so
+// every index computation and byte shuffle can be checked without a GPU -- the method
+// of the reference's tests/test-opencl-kq-i8.cpp (marfrit/arcint contrib/llama.cpp/
+// patches/0000-09-moe-routing-gemm-tiles.patch:1095-1697), which compiles its kernel
+// helpers as C++. Not part of the product library.
+#include <stdint.h>
+#include <string.h>
+
+#include <vector>
+
+#include "gemv_core.cuh"
+
+using namespace b200q;
+
+template <int TYPE, int NC, int R>
+static void emul_gemv_t(const uint8_t *W, size_t row_stride, int64_t M, int64_t K, const GemvAct &act, float *dst,
+                        int64_t ldd) {
+    typedef GemvFmt<TYPE> F;
+    typedef GemvStage<TYPE> S;
+    const int64_t nblk = K / F::BLK_W, row_bytes = nblk * F::BLK_B;
+    const int64_t nstages = (nblk + F::STAGE_BLOCKS - 1) / F::STAGE_BLOCKS;
+    const int64_t n_rg = (M + R - 1) / R;
+    std::vector<uint32_t> slot((size_t)R * S::SLOT / 4);
+    for (int64_t rg = 0; rg < n_rg; ++rg) {
+        float acc[32][R][NC];
+        memset(acc, 0, sizeof(acc));
+        for (int64_t s = 0; s < nstages; ++s) {
+            const int64_t off = s * S::BYTES;
+            const int bytes = (int)(row_bytes - off < S::BYTES ? row_bytes - off : S::BYTES);
+            memset(slot.data(), 0xA5, slot.size() * 4);     // stale ring contents must not matter
+            const uint32_t *srow[R];
+            for (int r = 0; r < R; ++r) {
+                const int64_t row = rg * R + r < M ? rg * R + r : M - 1;
+                memcpy((uint8_t *)slot.data() + r * S::SLOT, W + (size_t)row * row_stride + off, (size_t)bytes);
+                srow[r] = slot.data() + r * S::SLOT / 4;
+            }
+            for (int lane = 0; lane < 32; ++lane) gemv_lane_stage<TYPE, NC, R>(srow, lane, s, nblk, act, acc[lane]);
+        }
+        for (int r = 0; r < R; ++r)
+            for (int c = 0; c < NC; ++c) {
+                float v[32];
+                for (int l = 0; l < 32; ++l) v[l] = acc[l][r][c];
+                for (int o = 16; o > 0; o >>= 1)            // the shuffle butterfly's order
+                    for (int l = 0; l < o; ++l) v[l] += v[l + o];
+                if (rg * R + r < M) dst[rg * R + r + c * ldd] = v[0];
+            }
+    }
+}
+
+template <int TYPE, int NC>
+static void emul_gemv_r(int R, const uint8_t *W, size_t rs, int64_t M, int64_t K, const GemvAct &a, float *d, int64_t ldd) {
+    if (R == 1) emul_gemv_t<TYPE, NC, 1>(W, rs, M, K, a, d, ldd);
+    else        emul_gemv_t<TYPE, NC, 2>(W, rs, M, K, a, d, ldd);
+}
+
+template <int TYPE>
+static int emul_gemv_nc(int nc, int R, const uint8_t *W, size_t rs, int64_t M, int64_t K, const GemvAct &a, float *d,
+                        int64_t ldd) {
+    switch (nc) {
+    case 1: emul_gemv_r<TYPE, 1>(R, W, rs, M, K, a, d, ldd); return 0;
+    case 2: emul_gemv_r<TYPE, 2>(R, W, rs, M, K, a, d, ldd); return 0;
+    case 3: emul_gemv_r<TYPE, 3>(R, W, rs, M, K, a, d, ldd); return 0;
+    case 5: emul_gemv_r<TYPE, 5>(R, W, rs, M, K, a, d, ldd); return 0;
+    case 8: emul_gemv_r<TYPE, 8>(R, W, rs, M, K, a, d, ldd); return 0;
+    }
+    return -1;
+}
+
+extern "C" {
+
+int emul_gemv(int type, const uint8_t *W, size_t row_stride, int64_t M, int64_t K, const int8_t *xq,
+              const uint16_t *d16, const float *d32, int ncols, int R, float *dst, int64_t ldd) {
+    GemvAct a;
+    a.q = xq;
+    a.d16 = d16;
+    a.d32 = d32;
+    a.K = K;
+    switch (type) {
+    case B200Q_TYPE_Q4_0:   return emul_gemv_nc<B200Q_TYPE_Q4_0>(ncols, R, W, row_stride, M, K, a, dst, ldd);
+    case B200Q_TYPE_Q8_0:   return emul_gemv_nc<B200Q_TYPE_Q8_0>(ncols, R, W, row_stride, M, K, a, dst, ldd);
+    case B200Q_TYPE_Q4_K:   return emul_gemv_nc<B200Q_TYPE_Q4_K>(ncols, R, W, row_stride, M, K, a, dst, ldd);
+    case B200Q_TYPE_Q6_K:   return emul_gemv_nc<B200Q_TYPE_Q6_K>(ncols, R, W, row_stride, M, K, a, dst, ldd);
+    case B200Q_TYPE_IQ4_XS: return emul_gemv_nc<B200Q_TYPE_IQ4_XS>(ncols, R, W, row_stride, M, K, a, dst, ldd);
+    }
+    return -1;
+}
+
+void emul_dequantize_row(int type, const uint8_t *row, int64_t K, float *out) {
+    for (int64_t i = 0; i < K; ++i) out[i] = decode_weight(type, row, i);
+}
+
+uint32_t emul_iq4nl_lookup4(uint32_t idx) { return iq4nl_lookup4(idx); }
+uint32_t emul_nib_minus8(uint32_t t) { return nib_minus8(t); }
+uint32_t emul_six_minus32(uint32_t t) { return six_minus32(t); }
+
+}

@@ -1,0 +1,144 @@
+// formats.cuh -- device-side decoders of the five GGUF block formats.
+//
+// Layouts follow ggml's block structs as the reference kernels read them
+// (marfrit/arcint, contrib/llama.cpp/patches; line numbers are lines of the .patch):
+//   Q4_0   18 B: fp16 d, 16 B nibbles; byte j low -> weight j, high -> j+16; w = d (n - 8)
+//          (0099-opencl-q4_0-q8_0-int8-gemm.patch:323-326)
+//   Q8_0   34 B: fp16 d, 32 int8; w = d q                      (0099-...:575-576)
+//   Q4_K  144 B: fp16 d, fp16 dmin, 12 B of 6-bit scales/mins, 128 B nibbles; group g of
+//          32 bytes: low -> sub-block 2g, high -> 2g+1; w = d sc q - dmin m
+//          (0000-01-kquant-integer-dpas.patch:1562-1576, 3735-3739)
+//   Q6_K  210 B: ql[128], qh[64], int8 scales[16], fp16 d; w = d sc (q - 32)
+//          (0000-01-...:1789-1794, 3798-3802, 3849-3860)
+//   IQ4_XS 136 B: fp16 d, u16 scales_h, scales_l[4], 128 B nibbles indexing kvalues_iq4nl;
+//          w = d (ls - 32) kv[n]                                (0000-01-...:2143-2145, 2287-2298)
+#pragma once
+
+#include "intrin.cuh"
+#include "../../include/b200q.h"
+
+namespace b200q {
+
+B200Q_HD float half_bits_to_float(uint16_t h) { return hd_half_bits(h); }
+
+// one IEEE rounding per operation on both sides (no fused multiply-add), so the decode is
+// bit-identical to ggml's dequantize_row_* and to gguf-py
+B200Q_HD float mul_rn(float a, float b) {
+#ifdef __CUDA_ARCH__
+    return __fmul_rn(a, b);
+#else
+    volatile float r = a * b;
+    return r;
+#endif
+}
+B200Q_HD float sub_rn(float a, float b) {
+#ifdef __CUDA_ARCH__
+    return __fsub_rn(a, b);
+#else
+    volatile float r = a - b;
+    return r;
+#endif
+}
+
+B200Q_HD int kvalue_iq4nl(int n) {
+    const int8_t kv[16] = { -127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113 };
+    return kv[n & 15];
+}
+
+// 6-bit scale and min of Q4_K sub-block j from the 12 scale bytes held as three words
+B200Q_HD void q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int j, int *sc, int *m) {
+    const int sh = 8 * (j & 3);
+    if (j < 4) {
+        *sc = (s0 >> sh) & 63;
+        *m  = (s1 >> sh) & 63;
+    } else {
+        const uint32_t q8 = (s2 >> sh) & 0xFF, lo = (s0 >> sh) & 0xFF, hi = (s1 >> sh) & 0xFF;
+        *sc = (q8 & 0xF) | ((lo >> 6) << 4);
+        *m  = (q8 >> 4) | ((hi >> 6) << 4);
+    }
+}
+
+// IQ4_XS sub-block scale in 0..63 from scales_h and the four scales_l bytes as one word
+B200Q_HD int iq4xs_ls(uint32_t scales_h, uint32_t scales_l, int p) {
+    return ((scales_l >> (4 * p)) & 0xF) | (((scales_h >> (2 * p)) & 3) << 4);
+}
+
+// four nibble codes n (one per byte, 0..15) -> four int8 bytes n - 8, no carry between bytes
+B200Q_HD uint32_t nib_minus8(uint32_t t) { return (t + 0x78787878u) ^ 0x80808080u; }
+// four 6-bit codes (one per byte, 0..63) -> int8 bytes q - 32
+B200Q_HD uint32_t six_minus32(uint32_t t) { return (t + 0x60606060u) ^ 0x80808080u; }
+
+// kvalues_iq4nl lookup of four indices (one per byte, 0..15) with byte permutes: the table
+// lives in four registers, PRMT picks from eight bytes at a time, bit 3 chooses the half
+B200Q_HD uint32_t iq4nl_lookup4(uint32_t idx) {
+    const uint32_t t0 = 0xBFAD9881u;   // -127,-104,-83,-65 (little-endian bytes)
+    const uint32_t t1 = 0xF6EADDCFu;   // -49,-35,-22,-10
+    const uint32_t t2 = 0x26190D01u;   // 1,13,25,38
+    const uint32_t t3 = 0x71594535u;   // 53,69,89,113
+    // selector: one nibble per output byte, low three bits of each index
+    const uint32_t packed = idx | (idx >> 4);                      // bytes 0,2 hold (i1 i0), (i3 i2)
+    const uint32_t sel = hd_byte_perm(packed, 0, 0x4420) & 0x7777u; // 16-bit selector
+    const uint32_t lo = hd_byte_perm(t0, t1, sel);
+    const uint32_t hi = hd_byte_perm(t2, t3, sel);
+    const uint32_t msk = ((idx >> 3) & 0x01010101u) * 0xFFu;       // 0xFF where index >= 8
+    return (lo & ~msk) | (hi & msk);
+}
+
+// Generic, slow, exact f32 decode of weight i of a row (used by the debug dequantizer
+// and as the spec the fast kernels are tested against). One rounding per multiply,
+// like ggml's dequantize_row_* and gguf-py.
+__host__ __device__ inline float decode_weight(int type, const uint8_t *row, int64_t i) {
+    switch (type) {
+    case B200Q_TYPE_Q4_0: {
+        const uint8_t *b = row + (i / 32) * 18;
+        const int j = (int)(i % 32);
+        const float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
+        const int n = j < 16 ? (b[2 + j] & 0xF) : (b[2 + j - 16] >> 4);
+        return mul_rn(d, (float)(n - 8));
+    }
+    case B200Q_TYPE_Q8_0: {
+        const uint8_t *b = row + (i / 32) * 34;
+        const float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
+        return mul_rn((float)(int8_t)b[2 + i % 32], d);
+    }
+    case B200Q_TYPE_Q4_K: {
+        const uint8_t *b = row + (i / 256) * 144;
+        const int r = (int)(i % 256), j = r / 32, t = r % 32;
+        const float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
+        const float dmin = half_bits_to_float((uint16_t)(b[2] | (b[3] << 8)));
+        const uint8_t *s = b + 4;
+        const uint32_t s0 = s[0] | (s[1] << 8) | (s[2] << 16) | ((uint32_t)s[3] << 24);
+        const uint32_t s1 = s[4] | (s[5] << 8) | (s[6] << 16) | ((uint32_t)s[7] << 24);
+        const uint32_t s2 = s[8] | (s[9] << 8) | (s[10] << 16) | ((uint32_t)s[11] << 24);
+        int sc, m;
+        q4k_scale_min(s0, s1, s2, j, &sc, &m);
+        const uint8_t qb = b[16 + 32 * (j / 2) + t];
+        const int q = (j & 1) ? (qb >> 4) : (qb & 0xF);
+        return sub_rn(mul_rn(mul_rn(d, (float)sc), (float)q), mul_rn(dmin, (float)m));
+    }
+    case B200Q_TYPE_Q6_K: {
+        const uint8_t *b = row + (i / 256) * 210;
+        const int r = (int)(i % 256), n = r / 128, p = (r % 128) / 32, t = r % 32;
+        const uint8_t l = b[64 * n + 32 * (p & 1) + t];
+        const uint8_t h = b[128 + 32 * n + t];
+        const int q = ((p & 2) ? (l >> 4) : (l & 0xF)) | (((h >> (2 * p)) & 3) << 4);
+        const float d = half_bits_to_float((uint16_t)(b[208] | (b[209] << 8)));
+        const int sc = (int8_t)b[192 + 8 * n + 2 * p + (t >= 16)];
+        return mul_rn(mul_rn(d, (float)sc), (float)(q - 32));
+    }
+    case B200Q_TYPE_IQ4_XS: {
+        const uint8_t *b = row + (i / 256) * 136;
+        const int r = (int)(i % 256), p = r / 32, t = r % 32;
+        const float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
+        const uint32_t sh = b[2] | (b[3] << 8);
+        const uint32_t sl = b[4] | (b[5] << 8) | (b[6] << 16) | ((uint32_t)b[7] << 24);
+        const int ls = iq4xs_ls(sh, sl, p);
+        const uint8_t qb = b[8 + 16 * p + (t & 15)];
+        const int n = t < 16 ? (qb & 0xF) : (qb >> 4);
+        return mul_rn(mul_rn(d, (float)(ls - 32)), (float)kvalue_iq4nl(n));
+    }
+    }
+    return 0.f;
+}
+
+}  // namespace b200q

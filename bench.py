@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""bench.py -- the path's headline measurement on B200.
+
+Default workload ("decode_gemv", BASELINE config 2): the decode GEMV over a Llama-7B-shaped
+set of quantized weights -- Q4_K gate/up 11008x4096, Q4_K down 4096x11008, Q6_K LM head
+32000x4096 -- at batch 1, 2, 4 and 8 f32 activation columns. One step = all twelve
+products once, each through b200q_mul_mat (activation quantize + GEMV).
+
+  value      algorithmic GB/s of the whole step with inputs resident in HBM
+  roofline   the GEMV kernel alone (activation already quantized), CUDA events on the
+             launching stream, against the measured HBM copy peak
+  e2e        the same step through the C ABI with HOST buffers: pinned f32 activations
+             copied in and f32 results copied out inside the timed region (weights are
+             resident, as after ggml's set_tensor at model load)
+  cpu_baseline  the CPU oracle (a port of the reference math, not ggml) on the host cores
+
+Weights rotate over distinct device copies whose total footprint is several times the
+126 MB L2, so no product finds its weights in cache. Under torchrun each rank runs a
+replica (the decode config is single-GPU in BASELINE; it does not shard).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "quant mul_mat prefill TFLOPS + decode GEMV HBM GB/s (% roofline), 1/2/4/8 GPU"
+L2_BYTES = 126 << 20
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs, copy read+write)"
+    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# ---- the decode workload -------------------------------------------------------------------
+
+def decode_shapes():
+    import arcint_b200 as A
+    return [("gate_up", A.Q4_K, 11008, 4096), ("down", A.Q4_K, 4096, 11008), ("lm_head", A.Q6_K, 32000, 4096)]
+
+
+BATCHES = (1, 2, 4, 8)
+
+
+def algo_bytes(t, m, k, n):
+    import arcint_b200 as A
+    return m * A.row_bytes(t, k) + 4 * n * (k + m)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device, self.rows, self.proc = device, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def build_decode_inputs(seed=0x5EED0001):
+    """Seeded synthetic tensors of config 2: N(0,0.02) weights quantized on the host by the
+    oracle's quantizers (stand-ins for ggml's K-quant quantizers), N(0,1) activations."""
+    import oracle as O
+    out = []
+    for i, (name, t, m, k) in enumerate(decode_shapes()):
+        w = O.quantize(t, O.fill_normal(m * k, seed + i, 0.02).reshape(m, k))
+        out.append((name, t, m, k, w))
+    x = {k: O.fill_normal(8 * k, seed + 100 + k, 1.0).reshape(8, k) for k in (4096, 11008)}
+    return out, x
+
+
+def run_reference(args, rank):
+    """The CPU arm: the oracle (a port of the reference math; ggml's CPU backend is not
+    in this image) on all host cores, same workload, metric and unit."""
+    if rank != 0:
+        return
+    import oracle as O
+    mats, xs = build_decode_inputs()
+    total = sum(algo_bytes(t, m, k, n) for _, t, m, k, _ in mats for n in BATCHES)
+
+    def step():
+        for _, t, m, k, w in mats:
+            for n in BATCHES:
+                O.mul_mat(t, w, k, xs[k][:n])
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    v = total / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "decode_gemv: Q4_K 11008x4096 + Q4_K 4096x11008 + Q6_K 32000x4096, batch 1/2/4/8"},
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+                         "sample": "the full step (12 products) per timed step"},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def run_gpu(args, rank, world):
+    import arcint_b200 as A
+    import oracle as O
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist_mod
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        dist_mod.init_process_group("nccl")
+        dist = dist_mod
+    device = int(os.environ.get("LOCAL_RANK", 0)) if world > 1 else 0
+    ctx = A.Context(device)
+    mats, xs = build_decode_inputs()
+
+    # device copies: each shape rotates over enough copies to exceed 4x L2
+    dev = []
+    for name, t, m, k, w in mats:
+        copies = max(2, -(-4 * L2_BYTES // w.nbytes))
+        first = ctx.upload(w)
+        ptrs = [first]
+        for _ in range(copies - 1):
+            p = ctx.alloc(w.nbytes)
+            ctx.copy(p, first, w.nbytes)
+            ptrs.append(p)
+        dev.append((name, t, m, k, ptrs))
+    ctx.sync()
+    dx = {k: ctx.upload(v) for k, v in xs.items()}
+    max_m = max(m for _, _, m, _ in decode_shapes())
+    dy = ctx.alloc(8 * max_m * 4)
+    hx = {k: A.binding.PinnedArray((8, k), np.float32) for k in xs}
+    for k in xs:
+        hx[k].array[:] = xs[k]
+    hy = A.binding.PinnedArray((8, max_m), np.float32)
+
+    products = [(name, t, m, k, ptrs, n) for name, t, m, k, ptrs in dev for n in BATCHES]
+    total_bytes = sum(algo_bytes(t, m, k, n) for _, t, m, k, _, n in products)
+    counter = [0]
+
+    def step_device():
+        for name, t, m, k, ptrs, n in products:
+            counter[0] += 1
+            ctx.graph_begin()
+            ctx.mul_mat(A.Tensor.weights(t, ptrs[counter[0] % len(ptrs)], k, m), A.Tensor.f32(dx[k], [k, n]),
+                        A.Tensor.f32(dy, [m, n]))
+
+    def step_e2e():
+        for name, t, m, k, ptrs, n in products:
+            counter[0] += 1
+            ctx.graph_begin()
+            ctx.set_async(dx[k], hx[k].ptr, 4 * n * k)
+            ctx.mul_mat(A.Tensor.weights(t, ptrs[counter[0] % len(ptrs)], k, m), A.Tensor.f32(dx[k], [k, n]),
+                        A.Tensor.f32(dy, [m, n]))
+            ctx.get_async(hy.ptr, dy, 4 * n * m)
+            ctx.sync()                      # the caller reads the result before the next product
+
+    def barrier():
+        ctx.sync()
+        if dist:
+            dist.barrier()
+
+    def timed(fn, steps):
+        barrier()
+        ctx.timer_start()
+        for _ in range(steps):
+            fn()
+        ms = ctx.timer_stop()
+        if dist:
+            import torch
+            tt = torch.tensor([ms], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        return ms
+
+    # parity spot check before timing: sampled rows of one product against the oracle
+    name, t, m, k, ptrs = dev[0]
+    ctx.graph_begin()
+    ctx.mul_mat(A.Tensor.weights(t, ptrs[0], k, m), A.Tensor.f32(dx[k], [k, 8]), A.Tensor.f32(dy, [m, 8]))
+    got = ctx.download(dy, (8, m), np.float32)
+    rows = np.arange(0, m, max(1, m // 64))
+    ref = O.mul_mat_f64(t, mats[0][4][rows], k, xs[k], True)
+    floor = 1e-2 * np.abs(ref).max(axis=-1, keepdims=True)
+    err = float((np.abs(got[:, rows] - ref) / np.maximum(np.abs(ref), floor)).max())
+    if not err < 1e-3:
+        raise SystemExit("bench: parity check failed before timing (max rel err %.3e)" % err)
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    sampler = ClockSampler(device)
+    if rank == 0:
+        sampler.start()
+    ctx.stats_reset()
+    ms = timed(step_device, args.steps)
+    stats = ctx.stats()
+    launches = sum(v for key, v in stats.items() if key.startswith("gemv_") or key.startswith("quantize_"))
+    ms_step = ms / args.steps
+    value = world * total_bytes / (ms_step * 1e-3) / 1e9
+
+    # end to end through the C ABI with host buffers
+    for _ in range(3):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    e2e = world * total_bytes / (ms_e2e * 1e-3) / 1e9
+    h2d = sum(4 * n * k for _, _, _, k, _, n in products)
+    d2h = sum(4 * n * m for _, _, m, _, _, n in products)
+
+    # roofline of the dominant kernel: the GEMV alone (activation quantized once per graph)
+    peak, peak_src = measured_peaks()
+    detail, tot_b, tot_ms = [], 0, 0.0
+    reps = 40
+    for name, t, m, k, ptrs, n in products:
+        W = [A.Tensor.weights(t, p, k, m) for p in ptrs]
+        X, Y = A.Tensor.f32(dx[k], [k, n]), A.Tensor.f32(dy, [m, n])
+        ctx.graph_begin()
+        for i in range(len(ptrs) + 3):
+            ctx.mul_mat(W[i % len(W)], X, Y)
+        ctx.sync()
+        ctx.timer_start()
+        for i in range(reps):
+            ctx.mul_mat(W[i % len(W)], X, Y)
+        kms = ctx.timer_stop() / reps
+        b = algo_bytes(t, m, k, n)
+        detail.append({"shape": "%s %dx%d" % (O.TYPE_NAMES[t], m, k), "batch": n, "us": round(kms * 1e3, 2),
+                       "gbs": round(b / (kms * 1e-3) / 1e9, 1), "frac": round(b / (kms * 1e-3) / 1e9 / peak, 3)})
+        tot_b += b
+        tot_ms += kms
+    achieved = tot_b / (tot_ms * 1e-3) / 1e9
+
+    cpu = None
+    if rank == 0:
+        t0 = time.perf_counter()
+        reps_cpu = 0
+        while time.perf_counter() - t0 < 10.0:
+            for _, t, m, k, w in mats:
+                for n in BATCHES:
+                    O.mul_mat(t, w, k, xs[k][:n])
+            reps_cpu += 1
+        dt = (time.perf_counter() - t0) / reps_cpu
+        cpu = {"value": total_bytes / dt / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+               "sample": "the full step (12 products), %d repeats in ~10 s" % reps_cpu}
+
+    if dist:
+        dist.barrier()
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 block dots (dp4a), f32 accumulate", "data": "synthetic",
+            "config": {"workload": "decode_gemv: Q4_K 11008x4096 + Q4_K 4096x11008 + Q6_K 32000x4096, batch 1/2/4/8",
+                       "l2": "weights rotate over device copies totalling >= 4x L2 per shape",
+                       "parallelism": "replicas" if world > 1 else "single GPU", "parity_max_rel_err": err},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src, "kernel": "gemv_kernel (activation pre-quantized)",
+                         "detail": detail},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    ctx.close()
+    if dist:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200q", choices=["b200q", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_gpu(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,147 @@
+/*
+ * b200q.h -- C ABI of the B200 (sm_100a) quantized weight mat-mul: ggml's
+ * GGML_OP_MUL_MAT and GGML_OP_MUL_MAT_ID over Q4_0, Q8_0, Q4_K, Q6_K and IQ4_XS
+ * weights with f32 activations and f32 results.
+ *
+ * The entry points are what a ggml backend binds for this path. Each one names the
+ * interface of marfrit/arcint's ggml-opencl backend it stands in for; "P01" etc. are
+ * patch files under contrib/llama.cpp/patches/ of that tree and the numbers are
+ * lines of the .patch file:
+ *   P01  0000-01-kquant-integer-dpas.patch      P09  0000-09-moe-routing-gemm-tiles.patch
+ *   P99  0099-opencl-q4_0-q8_0-int8-gemm.patch  P100 0100-opencl-downgrade-lines-and-counts.patch
+ *   P103 0103-opencl-id-int8-sg8.patch          P115 0115-opencl-few-column-int8-q4_0-q8_0-iq4.patch
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every call returns a b200q_status and never aborts;
+ *   - one context per GPU, used from one host thread at a time (ggml drives a backend
+ *     instance from one thread); work is enqueued on the context's stream and is
+ *     asynchronous to the host unless the call says otherwise;
+ *   - tensor storage belongs to the caller; scratch belongs to the context, grows on
+ *     demand and is never shrunk (the reference's prealloc_* buffers, P01:66-88);
+ *   - there is no CPU fallback: a shape the kernels do not take is B200Q_UNSUPPORTED.
+ */
+#ifndef B200Q_H
+#define B200Q_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define B200Q_API
+#else
+#define B200Q_API __attribute__((visibility("default")))
+#endif
+
+typedef enum {
+    B200Q_OK = 0,
+    B200Q_UNSUPPORTED = 1,   /* shape / type / layout outside what the kernels take */
+    B200Q_INVALID = 2,       /* null pointer, inconsistent sizes, id out of range    */
+    B200Q_CUDA_ERROR = 3,
+    B200Q_NO_MEMORY = 4,
+    B200Q_NCCL_ERROR = 5,
+    B200Q_TIMEOUT = 6        /* a bounded device-side wait gave up                   */
+} b200q_status;
+
+/* ggml type ids (ggml.h enum ggml_type) */
+enum {
+    B200Q_TYPE_F32 = 0,
+    B200Q_TYPE_Q4_0 = 2,
+    B200Q_TYPE_Q8_0 = 8,
+    B200Q_TYPE_Q4_K = 12,
+    B200Q_TYPE_Q6_K = 14,
+    B200Q_TYPE_IQ4_XS = 23,
+    B200Q_TYPE_I32 = 26
+};
+
+enum { B200Q_OP_MUL_MAT = 0, B200Q_OP_MUL_MAT_ID = 1 };
+
+/*
+ * The fields of ggml_tensor this path reads (P01:817-857, 1174-1219): type, ne[4]
+ * (elements per dimension, ne[0] fastest), nb[4] (strides in bytes) and the device
+ * address of element 0 (ggml: extra->data_device + offset + view_offs).
+ */
+typedef struct {
+    int32_t type;
+    int64_t ne[4];
+    size_t  nb[4];
+    void   *data;
+} b200q_tensor;
+
+typedef struct b200q_ctx b200q_ctx;
+
+/* ggml_backend_opencl_init / ggml_backend_opencl_reg (P100:11-25): one context per
+ * device. `stream` is a cudaStream_t (NULL: the context creates its own). */
+B200Q_API b200q_status b200q_init(b200q_ctx **ctx, int device, void *stream);
+B200Q_API void         b200q_free(b200q_ctx *ctx);
+B200Q_API const char  *b200q_last_error(const b200q_ctx *ctx);
+B200Q_API const char  *b200q_version(void);
+
+/* ggml_opencl_supports_op (P01:615-652) with the shape gate ggml_cl_kq_mul_mat_shape
+ * (P01:807-812). B200Q_OK when b200q_mul_mat / b200q_mul_mat_id will take the op.
+ * ctx may be NULL (the answer does not depend on the device). */
+B200Q_API b200q_status b200q_supports(const b200q_ctx *ctx, int op, const b200q_tensor *src0,
+                                      const b200q_tensor *src1, const b200q_tensor *ids,
+                                      const b200q_tensor *dst);
+
+/* ggml_cl_mul_mat (P01:1135-1158; Q4_0/Q8_0 arms P99:120-290; few-column arm
+ * P115:588-594): dst[M, N] = src0[K, M] (quantized rows) x src1[K, N] (f32), the
+ * weight broadcast over src1's dimensions 2 and 3. */
+B200Q_API b200q_status b200q_mul_mat(b200q_ctx *ctx, const b200q_tensor *src0,
+                                     const b200q_tensor *src1, b200q_tensor *dst);
+
+/* ggml_cl_mul_mat_id (P01:1316-1328, ggml_cl_mul_mat_id_kq P01:1174-1313): src0
+ * [K, M, n_expert], src1 [K, ne11 in {1, n_used}, n_tok] f32, ids [n_used, n_tok] i32
+ * (row stride nb[1], may be a view), dst [M, n_used, n_tok]:
+ * dst[:, i, t] = src0[ids[i, t]] x src1[:, i % ne11, t]  (P01:3917-3934). */
+B200Q_API b200q_status b200q_mul_mat_id(b200q_ctx *ctx, const b200q_tensor *src0,
+                                        const b200q_tensor *src1, const b200q_tensor *ids,
+                                        b200q_tensor *dst);
+
+/* ggml_backend_opencl_graph_compute's generation bump (P01:609-611): starts a new
+ * graph. Within one graph an activation tensor that feeds several products (q/k/v,
+ * gate/up) is quantized once (P01:670-688) and a MoE route is computed once per ids
+ * tensor (P01:1264-1287); both caches are keyed by (address, shape, strides,
+ * generation), so the caller must call this whenever tensor contents may have changed. */
+B200Q_API b200q_status b200q_graph_begin(b200q_ctx *ctx);
+
+/* ggml backend buffer interface (buffer alloc, set_tensor, get_tensor, synchronize):
+ * device memory for tensors and stream-ordered copies between host and device. */
+B200Q_API b200q_status b200q_buffer_alloc(b200q_ctx *ctx, size_t bytes, void **dev_ptr);
+B200Q_API b200q_status b200q_buffer_free(b200q_ctx *ctx, void *dev_ptr);
+B200Q_API b200q_status b200q_tensor_set(b200q_ctx *ctx, void *dev_dst, const void *host_src, size_t bytes);
+B200Q_API b200q_status b200q_tensor_get(b200q_ctx *ctx, void *host_dst, const void *dev_src, size_t bytes);
+B200Q_API b200q_status b200q_tensor_copy(b200q_ctx *ctx, void *dev_dst, const void *dev_src, size_t bytes);
+B200Q_API b200q_status b200q_synchronize(b200q_ctx *ctx);
+/* page-locked host memory, so set/get copies run at full PCIe rate and asynchronously */
+B200Q_API b200q_status b200q_host_alloc(size_t bytes, void **host_ptr);
+B200Q_API b200q_status b200q_host_free(void *host_ptr);
+
+/* The reference's "a path other than the promised one says so" counters
+ * (ggml_cl_downgrade*, P100:51-64, 255-266): "key\tcount\n" lines, one per kernel
+ * path taken since the context was made (or since b200q_stats_reset). The string
+ * belongs to the context and is valid until the next call on it. */
+B200Q_API const char  *b200q_stats(b200q_ctx *ctx);
+B200Q_API void         b200q_stats_reset(b200q_ctx *ctx);
+
+/* Device timing for benchmarks: cudaEvent pairs on the context's stream. */
+B200Q_API b200q_status b200q_timer_start(b200q_ctx *ctx);
+B200Q_API b200q_status b200q_timer_stop(b200q_ctx *ctx, float *elapsed_ms);  /* synchronizes */
+/* writes a buffer larger than L2 so the next launch starts cold */
+B200Q_API b200q_status b200q_flush_l2(b200q_ctx *ctx);
+
+/* Debug views of what the kernels see, for bit-exact parity tests: the quantized
+ * activation (codes [N][K] int8; scales fp16 [N][K/32] for Q4_0/Q8_0 weights or f32
+ * [N][K/256] for the 256-block types; sums int16 [N][K/32], 256-block types only) and
+ * the dequantized weight rows the device decoders produce (f32 [M][K]). */
+B200Q_API b200q_status b200q_debug_quantize_act(b200q_ctx *ctx, int weight_type, const b200q_tensor *src1,
+                                                void *dev_codes, void *dev_scales, void *dev_sums);
+B200Q_API b200q_status b200q_debug_dequantize(b200q_ctx *ctx, const b200q_tensor *src0, float *dev_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

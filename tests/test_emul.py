@@ -1,0 +1,110 @@
+"""Device-free checks of the kernels' own text: the GEMV lane code, the block decoders and
+the bit tricks are host+device functions; arcint_b200/csrc/emul.cpp compiles them with g++
+and replays the kernel's loops on the CPU. What is checked here is the same source the GPU
+runs (the method of the reference's tests/test-opencl-kq-i8.cpp)."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+import oracle as O
+from arcint_b200 import build as B
+
+_emul = None
+
+
+def emul():
+    global _emul
+    if _emul is None:
+        so = B.build_emul()
+        E = C.CDLL(so)
+        vp, i64 = C.c_void_p, C.c_int64
+        E.emul_gemv.argtypes = [C.c_int, vp, C.c_size_t, i64, i64, vp, vp, vp, C.c_int, C.c_int, vp, i64]
+        E.emul_dequantize_row.argtypes = [C.c_int, vp, i64, vp]
+        for f in ("emul_iq4nl_lookup4", "emul_nib_minus8", "emul_six_minus32"):
+            getattr(E, f).argtypes = [C.c_uint32]
+            getattr(E, f).restype = C.c_uint32
+        _emul = E
+    return _emul
+
+
+def test_bit_tricks_exhaustive_per_byte():
+    E = emul()
+    for a in range(16):
+        for b in range(16):
+            idx = a | (b << 8) | (((a * 7 + 3) % 16) << 16) | (((b * 5 + 1) % 16) << 24)
+            got = E.emul_iq4nl_lookup4(idx)
+            want = 0
+            for i in range(4):
+                want |= (int(O.KVALUES_IQ4NL[(idx >> (8 * i)) & 0xF]) & 0xFF) << (8 * i)
+            assert got == want
+            got8 = E.emul_nib_minus8(idx)
+            assert [((got8 >> (8 * i)) & 0xFF) for i in range(4)] == [(((idx >> (8 * i)) & 0xF) - 8) & 0xFF for i in range(4)]
+    for a in range(64):
+        t = a | ((63 - a) << 8) | (((a * 11) % 64) << 16) | (((a * 29 + 5) % 64) << 24)
+        got = E.emul_six_minus32(t)
+        assert [((got >> (8 * i)) & 0xFF) for i in range(4)] == [(((t >> (8 * i)) & 0x3F) - 32) & 0xFF for i in range(4)]
+
+
+@pytest.mark.parametrize("name,t", [("q4_0", O.Q4_0), ("q8_0", O.Q8_0), ("q4_K", O.Q4_K), ("q6_K", O.Q6_K), ("iq4_xs", O.IQ4_XS)])
+def test_device_decoder_text_matches_gguf_golden(golden, name, t):
+    E = emul()
+    blocks, want = golden[name + "_blocks"], golden[name + "_deq"]
+    got = np.empty_like(want)
+    for r in range(blocks.shape[0]):
+        row = np.ascontiguousarray(blocks[r])
+        E.emul_dequantize_row(t, row.ctypes.data, want.shape[1], got[r].ctypes.data)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def _run_emul(t, w, k, x, R):
+    E = emul()
+    m, n = w.shape[0], x.shape[0]
+    if O.act_form(t) == O.ACT_Q8_0:
+        q, d = O.quantize_act_q8_0(x)
+        d16, d32 = d.ctypes.data, None
+    else:
+        q, d, _ = O.quantize_act_q8_256(x)
+        d16, d32 = None, d.ctypes.data
+    out = np.full((n, m), np.nan, dtype=np.float32)
+    rc = E.emul_gemv(t, w.ctypes.data, w.shape[1], m, k, q.ctypes.data, d16, d32, n, R, out.ctypes.data, m)
+    assert rc == 0
+    return out
+
+
+def rel_err(got, ref):
+    floor = 1e-2 * np.abs(ref).max(axis=-1, keepdims=True)
+    return float((np.abs(got - ref) / np.maximum(np.abs(ref), floor)).max())
+
+
+# K values: one full stage, several stages, a ragged last stage, a single block
+KS = {O.Q4_0: [32, 96, 1024, 2080, 4096], O.Q8_0: [32, 96, 1024, 2080], O.Q4_K: [256, 1024, 2816, 4096],
+      O.Q6_K: [256, 2048, 2816, 4096], O.IQ4_XS: [256, 1024, 2816]}
+
+
+@pytest.mark.parametrize("t", O.QUANT_TYPES)
+@pytest.mark.parametrize("n,R", [(1, 2), (2, 1), (3, 2), (5, 1), (8, 1)])
+def test_gemv_lane_code_matches_oracle(t, n, R):
+    rng = np.random.default_rng(1000 * t + n)
+    for k in KS[t]:
+        m = 7                                               # odd: exercises the ragged row group
+        w = O.random_blocks(t, m, k, rng)
+        x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
+        got = _run_emul(t, w, k, x, R)
+        ref = O.mul_mat_f64(t, w, k, x, True)
+        assert np.isfinite(got).all()
+        assert rel_err(got, ref) < 1e-4, (t, k, n)
+        assert rel_err(got, O.mul_mat(t, w, k, x)) < 1e-4
+
+
+def test_gemv_lane_code_red_case():
+    """The comparison must be able to fail: a wrong activation scale has to show."""
+    t, k = O.Q4_K, 1024
+    rng = np.random.default_rng(5)
+    w = O.random_blocks(t, 4, k, rng)
+    x = rng.normal(0, 1, size=(1, k)).astype(np.float32)
+    ref = O.mul_mat_f64(t, w, k, x, True)
+    x2 = x.copy()
+    x2[0, 700] += 0.5
+    assert rel_err(_run_emul(t, w, k, x2, 2), ref) > 1e-3
