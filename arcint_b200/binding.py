@@ -94,6 +94,11 @@ def lib():
     L.b200q_mul_mat.argtypes = [vp, TP, TP, TP]
     L.b200q_mul_mat_id.argtypes = [vp, TP, TP, TP, TP]
     L.b200q_graph_begin.argtypes = [vp]
+    L.b200q_capture_begin.argtypes = [vp]
+    L.b200q_capture_end.argtypes = [vp, C.POINTER(vp)]
+    L.b200q_graph_launch.argtypes = [vp, vp]
+    L.b200q_graph_free.argtypes = [vp]
+    L.b200q_graph_free.restype = None
     L.b200q_buffer_alloc.argtypes = [vp, sz, C.POINTER(vp)]
     L.b200q_buffer_free.argtypes = [vp, vp]
     L.b200q_tensor_set.argtypes = [vp, vp, vp, sz]
@@ -117,7 +122,8 @@ def lib():
 
 EXPORTS = [
     "b200q_init", "b200q_free", "b200q_last_error", "b200q_version", "b200q_supports", "b200q_mul_mat",
-    "b200q_mul_mat_id", "b200q_graph_begin", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
+    "b200q_mul_mat_id", "b200q_graph_begin", "b200q_capture_begin", "b200q_capture_end", "b200q_graph_launch",
+    "b200q_graph_free", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
     "b200q_tensor_get", "b200q_tensor_copy", "b200q_synchronize", "b200q_host_alloc", "b200q_host_free",
     "b200q_stats", "b200q_stats_reset", "b200q_timer_start", "b200q_timer_stop", "b200q_flush_l2",
     "b200q_debug_quantize_act", "b200q_debug_dequantize",
@@ -224,6 +230,24 @@ class Context:
 
     def mul_mat_status(self, src0, src1, dst):
         return self.L.b200q_mul_mat(self.h, src0, src1, dst)
+
+    # ---- CUDA graphs ----
+    def capture(self, fn):
+        """Record the calls fn() makes on this context into a graph; returns its handle."""
+        self.check(self.L.b200q_capture_begin(self.h))
+        try:
+            fn()
+        finally:
+            g = C.c_void_p()
+            st = self.L.b200q_capture_end(self.h, C.byref(g))
+        self.check(st)
+        return g
+
+    def graph_launch(self, g):
+        self.check(self.L.b200q_graph_launch(self.h, g))
+
+    def graph_free(self, g):
+        self.L.b200q_graph_free(g)
 
     # ---- stats / timing ----
     def stats(self):

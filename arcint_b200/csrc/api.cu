@@ -6,10 +6,29 @@
 // conversion cache (:670-715), ggml_cl_mul_mat (:1135-1158) and supports_op (:615-652).
 #include <stdarg.h>
 #include <stdio.h>
+#include <string.h>
 
 #include "common.cuh"
 
 namespace b200q {
+
+const char *stat_name(int s) {
+    static const char *fixed[] = { "quantize_act_q8_0", "quantize_act_q8_256", "act_cache_hit", "workspace_grow",
+                                   "mul_mat_gemv_chunks" };
+    static char cols[18][32];
+    if (s < ST_GEMV_COL0) return fixed[s];
+    if (s < ST_GEMV_ID) {
+        const bool un = s >= ST_GEMV_UNALIGNED_COL0;
+        const int n = s - (un ? ST_GEMV_UNALIGNED_COL0 : ST_GEMV_COL0);
+        char *b = cols[(un ? 9 : 0) + n];
+        snprintf(b, 32, "gemv_%s%dcol", un ? "unaligned_" : "", n);
+        return b;
+    }
+    static const char *rest[] = { "gemv_id", "gemv_id_unaligned", "moe_route", "route_cache_hit", "moe_gemm", "moe_pack",
+                                  "gemm_tc", "gemm_tc_quantize", "gemm_fallback_shape", "tp_allreduce", "tp_allgather",
+                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc" };
+    return rest[s - ST_GEMV_ID];
+}
 
 b200q_status fail(b200q_ctx *ctx, b200q_status st, const char *fmt, ...) {
     if (ctx) {
@@ -26,6 +45,8 @@ b200q_status fail(b200q_ctx *ctx, b200q_status st, const char *fmt, ...) {
 // grow-only scratch (the reference's prealloc_* buffers never shrink either)
 b200q_status ws_reserve(b200q_ctx *ctx, Workspace *ws, size_t bytes) {
     if (bytes <= ws->cap) return B200Q_OK;
+    if (ctx->capturing)
+        return fail(ctx, B200Q_INVALID, "scratch would grow inside a capture: run the sequence once before capturing");
     if (ws->ptr) {
         // the old block may still be in use by work already enqueued on the stream
         B200Q_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -40,7 +61,7 @@ b200q_status ws_reserve(b200q_ctx *ctx, Workspace *ws, size_t bytes) {
         return fail(ctx, B200Q_NO_MEMORY, "cudaMalloc(%zu): %s", want, cudaGetErrorString(e));
     }
     ws->cap = want;
-    count(ctx, "workspace_grow");
+    count(ctx, ST_WORKSPACE_GROW);
     return B200Q_OK;
 }
 
@@ -106,7 +127,7 @@ static b200q_status get_activation(b200q_ctx *ctx, int form, const b200q_tensor 
         e.valid = true;
         hit = &e;
     } else {
-        count(ctx, "act_cache_hit");
+        count(ctx, ST_ACT_CACHE_HIT);
     }
     out->codes = (const int8_t *)hit->codes.ptr;
     out->d16 = form == ACT_Q8_0 ? (const uint16_t *)hit->scales.ptr : nullptr;
@@ -228,7 +249,7 @@ b200q_status b200q_mul_mat(b200q_ctx *ctx, const b200q_tensor *src0, const b200q
         const int64_t c23 = c0 / dst->ne[1], c2 = c23 % dst->ne[2], c3 = c23 / dst->ne[2];
         float *base = uniform ? (float *)dst->data
                               : (float *)((uint8_t *)dst->data + c2 * dst->nb[2] + c3 * dst->nb[3]);
-        if (N > 8) count(ctx, "mul_mat_gemv_chunks");
+        if (N > 8) count(ctx, ST_MUL_MAT_GEMV_CHUNKS);
         for (int64_t c = 0; c < run; c += 8) {
             const int nc = (int)(run - c < 8 ? run - c : 8);
             st = launch_gemv(ctx, src0->type, src0->data, src0->nb[1], M, K, act, c0 + c, nc, base + c * ldd, ldd);
@@ -242,6 +263,53 @@ b200q_status b200q_mul_mat_id(b200q_ctx *ctx, const b200q_tensor *src0, const b2
                               const b200q_tensor *ids, b200q_tensor *dst) {
     (void)src0; (void)src1; (void)ids; (void)dst;
     return fail(ctx, B200Q_UNSUPPORTED, "MUL_MAT_ID not built yet");
+}
+
+// ---- CUDA graphs ----------------------------------------------------------------------
+
+struct b200q_graph {
+    cudaGraph_t     graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+};
+
+b200q_status b200q_capture_begin(b200q_ctx *ctx) {
+    if (!ctx) return B200Q_INVALID;
+    if (ctx->capturing) return fail(ctx, B200Q_INVALID, "capture already open");
+    B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+    B200Q_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    return B200Q_OK;
+}
+
+b200q_status b200q_capture_end(b200q_ctx *ctx, b200q_graph **out) {
+    if (!ctx || !out) return B200Q_INVALID;
+    *out = nullptr;
+    if (!ctx->capturing) return fail(ctx, B200Q_INVALID, "no capture open");
+    ctx->capturing = false;
+    b200q_graph *g = new b200q_graph();
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+    if (e != cudaSuccess) {
+        if (g->graph) cudaGraphDestroy(g->graph);
+        delete g;
+        return fail(ctx, B200Q_CUDA_ERROR, "graph capture: %s", cudaGetErrorString(e));
+    }
+    *out = g;
+    return B200Q_OK;
+}
+
+b200q_status b200q_graph_launch(b200q_ctx *ctx, b200q_graph *g) {
+    if (!ctx || !g || !g->exec) return B200Q_INVALID;
+    B200Q_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+    count(ctx, ST_GRAPH_LAUNCH);
+    return B200Q_OK;
+}
+
+void b200q_graph_free(b200q_graph *g) {
+    if (!g) return;
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
 }
 
 // ---- buffers and copies --------------------------------------------------------------
@@ -302,12 +370,13 @@ b200q_status b200q_host_free(void *host_ptr) {
 const char *b200q_stats(b200q_ctx *ctx) {
     if (!ctx) return "";
     ctx->stats_text.clear();
-    for (auto &kv : ctx->stats) ctx->stats_text += kv.first + "\t" + std::to_string(kv.second) + "\n";
+    for (int i = 0; i < ST_COUNT; ++i)
+        if (ctx->counters[i]) ctx->stats_text += std::string(stat_name(i)) + "\t" + std::to_string(ctx->counters[i]) + "\n";
     return ctx->stats_text.c_str();
 }
 
 void b200q_stats_reset(b200q_ctx *ctx) {
-    if (ctx) ctx->stats.clear();
+    if (ctx) memset(ctx->counters, 0, sizeof(ctx->counters));
 }
 
 b200q_status b200q_timer_start(b200q_ctx *ctx) {

@@ -81,6 +81,19 @@ struct ActEntry {
 
 struct RouteEntry;
 
+// Path-taken counters (the reference's downgrade counters, P100:51-64): fixed slots so a
+// launch does not pay for a string.
+enum Stat {
+    ST_QUANT_Q8_0, ST_QUANT_Q8_256, ST_ACT_CACHE_HIT, ST_WORKSPACE_GROW, ST_MUL_MAT_GEMV_CHUNKS,
+    ST_GEMV_COL0,                                 // + ncols (1..8)
+    ST_GEMV_UNALIGNED_COL0 = ST_GEMV_COL0 + 9,    // + ncols
+    ST_GEMV_ID = ST_GEMV_UNALIGNED_COL0 + 9, ST_GEMV_ID_UNALIGNED, ST_MOE_ROUTE, ST_ROUTE_CACHE_HIT, ST_MOE_GEMM,
+    ST_MOE_PACK, ST_GEMM_TC, ST_GEMM_TC_QUANT, ST_GEMM_FALLBACK_SHAPE, ST_TP_ALLREDUCE, ST_TP_ALLGATHER,
+    ST_EP_DISPATCH, ST_EP_COMBINE, ST_GRAPH_LAUNCH, ST_NO_ALLOC,
+    ST_COUNT
+};
+const char *stat_name(int s);
+
 }  // namespace b200q
 
 struct b200q_ctx {
@@ -89,9 +102,10 @@ struct b200q_ctx {
     bool         own_stream = false;
     int          sm_count = 148;
     uint64_t     generation = 1;
+    bool         capturing = false;
     std::string  last_error;
     std::string  stats_text;
-    std::map<std::string, uint64_t> stats;
+    uint64_t     counters[b200q::ST_COUNT] = {};
     // quantized-activation cache: a few entries, reused round-robin
     std::vector<b200q::ActEntry> act_cache;
     size_t       act_next = 0;
@@ -107,7 +121,7 @@ namespace b200q {
 
 b200q_status fail(b200q_ctx *ctx, b200q_status st, const char *fmt, ...);
 b200q_status ws_reserve(b200q_ctx *ctx, Workspace *ws, size_t bytes);
-inline void  count(b200q_ctx *ctx, const std::string &key) { ++ctx->stats[key]; }
+inline void  count(b200q_ctx *ctx, int stat) { ++ctx->counters[stat]; }
 
 #define B200Q_CUDA(ctx, expr)                                                                       \
     do {                                                                                            \

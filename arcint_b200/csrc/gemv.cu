@@ -156,7 +156,7 @@ b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_str
     if (!type_info(type, &ti)) return fail(ctx, B200Q_UNSUPPORTED, "gemv: type %d", type);
     const size_t row_bytes = (size_t)(K / ti.block) * ti.bytes;
     const bool aligned = ((uintptr_t)w % 16 == 0) && (row_stride % 16 == 0) && (row_bytes % 16 == 0);
-    count(ctx, std::string("gemv_") + (aligned ? "" : "unaligned_") + std::to_string(ncols) + "col");
+    count(ctx, (aligned ? ST_GEMV_COL0 : ST_GEMV_UNALIGNED_COL0) + ncols);
     switch (type) {
     case B200Q_TYPE_Q4_0:   return launch_type<B200Q_TYPE_Q4_0>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);
     case B200Q_TYPE_Q8_0:   return launch_type<B200Q_TYPE_Q8_0>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);

@@ -102,12 +102,12 @@ b200q_status launch_quantize_act(b200q_ctx *ctx, int form, const b200q_tensor *s
         const int64_t threads = ncols * (K / 4);
         quantize_q8_0_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, ctx->stream>>>(a, K, ncols, codes,
                                                                                        (uint16_t *)scales);
-        count(ctx, "quantize_act_q8_0");
+        count(ctx, ST_QUANT_Q8_0);
     } else {
         const int64_t warps = ncols * (K / 256);
         quantize_q8_256_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, ctx->stream>>>(a, K, ncols, codes,
                                                                                             (float *)scales, bsums);
-        count(ctx, "quantize_act_q8_256");
+        count(ctx, ST_QUANT_Q8_256);
     }
     B200Q_CUDA(ctx, cudaGetLastError());
     return B200Q_OK;

@@ -190,24 +190,22 @@ def run_gpu(args, rank, world):
 
     products = [(name, t, m, k, ptrs, n) for name, t, m, k, ptrs in dev for n in BATCHES]
     total_bytes = sum(algo_bytes(t, m, k, n) for _, t, m, k, _, n in products)
-    counter = [0]
+    ROT = 4                                 # step graphs, each on its own rotation of the weight copies
 
-    def step_device():
+    def step_device(rot):
         for name, t, m, k, ptrs, n in products:
-            counter[0] += 1
             ctx.graph_begin()
-            ctx.mul_mat(A.Tensor.weights(t, ptrs[counter[0] % len(ptrs)], k, m), A.Tensor.f32(dx[k], [k, n]),
+            ctx.mul_mat(A.Tensor.weights(t, ptrs[(rot * 5 + n) % len(ptrs)], k, m), A.Tensor.f32(dx[k], [k, n]),
                         A.Tensor.f32(dy, [m, n]))
 
-    def step_e2e():
+    def step_e2e(rot):
+        # host buffers in, host buffers out; the caller reads the results at the end of the step
         for name, t, m, k, ptrs, n in products:
-            counter[0] += 1
             ctx.graph_begin()
             ctx.set_async(dx[k], hx[k].ptr, 4 * n * k)
-            ctx.mul_mat(A.Tensor.weights(t, ptrs[counter[0] % len(ptrs)], k, m), A.Tensor.f32(dx[k], [k, n]),
+            ctx.mul_mat(A.Tensor.weights(t, ptrs[(rot * 5 + n) % len(ptrs)], k, m), A.Tensor.f32(dx[k], [k, n]),
                         A.Tensor.f32(dy, [m, n]))
             ctx.get_async(hy.ptr, dy, 4 * n * m)
-            ctx.sync()                      # the caller reads the result before the next product
 
     def barrier():
         ctx.sync()
@@ -217,8 +215,8 @@ def run_gpu(args, rank, world):
     def timed(fn, steps):
         barrier()
         ctx.timer_start()
-        for _ in range(steps):
-            fn()
+        for i in range(steps):
+            fn(i)
         ms = ctx.timer_stop()
         if dist:
             import torch
@@ -239,48 +237,79 @@ def run_gpu(args, rank, world):
     if not err < 1e-3:
         raise SystemExit("bench: parity check failed before timing (max rel err %.3e)" % err)
 
-    for _ in range(max(args.warmup, 3)):
-        step_device()
     sampler = ClockSampler(device)
     if rank == 0:
         sampler.start()
+    # the step as CUDA graphs (one per rotation): scratch is sized by an eager pass first
+    for r in range(ROT):
+        step_device(r)
+    ctx.sync()
     ctx.stats_reset()
-    ms = timed(step_device, args.steps)
-    stats = ctx.stats()
-    launches = sum(v for key, v in stats.items() if key.startswith("gemv_") or key.startswith("quantize_"))
+    graphs = [ctx.capture(lambda r=r: step_device(r)) for r in range(ROT)]
+    st = ctx.stats()
+    launches_per_step = sum(v for key, v in st.items() if key.startswith("gemv_") or key.startswith("quantize_")) // ROT
+    for i in range(max(args.warmup, 3)):
+        ctx.graph_launch(graphs[i % ROT])
+    ms = timed(lambda i: ctx.graph_launch(graphs[i % ROT]), args.steps)
     ms_step = ms / args.steps
     value = world * total_bytes / (ms_step * 1e-3) / 1e9
+    launches = launches_per_step * args.steps
 
-    # end to end through the C ABI with host buffers
-    for _ in range(3):
-        step_e2e()
-    ms_e2e = timed(step_e2e, args.steps) / args.steps
-    clocks = sampler.stop() if rank == 0 else None
+    # end to end through the C ABI with host buffers (eager calls, and the same as graphs)
+    for i in range(3):
+        step_e2e(i)
+        ctx.sync()
+
+    def e2e_eager(i):
+        step_e2e(i)
+        ctx.sync()
+
+    ms_e2e = timed(e2e_eager, args.steps) / args.steps
     e2e = world * total_bytes / (ms_e2e * 1e-3) / 1e9
+    egraphs = [ctx.capture(lambda r=r: step_e2e(r)) for r in range(ROT)]
+
+    def e2e_graph(i):
+        ctx.graph_launch(egraphs[i % ROT])
+        ctx.sync()
+
+    for i in range(3):
+        e2e_graph(i)
+    ms_e2e_graph = timed(e2e_graph, args.steps) / args.steps
     h2d = sum(4 * n * k for _, _, _, k, _, n in products)
     d2h = sum(4 * n * m for _, _, m, _, _, n in products)
 
-    # roofline of the dominant kernel: the GEMV alone (activation quantized once per graph)
+    # roofline of the dominant kernel: the GEMV alone (activation quantized once per graph),
+    # a graph of back-to-back launches over the rotating weight copies
     peak, peak_src = measured_peaks()
     detail, tot_b, tot_ms = [], 0, 0.0
-    reps = 40
+    reps = 50
     for name, t, m, k, ptrs, n in products:
         W = [A.Tensor.weights(t, p, k, m) for p in ptrs]
         X, Y = A.Tensor.f32(dx[k], [k, n]), A.Tensor.f32(dy, [m, n])
         ctx.graph_begin()
-        for i in range(len(ptrs) + 3):
-            ctx.mul_mat(W[i % len(W)], X, Y)
+        ctx.mul_mat(W[0], X, Y)
+
+        def gemv_only():
+            for i in range(reps):
+                ctx.mul_mat(W[i % len(W)], X, Y)
+
+        g = ctx.capture(gemv_only)
+        for _ in range(3):
+            ctx.graph_launch(g)
         ctx.sync()
+        nl = 4
         ctx.timer_start()
-        for i in range(reps):
-            ctx.mul_mat(W[i % len(W)], X, Y)
-        kms = ctx.timer_stop() / reps
+        for _ in range(nl):
+            ctx.graph_launch(g)
+        kms = ctx.timer_stop() / (reps * nl)
+        ctx.graph_free(g)
         b = algo_bytes(t, m, k, n)
         detail.append({"shape": "%s %dx%d" % (O.TYPE_NAMES[t], m, k), "batch": n, "us": round(kms * 1e3, 2),
                        "gbs": round(b / (kms * 1e-3) / 1e9, 1), "frac": round(b / (kms * 1e-3) / 1e9 / peak, 3)})
         tot_b += b
         tot_ms += kms
     achieved = tot_b / (tot_ms * 1e-3) / 1e9
+    clocks = sampler.stop() if rank == 0 else None
 
     cpu = None
     if rank == 0:
@@ -304,13 +333,15 @@ def run_gpu(args, rank, world):
             "vs_baseline": None, "dtype": "int8 block dots (dp4a), f32 accumulate", "data": "synthetic",
             "config": {"workload": "decode_gemv: Q4_K 11008x4096 + Q4_K 4096x11008 + Q6_K 32000x4096, batch 1/2/4/8",
                        "l2": "weights rotate over device copies totalling >= 4x L2 per shape",
+                       "launch": "each step is one CUDA-graph replay of 12 x (quantize, GEMV)",
                        "parallelism": "replicas" if world > 1 else "single GPU", "parity_max_rel_err": err},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "kernel": "gemv_kernel (activation pre-quantized)",
+                         "traffic": None, "peak_source": peak_src, "kernel": "gemv_kernel (activation pre-quantized), back-to-back launches in a CUDA graph",
                          "detail": detail},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": ms_e2e},
+                    "ms_per_step": ms_e2e, "how": "eager C-ABI calls per product: tensor_set, mul_mat, tensor_get; one "
+                    "synchronize per step", "graph_replay_value": world * total_bytes / (ms_e2e_graph * 1e-3) / 1e9},
             "gpu_launches": launches,
             "clocks": clocks,
         }

@@ -108,6 +108,19 @@ B200Q_API b200q_status b200q_mul_mat_id(b200q_ctx *ctx, const b200q_tensor *src0
  * generation), so the caller must call this whenever tensor contents may have changed. */
 B200Q_API b200q_status b200q_graph_begin(b200q_ctx *ctx);
 
+/* CUDA-graph replay of a recorded call sequence (what ggml's CUDA backend does for its
+ * graph_compute; the reference's OpenCL backend enqueues each node, P01:855). Calls made on
+ * the context between capture_begin and capture_end are recorded instead of run; the graph
+ * then replays them on the context's stream with one launch. Scratch must already be large
+ * enough (run the sequence once before capturing: growth inside a capture is refused), and
+ * a graph is stale once the context's scratch has grown ("workspace_grow" in b200q_stats)
+ * or any tensor it touched has moved. */
+typedef struct b200q_graph b200q_graph;
+B200Q_API b200q_status b200q_capture_begin(b200q_ctx *ctx);
+B200Q_API b200q_status b200q_capture_end(b200q_ctx *ctx, b200q_graph **graph);
+B200Q_API b200q_status b200q_graph_launch(b200q_ctx *ctx, b200q_graph *graph);
+B200Q_API void         b200q_graph_free(b200q_graph *graph);
+
 /* ggml backend buffer interface (buffer alloc, set_tensor, get_tensor, synchronize):
  * device memory for tensors and stream-ordered copies between host and device. */
 B200Q_API b200q_status b200q_buffer_alloc(b200q_ctx *ctx, size_t bytes, void **dev_ptr);
