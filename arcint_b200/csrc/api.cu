@@ -119,9 +119,11 @@ static b200q_status get_activation(b200q_ctx *ctx, int form, const b200q_tensor 
         if ((st = ws_reserve(ctx, &e.codes, (size_t)(N * K) + 64)) != B200Q_OK) return st;
         const size_t sbytes = form == ACT_Q8_0 ? sizeof(uint16_t) * (size_t)(N * (K / 32)) : sizeof(float) * (size_t)(N * (K / 256));
         if ((st = ws_reserve(ctx, &e.scales, sbytes + 64)) != B200Q_OK) return st;
-        if (form == ACT_Q8_256 && (st = ws_reserve(ctx, &e.sums, sizeof(int16_t) * (size_t)(N * (K / 32)) + 64)) != B200Q_OK)
+        if ((st = ws_reserve(ctx, &e.sums, sizeof(int16_t) * (size_t)(N * (K / 32)) + 64)) != B200Q_OK) return st;
+        if (form == ACT_Q8_256 && (st = ws_reserve(ctx, &e.sums16, sizeof(int16_t) * (size_t)(N * (K / 16)) + 64)) != B200Q_OK)
             return st;
-        if ((st = launch_quantize_act(ctx, form, src1, (int8_t *)e.codes.ptr, e.scales.ptr, (int16_t *)e.sums.ptr)) != B200Q_OK)
+        if ((st = launch_quantize_act(ctx, form, src1, (int8_t *)e.codes.ptr, e.scales.ptr, (int16_t *)e.sums.ptr,
+                                      (int16_t *)e.sums16.ptr)) != B200Q_OK)
             return st;
         e.key = key;
         e.valid = true;
@@ -132,7 +134,8 @@ static b200q_status get_activation(b200q_ctx *ctx, int form, const b200q_tensor 
     out->codes = (const int8_t *)hit->codes.ptr;
     out->d16 = form == ACT_Q8_0 ? (const uint16_t *)hit->scales.ptr : nullptr;
     out->d32 = form == ACT_Q8_256 ? (const float *)hit->scales.ptr : nullptr;
-    out->bsums = form == ACT_Q8_256 ? (const int16_t *)hit->sums.ptr : nullptr;
+    out->s32 = (const int16_t *)hit->sums.ptr;
+    out->s16 = form == ACT_Q8_256 ? (const int16_t *)hit->sums16.ptr : nullptr;
     out->form = form;
     out->K = K;
     out->N = N;
@@ -192,6 +195,7 @@ void b200q_free(b200q_ctx *ctx) {
         if (e.codes.ptr) cudaFree(e.codes.ptr);
         if (e.scales.ptr) cudaFree(e.scales.ptr);
         if (e.sums.ptr) cudaFree(e.sums.ptr);
+        if (e.sums16.ptr) cudaFree(e.sums16.ptr);
     }
     if (ctx->flush_buf.ptr) cudaFree(ctx->flush_buf.ptr);
     for (auto &w : ctx->moe_ws)
@@ -410,8 +414,12 @@ b200q_status b200q_debug_quantize_act(b200q_ctx *ctx, int weight_type, const b20
     TypeInfo ti;
     if (!type_info(weight_type, &ti)) return fail(ctx, B200Q_UNSUPPORTED, "weight type %d", weight_type);
     if (!is_contiguous_f32(src1) || src1->ne[0] % ti.block) return fail(ctx, B200Q_UNSUPPORTED, "src1 layout");
-    if (ti.act_form == ACT_Q8_256 && !dev_sums) return B200Q_INVALID;
-    return launch_quantize_act(ctx, ti.act_form, src1, (int8_t *)dev_codes, dev_scales, (int16_t *)dev_sums);
+    if (!dev_sums) return B200Q_INVALID;
+    const int64_t K = src1->ne[0], N = src1->ne[1] * src1->ne[2] * src1->ne[3];
+    b200q_status st = ws_reserve(ctx, &ctx->moe_ws[7], sizeof(int16_t) * (size_t)(N * (K / 16)) + 64);
+    if (st != B200Q_OK) return st;
+    return launch_quantize_act(ctx, ti.act_form, src1, (int8_t *)dev_codes, dev_scales, (int16_t *)dev_sums,
+                               (int16_t *)ctx->moe_ws[7].ptr);
 }
 
 b200q_status b200q_debug_dequantize(b200q_ctx *ctx, const b200q_tensor *src0, float *dev_out) {

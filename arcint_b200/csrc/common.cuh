@@ -42,12 +42,14 @@ enum { ACT_Q8_0 = 0, ACT_Q8_256 = 1 };
 //   codes  + c*K            int8
 //   d16    + c*(K/32)       fp16 bits, per-32 form
 //   d32    + c*(K/256)      f32,       per-256 form
-//   bsums  + c*(K/32)       int16 sums of each 32 codes, per-256 form
+//   s32    + c*(K/32)       int16 sums of each 32 codes, both forms
+//   s16    + c*(K/16)       int16 sums of each 16 codes, per-256 form
 struct ActView {
     const int8_t   *codes;
     const uint16_t *d16;
     const float    *d32;
-    const int16_t  *bsums;
+    const int16_t  *s32;
+    const int16_t  *s16;
     int             form;
     int64_t         K;
     int64_t         N;
@@ -75,7 +77,7 @@ struct ActKey {
 
 struct ActEntry {
     ActKey    key;
-    Workspace codes, scales, sums;
+    Workspace codes, scales, sums, sums16;
     bool      valid = false;
 };
 
@@ -133,7 +135,7 @@ inline void  count(b200q_ctx *ctx, int stat) { ++ctx->counters[stat]; }
 
 // quantize.cu
 b200q_status launch_quantize_act(b200q_ctx *ctx, int form, const b200q_tensor *src1, int8_t *codes, void *scales,
-                                 int16_t *bsums);
+                                 int16_t *sums32, int16_t *sums16);
 b200q_status launch_dequantize(b200q_ctx *ctx, int type, const void *w, int64_t M, int64_t K, size_t row_stride,
                                float *out);
 

@@ -21,15 +21,15 @@ static void emul_gemv_t(const uint8_t *W, size_t row_stride, int64_t M, int64_t 
                         int64_t ldd) {
     typedef GemvFmt<TYPE> F;
     typedef GemvStage<TYPE> S;
-    const int64_t nblk = K / F::BLK_W, row_bytes = nblk * F::BLK_B;
-    const int64_t nstages = (nblk + F::STAGE_BLOCKS - 1) / F::STAGE_BLOCKS;
+    const int nblk = (int)(K / F::BLK_W), row_bytes = nblk * F::BLK_B;
+    const int nstages = (nblk + F::STAGE_BLOCKS - 1) / F::STAGE_BLOCKS;
     const int64_t n_rg = (M + R - 1) / R;
     std::vector<uint32_t> slot((size_t)R * S::SLOT / 4);
     for (int64_t rg = 0; rg < n_rg; ++rg) {
         float acc[32][R][NC];
         memset(acc, 0, sizeof(acc));
-        for (int64_t s = 0; s < nstages; ++s) {
-            const int64_t off = s * S::BYTES;
+        for (int s = 0; s < nstages; ++s) {
+            const int off = s * S::BYTES;
             const int bytes = (int)(row_bytes - off < S::BYTES ? row_bytes - off : S::BYTES);
             memset(slot.data(), 0xA5, slot.size() * 4);     // stale ring contents must not matter
             const uint32_t *srow[R];
@@ -73,12 +73,15 @@ static int emul_gemv_nc(int nc, int R, const uint8_t *W, size_t rs, int64_t M, i
 extern "C" {
 
 int emul_gemv(int type, const uint8_t *W, size_t row_stride, int64_t M, int64_t K, const int8_t *xq,
-              const uint16_t *d16, const float *d32, int ncols, int R, float *dst, int64_t ldd) {
+              const uint16_t *d16, const float *d32, const int16_t *s32, const int16_t *s16, int ncols, int R,
+              float *dst, int64_t ldd) {
     GemvAct a;
     a.q = xq;
     a.d16 = d16;
     a.d32 = d32;
-    a.K = K;
+    a.s32 = s32;
+    a.s16 = s16;
+    a.K = (int)K;
     switch (type) {
     case B200Q_TYPE_Q4_0:   return emul_gemv_nc<B200Q_TYPE_Q4_0>(ncols, R, W, row_stride, M, K, a, dst, ldd);
     case B200Q_TYPE_Q8_0:   return emul_gemv_nc<B200Q_TYPE_Q8_0>(ncols, R, W, row_stride, M, K, a, dst, ldd);

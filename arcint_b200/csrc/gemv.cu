@@ -14,6 +14,8 @@
 #include "gemv_core.cuh"
 #include "common.cuh"
 
+#include <limits.h>
+
 namespace b200q {
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
@@ -27,40 +29,42 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 
 template <int TYPE, int NC, int R, int WARPS, int STAGES, bool ALIGNED>
 __global__ void __launch_bounds__(WARPS * 32)
-gemv_kernel(const uint8_t *__restrict__ W, size_t row_stride, int64_t M, int64_t K, GemvAct act,
-            float *__restrict__ dst, int64_t ldd) {
+gemv_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk, GemvAct act,
+            float *__restrict__ dst, int ldd) {
     typedef GemvFmt<TYPE> F;
     typedef GemvStage<TYPE> S;
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint8_t *ring = smem + (size_t)warp * (STAGES * R * S::SLOT);
+    uint8_t *ring = smem + warp * (STAGES * R * S::SLOT);
 
-    const int64_t nblk = K / F::BLK_W;
-    const int64_t row_bytes = nblk * F::BLK_B;
-    const int64_t nstages = (nblk + F::STAGE_BLOCKS - 1) / F::STAGE_BLOCKS;
-    const int64_t n_rg = (M + R - 1) / R;
-    const int64_t gw = (int64_t)blockIdx.x * WARPS + warp, tw = (int64_t)gridDim.x * WARPS;
-    const int64_t my_rg = gw < n_rg ? (n_rg - gw + tw - 1) / tw : 0;
-    const int64_t total = my_rg * nstages;
+    const int row_bytes = nblk * F::BLK_B;
+    const int nstages = (nblk + F::STAGE_BLOCKS - 1) / F::STAGE_BLOCKS;
+    const int n_rg = (M + R - 1) / R;
+    const int gw = blockIdx.x * WARPS + warp, tw = gridDim.x * WARPS;
 
-    // item i = (row group gw + (i / nstages) * tw, stage i % nstages), ring slot i % STAGES
-    auto issue = [&](int64_t i) {
-        const int64_t rg = gw + (i / nstages) * tw, s = i % nstages;
-        const int64_t off = s * S::BYTES;
-        const int bytes = (int)min((int64_t)S::BYTES, row_bytes - off);
-        uint8_t *slot = ring + (size_t)(i % STAGES) * (R * S::SLOT);
+    // producer cursor: (row group, stage) of the next chunk to fetch, and its ring slot
+    int p_rg = gw, p_s = 0, p_slot = 0;
+    auto issue = [&]() {
+        if (p_rg < n_rg) {
+            const int off = p_s * S::BYTES;
+            const int bytes = min((int)S::BYTES, row_bytes - off);
+            uint8_t *slot = ring + p_slot * (R * S::SLOT);
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int64_t row = min(rg * R + r, M - 1);     // ragged tail: re-read the last row
-            const uint8_t *src = W + (size_t)row * row_stride + off;
-            uint8_t *d = slot + r * S::SLOT;
-            if (ALIGNED) {
-                for (int b = lane * 16; b < bytes; b += 32 * 16) cp_async16(d + b, src + b);
-            } else {
-                for (int b = lane * 2; b < bytes; b += 32 * 2)
-                    *reinterpret_cast<uint16_t *>(d + b) = *reinterpret_cast<const uint16_t *>(src + b);
+            for (int r = 0; r < R; ++r) {
+                const int row = min(p_rg * R + r, M - 1);       // ragged tail: re-read the last row
+                const uint8_t *src = W + (size_t)row * row_stride + off;
+                uint8_t *d = slot + r * S::SLOT;
+                if (ALIGNED) {
+                    for (int b = lane * 16; b < bytes; b += 32 * 16) cp_async16(d + b, src + b);
+                } else {
+                    for (int b = lane * 2; b < bytes; b += 32 * 2)
+                        *reinterpret_cast<uint16_t *>(d + b) = *reinterpret_cast<const uint16_t *>(src + b);
+                }
             }
+            if (++p_s == nstages) { p_s = 0; p_rg += tw; }
         }
+        p_slot = p_slot + 1 == STAGES ? 0 : p_slot + 1;
+        cp_async_commit();
     };
 
     float acc[R][NC];
@@ -70,36 +74,33 @@ gemv_kernel(const uint8_t *__restrict__ W, size_t row_stride, int64_t M, int64_t
         for (int c = 0; c < NC; ++c) acc[r][c] = 0.f;
 
 #pragma unroll
-    for (int i = 0; i < STAGES - 1; ++i) {
-        if (i < total) issue(i);
-        cp_async_commit();
-    }
-    for (int64_t i = 0; i < total; ++i) {
-        if (i + STAGES - 1 < total) issue(i + STAGES - 1);
-        cp_async_commit();
-        cp_async_wait<STAGES - 1>();
-        __syncwarp();
-        const int64_t s = i % nstages;
-        const uint8_t *slot = ring + (size_t)(i % STAGES) * (R * S::SLOT);
-        const uint32_t *srow[R];
+    for (int i = 0; i < STAGES - 1; ++i) issue();
+    int c_slot = 0;
+    for (int rg = gw; rg < n_rg; rg += tw) {
+        for (int s = 0; s < nstages; ++s) {
+            issue();
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();
+            const uint8_t *slot = ring + c_slot * (R * S::SLOT);
+            const uint32_t *srow[R];
 #pragma unroll
-        for (int r = 0; r < R; ++r) srow[r] = reinterpret_cast<const uint32_t *>(slot + r * S::SLOT);
-        gemv_lane_stage<TYPE, NC, R>(srow, lane, s, nblk, act, acc);
-        if (s == nstages - 1) {
-            const int64_t rg = gw + (i / nstages) * tw;
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-                for (int c = 0; c < NC; ++c) {
-                    float v = acc[r][c];
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-                    if (lane == 0 && rg * R + r < M) dst[rg * R + r + c * ldd] = v;
-                    acc[r][c] = 0.f;
-                }
+            for (int r = 0; r < R; ++r) srow[r] = reinterpret_cast<const uint32_t *>(slot + r * S::SLOT);
+            gemv_lane_stage<TYPE, NC, R>(srow, lane, s, nblk, act, acc);
+            c_slot = c_slot + 1 == STAGES ? 0 : c_slot + 1;
+            __syncwarp();
         }
-        __syncwarp();
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                float v = acc[r][c];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+                if (lane == 0 && rg * R + r < M) dst[(size_t)c * ldd + rg * R + r] = v;
+                acc[r][c] = 0.f;
+            }
     }
+    cp_async_wait<0>();
 }
 
 template <int TYPE, int NC, int R, int WARPS, int STAGES>
@@ -107,6 +108,8 @@ static b200q_status launch_one(b200q_ctx *ctx, const void *w, size_t row_stride,
                                const GemvAct &act, float *dst, int64_t ldd, bool aligned) {
     typedef GemvStage<TYPE> S;
     const size_t smem = (size_t)WARPS * STAGES * R * S::SLOT;
+    if (M > INT32_MAX / 2 || K / GemvFmt<TYPE>::BLK_W > INT32_MAX / 256 || ldd > INT32_MAX)
+        return fail(ctx, B200Q_UNSUPPORTED, "gemv: dimensions beyond 32-bit indexing");
     const int64_t n_rg = (M + R - 1) / R;
     int64_t blocks = (n_rg + WARPS - 1) / WARPS;
     const int64_t cap = (int64_t)ctx->sm_count * 16;     // enough CTAs to fill every SM several times over
@@ -117,7 +120,8 @@ static b200q_status launch_one(b200q_ctx *ctx, const void *w, size_t row_stride,
     auto kern = aligned ? kern_a : kern_u;
     if (smem > 48 * 1024)
         B200Q_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<(unsigned)blocks, WARPS * 32, smem, ctx->stream>>>((const uint8_t *)w, row_stride, M, K, act, dst, ldd);
+    kern<<<(unsigned)blocks, WARPS * 32, smem, ctx->stream>>>((const uint8_t *)w, row_stride, (int)M,
+                                                              (int)(K / GemvFmt<TYPE>::BLK_W), act, dst, (int)ldd);
     B200Q_CUDA(ctx, cudaGetLastError());
     return B200Q_OK;
 }
@@ -126,7 +130,7 @@ template <int TYPE, int NC>
 static b200q_status launch_nc(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K,
                               const GemvAct &act, float *dst, int64_t ldd, bool aligned) {
     // rows per warp pass: two while the activation registers allow it
-    return launch_one<TYPE, NC, (NC <= 4 ? 2 : 1), 4, 4>(ctx, w, row_stride, M, K, act, dst, ldd, aligned);
+    return launch_one<TYPE, NC, (NC <= 4 ? 2 : 1), 4, 3>(ctx, w, row_stride, M, K, act, dst, ldd, aligned);
 }
 
 template <int TYPE>
@@ -151,7 +155,9 @@ b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_str
     act.q = av.codes + col0 * K;
     act.d16 = av.d16 ? av.d16 + col0 * (K / 32) : nullptr;
     act.d32 = av.d32 ? av.d32 + col0 * (K / 256) : nullptr;
-    act.K = K;
+    act.s32 = av.s32 ? av.s32 + col0 * (K / 32) : nullptr;
+    act.s16 = av.s16 ? av.s16 + col0 * (K / 16) : nullptr;
+    act.K = (int)K;
     TypeInfo ti;
     if (!type_info(type, &ti)) return fail(ctx, B200Q_UNSUPPORTED, "gemv: type %d", type);
     const size_t row_bytes = (size_t)(K / ti.block) * ti.bytes;

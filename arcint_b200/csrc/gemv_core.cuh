@@ -2,17 +2,23 @@
 // rows and NC activation columns. Host+device text: the kernel (gemv.cu) calls it from
 // 32 lanes of a warp; the device-free emulation (emul.cpp) calls it for lane 0..31 in turn.
 //
-// A "stage" is the chunk of a row a warp decodes in one pass: 1024 weights (2048 for
-// Q6_K, in two sub-passes), chosen so its byte size is a multiple of 16 for every type and
-// stages can be fetched with 16-byte copies:
-//   Q4_0 32 blocks = 576 B    Q8_0 32 blocks = 1088 B   Q4_K 4 blocks = 576 B
-//   IQ4_XS 4 blocks = 544 B   Q6_K 8 blocks = 1680 B
-// Each lane owns 32 weights of a pass. Integer block dots are exact (dp4a against the
-// int8 activation codes); float enters once per 32 (Q4_0/Q8_0: d_w * d_x) or once per
-// 256-block (K types: integer sub-scales first), the form of ggml's CPU vec_dot and of the
-// reference GEMV bodies mv_q45_K / mv_q6_K / mv_q4_0 / mv_iq
-// (marfrit/arcint contrib/llama.cpp/patches/0000-01-kquant-integer-dpas.patch:3740-3874,
-// 0000-02-lowbit-iq-types.patch:5947-5955, 6100-6130) without their residual term.
+// A "stage" is 2048 weights of a row (64 per lane); its byte size is a multiple of 16 for
+// every type, so stages are fetched with 16-byte copies:
+//   Q4_0 64 blocks = 1152 B   Q8_0 64 blocks = 2176 B   Q4_K 8 blocks = 1152 B
+//   IQ4_XS 8 blocks = 1088 B  Q6_K 8 blocks = 1680 B
+// The kernel is bound by instruction issue as much as by HBM (a B200 SM receives ~23 weight
+// bytes per clock: about 100 lane instructions per 32 four-bit weights), so the lane code is
+// written for instruction count: nibbles stay unsigned (the -8 / -32 offsets ride on the
+// activation block sums the quantizer already made), high nibbles are multiplied in place
+// (x16, unsigned dp4a) and the 1/16 is folded into the float scale, sub-scales are unpacked
+// four at a time.
+//
+// Integer block dots are exact (dp4a against the int8 activation codes); float enters once
+// per 32 (Q4_0/Q8_0: d_w * d_x) or once per 256-block (K types: integer sub-scales first),
+// the form of ggml's CPU vec_dot and of the reference GEMV bodies mv_q45_K / mv_q6_K /
+// mv_q4_0 / mv_iq (marfrit/arcint contrib/llama.cpp/patches/
+// 0000-01-kquant-integer-dpas.patch:3740-3874, 0000-02-lowbit-iq-types.patch:5947-5955,
+// 6100-6130) without their residual term.
 #pragma once
 
 #include "formats.cuh"
@@ -20,208 +26,283 @@
 namespace b200q {
 
 template <int TYPE> struct GemvFmt;
-template <> struct GemvFmt<B200Q_TYPE_Q4_0>   { enum { BLK_W = 32,  BLK_B = 18,  STAGE_BLOCKS = 32, SUBS = 1 }; };
-template <> struct GemvFmt<B200Q_TYPE_Q8_0>   { enum { BLK_W = 32,  BLK_B = 34,  STAGE_BLOCKS = 32, SUBS = 1 }; };
-template <> struct GemvFmt<B200Q_TYPE_Q4_K>   { enum { BLK_W = 256, BLK_B = 144, STAGE_BLOCKS = 4,  SUBS = 1 }; };
-template <> struct GemvFmt<B200Q_TYPE_IQ4_XS> { enum { BLK_W = 256, BLK_B = 136, STAGE_BLOCKS = 4,  SUBS = 1 }; };
-template <> struct GemvFmt<B200Q_TYPE_Q6_K>   { enum { BLK_W = 256, BLK_B = 210, STAGE_BLOCKS = 8,  SUBS = 2 }; };
+template <> struct GemvFmt<B200Q_TYPE_Q4_0>   { enum { BLK_W = 32,  BLK_B = 18,  STAGE_BLOCKS = 64 }; };
+template <> struct GemvFmt<B200Q_TYPE_Q8_0>   { enum { BLK_W = 32,  BLK_B = 34,  STAGE_BLOCKS = 64 }; };
+template <> struct GemvFmt<B200Q_TYPE_Q4_K>   { enum { BLK_W = 256, BLK_B = 144, STAGE_BLOCKS = 8 }; };
+template <> struct GemvFmt<B200Q_TYPE_IQ4_XS> { enum { BLK_W = 256, BLK_B = 136, STAGE_BLOCKS = 8 }; };
+template <> struct GemvFmt<B200Q_TYPE_Q6_K>   { enum { BLK_W = 256, BLK_B = 210, STAGE_BLOCKS = 8 }; };
 
 template <int TYPE> struct GemvStage {
     enum { BYTES = GemvFmt<TYPE>::STAGE_BLOCKS * GemvFmt<TYPE>::BLK_B,     // multiple of 16
            SLOT  = ((BYTES + 4 + 15) / 16) * 16 };                         // + one word of over-read
 };
 
-// Activation pointers already offset to the first column of this launch.
+// Activation pointers already offset to the first column of this launch; column c is
+// `cstride` columns of the quantized buffer further on (1 for a dense product).
 struct GemvAct {
-    const int8_t   *q;     // [NC][K]
-    const uint16_t *d16;   // [NC][K/32]   per-32 form
-    const float    *d32;   // [NC][K/256]  per-256 form
-    int64_t         K;
+    const int8_t   *q;     // [ ][K]      codes
+    const uint16_t *d16;   // [ ][K/32]   per-32 form: fp16 scales
+    const float    *d32;   // [ ][K/256]  per-256 form: f32 scales
+    const int16_t  *s32;   // [ ][K/32]   sums of each 32 codes (both forms)
+    const int16_t  *s16;   // [ ][K/16]   sums of each 16 codes (per-256 form)
+    int             K;
 };
+
+// signed x signed and unsigned x signed 4-way byte dot products
+B200Q_HD int dp4a_ss(uint32_t a, int b, int c) { return hd_dp4a(a, b, c); }
+B200Q_HD int dp4a_us(uint32_t a, int b, int c) {
+#ifdef __CUDA_ARCH__
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+#else
+    for (int i = 0; i < 4; ++i) c += (int)(uint8_t)(a >> (8 * i)) * (int)(int8_t)((uint32_t)b >> (8 * i));
+    return c;
+#endif
+}
+
+B200Q_HD int ld_s16(const int16_t *p) {
+#ifdef __CUDA_ARCH__
+    return (int)__ldg(p);
+#else
+    return (int)*p;
+#endif
+}
+B200Q_HD uint32_t ld_u32(const void *p) {
+#ifdef __CUDA_ARCH__
+    return __ldg(reinterpret_cast<const unsigned int *>(p));
+#else
+    uint32_t v;
+    memcpy(&v, p, 4);
+    return v;
+#endif
+}
+B200Q_HD float ld_f32(const float *p) {
+#ifdef __CUDA_ARCH__
+    return __ldg(p);
+#else
+    return *p;
+#endif
+}
+B200Q_HD uint16_t ld_u16(const uint16_t *p) {
+#ifdef __CUDA_ARCH__
+    return __ldg(p);
+#else
+    return *p;
+#endif
+}
+B200Q_HD int sext8(uint32_t v) { return (int)(int8_t)(v & 0xFFu); }
+B200Q_HD int sext16(uint32_t v) { return (int)(int16_t)(v & 0xFFFFu); }
 
 // srow[r]: staged words of row r for stage s. nblk: blocks per row. acc[r][c] += partial.
 template <int TYPE, int NC, int R>
-B200Q_HD void gemv_lane_stage(const uint32_t *const (&srow)[R], int lane, int64_t s, int64_t nblk,
+B200Q_HD void gemv_lane_stage(const uint32_t *const (&srow)[R], int lane, int s, int nblk,
                               const GemvAct &act, float (&acc)[R][NC]) {
     typedef GemvFmt<TYPE> F;
-    const int64_t K = act.K;
+    const int K = act.K;
 
     if (TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_Q8_0) {
-        const int64_t blk = s * F::STAGE_BLOCKS + lane;
-        if (blk >= nblk) return;
-        I4 xa[NC], xb[NC];
-        float dx[NC];
+        // two 32-blocks per lane: lane and lane + 32 of the stage
 #pragma unroll
-        for (int c = 0; c < NC; ++c) {
-            const int8_t *xp = act.q + c * K + 32 * blk;
-            xa[c] = hd_ld16(xp);
-            xb[c] = hd_ld16(xp + 16);
-            dx[c] = hd_half_bits(act.d16[c * (K / 32) + blk]);
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const uint32_t off = (uint32_t)F::BLK_B * (uint32_t)lane;
-            const float d = hd_half_bits(stage_u16(srow[r], off));
-            uint32_t w[8];
-            if (TYPE == B200Q_TYPE_Q4_0) {
-                uint32_t q[4];
-                stage_words<4>(srow[r], off + 2, q);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    w[j]     = nib_minus8(q[j] & 0x0F0F0F0Fu);          // weights 4j .. 4j+3
-                    w[j + 4] = nib_minus8((q[j] >> 4) & 0x0F0F0F0Fu);   // weights 16+4j ..
-                }
-            } else {
-                stage_words<8>(srow[r], off + 2, w);
-            }
+        for (int u = 0; u < 2; ++u) {
+            const int sblk = 32 * u + lane, blk = s * F::STAGE_BLOCKS + sblk;
+            if (blk >= nblk) continue;
+            I4 xa[NC], xb[NC];
+            float dx[NC];
+            int bs8[NC];
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
-                int si = 0;
-                si = hd_dp4a(w[0], xa[c].x, si); si = hd_dp4a(w[1], xa[c].y, si);
-                si = hd_dp4a(w[2], xa[c].z, si); si = hd_dp4a(w[3], xa[c].w, si);
-                si = hd_dp4a(w[4], xb[c].x, si); si = hd_dp4a(w[5], xb[c].y, si);
-                si = hd_dp4a(w[6], xb[c].z, si); si = hd_dp4a(w[7], xb[c].w, si);
-                acc[r][c] += (float)si * (d * dx[c]);
+                const int8_t *xp = act.q + (size_t)c * K + 32 * blk;
+                xa[c] = hd_ld16(xp);
+                xb[c] = hd_ld16(xp + 16);
+                dx[c] = hd_half_bits(ld_u16(act.d16 + (size_t)c * (K / 32) + blk));
+                if (TYPE == B200Q_TYPE_Q4_0) {
+                    bs8[c] = -128 * ld_s16(act.s32 + (size_t)c * (K / 32) + blk);   // -8 * 16 * sum(x)
+                    dx[c] *= 0.0625f;                                                // the nibble dot is kept x16
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint32_t off = (uint32_t)F::BLK_B * (uint32_t)sblk;
+                const float d = hd_half_bits(stage_u16(srow[r], off));
+                if (TYPE == B200Q_TYPE_Q4_0) {
+                    uint32_t q[4];
+                    stage_words<4>(srow[r], off + 2, q);
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        // weights 4j..4j+3 in the low nibbles, 16+4j.. in the high ones (left x16)
+                        int lo = 0, hi = 0;
+                        lo = dp4a_ss(q[0] & 0x0F0F0F0Fu, xa[c].x, lo); lo = dp4a_ss(q[1] & 0x0F0F0F0Fu, xa[c].y, lo);
+                        lo = dp4a_ss(q[2] & 0x0F0F0F0Fu, xa[c].z, lo); lo = dp4a_ss(q[3] & 0x0F0F0F0Fu, xa[c].w, lo);
+                        hi = dp4a_us(q[0] & 0xF0F0F0F0u, xb[c].x, hi); hi = dp4a_us(q[1] & 0xF0F0F0F0u, xb[c].y, hi);
+                        hi = dp4a_us(q[2] & 0xF0F0F0F0u, xb[c].z, hi); hi = dp4a_us(q[3] & 0xF0F0F0F0u, xb[c].w, hi);
+                        const int si = 16 * lo + hi + bs8[c];                       // 16 * sum((n - 8) x)
+                        acc[r][c] += (float)si * (d * dx[c]);
+                    }
+                } else {
+                    uint32_t w[8];
+                    stage_words<8>(srow[r], off + 2, w);
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        int si = 0;
+                        si = dp4a_ss(w[0], xa[c].x, si); si = dp4a_ss(w[1], xa[c].y, si);
+                        si = dp4a_ss(w[2], xa[c].z, si); si = dp4a_ss(w[3], xa[c].w, si);
+                        si = dp4a_ss(w[4], xb[c].x, si); si = dp4a_ss(w[5], xb[c].y, si);
+                        si = dp4a_ss(w[6], xb[c].z, si); si = dp4a_ss(w[7], xb[c].w, si);
+                        acc[r][c] += (float)si * (d * dx[c]);
+                    }
+                }
             }
         }
     } else if (TYPE == B200Q_TYPE_Q4_K) {
-        // lane -> block sb of the stage, 32-byte group g, half h: 16 bytes of nibbles =
-        // weights 16h..16h+15 of sub-block 2g (low) and of sub-block 2g+1 (high)
-        const int sb = lane >> 3, g = (lane & 7) >> 1, h = lane & 1;
-        const int64_t blk = s * F::STAGE_BLOCKS + sb;
+        // lane -> block sb of the stage and 32-byte group g: sub-blocks 2g (low nibbles) and
+        // 2g+1 (high nibbles), 64 weights
+        const int sb = lane >> 2, g = lane & 3;
+        const int blk = s * F::STAGE_BLOCKS + sb;
         if (blk >= nblk) return;
-        I4 xl[NC], xh[NC];
-        float dxl[NC], dxh[NC], dx[NC];
+        I4 xl[NC][2], xh[NC][2];
+        float dxs[NC], dxm[NC];
+        int bs0[NC], bs1[NC];
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
-            const int8_t *xp = act.q + c * K + 256 * blk + 64 * g + 16 * h;
-            xl[c] = hd_ld16(xp);
-            xh[c] = hd_ld16(xp + 32);
-            dx[c] = act.d32[c * (K / 256) + blk];
-            // this lane's share of the sub-block sums the min term needs
-            int sl = 0, sh = 0;
-            sl = hd_dp4a(0x01010101u, xl[c].x, sl); sl = hd_dp4a(0x01010101u, xl[c].y, sl);
-            sl = hd_dp4a(0x01010101u, xl[c].z, sl); sl = hd_dp4a(0x01010101u, xl[c].w, sl);
-            sh = hd_dp4a(0x01010101u, xh[c].x, sh); sh = hd_dp4a(0x01010101u, xh[c].y, sh);
-            sh = hd_dp4a(0x01010101u, xh[c].z, sh); sh = hd_dp4a(0x01010101u, xh[c].w, sh);
-            dxl[c] = dx[c] * (float)sl;
-            dxh[c] = dx[c] * (float)sh;
+            const int8_t *xp = act.q + (size_t)c * K + 256 * blk + 64 * g;
+            xl[c][0] = hd_ld16(xp);      xl[c][1] = hd_ld16(xp + 16);
+            xh[c][0] = hd_ld16(xp + 32); xh[c][1] = hd_ld16(xp + 48);
+            const float dx = ld_f32(act.d32 + (size_t)c * (K / 256) + blk);
+            dxs[c] = dx * 0.0625f;       // both nibble dots are kept x16
+            dxm[c] = dx;
+            const uint32_t bp = ld_u32(act.s32 + (size_t)c * (K / 32) + 8 * blk + 2 * g);
+            bs0[c] = sext16(bp);
+            bs1[c] = sext16(bp >> 16);
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const uint32_t *bw = srow[r] + sb * (144 / 4);
-            const uint32_t hd = bw[0];
+            const uint32_t hd = bw[0], s0 = bw[1], s1 = bw[2], s2 = bw[3];
             const float d = hd_half_bits((uint16_t)hd), dmin = hd_half_bits((uint16_t)(hd >> 16));
-            int sc0, m0, sc1, m1;
-            q4k_scale_min(bw[1], bw[2], bw[3], 2 * g, &sc0, &m0);
-            q4k_scale_min(bw[1], bw[2], bw[3], 2 * g + 1, &sc1, &m1);
-            const uint32_t *qp = bw + 4 + 8 * g + 4 * h;
-            uint32_t lo[4], hi[4];
+            // the 6-bit scales / mins of sub-blocks 0..3 and 4..7 as four bytes each
+            const uint32_t scw = g < 2 ? (s0 & 0x3F3F3F3Fu) : ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u));
+            const uint32_t mnw = g < 2 ? (s1 & 0x3F3F3F3Fu) : (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u));
+            const int sh = 16 * (g & 1);
+            const int sc0 = (int)((scw >> sh) & 0xFFu) * 16, sc1 = (int)((scw >> (sh + 8)) & 0xFFu);
+            const int m0 = (int)((mnw >> sh) & 0xFFu), m1 = (int)((mnw >> (sh + 8)) & 0xFFu);
+            const uint32_t *qp = bw + 4 + 8 * g;
+            uint32_t q[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t q = qp[j];
-                lo[j] = q & 0x0F0F0F0Fu;
-                hi[j] = (q >> 4) & 0x0F0F0F0Fu;
-            }
-            const float dm0 = dmin * (float)m0, dm1 = dmin * (float)m1;
+            for (int j = 0; j < 8; ++j) q[j] = qp[j];
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
                 int il = 0, ih = 0;
-                il = hd_dp4a(lo[0], xl[c].x, il); il = hd_dp4a(lo[1], xl[c].y, il);
-                il = hd_dp4a(lo[2], xl[c].z, il); il = hd_dp4a(lo[3], xl[c].w, il);
-                ih = hd_dp4a(hi[0], xh[c].x, ih); ih = hd_dp4a(hi[1], xh[c].y, ih);
-                ih = hd_dp4a(hi[2], xh[c].z, ih); ih = hd_dp4a(hi[3], xh[c].w, ih);
-                const int si = sc0 * il + sc1 * ih;
-                acc[r][c] += (d * dx[c]) * (float)si - (dm0 * dxl[c] + dm1 * dxh[c]);
+                il = dp4a_ss(q[0] & 0x0F0F0F0Fu, xl[c][0].x, il); il = dp4a_ss(q[1] & 0x0F0F0F0Fu, xl[c][0].y, il);
+                il = dp4a_ss(q[2] & 0x0F0F0F0Fu, xl[c][0].z, il); il = dp4a_ss(q[3] & 0x0F0F0F0Fu, xl[c][0].w, il);
+                il = dp4a_ss(q[4] & 0x0F0F0F0Fu, xl[c][1].x, il); il = dp4a_ss(q[5] & 0x0F0F0F0Fu, xl[c][1].y, il);
+                il = dp4a_ss(q[6] & 0x0F0F0F0Fu, xl[c][1].z, il); il = dp4a_ss(q[7] & 0x0F0F0F0Fu, xl[c][1].w, il);
+                ih = dp4a_us(q[0] & 0xF0F0F0F0u, xh[c][0].x, ih); ih = dp4a_us(q[1] & 0xF0F0F0F0u, xh[c][0].y, ih);
+                ih = dp4a_us(q[2] & 0xF0F0F0F0u, xh[c][0].z, ih); ih = dp4a_us(q[3] & 0xF0F0F0F0u, xh[c][0].w, ih);
+                ih = dp4a_us(q[4] & 0xF0F0F0F0u, xh[c][1].x, ih); ih = dp4a_us(q[5] & 0xF0F0F0F0u, xh[c][1].y, ih);
+                ih = dp4a_us(q[6] & 0xF0F0F0F0u, xh[c][1].z, ih); ih = dp4a_us(q[7] & 0xF0F0F0F0u, xh[c][1].w, ih);
+                const int si = sc0 * il + sc1 * ih;                  // 16 * sum_sb sc * dot
+                const int sm = m0 * bs0[c] + m1 * bs1[c];
+                acc[r][c] += (d * dxs[c]) * (float)si - (dmin * dxm[c]) * (float)sm;
             }
         }
     } else if (TYPE == B200Q_TYPE_IQ4_XS) {
-        // lane -> block sb, sub-block p: 16 bytes, low nibbles = weights 0..15, high = 16..31
-        const int sb = lane >> 3, p = lane & 7;
-        const int64_t blk = s * F::STAGE_BLOCKS + sb;
+        // lane -> block sb and sub-block pair pp: 32 bytes = sub-blocks 2pp and 2pp+1
+        const int sb = lane >> 2, pp = lane & 3;
+        const int blk = s * F::STAGE_BLOCKS + sb;
         if (blk >= nblk) return;
-        I4 xa[NC], xb[NC];
+        I4 x[NC][4];
         float dx[NC];
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
-            const int8_t *xp = act.q + c * K + 256 * blk + 32 * p;
-            xa[c] = hd_ld16(xp);
-            xb[c] = hd_ld16(xp + 16);
-            dx[c] = act.d32[c * (K / 256) + blk];
+            const int8_t *xp = act.q + (size_t)c * K + 256 * blk + 64 * pp;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[c][j] = hd_ld16(xp + 16 * j);
+            dx[c] = ld_f32(act.d32 + (size_t)c * (K / 256) + blk);
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const uint32_t *bw = srow[r] + sb * (136 / 4);
             const uint32_t hd = bw[0];
             const float d = hd_half_bits((uint16_t)hd);
-            const int ls = iq4xs_ls(hd >> 16, bw[1], p) - 32;
-            const uint32_t *qp = bw + 2 + 4 * p;
-            uint32_t w[8];
+            const int ls0 = iq4xs_ls(hd >> 16, bw[1], 2 * pp) - 32, ls1 = iq4xs_ls(hd >> 16, bw[1], 2 * pp + 1) - 32;
+            const uint32_t *qp = bw + 2 + 8 * pp;
+            uint32_t w[16];      // sub-block 2pp: w[0..3] weights 0..15, w[4..7] weights 16..31; then 2pp+1
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t q = qp[j];
-                w[j]     = iq4nl_lookup4(q & 0x0F0F0F0Fu);
-                w[j + 4] = iq4nl_lookup4((q >> 4) & 0x0F0F0F0Fu);
-            }
-            const float dl = d * (float)ls;
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t q = qp[4 * h + j];
+                    w[8 * h + j]     = iq4nl_lookup4(q & 0x0F0F0F0Fu);
+                    w[8 * h + j + 4] = iq4nl_lookup4((q >> 4) & 0x0F0F0F0Fu);
+                }
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
-                int si = 0;
-                si = hd_dp4a(w[0], xa[c].x, si); si = hd_dp4a(w[1], xa[c].y, si);
-                si = hd_dp4a(w[2], xa[c].z, si); si = hd_dp4a(w[3], xa[c].w, si);
-                si = hd_dp4a(w[4], xb[c].x, si); si = hd_dp4a(w[5], xb[c].y, si);
-                si = hd_dp4a(w[6], xb[c].z, si); si = hd_dp4a(w[7], xb[c].w, si);
-                acc[r][c] += (dl * dx[c]) * (float)si;
+                int i0 = 0, i1 = 0;
+                i0 = dp4a_ss(w[0], x[c][0].x, i0); i0 = dp4a_ss(w[1], x[c][0].y, i0);
+                i0 = dp4a_ss(w[2], x[c][0].z, i0); i0 = dp4a_ss(w[3], x[c][0].w, i0);
+                i0 = dp4a_ss(w[4], x[c][1].x, i0); i0 = dp4a_ss(w[5], x[c][1].y, i0);
+                i0 = dp4a_ss(w[6], x[c][1].z, i0); i0 = dp4a_ss(w[7], x[c][1].w, i0);
+                i1 = dp4a_ss(w[8], x[c][2].x, i1);  i1 = dp4a_ss(w[9], x[c][2].y, i1);
+                i1 = dp4a_ss(w[10], x[c][2].z, i1); i1 = dp4a_ss(w[11], x[c][2].w, i1);
+                i1 = dp4a_ss(w[12], x[c][3].x, i1); i1 = dp4a_ss(w[13], x[c][3].y, i1);
+                i1 = dp4a_ss(w[14], x[c][3].z, i1); i1 = dp4a_ss(w[15], x[c][3].w, i1);
+                acc[r][c] += (d * dx[c]) * (float)(ls0 * i0 + ls1 * i1);
             }
         }
     } else if (TYPE == B200Q_TYPE_Q6_K) {
-        // two sub-passes of four blocks; lane -> block, half n, positions t0..t0+7 of the
-        // four 32-weight parts of that half (each part in one 16-wide scale group)
+        // lane -> block sb, half n, positions t0..t0+15 of the four 32-weight parts of that
+        // half: each part's 16 weights are exactly one scale group
+        const int sb = lane >> 2, n = (lane >> 1) & 1, hi16 = lane & 1, t0 = 16 * hi16;
+        const int blk = s * F::STAGE_BLOCKS + sb;
+        if (blk >= nblk) return;
+        I4 x[NC][4];
+        float dx[NC];
+        int s32x[NC][4];         // 32 * (sum of the 16 activation codes of part p)
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int sb = 4 * u + (lane >> 3), n = (lane & 7) >> 2, t0 = 8 * (lane & 3);
-            const int64_t blk = s * F::STAGE_BLOCKS + sb;
-            if (blk >= nblk) continue;
-            I2 x[NC][4];
-            float dx[NC];
+        for (int c = 0; c < NC; ++c) {
+            const int8_t *xp = act.q + (size_t)c * K + 256 * blk + 128 * n + t0;
 #pragma unroll
-            for (int c = 0; c < NC; ++c) {
-                const int8_t *xp = act.q + c * K + 256 * blk + 128 * n + t0;
+            for (int p = 0; p < 4; ++p) x[c][p] = hd_ld16(xp + 32 * p);
+            dx[c] = ld_f32(act.d32 + (size_t)c * (K / 256) + blk);
+            // sums of groups 8n + 2p + hi16, p = 0..3: eight int16 from one 16-byte load
+            const I4 sv = hd_ld16(act.s16 + (size_t)c * (K / 16) + 16 * blk + 8 * n);
+            const uint32_t a0 = (uint32_t)sv.x >> (16 * hi16), a1 = (uint32_t)sv.y >> (16 * hi16);
+            const uint32_t a2 = (uint32_t)sv.z >> (16 * hi16), a3 = (uint32_t)sv.w >> (16 * hi16);
+            s32x[c][0] = 32 * sext16(a0); s32x[c][1] = 32 * sext16(a1);
+            s32x[c][2] = 32 * sext16(a2); s32x[c][3] = 32 * sext16(a3);
+        }
 #pragma unroll
-                for (int p = 0; p < 4; ++p) x[c][p] = hd_ld8(xp + 32 * p);
-                dx[c] = act.d32[c * (K / 256) + blk];
+        for (int r = 0; r < R; ++r) {
+            const uint32_t off = 210u * (uint32_t)sb;
+            uint32_t qa[4], qb[4], qh[4], sw[2];
+            stage_words<4>(srow[r], off + 64 * n + t0, qa);            // parts 0 (low) and 2 (high)
+            stage_words<4>(srow[r], off + 64 * n + 32 + t0, qb);       // parts 1 and 3
+            stage_words<4>(srow[r], off + 128 + 32 * n + t0, qh);
+            stage_words<2>(srow[r], off + 192 + 8 * n, sw);            // the half's eight scales
+            const float d = hd_half_bits(stage_u16(srow[r], off + 208));
+            const uint32_t w0 = sw[0] >> (8 * hi16), w1 = sw[1] >> (8 * hi16);
+            const int sc0 = sext8(w0), sc1 = sext8(w0 >> 16), sc2 = sext8(w1), sc3 = sext8(w1 >> 16);
+            uint32_t w[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                w[0][j] = (qa[j] & 0x0F0F0F0Fu)        | ((qh[j] << 4) & 0x30303030u);
+                w[1][j] = (qb[j] & 0x0F0F0F0Fu)        | ((qh[j] << 2) & 0x30303030u);
+                w[2][j] = ((qa[j] >> 4) & 0x0F0F0F0Fu) | (qh[j] & 0x30303030u);
+                w[3][j] = ((qb[j] >> 4) & 0x0F0F0F0Fu) | ((qh[j] >> 2) & 0x30303030u);
             }
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const uint32_t off = 210u * (uint32_t)sb;
-                uint32_t qa[2], qb[2], qh[2];
-                stage_words<2>(srow[r], off + 64 * n + t0, qa);            // parts 0 (low) and 2 (high)
-                stage_words<2>(srow[r], off + 64 * n + 32 + t0, qb);       // parts 1 and 3
-                stage_words<2>(srow[r], off + 128 + 32 * n + t0, qh);
-                const float d = hd_half_bits(stage_u16(srow[r], off + 208));
-                int sc[4];
+            for (int c = 0; c < NC; ++c) {
+                int ip[4];
 #pragma unroll
-                for (int p = 0; p < 4; ++p)
-                    sc[p] = (int)(int8_t)stage_u8(srow[r], off + 192 + 8 * n + 2 * p + (t0 >= 16 ? 1 : 0));
-                uint32_t w[4][2];
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    w[0][j] = six_minus32((qa[j] & 0x0F0F0F0Fu)        | ((qh[j] & 0x03030303u) << 4));
-                    w[1][j] = six_minus32((qb[j] & 0x0F0F0F0Fu)        | (((qh[j] >> 2) & 0x03030303u) << 4));
-                    w[2][j] = six_minus32(((qa[j] >> 4) & 0x0F0F0F0Fu) | (((qh[j] >> 4) & 0x03030303u) << 4));
-                    w[3][j] = six_minus32(((qb[j] >> 4) & 0x0F0F0F0Fu) | (((qh[j] >> 6) & 0x03030303u) << 4));
+                for (int p = 0; p < 4; ++p) {
+                    int v = -s32x[c][p];                               // sum((q - 32) x) = sum(q x) - 32 sum(x)
+                    v = dp4a_ss(w[p][0], x[c][p].x, v); v = dp4a_ss(w[p][1], x[c][p].y, v);
+                    v = dp4a_ss(w[p][2], x[c][p].z, v); v = dp4a_ss(w[p][3], x[c][p].w, v);
+                    ip[p] = v;
                 }
-#pragma unroll
-                for (int c = 0; c < NC; ++c) {
-                    int si = 0;
-#pragma unroll
-                    for (int p = 0; p < 4; ++p) {
-                        int ip = hd_dp4a(w[p][0], x[c][p].x, 0);
-                        ip = hd_dp4a(w[p][1], x[c][p].y, ip);
-                        si += sc[p] * ip;
-                    }
-                    acc[r][c] += (d * dx[c]) * (float)si;
-                }
+                const int si = sc0 * ip[0] + sc1 * ip[1] + sc2 * ip[2] + sc3 * ip[3];
+                acc[r][c] += (d * dx[c]) * (float)si;
             }
         }
     }

@@ -9,6 +9,8 @@
 //           (0000-01-kquant-integer-dpas.patch:1862-1889) -- scale bm/127 in f32, code =
 //           round-to-nearest-even of x * (127/bm), a block below 1e-30 quantizes to zeros,
 //           plus the integer sum of each 32 codes.
+// Both also write the integer sum of each 32 codes (and of each 16, per-256 form): the
+// kernels keep weight codes unsigned and take the -8 / -32 offsets from these sums.
 // Column c of src1 (flattened over dimensions 1..3) lands at codes + c*K.
 #include "formats.cuh"
 #include "common.cuh"
@@ -28,7 +30,8 @@ __device__ __forceinline__ const float *col_ptr(const ColAddr &a, int64_t c) {
 
 // 8 lanes per 32-block, 4 values per lane
 __global__ void __launch_bounds__(256)
-quantize_q8_0_kernel(ColAddr src, int64_t K, int64_t ncols, int8_t *__restrict__ codes, uint16_t *__restrict__ d16) {
+quantize_q8_0_kernel(ColAddr src, int64_t K, int64_t ncols, int8_t *__restrict__ codes, uint16_t *__restrict__ d16,
+                     int16_t *__restrict__ sums32) {
     const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t per_col = K / 4;
     const int64_t c = gid / per_col, i4 = gid % per_col;
@@ -39,21 +42,28 @@ quantize_q8_0_kernel(ColAddr src, int64_t K, int64_t ncols, int8_t *__restrict__
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 4));
-    if (!live) return;
     const float d = __fdiv_rn(amax, 127.f);
     const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;
     const int q0 = (int)roundf(__fmul_rn(v.x, id)), q1 = (int)roundf(__fmul_rn(v.y, id));
     const int q2 = (int)roundf(__fmul_rn(v.z, id)), q3 = (int)roundf(__fmul_rn(v.w, id));
+    int sum = q0 + q1 + q2 + q3;
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+    if (!live) return;
     const uint32_t packed = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
                             ((uint32_t)(q3 & 0xFF) << 24);
     reinterpret_cast<uint32_t *>(codes + c * K)[i4] = packed;
-    if ((i4 & 7) == 0) d16[c * (K / 32) + i4 / 8] = __half_as_ushort(__float2half_rn(d));
+    if ((i4 & 7) == 0) {
+        d16[c * (K / 32) + i4 / 8] = __half_as_ushort(__float2half_rn(d));
+        sums32[c * (K / 32) + i4 / 8] = (int16_t)sum;
+    }
 }
 
 // one warp per 256-block, 8 values per lane
 __global__ void __launch_bounds__(256)
 quantize_q8_256_kernel(ColAddr src, int64_t K, int64_t ncols, int8_t *__restrict__ codes, float *__restrict__ d32,
-                       int16_t *__restrict__ bsums) {
+                       int16_t *__restrict__ bsums, int16_t *__restrict__ bsums16) {
     const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int64_t per_col = K / 256;
@@ -79,15 +89,16 @@ quantize_q8_256_kernel(ColAddr src, int64_t K, int64_t ncols, int8_t *__restrict
         p0 |= (uint32_t)(q[i] & 0xFF) << (8 * i);
         p1 |= (uint32_t)(q[i + 4] & 0xFF) << (8 * i);
     }
-    s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);      // a 32-block is four lanes
-    s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);      // a group of 16 is two lanes
+    if ((lane & 1) == 0) bsums16[c * (K / 16) + 16 * b + lane / 2] = (int16_t)s;
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);      // a 32-block is four lanes
     *reinterpret_cast<uint2 *>(codes + c * K + 256 * b + 8 * lane) = make_uint2(p0, p1);
     if ((lane & 3) == 0) bsums[c * (K / 32) + 8 * b + lane / 4] = (int16_t)s;
     if (lane == 0) d32[c * per_col + b] = __fdiv_rn(bm, 127.f);
 }
 
 b200q_status launch_quantize_act(b200q_ctx *ctx, int form, const b200q_tensor *src1, int8_t *codes, void *scales,
-                                 int16_t *bsums) {
+                                 int16_t *bsums, int16_t *bsums16) {
     const int64_t K = src1->ne[0];
     const int64_t ncols = src1->ne[1] * src1->ne[2] * src1->ne[3];
     if (ncols == 0) return B200Q_OK;
@@ -101,12 +112,12 @@ b200q_status launch_quantize_act(b200q_ctx *ctx, int form, const b200q_tensor *s
     if (form == ACT_Q8_0) {
         const int64_t threads = ncols * (K / 4);
         quantize_q8_0_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, ctx->stream>>>(a, K, ncols, codes,
-                                                                                       (uint16_t *)scales);
+                                                                                       (uint16_t *)scales, bsums);
         count(ctx, ST_QUANT_Q8_0);
     } else {
         const int64_t warps = ncols * (K / 256);
-        quantize_q8_256_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, ctx->stream>>>(a, K, ncols, codes,
-                                                                                            (float *)scales, bsums);
+        quantize_q8_256_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, ctx->stream>>>(
+            a, K, ncols, codes, (float *)scales, bsums, bsums16);
         count(ctx, ST_QUANT_Q8_256);
     }
     B200Q_CUDA(ctx, cudaGetLastError());

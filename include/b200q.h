@@ -148,7 +148,7 @@ B200Q_API b200q_status b200q_flush_l2(b200q_ctx *ctx);
 
 /* Debug views of what the kernels see, for bit-exact parity tests: the quantized
  * activation (codes [N][K] int8; scales fp16 [N][K/32] for Q4_0/Q8_0 weights or f32
- * [N][K/256] for the 256-block types; sums int16 [N][K/32], 256-block types only) and
+ * [N][K/256] for the 256-block types; sums int16 [N][K/32] of each 32 codes) and
  * the dequantized weight rows the device decoders produce (f32 [M][K]). */
 B200Q_API b200q_status b200q_debug_quantize_act(b200q_ctx *ctx, int weight_type, const b200q_tensor *src1,
                                                 void *dev_codes, void *dev_scales, void *dev_sums);

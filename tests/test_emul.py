@@ -20,7 +20,7 @@ def emul():
         so = B.build_emul()
         E = C.CDLL(so)
         vp, i64 = C.c_void_p, C.c_int64
-        E.emul_gemv.argtypes = [C.c_int, vp, C.c_size_t, i64, i64, vp, vp, vp, C.c_int, C.c_int, vp, i64]
+        E.emul_gemv.argtypes = [C.c_int, vp, C.c_size_t, i64, i64, vp, vp, vp, vp, vp, C.c_int, C.c_int, vp, i64]
         E.emul_dequantize_row.argtypes = [C.c_int, vp, i64, vp]
         for f in ("emul_iq4nl_lookup4", "emul_nib_minus8", "emul_six_minus32"):
             getattr(E, f).argtypes = [C.c_uint32]
@@ -67,8 +67,11 @@ def _run_emul(t, w, k, x, R):
     else:
         q, d, _ = O.quantize_act_q8_256(x)
         d16, d32 = None, d.ctypes.data
+    s32 = q.reshape(n, k // 32, 32).astype(np.int32).sum(-1).astype(np.int16)
+    s16 = q.reshape(n, k // 16, 16).astype(np.int32).sum(-1).astype(np.int16)
     out = np.full((n, m), np.nan, dtype=np.float32)
-    rc = E.emul_gemv(t, w.ctypes.data, w.shape[1], m, k, q.ctypes.data, d16, d32, n, R, out.ctypes.data, m)
+    rc = E.emul_gemv(t, w.ctypes.data, w.shape[1], m, k, q.ctypes.data, d16, d32, s32.ctypes.data, s16.ctypes.data, n, R,
+                     out.ctypes.data, m)
     assert rc == 0
     return out
 
@@ -79,8 +82,8 @@ def rel_err(got, ref):
 
 
 # K values: one full stage, several stages, a ragged last stage, a single block
-KS = {O.Q4_0: [32, 96, 1024, 2080, 4096], O.Q8_0: [32, 96, 1024, 2080], O.Q4_K: [256, 1024, 2816, 4096],
-      O.Q6_K: [256, 2048, 2816, 4096], O.IQ4_XS: [256, 1024, 2816]}
+KS = {O.Q4_0: [32, 96, 1024, 2080, 4096, 6176], O.Q8_0: [32, 96, 1024, 2080, 4128], O.Q4_K: [256, 1024, 2816, 4096, 5120],
+      O.Q6_K: [256, 2048, 2816, 4096, 4352], O.IQ4_XS: [256, 1024, 2816, 5120]}
 
 
 @pytest.mark.parametrize("t", O.QUANT_TYPES)
