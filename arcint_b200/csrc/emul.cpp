@@ -16,37 +16,60 @@
 
 using namespace b200q;
 
-template <int TYPE, int NC, int R>
+template <int TYPE, int NC, int B>
 static void emul_gemv_t(const uint8_t *W, size_t row_stride, int64_t M, int64_t K, const GemvAct &act, float *dst,
                         int64_t ldd) {
     typedef GemvFmt<TYPE> F;
     typedef GemvStage<TYPE> S;
+    constexpr int NCG = NC <= 4 ? NC : (NC + 1) / 2, NC2 = NC - NCG, N2 = NC2 > 0 ? NC2 : 1;
     const int nblk = (int)(K / F::BLK_W), row_bytes = nblk * F::BLK_B;
     const int nstages = (nblk + F::STAGE_BLOCKS - 1) / F::STAGE_BLOCKS;
-    const int64_t n_rg = (M + R - 1) / R;
-    std::vector<uint32_t> slot((size_t)R * S::SLOT / 4);
-    for (int64_t rg = 0; rg < n_rg; ++rg) {
-        float acc[32][R][NC];
+    const int64_t n_bt = (M + B - 1) / B;
+    std::vector<uint32_t> set((size_t)B * S::SLOT / 4);
+    for (int64_t bt = 0; bt < n_bt; ++bt) {
+        static float acc[32][B][8];
         memset(acc, 0, sizeof(acc));
         for (int s = 0; s < nstages; ++s) {
             const int off = s * S::BYTES;
             const int bytes = (int)(row_bytes - off < S::BYTES ? row_bytes - off : S::BYTES);
-            memset(slot.data(), 0xA5, slot.size() * 4);     // stale ring contents must not matter
-            const uint32_t *srow[R];
-            for (int r = 0; r < R; ++r) {
-                const int64_t row = rg * R + r < M ? rg * R + r : M - 1;
-                memcpy((uint8_t *)slot.data() + r * S::SLOT, W + (size_t)row * row_stride + off, (size_t)bytes);
-                srow[r] = slot.data() + r * S::SLOT / 4;
+            memset(set.data(), 0xA5, set.size() * 4);       // stale ring contents must not matter
+            for (int r = 0; r < B; ++r)
+                if (bt * B + r < M)
+                    memcpy((uint8_t *)set.data() + r * S::SLOT, W + (size_t)(bt * B + r) * row_stride + off, (size_t)bytes);
+            for (int lane = 0; lane < 32; ++lane) {
+                GemvX<NCG> X;
+                gemv_load_x<TYPE, NCG>(lane, s, nblk, act, X);
+                for (int r = 0; r < B; ++r) {
+                    float a[NCG];
+                    for (int c = 0; c < NCG; ++c) a[c] = acc[lane][r][c];
+                    gemv_lane_row<TYPE, NCG>(set.data() + r * S::SLOT / 4, lane, X, a);
+                    for (int c = 0; c < NCG; ++c) acc[lane][r][c] = a[c];
+                }
+                if (NC2 > 0) {
+                    GemvAct act2 = act;
+                    act2.q += (size_t)NCG * act.K;
+                    if (act.d16) act2.d16 += (size_t)NCG * (act.K / 32);
+                    if (act.d32) act2.d32 += (size_t)NCG * (act.K / 256);
+                    act2.s32 += (size_t)NCG * (act.K / 32);
+                    if (act.s16) act2.s16 += (size_t)NCG * (act.K / 16);
+                    GemvX<N2> X2;
+                    gemv_load_x<TYPE, N2>(lane, s, nblk, act2, X2);
+                    for (int r = 0; r < B; ++r) {
+                        float a[N2];
+                        for (int c = 0; c < N2; ++c) a[c] = acc[lane][r][NCG + (c < NC2 ? c : 0)];
+                        gemv_lane_row<TYPE, N2>(set.data() + r * S::SLOT / 4, lane, X2, a);
+                        for (int c = 0; c < NC2; ++c) acc[lane][r][NCG + c] = a[c];
+                    }
+                }
             }
-            for (int lane = 0; lane < 32; ++lane) gemv_lane_stage<TYPE, NC, R>(srow, lane, s, nblk, act, acc[lane]);
         }
-        for (int r = 0; r < R; ++r)
+        for (int r = 0; r < B; ++r)
             for (int c = 0; c < NC; ++c) {
                 float v[32];
                 for (int l = 0; l < 32; ++l) v[l] = acc[l][r][c];
                 for (int o = 16; o > 0; o >>= 1)            // the shuffle butterfly's order
                     for (int l = 0; l < o; ++l) v[l] += v[l + o];
-                if (rg * R + r < M) dst[rg * R + r + c * ldd] = v[0];
+                if (bt * B + r < M) dst[bt * B + r + c * ldd] = v[0];
             }
     }
 }
@@ -54,7 +77,7 @@ static void emul_gemv_t(const uint8_t *W, size_t row_stride, int64_t M, int64_t 
 template <int TYPE, int NC>
 static void emul_gemv_r(int R, const uint8_t *W, size_t rs, int64_t M, int64_t K, const GemvAct &a, float *d, int64_t ldd) {
     if (R == 1) emul_gemv_t<TYPE, NC, 1>(W, rs, M, K, a, d, ldd);
-    else        emul_gemv_t<TYPE, NC, 2>(W, rs, M, K, a, d, ldd);
+    else        emul_gemv_t<TYPE, NC, 4>(W, rs, M, K, a, d, ldd);
 }
 
 template <int TYPE>
@@ -64,7 +87,9 @@ static int emul_gemv_nc(int nc, int R, const uint8_t *W, size_t rs, int64_t M, i
     case 1: emul_gemv_r<TYPE, 1>(R, W, rs, M, K, a, d, ldd); return 0;
     case 2: emul_gemv_r<TYPE, 2>(R, W, rs, M, K, a, d, ldd); return 0;
     case 3: emul_gemv_r<TYPE, 3>(R, W, rs, M, K, a, d, ldd); return 0;
+    case 4: emul_gemv_r<TYPE, 4>(R, W, rs, M, K, a, d, ldd); return 0;
     case 5: emul_gemv_r<TYPE, 5>(R, W, rs, M, K, a, d, ldd); return 0;
+    case 7: emul_gemv_r<TYPE, 7>(R, W, rs, M, K, a, d, ldd); return 0;
     case 8: emul_gemv_r<TYPE, 8>(R, W, rs, M, K, a, d, ldd); return 0;
     }
     return -1;

@@ -1,17 +1,20 @@
-// gemv_core.cuh -- what ONE LANE of the decode GEMV does with one staged chunk of R weight
-// rows and NC activation columns. Host+device text: the kernel (gemv.cu) calls it from
-// 32 lanes of a warp; the device-free emulation (emul.cpp) calls it for lane 0..31 in turn.
+// gemv_core.cuh -- what ONE LANE of the decode GEMV does. Host+device text: the kernel
+// (gemv_kernel.cuh) calls it from the 32 lanes of a warp; the device-free emulation
+// (emul.cpp) calls it for lane 0..31 in turn.
 //
 // A "stage" is 2048 weights of a row (64 per lane); its byte size is a multiple of 16 for
 // every type, so stages are fetched with 16-byte copies:
 //   Q4_0 64 blocks = 1152 B   Q8_0 64 blocks = 2176 B   Q4_K 8 blocks = 1152 B
 //   IQ4_XS 8 blocks = 1088 B  Q6_K 8 blocks = 1680 B
-// The kernel is bound by instruction issue as much as by HBM (a B200 SM receives ~23 weight
-// bytes per clock: about 100 lane instructions per 32 four-bit weights), so the lane code is
-// written for instruction count: nibbles stay unsigned (the -8 / -32 offsets ride on the
-// activation block sums the quantizer already made), high nibbles are multiplied in place
-// (x16, unsigned dp4a) and the 1/16 is folded into the float scale, sub-scales are unpacked
-// four at a time.
+// Work is split in two so the activation side is paid once per stage, not once per row:
+//   gemv_load_x   loads the lane's 64 activation codes, scales and block sums of NC columns
+//                 for stage s into registers (GemvX);
+//   gemv_lane_row multiplies one staged weight row chunk against them.
+// A B200 SM receives ~23 weight bytes per clock, i.e. about 100 lane instructions per 32
+// four-bit weights, so the lane code is written for instruction count: nibbles stay
+// unsigned (the -8 / -32 offsets ride on the activation block sums the quantizer already
+// made), high nibbles are multiplied in place (x16, unsigned dp4a) and the 1/16 is folded
+// into the float scale, sub-scales are unpacked four at a time.
 //
 // Integer block dots are exact (dp4a against the int8 activation codes); float enters once
 // per 32 (Q4_0/Q8_0: d_w * d_x) or once per 256-block (K types: integer sub-scales first),
@@ -37,8 +40,7 @@ template <int TYPE> struct GemvStage {
            SLOT  = ((BYTES + 4 + 15) / 16) * 16 };                         // + one word of over-read
 };
 
-// Activation pointers already offset to the first column of this launch; column c is
-// `cstride` columns of the quantized buffer further on (1 for a dense product).
+// Activation pointers already offset to the first column of this launch.
 struct GemvAct {
     const int8_t   *q;     // [ ][K]      codes
     const uint16_t *d16;   // [ ][K/32]   per-32 form: fp16 scales
@@ -94,216 +96,238 @@ B200Q_HD uint16_t ld_u16(const uint16_t *p) {
 B200Q_HD int sext8(uint32_t v) { return (int)(int8_t)(v & 0xFFu); }
 B200Q_HD int sext16(uint32_t v) { return (int)(int16_t)(v & 0xFFFFu); }
 
-// srow[r]: staged words of row r for stage s. nblk: blocks per row. acc[r][c] += partial.
-template <int TYPE, int NC, int R>
-B200Q_HD void gemv_lane_stage(const uint32_t *const (&srow)[R], int lane, int s, int nblk,
-                              const GemvAct &act, float (&acc)[R][NC]) {
+// The lane's activation registers for one stage: 64 codes per column plus what the type's
+// scale/offset terms need. f0/f1: float factors; i0..i3: integer terms.
+template <int NC> struct GemvX {
+    I4    x[NC][4];
+    float f0[NC], f1[NC];
+    int   i0[NC], i1[NC], i2[NC], i3[NC];
+    bool  live;           // the lane's block exists in this stage (ragged last stage)
+    bool  live2;          // Q4_0/Q8_0: the lane's second block exists
+};
+
+template <int TYPE, int NC>
+B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, GemvX<NC> &X) {
     typedef GemvFmt<TYPE> F;
     const int K = act.K;
-
     if (TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_Q8_0) {
         // two 32-blocks per lane: lane and lane + 32 of the stage
+        const int b0 = s * F::STAGE_BLOCKS + lane, b1 = b0 + 32;
+        X.live = b0 < nblk;
+        X.live2 = b1 < nblk;
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int sblk = 32 * u + lane, blk = s * F::STAGE_BLOCKS + sblk;
-            if (blk >= nblk) continue;
-            I4 xa[NC], xb[NC];
-            float dx[NC];
-            int bs8[NC];
-#pragma unroll
-            for (int c = 0; c < NC; ++c) {
-                const int8_t *xp = act.q + (size_t)c * K + 32 * blk;
-                xa[c] = hd_ld16(xp);
-                xb[c] = hd_ld16(xp + 16);
-                dx[c] = hd_half_bits(ld_u16(act.d16 + (size_t)c * (K / 32) + blk));
+        for (int c = 0; c < NC; ++c) {
+            const int8_t *xp = act.q + (size_t)c * K;
+            const size_t sc = (size_t)c * (K / 32);
+            if (X.live) {
+                X.x[c][0] = hd_ld16(xp + 32 * b0);
+                X.x[c][1] = hd_ld16(xp + 32 * b0 + 16);
+                X.f0[c] = hd_half_bits(ld_u16(act.d16 + sc + b0));
                 if (TYPE == B200Q_TYPE_Q4_0) {
-                    bs8[c] = -128 * ld_s16(act.s32 + (size_t)c * (K / 32) + blk);   // -8 * 16 * sum(x)
-                    dx[c] *= 0.0625f;                                                // the nibble dot is kept x16
+                    X.i0[c] = -128 * ld_s16(act.s32 + sc + b0);      // -8 * 16 * sum(x)
+                    X.f0[c] *= 0.0625f;                              // the nibble dot is kept x16
                 }
             }
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const uint32_t off = (uint32_t)F::BLK_B * (uint32_t)sblk;
-                const float d = hd_half_bits(stage_u16(srow[r], off));
+            if (X.live2) {
+                X.x[c][2] = hd_ld16(xp + 32 * b1);
+                X.x[c][3] = hd_ld16(xp + 32 * b1 + 16);
+                X.f1[c] = hd_half_bits(ld_u16(act.d16 + sc + b1));
                 if (TYPE == B200Q_TYPE_Q4_0) {
-                    uint32_t q[4];
-                    stage_words<4>(srow[r], off + 2, q);
-#pragma unroll
-                    for (int c = 0; c < NC; ++c) {
-                        // weights 4j..4j+3 in the low nibbles, 16+4j.. in the high ones (left x16)
-                        int lo = 0, hi = 0;
-                        lo = dp4a_ss(q[0] & 0x0F0F0F0Fu, xa[c].x, lo); lo = dp4a_ss(q[1] & 0x0F0F0F0Fu, xa[c].y, lo);
-                        lo = dp4a_ss(q[2] & 0x0F0F0F0Fu, xa[c].z, lo); lo = dp4a_ss(q[3] & 0x0F0F0F0Fu, xa[c].w, lo);
-                        hi = dp4a_us(q[0] & 0xF0F0F0F0u, xb[c].x, hi); hi = dp4a_us(q[1] & 0xF0F0F0F0u, xb[c].y, hi);
-                        hi = dp4a_us(q[2] & 0xF0F0F0F0u, xb[c].z, hi); hi = dp4a_us(q[3] & 0xF0F0F0F0u, xb[c].w, hi);
-                        const int si = 16 * lo + hi + bs8[c];                       // 16 * sum((n - 8) x)
-                        acc[r][c] += (float)si * (d * dx[c]);
-                    }
-                } else {
-                    uint32_t w[8];
-                    stage_words<8>(srow[r], off + 2, w);
-#pragma unroll
-                    for (int c = 0; c < NC; ++c) {
-                        int si = 0;
-                        si = dp4a_ss(w[0], xa[c].x, si); si = dp4a_ss(w[1], xa[c].y, si);
-                        si = dp4a_ss(w[2], xa[c].z, si); si = dp4a_ss(w[3], xa[c].w, si);
-                        si = dp4a_ss(w[4], xb[c].x, si); si = dp4a_ss(w[5], xb[c].y, si);
-                        si = dp4a_ss(w[6], xb[c].z, si); si = dp4a_ss(w[7], xb[c].w, si);
-                        acc[r][c] += (float)si * (d * dx[c]);
-                    }
+                    X.i1[c] = -128 * ld_s16(act.s32 + sc + b1);
+                    X.f1[c] *= 0.0625f;
                 }
             }
         }
     } else if (TYPE == B200Q_TYPE_Q4_K) {
         // lane -> block sb of the stage and 32-byte group g: sub-blocks 2g (low nibbles) and
         // 2g+1 (high nibbles), 64 weights
-        const int sb = lane >> 2, g = lane & 3;
-        const int blk = s * F::STAGE_BLOCKS + sb;
-        if (blk >= nblk) return;
-        I4 xl[NC][2], xh[NC][2];
-        float dxs[NC], dxm[NC];
-        int bs0[NC], bs1[NC];
+        const int sb = lane >> 2, g = lane & 3, blk = s * F::STAGE_BLOCKS + sb;
+        X.live = blk < nblk;
+        if (!X.live) return;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
             const int8_t *xp = act.q + (size_t)c * K + 256 * blk + 64 * g;
-            xl[c][0] = hd_ld16(xp);      xl[c][1] = hd_ld16(xp + 16);
-            xh[c][0] = hd_ld16(xp + 32); xh[c][1] = hd_ld16(xp + 48);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) X.x[c][j] = hd_ld16(xp + 16 * j);
             const float dx = ld_f32(act.d32 + (size_t)c * (K / 256) + blk);
-            dxs[c] = dx * 0.0625f;       // both nibble dots are kept x16
-            dxm[c] = dx;
+            X.f0[c] = dx * 0.0625f;      // both nibble dots are kept x16
+            X.f1[c] = dx;
             const uint32_t bp = ld_u32(act.s32 + (size_t)c * (K / 32) + 8 * blk + 2 * g);
-            bs0[c] = sext16(bp);
-            bs1[c] = sext16(bp >> 16);
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const uint32_t *bw = srow[r] + sb * (144 / 4);
-            const uint32_t hd = bw[0], s0 = bw[1], s1 = bw[2], s2 = bw[3];
-            const float d = hd_half_bits((uint16_t)hd), dmin = hd_half_bits((uint16_t)(hd >> 16));
-            // the 6-bit scales / mins of sub-blocks 0..3 and 4..7 as four bytes each
-            const uint32_t scw = g < 2 ? (s0 & 0x3F3F3F3Fu) : ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u));
-            const uint32_t mnw = g < 2 ? (s1 & 0x3F3F3F3Fu) : (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u));
-            const int sh = 16 * (g & 1);
-            const int sc0 = (int)((scw >> sh) & 0xFFu) * 16, sc1 = (int)((scw >> (sh + 8)) & 0xFFu);
-            const int m0 = (int)((mnw >> sh) & 0xFFu), m1 = (int)((mnw >> (sh + 8)) & 0xFFu);
-            const uint32_t *qp = bw + 4 + 8 * g;
-            uint32_t q[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) q[j] = qp[j];
-#pragma unroll
-            for (int c = 0; c < NC; ++c) {
-                int il = 0, ih = 0;
-                il = dp4a_ss(q[0] & 0x0F0F0F0Fu, xl[c][0].x, il); il = dp4a_ss(q[1] & 0x0F0F0F0Fu, xl[c][0].y, il);
-                il = dp4a_ss(q[2] & 0x0F0F0F0Fu, xl[c][0].z, il); il = dp4a_ss(q[3] & 0x0F0F0F0Fu, xl[c][0].w, il);
-                il = dp4a_ss(q[4] & 0x0F0F0F0Fu, xl[c][1].x, il); il = dp4a_ss(q[5] & 0x0F0F0F0Fu, xl[c][1].y, il);
-                il = dp4a_ss(q[6] & 0x0F0F0F0Fu, xl[c][1].z, il); il = dp4a_ss(q[7] & 0x0F0F0F0Fu, xl[c][1].w, il);
-                ih = dp4a_us(q[0] & 0xF0F0F0F0u, xh[c][0].x, ih); ih = dp4a_us(q[1] & 0xF0F0F0F0u, xh[c][0].y, ih);
-                ih = dp4a_us(q[2] & 0xF0F0F0F0u, xh[c][0].z, ih); ih = dp4a_us(q[3] & 0xF0F0F0F0u, xh[c][0].w, ih);
-                ih = dp4a_us(q[4] & 0xF0F0F0F0u, xh[c][1].x, ih); ih = dp4a_us(q[5] & 0xF0F0F0F0u, xh[c][1].y, ih);
-                ih = dp4a_us(q[6] & 0xF0F0F0F0u, xh[c][1].z, ih); ih = dp4a_us(q[7] & 0xF0F0F0F0u, xh[c][1].w, ih);
-                const int si = sc0 * il + sc1 * ih;                  // 16 * sum_sb sc * dot
-                const int sm = m0 * bs0[c] + m1 * bs1[c];
-                acc[r][c] += (d * dxs[c]) * (float)si - (dmin * dxm[c]) * (float)sm;
-            }
+            X.i0[c] = sext16(bp);
+            X.i1[c] = sext16(bp >> 16);
         }
     } else if (TYPE == B200Q_TYPE_IQ4_XS) {
         // lane -> block sb and sub-block pair pp: 32 bytes = sub-blocks 2pp and 2pp+1
-        const int sb = lane >> 2, pp = lane & 3;
-        const int blk = s * F::STAGE_BLOCKS + sb;
-        if (blk >= nblk) return;
-        I4 x[NC][4];
-        float dx[NC];
+        const int sb = lane >> 2, pp = lane & 3, blk = s * F::STAGE_BLOCKS + sb;
+        X.live = blk < nblk;
+        if (!X.live) return;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
             const int8_t *xp = act.q + (size_t)c * K + 256 * blk + 64 * pp;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) x[c][j] = hd_ld16(xp + 16 * j);
-            dx[c] = ld_f32(act.d32 + (size_t)c * (K / 256) + blk);
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const uint32_t *bw = srow[r] + sb * (136 / 4);
-            const uint32_t hd = bw[0];
-            const float d = hd_half_bits((uint16_t)hd);
-            const int ls0 = iq4xs_ls(hd >> 16, bw[1], 2 * pp) - 32, ls1 = iq4xs_ls(hd >> 16, bw[1], 2 * pp + 1) - 32;
-            const uint32_t *qp = bw + 2 + 8 * pp;
-            uint32_t w[16];      // sub-block 2pp: w[0..3] weights 0..15, w[4..7] weights 16..31; then 2pp+1
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t q = qp[4 * h + j];
-                    w[8 * h + j]     = iq4nl_lookup4(q & 0x0F0F0F0Fu);
-                    w[8 * h + j + 4] = iq4nl_lookup4((q >> 4) & 0x0F0F0F0Fu);
-                }
-#pragma unroll
-            for (int c = 0; c < NC; ++c) {
-                int i0 = 0, i1 = 0;
-                i0 = dp4a_ss(w[0], x[c][0].x, i0); i0 = dp4a_ss(w[1], x[c][0].y, i0);
-                i0 = dp4a_ss(w[2], x[c][0].z, i0); i0 = dp4a_ss(w[3], x[c][0].w, i0);
-                i0 = dp4a_ss(w[4], x[c][1].x, i0); i0 = dp4a_ss(w[5], x[c][1].y, i0);
-                i0 = dp4a_ss(w[6], x[c][1].z, i0); i0 = dp4a_ss(w[7], x[c][1].w, i0);
-                i1 = dp4a_ss(w[8], x[c][2].x, i1);  i1 = dp4a_ss(w[9], x[c][2].y, i1);
-                i1 = dp4a_ss(w[10], x[c][2].z, i1); i1 = dp4a_ss(w[11], x[c][2].w, i1);
-                i1 = dp4a_ss(w[12], x[c][3].x, i1); i1 = dp4a_ss(w[13], x[c][3].y, i1);
-                i1 = dp4a_ss(w[14], x[c][3].z, i1); i1 = dp4a_ss(w[15], x[c][3].w, i1);
-                acc[r][c] += (d * dx[c]) * (float)(ls0 * i0 + ls1 * i1);
-            }
+            for (int j = 0; j < 4; ++j) X.x[c][j] = hd_ld16(xp + 16 * j);
+            X.f0[c] = ld_f32(act.d32 + (size_t)c * (K / 256) + blk);
         }
     } else if (TYPE == B200Q_TYPE_Q6_K) {
         // lane -> block sb, half n, positions t0..t0+15 of the four 32-weight parts of that
         // half: each part's 16 weights are exactly one scale group
         const int sb = lane >> 2, n = (lane >> 1) & 1, hi16 = lane & 1, t0 = 16 * hi16;
         const int blk = s * F::STAGE_BLOCKS + sb;
-        if (blk >= nblk) return;
-        I4 x[NC][4];
-        float dx[NC];
-        int s32x[NC][4];         // 32 * (sum of the 16 activation codes of part p)
+        X.live = blk < nblk;
+        if (!X.live) return;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
             const int8_t *xp = act.q + (size_t)c * K + 256 * blk + 128 * n + t0;
 #pragma unroll
-            for (int p = 0; p < 4; ++p) x[c][p] = hd_ld16(xp + 32 * p);
-            dx[c] = ld_f32(act.d32 + (size_t)c * (K / 256) + blk);
+            for (int p = 0; p < 4; ++p) X.x[c][p] = hd_ld16(xp + 32 * p);
+            X.f0[c] = ld_f32(act.d32 + (size_t)c * (K / 256) + blk);
             // sums of groups 8n + 2p + hi16, p = 0..3: eight int16 from one 16-byte load
             const I4 sv = hd_ld16(act.s16 + (size_t)c * (K / 16) + 16 * blk + 8 * n);
-            const uint32_t a0 = (uint32_t)sv.x >> (16 * hi16), a1 = (uint32_t)sv.y >> (16 * hi16);
-            const uint32_t a2 = (uint32_t)sv.z >> (16 * hi16), a3 = (uint32_t)sv.w >> (16 * hi16);
-            s32x[c][0] = 32 * sext16(a0); s32x[c][1] = 32 * sext16(a1);
-            s32x[c][2] = 32 * sext16(a2); s32x[c][3] = 32 * sext16(a3);
+            X.i0[c] = -32 * sext16((uint32_t)sv.x >> (16 * hi16));     // sum((q-32) x) = sum(q x) - 32 sum(x)
+            X.i1[c] = -32 * sext16((uint32_t)sv.y >> (16 * hi16));
+            X.i2[c] = -32 * sext16((uint32_t)sv.z >> (16 * hi16));
+            X.i3[c] = -32 * sext16((uint32_t)sv.w >> (16 * hi16));
         }
+    }
+}
+
+// sw: the staged words of one weight row for the stage X was loaded for. acc[c] += partial.
+template <int TYPE, int NC>
+B200Q_HD void gemv_lane_row(const uint32_t *sw, int lane, const GemvX<NC> &X, float (&acc)[NC]) {
+    typedef GemvFmt<TYPE> F;
+    if (TYPE == B200Q_TYPE_Q4_0) {
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const uint32_t off = 210u * (uint32_t)sb;
-            uint32_t qa[4], qb[4], qh[4], sw[2];
-            stage_words<4>(srow[r], off + 64 * n + t0, qa);            // parts 0 (low) and 2 (high)
-            stage_words<4>(srow[r], off + 64 * n + 32 + t0, qb);       // parts 1 and 3
-            stage_words<4>(srow[r], off + 128 + 32 * n + t0, qh);
-            stage_words<2>(srow[r], off + 192 + 8 * n, sw);            // the half's eight scales
-            const float d = hd_half_bits(stage_u16(srow[r], off + 208));
-            const uint32_t w0 = sw[0] >> (8 * hi16), w1 = sw[1] >> (8 * hi16);
-            const int sc0 = sext8(w0), sc1 = sext8(w0 >> 16), sc2 = sext8(w1), sc3 = sext8(w1 >> 16);
-            uint32_t w[4][4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                w[0][j] = (qa[j] & 0x0F0F0F0Fu)        | ((qh[j] << 4) & 0x30303030u);
-                w[1][j] = (qb[j] & 0x0F0F0F0Fu)        | ((qh[j] << 2) & 0x30303030u);
-                w[2][j] = ((qa[j] >> 4) & 0x0F0F0F0Fu) | (qh[j] & 0x30303030u);
-                w[3][j] = ((qb[j] >> 4) & 0x0F0F0F0Fu) | ((qh[j] >> 2) & 0x30303030u);
-            }
+        for (int u = 0; u < 2; ++u) {
+            if (!(u ? X.live2 : X.live)) continue;
+            const uint32_t off = (uint32_t)F::BLK_B * (uint32_t)(32 * u + lane);
+            const float d = hd_half_bits(stage_u16(sw, off));
+            uint32_t q[4];
+            stage_words<4>(sw, off + 2, q);
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
-                int ip[4];
-#pragma unroll
-                for (int p = 0; p < 4; ++p) {
-                    int v = -s32x[c][p];                               // sum((q - 32) x) = sum(q x) - 32 sum(x)
-                    v = dp4a_ss(w[p][0], x[c][p].x, v); v = dp4a_ss(w[p][1], x[c][p].y, v);
-                    v = dp4a_ss(w[p][2], x[c][p].z, v); v = dp4a_ss(w[p][3], x[c][p].w, v);
-                    ip[p] = v;
-                }
-                const int si = sc0 * ip[0] + sc1 * ip[1] + sc2 * ip[2] + sc3 * ip[3];
-                acc[r][c] += (d * dx[c]) * (float)si;
+                // weights 4j..4j+3 in the low nibbles, 16+4j.. in the high ones (left x16)
+                const I4 xa = X.x[c][2 * u], xb = X.x[c][2 * u + 1];
+                int lo0 = dp4a_ss(q[0] & 0x0F0F0F0Fu, xa.x, 0), lo1 = dp4a_ss(q[1] & 0x0F0F0F0Fu, xa.y, 0);
+                lo0 = dp4a_ss(q[2] & 0x0F0F0F0Fu, xa.z, lo0);   lo1 = dp4a_ss(q[3] & 0x0F0F0F0Fu, xa.w, lo1);
+                int hi0 = dp4a_us(q[0] & 0xF0F0F0F0u, xb.x, u ? X.i1[c] : X.i0[c]);
+                int hi1 = dp4a_us(q[1] & 0xF0F0F0F0u, xb.y, 0);
+                hi0 = dp4a_us(q[2] & 0xF0F0F0F0u, xb.z, hi0);   hi1 = dp4a_us(q[3] & 0xF0F0F0F0u, xb.w, hi1);
+                const int si = 16 * (lo0 + lo1) + hi0 + hi1;                  // 16 * sum((n - 8) x)
+                acc[c] += (float)si * (d * (u ? X.f1[c] : X.f0[c]));
             }
+        }
+    } else if (TYPE == B200Q_TYPE_Q8_0) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (!(u ? X.live2 : X.live)) continue;
+            const uint32_t off = (uint32_t)F::BLK_B * (uint32_t)(32 * u + lane);
+            const float d = hd_half_bits(stage_u16(sw, off));
+            uint32_t w[8];
+            stage_words<8>(sw, off + 2, w);
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const I4 xa = X.x[c][2 * u], xb = X.x[c][2 * u + 1];
+                int s0 = dp4a_ss(w[0], xa.x, 0), s1 = dp4a_ss(w[1], xa.y, 0);
+                s0 = dp4a_ss(w[2], xa.z, s0); s1 = dp4a_ss(w[3], xa.w, s1);
+                s0 = dp4a_ss(w[4], xb.x, s0); s1 = dp4a_ss(w[5], xb.y, s1);
+                s0 = dp4a_ss(w[6], xb.z, s0); s1 = dp4a_ss(w[7], xb.w, s1);
+                acc[c] += (float)(s0 + s1) * (d * (u ? X.f1[c] : X.f0[c]));
+            }
+        }
+    } else if (TYPE == B200Q_TYPE_Q4_K) {
+        if (!X.live) return;
+        const int sb = lane >> 2, g = lane & 3;
+        const uint32_t *bw = sw + sb * (144 / 4);
+        const uint32_t hd = bw[0], s0 = bw[1], s1 = bw[2], s2 = bw[3];
+        const float d = hd_half_bits((uint16_t)hd), dmin = hd_half_bits((uint16_t)(hd >> 16));
+        // the 6-bit scales / mins of sub-blocks 0..3 and 4..7 as four bytes each
+        const uint32_t scw = g < 2 ? (s0 & 0x3F3F3F3Fu) : ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u));
+        const uint32_t mnw = g < 2 ? (s1 & 0x3F3F3F3Fu) : (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u));
+        const int sh = 16 * (g & 1);
+        const int sc0 = (int)((scw >> sh) & 0xFFu) * 16, sc1 = (int)((scw >> (sh + 8)) & 0xFFu);
+        const int m0 = (int)((mnw >> sh) & 0xFFu), m1 = (int)((mnw >> (sh + 8)) & 0xFFu);
+        const uint32_t *qp = bw + 4 + 8 * g;
+        uint32_t q[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[j] = qp[j];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            const I4 a0 = X.x[c][0], a1 = X.x[c][1], b0 = X.x[c][2], b1 = X.x[c][3];
+            int il0 = dp4a_ss(q[0] & 0x0F0F0F0Fu, a0.x, 0), il1 = dp4a_ss(q[1] & 0x0F0F0F0Fu, a0.y, 0);
+            il0 = dp4a_ss(q[2] & 0x0F0F0F0Fu, a0.z, il0); il1 = dp4a_ss(q[3] & 0x0F0F0F0Fu, a0.w, il1);
+            il0 = dp4a_ss(q[4] & 0x0F0F0F0Fu, a1.x, il0); il1 = dp4a_ss(q[5] & 0x0F0F0F0Fu, a1.y, il1);
+            il0 = dp4a_ss(q[6] & 0x0F0F0F0Fu, a1.z, il0); il1 = dp4a_ss(q[7] & 0x0F0F0F0Fu, a1.w, il1);
+            int ih0 = dp4a_us(q[0] & 0xF0F0F0F0u, b0.x, 0), ih1 = dp4a_us(q[1] & 0xF0F0F0F0u, b0.y, 0);
+            ih0 = dp4a_us(q[2] & 0xF0F0F0F0u, b0.z, ih0); ih1 = dp4a_us(q[3] & 0xF0F0F0F0u, b0.w, ih1);
+            ih0 = dp4a_us(q[4] & 0xF0F0F0F0u, b1.x, ih0); ih1 = dp4a_us(q[5] & 0xF0F0F0F0u, b1.y, ih1);
+            ih0 = dp4a_us(q[6] & 0xF0F0F0F0u, b1.z, ih0); ih1 = dp4a_us(q[7] & 0xF0F0F0F0u, b1.w, ih1);
+            const int si = sc0 * (il0 + il1) + sc1 * (ih0 + ih1);            // 16 * sum_sb sc * dot
+            const int sm = m0 * X.i0[c] + m1 * X.i1[c];
+            acc[c] += (d * X.f0[c]) * (float)si - (dmin * X.f1[c]) * (float)sm;
+        }
+    } else if (TYPE == B200Q_TYPE_IQ4_XS) {
+        if (!X.live) return;
+        const int sb = lane >> 2, pp = lane & 3;
+        const uint32_t *bw = sw + sb * (136 / 4);
+        const uint32_t hd = bw[0];
+        const float d = hd_half_bits((uint16_t)hd);
+        const int ls0 = iq4xs_ls(hd >> 16, bw[1], 2 * pp) - 32, ls1 = iq4xs_ls(hd >> 16, bw[1], 2 * pp + 1) - 32;
+        const uint32_t *qp = bw + 2 + 8 * pp;
+        uint32_t w[16];      // sub-block 2pp: w[0..3] weights 0..15, w[4..7] weights 16..31; then 2pp+1
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t q = qp[4 * h + j];
+                w[8 * h + j]     = iq4nl_lookup4(q & 0x0F0F0F0Fu);
+                w[8 * h + j + 4] = iq4nl_lookup4((q >> 4) & 0x0F0F0F0Fu);
+            }
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            int i0 = 0, i1 = 0;
+            i0 = dp4a_ss(w[0], X.x[c][0].x, i0); i0 = dp4a_ss(w[1], X.x[c][0].y, i0);
+            i0 = dp4a_ss(w[2], X.x[c][0].z, i0); i0 = dp4a_ss(w[3], X.x[c][0].w, i0);
+            i0 = dp4a_ss(w[4], X.x[c][1].x, i0); i0 = dp4a_ss(w[5], X.x[c][1].y, i0);
+            i0 = dp4a_ss(w[6], X.x[c][1].z, i0); i0 = dp4a_ss(w[7], X.x[c][1].w, i0);
+            i1 = dp4a_ss(w[8], X.x[c][2].x, i1);  i1 = dp4a_ss(w[9], X.x[c][2].y, i1);
+            i1 = dp4a_ss(w[10], X.x[c][2].z, i1); i1 = dp4a_ss(w[11], X.x[c][2].w, i1);
+            i1 = dp4a_ss(w[12], X.x[c][3].x, i1); i1 = dp4a_ss(w[13], X.x[c][3].y, i1);
+            i1 = dp4a_ss(w[14], X.x[c][3].z, i1); i1 = dp4a_ss(w[15], X.x[c][3].w, i1);
+            acc[c] += (d * X.f0[c]) * (float)(ls0 * i0 + ls1 * i1);
+        }
+    } else if (TYPE == B200Q_TYPE_Q6_K) {
+        if (!X.live) return;
+        const int sb = lane >> 2, n = (lane >> 1) & 1, hi16 = lane & 1, t0 = 16 * hi16;
+        const uint32_t off = 210u * (uint32_t)sb;
+        uint32_t qa[4], qb[4], qh[4], scw[2];
+        stage_words<4>(sw, off + 64 * n + t0, qa);            // parts 0 (low) and 2 (high)
+        stage_words<4>(sw, off + 64 * n + 32 + t0, qb);       // parts 1 and 3
+        stage_words<4>(sw, off + 128 + 32 * n + t0, qh);
+        stage_words<2>(sw, off + 192 + 8 * n, scw);           // the half's eight scales
+        const float d = hd_half_bits(stage_u16(sw, off + 208));
+        const uint32_t w0 = scw[0] >> (8 * hi16), w1 = scw[1] >> (8 * hi16);
+        const int sc0 = sext8(w0), sc1 = sext8(w0 >> 16), sc2 = sext8(w1), sc3 = sext8(w1 >> 16);
+        uint32_t w[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            w[0][j] = (qa[j] & 0x0F0F0F0Fu)        | ((qh[j] << 4) & 0x30303030u);
+            w[1][j] = (qb[j] & 0x0F0F0F0Fu)        | ((qh[j] << 2) & 0x30303030u);
+            w[2][j] = ((qa[j] >> 4) & 0x0F0F0F0Fu) | (qh[j] & 0x30303030u);
+            w[3][j] = ((qb[j] >> 4) & 0x0F0F0F0Fu) | ((qh[j] >> 2) & 0x30303030u);
+        }
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            int v0 = X.i0[c], v1 = X.i1[c], v2 = X.i2[c], v3 = X.i3[c];
+            v0 = dp4a_ss(w[0][0], X.x[c][0].x, v0); v1 = dp4a_ss(w[1][0], X.x[c][1].x, v1);
+            v2 = dp4a_ss(w[2][0], X.x[c][2].x, v2); v3 = dp4a_ss(w[3][0], X.x[c][3].x, v3);
+            v0 = dp4a_ss(w[0][1], X.x[c][0].y, v0); v1 = dp4a_ss(w[1][1], X.x[c][1].y, v1);
+            v2 = dp4a_ss(w[2][1], X.x[c][2].y, v2); v3 = dp4a_ss(w[3][1], X.x[c][3].y, v3);
+            v0 = dp4a_ss(w[0][2], X.x[c][0].z, v0); v1 = dp4a_ss(w[1][2], X.x[c][1].z, v1);
+            v2 = dp4a_ss(w[2][2], X.x[c][2].z, v2); v3 = dp4a_ss(w[3][2], X.x[c][3].z, v3);
+            v0 = dp4a_ss(w[0][3], X.x[c][0].w, v0); v1 = dp4a_ss(w[1][3], X.x[c][1].w, v1);
+            v2 = dp4a_ss(w[2][3], X.x[c][2].w, v2); v3 = dp4a_ss(w[3][3], X.x[c][3].w, v3);
+            const int si = sc0 * v0 + sc1 * v1 + sc2 * v2 + sc3 * v3;
+            acc[c] += (d * X.f0[c]) * (float)si;
         }
     }
 }
