@@ -6,6 +6,7 @@
 // conversion cache (:670-715), ggml_cl_mul_mat (:1135-1158) and supports_op (:615-652).
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -116,6 +117,17 @@ static b200q_status get_activation(b200q_ctx *ctx, int form, const b200q_tensor 
         ctx->act_next = (ctx->act_next + 1) % ctx->act_cache.size();
         e.valid = false;
         b200q_status st;
+        if (form == ACT_Q8_0_TILED) {
+            if ((st = ws_reserve(ctx, &e.codes, gemm_tc_act_bytes(K, N))) != B200Q_OK) return st;
+            if ((st = launch_quantize_tiled(ctx, src1, (uint8_t *)e.codes.ptr)) != B200Q_OK) return st;
+            e.key = key;
+            e.valid = true;
+            out->codes = (const int8_t *)e.codes.ptr;
+            out->form = form;
+            out->K = K;
+            out->N = N;
+            return B200Q_OK;
+        }
         if ((st = ws_reserve(ctx, &e.codes, (size_t)(N * K) + 64)) != B200Q_OK) return st;
         const size_t sbytes = form == ACT_Q8_0 ? sizeof(uint16_t) * (size_t)(N * (K / 32)) : sizeof(float) * (size_t)(N * (K / 256));
         if ((st = ws_reserve(ctx, &e.scales, sbytes + 64)) != B200Q_OK) return st;
@@ -183,6 +195,12 @@ b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
     }
     cudaEventCreate(&ctx->ev0);
     cudaEventCreate(&ctx->ev1);
+    if (cudaMalloc(&ctx->error_word, sizeof(int)) != cudaSuccess || cudaMemset(ctx->error_word, 0, sizeof(int)) != cudaSuccess) {
+        b200q_free(ctx);
+        return B200Q_NO_MEMORY;
+    }
+    const char *no_tc = getenv("B200Q_NO_TC");      // read once: force the CUDA-core path (tests, comparisons)
+    ctx->no_tc = no_tc && no_tc[0] == '1';
     *out = ctx;
     return B200Q_OK;
 }
@@ -198,6 +216,7 @@ void b200q_free(b200q_ctx *ctx) {
         if (e.sums16.ptr) cudaFree(e.sums16.ptr);
     }
     if (ctx->flush_buf.ptr) cudaFree(ctx->flush_buf.ptr);
+    if (ctx->error_word) cudaFree(ctx->error_word);
     for (auto &w : ctx->moe_ws)
         if (w.ptr) cudaFree(w.ptr);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
@@ -243,9 +262,16 @@ b200q_status b200q_mul_mat(b200q_ctx *ctx, const b200q_tensor *src0, const b200q
     const int64_t N = src1->ne[1] * src1->ne[2] * src1->ne[3];
     if (M == 0 || N == 0) return B200Q_OK;
     ActView act;
-    if ((st = get_activation(ctx, ti.act_form, src1, &act)) != B200Q_OK) return st;
     int64_t ldd;
     const bool uniform = dst_uniform(dst, &ldd);
+    // prompt widths of the per-32 types go to the tensor cores
+    if (N > 8 && uniform && !ctx->no_tc && gemm_tc_supported(src0->type, M, K, N, src0->data, src0->nb[1])) {
+        if ((st = get_activation(ctx, ACT_Q8_0_TILED, src1, &act)) != B200Q_OK) return st;
+        return launch_gemm_tc(ctx, src0->type, src0->data, src0->nb[1], M, K, (const uint8_t *)act.codes, N,
+                              (float *)dst->data, ldd);
+    }
+    if (N > 8) count(ctx, ST_GEMM_FALLBACK_SHAPE);
+    if ((st = get_activation(ctx, ti.act_form, src1, &act)) != B200Q_OK) return st;
     // decode widths go to the GEMV; wider products walk it in groups of eight columns
     // until the tensor-core GEMM takes them
     const int64_t run = uniform ? N : dst->ne[1];     // columns that share one stride
@@ -357,6 +383,13 @@ b200q_status b200q_tensor_copy(b200q_ctx *ctx, void *dev_dst, const void *dev_sr
 b200q_status b200q_synchronize(b200q_ctx *ctx) {
     if (!ctx) return B200Q_INVALID;
     B200Q_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // a kernel whose bounded wait ran out says so here
+    int err = 0;
+    B200Q_CUDA(ctx, cudaMemcpy(&err, ctx->error_word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (err) {
+        cudaMemset(ctx->error_word, 0, sizeof(int));
+        return fail(ctx, B200Q_TIMEOUT, "a device-side wait gave up (error word %d)", err);
+    }
     return B200Q_OK;
 }
 

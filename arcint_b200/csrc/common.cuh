@@ -36,7 +36,7 @@ __host__ __device__ inline bool type_info(int type, TypeInfo *ti) {
     }
 }
 
-enum { ACT_Q8_0 = 0, ACT_Q8_256 = 1 };
+enum { ACT_Q8_0 = 0, ACT_Q8_256 = 1, ACT_Q8_0_TILED = 2 };   // TILED: the tensor-core GEMM's chunk layout
 
 // Quantized activation as the kernels read it: column c of K values at
 //   codes  + c*K            int8
@@ -105,6 +105,7 @@ struct b200q_ctx {
     int          sm_count = 148;
     uint64_t     generation = 1;
     bool         capturing = false;
+    bool         no_tc = false;           // B200Q_NO_TC=1: never take the tensor-core GEMM
     std::string  last_error;
     std::string  stats_text;
     uint64_t     counters[b200q::ST_COUNT] = {};
@@ -116,7 +117,7 @@ struct b200q_ctx {
     std::vector<b200q::RouteEntry *> routes;
     cudaEvent_t  ev0 = nullptr, ev1 = nullptr;
     void        *tp = nullptr;   // tensor/expert-parallel state (tp.cu)
-    void        *gemm = nullptr; // tcgen05 GEMM state (gemm_tc.cu)
+    int         *error_word = nullptr;   // device word a kernel sets when a bounded wait runs out
 };
 
 namespace b200q {
@@ -142,5 +143,12 @@ b200q_status launch_dequantize(b200q_ctx *ctx, int type, const void *w, int64_t 
 // gemv.cu: dst[m + c*ldd] for c < ncols (<= 8), rows [0, M)
 b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                          const ActView &act, int64_t col0, int ncols, float *dst, int64_t ldd);
+
+// gemm_tc.cu: tensor-core prefill GEMM (Q4_0, Q8_0)
+bool         gemm_tc_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride);
+size_t       gemm_tc_act_bytes(int64_t K, int64_t N);
+b200q_status launch_quantize_tiled(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out);
+b200q_status launch_gemm_tc(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
+                            const uint8_t *act, int64_t N, float *dst, int64_t ldd);
 
 }  // namespace b200q

@@ -1,0 +1,438 @@
+// gemm_tc.cu -- prefill GEMM for Q4_0 / Q8_0 weights on the 5th-generation tensor cores.
+//
+//   dst[M, N] = W[M, K] (packed GGUF blocks) x X[K, N] (f32), N > 8 tokens
+//
+// ggml's form is kept exactly: the activation is quantized per 32 to int8 with an fp16
+// scale (block_q8_0), every 32-wide block dot I_b[r, c] is an exact int32 from one
+// tcgen05.mma kind::i8 (M=128, N=128, K=32) whose accumulator lives in tensor memory,
+// and the result is sum_b float(I_b) * d_w[r, b] * d_x[c, b] in f32 -- the arithmetic of
+// the reference's int8 GEMM (marfrit/arcint contrib/llama.cpp/patches/
+// 0099-opencl-q4_0-q8_0-int8-gemm.patch:377-455, 583-628: one int8 DPAS per 32 weights,
+// af = fma(float(ir), d_w, af)), with ggml's per-32 activation scale instead of the
+// reference's per-256 one.
+//
+// One CTA owns a 128-row x 128-token output tile. Warp roles:
+//   warp 0      producer: bulk copies (cp.async.bulk + mbarrier complete_tx) of the raw
+//               packed weight rows of a k-stage (256 weights per row) and of the
+//               activation chunk (int8 codes already in the tensor core's K-major core-matrix
+//               order, plus their scales), three stages deep;
+//   warp 1      allocates tensor memory, issues the MMAs (one elected thread) and commits
+//               them to mbarriers;
+//   warps 2..5  one thread per weight row: unpack the row's blocks to int8 (code - 8) into
+//               the A-operand ring in core-matrix order, and, two blocks behind, pull the
+//               finished block accumulator out of tensor memory (tcgen05.ld), scale and
+//               accumulate it into 128 f32 registers.
+// Four 128-column accumulators fill the 512 tensor-memory columns, so the MMA of block b+1..
+// b+3 runs while block b is being scaled. The scaling is the bound, not the tensor pipe:
+// every output element needs a convert, a multiply and a fused multiply-add per 32 of K,
+// 16K elements per block against 128 FP32 lanes per SM and clock.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets an error word, all roles
+// leave their loops, tensor memory is freed and the launch reports B200Q_TIMEOUT at the
+// next synchronize.
+#include "formats.cuh"
+#include "common.cuh"
+
+namespace b200q {
+
+namespace tc {
+
+constexpr int BM = 128;            // weight rows per tile (MMA M, tensor-memory lanes)
+constexpr int BN = 128;            // tokens per tile (MMA N, tensor-memory columns per accumulator)
+constexpr int KB = 32;             // weights per MMA (one quantization block)
+constexpr int SB = 8;              // blocks per k-stage (256 weights)
+constexpr int NACC = 4;            // accumulators in tensor memory (4 x 128 = 512 columns)
+constexpr int LAG = 2;             // blocks between a thread's unpack and its scale-accumulate
+constexpr int OPER_BYTES = BM * KB;                         // one int8 operand block: 4096 B
+constexpr int ACT_CHUNK = SB * OPER_BYTES + SB * BN * 4;    // codes + f32 scales of a stage: 36864 B
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 20;
+
+// K-major, no swizzle: 8 rows x 16 bytes are one contiguous 128-byte core matrix; the two
+// 16-byte halves of K=32 are LBO apart, the sixteen 8-row groups SBO apart.
+constexpr uint32_t LBO = 16 * 128, SBO = 128;
+
+template <int TYPE> struct Raw;     // packed bytes of one row per stage
+template <> struct Raw<B200Q_TYPE_Q4_0> { enum { ROW = SB * 18, NSTAGE = 3 }; };     // 144 B per row and stage
+template <> struct Raw<B200Q_TYPE_Q8_0> { enum { ROW = SB * 34, NSTAGE = 2 }; };     // 272 B: two stages fit
+
+template <int TYPE> struct Smem {
+    enum {
+        NSTAGE = Raw<TYPE>::NSTAGE,         // raw-weight / activation stages in flight
+        RAW_STAGE = BM * Raw<TYPE>::ROW,
+        RAW_OFF = 0,
+        ACT_OFF = RAW_OFF + NSTAGE * RAW_STAGE,
+        A_OFF = ACT_OFF + NSTAGE * ACT_CHUNK,
+        BAR_OFF = A_OFF + SB * OPER_BYTES,
+        TOTAL = BAR_OFF + 8 * 64             // room for up to 64 mbarriers (BAR_COUNT of them are used)
+    };
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false when the limit ran out or another role already gave up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 63) == 63 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+// the same for a whole warp: every lane finishes its own bounded wait, then the warp agrees
+// on the outcome, so the warp-synchronous instructions that follow never see a split warp
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag) ? 1 : 0) != 0;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)(LBO >> 4) << 16) | ((uint64_t)(SBO >> 4) << 32) | (1ull << 46);
+}
+// D[128 x 128] (int32, tensor memory) = A[128 x 32] (int8, K-major) x B[128 x 32]^T
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+constexpr uint32_t IDESC_I8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+// barrier slots inside the shared block
+enum { BAR_RAW_FULL = 0, BAR_RAW_EMPTY = 3, BAR_ACT_FULL = 6, BAR_ACT_EMPTY = 9, BAR_A_FULL = 12, BAR_A_EMPTY = 20,
+       BAR_ACC_FULL = 28, BAR_ACC_EMPTY = 32, BAR_COUNT = 36 };
+static_assert(BAR_COUNT <= 64, "the shared block reserves 64 mbarrier slots");
+
+// Activation chunk (n-tile t, k-stage s) in global memory, written by quantize_tiled_kernel:
+//   codes  [block j < 8][half c < 2][group g < 16][column r < 8][16 bytes]   column 8g + r, k = 32j + 16c + byte
+//   scales [block j < 8][column < 128] f32 (the fp16-rounded block scale)
+__global__ void __launch_bounds__(256)
+quantize_tiled_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t nb1, size_t nb2, size_t nb3, int64_t K,
+                      int64_t N, uint8_t *__restrict__ out) {
+    const int t = blockIdx.y, s = blockIdx.x, nst = gridDim.x;
+    const int col = threadIdx.x & 127, half = threadIdx.x >> 7;
+    const int64_t n = (int64_t)t * BN + col;
+    uint8_t *chunk = out + ((size_t)t * nst + s) * ACT_CHUNK;
+    const float *x = nullptr;
+    if (n < N) {
+        const int64_t c1 = n % ne1, c23 = n / ne1, c2 = c23 % ne2, c3 = c23 / ne2;
+        x = reinterpret_cast<const float *>(base + c1 * nb1 + c2 * nb2 + c3 * nb3) + (int64_t)s * (SB * KB);
+    }
+#pragma unroll 1
+    for (int jj = 0; jj < 4; ++jj) {
+        const int j = 4 * half + jj;
+        float v[32];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float4 f = x ? *reinterpret_cast<const float4 *>(x + 32 * j + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+        }
+        const float d = __fdiv_rn(amax, 127.f);
+        const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint32_t p = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) p |= (uint32_t)((int)roundf(__fmul_rn(v[4 * i + b], id)) & 0xFF) << (8 * b);
+            w[i] = p;
+        }
+        uint8_t *o = chunk + j * OPER_BYTES + (col >> 3) * 128 + (col & 7) * 16;
+        *reinterpret_cast<uint4 *>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4 *>(o + LBO) = make_uint4(w[4], w[5], w[6], w[7]);
+        reinterpret_cast<float *>(chunk + SB * OPER_BYTES)[j * BN + col] = __half2float(__float2half_rn(d));
+    }
+}
+
+template <int N> __device__ __forceinline__ uint32_t word_at(const uint32_t (&w)[N], int byte_off) {
+    // 32-bit word at a compile-time even byte offset of a register array
+    const int i = byte_off >> 2, sh = (byte_off & 3) * 8;
+    return sh == 0 ? w[i] : __funnelshift_r(w[i], w[i + 1], sh);
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, const uint8_t *__restrict__ act,
+               int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word) {
+    typedef Smem<TYPE> L;
+    constexpr int ROWB = Raw<TYPE>::ROW;
+    constexpr int NSTAGE = L::NSTAGE;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+    const int row0 = tile_m * BM;
+    const int nst = K / (SB * KB);              // k-stages
+    const int nblk = nst * SB;
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bars = sbase + L::BAR_OFF;
+    auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+    const int valid_rows = min(BM, M - row0);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int i = 0; i < NSTAGE; ++i) {
+            mbar_init(bar(BAR_RAW_FULL + i), 1);
+            mbar_init(bar(BAR_RAW_EMPTY + i), 128);
+            mbar_init(bar(BAR_ACT_FULL + i), 1);
+            mbar_init(bar(BAR_ACT_EMPTY + i), 1 + 128);      // MMA commit + every scaling thread
+        }
+        for (int i = 0; i < SB; ++i) {
+            mbar_init(bar(BAR_A_FULL + i), 128);
+            mbar_init(bar(BAR_A_EMPTY + i), 1);
+        }
+        for (int i = 0; i < NACC; ++i) {
+            mbar_init(bar(BAR_ACC_FULL + i), 1);
+            mbar_init(bar(BAR_ACC_EMPTY + i), 128);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int *abortp = &abort_flag;
+
+    if (warp == 0) {
+        // ---- producer ----
+        const uint8_t *act_tile = act + (size_t)tile_n * nst * ACT_CHUNK;
+        for (int s = 0; s < nst; ++s) {
+            const int st = s % NSTAGE;
+            const uint32_t par = ((s / NSTAGE) & 1) ^ 1;        // first pass over the ring: slots are free
+            if (!mbar_wait_warp(bar(BAR_RAW_EMPTY + st), par, abortp)) break;
+            if (lane == 0) mbar_expect_tx(bar(BAR_RAW_FULL + st), (uint32_t)valid_rows * ROWB);
+            __syncwarp();
+            for (int r = lane; r < valid_rows; r += 32)
+                bulk_g2s(sbase + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB,
+                         W + (size_t)(row0 + r) * row_stride + (size_t)s * ROWB, ROWB, bar(BAR_RAW_FULL + st));
+            if (!mbar_wait_warp(bar(BAR_ACT_EMPTY + st), par, abortp)) break;
+            if (lane == 0) {
+                mbar_expect_tx(bar(BAR_ACT_FULL + st), ACT_CHUNK);
+                bulk_g2s(sbase + L::ACT_OFF + st * ACT_CHUNK, act_tile + (size_t)s * ACT_CHUNK, ACT_CHUNK,
+                         bar(BAR_ACT_FULL + st));
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        for (int b = 0; b < nblk; ++b) {
+            const int s = b / SB, j = b % SB, st = s % NSTAGE, acc = b % NACC;
+            if (j == 0 && !mbar_wait_warp(bar(BAR_ACT_FULL + st), (s / NSTAGE) & 1, abortp)) break;
+            if (!mbar_wait_warp(bar(BAR_A_FULL + j), (b / SB) & 1, abortp)) break;
+            if (!mbar_wait_warp(bar(BAR_ACC_EMPTY + acc), ((b / NACC) & 1) ^ 1, abortp)) break;
+            tc_fence_after();
+            if (lane == 0) {
+                umma_i8(tmem_base + (uint32_t)acc * BN, umma_desc(sbase + L::A_OFF + j * OPER_BYTES),
+                        umma_desc(sbase + L::ACT_OFF + st * ACT_CHUNK + j * OPER_BYTES), IDESC_I8);
+                tc_commit(bar(BAR_ACC_FULL + acc));
+                tc_commit(bar(BAR_A_EMPTY + j));
+                if (j == SB - 1) tc_commit(bar(BAR_ACT_EMPTY + st));
+            }
+            __syncwarp();
+        }
+    } else {
+        // ---- one thread per weight row: unpack ahead, scale-accumulate behind ----
+        const int r = (warp & 3) * 32 + lane;              // tensor-memory lane = row of the tile
+        const bool row_ok = r < valid_rows;
+        float accf[BN];
+#pragma unroll
+        for (int c = 0; c < BN; ++c) accf[c] = 0.f;
+        float dw[SB];                 // block scales by position in the stage; the entries not yet
+                                      // overwritten still belong to the stage before (for the lag)
+#pragma unroll
+        for (int j = 0; j < SB; ++j) dw[j] = 0.f;
+        bool ok = true;
+
+        auto scale_block = [&](int b, float dwb) -> bool {
+            const int s = b / SB, j = b % SB, st = s % NSTAGE, acc = b % NACC;
+            if (!mbar_wait_warp(bar(BAR_ACC_FULL + acc), (b / NACC) & 1, abortp)) return false;
+            tc_fence_after();
+            const float *dx = reinterpret_cast<const float *>(smem + L::ACT_OFF + st * ACT_CHUNK + SB * OPER_BYTES) + j * BN;
+            const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)acc * BN;
+#pragma unroll
+            for (int q = 0; q < BN / 32; ++q) {
+                uint32_t v[32];
+                tmem_ld32(taddr + q * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                    accf[q * 32 + c] = fmaf((float)(int)v[c], dwb * dx[q * 32 + c], accf[q * 32 + c]);
+            }
+            tc_fence_before();
+            mbar_arrive(bar(BAR_ACC_EMPTY + acc));
+            if (j == SB - 1) mbar_arrive(bar(BAR_ACT_EMPTY + st));     // done reading this stage's scales
+            return true;
+        };
+
+        for (int s = 0; s < nst && ok; ++s) {
+            const int st = s % NSTAGE;
+            if (!mbar_wait_warp(bar(BAR_RAW_FULL + st), (s / NSTAGE) & 1, abortp)) { ok = false; break; }
+            // the row's packed bytes of this stage, as words
+            uint32_t rw[ROWB / 4 + 1];
+            const uint4 *rp = reinterpret_cast<const uint4 *>(smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB);
+#pragma unroll
+            for (int i = 0; i < ROWB / 16; ++i) {
+                const uint4 t = row_ok ? rp[i] : make_uint4(0, 0, 0, 0);
+                rw[4 * i] = t.x; rw[4 * i + 1] = t.y; rw[4 * i + 2] = t.z; rw[4 * i + 3] = t.w;
+            }
+            rw[ROWB / 4] = 0;
+            mbar_arrive(bar(BAR_RAW_EMPTY + st));
+            // the activation stage must have landed before its scales are read below
+            if (!mbar_wait_warp(bar(BAR_ACT_FULL + st), (s / NSTAGE) & 1, abortp)) { ok = false; break; }
+#pragma unroll
+            for (int j = 0; j < SB; ++j) {
+                const int b = s * SB + j;
+                if (!mbar_wait_warp(bar(BAR_A_EMPTY + j), ((b / SB) & 1) ^ 1, abortp)) { ok = false; break; }
+                constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
+                const uint32_t hw = word_at(rw, BB * j);
+                dw[j] = half_bits_to_float((uint16_t)hw);
+                uint32_t lo[4], hi[4];
+                if (TYPE == B200Q_TYPE_Q4_0) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t q = word_at(rw, BB * j + 2 + 4 * i);
+                        lo[i] = nib_minus8(q & 0x0F0F0F0Fu);           // weights 4i..4i+3
+                        hi[i] = nib_minus8((q >> 4) & 0x0F0F0F0Fu);    // weights 16+4i..
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        lo[i] = word_at(rw, BB * j + 2 + 4 * i);
+                        hi[i] = word_at(rw, BB * j + 18 + 4 * i);
+                    }
+                }
+                uint8_t *a = smem + L::A_OFF + j * OPER_BYTES + (r >> 3) * 128 + (r & 7) * 16;
+                *reinterpret_cast<uint4 *>(a) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4 *>(a + LBO) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                fence_async_smem();
+                mbar_arrive(bar(BAR_A_FULL + j));
+                // scale-accumulate the block LAG behind
+                const int bl = b - LAG;
+                if (bl >= 0) {
+                    const float dwb = dw[(j - LAG + SB) % SB];
+                    if (!scale_block(bl, dwb)) { ok = false; break; }
+                }
+            }
+        }
+        // drain the last LAG blocks
+#pragma unroll
+        for (int t = LAG; t >= 1; --t) {
+            const int bl = nblk - t;
+            if (ok && bl >= 0) ok = scale_block(bl, dw[SB - t]);
+        }
+        if (ok && row_ok) {
+            float *o = dst + row0 + r;
+            const int n0 = tile_n * BN;
+#pragma unroll
+            for (int c = 0; c < BN; ++c)
+                if (n0 + c < N) o[(int64_t)(n0 + c) * ldd] = accf[c];
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        // a wait ran out: give copies still in flight time to land before the block's shared
+        // memory is released, and tell the host
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        if (threadIdx.x == 0) atomicExch(error_word, 1);
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+}  // namespace tc
+
+size_t gemm_tc_act_bytes(int64_t K, int64_t N) {
+    const int64_t ntile = (N + tc::BN - 1) / tc::BN, nst = K / (tc::SB * tc::KB);
+    return (size_t)(ntile * nst) * tc::ACT_CHUNK;
+}
+
+bool gemm_tc_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride) {
+    if (type != B200Q_TYPE_Q4_0 && type != B200Q_TYPE_Q8_0) return false;
+    if (K % (tc::SB * tc::KB) || K <= 0 || M <= 0 || N <= 0) return false;
+    if ((uintptr_t)w % 16 || row_stride % 16) return false;          // bulk copies of row pieces
+    if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return false;
+    return true;
+}
+
+b200q_status launch_quantize_tiled(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out) {
+    const int64_t K = src1->ne[0], N = src1->ne[1] * src1->ne[2] * src1->ne[3];
+    dim3 grid((unsigned)(K / (tc::SB * tc::KB)), (unsigned)((N + tc::BN - 1) / tc::BN));
+    tc::quantize_tiled_kernel<<<grid, 256, 0, ctx->stream>>>((const uint8_t *)src1->data, src1->ne[1], src1->ne[2],
+                                                            src1->nb[1], src1->nb[2], src1->nb[3], K, N, out);
+    B200Q_CUDA(ctx, cudaGetLastError());
+    count(ctx, ST_GEMM_TC_QUANT);
+    return B200Q_OK;
+}
+
+template <int TYPE>
+static b200q_status launch_t(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K, const uint8_t *act,
+                             int64_t N, float *dst, int64_t ldd) {
+    typedef tc::Smem<TYPE> L;
+    auto kern = tc::gemm_tc_kernel<TYPE>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        B200Q_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::TOTAL));
+        attr_set = true;
+    }
+    dim3 grid((unsigned)((N + tc::BN - 1) / tc::BN), (unsigned)((M + tc::BM - 1) / tc::BM));
+    kern<<<grid, tc::THREADS, L::TOTAL, ctx->stream>>>((const uint8_t *)w, row_stride, (int)M, (int)K, act, (int)N, dst,
+                                                       ldd, ctx->error_word);
+    B200Q_CUDA(ctx, cudaGetLastError());
+    count(ctx, ST_GEMM_TC);
+    return B200Q_OK;
+}
+
+b200q_status launch_gemm_tc(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
+                            const uint8_t *act, int64_t N, float *dst, int64_t ldd) {
+    if (type == B200Q_TYPE_Q4_0) return launch_t<B200Q_TYPE_Q4_0>(ctx, w, row_stride, M, K, act, N, dst, ldd);
+    if (type == B200Q_TYPE_Q8_0) return launch_t<B200Q_TYPE_Q8_0>(ctx, w, row_stride, M, K, act, N, dst, ldd);
+    return fail(ctx, B200Q_UNSUPPORTED, "gemm_tc: type %d", type);
+}
+
+}  // namespace b200q

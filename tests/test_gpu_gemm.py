@@ -1,0 +1,85 @@
+"""GPU parity of the tensor-core prefill GEMM (Q4_0 / Q8_0, more than 8 tokens) through the
+C ABI against the CPU oracle: f32 outputs within max relative error 1e-3 of the fp64 product
+of the same quantized operands; NMSE against the unquantized-activation product under the
+reference's op-suite bound (5e-4). Shapes follow the reference's cases (marfrit/arcint
+contrib/llama.cpp/patches/0000-01-kquant-integer-dpas.patch:3965-4035: 300 x {17,40,64,100}
+x 1024, 1023 x n x 4096)."""
+import numpy as np
+import pytest
+
+import arcint_b200 as A
+import oracle as O
+from gpu_util import TOL, make_weights, nmse, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = A.Context(0)
+    yield c
+    c.close()
+
+
+def run(ctx, t, w, k, x):
+    ctx.stats_reset()
+    got = ctx.run_mul_mat(t, w, k, x)
+    return got, ctx.stats()
+
+
+@pytest.mark.parametrize("t", [A.Q4_0, A.Q8_0])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (128, 16, 256), (256, 128, 512), (300, 17, 1024), (300, 40, 1024),
+                                   (300, 64, 1024), (300, 100, 1024), (1023, 33, 4096), (77, 9, 4096), (512, 300, 2560)])
+def test_gemm_tc_matches_oracle(ctx, t, m, n, k):
+    rng = np.random.default_rng(m * 7 + n)
+    w = O.random_blocks(t, m, k, rng)
+    x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1, st                  # the tensor-core path ran, not the fallback
+    assert np.isfinite(got).all()
+    assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
+
+
+@pytest.mark.parametrize("t", [A.Q4_0, A.Q8_0])
+def test_gemm_tc_nmse_against_f32_activations(ctx, t):
+    m, n, k = 384, 200, 2048
+    w = make_weights(t, m, k, 60 + t)
+    x = O.fill_normal(n * k, 61, 1.0).reshape(n, k)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1
+    assert nmse(got, O.mul_mat_f64(t, w, k, x, False)) < 5e-4
+
+
+def test_gemm_tc_agrees_with_gemv_path(ctx):
+    """The same product through the decode kernel (8 columns at a time) and the tensor cores."""
+    t, m, n, k = A.Q4_0, 256, 24, 1024
+    rng = np.random.default_rng(5)
+    w = O.random_blocks(t, m, k, rng)
+    x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
+    got, _ = run(ctx, t, w, k, x)
+    parts = np.concatenate([ctx.run_mul_mat(t, w, k, x[i:i + 8]) for i in range(0, n, 8)])
+    assert rel_err(got, parts.astype(np.float64)) < 1e-4
+
+
+def test_gemm_shapes_outside_the_tensor_core_gate_fall_back(ctx):
+    """K not a multiple of 256: the product still runs (decode kernel in column groups) and says so."""
+    t, m, n, k = A.Q4_0, 64, 20, 2080
+    rng = np.random.default_rng(6)
+    w = O.random_blocks(t, m, k, rng)
+    x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 0 and st.get("gemm_fallback_shape", 0) == 1
+    assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
+
+
+def test_config1_full_size(ctx):
+    """BASELINE config 1: Q4_0 4096 x 4096 weights, 512 tokens; sampled rows against the oracle."""
+    t, m, n, k = A.Q4_0, 4096, 512, 4096
+    w = make_weights(t, m, k, 0x5EED0000)
+    x = O.fill_normal(n * k, 0x5EED0100, 1.0).reshape(n, k)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1
+    rows = np.unique(np.concatenate([[0, 1, 127, 128, m - 1], np.random.default_rng(1).integers(0, m, 40)]))
+    ref = O.mul_mat_f64(t, w[rows], k, x, True)
+    assert rel_err(got[:, rows], ref) < TOL
+    assert np.isfinite(got).all()
