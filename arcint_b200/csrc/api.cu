@@ -113,8 +113,17 @@ static b200q_status get_activation(b200q_ctx *ctx, int form, const b200q_tensor 
     const int64_t K = src1->ne[0], N = src1->ne[1] * src1->ne[2] * src1->ne[3];
     if (!hit) {
         if (ctx->act_cache.size() < 4) ctx->act_cache.resize(4);
-        ActEntry &e = ctx->act_cache[ctx->act_next];
-        ctx->act_next = (ctx->act_next + 1) % ctx->act_cache.size();
+        // victim: an entry of an older graph (its contents are dead), the first one if several,
+        // so a steady sequence of graphs keeps landing in the same, already sized, buffers;
+        // only when all four belong to this graph do they rotate
+        size_t pick = ctx->act_cache.size();
+        for (size_t i = 0; i < ctx->act_cache.size(); ++i)
+            if (!ctx->act_cache[i].valid || ctx->act_cache[i].key.gen != ctx->generation) { pick = i; break; }
+        if (pick == ctx->act_cache.size()) {
+            pick = ctx->act_next;
+            ctx->act_next = (ctx->act_next + 1) % ctx->act_cache.size();
+        }
+        ActEntry &e = ctx->act_cache[pick];
         e.valid = false;
         b200q_status st;
         if (form == ACT_Q8_0_TILED) {

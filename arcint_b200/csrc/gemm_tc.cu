@@ -18,10 +18,11 @@
 //               order, plus their scales), three stages deep;
 //   warp 1      allocates tensor memory, issues the MMAs (one elected thread) and commits
 //               them to mbarriers;
-//   warps 2..5  one thread per weight row: unpack the row's blocks to int8 (code - 8) into
-//               the A-operand ring in core-matrix order, and, two blocks behind, pull the
-//               finished block accumulator out of tensor memory (tcgen05.ld), scale and
-//               accumulate it into 128 f32 registers.
+//   warps 4..7  one thread per weight row: unpack the row's blocks to int8 (code - 8) into
+//               the A-operand ring in core-matrix order and publish the block's fp16 scale;
+//   warps 8..   scale-accumulate, NW warps per tensor-memory lane quarter: pull the finished
+//               block accumulator out of tensor memory (tcgen05.ld), free it, convert, scale by
+//               d_w * d_x and accumulate into f32 registers (thread = row x 128/NW columns).
 // Four 128-column accumulators fill the 512 tensor-memory columns, so the MMA of block b+1..
 // b+3 runs while block b is being scaled. The scaling is the bound, not the tensor pipe:
 // every output element needs a convert, a multiply and a fused multiply-add per 32 of K,
@@ -42,10 +43,10 @@ constexpr int BN = 128;            // tokens per tile (MMA N, tensor-memory colu
 constexpr int KB = 32;             // weights per MMA (one quantization block)
 constexpr int SB = 8;              // blocks per k-stage (256 weights)
 constexpr int NACC = 4;            // accumulators in tensor memory (4 x 128 = 512 columns)
-constexpr int LAG = 2;             // blocks between a thread's unpack and its scale-accumulate
 constexpr int OPER_BYTES = BM * KB;                         // one int8 operand block: 4096 B
 constexpr int ACT_CHUNK = SB * OPER_BYTES + SB * BN * 4;    // codes + f32 scales of a stage: 36864 B
-constexpr int THREADS = 192;
+constexpr int NW = 2;              // scale-accumulate warps per tensor-memory lane quarter
+constexpr int THREADS = 32 * (8 + 4 * NW);   // warp groups: {producer, MMA, 2 idle}, unpack, NW x scale-accumulate
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
 
 // K-major, no swizzle: 8 rows x 16 bytes are one contiguous 128-byte core matrix; the two
@@ -89,6 +90,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try(bar, parity)) return true;
+        if (i > 8) __nanosleep(32);                 // leave the issue slots to the working warps
         if ((i & 63) == 63 && *abort_flag) return false;
     }
     *abort_flag = 1;
@@ -126,6 +128,50 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
                    "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
                    "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
                    "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(addr) : "memory");
+}
+// 16-byte shared load kept where it is written (volatile asm keeps program order), so the
+// compiler does not hoist a whole block's worth of scale loads into live registers
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+// two f32 lanes per register pair: Blackwell's packed FP32 instructions halve the issue slots
+// of the scale-accumulate (the FP32 pipe still does two lanes' worth of work per instruction)
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// two 64-bit shared loads kept in program order (see lds128)
+__device__ __forceinline__ void lds128_f2(uint32_t addr, f32x2 &a, f32x2 &b) {
+    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                  : "r"(addr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -210,9 +256,9 @@ gemm_tc_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, c
         abort_flag = 0;
         for (int i = 0; i < NSTAGE; ++i) {
             mbar_init(bar(BAR_RAW_FULL + i), 1);
-            mbar_init(bar(BAR_RAW_EMPTY + i), 128);
+            mbar_init(bar(BAR_RAW_EMPTY + i), 128 + 128 * NW);  // unpack threads + scaling threads (block scales)
             mbar_init(bar(BAR_ACT_FULL + i), 1);
-            mbar_init(bar(BAR_ACT_EMPTY + i), 1 + 128);      // MMA commit + every scaling thread
+            mbar_init(bar(BAR_ACT_EMPTY + i), 1 + 128 * NW);   // MMA commit + every scaling thread
         }
         for (int i = 0; i < SB; ++i) {
             mbar_init(bar(BAR_A_FULL + i), 128);
@@ -220,7 +266,7 @@ gemm_tc_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, c
         }
         for (int i = 0; i < NACC; ++i) {
             mbar_init(bar(BAR_ACC_FULL + i), 1);
-            mbar_init(bar(BAR_ACC_EMPTY + i), 128);
+            mbar_init(bar(BAR_ACC_EMPTY + i), 128 * NW);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -235,8 +281,12 @@ gemm_tc_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, c
     const uint32_t tmem_base = tmem_base_slot;
     volatile int *abortp = &abort_flag;
 
+    // Register budget by role (the launch gives every thread 65536/THREADS registers): each
+    // branch below starts by resizing its warp group's share -- the first two groups hand most
+    // of theirs back, the scale-accumulate groups take them.
     if (warp == 0) {
         // ---- producer ----
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
         const uint8_t *act_tile = act + (size_t)tile_n * nst * ACT_CHUNK;
         for (int s = 0; s < nst; ++s) {
             const int st = s % NSTAGE;
@@ -257,6 +307,7 @@ gemm_tc_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, c
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
         for (int b = 0; b < nblk; ++b) {
             const int s = b / SB, j = b % SB, st = s % NSTAGE, acc = b % NACC;
             if (j == 0 && !mbar_wait_warp(bar(BAR_ACT_FULL + st), (s / NSTAGE) & 1, abortp)) break;
@@ -272,45 +323,19 @@ gemm_tc_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, c
             }
             __syncwarp();
         }
-    } else {
-        // ---- one thread per weight row: unpack ahead, scale-accumulate behind ----
-        const int r = (warp & 3) * 32 + lane;              // tensor-memory lane = row of the tile
+    } else if (warp < 4) {
+        // idle warps of the first warp group
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+    } else if (warp < 8) {
+        // ---- unpack: one thread per weight row ----
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 112;" ::: "memory");
+        const int r = (warp - 4) * 32 + lane;
         const bool row_ok = r < valid_rows;
-        float accf[BN];
-#pragma unroll
-        for (int c = 0; c < BN; ++c) accf[c] = 0.f;
-        float dw[SB];                 // block scales by position in the stage; the entries not yet
-                                      // overwritten still belong to the stage before (for the lag)
-#pragma unroll
-        for (int j = 0; j < SB; ++j) dw[j] = 0.f;
         bool ok = true;
-
-        auto scale_block = [&](int b, float dwb) -> bool {
-            const int s = b / SB, j = b % SB, st = s % NSTAGE, acc = b % NACC;
-            if (!mbar_wait_warp(bar(BAR_ACC_FULL + acc), (b / NACC) & 1, abortp)) return false;
-            tc_fence_after();
-            const float *dx = reinterpret_cast<const float *>(smem + L::ACT_OFF + st * ACT_CHUNK + SB * OPER_BYTES) + j * BN;
-            const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)acc * BN;
-#pragma unroll
-            for (int q = 0; q < BN / 32; ++q) {
-                uint32_t v[32];
-                tmem_ld32(taddr + q * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < 32; ++c)
-                    accf[q * 32 + c] = fmaf((float)(int)v[c], dwb * dx[q * 32 + c], accf[q * 32 + c]);
-            }
-            tc_fence_before();
-            mbar_arrive(bar(BAR_ACC_EMPTY + acc));
-            if (j == SB - 1) mbar_arrive(bar(BAR_ACT_EMPTY + st));     // done reading this stage's scales
-            return true;
-        };
-
         for (int s = 0; s < nst && ok; ++s) {
             const int st = s % NSTAGE;
-            if (!mbar_wait_warp(bar(BAR_RAW_FULL + st), (s / NSTAGE) & 1, abortp)) { ok = false; break; }
-            // the row's packed bytes of this stage, as words
-            uint32_t rw[ROWB / 4 + 1];
+            if (!mbar_wait_warp(bar(BAR_RAW_FULL + st), (s / NSTAGE) & 1, abortp)) break;
+            uint32_t rw[ROWB / 4 + 1];                     // the row's packed bytes of this stage
             const uint4 *rp = reinterpret_cast<const uint4 *>(smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB);
 #pragma unroll
             for (int i = 0; i < ROWB / 16; ++i) {
@@ -319,15 +344,11 @@ gemm_tc_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, c
             }
             rw[ROWB / 4] = 0;
             mbar_arrive(bar(BAR_RAW_EMPTY + st));
-            // the activation stage must have landed before its scales are read below
-            if (!mbar_wait_warp(bar(BAR_ACT_FULL + st), (s / NSTAGE) & 1, abortp)) { ok = false; break; }
 #pragma unroll
             for (int j = 0; j < SB; ++j) {
                 const int b = s * SB + j;
                 if (!mbar_wait_warp(bar(BAR_A_EMPTY + j), ((b / SB) & 1) ^ 1, abortp)) { ok = false; break; }
                 constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
-                const uint32_t hw = word_at(rw, BB * j);
-                dw[j] = half_bits_to_float((uint16_t)hw);
                 uint32_t lo[4], hi[4];
                 if (TYPE == B200Q_TYPE_Q4_0) {
 #pragma unroll
@@ -348,26 +369,79 @@ gemm_tc_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, c
                 *reinterpret_cast<uint4 *>(a + LBO) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                 fence_async_smem();
                 mbar_arrive(bar(BAR_A_FULL + j));
-                // scale-accumulate the block LAG behind
-                const int bl = b - LAG;
-                if (bl >= 0) {
-                    const float dwb = dw[(j - LAG + SB) % SB];
-                    if (!scale_block(bl, dwb)) { ok = false; break; }
-                }
             }
         }
-        // drain the last LAG blocks
+    } else {
+        // ---- scale-accumulate: NW warps per tensor-memory lane quarter, BN/NW columns each ----
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 168;" ::: "memory");
+        constexpr int CW = BN / NW;                        // columns per thread
+        const int q4 = warp & 3, u = (warp - 8) >> 2;      // lane quarter (fixed by warp id % 4), column part
+        const int r = q4 * 32 + lane;
+        const bool row_ok = r < valid_rows;
+        f32x2 acc2[CW / 2];                                // column pairs
 #pragma unroll
-        for (int t = LAG; t >= 1; --t) {
-            const int bl = nblk - t;
-            if (ok && bl >= 0) ok = scale_block(bl, dw[SB - t]);
+        for (int c = 0; c < CW / 2; ++c) acc2[c] = 0ull;
+        bool done = false;                                 // every block was accumulated (no wait gave up)
+        for (int b = 0; b < nblk; ++b) {
+            const int s = b / SB, j = b % SB, st = s % NSTAGE, acc = b % NACC;
+            // A waiter on an mbarrier phase must see it before the phase after it completes:
+            // both stage barriers below cannot advance until this thread has released the stage.
+            if (j == 0 && !mbar_wait_warp(bar(BAR_ACT_FULL + st), (s / NSTAGE) & 1, abortp)) break;
+            if (j == 0 && !mbar_wait_warp(bar(BAR_RAW_FULL + st), (s / NSTAGE) & 1, abortp)) break;
+            if (!mbar_wait_warp(bar(BAR_ACC_FULL + acc), (b / NACC) & 1, abortp)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)acc * BN + (uint32_t)u * CW;
+            // the block's fp16 weight scale, straight from the packed row in the raw stage
+            constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
+            const float dwb = row_ok ? half_bits_to_float(*reinterpret_cast<const uint16_t *>(
+                                           smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + BB * j)) : 0.f;
+            const f32x2 dw2 = f2_pack(dwb, dwb), negc2 = f2_pack(-12582912.f, -12582912.f);
+            const uint32_t dxa = sbase + L::ACT_OFF + st * ACT_CHUNK + SB * OPER_BYTES + (j * BN + u * CW) * 4;
+            // sixteen columns at a time, the next sixteen in flight while these are scaled
+            uint32_t v[2][16];
+            tmem_ld16(taddr, v[0]);
+#pragma unroll
+            for (int q = 0; q < CW / 16; ++q) {
+                tmem_ld_wait();
+                if (q + 1 < CW / 16) {
+                    tmem_ld16(taddr + (q + 1) * 16, v[(q + 1) & 1]);
+                } else {
+                    tc_fence_before();
+                    mbar_arrive(bar(BAR_ACC_EMPTY + acc));     // the accumulator is in registers: free it
+                }
+#pragma unroll
+                for (int c = 0; c < 16; c += 4) {
+                    f32x2 d01, d23;
+                    lds128_f2(dxa + (q * 16 + c) * 4, d01, d23);
+                    const int e = (q * 16 + c) / 2;
+                    // exact int -> float without the conversion pipe (|I| < 2^22): add the
+                    // magic exponent as an integer, subtract it as a float
+                    const f32x2 x01 = f2_add(f2_pack(__int_as_float((int)v[q & 1][c] + 0x4B400000),
+                                                     __int_as_float((int)v[q & 1][c + 1] + 0x4B400000)), negc2);
+                    const f32x2 x23 = f2_add(f2_pack(__int_as_float((int)v[q & 1][c + 2] + 0x4B400000),
+                                                     __int_as_float((int)v[q & 1][c + 3] + 0x4B400000)), negc2);
+                    acc2[e]     = f2_fma(x01, f2_mul(dw2, d01), acc2[e]);
+                    acc2[e + 1] = f2_fma(x23, f2_mul(dw2, d23), acc2[e + 1]);
+                }
+            }
+            if (j == SB - 1) {                                         // done with this stage's scales
+                mbar_arrive(bar(BAR_ACT_EMPTY + st));
+                mbar_arrive(bar(BAR_RAW_EMPTY + st));
+            }
+            done = b == nblk - 1;
         }
-        if (ok && row_ok) {
-            float *o = dst + row0 + r;
-            const int n0 = tile_n * BN;
+        if (done && row_ok) {
+            float *o = dst + (int64_t)(tile_n * BN + u * CW) * ldd + row0 + r;
+            const int ncol = N - (tile_n * BN + u * CW);         // columns of this thread inside the matrix
 #pragma unroll
-            for (int c = 0; c < BN; ++c)
-                if (n0 + c < N) o[(int64_t)(n0 + c) * ldd] = accf[c];
+            for (int c = 0; c < CW; c += 2) {
+                float a0, a1;
+                f2_unpack(acc2[c / 2], a0, a1);
+                if (c < ncol) *o = a0;
+                o += ldd;
+                if (c + 1 < ncol) *o = a1;
+                o += ldd;
+            }
         }
     }
 
