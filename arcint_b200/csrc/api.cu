@@ -100,6 +100,26 @@ static b200q_status check_mul_mat(b200q_ctx *ctx, const b200q_tensor *src0, cons
     return B200Q_OK;
 }
 
+// MUL_MAT_ID shapes: src0 [K, M, n_expert], src1 [K, ne11 in {1, n_used}, n_tok], ids [n_used, n_tok] i32,
+// dst [M, n_used, n_tok] (P01:1174-1219; the column rule kq_i8_col, P09:573-577)
+static b200q_status check_ids(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1,
+                              const b200q_tensor *ids, const b200q_tensor *dst) {
+    if (!ids) return fail(ctx, B200Q_INVALID, "null ids");
+    if (ids->type != B200Q_TYPE_I32 || ids->nb[0] != sizeof(int32_t)) return fail(ctx, B200Q_UNSUPPORTED, "ids must be packed i32");
+    if (ids->ne[2] != 1 || ids->ne[3] != 1 || src1->ne[3] != 1 || dst->ne[3] != 1) return fail(ctx, B200Q_UNSUPPORTED, "4-D MUL_MAT_ID");
+    const int64_t n_used = ids->ne[0], n_tok = ids->ne[1];
+    if (src1->ne[2] != n_tok || (src1->ne[1] != 1 && src1->ne[1] != n_used))
+        return fail(ctx, B200Q_INVALID, "src1 [K, %lld, %lld] against ids [%lld, %lld]", (long long)src1->ne[1],
+                    (long long)src1->ne[2], (long long)n_used, (long long)n_tok);
+    if (dst->ne[1] != n_used || dst->ne[2] != n_tok) return fail(ctx, B200Q_INVALID, "dst shape against ids");
+    if (ids->nb[1] % 4 || (uintptr_t)ids->data % 4) return fail(ctx, B200Q_UNSUPPORTED, "ids rows must be 4-byte aligned");
+    if (src0->ne[2] < 1 || src0->ne[2] > 4096) return fail(ctx, B200Q_UNSUPPORTED, "%lld experts", (long long)src0->ne[2]);
+    if (src0->ne[2] > 1 && src0->nb[2] % 2) return fail(ctx, B200Q_UNSUPPORTED, "expert stride %zu", src0->nb[2]);
+    if (n_used * n_tok > (1 << 28)) return fail(ctx, B200Q_UNSUPPORTED, "too many pairs");
+    if (!ids->data && n_used * n_tok) return fail(ctx, B200Q_INVALID, "null ids data");
+    return B200Q_OK;
+}
+
 // Quantize src1 once per graph: q/k/v and gate/up share their input (P01:670-688).
 static b200q_status get_activation(b200q_ctx *ctx, int form, const b200q_tensor *src1, ActView *out) {
     ActKey key;
@@ -228,6 +248,7 @@ void b200q_free(b200q_ctx *ctx) {
     if (ctx->error_word) cudaFree(ctx->error_word);
     for (auto &w : ctx->moe_ws)
         if (w.ptr) cudaFree(w.ptr);
+    moe_free(ctx);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
@@ -246,8 +267,8 @@ b200q_status b200q_supports(const b200q_ctx *ctx, int op, const b200q_tensor *sr
         return B200Q_OK;
     }
     if (op == B200Q_OP_MUL_MAT_ID) {
-        if (!ids || ids->type != B200Q_TYPE_I32) return B200Q_UNSUPPORTED;
-        return check_mul_mat(nullptr, src0, src1, dst, true);
+        b200q_status st = check_mul_mat(nullptr, src0, src1, dst, true);
+        return st != B200Q_OK ? st : check_ids(nullptr, src0, src1, ids, dst);
     }
     return B200Q_UNSUPPORTED;
 }
@@ -300,8 +321,35 @@ b200q_status b200q_mul_mat(b200q_ctx *ctx, const b200q_tensor *src0, const b200q
 
 b200q_status b200q_mul_mat_id(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1,
                               const b200q_tensor *ids, b200q_tensor *dst) {
-    (void)src0; (void)src1; (void)ids; (void)dst;
-    return fail(ctx, B200Q_UNSUPPORTED, "MUL_MAT_ID not built yet");
+    if (!ctx) return B200Q_INVALID;
+    b200q_status st = check_mul_mat(ctx, src0, src1, dst, true);
+    if (st != B200Q_OK) return st;
+    st = check_ids(ctx, src0, src1, ids, dst);
+    if (st != B200Q_OK) return st;
+    B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+    TypeInfo ti;
+    type_info(src0->type, &ti);
+    const int64_t K = src0->ne[0], M = src0->ne[1];
+    const int n_expert = (int)src0->ne[2], n_used = (int)ids->ne[0], n_tok = (int)ids->ne[1], ne11 = (int)src1->ne[1];
+    if (M == 0 || n_used == 0 || n_tok == 0) return B200Q_OK;
+    ActView act;
+    if ((st = get_activation(ctx, ti.act_form, src1, &act)) != B200Q_OK) return st;
+    const int64_t ld1 = (int64_t)(dst->nb[1] / sizeof(float)), ld2 = (int64_t)(dst->nb[2] / sizeof(float));
+    // a handful of tokens: one unit per pair, its expert read on the device (the reference's
+    // per-pair GEMV below GGML_OPENCL_KQ_MM_ID_MIN_TOK); more: route once per ids tensor
+    // and graph, then one launch per tile size class
+    if (n_tok <= 4)
+        return launch_gemv_id(ctx, src0->type, src0->data, src0->nb[1], src0->nb[2], M, K, act, 1, nullptr, nullptr,
+                              (int64_t)n_used * n_tok, nullptr, ids, n_expert, n_used, ne11, (float *)dst->data, ld1, ld2);
+    RouteView rv;
+    if ((st = moe_route(ctx, ids, n_expert, &rv)) != B200Q_OK) return st;
+    static const int widths[4] = { 1, 2, 4, 8 };
+    for (int k = 3; k >= 0; --k) {
+        st = launch_gemv_id(ctx, src0->type, src0->data, src0->nb[1], src0->nb[2], M, K, act, widths[k], rv.tiles[k],
+                            rv.n_tiles + k, rv.max_tiles, rv.pairs, ids, n_expert, n_used, ne11, (float *)dst->data, ld1, ld2);
+        if (st != B200Q_OK) return st;
+    }
+    return B200Q_OK;
 }
 
 // ---- CUDA graphs ----------------------------------------------------------------------

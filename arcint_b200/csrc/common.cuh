@@ -114,7 +114,8 @@ struct b200q_ctx {
     size_t       act_next = 0;
     b200q::Workspace flush_buf;
     b200q::Workspace moe_ws[8];
-    std::vector<b200q::RouteEntry *> routes;
+    b200q::RouteEntry *routes[2] = { nullptr, nullptr };
+    size_t       route_next = 0;
     cudaEvent_t  ev0 = nullptr, ev1 = nullptr;
     void        *tp = nullptr;   // tensor/expert-parallel state (tp.cu)
     int         *error_word = nullptr;   // device word a kernel sets when a bounded wait runs out
@@ -143,6 +144,22 @@ b200q_status launch_dequantize(b200q_ctx *ctx, int type, const void *w, int64_t 
 // gemv.cu: dst[m + c*ldd] for c < ncols (<= 8), rows [0, M)
 b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                          const ActView &act, int64_t col0, int ncols, float *dst, int64_t ldd);
+
+// MUL_MAT_ID over route tiles of at most tile_pairs (1, 2, 4 or 8) pairs of one expert; tiles == NULL:
+// direct mode, one pair per unit with its expert read from ids on the device (small token counts)
+b200q_status launch_gemv_id(b200q_ctx *ctx, int type, const void *w, size_t row_stride, size_t expert_stride,
+                            int64_t M, int64_t K, const ActView &av, int tile_pairs, const int32_t *tiles,
+                            const int32_t *n_tiles, int64_t max_tiles, const int32_t *pairs, const b200q_tensor *ids,
+                            int n_expert, int n_used, int ne11, float *dst, int64_t ld1, int64_t ld2);
+// moe.cu: route (pairs sorted by expert, tile lists by size class)
+struct RouteView {
+    const int32_t *pairs;          // [n_pairs]
+    const int32_t *tiles[4];       // class k: tiles of at most 1, 2, 4, 8 pairs (int4 each)
+    const int32_t *n_tiles;        // [4] device counters
+    int64_t        max_tiles;      // upper bound of every list
+};
+b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, RouteView *out);
+void         moe_free(b200q_ctx *ctx);
 
 // gemm_tc.cu: tensor-core prefill GEMM (Q4_0, Q8_0)
 bool         gemm_tc_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride);

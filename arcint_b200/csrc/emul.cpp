@@ -37,8 +37,11 @@ static void emul_gemv_t(const uint8_t *W, size_t row_stride, int64_t M, int64_t 
                 if (bt * B + r < M)
                     memcpy((uint8_t *)set.data() + r * S::SLOT, W + (size_t)(bt * B + r) * row_stride + off, (size_t)bytes);
             for (int lane = 0; lane < 32; ++lane) {
+                int cols1[NCG], cols2[N2];
+                for (int c = 0; c < NCG; ++c) cols1[c] = c;
+                for (int c = 0; c < N2; ++c) cols2[c] = NCG + (c < NC2 ? c : 0);
                 GemvX<NCG> X;
-                gemv_load_x<TYPE, NCG>(lane, s, nblk, act, X);
+                gemv_load_x<TYPE, NCG>(lane, s, nblk, act, cols1, X);
                 for (int r = 0; r < B; ++r) {
                     float a[NCG];
                     for (int c = 0; c < NCG; ++c) a[c] = acc[lane][r][c];
@@ -46,14 +49,8 @@ static void emul_gemv_t(const uint8_t *W, size_t row_stride, int64_t M, int64_t 
                     for (int c = 0; c < NCG; ++c) acc[lane][r][c] = a[c];
                 }
                 if (NC2 > 0) {
-                    GemvAct act2 = act;
-                    act2.q += (size_t)NCG * act.K;
-                    if (act.d16) act2.d16 += (size_t)NCG * (act.K / 32);
-                    if (act.d32) act2.d32 += (size_t)NCG * (act.K / 256);
-                    act2.s32 += (size_t)NCG * (act.K / 32);
-                    if (act.s16) act2.s16 += (size_t)NCG * (act.K / 16);
                     GemvX<N2> X2;
-                    gemv_load_x<TYPE, N2>(lane, s, nblk, act2, X2);
+                    gemv_load_x<TYPE, N2>(lane, s, nblk, act, cols2, X2);
                     for (int r = 0; r < B; ++r) {
                         float a[N2];
                         for (int c = 0; c < N2; ++c) a[c] = acc[lane][r][NCG + (c < NC2 ? c : 0)];

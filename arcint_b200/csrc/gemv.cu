@@ -18,18 +18,19 @@
 
 namespace b200q {
 
-template <int TYPE, int NC, int B, int WARPS, int NSETS>
+template <int TYPE, int NC, int B, int WARPS, int NSETS, bool ID>
 static b200q_status launch_one(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K,
-                               const GemvAct &act, float *dst, int64_t ldd, bool aligned) {
+                               const GemvAct &act, float *dst, int64_t ldd, bool aligned, const GemvId &id,
+                               int64_t max_tiles) {
     typedef GemvStage<TYPE> S;
     const size_t smem = (size_t)WARPS * NSETS * B * S::SLOT;
     if (M > INT32_MAX / 2 || K / GemvFmt<TYPE>::BLK_W > INT32_MAX / 256 || ldd > INT32_MAX)
         return fail(ctx, B200Q_UNSUPPORTED, "gemv: dimensions beyond 32-bit indexing");
-    auto kern_a = gemv_kernel<TYPE, NC, B, WARPS, NSETS, true>;
-    auto kern_u = gemv_kernel<TYPE, NC, B, WARPS, NSETS, false>;
+    auto kern_a = gemv_kernel<TYPE, NC, B, WARPS, NSETS, true, ID>;
+    auto kern_u = gemv_kernel<TYPE, NC, B, WARPS, NSETS, false, ID>;
     auto kern = aligned ? kern_a : kern_u;
     // resident CTAs per SM of this instantiation, asked once: the grid is one full wave of
-    // persistent CTAs (or fewer when the matrix is small) and each warp strides over batches
+    // persistent CTAs (or fewer when the work is small) and each warp strides over its units
     static int occ[2] = { 0, 0 };
     if (occ[aligned] == 0) {
         if (smem > 48 * 1024)
@@ -39,12 +40,13 @@ static b200q_status launch_one(b200q_ctx *ctx, const void *w, size_t row_stride,
         occ[aligned] = n > 0 ? n : 1;
     }
     const int64_t n_bt = (M + B - 1) / B;
-    int64_t blocks = (n_bt + WARPS - 1) / WARPS;
+    const int64_t n_units = ID ? n_bt * max_tiles : n_bt;      // ID: an upper bound, the kernel reads the count
+    int64_t blocks = (n_units + WARPS - 1) / WARPS;
     const int64_t cap = (int64_t)ctx->sm_count * occ[aligned];
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     kern<<<(unsigned)blocks, WARPS * 32, smem, ctx->stream>>>((const uint8_t *)w, row_stride, (int)M,
-                                                              (int)(K / GemvFmt<TYPE>::BLK_W), act, dst, (int)ldd);
+                                                              (int)(K / GemvFmt<TYPE>::BLK_W), act, dst, (int)ldd, id);
     B200Q_CUDA(ctx, cudaGetLastError());
     return B200Q_OK;
 }
@@ -55,7 +57,8 @@ static b200q_status launch_nc(b200q_ctx *ctx, const void *w, size_t row_stride, 
     // rows per warp batch: four; eight for three or four columns of a small-block type, where
     // the activation registers are worth sharing further (measured on B200)
     constexpr bool wide = (NC == 3 || NC == 4) && GemvStage<TYPE>::BYTES <= 1152;
-    return launch_one<TYPE, NC, wide ? 8 : 4, 4, 2>(ctx, w, row_stride, M, K, act, dst, ldd, aligned);
+    GemvId none = {};
+    return launch_one<TYPE, NC, wide ? 8 : 4, 4, 2, false>(ctx, w, row_stride, M, K, act, dst, ldd, aligned, none, 0);
 }
 
 template <int TYPE>
@@ -74,8 +77,21 @@ static b200q_status launch_type(b200q_ctx *ctx, const void *w, size_t row_stride
     return fail(ctx, B200Q_INVALID, "gemv: %d columns", nc);
 }
 
-b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
-                         const ActView &av, int64_t col0, int ncols, float *dst, int64_t ldd) {
+// MUL_MAT_ID over route tiles of at most nc pairs (nc = 1, 2, 4 or 8)
+template <int TYPE>
+static b200q_status launch_id_type(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K,
+                                   const GemvAct &act, int nc, float *dst, bool aligned, const GemvId &id,
+                                   int64_t max_tiles) {
+    switch (nc) {
+    case 1: return launch_one<TYPE, 1, 4, 4, 2, true>(ctx, w, row_stride, M, K, act, dst, 0, aligned, id, max_tiles);
+    case 2: return launch_one<TYPE, 2, 4, 4, 2, true>(ctx, w, row_stride, M, K, act, dst, 0, aligned, id, max_tiles);
+    case 4: return launch_one<TYPE, 4, 4, 4, 2, true>(ctx, w, row_stride, M, K, act, dst, 0, aligned, id, max_tiles);
+    case 8: return launch_one<TYPE, 8, 4, 4, 2, true>(ctx, w, row_stride, M, K, act, dst, 0, aligned, id, max_tiles);
+    }
+    return fail(ctx, B200Q_INVALID, "gemv_id: tile of %d pairs", nc);
+}
+
+static GemvAct make_act(const ActView &av, int64_t col0, int64_t K) {
     GemvAct act;
     act.q = av.codes + col0 * K;
     act.d16 = av.d16 ? av.d16 + col0 * (K / 32) : nullptr;
@@ -83,6 +99,46 @@ b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_str
     act.s32 = av.s32 ? av.s32 + col0 * (K / 32) : nullptr;
     act.s16 = av.s16 ? av.s16 + col0 * (K / 16) : nullptr;
     act.K = (int)K;
+    return act;
+}
+
+b200q_status launch_gemv_id(b200q_ctx *ctx, int type, const void *w, size_t row_stride, size_t expert_stride,
+                            int64_t M, int64_t K, const ActView &av, int tile_pairs, const int32_t *tiles,
+                            const int32_t *n_tiles, int64_t max_tiles, const int32_t *pairs, const b200q_tensor *ids,
+                            int n_expert, int n_used, int ne11, float *dst, int64_t ld1, int64_t ld2) {
+    TypeInfo ti;
+    if (!type_info(type, &ti)) return fail(ctx, B200Q_UNSUPPORTED, "gemv_id: type %d", type);
+    const size_t row_bytes = (size_t)(K / ti.block) * ti.bytes;
+    const bool aligned = ((uintptr_t)w % 16 == 0) && (row_stride % 16 == 0) && (row_bytes % 16 == 0) &&
+                         (expert_stride % 16 == 0);
+    GemvId id;
+    id.tiles = tiles;
+    id.n_tiles = n_tiles;
+    id.pairs = pairs;
+    id.ids = (const uint8_t *)ids->data;
+    id.ids_stride = ids->nb[1];
+    id.n_pairs = (int)(ids->ne[0] * ids->ne[1]);
+    id.n_expert = n_expert;
+    id.n_used = n_used;
+    id.ne11 = ne11;
+    id.expert_stride = expert_stride;
+    id.ld1 = ld1;
+    id.ld2 = ld2;
+    const GemvAct act = make_act(av, 0, K);
+    count(ctx, aligned ? ST_GEMV_ID : ST_GEMV_ID_UNALIGNED);
+    switch (type) {
+    case B200Q_TYPE_Q4_0:   return launch_id_type<B200Q_TYPE_Q4_0>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
+    case B200Q_TYPE_Q8_0:   return launch_id_type<B200Q_TYPE_Q8_0>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
+    case B200Q_TYPE_Q4_K:   return launch_id_type<B200Q_TYPE_Q4_K>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
+    case B200Q_TYPE_Q6_K:   return launch_id_type<B200Q_TYPE_Q6_K>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
+    case B200Q_TYPE_IQ4_XS: return launch_id_type<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
+    }
+    return fail(ctx, B200Q_UNSUPPORTED, "gemv_id: type %d", type);
+}
+
+b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
+                         const ActView &av, int64_t col0, int ncols, float *dst, int64_t ldd) {
+    const GemvAct act = make_act(av, col0, K);
     TypeInfo ti;
     if (!type_info(type, &ti)) return fail(ctx, B200Q_UNSUPPORTED, "gemv: type %d", type);
     const size_t row_bytes = (size_t)(K / ti.block) * ti.bytes;

@@ -106,8 +106,10 @@ template <int NC> struct GemvX {
     bool  live2;          // Q4_0/Q8_0: the lane's second block exists
 };
 
+// cols[c]: which column of the quantized activation buffer column c of this launch is (the
+// identity for a dense product, a routed pair's column for MUL_MAT_ID).
 template <int TYPE, int NC>
-B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, GemvX<NC> &X) {
+B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, const int (&cols)[NC], GemvX<NC> &X) {
     typedef GemvFmt<TYPE> F;
     const int K = act.K;
     if (TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_Q8_0) {
@@ -117,8 +119,8 @@ B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, GemvX<N
         X.live2 = b1 < nblk;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
-            const int8_t *xp = act.q + (size_t)c * K;
-            const size_t sc = (size_t)c * (K / 32);
+            const int8_t *xp = act.q + (size_t)cols[c] * K;
+            const size_t sc = (size_t)cols[c] * (K / 32);
             if (X.live) {
                 X.x[c][0] = hd_ld16(xp + 32 * b0);
                 X.x[c][1] = hd_ld16(xp + 32 * b0 + 16);
@@ -146,13 +148,13 @@ B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, GemvX<N
         if (!X.live) return;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
-            const int8_t *xp = act.q + (size_t)c * K + 256 * blk + 64 * g;
+            const int8_t *xp = act.q + (size_t)cols[c] * K + 256 * blk + 64 * g;
 #pragma unroll
             for (int j = 0; j < 4; ++j) X.x[c][j] = hd_ld16(xp + 16 * j);
-            const float dx = ld_f32(act.d32 + (size_t)c * (K / 256) + blk);
+            const float dx = ld_f32(act.d32 + (size_t)cols[c] * (K / 256) + blk);
             X.f0[c] = dx * 0.0625f;      // both nibble dots are kept x16
             X.f1[c] = dx;
-            const uint32_t bp = ld_u32(act.s32 + (size_t)c * (K / 32) + 8 * blk + 2 * g);
+            const uint32_t bp = ld_u32(act.s32 + (size_t)cols[c] * (K / 32) + 8 * blk + 2 * g);
             X.i0[c] = sext16(bp);
             X.i1[c] = sext16(bp >> 16);
         }
@@ -163,10 +165,10 @@ B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, GemvX<N
         if (!X.live) return;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
-            const int8_t *xp = act.q + (size_t)c * K + 256 * blk + 64 * pp;
+            const int8_t *xp = act.q + (size_t)cols[c] * K + 256 * blk + 64 * pp;
 #pragma unroll
             for (int j = 0; j < 4; ++j) X.x[c][j] = hd_ld16(xp + 16 * j);
-            X.f0[c] = ld_f32(act.d32 + (size_t)c * (K / 256) + blk);
+            X.f0[c] = ld_f32(act.d32 + (size_t)cols[c] * (K / 256) + blk);
         }
     } else if (TYPE == B200Q_TYPE_Q6_K) {
         // lane -> block sb, half n, positions t0..t0+15 of the four 32-weight parts of that
@@ -177,12 +179,12 @@ B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, GemvX<N
         if (!X.live) return;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
-            const int8_t *xp = act.q + (size_t)c * K + 256 * blk + 128 * n + t0;
+            const int8_t *xp = act.q + (size_t)cols[c] * K + 256 * blk + 128 * n + t0;
 #pragma unroll
             for (int p = 0; p < 4; ++p) X.x[c][p] = hd_ld16(xp + 32 * p);
-            X.f0[c] = ld_f32(act.d32 + (size_t)c * (K / 256) + blk);
+            X.f0[c] = ld_f32(act.d32 + (size_t)cols[c] * (K / 256) + blk);
             // sums of groups 8n + 2p + hi16, p = 0..3: eight int16 from one 16-byte load
-            const I4 sv = hd_ld16(act.s16 + (size_t)c * (K / 16) + 16 * blk + 8 * n);
+            const I4 sv = hd_ld16(act.s16 + (size_t)cols[c] * (K / 16) + 16 * blk + 8 * n);
             X.i0[c] = -32 * sext16((uint32_t)sv.x >> (16 * hi16));     // sum((q-32) x) = sum(q x) - 32 sum(x)
             X.i1[c] = -32 * sext16((uint32_t)sv.y >> (16 * hi16));
             X.i2[c] = -32 * sext16((uint32_t)sv.z >> (16 * hi16));

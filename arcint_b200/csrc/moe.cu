@@ -1,0 +1,145 @@
+// moe.cu -- MUL_MAT_ID routing: the (token, slot) pairs sorted by expert and cut into tiles
+// of pairs of one expert, as the reference's kernel_moe_route_tiles does (marfrit/arcint
+// contrib/llama.cpp/patches/0000-01-kquant-integer-dpas.patch:2417-2444: count per expert
+// with shared-memory atomics, prefix, emit (expert, first, count) tiles, scatter), with two
+// differences: the tiles are split into four lists by size (at most 1, 2, 4, 8 pairs) so
+// each list runs on the kernel instantiation of that many columns, and the route is kept
+// per ids tensor for the rest of the graph (the reference's route cache, :1264-1287) so
+// gate, up and down of a layer share one.
+//
+// Pair p = t*n_used + i. Ids outside [0, n_expert) are clamped, as in the reference kernel.
+// The order of pairs inside an expert is whatever the atomics give: every pair's result is
+// computed independently of its tile mates, so the order does not reach the output.
+#include "common.cuh"
+
+namespace b200q {
+
+struct RouteEntry {
+    const void *ids_data = nullptr;
+    int64_t ne[2] = { 0, 0 };
+    size_t  nb1 = 0;
+    int     n_expert = 0;
+    uint64_t gen = 0;
+    bool    valid = false;
+    Workspace buf;               // pairs | 4 tile lists | 4 counters
+    RouteView view;
+};
+
+__global__ void __launch_bounds__(1024)
+moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_expert, int32_t *pairs,
+                 int32_t *tiles0, int32_t *tiles1, int32_t *tiles2, int32_t *tiles3, int32_t *n_tiles) {
+    extern __shared__ int sm[];
+    int *cnt = sm, *base = sm + n_expert, *fill = sm + 2 * n_expert, *toff = sm + 3 * n_expert;   // toff: [4][n_expert]
+    const int tid = threadIdx.x, nth = blockDim.x;
+    const int n_pairs = n_used * n_tok;
+    auto expert_of = [&](int p) {
+        const int t = p / n_used, i = p - t * n_used;
+        const int e = reinterpret_cast<const int32_t *>(ids + (size_t)t * nb1)[i];
+        return min(max(e, 0), n_expert - 1);
+    };
+    for (int e = tid; e < n_expert; e += nth) { cnt[e] = 0; fill[e] = 0; }
+    __syncthreads();
+    for (int p = tid; p < n_pairs; p += nth) atomicAdd(&cnt[expert_of(p)], 1);
+    __syncthreads();
+    if (tid < 5) {
+        // five independent prefix sums over the experts, one thread each: the pair offsets and
+        // the tile offsets of the four size classes
+        int acc = 0;
+        for (int e = 0; e < n_expert; ++e) {
+            const int c = cnt[e], rem = c & 7;
+            int v;
+            if (tid == 4) v = c;
+            else if (tid == 3) v = (c >> 3) + (rem >= 5);
+            else if (tid == 2) v = rem == 3 || rem == 4;
+            else if (tid == 1) v = rem == 2;
+            else v = rem == 1;
+            if (tid == 4) base[e] = acc; else toff[tid * n_expert + e] = acc;
+            acc += v;
+        }
+        if (tid < 4) n_tiles[tid] = acc;
+    }
+    __syncthreads();
+    for (int e = tid; e < n_expert; e += nth) {
+        const int c = cnt[e], rem = c & 7, full = c >> 3, first = base[e];
+        int32_t *t3 = tiles3 + 4 * toff[3 * n_expert + e];
+        for (int k = 0; k < full; ++k) { t3[4 * k] = e; t3[4 * k + 1] = first + 8 * k; t3[4 * k + 2] = 8; t3[4 * k + 3] = 0; }
+        if (rem) {
+            int32_t *t = rem >= 5 ? t3 + 4 * full
+                       : rem >= 3 ? tiles2 + 4 * toff[2 * n_expert + e]
+                       : rem == 2 ? tiles1 + 4 * toff[1 * n_expert + e]
+                                  : tiles0 + 4 * toff[e];
+            t[0] = e; t[1] = first + 8 * full; t[2] = rem; t[3] = 0;
+        }
+    }
+    for (int p = tid; p < n_pairs; p += nth) {
+        const int e = expert_of(p);
+        pairs[base[e] + atomicAdd(&fill[e], 1)] = p;
+    }
+}
+
+b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, RouteView *out) {
+    const int n_used = (int)ids->ne[0], n_tok = (int)ids->ne[1];
+    const int64_t n_pairs = (int64_t)n_used * n_tok;
+    RouteEntry *hit = nullptr;
+    for (RouteEntry *e : ctx->routes)
+        if (e && e->valid && e->ids_data == ids->data && e->ne[0] == ids->ne[0] && e->ne[1] == ids->ne[1] &&
+            e->nb1 == ids->nb[1] && e->n_expert == n_expert && e->gen == ctx->generation) { hit = e; break; }
+    if (hit) {
+        count(ctx, ST_ROUTE_CACHE_HIT);
+        *out = hit->view;
+        return B200Q_OK;
+    }
+    // victim: an entry of an older graph first, else round robin
+    size_t pick = 2;
+    for (size_t i = 0; i < 2; ++i)
+        if (!ctx->routes[i] || !ctx->routes[i]->valid || ctx->routes[i]->gen != ctx->generation) { pick = i; break; }
+    if (pick == 2) { pick = ctx->route_next; ctx->route_next ^= 1; }
+    if (!ctx->routes[pick]) ctx->routes[pick] = new RouteEntry();
+    RouteEntry &e = *ctx->routes[pick];
+    e.valid = false;
+    const int64_t max_tiles = (n_pairs + 7) / 8 + (n_expert < n_pairs ? n_expert : n_pairs);
+    const size_t bytes = sizeof(int32_t) * (size_t)(n_pairs + 4 * 4 * max_tiles + 4) + 64;
+    b200q_status st = ws_reserve(ctx, &e.buf, bytes);
+    if (st != B200Q_OK) return st;
+    int32_t *p = (int32_t *)e.buf.ptr;
+    int32_t *pairs = p;
+    int32_t *tl[4];
+    for (int k = 0; k < 4; ++k) tl[k] = p + n_pairs + (size_t)k * 4 * max_tiles;
+    int32_t *n_tiles = p + n_pairs + (size_t)16 * max_tiles;
+    const size_t smem = sizeof(int) * (size_t)n_expert * 7;
+    if (smem > 200 * 1024) return fail(ctx, B200Q_UNSUPPORTED, "route: %d experts", n_expert);
+    static bool attr = false;
+    if (!attr) {
+        B200Q_CUDA(ctx, cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr = true;
+    }
+    moe_route_kernel<<<1, 1024, smem, ctx->stream>>>((const uint8_t *)ids->data, ids->nb[1], n_used, n_tok, n_expert, pairs,
+                                                     tl[0], tl[1], tl[2], tl[3], n_tiles);
+    B200Q_CUDA(ctx, cudaGetLastError());
+    count(ctx, ST_MOE_ROUTE);
+    e.ids_data = ids->data;
+    e.ne[0] = ids->ne[0];
+    e.ne[1] = ids->ne[1];
+    e.nb1 = ids->nb[1];
+    e.n_expert = n_expert;
+    e.gen = ctx->generation;
+    e.view.pairs = pairs;
+    for (int k = 0; k < 4; ++k) e.view.tiles[k] = tl[k];
+    e.view.n_tiles = n_tiles;
+    e.view.max_tiles = max_tiles;
+    e.valid = true;
+    *out = e.view;
+    return B200Q_OK;
+}
+
+void moe_free(b200q_ctx *ctx) {
+    for (RouteEntry *&e : ctx->routes) {
+        if (e) {
+            if (e->buf.ptr) cudaFree(e->buf.ptr);
+            delete e;
+            e = nullptr;
+        }
+    }
+}
+
+}  // namespace b200q
