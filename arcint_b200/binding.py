@@ -29,6 +29,24 @@ def row_bytes(t, k):
     return k // _BLOCK[t][0] * _BLOCK[t][1]
 
 
+def tp_unique_id():
+    """128-byte communicator id (rank 0 makes it, every rank gets a copy)."""
+    buf = (C.c_uint8 * 128)()
+    st = lib().b200q_tp_unique_id(buf)
+    if st != OK:
+        raise B200QError(st, "tp_unique_id")
+    return bytes(buf)
+
+
+def tp_shard(total, unit, nranks, rank):
+    """(first, count) of the slice of `total` rank owns, in whole `unit`s."""
+    first, count = C.c_int64(), C.c_int64()
+    st = lib().b200q_tp_shard(total, unit, nranks, rank, C.byref(first), C.byref(count))
+    if st != OK:
+        raise B200QError(st, "tp_shard")
+    return first.value, count.value
+
+
 class B200QError(RuntimeError):
     def __init__(self, status, msg=""):
         self.status = status
@@ -99,6 +117,14 @@ def lib():
     L.b200q_graph_launch.argtypes = [vp, vp]
     L.b200q_graph_free.argtypes = [vp]
     L.b200q_graph_free.restype = None
+    L.b200q_tp_unique_id.argtypes = [vp]
+    L.b200q_tp_init.argtypes = [vp, vp, C.c_int, C.c_int]
+    L.b200q_tp_rank.argtypes = [vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    L.b200q_tp_shard.argtypes = [C.c_int64, C.c_int64, C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+    L.b200q_all_reduce_f32.argtypes = [vp, vp, sz]
+    L.b200q_all_gather.argtypes = [vp, vp, vp, sz]
+    L.b200q_all_to_all_v.argtypes = [vp, vp, C.POINTER(sz), C.POINTER(sz), vp, C.POINTER(sz), C.POINTER(sz)]
+    L.b200q_tp_check.argtypes = [vp]
     L.b200q_buffer_alloc.argtypes = [vp, sz, C.POINTER(vp)]
     L.b200q_buffer_free.argtypes = [vp, vp]
     L.b200q_tensor_set.argtypes = [vp, vp, vp, sz]
@@ -123,7 +149,8 @@ def lib():
 EXPORTS = [
     "b200q_init", "b200q_free", "b200q_last_error", "b200q_version", "b200q_supports", "b200q_mul_mat",
     "b200q_mul_mat_id", "b200q_graph_begin", "b200q_capture_begin", "b200q_capture_end", "b200q_graph_launch",
-    "b200q_graph_free", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
+    "b200q_graph_free", "b200q_tp_unique_id", "b200q_tp_init", "b200q_tp_rank", "b200q_tp_shard", "b200q_all_reduce_f32",
+    "b200q_all_gather", "b200q_all_to_all_v", "b200q_tp_check", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
     "b200q_tensor_get", "b200q_tensor_copy", "b200q_synchronize", "b200q_host_alloc", "b200q_host_free",
     "b200q_stats", "b200q_stats_reset", "b200q_timer_start", "b200q_timer_stop", "b200q_flush_l2",
     "b200q_debug_quantize_act", "b200q_debug_dequantize",
@@ -230,6 +257,22 @@ class Context:
 
     def mul_mat_status(self, src0, src1, dst):
         return self.L.b200q_mul_mat(self.h, src0, src1, dst)
+
+    # ---- multi-GPU ----
+    def tp_init(self, id_bytes, rank, nranks):
+        buf = (C.c_uint8 * 128).from_buffer_copy(id_bytes)
+        self.check(self.L.b200q_tp_init(self.h, buf, rank, nranks))
+
+    def all_reduce_f32(self, dev, count):
+        self.check(self.L.b200q_all_reduce_f32(self.h, dev, count))
+
+    def all_gather(self, send, recv, bytes_per_rank):
+        self.check(self.L.b200q_all_gather(self.h, send, recv, bytes_per_rank))
+
+    def all_to_all_v(self, send, send_off, send_bytes, recv, recv_off, recv_bytes):
+        n = len(send_bytes)
+        arr = lambda v: (C.c_size_t * n)(*[int(x) for x in v])
+        self.check(self.L.b200q_all_to_all_v(self.h, send, arr(send_off), arr(send_bytes), recv, arr(recv_off), arr(recv_bytes)))
 
     # ---- CUDA graphs ----
     def capture(self, fn):

@@ -73,7 +73,7 @@ def build(force=False, verbose=False):
 
 
 def _extra_link():
-    return []
+    return ["-ldl"]
 
 
 def build_emul(force=False):

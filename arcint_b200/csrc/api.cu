@@ -249,6 +249,7 @@ void b200q_free(b200q_ctx *ctx) {
     for (auto &w : ctx->moe_ws)
         if (w.ptr) cudaFree(w.ptr);
     moe_free(ctx);
+    tp_free(ctx);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);

@@ -161,6 +161,9 @@ struct RouteView {
 b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, RouteView *out);
 void         moe_free(b200q_ctx *ctx);
 
+// tp.cu
+void         tp_free(b200q_ctx *ctx);
+
 // gemm_tc.cu: tensor-core prefill GEMM (Q4_0, Q8_0)
 bool         gemm_tc_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride);
 size_t       gemm_tc_act_bytes(int64_t K, int64_t N);

@@ -1,0 +1,218 @@
+// tp.cu -- the exchanges the multi-GPU splits of the path need, over NCCL (NVLink 5 /
+// NVSwitch): all-reduce of the f32 partial results of a row (K) split, all-gather of the
+// row blocks of a column (output-feature) split, and the variable all-to-all of expert
+// parallelism (dispatch of routed activations to the ranks that own the experts, combine of
+// their results). One process per GPU; a context joins a communicator from a 128-byte id
+// made by rank 0 and handed over by whatever launcher the caller uses.
+//
+// The reference has no tensor- or expert-parallel mode (its only multi-device mode is a
+// layer split through ggml's scheduler, marfrit/arcint DESIGN.md:782-788), so there is no
+// reference behaviour to match here beyond the single-GPU op result.
+//
+// NCCL is opened at run time (dlopen "libnccl.so.2"): a single-GPU user never needs it, and a
+// process that already carries an NCCL (PyTorch's) shares that copy instead of loading a
+// second one. No kernel here touches a peer's memory itself; every byte crosses in NCCL.
+#include <dlfcn.h>
+#include <nccl.h>
+#include <string.h>
+
+#include <vector>
+
+#include "common.cuh"
+
+namespace b200q {
+
+struct Nccl {
+    void *lib = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Send)(const void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+static Nccl *nccl_api(std::string *err) {
+    static Nccl api;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        api.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!api.lib) api.lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (api.lib) {
+#define B200Q_SYM(name) *(void **)(&api.name) = dlsym(api.lib, "nccl" #name)
+            B200Q_SYM(GetUniqueId); B200Q_SYM(CommInitRank); B200Q_SYM(CommDestroy); B200Q_SYM(CommAbort);
+            B200Q_SYM(CommGetAsyncError); B200Q_SYM(AllReduce); B200Q_SYM(AllGather); B200Q_SYM(Send); B200Q_SYM(Recv);
+            B200Q_SYM(GroupStart); B200Q_SYM(GroupEnd); B200Q_SYM(GetErrorString);
+#undef B200Q_SYM
+        }
+    }
+    if (!api.lib || !api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.AllGather || !api.Send || !api.Recv ||
+        !api.GroupStart || !api.GroupEnd) {
+        if (err) *err = api.lib ? "libnccl.so.2 lacks a needed symbol" : "libnccl.so.2 not found";
+        return nullptr;
+    }
+    return &api;
+}
+
+struct TpState {
+    ncclComm_t comm = nullptr;
+    int rank = 0, nranks = 1;
+};
+
+#define B200Q_NCCL(ctx, api, expr)                                                                     \
+    do {                                                                                               \
+        ncclResult_t r_ = (expr);                                                                      \
+        if (r_ != ncclSuccess)                                                                         \
+            return fail((ctx), B200Q_NCCL_ERROR, "%s: %s", #expr,                                      \
+                        (api)->GetErrorString ? (api)->GetErrorString(r_) : "nccl error");             \
+    } while (0)
+
+void tp_free(b200q_ctx *ctx) {
+    TpState *tp = (TpState *)ctx->tp;
+    if (!tp) return;
+    Nccl *api = nccl_api(nullptr);
+    if (api && tp->comm && api->CommDestroy) api->CommDestroy(tp->comm);
+    delete tp;
+    ctx->tp = nullptr;
+}
+
+static b200q_status tp_get(b200q_ctx *ctx, TpState **tp, Nccl **api) {
+    if (!ctx) return B200Q_INVALID;
+    *tp = (TpState *)ctx->tp;
+    if (!*tp || !(*tp)->comm) return fail(ctx, B200Q_INVALID, "b200q_tp_init was not called on this context");
+    std::string err;
+    *api = nccl_api(&err);
+    if (!*api) return fail(ctx, B200Q_NCCL_ERROR, "%s", err.c_str());
+    return B200Q_OK;
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+b200q_status b200q_tp_unique_id(void *id128) {
+    if (!id128) return B200Q_INVALID;
+    Nccl *api = nccl_api(nullptr);
+    if (!api) return B200Q_NCCL_ERROR;
+    static_assert(sizeof(ncclUniqueId) == 128, "the id is passed as 128 bytes");
+    ncclUniqueId id;
+    if (api->GetUniqueId(&id) != ncclSuccess) return B200Q_NCCL_ERROR;
+    memcpy(id128, &id, 128);
+    return B200Q_OK;
+}
+
+b200q_status b200q_tp_init(b200q_ctx *ctx, const void *id128, int rank, int nranks) {
+    if (!ctx || !id128 || nranks < 1 || rank < 0 || rank >= nranks) return B200Q_INVALID;
+    if (ctx->tp) return fail(ctx, B200Q_INVALID, "the context already belongs to a communicator");
+    std::string err;
+    Nccl *api = nccl_api(&err);
+    if (!api) return fail(ctx, B200Q_NCCL_ERROR, "%s", err.c_str());
+    B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+    ncclUniqueId id;
+    memcpy(&id, id128, 128);
+    TpState *tp = new TpState();
+    tp->rank = rank;
+    tp->nranks = nranks;
+    ncclResult_t r = api->CommInitRank(&tp->comm, nranks, id, rank);
+    if (r != ncclSuccess) {
+        delete tp;
+        return fail(ctx, B200Q_NCCL_ERROR, "ncclCommInitRank: %s", api->GetErrorString ? api->GetErrorString(r) : "error");
+    }
+    ctx->tp = tp;
+    return B200Q_OK;
+}
+
+b200q_status b200q_tp_rank(const b200q_ctx *ctx, int *rank, int *nranks) {
+    if (!ctx || !ctx->tp) return B200Q_INVALID;
+    const TpState *tp = (const TpState *)ctx->tp;
+    if (rank) *rank = tp->rank;
+    if (nranks) *nranks = tp->nranks;
+    return B200Q_OK;
+}
+
+// Which slice of `total` rank `rank` of `nranks` owns, in units of `unit` (rows: 1; K of a row
+// split: the weight type's block size, so every shard is whole blocks; experts: 1). The first
+// total/unit % nranks ranks get one unit more.
+b200q_status b200q_tp_shard(int64_t total, int64_t unit, int nranks, int rank, int64_t *first, int64_t *count) {
+    if (!first || !count || unit <= 0 || nranks < 1 || rank < 0 || rank >= nranks || total < 0 || total % unit)
+        return B200Q_INVALID;
+    const int64_t units = total / unit, q = units / nranks, r = units % nranks;
+    *first = ((int64_t)rank * q + (rank < r ? rank : r)) * unit;
+    *count = (q + (rank < r ? 1 : 0)) * unit;
+    return B200Q_OK;
+}
+
+b200q_status b200q_all_reduce_f32(b200q_ctx *ctx, void *dev_buf, size_t count) {
+    TpState *tp;
+    Nccl *api;
+    b200q_status st = tp_get(ctx, &tp, &api);
+    if (st != B200Q_OK) return st;
+    if (!dev_buf && count) return B200Q_INVALID;
+    if (count == 0 || tp->nranks == 1) return B200Q_OK;
+    B200Q_NCCL(ctx, api, api->AllReduce(dev_buf, dev_buf, count, ncclFloat32, ncclSum, tp->comm, ctx->stream));
+    b200q::count(ctx, ST_TP_ALLREDUCE);
+    return B200Q_OK;
+}
+
+b200q_status b200q_all_gather(b200q_ctx *ctx, const void *dev_send, void *dev_recv, size_t bytes_per_rank) {
+    TpState *tp;
+    Nccl *api;
+    b200q_status st = tp_get(ctx, &tp, &api);
+    if (st != B200Q_OK) return st;
+    if ((!dev_send || !dev_recv) && bytes_per_rank) return B200Q_INVALID;
+    if (bytes_per_rank == 0) return B200Q_OK;
+    B200Q_NCCL(ctx, api, api->AllGather(dev_send, dev_recv, bytes_per_rank, ncclInt8, tp->comm, ctx->stream));
+    b200q::count(ctx, ST_TP_ALLGATHER);
+    return B200Q_OK;
+}
+
+// Variable all-to-all (expert-parallel dispatch and combine): rank r's slice for peer p starts at
+// send_offsets[p] bytes of dev_send and is send_bytes[p] long; what peer p sends lands at
+// recv_offsets[p] of dev_recv. Host arrays of nranks entries each. One grouped send/recv.
+b200q_status b200q_all_to_all_v(b200q_ctx *ctx, const void *dev_send, const size_t *send_offsets, const size_t *send_bytes,
+                                void *dev_recv, const size_t *recv_offsets, const size_t *recv_bytes) {
+    TpState *tp;
+    Nccl *api;
+    b200q_status st = tp_get(ctx, &tp, &api);
+    if (st != B200Q_OK) return st;
+    if (!send_offsets || !send_bytes || !recv_offsets || !recv_bytes) return B200Q_INVALID;
+    B200Q_NCCL(ctx, api, api->GroupStart());
+    for (int p = 0; p < tp->nranks; ++p) {
+        if (send_bytes[p])
+            B200Q_NCCL(ctx, api, api->Send((const uint8_t *)dev_send + send_offsets[p], send_bytes[p], ncclInt8, p, tp->comm, ctx->stream));
+        if (recv_bytes[p])
+            B200Q_NCCL(ctx, api, api->Recv((uint8_t *)dev_recv + recv_offsets[p], recv_bytes[p], ncclInt8, p, tp->comm, ctx->stream));
+    }
+    B200Q_NCCL(ctx, api, api->GroupEnd());
+    b200q::count(ctx, ST_EP_DISPATCH);
+    return B200Q_OK;
+}
+
+// The communicator's asynchronous error state, for callers that watch a stuck peer from the
+// host: B200Q_OK, or B200Q_NCCL_ERROR after aborting the communicator.
+b200q_status b200q_tp_check(b200q_ctx *ctx) {
+    TpState *tp;
+    Nccl *api;
+    b200q_status st = tp_get(ctx, &tp, &api);
+    if (st != B200Q_OK) return st;
+    if (!api->CommGetAsyncError) return B200Q_OK;
+    ncclResult_t async = ncclSuccess;
+    B200Q_NCCL(ctx, api, api->CommGetAsyncError(tp->comm, &async));
+    if (async != ncclSuccess && async != ncclInProgress) {
+        if (api->CommAbort) api->CommAbort(tp->comm);
+        tp->comm = nullptr;
+        return fail(ctx, B200Q_NCCL_ERROR, "communicator failed: %s", api->GetErrorString ? api->GetErrorString(async) : "error");
+    }
+    return B200Q_OK;
+}
+
+}  // extern "C"

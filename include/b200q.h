@@ -121,6 +121,28 @@ B200Q_API b200q_status b200q_capture_end(b200q_ctx *ctx, b200q_graph **graph);
 B200Q_API b200q_status b200q_graph_launch(b200q_ctx *ctx, b200q_graph *graph);
 B200Q_API void         b200q_graph_free(b200q_graph *graph);
 
+/* Multi-GPU, one process and one context per GPU, NCCL over NVLink/NVSwitch. The reference
+ * has no tensor- or expert-parallel mode (only a layer split through ggml's scheduler), so
+ * these have no counterpart there; the single-GPU op result is what they must reproduce.
+ *   column split: each rank owns a row range of the weight (b200q_tp_shard with unit 1) and
+ *                 runs b200q_mul_mat on it; b200q_all_gather joins the row blocks if wanted;
+ *   row split:    each rank owns a K range on block boundaries (unit = the type's block
+ *                 size) of the weight and of the activation and runs b200q_mul_mat into a
+ *                 full-size partial result; b200q_all_reduce_f32 sums the partials;
+ *   expert split: each rank owns an expert range; b200q_all_to_all_v carries the routed
+ *                 activations to their owners and the results back.
+ * Rank 0 makes the 128-byte id, the launcher hands it to every rank. */
+B200Q_API b200q_status b200q_tp_unique_id(void *id128);
+B200Q_API b200q_status b200q_tp_init(b200q_ctx *ctx, const void *id128, int rank, int nranks);
+B200Q_API b200q_status b200q_tp_rank(const b200q_ctx *ctx, int *rank, int *nranks);
+B200Q_API b200q_status b200q_tp_shard(int64_t total, int64_t unit, int nranks, int rank, int64_t *first, int64_t *count);
+B200Q_API b200q_status b200q_all_reduce_f32(b200q_ctx *ctx, void *dev_buf, size_t count);
+B200Q_API b200q_status b200q_all_gather(b200q_ctx *ctx, const void *dev_send, void *dev_recv, size_t bytes_per_rank);
+B200Q_API b200q_status b200q_all_to_all_v(b200q_ctx *ctx, const void *dev_send, const size_t *send_offsets,
+                                          const size_t *send_bytes, void *dev_recv, const size_t *recv_offsets,
+                                          const size_t *recv_bytes);
+B200Q_API b200q_status b200q_tp_check(b200q_ctx *ctx);
+
 /* ggml backend buffer interface (buffer alloc, set_tensor, get_tensor, synchronize):
  * device memory for tensors and stream-ordered copies between host and device. */
 B200Q_API b200q_status b200q_buffer_alloc(b200q_ctx *ctx, size_t bytes, void **dev_ptr);

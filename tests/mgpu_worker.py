@@ -1,0 +1,89 @@
+"""One rank of the multi-GPU parity check; launched by tests/test_gpu_multi.py as
+  python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 ... tests/mgpu_worker.py
+Every rank: its own GPU and b200q context, joins the NCCL communicator (id broadcast over a gloo
+group), runs a column split (Q8_0 prompt GEMM, all-gather), a row split (Q4_0 and Q4_K, all-reduce
+of the f32 partials) and a variable all-to-all, and compares with the CPU oracle."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import torch
+import torch.distributed as dist
+
+import arcint_b200 as A
+import oracle as O
+from gpu_util import TOL, rel_err
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    dist.init_process_group("gloo")
+    ctx = A.Context(local)
+    idt = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        idt = torch.frombuffer(bytearray(A.tp_unique_id()), dtype=torch.uint8).clone()
+    dist.broadcast(idt, 0)
+    ctx.tp_init(bytes(idt.numpy().tobytes()), rank, world)
+
+    # column split: Q8_0, 64 tokens (tensor-core path), rows sharded, results gathered
+    t, m, k, n = A.Q8_0, 512 * world, 1024, 64
+    w = O.quantize(t, O.fill_normal(m * k, 21, 0.02).reshape(m, k))
+    x = O.fill_normal(n * k, 22, 1.0).reshape(n, k)
+    r0, rc = A.tp_shard(m, 1, world, rank)
+    dw, dx = ctx.upload(w[r0:r0 + rc]), ctx.upload(x)
+    dpart, dall = ctx.alloc(n * rc * 4), ctx.alloc(world * n * rc * 4)
+    ctx.graph_begin()
+    ctx.mul_mat(A.Tensor.weights(t, dw, k, rc), A.Tensor.f32(dx, [k, n]), A.Tensor.f32(dpart, [rc, n]))
+    ctx.all_gather(dpart, dall, n * rc * 4)
+    got = ctx.download(dall, (world, n, rc), np.float32)
+    got = np.concatenate([got[r] for r in range(world)], axis=1)
+    e1 = rel_err(got, O.mul_mat_f64(t, w, k, x, True))
+    assert e1 < TOL, ("column split", e1)
+
+    # row split: K sharded on block boundaries, f32 partials all-reduced
+    errs = []
+    for t, k in ((A.Q4_0, 2048), (A.Q4_K, 2816)):
+        m, n = 256, 3
+        w = O.quantize(t, O.fill_normal(m * k, 31 + t, 0.02).reshape(m, k))
+        x = O.fill_normal(n * k, 32, 1.0).reshape(n, k)
+        k0, kc = A.tp_shard(k, A.block_size(t), world, rank)
+        b0, bc = k0 // A.block_size(t) * A.block_bytes(t), kc // A.block_size(t) * A.block_bytes(t)
+        wk = np.ascontiguousarray(w[:, b0:b0 + bc])
+        dw, dx, dy = ctx.upload(wk), ctx.upload(np.ascontiguousarray(x[:, k0:k0 + kc])), ctx.alloc(n * m * 4)
+        ctx.graph_begin()
+        if kc:
+            ctx.mul_mat(A.Tensor.weights(t, dw, kc, m), A.Tensor.f32(dx, [kc, n]), A.Tensor.f32(dy, [m, n]))
+        else:
+            ctx.upload(np.zeros((n, m), dtype=np.float32), dy)
+        ctx.all_reduce_f32(dy, n * m)
+        got = ctx.download(dy, (n, m), np.float32)
+        errs.append(rel_err(got, O.mul_mat_f64(t, w, k, x, True)))
+        assert errs[-1] < TOL, ("row split", t, errs[-1])
+
+    # variable all-to-all: rank r sends (r + p + 1) floats of value 100 r + p to peer p
+    send_counts = [rank + p + 1 for p in range(world)]
+    recv_counts = [p + rank + 1 for p in range(world)]
+    send = np.concatenate([np.full(c, 100 * rank + p, dtype=np.float32) for p, c in enumerate(send_counts)])
+    ds, dr = ctx.upload(send), ctx.alloc(sum(recv_counts) * 4)
+    so, ro = np.concatenate([[0], np.cumsum(send_counts)[:-1]]) * 4, np.concatenate([[0], np.cumsum(recv_counts)[:-1]]) * 4
+    ctx.all_to_all_v(ds, so, [4 * c for c in send_counts], dr, ro, [4 * c for c in recv_counts])
+    got = ctx.download(dr, (sum(recv_counts),), np.float32)
+    want = np.concatenate([np.full(c, 100 * p + rank, dtype=np.float32) for p, c in enumerate(recv_counts)])
+    assert np.array_equal(got, want), "all_to_all_v"
+
+    st = ctx.stats()
+    assert st.get("tp_allgather") == 1 and st.get("tp_allreduce") == 2 and st.get("gemm_tc") == 1, st
+    dist.barrier()
+    print("MGPU_OK rank %d/%d colsplit %.2e rowsplit %s" % (rank, world, e1, ["%.2e" % e for e in errs]), flush=True)
+    ctx.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
