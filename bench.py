@@ -120,6 +120,73 @@ def build_decode_inputs(seed=0x5EED0001):
     return out, x
 
 
+def prefill_section(ctx, world, rank, dist):
+    """Prompt GEMM on the tensor cores (tcgen05 int8 MMA), reported beside the decode headline:
+    config 1 (Q4_0 4096x4096, 512 tokens) on one GPU, and config 3's Q8_0 12288x3072 at 4096
+    tokens column-split over the ranks (each rank owns a row range; no collective is needed
+    for the compute, activations are replicated). Each timed product is quantize + GEMM."""
+    import arcint_b200 as A
+    import oracle as O
+    peaks = {}
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            peaks = json.load(f)
+    # the int8 tensor pipe runs at twice the bf16 rate; MEASURED_PEAKS has the bf16 number
+    peak_tops = 2.0 * float(peaks.get("bf16_tflops", 1590.0))
+    peak_src = "2 x measured bf16 burst (MEASURED_PEAKS.json)" if peaks else "2 x fallback bf16 1.59 PF"
+    cases = [("config1 q4_0 4096x4096 x 512", A.Q4_0, 4096, 4096, 512, False),
+             ("config3 q8_0 12288x3072 x 4096%s" % (" column-split" if world > 1 else ""), A.Q8_0, 12288, 3072, 4096, True)]
+    out = []
+    for name, t, m, k, n, split in cases:
+        if world > 1 and not split:
+            continue
+        r0, rc = A.tp_shard(m, 1, world, rank) if split else (0, m)
+        base = O.quantize(t, O.fill_normal(512 * k, 0x5EED0300 + t, 0.02).reshape(512, k))
+        w = np.tile(base, (-(-rc // 512), 1))[:rc]
+        x = O.fill_normal(256 * k, 0x5EED0400, 1.0).reshape(256, k)
+        x = np.tile(x, (-(-n // 256), 1))[:n]
+        dw, dx, dy = ctx.upload(w), ctx.upload(x), ctx.alloc(n * rc * 4)
+        W, X, Y = A.Tensor.weights(t, dw, k, rc), A.Tensor.f32(dx, [k, n]), A.Tensor.f32(dy, [rc, n])
+        ctx.graph_begin()
+        ctx.mul_mat(W, X, Y)
+        got = ctx.download(dy, (n, rc), np.float32)
+        rows = np.arange(0, rc, max(1, rc // 16))
+        ref = O.mul_mat_f64(t, w[rows], k, x[:32], True)
+        floor = 1e-2 * np.abs(ref).max(axis=-1, keepdims=True)
+        err = float((np.abs(got[:32][:, rows] - ref) / np.maximum(np.abs(ref), floor)).max())
+        reps = 5
+
+        def seq():
+            for _ in range(reps):
+                ctx.graph_begin()
+                ctx.mul_mat(W, X, Y)
+
+        seq()
+        g = ctx.capture(seq)
+        ctx.graph_launch(g)
+        ctx.sync()
+        if dist:
+            dist.barrier()
+        ctx.timer_start()
+        for _ in range(3):
+            ctx.graph_launch(g)
+        ms = ctx.timer_stop() / (3 * reps)
+        if dist:
+            import torch
+            tt = torch.tensor([ms], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        ctx.graph_free(g)
+        tops = 2.0 * m * k * n / (ms * 1e-3) / 1e12
+        out.append({"workload": name, "ms": ms, "tops": tops, "roofline": {"bound": "tensor", "achieved": tops,
+                    "peak": peak_tops * world, "unit": "TOP/s", "frac": tops / (peak_tops * world), "peak_source": peak_src},
+                    "parity_max_rel_err": err, "timed": "activation quantize + tcgen05 int8 GEMM, CUDA-graph replay"})
+        for ptr in (dw, dx, dy):
+            ctx.free(ptr)
+    return out
+
+
 def run_reference(args, rank):
     """The CPU arm: the oracle (a port of the reference math; ggml's CPU backend is not
     in this image) on all host cores, same workload, metric and unit."""
@@ -311,6 +378,8 @@ def run_gpu(args, rank, world):
     achieved = tot_b / (tot_ms * 1e-3) / 1e9
     clocks = sampler.stop() if rank == 0 else None
 
+    prefill = prefill_section(ctx, world, rank, dist)
+
     cpu = None
     if rank == 0:
         t0 = time.perf_counter()
@@ -338,6 +407,7 @@ def run_gpu(args, rank, world):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": peak_src, "kernel": "gemv_kernel (activation pre-quantized), back-to-back launches in a CUDA graph",
                          "detail": detail},
+            "prefill": prefill,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e, "how": "eager C-ABI calls per product: tensor_set, mul_mat, tensor_get; one "
