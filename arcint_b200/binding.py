@@ -108,6 +108,7 @@ def lib():
     L.b200q_last_error.argtypes = [vp]
     L.b200q_last_error.restype = C.c_char_p
     L.b200q_version.restype = C.c_char_p
+    L.b200q_get_stream.argtypes = [vp, C.POINTER(vp)]
     L.b200q_supports.argtypes = [vp, C.c_int, TP, TP, TP, TP]
     L.b200q_mul_mat.argtypes = [vp, TP, TP, TP]
     L.b200q_mul_mat_id.argtypes = [vp, TP, TP, TP, TP]
@@ -147,7 +148,7 @@ def lib():
 
 
 EXPORTS = [
-    "b200q_init", "b200q_free", "b200q_last_error", "b200q_version", "b200q_supports", "b200q_mul_mat",
+    "b200q_init", "b200q_free", "b200q_last_error", "b200q_get_stream", "b200q_version", "b200q_supports", "b200q_mul_mat",
     "b200q_mul_mat_id", "b200q_graph_begin", "b200q_capture_begin", "b200q_capture_end", "b200q_graph_launch",
     "b200q_graph_free", "b200q_tp_unique_id", "b200q_tp_init", "b200q_tp_rank", "b200q_tp_shard", "b200q_all_reduce_f32",
     "b200q_all_gather", "b200q_all_to_all_v", "b200q_tp_check", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
@@ -241,6 +242,12 @@ class Context:
 
     def sync(self):
         self.check(self.L.b200q_synchronize(self.h))
+
+    def stream(self):
+        """The cudaStream_t (as an integer handle) the context enqueues on."""
+        p = C.c_void_p()
+        self.check(self.L.b200q_get_stream(self.h, C.byref(p)))
+        return p.value
 
     # ---- the op ----
     def graph_begin(self):

@@ -258,6 +258,12 @@ void b200q_free(b200q_ctx *ctx) {
 
 const char *b200q_last_error(const b200q_ctx *ctx) { return ctx ? ctx->last_error.c_str() : ""; }
 
+b200q_status b200q_get_stream(const b200q_ctx *ctx, void **stream) {
+    if (!ctx || !stream) return B200Q_INVALID;
+    *stream = (void *)ctx->stream;
+    return B200Q_OK;
+}
+
 b200q_status b200q_supports(const b200q_ctx *ctx, int op, const b200q_tensor *src0, const b200q_tensor *src1,
                             const b200q_tensor *ids, const b200q_tensor *dst) {
     (void)ctx;

@@ -78,6 +78,8 @@ typedef struct b200q_ctx b200q_ctx;
 B200Q_API b200q_status b200q_init(b200q_ctx **ctx, int device, void *stream);
 B200Q_API void         b200q_free(b200q_ctx *ctx);
 B200Q_API const char  *b200q_last_error(const b200q_ctx *ctx);
+/* the cudaStream_t the context enqueues on (the caller's, or the one the context made) */
+B200Q_API b200q_status b200q_get_stream(const b200q_ctx *ctx, void **stream);
 B200Q_API const char  *b200q_version(void);
 
 /* ggml_opencl_supports_op (P01:615-652) with the shape gate ggml_cl_kq_mul_mat_shape
