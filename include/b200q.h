@@ -170,6 +170,22 @@ B200Q_API b200q_status b200q_timer_stop(b200q_ctx *ctx, float *elapsed_ms);  /* 
 /* writes a buffer larger than L2 so the next launch starts cold */
 B200Q_API b200q_status b200q_flush_l2(b200q_ctx *ctx);
 
+/* No counterpart in the reference (its backend always owns scratch buffers it may grow).
+ * b200q_mul_mat for at most 8 activation columns of at most 32768 values each, for callers
+ * that cannot allocate device memory: a host whose own pool took all of the GPU's memory at
+ * start-up, or a serving loop that must not meet the device-wide synchronisation of
+ * cudaMalloc / cudaFree. It needs no context and allocates nothing; the quantized activation
+ * passes through a fixed 352 KiB array inside the library image (held by every GPU that loads
+ * the library until the process exits). Larger shapes are refused with B200Q_UNSUPPORTED and a
+ * message in b200q_noalloc_last_error(). All calls share that array and it keeps the last
+ * call's contents (each call overwrites what it reads, so nothing needs clearing); calls that
+ * overlap on one GPU race on it, so keep them ordered. The first call on a device looks up the
+ * array's device address, so make that call before opening any stream capture. `stream` is a
+ * cudaStream_t (NULL: the default stream); work is enqueued, not waited for. */
+B200Q_API b200q_status b200q_mul_mat_noalloc(int device, void *stream, const b200q_tensor *src0,
+                                             const b200q_tensor *src1, b200q_tensor *dst);
+B200Q_API const char  *b200q_noalloc_last_error(void);
+
 /* Debug views of what the kernels see, for bit-exact parity tests: the quantized
  * activation (codes [N][K] int8; scales fp16 [N][K/32] for Q4_0/Q8_0 weights or f32
  * [N][K/256] for the 256-block types; sums int16 [N][K/32] of each 32 codes) and

@@ -29,12 +29,10 @@ def both_ways(ctx, t, w, k, x):
     ctx.graph_begin()
     ctx.mul_mat(W, X, A.Tensor.f32(dy0, [m, n]))
     want = ctx.download(dy0, (n, m), np.float32)
-    st = ctx.L.b200q_mul_mat_noalloc(0, None, W, X, A.Tensor.f32(dy1, [m, n]))      # default stream
+    # the context is only used for memory and the reference result; the new entry point gets no
+    # context, just the stream to enqueue on (the context's, so the download below is ordered after it)
+    st = ctx.L.b200q_mul_mat_noalloc(0, ctx.stream(), W, X, A.Tensor.f32(dy1, [m, n]))
     assert st == A.OK, ctx.L.b200q_noalloc_last_error()
-    # the call above ran on the default stream, which the context's non-blocking stream does not wait
-    # for: a device-to-host copy on the default stream does
-    got = np.empty((n, m), dtype=np.float32)
-    ctx.sync()
     got = ctx.download(dy1, (n, m), np.float32)
     for p in (dw, dx, dy0, dy1):
         ctx.free(p)
