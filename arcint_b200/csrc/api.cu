@@ -146,9 +146,12 @@ static b200q_status get_activation(b200q_ctx *ctx, int form, const b200q_tensor 
         ActEntry &e = ctx->act_cache[pick];
         e.valid = false;
         b200q_status st;
-        if (form == ACT_Q8_0_TILED) {
-            if ((st = ws_reserve(ctx, &e.codes, gemm_tc_act_bytes(K, N))) != B200Q_OK) return st;
-            if ((st = launch_quantize_tiled(ctx, src1, (uint8_t *)e.codes.ptr)) != B200Q_OK) return st;
+        if (form == ACT_Q8_0_TILED || form == ACT_Q8_256_TILED) {
+            const bool per32 = form == ACT_Q8_0_TILED;
+            if ((st = ws_reserve(ctx, &e.codes, per32 ? gemm_tc_act_bytes(K, N) : gemm_kq_act_bytes(K, N))) != B200Q_OK) return st;
+            st = per32 ? launch_quantize_tiled(ctx, src1, (uint8_t *)e.codes.ptr)
+                       : launch_quantize_tiled256(ctx, src1, (uint8_t *)e.codes.ptr);
+            if (st != B200Q_OK) return st;
             e.key = key;
             e.valid = true;
             out->codes = (const int8_t *)e.codes.ptr;
@@ -305,6 +308,11 @@ b200q_status b200q_mul_mat(b200q_ctx *ctx, const b200q_tensor *src0, const b200q
     if (N > 8 && uniform && !ctx->no_tc && gemm_tc_supported(src0->type, M, K, N, src0->data, src0->nb[1])) {
         if ((st = get_activation(ctx, ACT_Q8_0_TILED, src1, &act)) != B200Q_OK) return st;
         return launch_gemm_tc(ctx, src0->type, src0->data, src0->nb[1], M, K, (const uint8_t *)act.codes, N,
+                              (float *)dst->data, ldd);
+    }
+    if (N > 8 && uniform && !ctx->no_tc && gemm_kq_supported(src0->type, M, K, N, src0->data, src0->nb[1])) {
+        if ((st = get_activation(ctx, ACT_Q8_256_TILED, src1, &act)) != B200Q_OK) return st;
+        return launch_gemm_kq(ctx, src0->type, src0->data, src0->nb[1], M, K, (const uint8_t *)act.codes, N,
                               (float *)dst->data, ldd);
     }
     if (N > 8) count(ctx, ST_GEMM_FALLBACK_SHAPE);

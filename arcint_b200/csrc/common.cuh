@@ -36,7 +36,7 @@ __host__ __device__ inline bool type_info(int type, TypeInfo *ti) {
     }
 }
 
-enum { ACT_Q8_0 = 0, ACT_Q8_256 = 1, ACT_Q8_0_TILED = 2 };   // TILED: the tensor-core GEMM's chunk layout
+enum { ACT_Q8_0 = 0, ACT_Q8_256 = 1, ACT_Q8_0_TILED = 2, ACT_Q8_256_TILED = 3 };   // TILED: the tensor-core GEMM's chunk layout
 
 // Quantized activation as the kernels read it: column c of K values at
 //   codes  + c*K            int8
@@ -169,6 +169,13 @@ bool         gemm_tc_supported(int type, int64_t M, int64_t K, int64_t N, const 
 size_t       gemm_tc_act_bytes(int64_t K, int64_t N);
 b200q_status launch_quantize_tiled(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out);
 b200q_status launch_gemm_tc(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
+                            const uint8_t *act, int64_t N, float *dst, int64_t ldd);
+
+// gemm_kq.cu: tensor-core prefill GEMM for IQ4_XS (integer sub-scales folded into two int8 limbs)
+bool         gemm_kq_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride);
+size_t       gemm_kq_act_bytes(int64_t K, int64_t N);
+b200q_status launch_quantize_tiled256(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out);
+b200q_status launch_gemm_kq(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                             const uint8_t *act, int64_t N, float *dst, int64_t ldd);
 
 }  // namespace b200q

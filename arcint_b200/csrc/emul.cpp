@@ -119,6 +119,15 @@ void emul_dequantize_row(int type, const uint8_t *row, int64_t K, float *out) {
 }
 
 uint32_t emul_iq4nl_lookup4(uint32_t idx) { return iq4nl_lookup4(idx); }
+
+// lookup of four indices in a 16-byte table given as four words
+uint32_t emul_lookup4_tab(const uint32_t *t, uint32_t idx) {
+    uint32_t sel, msk;
+    lookup4_prepare(idx, &sel, &msk);
+    return lookup4_apply(t[0], t[1], t[2], t[3], sel, msk);
+}
+
+void emul_iq4xs_limbs(int ls, int n, int *hi, int *lo) { iq4xs_limbs(ls, n, hi, lo); }
 uint32_t emul_nib_minus8(uint32_t t) { return nib_minus8(t); }
 uint32_t emul_six_minus32(uint32_t t) { return six_minus32(t); }
 

@@ -84,6 +84,29 @@ B200Q_HD uint32_t iq4nl_lookup4(uint32_t idx) {
     return (lo & ~msk) | (hi & msk);
 }
 
+// The same lookup with the 16-entry byte table in four registers (t0: entries 0..3, ...), split
+// so that several tables can share the selector work: `sel` picks among eight entries, `msk`
+// is 0xFF in the bytes whose index is 8 or more.
+B200Q_HD void lookup4_prepare(uint32_t idx, uint32_t *sel, uint32_t *msk) {
+    const uint32_t packed = idx | (idx >> 4);
+    *sel = hd_byte_perm(packed, 0, 0x4420) & 0x7777u;
+    *msk = hd_byte_perm(idx << 4, 0, 0xBA98);          // sign-replicate: bit 3 of each index
+}
+B200Q_HD uint32_t lookup4_apply(uint32_t t0, uint32_t t1, uint32_t t2, uint32_t t3, uint32_t sel, uint32_t msk) {
+    return (hd_byte_perm(t0, t1, sel) & ~msk) | (hd_byte_perm(t2, t3, sel) & msk);
+}
+
+// IQ4_XS for the int8 tensor cores: the product p = (ls - 32) * kvalues[n] of a weight's integer
+// sub-scale and codebook value (|p| <= 4064) as two int8 limbs, p = 64 * hi + lo with
+// lo in [-32, 31] and hi in [-64, 64]. One MMA per limb against the same activation gives
+// sum(p x) = 64 * sum(hi x) + sum(lo x) exactly.
+B200Q_HD void iq4xs_limbs(int ls, int n, int *hi, int *lo) {
+    const int p = (ls - 32) * kvalue_iq4nl(n);
+    const int h = (p + 32) >> 6;                        // arithmetic shift: floor((p + 32) / 64)
+    *hi = h;
+    *lo = p - 64 * h;
+}
+
 // Generic, slow, exact f32 decode of weight i of a row (used by the debug dequantizer
 // and as the spec the fast kernels are tested against). One rounding per multiply,
 // like ggml's dequantize_row_* and gguf-py.

@@ -1,0 +1,387 @@
+// gemm_kq.cu -- prefill GEMM for IQ4_XS weights on the tensor cores (tcgen05 int8 MMA).
+//
+//   dst[M, N] = W[M, K] (136-byte IQ4_XS super-blocks) x X[K, N] (f32), N > 8 tokens
+//
+// ggml's form for this type is integer inside a 256-weight super-block and float once per
+// super-block: out += d_w * d_x * sum_sb (ls_sb - 32) * I_sb, with I_sb the exact dot of the
+// codebook values with the int8 activation (per-256 activation scale). Here the integer
+// sub-scale is folded into the int8 operand so the tensor core accumulates the whole
+// super-block: p = (ls - 32) * kvalues[n] (|p| <= 4064) is split into two int8 limbs,
+// p = 64 hi + lo, and two MMAs per 32 weights (hi and lo against the same activation block)
+// accumulate over the eight blocks into two int32 accumulators in tensor memory;
+// 64 * sum(hi x) + sum(lo x) is the exact integer sum_sb (ls_sb - 32) I_sb. The f32 work drops
+// from once per 32 to once per 256 of K, so this kernel is bound by the tensor pipe and the
+// operand unpack rather than by the FP32 pipe.
+//
+// The reference has no dense IQ4_XS int8 GEMM (its dense path is the fp16 tile
+// kernel_mul_mm_iq4_xs_f16, marfrit/arcint contrib/llama.cpp/patches/
+// 0000-01-kquant-integer-dpas.patch:2505, deq_iq4_xs :2287-2298); its MoE int8 kernel
+// kernel_mul_mm_id_iq4_xs_i8_sg8 (0103-opencl-id-int8-sg8.patch:515-538) rescales in float per
+// 32 (af = fma(float(ir), ws, af)). The two-limb fold is this build's own; the reference tried
+// the analogous 8*s_hi + s_lo on Q4_K and found it slower on Xe2 (README of the patch series,
+// lines 860-862), where the systolic pipe is the scarce resource -- on B200 it is the cheap one.
+//
+// Layout of roles, staging and barriers follows gemm_tc.cu: producer warp (bulk copies of raw
+// rows and activation chunks), MMA warp, four unpack warps (thread = weight row), 4*NW
+// scale-accumulate warps. One stage = one super-block (eight MMA pairs); two accumulator pairs
+// (2 x 2 x 128 columns = all 512 tensor-memory columns) let the MMAs of super-block s+1 run
+// while s is scaled. Every mbarrier wait is bounded.
+#include "formats.cuh"
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace b200q {
+
+namespace kq {
+
+using namespace tc;
+
+constexpr int BM = 128, BN = 128, KB = 32, SB = 8;
+constexpr int NACT = 3;                                   // activation chunks (one super-block each) in flight
+constexpr int NRAW = 2;                                   // raw stages (two super-blocks each) in flight
+constexpr int NA = 4;                                     // A-operand slots (blocks unpacked ahead of the MMA)
+constexpr int NBUF = 2;                                   // accumulator pairs (hi, lo)
+constexpr int NW = 2;
+constexpr int THREADS = 32 * (8 + 4 * NW);
+constexpr int OPER_BYTES = BM * KB;                       // 4096
+constexpr int ACT_CHUNK = SB * OPER_BYTES + BN * 4;       // codes of a super-block + one f32 scale per token
+constexpr int SBB = 136;                                  // bytes of one IQ4_XS super-block
+constexpr int ROWB = 2 * SBB;                             // a raw stage holds two super-blocks per row: 272 B = 17 x 16
+constexpr int RAW_STAGE = BM * ROWB;
+constexpr int A_SLOT = 2 * OPER_BYTES;                    // hi limb, lo limb
+constexpr int RAW_OFF = 0;
+constexpr int ACT_OFF = RAW_OFF + NRAW * RAW_STAGE;
+constexpr int A_OFF = ACT_OFF + NACT * ACT_CHUNK;
+constexpr int TAB_OFF = A_OFF + NA * A_SLOT;              // [64 ls][hi 16 B | lo 16 B]
+constexpr int BAR_OFF = TAB_OFF + 64 * 32;
+constexpr int SMEM_TOTAL = BAR_OFF + 8 * 64;
+static_assert(SMEM_TOTAL <= 227 * 1024, "shared memory budget");
+
+constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+enum { BAR_RAW_FULL = 0, BAR_RAW_EMPTY = 2, BAR_ACT_FULL = 4, BAR_ACT_EMPTY = 7, BAR_A_FULL = 10, BAR_A_EMPTY = 14,
+       BAR_ACC_FULL = 18, BAR_ACC_EMPTY = 20, BAR_COUNT = 22 };
+
+// D (+)= A x B^T with the accumulate flag as an operand
+__device__ __forceinline__ void umma_i8_acc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Activation chunk (128-token tile t, super-block s), per-256 form (the reference's
+// kernel_quant_i8 rule: scale bm/127, round to nearest even, zero below 1e-30):
+//   codes  [block j < 8][half c < 2][group g < 16][column r < 8][16 bytes]
+//   scales [column < 128] f32
+__global__ void __launch_bounds__(256)
+quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t nb1, size_t nb2, size_t nb3, int64_t K,
+                         int64_t N, uint8_t *__restrict__ out) {
+    __shared__ float part[256];
+    const int t = blockIdx.y, s = blockIdx.x, nst = gridDim.x;
+    const int col = threadIdx.x & 127, half = threadIdx.x >> 7;
+    const int64_t n = (int64_t)t * BN + col;
+    uint8_t *chunk = out + ((size_t)t * nst + s) * ACT_CHUNK;
+    const float *x = nullptr;
+    if (n < N) {
+        const int64_t c1 = n % ne1, c23 = n / ne1, c2 = c23 % ne2, c3 = c23 / ne2;
+        x = reinterpret_cast<const float *>(base + c1 * nb1 + c2 * nb2 + c3 * nb3) + (int64_t)s * 256 + 128 * half;
+    }
+    float amax = 0.f;
+    if (x)
+        for (int i = 0; i < 32; ++i) {
+            const float4 f = *reinterpret_cast<const float4 *>(x + 4 * i);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+        }
+    part[threadIdx.x] = amax;
+    __syncthreads();
+    const float bm = fmaxf(part[col], part[col + 128]);
+    const float iq = bm > 1e-30f ? __fdiv_rn(127.f, bm) : 0.f;
+#pragma unroll 1
+    for (int jj = 0; jj < 4; ++jj) {
+        const int j = 4 * half + jj;
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float4 f = x ? *reinterpret_cast<const float4 *>(x + 32 * jj + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            w[i] = (uint32_t)(__float2int_rn(__fmul_rn(f.x, iq)) & 0xFF) | ((uint32_t)(__float2int_rn(__fmul_rn(f.y, iq)) & 0xFF) << 8) |
+                   ((uint32_t)(__float2int_rn(__fmul_rn(f.z, iq)) & 0xFF) << 16) | ((uint32_t)(__float2int_rn(__fmul_rn(f.w, iq)) & 0xFF) << 24);
+        }
+        uint8_t *o = chunk + j * OPER_BYTES + (col >> 3) * 128 + (col & 7) * 16;
+        *reinterpret_cast<uint4 *>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4 *>(o + LBO) = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    if (half == 0) reinterpret_cast<float *>(chunk + SB * OPER_BYTES)[col] = __fdiv_rn(bm, 127.f);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_iq4xs_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, const uint8_t *__restrict__ act,
+                  int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+    const int row0 = tile_m * BM;
+    const int nsb = K / 256;                    // super-blocks (even: the host gate asks K % 512 == 0)
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bars = sbase + BAR_OFF;
+    auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+    const int valid_rows = min(BM, M - row0);
+
+    // the limb tables: for every sub-scale ls the 16 codebook entries times (ls - 32), hi and lo bytes
+    for (int i = threadIdx.x; i < 64 * 16; i += THREADS) {
+        int hi, lo;
+        iq4xs_limbs(i >> 4, i & 15, &hi, &lo);
+        smem[TAB_OFF + (i >> 4) * 32 + (i & 15)] = (uint8_t)hi;
+        smem[TAB_OFF + (i >> 4) * 32 + 16 + (i & 15)] = (uint8_t)lo;
+    }
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int i = 0; i < NRAW; ++i) {
+            mbar_init(bar(BAR_RAW_FULL + i), 1);
+            mbar_init(bar(BAR_RAW_EMPTY + i), 128 + 128 * NW);     // unpack threads + scaling threads (d_w)
+        }
+        for (int i = 0; i < NACT; ++i) {
+            mbar_init(bar(BAR_ACT_FULL + i), 1);
+            mbar_init(bar(BAR_ACT_EMPTY + i), 1 + 128 * NW);       // MMA commit + scaling threads (d_x)
+        }
+        for (int i = 0; i < NA; ++i) {
+            mbar_init(bar(BAR_A_FULL + i), 128);
+            mbar_init(bar(BAR_A_EMPTY + i), 1);
+        }
+        for (int i = 0; i < NBUF; ++i) {
+            mbar_init(bar(BAR_ACC_FULL + i), 1);
+            mbar_init(bar(BAR_ACC_EMPTY + i), 128 * NW);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int *abortp = &abort_flag;
+
+    if (warp == 0) {
+        // ---- producer ----
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+        const uint8_t *act_tile = act + (size_t)tile_n * nsb * ACT_CHUNK;
+        for (int s = 0; s < nsb; ++s) {
+            if ((s & 1) == 0) {
+                const int rs = s >> 1, st = rs % NRAW;
+                if (!mbar_wait_warp(bar(BAR_RAW_EMPTY + st), ((rs / NRAW) & 1) ^ 1, abortp)) break;
+                if (lane == 0) mbar_expect_tx(bar(BAR_RAW_FULL + st), (uint32_t)valid_rows * ROWB);
+                __syncwarp();
+                for (int r = lane; r < valid_rows; r += 32)
+                    bulk_g2s(sbase + RAW_OFF + st * RAW_STAGE + r * ROWB,
+                             W + (size_t)(row0 + r) * row_stride + (size_t)rs * ROWB, ROWB, bar(BAR_RAW_FULL + st));
+            }
+            const int at = s % NACT;
+            if (!mbar_wait_warp(bar(BAR_ACT_EMPTY + at), ((s / NACT) & 1) ^ 1, abortp)) break;
+            if (lane == 0) {
+                mbar_expect_tx(bar(BAR_ACT_FULL + at), ACT_CHUNK);
+                bulk_g2s(sbase + ACT_OFF + at * ACT_CHUNK, act_tile + (size_t)s * ACT_CHUNK, ACT_CHUNK, bar(BAR_ACT_FULL + at));
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer: per block one MMA per limb, accumulating over the super-block ----
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+        bool ok = true;
+        for (int s = 0; s < nsb && ok; ++s) {
+            const int at = s % NACT, buf = s % NBUF;
+            if (!mbar_wait_warp(bar(BAR_ACT_FULL + at), (s / NACT) & 1, abortp)) break;
+            if (!mbar_wait_warp(bar(BAR_ACC_EMPTY + buf), ((s / NBUF) & 1) ^ 1, abortp)) break;
+            for (int j = 0; j < SB; ++j) {
+                const int b = s * SB + j, slot = b % NA;
+                if (!mbar_wait_warp(bar(BAR_A_FULL + slot), (b / NA) & 1, abortp)) { ok = false; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint64_t db = umma_desc(sbase + ACT_OFF + at * ACT_CHUNK + j * OPER_BYTES);
+                    const uint32_t d = tmem_base + (uint32_t)buf * (2 * BN);
+                    umma_i8_acc(d, umma_desc(sbase + A_OFF + slot * A_SLOT), db, IDESC, j > 0);
+                    umma_i8_acc(d + BN, umma_desc(sbase + A_OFF + slot * A_SLOT + OPER_BYTES), db, IDESC, j > 0);
+                    tc_commit(bar(BAR_A_EMPTY + slot));
+                    if (j == SB - 1) {
+                        tc_commit(bar(BAR_ACC_FULL + buf));
+                        tc_commit(bar(BAR_ACT_EMPTY + at));
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+    } else if (warp < 8) {
+        // ---- unpack: one thread per weight row ----
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 112;" ::: "memory");
+        const int r = (warp - 4) * 32 + lane;
+        const bool row_ok = r < valid_rows;
+        bool ok = true;
+        for (int rs = 0; rs < nsb / 2 && ok; ++rs) {
+            const int st = rs % NRAW;
+            if (!mbar_wait_warp(bar(BAR_RAW_FULL + st), (rs / NRAW) & 1, abortp)) break;
+            uint32_t rw[ROWB / 4];                       // two super-blocks of this row
+            const uint4 *rp = reinterpret_cast<const uint4 *>(smem + RAW_OFF + st * RAW_STAGE + r * ROWB);
+#pragma unroll
+            for (int i = 0; i < ROWB / 16; ++i) {
+                const uint4 t = row_ok ? rp[i] : make_uint4(0, 0, 0, 0);
+                rw[4 * i] = t.x; rw[4 * i + 1] = t.y; rw[4 * i + 2] = t.z; rw[4 * i + 3] = t.w;
+            }
+            mbar_arrive(bar(BAR_RAW_EMPTY + st));
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t scales_h = rw[34 * h] >> 16, scales_l = rw[34 * h + 1];
+#pragma unroll
+                for (int j = 0; j < SB; ++j) {
+                    const int b = (2 * rs + h) * SB + j, slot = b % NA;
+                    if (!mbar_wait_warp(bar(BAR_A_EMPTY + slot), ((b / NA) & 1) ^ 1, abortp)) { ok = false; break; }
+                    const int ls = row_ok ? iq4xs_ls(scales_h, scales_l, j) : 32;
+                    const uint4 th = *reinterpret_cast<const uint4 *>(smem + TAB_OFF + ls * 32);
+                    const uint4 tl = *reinterpret_cast<const uint4 *>(smem + TAB_OFF + ls * 32 + 16);
+                    uint32_t ah[8], al[8];               // words 0..3: weights 0..15, words 4..7: weights 16..31
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t q = rw[34 * h + 2 + 4 * j + i];
+                        uint32_t sel, msk;
+                        lookup4_prepare(q & 0x0F0F0F0Fu, &sel, &msk);
+                        ah[i] = lookup4_apply(th.x, th.y, th.z, th.w, sel, msk);
+                        al[i] = lookup4_apply(tl.x, tl.y, tl.z, tl.w, sel, msk);
+                        lookup4_prepare((q >> 4) & 0x0F0F0F0Fu, &sel, &msk);
+                        ah[4 + i] = lookup4_apply(th.x, th.y, th.z, th.w, sel, msk);
+                        al[4 + i] = lookup4_apply(tl.x, tl.y, tl.z, tl.w, sel, msk);
+                    }
+                    uint8_t *a = smem + A_OFF + slot * A_SLOT + (r >> 3) * 128 + (r & 7) * 16;
+                    *reinterpret_cast<uint4 *>(a) = make_uint4(ah[0], ah[1], ah[2], ah[3]);
+                    *reinterpret_cast<uint4 *>(a + LBO) = make_uint4(ah[4], ah[5], ah[6], ah[7]);
+                    *reinterpret_cast<uint4 *>(a + OPER_BYTES) = make_uint4(al[0], al[1], al[2], al[3]);
+                    *reinterpret_cast<uint4 *>(a + OPER_BYTES + LBO) = make_uint4(al[4], al[5], al[6], al[7]);
+                    fence_async_smem();
+                    mbar_arrive(bar(BAR_A_FULL + slot));
+                }
+                if (!ok) break;
+            }
+        }
+    } else {
+        // ---- scale-accumulate, once per super-block ----
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 168;" ::: "memory");
+        constexpr int CW = BN / NW;
+        const int q4 = warp & 3, u = (warp - 8) >> 2;
+        const int r = q4 * 32 + lane;
+        const bool row_ok = r < valid_rows;
+        f32x2 acc2[CW / 2];
+#pragma unroll
+        for (int c = 0; c < CW / 2; ++c) acc2[c] = 0ull;
+        bool done = false;
+        for (int s = 0; s < nsb; ++s) {
+            const int rs = s >> 1, st = rs % NRAW, at = s % NACT, buf = s % NBUF;
+            // stage barriers cannot advance past this thread: it releases both stages itself
+            if ((s & 1) == 0 && !mbar_wait_warp(bar(BAR_RAW_FULL + st), (rs / NRAW) & 1, abortp)) break;
+            if (!mbar_wait_warp(bar(BAR_ACT_FULL + at), (s / NACT) & 1, abortp)) break;
+            if (!mbar_wait_warp(bar(BAR_ACC_FULL + buf), (s / NBUF) & 1, abortp)) break;
+            tc_fence_after();
+            const float dwb = row_ok ? half_bits_to_float(*reinterpret_cast<const uint16_t *>(
+                                           smem + RAW_OFF + st * RAW_STAGE + r * ROWB + SBB * (s & 1))) : 0.f;
+            const f32x2 dw2 = f2_pack(dwb, dwb), negc2 = f2_pack(-12582912.f, -12582912.f), k64 = f2_pack(64.f, 64.f);
+            const uint32_t dxa = sbase + ACT_OFF + at * ACT_CHUNK + SB * OPER_BYTES + (u * CW) * 4;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * (2 * BN) + (uint32_t)u * CW;
+#pragma unroll
+            for (int q = 0; q < CW / 16; ++q) {
+                uint32_t vh[16], vl[16];
+                tmem_ld16(taddr + q * 16, vh);
+                tmem_ld16(taddr + BN + q * 16, vl);
+                tmem_ld_wait();
+                if (q == CW / 16 - 1) {
+                    tc_fence_before();
+                    mbar_arrive(bar(BAR_ACC_EMPTY + buf));
+                }
+#pragma unroll
+                for (int c = 0; c < 16; c += 4) {
+                    f32x2 d01, d23;
+                    lds128_f2(dxa + (q * 16 + c) * 4, d01, d23);
+                    const int e = (q * 16 + c) / 2;
+                    // exact int -> float of each limb sum (both below 2^22 in magnitude), then 64 hi + lo
+                    const f32x2 h01 = f2_add(f2_pack(__int_as_float((int)vh[c] + 0x4B400000), __int_as_float((int)vh[c + 1] + 0x4B400000)), negc2);
+                    const f32x2 h23 = f2_add(f2_pack(__int_as_float((int)vh[c + 2] + 0x4B400000), __int_as_float((int)vh[c + 3] + 0x4B400000)), negc2);
+                    const f32x2 l01 = f2_add(f2_pack(__int_as_float((int)vl[c] + 0x4B400000), __int_as_float((int)vl[c + 1] + 0x4B400000)), negc2);
+                    const f32x2 l23 = f2_add(f2_pack(__int_as_float((int)vl[c + 2] + 0x4B400000), __int_as_float((int)vl[c + 3] + 0x4B400000)), negc2);
+                    acc2[e]     = f2_fma(f2_fma(h01, k64, l01), f2_mul(dw2, d01), acc2[e]);
+                    acc2[e + 1] = f2_fma(f2_fma(h23, k64, l23), f2_mul(dw2, d23), acc2[e + 1]);
+                }
+            }
+            mbar_arrive(bar(BAR_ACT_EMPTY + at));
+            if (s & 1) mbar_arrive(bar(BAR_RAW_EMPTY + st));
+            done = s == nsb - 1;
+        }
+        if (done && row_ok) {
+            float *o = dst + (int64_t)(tile_n * BN + u * CW) * ldd + row0 + r;
+            const int ncol = N - (tile_n * BN + u * CW);
+#pragma unroll
+            for (int c = 0; c < CW; c += 2) {
+                float a0, a1;
+                f2_unpack(acc2[c / 2], a0, a1);
+                if (c < ncol) *o = a0;
+                o += ldd;
+                if (c + 1 < ncol) *o = a1;
+                o += ldd;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        if (threadIdx.x == 0) atomicExch(error_word, 2);
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+}  // namespace kq
+
+size_t gemm_kq_act_bytes(int64_t K, int64_t N) {
+    return (size_t)(((N + kq::BN - 1) / kq::BN) * (K / 256)) * kq::ACT_CHUNK;
+}
+
+bool gemm_kq_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride) {
+    if (type != B200Q_TYPE_IQ4_XS) return false;
+    if (K <= 0 || K % 512 || M <= 0 || N <= 0) return false;          // raw stages hold two super-blocks (16-byte pieces)
+    if ((uintptr_t)w % 16 || row_stride % 16) return false;
+    if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return false;
+    return true;
+}
+
+b200q_status launch_quantize_tiled256(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out) {
+    const int64_t K = src1->ne[0], N = src1->ne[1] * src1->ne[2] * src1->ne[3];
+    dim3 grid((unsigned)(K / 256), (unsigned)((N + kq::BN - 1) / kq::BN));
+    kq::quantize_tiled256_kernel<<<grid, 256, 0, ctx->stream>>>((const uint8_t *)src1->data, src1->ne[1], src1->ne[2],
+                                                               src1->nb[1], src1->nb[2], src1->nb[3], K, N, out);
+    B200Q_CUDA(ctx, cudaGetLastError());
+    count(ctx, ST_GEMM_TC_QUANT);
+    return B200Q_OK;
+}
+
+b200q_status launch_gemm_kq(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
+                            const uint8_t *act, int64_t N, float *dst, int64_t ldd) {
+    if (type != B200Q_TYPE_IQ4_XS) return fail(ctx, B200Q_UNSUPPORTED, "gemm_kq: type %d", type);
+    static bool attr_set = false;
+    if (!attr_set) {
+        B200Q_CUDA(ctx, cudaFuncSetAttribute(kq::gemm_iq4xs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kq::SMEM_TOTAL));
+        attr_set = true;
+    }
+    dim3 grid((unsigned)((N + kq::BN - 1) / kq::BN), (unsigned)((M + kq::BM - 1) / kq::BM));
+    kq::gemm_iq4xs_kernel<<<grid, kq::THREADS, kq::SMEM_TOTAL, ctx->stream>>>((const uint8_t *)w, row_stride, (int)M, (int)K, act,
+                                                                              (int)N, dst, ldd, ctx->error_word);
+    B200Q_CUDA(ctx, cudaGetLastError());
+    count(ctx, ST_GEMM_TC);
+    return B200Q_OK;
+}
+
+}  // namespace b200q

@@ -17,7 +17,11 @@ struct alignas(8)  I2 { int x, y; };
 
 B200Q_HD uint32_t hd_byte_perm(uint32_t a, uint32_t b, uint32_t s) {
 #ifdef __CUDA_ARCH__
-    return __byte_perm(a, b, s);
+    // the PTX instruction itself: bit 3 of a selector nibble replicates the sign of the picked
+    // byte, which the lookups below rely on and the __byte_perm intrinsic does not promise
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(s));
+    return r;
 #else
     const uint64_t v = ((uint64_t)b << 32) | a;
     uint32_t r = 0;

@@ -22,6 +22,9 @@ def emul():
         vp, i64 = C.c_void_p, C.c_int64
         E.emul_gemv.argtypes = [C.c_int, vp, C.c_size_t, i64, i64, vp, vp, vp, vp, vp, C.c_int, C.c_int, vp, i64]
         E.emul_dequantize_row.argtypes = [C.c_int, vp, i64, vp]
+        E.emul_lookup4_tab.argtypes = [vp, C.c_uint32]
+        E.emul_lookup4_tab.restype = C.c_uint32
+        E.emul_iq4xs_limbs.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]
         for f in ("emul_iq4nl_lookup4", "emul_nib_minus8", "emul_six_minus32"):
             getattr(E, f).argtypes = [C.c_uint32]
             getattr(E, f).restype = C.c_uint32
@@ -45,6 +48,30 @@ def test_bit_tricks_exhaustive_per_byte():
         t = a | ((63 - a) << 8) | (((a * 11) % 64) << 16) | (((a * 29 + 5) % 64) << 24)
         got = E.emul_six_minus32(t)
         assert [((got >> (8 * i)) & 0xFF) for i in range(4)] == [(((t >> (8 * i)) & 0x3F) - 32) & 0xFF for i in range(4)]
+
+
+def test_iq4xs_two_limb_tables():
+    """The tensor-core IQ4_XS path folds (ls - 32) * kvalues[n] into two int8 limbs and looks them up
+    with byte permutes: every (ls, n) must satisfy 64 hi + lo = product with both limbs in int8."""
+    E = emul()
+    rng = np.random.default_rng(0)
+    for ls in range(64):
+        his, los = [], []
+        for n in range(16):
+            hi, lo = C.c_int(), C.c_int()
+            E.emul_iq4xs_limbs(ls, n, C.byref(hi), C.byref(lo))
+            assert 64 * hi.value + lo.value == (ls - 32) * int(O.KVALUES_IQ4NL[n])
+            assert -32 <= lo.value <= 31 and -64 <= hi.value <= 64
+            his.append(hi.value & 0xFF)
+            los.append(lo.value & 0xFF)
+        for tab in (his, los):
+            words = np.frombuffer(bytes(tab), dtype=np.uint32).copy()
+            for _ in range(8):
+                idx4 = rng.integers(0, 16, 4)
+                idx = int(idx4[0] | (idx4[1] << 8) | (idx4[2] << 16) | (idx4[3] << 24))
+                got = E.emul_lookup4_tab(words.ctypes.data, idx)
+                want = sum(tab[int(i)] << (8 * b) for b, i in enumerate(idx4))
+                assert got == want
 
 
 @pytest.mark.parametrize("name,t", [("q4_0", O.Q4_0), ("q8_0", O.Q8_0), ("q4_K", O.Q4_K), ("q6_K", O.Q6_K), ("iq4_xs", O.IQ4_XS)])

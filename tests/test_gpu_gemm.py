@@ -83,3 +83,57 @@ def test_config1_full_size(ctx):
     ref = O.mul_mat_f64(t, w[rows], k, x, True)
     assert rel_err(got[:, rows], ref) < TOL
     assert np.isfinite(got).all()
+
+
+# ---- IQ4_XS: integer sub-scales folded into two int8 limbs, float once per 256 ----
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 512), (128, 16, 512), (300, 17, 1024), (300, 100, 1024), (512, 300, 2560),
+                                   (1023, 33, 4096), (77, 9, 5120)])
+def test_gemm_iq4_xs_matches_oracle(ctx, m, n, k):
+    rng = np.random.default_rng(m * 3 + n)
+    t = A.IQ4_XS
+    w = O.random_blocks(t, m, k, rng)
+    x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1, st
+    assert np.isfinite(got).all()
+    assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
+
+
+def test_gemm_iq4_xs_extreme_codes(ctx):
+    """Every sub-scale at its extremes and every nibble equal: the largest limb sums the accumulators see."""
+    t, m, n, k = A.IQ4_XS, 128, 32, 512
+    rng = np.random.default_rng(1)
+    w = O.random_blocks(t, m, k, rng).reshape(m, k // 256, 136)
+    w[:, :, 2:8] = 0xFF                                   # ls = 63 everywhere
+    w[: m // 2, :, 2:8] = 0x00                            # ... and ls = 0 (factor -32) in half the rows
+    w[:, :, 8:] = 0x00                                    # codebook entry -127 everywhere
+    w = w.reshape(m, -1)
+    x = np.full((n, k), 3.0, dtype=np.float32)
+    x[::2] *= -1
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1
+    assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
+
+
+def test_gemm_iq4_xs_odd_superblock_count_falls_back(ctx):
+    t, m, n, k = A.IQ4_XS, 64, 20, 768                    # three super-blocks: not a multiple of 512
+    rng = np.random.default_rng(2)
+    w = O.random_blocks(t, m, k, rng)
+    x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 0 and st.get("gemm_fallback_shape", 0) == 1
+    assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
+
+
+def test_config3_iq4_xs_full_size(ctx):
+    """BASELINE config 3: IQ4_XS 17408 x 5120 at 512 tokens; sampled rows against the oracle."""
+    t, m, n, k = A.IQ4_XS, 17408, 512, 5120
+    base = make_weights(t, 512, k, 0x5EED0002)
+    w = np.tile(base, (m // 512, 1))
+    x = O.fill_normal(n * k, 0x5EED0102, 1.0).reshape(n, k)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1
+    rows = np.unique(np.concatenate([[0, 127, 128, m - 1], np.random.default_rng(1).integers(0, m, 28)]))
+    assert rel_err(got[:, rows], O.mul_mat_f64(t, w[rows], k, x, True)) < TOL
+    assert np.isfinite(got).all()
