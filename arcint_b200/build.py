@@ -40,7 +40,8 @@ def _stale(dst, srcs):
 
 
 def _compile(src, obj, verbose):
-    cmd = [nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+    extra = os.environ.get("B200Q_NVCC_EXTRA", "").split()          # e.g. -DNAME for a one-off experiment build
+    cmd = [nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     return src, r.returncode, r.stdout + r.stderr
 

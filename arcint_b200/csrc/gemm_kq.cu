@@ -22,8 +22,8 @@
 // lines 860-862), where the systolic pipe is the scarce resource -- on B200 it is the cheap one.
 //
 // Layout of roles, staging and barriers follows gemm_tc.cu: producer warp (bulk copies of raw
-// rows and activation chunks), MMA warp, four unpack warps (thread = weight row), 4*NW
-// scale-accumulate warps. One stage = one super-block (eight MMA pairs); two accumulator pairs
+// rows and activation chunks), MMA warp, eight unpack warps (two threads per weight row, one
+// per 16-weight half of a block), 4*NW scale-accumulate warps. One stage = one super-block (eight MMA pairs); two accumulator pairs
 // (2 x 2 x 128 columns = all 512 tensor-memory columns) let the MMAs of super-block s+1 run
 // while s is scaled. Every mbarrier wait is bounded.
 #include "formats.cuh"
@@ -37,12 +37,12 @@ namespace kq {
 using namespace tc;
 
 constexpr int BM = 128, BN = 128, KB = 32, SB = 8;
-constexpr int NACT = 3;                                   // activation chunks (one super-block each) in flight
+constexpr int NACT = 2;                                   // activation chunks (one super-block each) in flight
 constexpr int NRAW = 2;                                   // raw stages (two super-blocks each) in flight
-constexpr int NA = 4;                                     // A-operand slots (blocks unpacked ahead of the MMA)
+constexpr int NA = 8;                                     // A-operand slots (blocks unpacked ahead of the MMA)
 constexpr int NBUF = 2;                                   // accumulator pairs (hi, lo)
 constexpr int NW = 2;
-constexpr int THREADS = 32 * (8 + 4 * NW);
+constexpr int THREADS = 32 * (12 + 4 * NW);               // warp groups: {producer, MMA, 2 idle}, 2 x unpack, NW x scale-accumulate
 constexpr int OPER_BYTES = BM * KB;                       // 4096
 constexpr int ACT_CHUNK = SB * OPER_BYTES + BN * 4;       // codes of a super-block + one f32 scale per token
 constexpr int SBB = 136;                                  // bytes of one IQ4_XS super-block
@@ -59,8 +59,10 @@ static_assert(SMEM_TOTAL <= 227 * 1024, "shared memory budget");
 
 constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
-enum { BAR_RAW_FULL = 0, BAR_RAW_EMPTY = 2, BAR_ACT_FULL = 4, BAR_ACT_EMPTY = 7, BAR_A_FULL = 10, BAR_A_EMPTY = 14,
-       BAR_ACC_FULL = 18, BAR_ACC_EMPTY = 20, BAR_COUNT = 22 };
+constexpr int GB = 4;                                     // blocks per A-ring group: one fence and one barrier round per group
+constexpr int NG = NA / GB;                               // groups in the ring
+enum { BAR_RAW_FULL = 0, BAR_RAW_EMPTY = 2, BAR_ACT_FULL = 4, BAR_ACT_EMPTY = 6, BAR_A_FULL = 8, BAR_A_EMPTY = 10,
+       BAR_ACC_FULL = 12, BAR_ACC_EMPTY = 14, BAR_COUNT = 16 };
 
 // D (+)= A x B^T with the accumulate flag as an operand
 __device__ __forceinline__ void umma_i8_acc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
@@ -139,14 +141,14 @@ gemm_iq4xs_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K
         abort_flag = 0;
         for (int i = 0; i < NRAW; ++i) {
             mbar_init(bar(BAR_RAW_FULL + i), 1);
-            mbar_init(bar(BAR_RAW_EMPTY + i), 128 + 128 * NW);     // unpack threads + scaling threads (d_w)
+            mbar_init(bar(BAR_RAW_EMPTY + i), 256 + 128 * NW);     // unpack threads + scaling threads (d_w)
         }
         for (int i = 0; i < NACT; ++i) {
             mbar_init(bar(BAR_ACT_FULL + i), 1);
             mbar_init(bar(BAR_ACT_EMPTY + i), 1 + 128 * NW);       // MMA commit + scaling threads (d_x)
         }
-        for (int i = 0; i < NA; ++i) {
-            mbar_init(bar(BAR_A_FULL + i), 128);
+        for (int i = 0; i < NG; ++i) {
+            mbar_init(bar(BAR_A_FULL + i), 256);
             mbar_init(bar(BAR_A_EMPTY + i), 1);
         }
         for (int i = 0; i < NBUF; ++i) {
@@ -168,7 +170,7 @@ gemm_iq4xs_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K
 
     if (warp == 0) {
         // ---- producer ----
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
         const uint8_t *act_tile = act + (size_t)tile_n * nsb * ACT_CHUNK;
         for (int s = 0; s < nsb; ++s) {
             if ((s & 1) == 0) {
@@ -190,23 +192,27 @@ gemm_iq4xs_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K
         }
     } else if (warp == 1) {
         // ---- MMA issuer: per block one MMA per limb, accumulating over the super-block ----
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
         bool ok = true;
         for (int s = 0; s < nsb && ok; ++s) {
             const int at = s % NACT, buf = s % NBUF;
             if (!mbar_wait_warp(bar(BAR_ACT_FULL + at), (s / NACT) & 1, abortp)) break;
             if (!mbar_wait_warp(bar(BAR_ACC_EMPTY + buf), ((s / NBUF) & 1) ^ 1, abortp)) break;
-            for (int j = 0; j < SB; ++j) {
-                const int b = s * SB + j, slot = b % NA;
-                if (!mbar_wait_warp(bar(BAR_A_FULL + slot), (b / NA) & 1, abortp)) { ok = false; break; }
+            for (int jg = 0; jg < SB / GB; ++jg) {
+                const int g = s * (SB / GB) + jg, gs = g % NG;          // group index, its place in the ring
+                if (!mbar_wait_warp(bar(BAR_A_FULL + gs), (g / NG) & 1, abortp)) { ok = false; break; }
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint64_t db = umma_desc(sbase + ACT_OFF + at * ACT_CHUNK + j * OPER_BYTES);
                     const uint32_t d = tmem_base + (uint32_t)buf * (2 * BN);
-                    umma_i8_acc(d, umma_desc(sbase + A_OFF + slot * A_SLOT), db, IDESC, j > 0);
-                    umma_i8_acc(d + BN, umma_desc(sbase + A_OFF + slot * A_SLOT + OPER_BYTES), db, IDESC, j > 0);
-                    tc_commit(bar(BAR_A_EMPTY + slot));
-                    if (j == SB - 1) {
+#pragma unroll
+                    for (int jj = 0; jj < GB; ++jj) {
+                        const int j = jg * GB + jj, slot = gs * GB + jj;
+                        const uint64_t db = umma_desc(sbase + ACT_OFF + at * ACT_CHUNK + j * OPER_BYTES);
+                        umma_i8_acc(d, umma_desc(sbase + A_OFF + slot * A_SLOT), db, IDESC, j > 0);
+                        umma_i8_acc(d + BN, umma_desc(sbase + A_OFF + slot * A_SLOT + OPER_BYTES), db, IDESC, j > 0);
+                    }
+                    tc_commit(bar(BAR_A_EMPTY + gs));
+                    if (jg == SB / GB - 1) {
                         tc_commit(bar(BAR_ACC_FULL + buf));
                         tc_commit(bar(BAR_ACT_EMPTY + at));
                     }
@@ -215,62 +221,58 @@ gemm_iq4xs_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K
             }
         }
     } else if (warp < 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
-    } else if (warp < 8) {
-        // ---- unpack: one thread per weight row ----
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 112;" ::: "memory");
-        const int r = (warp - 4) * 32 + lane;
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+    } else if (warp < 12) {
+        // ---- unpack: two threads per weight row, one per 16-weight half of every block ----
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
+        const int r = ((warp - 4) & 3) * 32 + lane, kh = (warp - 4) >> 2;      // row of the tile, half of K inside a block
         const bool row_ok = r < valid_rows;
         bool ok = true;
         for (int rs = 0; rs < nsb / 2 && ok; ++rs) {
             const int st = rs % NRAW;
             if (!mbar_wait_warp(bar(BAR_RAW_FULL + st), (rs / NRAW) & 1, abortp)) break;
-            uint32_t rw[ROWB / 4];                       // two super-blocks of this row
-            const uint4 *rp = reinterpret_cast<const uint4 *>(smem + RAW_OFF + st * RAW_STAGE + r * ROWB);
-#pragma unroll
-            for (int i = 0; i < ROWB / 16; ++i) {
-                const uint4 t = row_ok ? rp[i] : make_uint4(0, 0, 0, 0);
-                rw[4 * i] = t.x; rw[4 * i + 1] = t.y; rw[4 * i + 2] = t.z; rw[4 * i + 3] = t.w;
-            }
-            mbar_arrive(bar(BAR_RAW_EMPTY + st));
+            const uint8_t *rowp = smem + RAW_OFF + st * RAW_STAGE + r * ROWB;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const uint32_t scales_h = rw[34 * h] >> 16, scales_l = rw[34 * h + 1];
+                const uint2 hdr = *reinterpret_cast<const uint2 *>(rowp + SBB * h);      // d | scales_h, scales_l
+                const uint32_t scales_h = hdr.x >> 16, scales_l = hdr.y;
 #pragma unroll
-                for (int j = 0; j < SB; ++j) {
-                    const int b = (2 * rs + h) * SB + j, slot = b % NA;
-                    if (!mbar_wait_warp(bar(BAR_A_EMPTY + slot), ((b / NA) & 1) ^ 1, abortp)) { ok = false; break; }
-                    const int ls = row_ok ? iq4xs_ls(scales_h, scales_l, j) : 32;
-                    const uint4 th = *reinterpret_cast<const uint4 *>(smem + TAB_OFF + ls * 32);
-                    const uint4 tl = *reinterpret_cast<const uint4 *>(smem + TAB_OFF + ls * 32 + 16);
-                    uint32_t ah[8], al[8];               // words 0..3: weights 0..15, words 4..7: weights 16..31
+                for (int jg = 0; jg < SB / GB; ++jg) {
+                    const int g = (2 * rs + h) * (SB / GB) + jg, gs = g % NG;
+                    if (!mbar_wait_warp(bar(BAR_A_EMPTY + gs), ((g / NG) & 1) ^ 1, abortp)) { ok = false; break; }
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t q = rw[34 * h + 2 + 4 * j + i];
-                        uint32_t sel, msk;
-                        lookup4_prepare(q & 0x0F0F0F0Fu, &sel, &msk);
-                        ah[i] = lookup4_apply(th.x, th.y, th.z, th.w, sel, msk);
-                        al[i] = lookup4_apply(tl.x, tl.y, tl.z, tl.w, sel, msk);
-                        lookup4_prepare((q >> 4) & 0x0F0F0F0Fu, &sel, &msk);
-                        ah[4 + i] = lookup4_apply(th.x, th.y, th.z, th.w, sel, msk);
-                        al[4 + i] = lookup4_apply(tl.x, tl.y, tl.z, tl.w, sel, msk);
+                    for (int jj = 0; jj < GB; ++jj) {
+                        const int j = jg * GB + jj, slot = gs * GB + jj;
+                        const int ls = row_ok ? iq4xs_ls(scales_h, scales_l, j) : 32;        // 32: factor zero
+                        const uint4 th = *reinterpret_cast<const uint4 *>(smem + TAB_OFF + ls * 32);
+                        const uint4 tl = *reinterpret_cast<const uint4 *>(smem + TAB_OFF + ls * 32 + 16);
+                        const uint2 q01 = *reinterpret_cast<const uint2 *>(rowp + SBB * h + 8 + 16 * j);
+                        const uint2 q23 = *reinterpret_cast<const uint2 *>(rowp + SBB * h + 16 + 16 * j);
+                        const uint32_t q[4] = { q01.x, q01.y, q23.x, q23.y };
+                        uint32_t ah[4], al[4];           // this thread's 16 weights: 16 kh .. 16 kh + 15 of the block
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t sel, msk;
+                            lookup4_prepare((kh ? q[i] >> 4 : q[i]) & 0x0F0F0F0Fu, &sel, &msk);
+                            ah[i] = lookup4_apply(th.x, th.y, th.z, th.w, sel, msk);
+                            al[i] = lookup4_apply(tl.x, tl.y, tl.z, tl.w, sel, msk);
+                        }
+                        uint8_t *a = smem + A_OFF + slot * A_SLOT + kh * LBO + (r >> 3) * 128 + (r & 7) * 16;
+                        *reinterpret_cast<uint4 *>(a) = make_uint4(ah[0], ah[1], ah[2], ah[3]);
+                        *reinterpret_cast<uint4 *>(a + OPER_BYTES) = make_uint4(al[0], al[1], al[2], al[3]);
                     }
-                    uint8_t *a = smem + A_OFF + slot * A_SLOT + (r >> 3) * 128 + (r & 7) * 16;
-                    *reinterpret_cast<uint4 *>(a) = make_uint4(ah[0], ah[1], ah[2], ah[3]);
-                    *reinterpret_cast<uint4 *>(a + LBO) = make_uint4(ah[4], ah[5], ah[6], ah[7]);
-                    *reinterpret_cast<uint4 *>(a + OPER_BYTES) = make_uint4(al[0], al[1], al[2], al[3]);
-                    *reinterpret_cast<uint4 *>(a + OPER_BYTES + LBO) = make_uint4(al[4], al[5], al[6], al[7]);
-                    fence_async_smem();
-                    mbar_arrive(bar(BAR_A_FULL + slot));
+                    fence_async_smem();                  // one proxy fence per group of blocks
+                    mbar_arrive(bar(BAR_A_FULL + gs));
                 }
                 if (!ok) break;
             }
+            if (ok) mbar_arrive(bar(BAR_RAW_EMPTY + st));
         }
     } else {
         // ---- scale-accumulate, once per super-block ----
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 168;" ::: "memory");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 144;" ::: "memory");
         constexpr int CW = BN / NW;
-        const int q4 = warp & 3, u = (warp - 8) >> 2;
+        const int q4 = warp & 3, u = (warp - 12) >> 2;
         const int r = q4 * 32 + lane;
         const bool row_ok = r < valid_rows;
         f32x2 acc2[CW / 2];

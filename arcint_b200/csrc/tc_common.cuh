@@ -34,7 +34,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try(bar, parity)) return true;
-        if (i > 8) __nanosleep(32);                 // leave the issue slots to the working warps
+        if (i > 64) __nanosleep(20);                // after a short hot spin, leave the issue slots to the working warps
         if ((i & 63) == 63 && *abort_flag) return false;
     }
     *abort_flag = 1;
