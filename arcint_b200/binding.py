@@ -126,6 +126,7 @@ def lib():
     L.b200q_all_gather.argtypes = [vp, vp, vp, sz]
     L.b200q_all_to_all_v.argtypes = [vp, vp, C.POINTER(sz), C.POINTER(sz), vp, C.POINTER(sz), C.POINTER(sz)]
     L.b200q_tp_check.argtypes = [vp]
+    L.b200q_mul_mat_id_ep.argtypes = [vp, TP, TP, TP, TP, C.c_int]
     L.b200q_mul_mat_noalloc.argtypes = [C.c_int, vp, TP, TP, TP]
     L.b200q_noalloc_last_error.restype = C.c_char_p
     L.b200q_buffer_alloc.argtypes = [vp, sz, C.POINTER(vp)]
@@ -153,7 +154,7 @@ EXPORTS = [
     "b200q_init", "b200q_free", "b200q_last_error", "b200q_get_stream", "b200q_version", "b200q_supports", "b200q_mul_mat",
     "b200q_mul_mat_id", "b200q_graph_begin", "b200q_capture_begin", "b200q_capture_end", "b200q_graph_launch",
     "b200q_graph_free", "b200q_tp_unique_id", "b200q_tp_init", "b200q_tp_rank", "b200q_tp_shard", "b200q_all_reduce_f32",
-    "b200q_all_gather", "b200q_all_to_all_v", "b200q_tp_check", "b200q_mul_mat_noalloc", "b200q_noalloc_last_error", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
+    "b200q_all_gather", "b200q_all_to_all_v", "b200q_tp_check", "b200q_mul_mat_id_ep", "b200q_mul_mat_noalloc", "b200q_noalloc_last_error", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
     "b200q_tensor_get", "b200q_tensor_copy", "b200q_synchronize", "b200q_host_alloc", "b200q_host_free",
     "b200q_stats", "b200q_stats_reset", "b200q_timer_start", "b200q_timer_stop", "b200q_flush_l2",
     "b200q_debug_quantize_act", "b200q_debug_dequantize",
@@ -282,6 +283,9 @@ class Context:
         n = len(send_bytes)
         arr = lambda v: (C.c_size_t * n)(*[int(x) for x in v])
         self.check(self.L.b200q_all_to_all_v(self.h, send, arr(send_off), arr(send_bytes), recv, arr(recv_off), arr(recv_bytes)))
+
+    def mul_mat_id_ep(self, src0_local, src1, ids, dst, n_expert_total):
+        self.check(self.L.b200q_mul_mat_id_ep(self.h, src0_local, src1, ids, dst, n_expert_total))
 
     # ---- CUDA graphs ----
     def capture(self, fn):

@@ -157,8 +157,13 @@ struct RouteView {
     const int32_t *tiles[4];       // class k: tiles of at most 1, 2, 4, 8 pairs (int4 each)
     const int32_t *n_tiles;        // [4] device counters
     int64_t        max_tiles;      // upper bound of every list
+    const int32_t *owner_counts;   // expert parallelism: pairs per owner rank (device), else unused
 };
-b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, RouteView *out);
+b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, RouteView *out, int experts_per_owner = 0);
+b200q_status launch_ep_pack(b200q_ctx *ctx, const b200q_tensor *src1, const b200q_tensor *ids, int n_expert,
+                            int experts_per_owner, const int32_t *pairs, float *send_x, int32_t *send_e);
+b200q_status launch_ep_unpack(b200q_ctx *ctx, const float *back, const int32_t *pairs, int n_used, int n_pairs, int M,
+                              float *dst, int64_t ld1, int64_t ld2);
 void         moe_free(b200q_ctx *ctx);
 
 // tp.cu

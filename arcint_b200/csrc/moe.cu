@@ -21,13 +21,15 @@ struct RouteEntry {
     int     n_expert = 0;
     uint64_t gen = 0;
     bool    valid = false;
+    int     experts_per_owner = 0;
     Workspace buf;               // pairs | 4 tile lists | 4 counters
     RouteView view;
 };
 
 __global__ void __launch_bounds__(1024)
 moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_expert, int32_t *pairs,
-                 int32_t *tiles0, int32_t *tiles1, int32_t *tiles2, int32_t *tiles3, int32_t *n_tiles) {
+                 int32_t *tiles0, int32_t *tiles1, int32_t *tiles2, int32_t *tiles3, int32_t *n_tiles,
+                 int32_t *owner_counts, int experts_per_owner) {
     extern __shared__ int sm[];
     int *cnt = sm, *base = sm + n_expert, *fill = sm + 2 * n_expert, *toff = sm + 3 * n_expert;   // toff: [4][n_expert]
     const int tid = threadIdx.x, nth = blockDim.x;
@@ -75,15 +77,73 @@ moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_ex
         const int e = expert_of(p);
         pairs[base[e] + atomicAdd(&fill[e], 1)] = p;
     }
+    // expert parallelism: how many pairs go to each owner (experts are owned in contiguous ranges)
+    if (owner_counts) {
+        const int n_owner = n_expert / experts_per_owner;
+        for (int g = tid; g < n_owner; g += nth) {
+            int c = 0;
+            for (int e = g * experts_per_owner; e < (g + 1) * experts_per_owner; ++e) c += cnt[e];
+            owner_counts[g] = c;
+        }
+    }
 }
 
-b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, RouteView *out) {
+// expert-parallel dispatch: the activation row and the owner-local expert index of every pair, in
+// the order of the sorted pair list (which groups pairs by owner because owners hold expert ranges)
+__global__ void ep_pack_kernel(const uint8_t *src1, size_t nb1, size_t nb2, int ne11, const uint8_t *ids, size_t ids_nb1,
+                               int n_used, int n_pairs, int K, int n_expert, int experts_per_owner,
+                               const int32_t *pairs, float *send_x, int32_t *send_e) {
+    const int pos = blockIdx.x;
+    if (pos >= n_pairs) return;
+    const int p = pairs[pos], t = p / n_used, i = p - t * n_used;
+    const float4 *x = reinterpret_cast<const float4 *>(src1 + (size_t)(i % ne11) * nb1 + (size_t)t * nb2);
+    float4 *o = reinterpret_cast<float4 *>(send_x + (size_t)pos * K);
+    for (int k = threadIdx.x; k < K / 4; k += blockDim.x) o[k] = x[k];
+    if (threadIdx.x == 0) {
+        const int e = min(max(reinterpret_cast<const int32_t *>(ids + (size_t)t * ids_nb1)[i], 0), n_expert - 1);
+        send_e[pos] = e % experts_per_owner;
+    }
+}
+
+// expert-parallel combine: result row pos of the returned buffer belongs to pair pairs[pos]
+__global__ void ep_unpack_kernel(const float *back, const int32_t *pairs, int n_used, int n_pairs, int M, float *dst,
+                                 int64_t ld1, int64_t ld2) {
+    const int pos = blockIdx.x;
+    if (pos >= n_pairs) return;
+    const int p = pairs[pos], t = p / n_used, i = p - t * n_used;
+    const float *b = back + (size_t)pos * M;
+    float *o = dst + t * ld2 + i * ld1;
+    for (int m = threadIdx.x; m < M; m += blockDim.x) o[m] = b[m];
+}
+
+b200q_status launch_ep_pack(b200q_ctx *ctx, const b200q_tensor *src1, const b200q_tensor *ids, int n_expert,
+                            int experts_per_owner, const int32_t *pairs, float *send_x, int32_t *send_e) {
+    const int n_pairs = (int)(ids->ne[0] * ids->ne[1]);
+    if (n_pairs == 0) return B200Q_OK;
+    ep_pack_kernel<<<n_pairs, 128, 0, ctx->stream>>>((const uint8_t *)src1->data, src1->nb[1], src1->nb[2], (int)src1->ne[1],
+                                                   (const uint8_t *)ids->data, ids->nb[1], (int)ids->ne[0], n_pairs,
+                                                   (int)src1->ne[0], n_expert, experts_per_owner, pairs, send_x, send_e);
+    B200Q_CUDA(ctx, cudaGetLastError());
+    count(ctx, ST_MOE_PACK);
+    return B200Q_OK;
+}
+
+b200q_status launch_ep_unpack(b200q_ctx *ctx, const float *back, const int32_t *pairs, int n_used, int n_pairs, int M,
+                              float *dst, int64_t ld1, int64_t ld2) {
+    if (n_pairs == 0) return B200Q_OK;
+    ep_unpack_kernel<<<n_pairs, 128, 0, ctx->stream>>>(back, pairs, n_used, n_pairs, M, dst, ld1, ld2);
+    B200Q_CUDA(ctx, cudaGetLastError());
+    return B200Q_OK;
+}
+
+b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, RouteView *out, int experts_per_owner) {
     const int n_used = (int)ids->ne[0], n_tok = (int)ids->ne[1];
     const int64_t n_pairs = (int64_t)n_used * n_tok;
     RouteEntry *hit = nullptr;
     for (RouteEntry *e : ctx->routes)
         if (e && e->valid && e->ids_data == ids->data && e->ne[0] == ids->ne[0] && e->ne[1] == ids->ne[1] &&
-            e->nb1 == ids->nb[1] && e->n_expert == n_expert && e->gen == ctx->generation) { hit = e; break; }
+            e->nb1 == ids->nb[1] && e->n_expert == n_expert && e->gen == ctx->generation &&
+            e->experts_per_owner == experts_per_owner) { hit = e; break; }
     if (hit) {
         count(ctx, ST_ROUTE_CACHE_HIT);
         *out = hit->view;
@@ -98,7 +158,7 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     RouteEntry &e = *ctx->routes[pick];
     e.valid = false;
     const int64_t max_tiles = (n_pairs + 7) / 8 + (n_expert < n_pairs ? n_expert : n_pairs);
-    const size_t bytes = sizeof(int32_t) * (size_t)(n_pairs + 4 * 4 * max_tiles + 4) + 64;
+    const size_t bytes = sizeof(int32_t) * (size_t)(n_pairs + 4 * 4 * max_tiles + 4 + 4096) + 64;   // + owner counts
     b200q_status st = ws_reserve(ctx, &e.buf, bytes);
     if (st != B200Q_OK) return st;
     int32_t *p = (int32_t *)e.buf.ptr;
@@ -106,6 +166,7 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     int32_t *tl[4];
     for (int k = 0; k < 4; ++k) tl[k] = p + n_pairs + (size_t)k * 4 * max_tiles;
     int32_t *n_tiles = p + n_pairs + (size_t)16 * max_tiles;
+    int32_t *owner_counts = n_tiles + 4;
     const size_t smem = sizeof(int) * (size_t)n_expert * 7;
     if (smem > 200 * 1024) return fail(ctx, B200Q_UNSUPPORTED, "route: %d experts", n_expert);
     static bool attr = false;
@@ -114,7 +175,9 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
         attr = true;
     }
     moe_route_kernel<<<1, 1024, smem, ctx->stream>>>((const uint8_t *)ids->data, ids->nb[1], n_used, n_tok, n_expert, pairs,
-                                                     tl[0], tl[1], tl[2], tl[3], n_tiles);
+                                                     tl[0], tl[1], tl[2], tl[3], n_tiles,
+                                                     experts_per_owner > 0 ? owner_counts : nullptr,
+                                                     experts_per_owner > 0 ? experts_per_owner : 1);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_MOE_ROUTE);
     e.ids_data = ids->data;
@@ -127,6 +190,8 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     for (int k = 0; k < 4; ++k) e.view.tiles[k] = tl[k];
     e.view.n_tiles = n_tiles;
     e.view.max_tiles = max_tiles;
+    e.view.owner_counts = owner_counts;
+    e.experts_per_owner = experts_per_owner;
     e.valid = true;
     *out = e.view;
     return B200Q_OK;

@@ -197,6 +197,97 @@ b200q_status b200q_all_to_all_v(b200q_ctx *ctx, const void *dev_send, const size
     return B200Q_OK;
 }
 
+// Expert-parallel MUL_MAT_ID. Every rank holds its own tokens (src1 [K, ne11, n_tok], ids [n_used, n_tok]
+// with GLOBAL expert ids, dst [M, n_used, n_tok]) and the experts [rank * n_local, (rank + 1) * n_local)
+// as src0 [K, M, n_local]; n_expert_total = n_local * nranks. The call routes the local pairs by owner,
+// exchanges the per-owner counts (one small all-gather and one host synchronisation: the send and receive
+// sizes must be known on the host), sends every pair's f32 activation row and owner-local expert index to
+// the owner (all-to-all), runs b200q_mul_mat_id over what it received, returns the result rows (all-to-all)
+// and scatters them into dst. It starts a new cache generation on the context (its receive buffers are
+// reused with other contents by the next call).
+b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local, const b200q_tensor *src1,
+                                 const b200q_tensor *ids, b200q_tensor *dst, int n_expert_total) {
+    TpState *tp;
+    Nccl *api;
+    b200q_status st = tp_get(ctx, &tp, &api);
+    if (st != B200Q_OK) return st;
+    if (!src0_local || !src1 || !ids || !dst) return B200Q_INVALID;
+    const int G = tp->nranks;
+    if (n_expert_total <= 0 || n_expert_total % G || src0_local->ne[2] != n_expert_total / G)
+        return fail(ctx, B200Q_INVALID, "experts: %d in total over %d ranks, %lld here", n_expert_total, G,
+                    (long long)src0_local->ne[2]);
+    if (n_expert_total > 4096 || G > 64) return fail(ctx, B200Q_UNSUPPORTED, "expert-parallel limits: 4096 experts, 64 ranks");
+    if (ids->type != B200Q_TYPE_I32 || src1->type != B200Q_TYPE_F32 || dst->type != B200Q_TYPE_F32 || src1->nb[0] != 4 ||
+        dst->nb[0] != 4 || (uintptr_t)src1->data % 16 || src1->nb[1] % 16 || src1->nb[2] % 16 || src1->ne[0] % 4)
+        return fail(ctx, B200Q_UNSUPPORTED, "expert-parallel MUL_MAT_ID needs packed f32 activations and i32 ids");
+    const int n_local = n_expert_total / G, n_used = (int)ids->ne[0], n_tok = (int)ids->ne[1];
+    const int64_t K = src0_local->ne[0], M = src0_local->ne[1];
+    const int n_pairs = n_used * n_tok;
+    if (src1->ne[0] != K || dst->ne[0] != M || dst->ne[1] != n_used || dst->ne[2] != n_tok ||
+        (src1->ne[1] != 1 && src1->ne[1] != n_used) || src1->ne[2] != n_tok)
+        return fail(ctx, B200Q_INVALID, "expert-parallel MUL_MAT_ID shapes");
+    B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+    ++ctx->generation;
+
+    // 1. route by global expert (which groups by owner) and count pairs per owner
+    RouteView rv;
+    if ((st = moe_route(ctx, ids, n_expert_total, &rv, n_local)) != B200Q_OK) return st;
+    // 2. everyone learns everyone's counts
+    if ((st = ws_reserve(ctx, &ctx->moe_ws[0], sizeof(int32_t) * (size_t)G * G)) != B200Q_OK) return st;
+    int32_t *all_counts = (int32_t *)ctx->moe_ws[0].ptr;
+    B200Q_NCCL(ctx, api, api->AllGather(rv.owner_counts, all_counts, (size_t)G, ncclInt32, tp->comm, ctx->stream));
+    std::vector<int32_t> h((size_t)G * G);
+    B200Q_CUDA(ctx, cudaMemcpyAsync(h.data(), all_counts, sizeof(int32_t) * h.size(), cudaMemcpyDeviceToHost, ctx->stream));
+    B200Q_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    std::vector<size_t> so(G), sb(G), ro(G), rb(G), zo(G), zb(G), wo(G), wb(G);
+    size_t n_send = 0, n_recv = 0;
+    for (int g = 0; g < G; ++g) {
+        const size_t cs = (size_t)h[(size_t)tp->rank * G + g], cr = (size_t)h[(size_t)g * G + tp->rank];
+        so[g] = n_send; sb[g] = cs; ro[g] = n_recv; rb[g] = cr;
+        n_send += cs;
+        n_recv += cr;
+    }
+    if ((int64_t)n_send != n_pairs) return fail(ctx, B200Q_INVALID, "route counted %zu of %d pairs", n_send, n_pairs);
+    // 3. pack and dispatch
+    const size_t rowx = (size_t)K * 4, rowy = (size_t)M * 4;
+    if ((st = ws_reserve(ctx, &ctx->moe_ws[1], rowx * (n_send ? n_send : 1))) != B200Q_OK) return st;
+    if ((st = ws_reserve(ctx, &ctx->moe_ws[2], 4 * (n_send ? n_send : 1))) != B200Q_OK) return st;
+    if ((st = ws_reserve(ctx, &ctx->moe_ws[3], rowx * (n_recv ? n_recv : 1))) != B200Q_OK) return st;
+    if ((st = ws_reserve(ctx, &ctx->moe_ws[4], 4 * (n_recv ? n_recv : 1))) != B200Q_OK) return st;
+    if ((st = ws_reserve(ctx, &ctx->moe_ws[5], rowy * (n_recv ? n_recv : 1))) != B200Q_OK) return st;
+    if ((st = ws_reserve(ctx, &ctx->moe_ws[6], rowy * (n_send ? n_send : 1))) != B200Q_OK) return st;
+    float *send_x = (float *)ctx->moe_ws[1].ptr, *recv_x = (float *)ctx->moe_ws[3].ptr;
+    int32_t *send_e = (int32_t *)ctx->moe_ws[2].ptr, *recv_e = (int32_t *)ctx->moe_ws[4].ptr;
+    float *out = (float *)ctx->moe_ws[5].ptr, *back = (float *)ctx->moe_ws[6].ptr;
+    if ((st = launch_ep_pack(ctx, src1, ids, n_expert_total, n_local, rv.pairs, send_x, send_e)) != B200Q_OK) return st;
+    for (int g = 0; g < G; ++g) { zo[g] = so[g] * rowx; zb[g] = sb[g] * rowx; wo[g] = ro[g] * rowx; wb[g] = rb[g] * rowx; }
+    if ((st = b200q_all_to_all_v(ctx, send_x, zo.data(), zb.data(), recv_x, wo.data(), wb.data())) != B200Q_OK) return st;
+    for (int g = 0; g < G; ++g) { zo[g] = so[g] * 4; zb[g] = sb[g] * 4; wo[g] = ro[g] * 4; wb[g] = rb[g] * 4; }
+    if ((st = b200q_all_to_all_v(ctx, send_e, zo.data(), zb.data(), recv_e, wo.data(), wb.data())) != B200Q_OK) return st;
+    // 4. the local experts over everything received: one slot per received pair
+    if (n_recv) {
+        b200q_tensor x1, id1, y1;
+        x1.type = B200Q_TYPE_F32; x1.data = recv_x;
+        x1.ne[0] = K; x1.ne[1] = 1; x1.ne[2] = (int64_t)n_recv; x1.ne[3] = 1;
+        x1.nb[0] = 4; x1.nb[1] = rowx; x1.nb[2] = rowx; x1.nb[3] = rowx * n_recv;
+        id1.type = B200Q_TYPE_I32; id1.data = recv_e;
+        id1.ne[0] = 1; id1.ne[1] = (int64_t)n_recv; id1.ne[2] = 1; id1.ne[3] = 1;
+        id1.nb[0] = 4; id1.nb[1] = 4; id1.nb[2] = 4 * n_recv; id1.nb[3] = 4 * n_recv;
+        y1.type = B200Q_TYPE_F32; y1.data = out;
+        y1.ne[0] = M; y1.ne[1] = 1; y1.ne[2] = (int64_t)n_recv; y1.ne[3] = 1;
+        y1.nb[0] = 4; y1.nb[1] = rowy; y1.nb[2] = rowy; y1.nb[3] = rowy * n_recv;
+        if ((st = b200q_mul_mat_id(ctx, src0_local, &x1, &id1, &y1)) != B200Q_OK) return st;
+    }
+    // 5. combine: results travel back the way the activations came
+    for (int g = 0; g < G; ++g) { zo[g] = ro[g] * rowy; zb[g] = rb[g] * rowy; wo[g] = so[g] * rowy; wb[g] = sb[g] * rowy; }
+    if ((st = b200q_all_to_all_v(ctx, out, zo.data(), zb.data(), back, wo.data(), wb.data())) != B200Q_OK) return st;
+    b200q::count(ctx, ST_EP_COMBINE);
+    st = launch_ep_unpack(ctx, back, rv.pairs, n_used, n_pairs, (int)M, (float *)dst->data, (int64_t)(dst->nb[1] / 4),
+                          (int64_t)(dst->nb[2] / 4));
+    ++ctx->generation;
+    return st;
+}
+
 // The communicator's asynchronous error state, for callers that watch a stuck peer from the
 // host: B200Q_OK, or B200Q_NCCL_ERROR after aborting the communicator.
 b200q_status b200q_tp_check(b200q_ctx *ctx) {

@@ -143,6 +143,12 @@ B200Q_API b200q_status b200q_all_gather(b200q_ctx *ctx, const void *dev_send, vo
 B200Q_API b200q_status b200q_all_to_all_v(b200q_ctx *ctx, const void *dev_send, const size_t *send_offsets,
                                           const size_t *send_bytes, void *dev_recv, const size_t *recv_offsets,
                                           const size_t *recv_bytes);
+/* MUL_MAT_ID with the experts split over the ranks: src0_local holds this rank's experts
+ * [K, M, n_expert_total / nranks]; src1, ids (global expert ids) and dst are this rank's tokens.
+ * Dispatch and combine are all-to-alls; the call synchronizes the stream once (the exchange sizes
+ * must reach the host) and starts a new cache generation on the context. */
+B200Q_API b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local, const b200q_tensor *src1,
+                                           const b200q_tensor *ids, b200q_tensor *dst, int n_expert_total);
 B200Q_API b200q_status b200q_tp_check(b200q_ctx *ctx);
 
 /* ggml backend buffer interface (buffer alloc, set_tensor, get_tensor, synchronize):

@@ -2,7 +2,7 @@
   python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 ... tests/mgpu_worker.py
 Every rank: its own GPU and b200q context, joins the NCCL communicator (id broadcast over a gloo
 group), runs a column split (Q8_0 prompt GEMM, all-gather), a row split (Q4_0 and Q4_K, all-reduce
-of the f32 partials) and a variable all-to-all, and compares with the CPU oracle."""
+of the f32 partials), a variable all-to-all and an expert-parallel MUL_MAT_ID, and compares with the CPU oracle."""
 import os
 import sys
 
@@ -77,10 +77,30 @@ def main():
     want = np.concatenate([np.full(c, 100 * p + rank, dtype=np.float32) for p, c in enumerate(recv_counts)])
     assert np.array_equal(got, want), "all_to_all_v"
 
+    # expert parallelism: 8 experts split over the ranks, every rank brings its own tokens (a different
+    # count per rank) with global expert ids; against the oracle's MUL_MAT_ID over all experts
+    ep_errs = []
+    for t, m, k, n_tok, ne11 in ((A.Q4_K, 192, 512, 5 + 3 * rank, 1), (A.Q4_0, 96, 256, 37 + rank, 2), (A.Q6_K, 64, 256, 1, 1)):
+        n_exp, n_used = 4 * world, 2
+        per = n_exp // world
+        w = np.stack([O.quantize(t, O.fill_normal(m * k, 500 + 10 * t + e, 0.05).reshape(m, k)) for e in range(n_exp)])
+        x = O.fill_normal(n_tok * ne11 * k, 600 + rank, 1.0).reshape(n_tok, ne11, k)
+        ids = O.route_ids(n_used, n_tok, n_exp, 700 + rank)
+        dw = ctx.upload(np.ascontiguousarray(w[rank * per:(rank + 1) * per]))
+        dx, di, dy = ctx.upload(x), ctx.upload(ids), ctx.alloc(n_tok * n_used * m * 4)
+        rb = w.shape[-1]
+        src0 = A.Tensor.make(t, [k, m, per, 1], [A.block_bytes(t), rb, rb * m, rb * m * per], dw)
+        ctx.mul_mat_id_ep(src0, A.Tensor.f32(dx, [k, ne11, n_tok]), A.Tensor.make(A.I32, [n_used, n_tok, 1, 1], [4, 4 * n_used], di),
+                          A.Tensor.f32(dy, [m, n_used, n_tok]), n_exp)
+        got = ctx.download(dy, (n_tok, n_used, m), np.float32)
+        ep_errs.append(rel_err(got.reshape(-1, m), O.mul_mat_id(t, w, m, k, x, ids, f64=True).reshape(-1, m)))
+        assert ep_errs[-1] < TOL, ("expert parallel", t, ep_errs[-1])
+
     st = ctx.stats()
     assert st.get("tp_allgather") == 1 and st.get("tp_allreduce") == 2 and st.get("gemm_tc") == 1, st
     dist.barrier()
-    print("MGPU_OK rank %d/%d colsplit %.2e rowsplit %s" % (rank, world, e1, ["%.2e" % e for e in errs]), flush=True)
+    print("MGPU_OK rank %d/%d colsplit %.2e rowsplit %s ep %s" % (rank, world, e1, ["%.2e" % e for e in errs],
+                                                                     ["%.2e" % e for e in ep_errs]), flush=True)
     ctx.close()
     dist.destroy_process_group()
 
