@@ -159,6 +159,9 @@ struct RouteView {
     int64_t        max_tiles;      // upper bound of every list
     const int32_t *owner_counts;   // expert parallelism: pairs per owner rank (device), else unused
 };
+// tensor map of a packed weight matrix seen as [M rows][row_bytes / 4] 32-bit elements, box = 128 rows x box_bytes
+b200q_status make_weight_tmap(b200q_ctx *ctx, void *tmap_out, const void *w, size_t row_stride, int64_t M, int64_t row_bytes,
+                              int box_bytes);
 b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, RouteView *out, int experts_per_owner = 0);
 b200q_status launch_ep_pack(b200q_ctx *ctx, const b200q_tensor *src1, const b200q_tensor *ids, int n_expert,
                             int experts_per_owner, const int32_t *pairs, float *send_x, int32_t *send_e);

@@ -26,6 +26,8 @@
 // per 16-weight half of a block), 4*NW scale-accumulate warps. One stage = one super-block (eight MMA pairs); two accumulator pairs
 // (2 x 2 x 128 columns = all 512 tensor-memory columns) let the MMAs of super-block s+1 run
 // while s is scaled. Every mbarrier wait is bounded.
+#include <cuda.h>
+
 #include "formats.cuh"
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -116,7 +118,7 @@ quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t n
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_iq4xs_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, const uint8_t *__restrict__ act,
+gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
                   int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint32_t tmem_base_slot;
@@ -172,15 +174,16 @@ gemm_iq4xs_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K
         // ---- producer ----
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
         const uint8_t *act_tile = act + (size_t)tile_n * nsb * ACT_CHUNK;
+        if (lane == 0) tma_prefetch_desc(&wmap);
         for (int s = 0; s < nsb; ++s) {
             if ((s & 1) == 0) {
                 const int rs = s >> 1, st = rs % NRAW;
                 if (!mbar_wait_warp(bar(BAR_RAW_EMPTY + st), ((rs / NRAW) & 1) ^ 1, abortp)) break;
-                if (lane == 0) mbar_expect_tx(bar(BAR_RAW_FULL + st), (uint32_t)valid_rows * ROWB);
-                __syncwarp();
-                for (int r = lane; r < valid_rows; r += 32)
-                    bulk_g2s(sbase + RAW_OFF + st * RAW_STAGE + r * ROWB,
-                             W + (size_t)(row0 + r) * row_stride + (size_t)rs * ROWB, ROWB, bar(BAR_RAW_FULL + st));
+                if (lane == 0) {
+                    // the whole [128 rows x 272 B] box in one tiled copy; rows past M arrive as zeros
+                    mbar_expect_tx(bar(BAR_RAW_FULL + st), RAW_STAGE);
+                    tma_load_2d(sbase + RAW_OFF + st * RAW_STAGE, &wmap, rs * (ROWB / 4), row0, bar(BAR_RAW_FULL + st));
+                }
             }
             const int at = s % NACT;
             if (!mbar_wait_warp(bar(BAR_ACT_EMPTY + at), ((s / NACT) & 1) ^ 1, abortp)) break;
@@ -378,9 +381,12 @@ b200q_status launch_gemm_kq(b200q_ctx *ctx, int type, const void *w, size_t row_
         B200Q_CUDA(ctx, cudaFuncSetAttribute(kq::gemm_iq4xs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kq::SMEM_TOTAL));
         attr_set = true;
     }
+    CUtensorMap wmap;
+    b200q_status st = make_weight_tmap(ctx, &wmap, w, row_stride, M, (K / 256) * kq::SBB, kq::ROWB);
+    if (st != B200Q_OK) return st;
     dim3 grid((unsigned)((N + kq::BN - 1) / kq::BN), (unsigned)((M + kq::BM - 1) / kq::BM));
-    kq::gemm_iq4xs_kernel<<<grid, kq::THREADS, kq::SMEM_TOTAL, ctx->stream>>>((const uint8_t *)w, row_stride, (int)M, (int)K, act,
-                                                                              (int)N, dst, ldd, ctx->error_word);
+    kq::gemm_iq4xs_kernel<<<grid, kq::THREADS, kq::SMEM_TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd,
+                                                                              ctx->error_word);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
     return B200Q_OK;

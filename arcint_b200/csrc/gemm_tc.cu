@@ -31,6 +31,8 @@
 // Every wait on an mbarrier is bounded; a wait that runs out sets an error word, all roles
 // leave their loops, tensor memory is freed and the launch reports B200Q_TIMEOUT at the
 // next synchronize.
+#include <cuda.h>
+
 #include "formats.cuh"
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -124,7 +126,7 @@ template <int N> __device__ __forceinline__ uint32_t word_at(const uint32_t (&w)
 
 template <int TYPE>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, const uint8_t *__restrict__ act,
+gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
                int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word) {
     typedef Smem<TYPE> L;
     constexpr int ROWB = Raw<TYPE>::ROW;
@@ -178,15 +180,16 @@ gemm_tc_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int K, c
         // ---- producer ----
         asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
         const uint8_t *act_tile = act + (size_t)tile_n * nst * ACT_CHUNK;
+        if (lane == 0) tma_prefetch_desc(&wmap);
         for (int s = 0; s < nst; ++s) {
             const int st = s % NSTAGE;
             const uint32_t par = ((s / NSTAGE) & 1) ^ 1;        // first pass over the ring: slots are free
             if (!mbar_wait_warp(bar(BAR_RAW_EMPTY + st), par, abortp)) break;
-            if (lane == 0) mbar_expect_tx(bar(BAR_RAW_FULL + st), (uint32_t)valid_rows * ROWB);
-            __syncwarp();
-            for (int r = lane; r < valid_rows; r += 32)
-                bulk_g2s(sbase + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB,
-                         W + (size_t)(row0 + r) * row_stride + (size_t)s * ROWB, ROWB, bar(BAR_RAW_FULL + st));
+            if (lane == 0) {
+                // the stage's [128 rows x ROWB] box in one tiled copy; rows past M arrive as zeros
+                mbar_expect_tx(bar(BAR_RAW_FULL + st), L::RAW_STAGE);
+                tma_load_2d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, s * (ROWB / 4), row0, bar(BAR_RAW_FULL + st));
+            }
             if (!mbar_wait_warp(bar(BAR_ACT_EMPTY + st), par, abortp)) break;
             if (lane == 0) {
                 mbar_expect_tx(bar(BAR_ACT_FULL + st), ACT_CHUNK);
@@ -384,9 +387,12 @@ static b200q_status launch_t(b200q_ctx *ctx, const void *w, size_t row_stride, i
         B200Q_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::TOTAL));
         attr_set = true;
     }
+    CUtensorMap wmap;
+    constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
+    b200q_status st = make_weight_tmap(ctx, &wmap, w, row_stride, M, (K / 32) * BB, tc::Raw<TYPE>::ROW);
+    if (st != B200Q_OK) return st;
     dim3 grid((unsigned)((N + tc::BN - 1) / tc::BN), (unsigned)((M + tc::BM - 1) / tc::BM));
-    kern<<<grid, tc::THREADS, L::TOTAL, ctx->stream>>>((const uint8_t *)w, row_stride, (int)M, (int)K, act, (int)N, dst,
-                                                       ldd, ctx->error_word);
+    kern<<<grid, tc::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd, ctx->error_word);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
     return B200Q_OK;
