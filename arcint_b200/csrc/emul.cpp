@@ -128,6 +128,7 @@ uint32_t emul_lookup4_tab(const uint32_t *t, uint32_t idx) {
 }
 
 void emul_iq4xs_limbs(int ls, int n, int *hi, int *lo) { iq4xs_limbs(ls, n, hi, lo); }
+void emul_iq4xs_limbs8(uint32_t q, int m, uint32_t *out4) { iq4xs_limbs8(q, m, out4, out4 + 1, out4 + 2, out4 + 3); }
 uint32_t emul_nib_minus8(uint32_t t) { return nib_minus8(t); }
 uint32_t emul_six_minus32(uint32_t t) { return six_minus32(t); }
 

@@ -97,14 +97,42 @@ B200Q_HD uint32_t lookup4_apply(uint32_t t0, uint32_t t1, uint32_t t2, uint32_t 
 }
 
 // IQ4_XS for the int8 tensor cores: the product p = (ls - 32) * kvalues[n] of a weight's integer
-// sub-scale and codebook value (|p| <= 4064) as two int8 limbs, p = 64 * hi + lo with
-// lo in [-32, 31] and hi in [-64, 64]. One MMA per limb against the same activation gives
-// sum(p x) = 64 * sum(hi x) + sum(lo x) exactly.
+// sub-scale and codebook value (|p| <= 4064) as two int8 limbs, p = 256 * hi + lo with
+// hi = (p + 128) >> 8 in [-16, 16] and lo in [-128, 127]. One MMA per limb against the same
+// activation gives sum(p x) = 256 * sum(hi x) + sum(lo x) exactly.
 B200Q_HD void iq4xs_limbs(int ls, int n, int *hi, int *lo) {
     const int p = (ls - 32) * kvalue_iq4nl(n);
-    const int h = (p + 32) >> 6;                        // arithmetic shift: floor((p + 32) / 64)
+    const int h = (p + 128) >> 8;                       // arithmetic shift: floor((p + 128) / 256)
     *hi = h;
-    *lo = p - 64 * h;
+    *lo = p - 256 * h;
+}
+
+// The same limbs for the eight weights of one packed word q (byte b holds weight b of the word's
+// group of four in its low nibble and weight 16 + b in its high nibble), in registers only:
+//   hi_l / lo_l: limbs of the four low-nibble weights, hi_h / lo_h: of the four high-nibble ones.
+// The codebook is looked up biased by 128 (unsigned bytes) with byte permutes whose selectors are
+// the nibbles of q as they lie (q & 0x7777 7777 picks among eight entries, bit 3 of each nibble
+// chooses the table half), widened to two 16-bit halves per register and multiplied by
+// m = ls - 32 with one integer multiply-add per pair of weights:
+//   half = (kv + 128) * m + (32896 - 128 m) = p + 128 + 32768, always inside 0..65535,
+// so no carry crosses the halves; flipping bit 15 gives the 16-bit two's complement of p + 128,
+// whose high byte is hi, and flipping bit 7 of its low byte gives lo.
+B200Q_HD void iq4xs_limbs8(uint32_t q, int m, uint32_t *hi_l, uint32_t *lo_l, uint32_t *hi_h, uint32_t *lo_h) {
+    const uint32_t t0 = 0x3F2D1801u, t1 = 0x766A5D4Fu, t2 = 0xA6998D81u, t3 = 0xF1D9C5B5u;   // kvalues + 128
+    const uint32_t sel_a = q & 0x77777777u, sel_b = sel_a >> 16;      // nibbles (l0 h0 l1 h1), (l2 h2 l3 h3)
+    const uint32_t q4 = q << 4;                                       // low nibbles' bit 3 at byte bit 7
+    const uint32_t msk_a = hd_byte_perm(q4, q, 0xD9C8), msk_b = hd_byte_perm(q4, q, 0xFBEA);   // sign-replicate
+    const uint32_t v_a = (hd_byte_perm(t0, t1, sel_a) & ~msk_a) | (hd_byte_perm(t2, t3, sel_a) & msk_a);
+    const uint32_t v_b = (hd_byte_perm(t0, t1, sel_b) & ~msk_b) | (hd_byte_perm(t2, t3, sel_b) & msk_b);
+    const uint32_t c = (uint32_t)(32896 - 128 * m) * 0x10001u, um = (uint32_t)m;
+    const uint32_t za = (hd_byte_perm(v_a, 0, 0x4240) * um + c) ^ 0x80808080u;     // low-nibble weights 0, 1
+    const uint32_t zb = (hd_byte_perm(v_a, 0, 0x4341) * um + c) ^ 0x80808080u;     // high-nibble weights 0, 1
+    const uint32_t zc = (hd_byte_perm(v_b, 0, 0x4240) * um + c) ^ 0x80808080u;     // low-nibble weights 2, 3
+    const uint32_t zd = (hd_byte_perm(v_b, 0, 0x4341) * um + c) ^ 0x80808080u;     // high-nibble weights 2, 3
+    *hi_l = hd_byte_perm(za, zc, 0x7531);
+    *lo_l = hd_byte_perm(za, zc, 0x6420);
+    *hi_h = hd_byte_perm(zb, zd, 0x7531);
+    *lo_h = hd_byte_perm(zb, zd, 0x6420);
 }
 
 // Generic, slow, exact f32 decode of weight i of a row (used by the debug dequantizer

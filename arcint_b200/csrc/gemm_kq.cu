@@ -7,9 +7,12 @@
 // codebook values with the int8 activation (per-256 activation scale). Here the integer
 // sub-scale is folded into the int8 operand so the tensor core accumulates the whole
 // super-block: p = (ls - 32) * kvalues[n] (|p| <= 4064) is split into two int8 limbs,
-// p = 64 hi + lo, and two MMAs per 32 weights (hi and lo against the same activation block)
+// p = 256 hi + lo, and two MMAs per 32 weights (hi and lo against the same activation block)
 // accumulate over the eight blocks into two int32 accumulators in tensor memory;
-// 64 * sum(hi x) + sum(lo x) is the exact integer sum_sb (ls_sb - 32) I_sb. The f32 work drops
+// 256 * sum(hi x) + sum(lo x) is the exact integer sum_sb (ls_sb - 32) I_sb. The limbs are
+// computed in registers (a biased codebook lookup and one multiply-add per two weights): the
+// kernel's scarce resource is the shared-memory port (operand reads of the MMAs, the staged
+// copies, the unpack warps' loads and stores), so nothing that can be computed is looked up there. The f32 work drops
 // from once per 32 to once per 256 of K, so this kernel is bound by the tensor pipe and the
 // operand unpack rather than by the FP32 pipe.
 //
@@ -23,7 +26,7 @@
 //
 // Layout of roles, staging and barriers follows gemm_tc.cu: producer warp (bulk copies of raw
 // rows and activation chunks), MMA warp, eight unpack warps (two threads per weight row, one
-// per 16-weight half of a block), 4*NW scale-accumulate warps. One stage = one super-block (eight MMA pairs); two accumulator pairs
+// per eight packed bytes of a block), 4*NW scale-accumulate warps. One stage = one super-block (eight MMA pairs); two accumulator pairs
 // (2 x 2 x 128 columns = all 512 tensor-memory columns) let the MMAs of super-block s+1 run
 // while s is scaled. Every mbarrier wait is bounded.
 #include <cuda.h>
@@ -54,8 +57,7 @@ constexpr int A_SLOT = 2 * OPER_BYTES;                    // hi limb, lo limb
 constexpr int RAW_OFF = 0;
 constexpr int ACT_OFF = RAW_OFF + NRAW * RAW_STAGE;
 constexpr int A_OFF = ACT_OFF + NACT * ACT_CHUNK;
-constexpr int TAB_OFF = A_OFF + NA * A_SLOT;              // [64 ls][hi 16 B | lo 16 B]
-constexpr int BAR_OFF = TAB_OFF + 64 * 32;
+constexpr int BAR_OFF = A_OFF + NA * A_SLOT;
 constexpr int SMEM_TOTAL = BAR_OFF + 8 * 64;
 static_assert(SMEM_TOTAL <= 227 * 1024, "shared memory budget");
 
@@ -65,6 +67,16 @@ constexpr int GB = 4;                                     // blocks per A-ring g
 constexpr int NG = NA / GB;                               // groups in the ring
 enum { BAR_RAW_FULL = 0, BAR_RAW_EMPTY = 2, BAR_ACT_FULL = 4, BAR_ACT_EMPTY = 6, BAR_A_FULL = 8, BAR_A_EMPTY = 10,
        BAR_ACC_FULL = 12, BAR_ACC_EMPTY = 14, BAR_COUNT = 16 };
+
+#ifdef B200Q_TC_PROF
+#define PROF_DECL long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_t0_ = clock64();
+#define WAITP(slot, b, par) ([&]() { const long long t_ = clock64(); const bool r_ = mbar_wait_warp(b, par, abortp); prof_[slot] += clock64() - t_; return r_; }())
+#define PROF_DUMP(role) if (lane == 0 && blockIdx.x == 1 && blockIdx.y == 3) printf("%s warp %2d total %lld waits: rawF %lld rawE %lld actF %lld actE %lld aF %lld aE %lld accF %lld accE %lld\n", role, warp, clock64() - prof_t0_, prof_[0], prof_[1], prof_[2], prof_[3], prof_[4], prof_[5], prof_[6], prof_[7]);
+#else
+#define PROF_DECL
+#define WAITP(slot, b, par) mbar_wait_warp(b, par, abortp)
+#define PROF_DUMP(role)
+#endif
 
 // D (+)= A x B^T with the accumulate flag as an operand
 __device__ __forceinline__ void umma_i8_acc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
@@ -132,30 +144,23 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
     const int valid_rows = min(BM, M - row0);
 
-    // the limb tables: for every sub-scale ls the 16 codebook entries times (ls - 32), hi and lo bytes
-    for (int i = threadIdx.x; i < 64 * 16; i += THREADS) {
-        int hi, lo;
-        iq4xs_limbs(i >> 4, i & 15, &hi, &lo);
-        smem[TAB_OFF + (i >> 4) * 32 + (i & 15)] = (uint8_t)hi;
-        smem[TAB_OFF + (i >> 4) * 32 + 16 + (i & 15)] = (uint8_t)lo;
-    }
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int i = 0; i < NRAW; ++i) {
             mbar_init(bar(BAR_RAW_FULL + i), 1);
-            mbar_init(bar(BAR_RAW_EMPTY + i), 256 + 128 * NW);     // unpack threads + scaling threads (d_w)
+            mbar_init(bar(BAR_RAW_EMPTY + i), 8 + 4 * NW);          // unpack warps + scaling warps (d_w)
         }
         for (int i = 0; i < NACT; ++i) {
             mbar_init(bar(BAR_ACT_FULL + i), 1);
-            mbar_init(bar(BAR_ACT_EMPTY + i), 1 + 128 * NW);       // MMA commit + scaling threads (d_x)
+            mbar_init(bar(BAR_ACT_EMPTY + i), 1 + 4 * NW);         // MMA commit + scaling warps (d_x)
         }
         for (int i = 0; i < NG; ++i) {
-            mbar_init(bar(BAR_A_FULL + i), 256);
+            mbar_init(bar(BAR_A_FULL + i), 8);                     // unpack warps
             mbar_init(bar(BAR_A_EMPTY + i), 1);
         }
         for (int i = 0; i < NBUF; ++i) {
             mbar_init(bar(BAR_ACC_FULL + i), 1);
-            mbar_init(bar(BAR_ACC_EMPTY + i), 128 * NW);
+            mbar_init(bar(BAR_ACC_EMPTY + i), 4 * NW);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -169,6 +174,7 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int *abortp = &abort_flag;
+    PROF_DECL
 
     if (warp == 0) {
         // ---- producer ----
@@ -178,7 +184,7 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
         for (int s = 0; s < nsb; ++s) {
             if ((s & 1) == 0) {
                 const int rs = s >> 1, st = rs % NRAW;
-                if (!mbar_wait_warp(bar(BAR_RAW_EMPTY + st), ((rs / NRAW) & 1) ^ 1, abortp)) break;
+                if (!WAITP(1, bar(BAR_RAW_EMPTY + st), ((rs / NRAW) & 1) ^ 1)) break;
                 if (lane == 0) {
                     // the whole [128 rows x 272 B] box in one tiled copy; rows past M arrive as zeros
                     mbar_expect_tx(bar(BAR_RAW_FULL + st), RAW_STAGE);
@@ -186,7 +192,7 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
                 }
             }
             const int at = s % NACT;
-            if (!mbar_wait_warp(bar(BAR_ACT_EMPTY + at), ((s / NACT) & 1) ^ 1, abortp)) break;
+            if (!WAITP(3, bar(BAR_ACT_EMPTY + at), ((s / NACT) & 1) ^ 1)) break;
             if (lane == 0) {
                 mbar_expect_tx(bar(BAR_ACT_FULL + at), ACT_CHUNK);
                 bulk_g2s(sbase + ACT_OFF + at * ACT_CHUNK, act_tile + (size_t)s * ACT_CHUNK, ACT_CHUNK, bar(BAR_ACT_FULL + at));
@@ -199,11 +205,11 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
         bool ok = true;
         for (int s = 0; s < nsb && ok; ++s) {
             const int at = s % NACT, buf = s % NBUF;
-            if (!mbar_wait_warp(bar(BAR_ACT_FULL + at), (s / NACT) & 1, abortp)) break;
-            if (!mbar_wait_warp(bar(BAR_ACC_EMPTY + buf), ((s / NBUF) & 1) ^ 1, abortp)) break;
+            if (!WAITP(2, bar(BAR_ACT_FULL + at), (s / NACT) & 1)) break;
+            if (!WAITP(7, bar(BAR_ACC_EMPTY + buf), ((s / NBUF) & 1) ^ 1)) break;
             for (int jg = 0; jg < SB / GB; ++jg) {
                 const int g = s * (SB / GB) + jg, gs = g % NG;          // group index, its place in the ring
-                if (!mbar_wait_warp(bar(BAR_A_FULL + gs), (g / NG) & 1, abortp)) { ok = false; break; }
+                if (!WAITP(4, bar(BAR_A_FULL + gs), (g / NG) & 1)) { ok = false; break; }
                 tc_fence_after();
                 if (lane == 0) {
                     const uint32_t d = tmem_base + (uint32_t)buf * (2 * BN);
@@ -228,12 +234,14 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
     } else if (warp < 12) {
         // ---- unpack: two threads per weight row, one per 16-weight half of every block ----
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
-        const int r = ((warp - 4) & 3) * 32 + lane, kh = (warp - 4) >> 2;      // row of the tile, half of K inside a block
+        // A half-warp holds eight rows times the two halves, so that the two threads of a row read
+        // the same shared-memory words (one broadcast) and rows 272 bytes apart fall on distinct banks.
+        const int r = (warp - 4) * 16 + (lane >> 4) * 8 + (lane & 7), kh = (lane >> 3) & 1;
         const bool row_ok = r < valid_rows;
         bool ok = true;
         for (int rs = 0; rs < nsb / 2 && ok; ++rs) {
             const int st = rs % NRAW;
-            if (!mbar_wait_warp(bar(BAR_RAW_FULL + st), (rs / NRAW) & 1, abortp)) break;
+            if (!WAITP(0, bar(BAR_RAW_FULL + st), (rs / NRAW) & 1)) break;
             const uint8_t *rowp = smem + RAW_OFF + st * RAW_STAGE + r * ROWB;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -242,34 +250,29 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
 #pragma unroll
                 for (int jg = 0; jg < SB / GB; ++jg) {
                     const int g = (2 * rs + h) * (SB / GB) + jg, gs = g % NG;
-                    if (!mbar_wait_warp(bar(BAR_A_EMPTY + gs), ((g / NG) & 1) ^ 1, abortp)) { ok = false; break; }
+                    if (!WAITP(5, bar(BAR_A_EMPTY + gs), ((g / NG) & 1) ^ 1)) { ok = false; break; }
 #pragma unroll
                     for (int jj = 0; jj < GB; ++jj) {
                         const int j = jg * GB + jj, slot = gs * GB + jj;
-                        const int ls = row_ok ? iq4xs_ls(scales_h, scales_l, j) : 32;        // 32: factor zero
-                        const uint4 th = *reinterpret_cast<const uint4 *>(smem + TAB_OFF + ls * 32);
-                        const uint4 tl = *reinterpret_cast<const uint4 *>(smem + TAB_OFF + ls * 32 + 16);
-                        const uint2 q01 = *reinterpret_cast<const uint2 *>(rowp + SBB * h + 8 + 16 * j);
-                        const uint2 q23 = *reinterpret_cast<const uint2 *>(rowp + SBB * h + 16 + 16 * j);
-                        const uint32_t q[4] = { q01.x, q01.y, q23.x, q23.y };
-                        uint32_t ah[4], al[4];           // this thread's 16 weights: 16 kh .. 16 kh + 15 of the block
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint32_t sel, msk;
-                            lookup4_prepare((kh ? q[i] >> 4 : q[i]) & 0x0F0F0F0Fu, &sel, &msk);
-                            ah[i] = lookup4_apply(th.x, th.y, th.z, th.w, sel, msk);
-                            al[i] = lookup4_apply(tl.x, tl.y, tl.z, tl.w, sel, msk);
-                        }
-                        uint8_t *a = smem + A_OFF + slot * A_SLOT + kh * LBO + (r >> 3) * 128 + (r & 7) * 16;
-                        *reinterpret_cast<uint4 *>(a) = make_uint4(ah[0], ah[1], ah[2], ah[3]);
-                        *reinterpret_cast<uint4 *>(a + OPER_BYTES) = make_uint4(al[0], al[1], al[2], al[3]);
+                        const int m = row_ok ? iq4xs_ls(scales_h, scales_l, j) - 32 : 0;     // 0: every limb zero
+                        // this thread's packed bytes 8 kh .. 8 kh + 7 of the block: weights 8 kh .. + 7 in the
+                        // low nibbles (first 16-byte half of K) and 16 + 8 kh .. in the high ones (second half)
+                        const uint2 qq = *reinterpret_cast<const uint2 *>(rowp + SBB * h + 8 + 16 * j + 8 * kh);
+                        uint32_t hl[2], ll[2], hh[2], lh[2];
+                        iq4xs_limbs8(qq.x, m, &hl[0], &ll[0], &hh[0], &lh[0]);
+                        iq4xs_limbs8(qq.y, m, &hl[1], &ll[1], &hh[1], &lh[1]);
+                        uint8_t *a = smem + A_OFF + slot * A_SLOT + (r >> 3) * 128 + (r & 7) * 16 + 8 * kh;
+                        *reinterpret_cast<uint2 *>(a) = make_uint2(hl[0], hl[1]);
+                        *reinterpret_cast<uint2 *>(a + LBO) = make_uint2(hh[0], hh[1]);
+                        *reinterpret_cast<uint2 *>(a + OPER_BYTES) = make_uint2(ll[0], ll[1]);
+                        *reinterpret_cast<uint2 *>(a + OPER_BYTES + LBO) = make_uint2(lh[0], lh[1]);
                     }
                     fence_async_smem();                  // one proxy fence per group of blocks
-                    mbar_arrive(bar(BAR_A_FULL + gs));
+                    mbar_arrive_warp(bar(BAR_A_FULL + gs), lane);
                 }
                 if (!ok) break;
             }
-            if (ok) mbar_arrive(bar(BAR_RAW_EMPTY + st));
+            if (ok) mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
         }
     } else {
         // ---- scale-accumulate, once per super-block ----
@@ -285,13 +288,13 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
         for (int s = 0; s < nsb; ++s) {
             const int rs = s >> 1, st = rs % NRAW, at = s % NACT, buf = s % NBUF;
             // stage barriers cannot advance past this thread: it releases both stages itself
-            if ((s & 1) == 0 && !mbar_wait_warp(bar(BAR_RAW_FULL + st), (rs / NRAW) & 1, abortp)) break;
-            if (!mbar_wait_warp(bar(BAR_ACT_FULL + at), (s / NACT) & 1, abortp)) break;
-            if (!mbar_wait_warp(bar(BAR_ACC_FULL + buf), (s / NBUF) & 1, abortp)) break;
+            if ((s & 1) == 0 && !WAITP(0, bar(BAR_RAW_FULL + st), (rs / NRAW) & 1)) break;
+            if (!WAITP(2, bar(BAR_ACT_FULL + at), (s / NACT) & 1)) break;
+            if (!WAITP(6, bar(BAR_ACC_FULL + buf), (s / NBUF) & 1)) break;
             tc_fence_after();
             const float dwb = row_ok ? half_bits_to_float(*reinterpret_cast<const uint16_t *>(
                                            smem + RAW_OFF + st * RAW_STAGE + r * ROWB + SBB * (s & 1))) : 0.f;
-            const f32x2 dw2 = f2_pack(dwb, dwb), negc2 = f2_pack(-12582912.f, -12582912.f), k64 = f2_pack(64.f, 64.f);
+            const f32x2 dw2 = f2_pack(dwb, dwb), negc2 = f2_pack(-12582912.f, -12582912.f), k256 = f2_pack(256.f, 256.f);
             const uint32_t dxa = sbase + ACT_OFF + at * ACT_CHUNK + SB * OPER_BYTES + (u * CW) * 4;
             const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * (2 * BN) + (uint32_t)u * CW;
 #pragma unroll
@@ -302,24 +305,24 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
                 tmem_ld_wait();
                 if (q == CW / 16 - 1) {
                     tc_fence_before();
-                    mbar_arrive(bar(BAR_ACC_EMPTY + buf));
+                    mbar_arrive_warp(bar(BAR_ACC_EMPTY + buf), lane);
                 }
 #pragma unroll
                 for (int c = 0; c < 16; c += 4) {
                     f32x2 d01, d23;
                     lds128_f2(dxa + (q * 16 + c) * 4, d01, d23);
                     const int e = (q * 16 + c) / 2;
-                    // exact int -> float of each limb sum (both below 2^22 in magnitude), then 64 hi + lo
+                    // exact int -> float of each limb sum (both below 2^22 in magnitude), then 256 hi + lo
                     const f32x2 h01 = f2_add(f2_pack(__int_as_float((int)vh[c] + 0x4B400000), __int_as_float((int)vh[c + 1] + 0x4B400000)), negc2);
                     const f32x2 h23 = f2_add(f2_pack(__int_as_float((int)vh[c + 2] + 0x4B400000), __int_as_float((int)vh[c + 3] + 0x4B400000)), negc2);
                     const f32x2 l01 = f2_add(f2_pack(__int_as_float((int)vl[c] + 0x4B400000), __int_as_float((int)vl[c + 1] + 0x4B400000)), negc2);
                     const f32x2 l23 = f2_add(f2_pack(__int_as_float((int)vl[c + 2] + 0x4B400000), __int_as_float((int)vl[c + 3] + 0x4B400000)), negc2);
-                    acc2[e]     = f2_fma(f2_fma(h01, k64, l01), f2_mul(dw2, d01), acc2[e]);
-                    acc2[e + 1] = f2_fma(f2_fma(h23, k64, l23), f2_mul(dw2, d23), acc2[e + 1]);
+                    acc2[e]     = f2_fma(f2_fma(h01, k256, l01), f2_mul(dw2, d01), acc2[e]);
+                    acc2[e + 1] = f2_fma(f2_fma(h23, k256, l23), f2_mul(dw2, d23), acc2[e + 1]);
                 }
             }
-            mbar_arrive(bar(BAR_ACT_EMPTY + at));
-            if (s & 1) mbar_arrive(bar(BAR_RAW_EMPTY + st));
+            mbar_arrive_warp(bar(BAR_ACT_EMPTY + at), lane);
+            if (s & 1) mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
             done = s == nsb - 1;
         }
         if (done && row_ok) {
@@ -337,6 +340,7 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
         }
     }
 
+    PROF_DUMP(warp == 0 ? "prod" : warp == 1 ? "mma " : warp < 4 ? "idle" : warp < 12 ? "unpk" : "epi ")
     tc_fence_before();
     __syncthreads();
     if (abort_flag) {

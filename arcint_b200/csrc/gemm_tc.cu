@@ -148,17 +148,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         abort_flag = 0;
         for (int i = 0; i < NSTAGE; ++i) {
             mbar_init(bar(BAR_RAW_FULL + i), 1);
-            mbar_init(bar(BAR_RAW_EMPTY + i), 128 + 128 * NW);  // unpack threads + scaling threads (block scales)
+            mbar_init(bar(BAR_RAW_EMPTY + i), 4 + 4 * NW);      // unpack warps + scaling warps (block scales)
             mbar_init(bar(BAR_ACT_FULL + i), 1);
-            mbar_init(bar(BAR_ACT_EMPTY + i), 1 + 128 * NW);   // MMA commit + every scaling thread
+            mbar_init(bar(BAR_ACT_EMPTY + i), 1 + 4 * NW);     // MMA commit + every scaling warp
         }
         for (int i = 0; i < SB; ++i) {
-            mbar_init(bar(BAR_A_FULL + i), 128);
+            mbar_init(bar(BAR_A_FULL + i), 4);                  // unpack warps
             mbar_init(bar(BAR_A_EMPTY + i), 1);
         }
         for (int i = 0; i < NACC; ++i) {
             mbar_init(bar(BAR_ACC_FULL + i), 1);
-            mbar_init(bar(BAR_ACC_EMPTY + i), 128 * NW);
+            mbar_init(bar(BAR_ACC_EMPTY + i), 4 * NW);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -236,7 +236,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 rw[4 * i] = t.x; rw[4 * i + 1] = t.y; rw[4 * i + 2] = t.z; rw[4 * i + 3] = t.w;
             }
             rw[ROWB / 4] = 0;
-            mbar_arrive(bar(BAR_RAW_EMPTY + st));
+            mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
 #pragma unroll
             for (int j = 0; j < SB; ++j) {
                 const int b = s * SB + j;
@@ -261,7 +261,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 *reinterpret_cast<uint4 *>(a) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 *reinterpret_cast<uint4 *>(a + LBO) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                 fence_async_smem();
-                mbar_arrive(bar(BAR_A_FULL + j));
+                mbar_arrive_warp(bar(BAR_A_FULL + j), lane);
             }
         }
     } else {
@@ -300,7 +300,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                     tmem_ld16(taddr + (q + 1) * 16, v[(q + 1) & 1]);
                 } else {
                     tc_fence_before();
-                    mbar_arrive(bar(BAR_ACC_EMPTY + acc));     // the accumulator is in registers: free it
+                    mbar_arrive_warp(bar(BAR_ACC_EMPTY + acc), lane);     // the accumulator is in registers: free it
                 }
 #pragma unroll
                 for (int c = 0; c < 16; c += 4) {
@@ -318,8 +318,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 }
             }
             if (j == SB - 1) {                                         // done with this stage's scales
-                mbar_arrive(bar(BAR_ACT_EMPTY + st));
-                mbar_arrive(bar(BAR_RAW_EMPTY + st));
+                mbar_arrive_warp(bar(BAR_ACT_EMPTY + st), lane);
+                mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
             }
             done = b == nblk - 1;
         }

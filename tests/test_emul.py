@@ -50,28 +50,34 @@ def test_bit_tricks_exhaustive_per_byte():
         assert [((got >> (8 * i)) & 0xFF) for i in range(4)] == [(((t >> (8 * i)) & 0x3F) - 32) & 0xFF for i in range(4)]
 
 
-def test_iq4xs_two_limb_tables():
-    """The tensor-core IQ4_XS path folds (ls - 32) * kvalues[n] into two int8 limbs and looks them up
-    with byte permutes: every (ls, n) must satisfy 64 hi + lo = product with both limbs in int8."""
+def test_iq4xs_two_limbs():
+    """The tensor-core IQ4_XS path folds (ls - 32) * kvalues[n] into two int8 limbs, computed eight
+    weights (one packed word) at a time in registers (biased lookup, one multiply-add per pair of
+    16-bit halves): every (ls, n) must satisfy 256 hi + lo = product with both limbs in int8, and
+    the packed form must agree with the scalar one for low and high nibbles."""
     E = emul()
+    E.emul_iq4xs_limbs8.argtypes = [C.c_uint32, C.c_int, C.POINTER(C.c_uint32)]
     rng = np.random.default_rng(0)
     for ls in range(64):
         his, los = [], []
         for n in range(16):
             hi, lo = C.c_int(), C.c_int()
             E.emul_iq4xs_limbs(ls, n, C.byref(hi), C.byref(lo))
-            assert 64 * hi.value + lo.value == (ls - 32) * int(O.KVALUES_IQ4NL[n])
-            assert -32 <= lo.value <= 31 and -64 <= hi.value <= 64
+            assert 256 * hi.value + lo.value == (ls - 32) * int(O.KVALUES_IQ4NL[n])
+            assert -128 <= lo.value <= 127 and -16 <= hi.value <= 16
             his.append(hi.value & 0xFF)
             los.append(lo.value & 0xFF)
-        for tab in (his, los):
-            words = np.frombuffer(bytes(tab), dtype=np.uint32).copy()
-            for _ in range(8):
-                idx4 = rng.integers(0, 16, 4)
-                idx = int(idx4[0] | (idx4[1] << 8) | (idx4[2] << 16) | (idx4[3] << 24))
-                got = E.emul_lookup4_tab(words.ctypes.data, idx)
-                want = sum(tab[int(i)] << (8 * b) for b, i in enumerate(idx4))
-                assert got == want
+        words = [0x10325476, 0x98BADCFE, 0x00000000, 0xFFFFFFFF, 0x88888888, 0x77777777] + \
+                [int(x) for x in rng.integers(0, 1 << 32, 10, dtype=np.uint64)]
+        for q in words:
+            out = (C.c_uint32 * 4)()
+            E.emul_iq4xs_limbs8(q, ls - 32, out)
+            low = [(q >> (8 * b)) & 0xF for b in range(4)]
+            high = [(q >> (8 * b + 4)) & 0xF for b in range(4)]
+            assert out[0] == sum(his[i] << (8 * b) for b, i in enumerate(low))
+            assert out[1] == sum(los[i] << (8 * b) for b, i in enumerate(low))
+            assert out[2] == sum(his[i] << (8 * b) for b, i in enumerate(high))
+            assert out[3] == sum(los[i] << (8 * b) for b, i in enumerate(high))
 
 
 @pytest.mark.parametrize("name,t", [("q4_0", O.Q4_0), ("q8_0", O.Q8_0), ("q4_K", O.Q4_K), ("q6_K", O.Q6_K), ("iq4_xs", O.IQ4_XS)])
