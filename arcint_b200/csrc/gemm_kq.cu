@@ -68,16 +68,6 @@ constexpr int NG = NA / GB;                               // groups in the ring
 enum { BAR_RAW_FULL = 0, BAR_RAW_EMPTY = 2, BAR_ACT_FULL = 4, BAR_ACT_EMPTY = 6, BAR_A_FULL = 8, BAR_A_EMPTY = 10,
        BAR_ACC_FULL = 12, BAR_ACC_EMPTY = 14, BAR_COUNT = 16 };
 
-#ifdef B200Q_TC_PROF
-#define PROF_DECL long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_t0_ = clock64();
-#define WAITP(slot, b, par) ([&]() { const long long t_ = clock64(); const bool r_ = mbar_wait_warp(b, par, abortp); prof_[slot] += clock64() - t_; return r_; }())
-#define PROF_DUMP(role) if (lane == 0 && blockIdx.x == 1 && blockIdx.y == 3) printf("%s warp %2d total %lld waits: rawF %lld rawE %lld actF %lld actE %lld aF %lld aE %lld accF %lld accE %lld\n", role, warp, clock64() - prof_t0_, prof_[0], prof_[1], prof_[2], prof_[3], prof_[4], prof_[5], prof_[6], prof_[7]);
-#else
-#define PROF_DECL
-#define WAITP(slot, b, par) mbar_wait_warp(b, par, abortp)
-#define PROF_DUMP(role)
-#endif
-
 // D (+)= A x B^T with the accumulate flag as an operand
 __device__ __forceinline__ void umma_i8_acc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -302,6 +292,9 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
                 uint32_t vh[16], vl[16];
                 tmem_ld16(taddr + q * 16, vh);
                 tmem_ld16(taddr + BN + q * 16, vl);
+                f32x2 dx[8];                             // sixteen activation scales, in flight under the tensor-memory loads
+#pragma unroll
+                for (int c = 0; c < 4; ++c) lds128_f2(dxa + (q * 16 + 4 * c) * 4, dx[2 * c], dx[2 * c + 1]);
                 tmem_ld_wait();
                 if (q == CW / 16 - 1) {
                     tc_fence_before();
@@ -309,16 +302,12 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
                 }
 #pragma unroll
                 for (int c = 0; c < 16; c += 4) {
-                    f32x2 d01, d23;
-                    lds128_f2(dxa + (q * 16 + c) * 4, d01, d23);
                     const int e = (q * 16 + c) / 2;
-                    // exact int -> float of each limb sum (both below 2^22 in magnitude), then 256 hi + lo
-                    const f32x2 h01 = f2_add(f2_pack(__int_as_float((int)vh[c] + 0x4B400000), __int_as_float((int)vh[c + 1] + 0x4B400000)), negc2);
-                    const f32x2 h23 = f2_add(f2_pack(__int_as_float((int)vh[c + 2] + 0x4B400000), __int_as_float((int)vh[c + 3] + 0x4B400000)), negc2);
-                    const f32x2 l01 = f2_add(f2_pack(__int_as_float((int)vl[c] + 0x4B400000), __int_as_float((int)vl[c + 1] + 0x4B400000)), negc2);
-                    const f32x2 l23 = f2_add(f2_pack(__int_as_float((int)vl[c + 2] + 0x4B400000), __int_as_float((int)vl[c + 3] + 0x4B400000)), negc2);
-                    acc2[e]     = f2_fma(f2_fma(h01, k256, l01), f2_mul(dw2, d01), acc2[e]);
-                    acc2[e + 1] = f2_fma(f2_fma(h23, k256, l23), f2_mul(dw2, d23), acc2[e + 1]);
+                    // 256 hi + lo as an integer, one rounding to float (ggml's float(sumi))
+                    const f32x2 s01 = f2_pack(__int2float_rn((int)vl[c] + ((int)vh[c] << 8)), __int2float_rn((int)vl[c + 1] + ((int)vh[c + 1] << 8)));
+                    const f32x2 s23 = f2_pack(__int2float_rn((int)vl[c + 2] + ((int)vh[c + 2] << 8)), __int2float_rn((int)vl[c + 3] + ((int)vh[c + 3] << 8)));
+                    acc2[e]     = f2_fma(s01, f2_mul(dw2, dx[c / 2]), acc2[e]);
+                    acc2[e + 1] = f2_fma(s23, f2_mul(dw2, dx[c / 2 + 1]), acc2[e + 1]);
                 }
             }
             mbar_arrive_warp(bar(BAR_ACT_EMPTY + at), lane);

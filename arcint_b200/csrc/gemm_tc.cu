@@ -172,6 +172,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int *abortp = &abort_flag;
+    PROF_DECL
 
     // Register budget by role (the launch gives every thread 65536/THREADS registers): each
     // branch below starts by resizing its warp group's share -- the first two groups hand most
@@ -184,13 +185,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         for (int s = 0; s < nst; ++s) {
             const int st = s % NSTAGE;
             const uint32_t par = ((s / NSTAGE) & 1) ^ 1;        // first pass over the ring: slots are free
-            if (!mbar_wait_warp(bar(BAR_RAW_EMPTY + st), par, abortp)) break;
+            if (!WAITP(1, bar(BAR_RAW_EMPTY + st), par)) break;
             if (lane == 0) {
                 // the stage's [128 rows x ROWB] box in one tiled copy; rows past M arrive as zeros
                 mbar_expect_tx(bar(BAR_RAW_FULL + st), L::RAW_STAGE);
                 tma_load_2d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, s * (ROWB / 4), row0, bar(BAR_RAW_FULL + st));
             }
-            if (!mbar_wait_warp(bar(BAR_ACT_EMPTY + st), par, abortp)) break;
+            if (!WAITP(3, bar(BAR_ACT_EMPTY + st), par)) break;
             if (lane == 0) {
                 mbar_expect_tx(bar(BAR_ACT_FULL + st), ACT_CHUNK);
                 bulk_g2s(sbase + L::ACT_OFF + st * ACT_CHUNK, act_tile + (size_t)s * ACT_CHUNK, ACT_CHUNK,
@@ -203,9 +204,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
         for (int b = 0; b < nblk; ++b) {
             const int s = b / SB, j = b % SB, st = s % NSTAGE, acc = b % NACC;
-            if (j == 0 && !mbar_wait_warp(bar(BAR_ACT_FULL + st), (s / NSTAGE) & 1, abortp)) break;
-            if (!mbar_wait_warp(bar(BAR_A_FULL + j), (b / SB) & 1, abortp)) break;
-            if (!mbar_wait_warp(bar(BAR_ACC_EMPTY + acc), ((b / NACC) & 1) ^ 1, abortp)) break;
+            if (j == 0 && !WAITP(2, bar(BAR_ACT_FULL + st), (s / NSTAGE) & 1)) break;
+            if (!WAITP(4, bar(BAR_A_FULL + j), (b / SB) & 1)) break;
+            if (!WAITP(7, bar(BAR_ACC_EMPTY + acc), ((b / NACC) & 1) ^ 1)) break;
             tc_fence_after();
             if (lane == 0) {
                 umma_i8(tmem_base + (uint32_t)acc * BN, umma_desc(sbase + L::A_OFF + j * OPER_BYTES),
@@ -227,7 +228,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         bool ok = true;
         for (int s = 0; s < nst && ok; ++s) {
             const int st = s % NSTAGE;
-            if (!mbar_wait_warp(bar(BAR_RAW_FULL + st), (s / NSTAGE) & 1, abortp)) break;
+            if (!WAITP(0, bar(BAR_RAW_FULL + st), (s / NSTAGE) & 1)) break;
             uint32_t rw[ROWB / 4 + 1];                     // the row's packed bytes of this stage
             const uint4 *rp = reinterpret_cast<const uint4 *>(smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB);
 #pragma unroll
@@ -240,7 +241,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
 #pragma unroll
             for (int j = 0; j < SB; ++j) {
                 const int b = s * SB + j;
-                if (!mbar_wait_warp(bar(BAR_A_EMPTY + j), ((b / SB) & 1) ^ 1, abortp)) { ok = false; break; }
+                if (!WAITP(5, bar(BAR_A_EMPTY + j), ((b / SB) & 1) ^ 1)) { ok = false; break; }
                 constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
                 uint32_t lo[4], hi[4];
                 if (TYPE == B200Q_TYPE_Q4_0) {
@@ -279,9 +280,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             const int s = b / SB, j = b % SB, st = s % NSTAGE, acc = b % NACC;
             // A waiter on an mbarrier phase must see it before the phase after it completes:
             // both stage barriers below cannot advance until this thread has released the stage.
-            if (j == 0 && !mbar_wait_warp(bar(BAR_ACT_FULL + st), (s / NSTAGE) & 1, abortp)) break;
-            if (j == 0 && !mbar_wait_warp(bar(BAR_RAW_FULL + st), (s / NSTAGE) & 1, abortp)) break;
-            if (!mbar_wait_warp(bar(BAR_ACC_FULL + acc), (b / NACC) & 1, abortp)) break;
+            if (j == 0 && !WAITP(2, bar(BAR_ACT_FULL + st), (s / NSTAGE) & 1)) break;
+            if (j == 0 && !WAITP(0, bar(BAR_RAW_FULL + st), (s / NSTAGE) & 1)) break;
+            if (!WAITP(6, bar(BAR_ACC_FULL + acc), (b / NACC) & 1)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)acc * BN + (uint32_t)u * CW;
             // the block's fp16 weight scale, straight from the packed row in the raw stage
@@ -295,6 +296,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             tmem_ld16(taddr, v[0]);
 #pragma unroll
             for (int q = 0; q < CW / 16; ++q) {
+                // the sixteen activation scales: four loads in flight together, under the wait for the
+                // tensor-memory load
+                f32x2 dx[8];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) lds128_f2(dxa + (q * 16 + 4 * c) * 4, dx[2 * c], dx[2 * c + 1]);
                 tmem_ld_wait();
                 if (q + 1 < CW / 16) {
                     tmem_ld16(taddr + (q + 1) * 16, v[(q + 1) & 1]);
@@ -304,8 +310,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 }
 #pragma unroll
                 for (int c = 0; c < 16; c += 4) {
-                    f32x2 d01, d23;
-                    lds128_f2(dxa + (q * 16 + c) * 4, d01, d23);
                     const int e = (q * 16 + c) / 2;
                     // exact int -> float without the conversion pipe (|I| < 2^22): add the
                     // magic exponent as an integer, subtract it as a float
@@ -313,8 +317,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                                                      __int_as_float((int)v[q & 1][c + 1] + 0x4B400000)), negc2);
                     const f32x2 x23 = f2_add(f2_pack(__int_as_float((int)v[q & 1][c + 2] + 0x4B400000),
                                                      __int_as_float((int)v[q & 1][c + 3] + 0x4B400000)), negc2);
-                    acc2[e]     = f2_fma(x01, f2_mul(dw2, d01), acc2[e]);
-                    acc2[e + 1] = f2_fma(x23, f2_mul(dw2, d23), acc2[e + 1]);
+                    acc2[e]     = f2_fma(x01, f2_mul(dw2, dx[c / 2]), acc2[e]);
+                    acc2[e + 1] = f2_fma(x23, f2_mul(dw2, dx[c / 2 + 1]), acc2[e + 1]);
                 }
             }
             if (j == SB - 1) {                                         // done with this stage's scales
@@ -338,6 +342,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         }
     }
 
+    PROF_DUMP(warp == 0 ? "prod" : warp == 1 ? "mma " : warp < 4 ? "idle" : warp < 8 ? "unpk" : "epi ")
     tc_fence_before();
     __syncthreads();
     if (abort_flag) {

@@ -137,5 +137,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Optional self-profile (compile with -DB200Q_TC_PROF): every role adds up the clocks it spends in
+// each kind of barrier wait and one block prints them when it ends -- who waits for whom.
+#ifdef B200Q_TC_PROF
+#define PROF_DECL long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_t0_ = clock64();
+#define WAITP(slot, b, par) ([&]() { const long long t_ = clock64(); const bool r_ = mbar_wait_warp(b, par, abortp); prof_[slot] += clock64() - t_; return r_; }())
+#define PROF_DUMP(role) if (lane == 0 && blockIdx.x == 1 && blockIdx.y == 1) printf("%s warp %2d total %lld waits: rawF %lld rawE %lld actF %lld actE %lld aF %lld aE %lld accF %lld accE %lld\n", role, warp, clock64() - prof_t0_, prof_[0], prof_[1], prof_[2], prof_[3], prof_[4], prof_[5], prof_[6], prof_[7]);
+#else
+#define PROF_DECL
+#define WAITP(slot, b, par) mbar_wait_warp(b, par, abortp)
+#define PROF_DUMP(role)
+#endif
+
 }  // namespace tc
 }  // namespace b200q
