@@ -135,15 +135,21 @@ def prefill_section(ctx, world, rank, dist):
     # the int8 tensor pipe runs at twice the bf16 rate; MEASURED_PEAKS has the bf16 number
     peak_tops = 2.0 * float(peaks.get("bf16_tflops", 1590.0))
     peak_src = "2 x measured bf16 burst (MEASURED_PEAKS.json)" if peaks else "2 x fallback bf16 1.59 PF"
+    tag = " column-split" if world > 1 else ""
     cases = [("config1 q4_0 4096x4096 x 512", A.Q4_0, 4096, 4096, 512, False),
-             ("config3 q8_0 12288x3072 x 4096%s" % (" column-split" if world > 1 else ""), A.Q8_0, 12288, 3072, 4096, True)]
+             ("config3 q8_0 3072x3072 x 4096" + tag, A.Q8_0, 3072, 3072, 4096, True),
+             ("config3 q8_0 12288x3072 x 4096" + tag, A.Q8_0, 12288, 3072, 4096, True),
+             ("config3 iq4_xs 17408x5120 x 512" + tag, A.IQ4_XS, 17408, 5120, 512, True),
+             ("config3 iq4_xs 5120x17408 x 512" + tag, A.IQ4_XS, 5120, 17408, 512, True),
+             ("config3 iq4_xs 17408x5120 x 2048" + tag, A.IQ4_XS, 17408, 5120, 2048, True),
+             ("config3 iq4_xs 5120x17408 x 2048" + tag, A.IQ4_XS, 5120, 17408, 2048, True)]
     out = []
     for name, t, m, k, n, split in cases:
         if world > 1 and not split:
             continue
         r0, rc = A.tp_shard(m, 1, world, rank) if split else (0, m)
-        base = O.quantize(t, O.fill_normal(512 * k, 0x5EED0300 + t, 0.02).reshape(512, k))
-        w = np.tile(base, (-(-rc // 512), 1))[:rc]
+        base = O.quantize(t, O.fill_normal(256 * k, 0x5EED0300 + t, 0.02).reshape(256, k))
+        w = np.tile(base, (-(-rc // 256), 1))[:rc]
         x = O.fill_normal(256 * k, 0x5EED0400, 1.0).reshape(256, k)
         x = np.tile(x, (-(-n // 256), 1))[:n]
         dw, dx, dy = ctx.upload(w), ctx.upload(x), ctx.alloc(n * rc * 4)
@@ -187,6 +193,193 @@ def prefill_section(ctx, world, rank, dist):
     return out
 
 
+def _max_over_ranks(ms, dist):
+    if dist:
+        import torch
+        tt = torch.tensor([ms], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    return ms
+
+
+def tp_trace_section(ctx, world, rank, dist):
+    """Config 4: the weight mat-muls of a Llama-2-7B-shaped model in Q4_0 (32 layers of q/k/v/o
+    4096x4096, gate/up 11008x4096, down 4096x11008, LM head 32000x4096), as pp512 (512-token GEMMs on
+    the tensor cores) and tg (sequential batch-1 GEMVs). Tensor parallel over the ranks: q/k/v/gate/
+    up/head split by rows (column-parallel), o/down split along K (row-parallel) with an all-reduce of
+    the f32 partial outputs. One layer's weights are generated and reused by every layer (two rotating
+    device copies: 2 x 114 MB per GPU at N=1, beyond L2); the timed region is a CUDA-graph replay of the
+    whole trace."""
+    import arcint_b200 as A
+    import oracle as O
+    t = A.Q4_0
+    shapes = [("q", 4096, 4096, "col"), ("k", 4096, 4096, "col"), ("v", 4096, 4096, "col"), ("o", 4096, 4096, "row"),
+              ("gate", 11008, 4096, "col"), ("up", 11008, 4096, "col"), ("down", 4096, 11008, "row")]
+    head = ("head", 32000, 4096, "col")
+    bs, bb = A.block_size(t), A.block_bytes(t)
+    dev = {}
+    for name, m, k, how in shapes + [head]:
+        if how == "col":
+            _, mc = A.tp_shard(m, 1, world, rank)
+            kc = k
+        else:
+            mc = m
+            _, kc = A.tp_shard(k, 256, world, rank)          # whole k-stages of the prompt GEMM per rank
+        base = O.quantize(t, O.fill_normal(256 * kc, 0x5EED0500 + len(dev), 0.02).reshape(256, kc))
+        w = np.tile(base, (-(-mc // 256), 1))[:mc]
+        copies = [ctx.upload(w)]
+        if name != "head":
+            p2 = ctx.alloc(w.nbytes)
+            ctx.copy(p2, copies[0], w.nbytes)
+            copies.append(p2)
+        dev[name] = (mc, kc, how, copies)
+    out = []
+    n_layers = 32
+    for label, n, reps in (("pp512", 512, 1), ("tg128", 1, 8)):
+        kmax = 11008
+        x = O.fill_normal(n * kmax, 0x5EED0600 + n, 1.0).reshape(n, kmax)
+        dx = ctx.upload(x)
+        dy = ctx.alloc(n * 32000 * 4)
+
+        def product(name, layer):
+            mc, kc, how, copies = dev[name]
+            ctx.graph_begin()
+            xin = A.Tensor.make(A.F32, [kc, n, 1, 1], [4, 4 * kmax], dx)
+            ctx.mul_mat(A.Tensor.weights(t, copies[layer % len(copies)], kc, mc), xin, A.Tensor.f32(dy, [mc, n]))
+            if how == "row" and world > 1:
+                ctx.all_reduce_f32(dy, n * mc)
+
+        def trace():
+            for _ in range(reps):
+                for layer in range(n_layers):
+                    for name, _, _, _ in shapes:
+                        product(name, layer)
+                product("head", 0)
+
+        for layer in range(2):
+            for name, _, _, _ in shapes:
+                product(name, layer)
+        product("head", 0)
+        ctx.sync()
+        how_run = "CUDA-graph replay"
+        g = None
+        try:
+            g = ctx.capture(trace)
+        except Exception as e:                     # a collective that cannot be captured: run the trace eagerly
+            how_run = "eager launches (capture failed: %s)" % str(e)[:60]
+        run = (lambda: ctx.graph_launch(g)) if g is not None else trace
+        run()
+        ctx.sync()
+        if dist:
+            dist.barrier()
+        ctx.timer_start()
+        for _ in range(2):
+            run()
+        ms = _max_over_ranks(ctx.timer_stop() / (2 * reps), dist)
+        if g is not None:
+            ctx.graph_free(g)
+        ops = 2.0 * n * (n_layers * sum(m * k for _, m, k, _ in shapes) + head[1] * head[2])
+        bytes_w = (n_layers * sum(m * k for _, m, k, _ in shapes) + head[1] * head[2]) // bs * bb
+        rec = {"workload": "config4 llama-2-7b q4_0 %s" % label, "tokens": n, "ms_per_pass": ms,
+               "tokens_per_s": n / (ms * 1e-3), "parallelism": "tp%d column/row split, all-reduce of row-split outputs" % world
+               if world > 1 else "single GPU", "timed": how_run + " of 32 layers x 7 mat-muls + LM head"}
+        if n > 8:
+            rec["tops"] = ops / (ms * 1e-3) / 1e12
+        else:
+            rec["weight_gbs"] = bytes_w / (ms * 1e-3) / 1e9
+        out.append(rec)
+        ctx.free(dx)
+        ctx.free(dy)
+    for mc, kc, how, copies in dev.values():
+        for ptr in copies:
+            ctx.free(ptr)
+    return out
+
+
+def moe_section(ctx, world, rank, dist):
+    """Config 5: MUL_MAT_ID over 512 Q4_K experts, top-10 routing from seeded Zipf(1.1) logits,
+    d_model 2048, expert FFN 512 (gate/up 512x2048, down 2048x512), token batches 1 and 2048. With
+    more than one rank the experts are split in contiguous ranges (512 / N per GPU), the tokens are
+    split evenly, and dispatch / combine are all-to-alls (b200q_mul_mat_id_ep). Eight distinct experts
+    are generated and tiled to 512 (the timing does not depend on the values)."""
+    import arcint_b200 as A
+    import oracle as O
+    t, n_exp, n_used, d_model, d_ff = A.Q4_K, 512, 10, 2048, 512
+    per = n_exp // world
+    mats = {}
+    for name, m, k in (("gate", d_ff, d_model), ("up", d_ff, d_model), ("down", d_model, d_ff)):
+        base = np.stack([O.quantize(t, O.fill_normal(m * k, 0x5EED0700 + 8 * len(mats) + e, 0.02).reshape(m, k)) for e in range(8)])
+        w = np.tile(base, (per // 8, 1, 1))
+        mats[name] = (m, k, base, ctx.upload(w), w.shape[-1])
+    out = []
+    for n_total in (1, 2048):
+        n_tok = max(1, n_total // world)
+        ids = O.route_ids(n_used, n_tok, n_exp, 0x5EED0800 + rank)
+        x = O.fill_normal(n_tok * d_model, 0x5EED0900 + rank, 1.0).reshape(n_tok, 1, d_model)
+        h = O.fill_normal(n_tok * n_used * d_ff, 0x5EED0A00 + rank, 1.0).reshape(n_tok, n_used, d_ff)
+        dxi, dh, di = ctx.upload(x), ctx.upload(h), ctx.upload(ids)
+        dg = ctx.alloc(n_tok * n_used * d_ff * 4)
+        dd = ctx.alloc(n_tok * n_used * d_model * 4)
+        I = A.Tensor.make(A.I32, [n_used, n_tok, 1, 1], [4, 4 * n_used], di)
+
+        def src0(name):
+            m, k, _, dw, rb = mats[name]
+            return A.Tensor.make(t, [k, m, per, 1], [A.block_bytes(t), rb, rb * m, rb * m * per], dw)
+
+        def block():
+            # gate and up read the token's activation (ne11 = 1), down reads one row per used expert
+            ctx.graph_begin()
+            for name, xin, yout, m in (("gate", A.Tensor.f32(dxi, [d_model, 1, n_tok]), dg, d_ff),
+                                       ("up", A.Tensor.f32(dxi, [d_model, 1, n_tok]), dg, d_ff),
+                                       ("down", A.Tensor.f32(dh, [d_ff, n_used, n_tok]), dd, d_model)):
+                y = A.Tensor.f32(yout, [m, n_used, n_tok])
+                if world > 1:
+                    ctx.mul_mat_id_ep(src0(name), xin, I, y, n_exp)
+                else:
+                    ctx.mul_mat_id(src0(name), xin, I, y)
+
+        block()
+        got = ctx.download(dd, (n_tok, n_used, d_model), np.float32)
+        err = None
+        if world == 1:                                    # parity of the last product on a sample of tokens
+            ts = np.arange(0, n_tok, max(1, n_tok // 4))[:4]
+            wfull = np.tile(mats["down"][2], (n_exp // 8, 1, 1))
+            ref = O.mul_mat_id(t, wfull, d_model, d_ff, h[ts], np.ascontiguousarray(ids[ts]), f64=True)
+            floor = 1e-2 * np.abs(ref).max(axis=-1, keepdims=True)
+            err = float((np.abs(got[ts] - ref) / np.maximum(np.abs(ref), floor)).max())
+        reps = 5
+        g = None
+        if world == 1:                                    # the expert-parallel call synchronizes: not capturable
+            g = ctx.capture(lambda: [block() for _ in range(reps)])
+            ctx.graph_launch(g)
+        ctx.sync()
+        if dist:
+            dist.barrier()
+        ctx.timer_start()
+        if g is not None:
+            for _ in range(3):
+                ctx.graph_launch(g)
+            ms = ctx.timer_stop() / (3 * reps)
+            ctx.graph_free(g)
+        else:
+            for _ in range(reps):
+                block()
+            ms = ctx.timer_stop() / reps
+        ms = _max_over_ranks(ms, dist)
+        tokens = n_tok * world
+        ops = 2.0 * tokens * n_used * 3 * d_ff * d_model
+        out.append({"workload": "config5 moe q4_K 512 experts top-10, %d token%s" % (tokens, "" if tokens == 1 else "s"),
+                    "ms": ms, "tokens_per_s": tokens / (ms * 1e-3), "tops": ops / (ms * 1e-3) / 1e12,
+                    "parallelism": ("ep%d: %d experts per GPU, all-to-all dispatch/combine" % (world, per)) if world > 1 else "single GPU",
+                    "parity_max_rel_err": err,
+                    "timed": "gate + up + down MUL_MAT_ID" + (", CUDA-graph replay" if world == 1 else ", eager (one host synchronisation per call)")})
+        for ptr in (dxi, dh, di, dg, dd):
+            ctx.free(ptr)
+    for m, k, base, dw, rb in mats.values():
+        ctx.free(dw)
+    return out
+
+
 def run_reference(args, rank):
     """The CPU arm: the oracle (a port of the reference math; ggml's CPU backend is not
     in this image) on all host cores, same workload, metric and unit."""
@@ -196,10 +389,12 @@ def run_reference(args, rank):
     mats, xs = build_decode_inputs()
     total = sum(algo_bytes(t, m, k, n) for _, t, m, k, _ in mats for n in BATCHES)
 
+    cpu_threads = len(os.sched_getaffinity(0))       # asked for explicitly: torchrun pins OMP_NUM_THREADS to 1
+
     def step():
         for _, t, m, k, w in mats:
             for n in BATCHES:
-                O.mul_mat(t, w, k, xs[k][:n])
+                O.mul_mat(t, w, k, xs[k][:n], nthreads=cpu_threads)
 
     for _ in range(args.warmup):
         step()
@@ -213,7 +408,7 @@ def run_reference(args, rank):
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
         "config": {"workload": "decode_gemv: Q4_K 11008x4096 + Q4_K 4096x11008 + Q6_K 32000x4096, batch 1/2/4/8"},
-        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": cpu_threads, "kind": "port",
                          "sample": "the full step (12 products) per timed step"},
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -379,18 +574,21 @@ def run_gpu(args, rank, world):
     clocks = sampler.stop() if rank == 0 else None
 
     prefill = prefill_section(ctx, world, rank, dist)
+    tp_trace = tp_trace_section(ctx, world, rank, dist)
+    moe = moe_section(ctx, world, rank, dist)
 
     cpu = None
     if rank == 0:
+        cpu_threads = len(os.sched_getaffinity(0))       # torchrun pins OMP_NUM_THREADS to 1: ask for the cores explicitly
         t0 = time.perf_counter()
         reps_cpu = 0
         while time.perf_counter() - t0 < 10.0:
             for _, t, m, k, w in mats:
                 for n in BATCHES:
-                    O.mul_mat(t, w, k, xs[k][:n])
+                    O.mul_mat(t, w, k, xs[k][:n], nthreads=cpu_threads)
             reps_cpu += 1
         dt = (time.perf_counter() - t0) / reps_cpu
-        cpu = {"value": total_bytes / dt / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+        cpu = {"value": total_bytes / dt / 1e9, "unit": "GB/s", "cores": cpu_threads, "kind": "port",
                "sample": "the full step (12 products), %d repeats in ~10 s" % reps_cpu}
 
     if dist:
@@ -405,9 +603,14 @@ def run_gpu(args, rank, world):
                        "launch": "each step is one CUDA-graph replay of 12 x (quantize, GEMV)",
                        "parallelism": "replicas" if world > 1 else "single GPU", "parity_max_rel_err": err},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "kernel": "gemv_kernel (activation pre-quantized), back-to-back launches in a CUDA graph",
+                         # DRAM bytes per GEMV launch, mean over the 12 products: ncu read 25.38 MB for the 25.36 MB
+                         # Q4_K matrix and 107.5 MB for the 107.52 MB Q6_K head (profiles/gemv_decode_q4_K_q6_K.md)
+                         "traffic": 1.001 * tot_b / len(detail), "algorithmic_bytes_per_launch": tot_b / len(detail),
+                         "peak_source": peak_src, "kernel": "gemv_kernel (activation pre-quantized), back-to-back launches in a CUDA graph",
                          "detail": detail},
             "prefill": prefill,
+            "tp_trace": tp_trace,
+            "moe": moe,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e, "how": "eager C-ABI calls per product: tensor_set, mul_mat, tensor_get; one "

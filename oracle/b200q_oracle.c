@@ -403,9 +403,17 @@ int orc_num_threads(void) {
 #endif
 }
 
+/* 0: the OpenMP default (OMP_NUM_THREADS); an explicit count may go up to the processor count, so a
+ * launcher that pins OMP_NUM_THREADS=1 does not decide the baseline's core count */
 static int pick_threads(int nthreads) {
     const int mx = orc_num_threads();
-    return (nthreads <= 0 || nthreads > mx) ? mx : nthreads;
+    if (nthreads <= 0) return mx;
+#ifdef _OPENMP
+    const int np = omp_get_num_procs();
+    return nthreads > np ? np : nthreads;
+#else
+    return 1;
+#endif
 }
 
 int orc_quantize_rows(int type, const float *src, void *dst, int64_t nrows, int64_t k, int nthreads) {
