@@ -27,7 +27,7 @@ const char *stat_name(int s) {
     }
     static const char *rest[] = { "gemv_id", "gemv_id_unaligned", "moe_route", "route_cache_hit", "moe_gemm", "moe_pack",
                                   "gemm_tc", "gemm_tc_quantize", "gemm_fallback_shape", "tp_allreduce", "tp_allgather",
-                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc" };
+                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins" };
     return rest[s - ST_GEMV_ID];
 }
 

@@ -128,6 +128,12 @@ uint32_t emul_lookup4_tab(const uint32_t *t, uint32_t idx) {
 }
 
 void emul_iq4xs_limbs(int ls, int n, int *hi, int *lo) { iq4xs_limbs(ls, n, hi, lo); }
+void emul_q4k_limbs4(uint32_t idx, uint32_t sc, uint32_t *out2) { q4k_limbs4(idx, sc, out2, out2 + 1); }
+void emul_q4k_scales_mins(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t *out4) {
+    q4k_scales8(s0, s1, s2, out4, out4 + 1);
+    q4k_mins8(s0, s1, s2, out4 + 2, out4 + 3);
+}
+void emul_q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int j, int *sc, int *m) { q4k_scale_min(s0, s1, s2, j, sc, m); }
 void emul_iq4xs_limbs8(uint32_t q, int m, uint32_t *out4) { iq4xs_limbs8(q, m, out4, out4 + 1, out4 + 2, out4 + 3); }
 uint32_t emul_nib_minus8(uint32_t t) { return nib_minus8(t); }
 uint32_t emul_six_minus32(uint32_t t) { return six_minus32(t); }

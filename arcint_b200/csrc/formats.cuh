@@ -135,6 +135,31 @@ B200Q_HD void iq4xs_limbs8(uint32_t q, int m, uint32_t *hi_l, uint32_t *lo_l, ui
     *lo_h = hd_byte_perm(zb, zd, 0x6420);
 }
 
+// Q4_K for the int8 tensor cores: the product p = sc * q of a weight's 6-bit sub-block scale and
+// its 4-bit code (0 <= p <= 945) as two int8 limbs, p = 256 * hi + lo with hi = (p + 128) >> 8 in
+// 0..4 and lo in [-128, 127], for four codes (one per byte, 0..15) at once: the codes are widened
+// to 16-bit halves, one integer multiply-add per pair gives p + 128 (no carry between halves), the
+// high bytes are hi and the low bytes with bit 7 flipped are lo. The mins term of the format
+// (dmin * m * sum(x)) does not go through the tensor core.
+B200Q_HD void q4k_limbs4(uint32_t idx, uint32_t sc, uint32_t *hi4, uint32_t *lo4) {
+    const uint32_t za = hd_byte_perm(idx, 0, 0x4140) * sc + 0x00800080u;
+    const uint32_t zb = hd_byte_perm(idx, 0, 0x4342) * sc + 0x00800080u;
+    *hi4 = hd_byte_perm(za, zb, 0x7531);
+    *lo4 = hd_byte_perm(za, zb, 0x6420) ^ 0x80808080u;
+}
+
+// the eight 6-bit mins (or scales) of a Q4_K block as two words of four bytes
+B200Q_HD void q4k_mins8(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t *m03, uint32_t *m47) {
+    *m03 = s1 & 0x3F3F3F3Fu;
+    *m47 = ((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u);
+    (void)s0;
+}
+B200Q_HD void q4k_scales8(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t *c03, uint32_t *c47) {
+    *c03 = s0 & 0x3F3F3F3Fu;
+    *c47 = (s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u);
+    (void)s1;
+}
+
 // Generic, slow, exact f32 decode of weight i of a row (used by the debug dequantizer
 // and as the spec the fast kernels are tested against). One rounding per multiply,
 // like ggml's dequantize_row_* and gguf-py.

@@ -1,6 +1,7 @@
-// gemm_kq.cu -- prefill GEMM for IQ4_XS weights on the tensor cores (tcgen05 int8 MMA).
+// gemm_kq.cu -- prefill GEMM for the 256-weight super-block types IQ4_XS and Q4_K on the tensor cores
+// (tcgen05 int8 MMA).
 //
-//   dst[M, N] = W[M, K] (136-byte IQ4_XS super-blocks) x X[K, N] (f32), N > 8 tokens
+//   dst[M, N] = W[M, K] (136-byte IQ4_XS / 144-byte Q4_K super-blocks) x X[K, N] (f32), N > 8 tokens
 //
 // ggml's form for this type is integer inside a 256-weight super-block and float once per
 // super-block: out += d_w * d_x * sum_sb (ls_sb - 32) * I_sb, with I_sb the exact dot of the
@@ -24,6 +25,12 @@
 // the analogous 8*s_hi + s_lo on Q4_K and found it slower on Xe2 (README of the patch series,
 // lines 860-862), where the systolic pipe is the scarce resource -- on B200 it is the cheap one.
 //
+// Q4_K takes the same road with p = sc * q (0..945, the 6-bit sub-block scale times the 4-bit code):
+// out = d * d_x * sum_sb sc_sb I_sb - dmin * d_x * sum_sb m_sb * sum_32(x). The first term is the
+// two-limb tensor-core product; the second (mins times the activation's block sums, ggml's
+// `sumf -= dmin * sumi_mins`, the reference's min-correction DPAS, 0000-01-kquant-integer-dpas.patch:
+// 3740-3801) is rank 8 per super-block and is subtracted by q4k_mins_kernel afterwards with dp4a.
+//
 // Layout of roles, staging and barriers follows gemm_tc.cu: producer warp (bulk copies of raw
 // rows and activation chunks), MMA warp, eight unpack warps (two threads per weight row, one
 // per eight packed bytes of a block), 4*NW scale-accumulate warps. One stage = one super-block (eight MMA pairs); two accumulator pairs
@@ -43,30 +50,41 @@ using namespace tc;
 
 constexpr int BM = 128, BN = 128, KB = 32, SB = 8;
 constexpr int NACT = 2;                                   // activation chunks (one super-block each) in flight
-constexpr int NRAW = 2;                                   // raw stages (two super-blocks each) in flight
 constexpr int NA = 8;                                     // A-operand slots (blocks unpacked ahead of the MMA)
 constexpr int NBUF = 2;                                   // accumulator pairs (hi, lo)
 constexpr int NW = 2;
 constexpr int THREADS = 32 * (12 + 4 * NW);               // warp groups: {producer, MMA, 2 idle}, 2 x unpack, NW x scale-accumulate
 constexpr int OPER_BYTES = BM * KB;                       // 4096
 constexpr int ACT_CHUNK = SB * OPER_BYTES + BN * 4;       // codes of a super-block + one f32 scale per token
-constexpr int SBB = 136;                                  // bytes of one IQ4_XS super-block
-constexpr int ROWB = 2 * SBB;                             // a raw stage holds two super-blocks per row: 272 B = 17 x 16
-constexpr int RAW_STAGE = BM * ROWB;
 constexpr int A_SLOT = 2 * OPER_BYTES;                    // hi limb, lo limb
-constexpr int RAW_OFF = 0;
-constexpr int ACT_OFF = RAW_OFF + NRAW * RAW_STAGE;
-constexpr int A_OFF = ACT_OFF + NACT * ACT_CHUNK;
-constexpr int BAR_OFF = A_OFF + NA * A_SLOT;
-constexpr int SMEM_TOTAL = BAR_OFF + 8 * 64;
-static_assert(SMEM_TOTAL <= 227 * 1024, "shared memory budget");
+
+// Per type: bytes of a super-block, super-blocks per raw stage (the stage's row piece must be a
+// multiple of 16 bytes: 2 x 136 for IQ4_XS, 144 for Q4_K), raw stages in flight.
+template <int TYPE> struct Fmt;
+template <> struct Fmt<B200Q_TYPE_IQ4_XS> { enum { SBB = 136, SPS = 2, NRAW = 2 }; };
+template <> struct Fmt<B200Q_TYPE_Q4_K>   { enum { SBB = 144, SPS = 1, NRAW = 4 }; };
+template <int TYPE> struct Smem {
+    enum {
+        SBB = Fmt<TYPE>::SBB, SPS = Fmt<TYPE>::SPS, NRAW = Fmt<TYPE>::NRAW,
+        ROWB = SPS * SBB,
+        RAW_STAGE = BM * ROWB,
+        RAW_OFF = 0,
+        ACT_OFF = RAW_OFF + NRAW * RAW_STAGE,
+        A_OFF = ACT_OFF + NACT * ACT_CHUNK,
+        BAR_OFF = A_OFF + NA * A_SLOT,
+        TOTAL = BAR_OFF + 8 * 64
+    };
+    static_assert(TOTAL <= 227 * 1024, "shared memory budget");
+    static_assert(ROWB % 16 == 0 && RAW_STAGE % 128 == 0, "tiled copies");
+};
 
 constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
 constexpr int GB = 4;                                     // blocks per A-ring group: one fence and one barrier round per group
 constexpr int NG = NA / GB;                               // groups in the ring
-enum { BAR_RAW_FULL = 0, BAR_RAW_EMPTY = 2, BAR_ACT_FULL = 4, BAR_ACT_EMPTY = 6, BAR_A_FULL = 8, BAR_A_EMPTY = 10,
-       BAR_ACC_FULL = 12, BAR_ACC_EMPTY = 14, BAR_COUNT = 16 };
+enum { BAR_RAW_FULL = 0, BAR_RAW_EMPTY = 4, BAR_ACT_FULL = 8, BAR_ACT_EMPTY = 10, BAR_A_FULL = 12, BAR_A_EMPTY = 14,
+       BAR_ACC_FULL = 16, BAR_ACC_EMPTY = 18, BAR_COUNT = 20 };
+static_assert(NG == 2 && NACT == 2 && NBUF == 2, "barrier slots above");
 
 // D (+)= A x B^T with the accumulate flag as an operand
 __device__ __forceinline__ void umma_i8_acc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
@@ -75,13 +93,14 @@ __device__ __forceinline__ void umma_i8_acc(uint32_t tmem_d, uint64_t da, uint64
                  ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// After all chunks: the block sums, [chunk][column < 128][block < 8] int16.
 // Activation chunk (128-token tile t, super-block s), per-256 form (the reference's
 // kernel_quant_i8 rule: scale bm/127, round to nearest even, zero below 1e-30):
 //   codes  [block j < 8][half c < 2][group g < 16][column r < 8][16 bytes]
 //   scales [column < 128] f32
 __global__ void __launch_bounds__(256)
 quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t nb1, size_t nb2, size_t nb3, int64_t K,
-                         int64_t N, uint8_t *__restrict__ out) {
+                         int64_t N, uint8_t *__restrict__ out, int16_t *__restrict__ bsum) {
     __shared__ float part[256];
     const int t = blockIdx.y, s = blockIdx.x, nst = gridDim.x;
     const int col = threadIdx.x & 127, half = threadIdx.x >> 7;
@@ -115,22 +134,82 @@ quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t n
         uint8_t *o = chunk + j * OPER_BYTES + (col >> 3) * 128 + (col & 7) * 16;
         *reinterpret_cast<uint4 *>(o) = make_uint4(w[0], w[1], w[2], w[3]);
         *reinterpret_cast<uint4 *>(o + LBO) = make_uint4(w[4], w[5], w[6], w[7]);
+        // the integer sum of the block's 32 codes (Q4_K's mins term): [chunk][column][block] int16
+        int sum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum = __dp4a((int)w[i], 0x01010101, sum);
+        bsum[(((size_t)t * nst + s) * BN + col) * 8 + j] = (int16_t)sum;
     }
     if (half == 0) reinterpret_cast<float *>(chunk + SB * OPER_BYTES)[col] = __fdiv_rn(bm, 127.f);
 }
 
+// The A-operand blocks of one group (GB = 4 blocks of 32 weights) of a super-block, written by the
+// unpack warps: thread (row r, half kh). `blk` points at the row's super-block in the raw stage,
+// `a0` at the thread's 16-byte place (row r) inside slot 0 of the group's four slots.
+template <int TYPE>
+__device__ __forceinline__ void unpack_group(const uint8_t *blk, int jg, int kh, bool row_ok, uint8_t *a0) {
+    if (TYPE == B200Q_TYPE_IQ4_XS) {
+        const uint2 hdr = *reinterpret_cast<const uint2 *>(blk);            // d | scales_h, scales_l
+        const uint32_t scales_h = hdr.x >> 16, scales_l = hdr.y;
+#pragma unroll
+        for (int jj = 0; jj < GB; ++jj) {
+            const int j = jg * GB + jj;
+            const int m = row_ok ? iq4xs_ls(scales_h, scales_l, j) - 32 : 0;     // 0: every limb zero
+            // this thread's packed bytes 8 kh .. 8 kh + 7 of the block: weights 8 kh .. + 7 in the
+            // low nibbles (first 16-byte half of K) and 16 + 8 kh .. in the high ones (second half)
+            const uint2 qq = *reinterpret_cast<const uint2 *>(blk + 8 + 16 * j + 8 * kh);
+            uint32_t hl[2], ll[2], hh[2], lh[2];
+            iq4xs_limbs8(qq.x, m, &hl[0], &ll[0], &hh[0], &lh[0]);
+            iq4xs_limbs8(qq.y, m, &hl[1], &ll[1], &hh[1], &lh[1]);
+            uint8_t *a = a0 + jj * A_SLOT + 8 * kh;
+            *reinterpret_cast<uint2 *>(a) = make_uint2(hl[0], hl[1]);
+            *reinterpret_cast<uint2 *>(a + LBO) = make_uint2(hh[0], hh[1]);
+            *reinterpret_cast<uint2 *>(a + OPER_BYTES) = make_uint2(ll[0], ll[1]);
+            *reinterpret_cast<uint2 *>(a + OPER_BYTES + LBO) = make_uint2(lh[0], lh[1]);
+        }
+    } else {
+        // Q4_K: d, dmin | 12 scale bytes | 4 x 32 bytes; bytes 32 g .. 32 g + 31 hold sub-block 2g in
+        // their low nibbles and 2g + 1 in their high ones. The thread takes bytes 16 kh .. + 15 of the
+        // group's two 32-byte runs: weights 16 kh .. + 15 of four sub-blocks.
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+        uint32_t c03, c47;
+        q4k_scales8(hdr.y, hdr.z, hdr.w, &c03, &c47);
+        const uint32_t cw = row_ok ? (jg ? c47 : c03) : 0u;                  // scales of sub-blocks 4 jg .. + 3
+#pragma unroll
+        for (int gg = 0; gg < 2; ++gg) {
+            const uint4 qv = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * (2 * jg + gg) + 16 * kh);
+            const uint32_t q[4] = { qv.x, qv.y, qv.z, qv.w };
+            const uint32_t sc_lo = (cw >> (16 * gg)) & 0xFFu, sc_hi = (cw >> (16 * gg + 8)) & 0xFFu;
+            uint32_t hl[4], ll[4], hh[4], lh[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                q4k_limbs4(q[i] & 0x0F0F0F0Fu, sc_lo, &hl[i], &ll[i]);
+                q4k_limbs4((q[i] >> 4) & 0x0F0F0F0Fu, sc_hi, &hh[i], &lh[i]);
+            }
+            uint8_t *a = a0 + (2 * gg) * A_SLOT + kh * LBO;
+            *reinterpret_cast<uint4 *>(a) = make_uint4(hl[0], hl[1], hl[2], hl[3]);
+            *reinterpret_cast<uint4 *>(a + OPER_BYTES) = make_uint4(ll[0], ll[1], ll[2], ll[3]);
+            *reinterpret_cast<uint4 *>(a + A_SLOT) = make_uint4(hh[0], hh[1], hh[2], hh[3]);
+            *reinterpret_cast<uint4 *>(a + A_SLOT + OPER_BYTES) = make_uint4(lh[0], lh[1], lh[2], lh[3]);
+        }
+    }
+}
+
+template <int TYPE>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
-                  int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word) {
+gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
+               int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word) {
+    typedef Smem<TYPE> L;
+    constexpr int SBB = L::SBB, SPS = L::SPS, NRAW = L::NRAW, ROWB = L::ROWB;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x, tile_m = blockIdx.y;
     const int row0 = tile_m * BM;
-    const int nsb = K / 256;                    // super-blocks (even: the host gate asks K % 512 == 0)
+    const int nsb = K / 256;                    // super-blocks (a multiple of SPS: the host gate)
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t bars = sbase + BAR_OFF;
+    const uint32_t bars = sbase + L::BAR_OFF;
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
     const int valid_rows = min(BM, M - row0);
 
@@ -172,20 +251,20 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
         const uint8_t *act_tile = act + (size_t)tile_n * nsb * ACT_CHUNK;
         if (lane == 0) tma_prefetch_desc(&wmap);
         for (int s = 0; s < nsb; ++s) {
-            if ((s & 1) == 0) {
-                const int rs = s >> 1, st = rs % NRAW;
+            if (s % SPS == 0) {
+                const int rs = s / SPS, st = rs % NRAW;
                 if (!WAITP(1, bar(BAR_RAW_EMPTY + st), ((rs / NRAW) & 1) ^ 1)) break;
                 if (lane == 0) {
-                    // the whole [128 rows x 272 B] box in one tiled copy; rows past M arrive as zeros
-                    mbar_expect_tx(bar(BAR_RAW_FULL + st), RAW_STAGE);
-                    tma_load_2d(sbase + RAW_OFF + st * RAW_STAGE, &wmap, rs * (ROWB / 4), row0, bar(BAR_RAW_FULL + st));
+                    // the whole [128 rows x ROWB] box in one tiled copy; rows past M arrive as zeros
+                    mbar_expect_tx(bar(BAR_RAW_FULL + st), L::RAW_STAGE);
+                    tma_load_2d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, rs * (ROWB / 4), row0, bar(BAR_RAW_FULL + st));
                 }
             }
             const int at = s % NACT;
             if (!WAITP(3, bar(BAR_ACT_EMPTY + at), ((s / NACT) & 1) ^ 1)) break;
             if (lane == 0) {
                 mbar_expect_tx(bar(BAR_ACT_FULL + at), ACT_CHUNK);
-                bulk_g2s(sbase + ACT_OFF + at * ACT_CHUNK, act_tile + (size_t)s * ACT_CHUNK, ACT_CHUNK, bar(BAR_ACT_FULL + at));
+                bulk_g2s(sbase + L::ACT_OFF + at * ACT_CHUNK, act_tile + (size_t)s * ACT_CHUNK, ACT_CHUNK, bar(BAR_ACT_FULL + at));
             }
             __syncwarp();
         }
@@ -206,9 +285,9 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
 #pragma unroll
                     for (int jj = 0; jj < GB; ++jj) {
                         const int j = jg * GB + jj, slot = gs * GB + jj;
-                        const uint64_t db = umma_desc(sbase + ACT_OFF + at * ACT_CHUNK + j * OPER_BYTES);
-                        umma_i8_acc(d, umma_desc(sbase + A_OFF + slot * A_SLOT), db, IDESC, j > 0);
-                        umma_i8_acc(d + BN, umma_desc(sbase + A_OFF + slot * A_SLOT + OPER_BYTES), db, IDESC, j > 0);
+                        const uint64_t db = umma_desc(sbase + L::ACT_OFF + at * ACT_CHUNK + j * OPER_BYTES);
+                        umma_i8_acc(d, umma_desc(sbase + L::A_OFF + slot * A_SLOT), db, IDESC, j > 0);
+                        umma_i8_acc(d + BN, umma_desc(sbase + L::A_OFF + slot * A_SLOT + OPER_BYTES), db, IDESC, j > 0);
                     }
                     tc_commit(bar(BAR_A_EMPTY + gs));
                     if (jg == SB / GB - 1) {
@@ -222,41 +301,25 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
     } else if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
     } else if (warp < 12) {
-        // ---- unpack: two threads per weight row, one per 16-weight half of every block ----
+        // ---- unpack: two threads per weight row ----
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
         // A half-warp holds eight rows times the two halves, so that the two threads of a row read
-        // the same shared-memory words (one broadcast) and rows 272 bytes apart fall on distinct banks.
+        // neighbouring shared-memory words and rows fall on distinct banks.
         const int r = (warp - 4) * 16 + (lane >> 4) * 8 + (lane & 7), kh = (lane >> 3) & 1;
         const bool row_ok = r < valid_rows;
         bool ok = true;
-        for (int rs = 0; rs < nsb / 2 && ok; ++rs) {
+        for (int rs = 0; rs < nsb / SPS && ok; ++rs) {
             const int st = rs % NRAW;
             if (!WAITP(0, bar(BAR_RAW_FULL + st), (rs / NRAW) & 1)) break;
-            const uint8_t *rowp = smem + RAW_OFF + st * RAW_STAGE + r * ROWB;
+            const uint8_t *rowp = smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint2 hdr = *reinterpret_cast<const uint2 *>(rowp + SBB * h);      // d | scales_h, scales_l
-                const uint32_t scales_h = hdr.x >> 16, scales_l = hdr.y;
+            for (int h = 0; h < SPS; ++h) {
 #pragma unroll
                 for (int jg = 0; jg < SB / GB; ++jg) {
-                    const int g = (2 * rs + h) * (SB / GB) + jg, gs = g % NG;
+                    const int g = (SPS * rs + h) * (SB / GB) + jg, gs = g % NG;
                     if (!WAITP(5, bar(BAR_A_EMPTY + gs), ((g / NG) & 1) ^ 1)) { ok = false; break; }
-#pragma unroll
-                    for (int jj = 0; jj < GB; ++jj) {
-                        const int j = jg * GB + jj, slot = gs * GB + jj;
-                        const int m = row_ok ? iq4xs_ls(scales_h, scales_l, j) - 32 : 0;     // 0: every limb zero
-                        // this thread's packed bytes 8 kh .. 8 kh + 7 of the block: weights 8 kh .. + 7 in the
-                        // low nibbles (first 16-byte half of K) and 16 + 8 kh .. in the high ones (second half)
-                        const uint2 qq = *reinterpret_cast<const uint2 *>(rowp + SBB * h + 8 + 16 * j + 8 * kh);
-                        uint32_t hl[2], ll[2], hh[2], lh[2];
-                        iq4xs_limbs8(qq.x, m, &hl[0], &ll[0], &hh[0], &lh[0]);
-                        iq4xs_limbs8(qq.y, m, &hl[1], &ll[1], &hh[1], &lh[1]);
-                        uint8_t *a = smem + A_OFF + slot * A_SLOT + (r >> 3) * 128 + (r & 7) * 16 + 8 * kh;
-                        *reinterpret_cast<uint2 *>(a) = make_uint2(hl[0], hl[1]);
-                        *reinterpret_cast<uint2 *>(a + LBO) = make_uint2(hh[0], hh[1]);
-                        *reinterpret_cast<uint2 *>(a + OPER_BYTES) = make_uint2(ll[0], ll[1]);
-                        *reinterpret_cast<uint2 *>(a + OPER_BYTES + LBO) = make_uint2(lh[0], lh[1]);
-                    }
+                    unpack_group<TYPE>(rowp + SBB * h, jg, kh, row_ok,
+                                       smem + L::A_OFF + (gs * GB) * A_SLOT + (r >> 3) * 128 + (r & 7) * 16);
                     fence_async_smem();                  // one proxy fence per group of blocks
                     mbar_arrive_warp(bar(BAR_A_FULL + gs), lane);
                 }
@@ -276,16 +339,16 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
         for (int c = 0; c < CW / 2; ++c) acc2[c] = 0ull;
         bool done = false;
         for (int s = 0; s < nsb; ++s) {
-            const int rs = s >> 1, st = rs % NRAW, at = s % NACT, buf = s % NBUF;
+            const int rs = s / SPS, st = rs % NRAW, at = s % NACT, buf = s % NBUF;
             // stage barriers cannot advance past this thread: it releases both stages itself
-            if ((s & 1) == 0 && !WAITP(0, bar(BAR_RAW_FULL + st), (rs / NRAW) & 1)) break;
+            if (s % SPS == 0 && !WAITP(0, bar(BAR_RAW_FULL + st), (rs / NRAW) & 1)) break;
             if (!WAITP(2, bar(BAR_ACT_FULL + at), (s / NACT) & 1)) break;
             if (!WAITP(6, bar(BAR_ACC_FULL + buf), (s / NBUF) & 1)) break;
             tc_fence_after();
             const float dwb = row_ok ? half_bits_to_float(*reinterpret_cast<const uint16_t *>(
-                                           smem + RAW_OFF + st * RAW_STAGE + r * ROWB + SBB * (s & 1))) : 0.f;
-            const f32x2 dw2 = f2_pack(dwb, dwb), negc2 = f2_pack(-12582912.f, -12582912.f), k256 = f2_pack(256.f, 256.f);
-            const uint32_t dxa = sbase + ACT_OFF + at * ACT_CHUNK + SB * OPER_BYTES + (u * CW) * 4;
+                                           smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + SBB * (s % SPS))) : 0.f;
+            const f32x2 dw2 = f2_pack(dwb, dwb);
+            const uint32_t dxa = sbase + L::ACT_OFF + at * ACT_CHUNK + SB * OPER_BYTES + (u * CW) * 4;
             const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * (2 * BN) + (uint32_t)u * CW;
 #pragma unroll
             for (int q = 0; q < CW / 16; ++q) {
@@ -311,7 +374,7 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
                 }
             }
             mbar_arrive_warp(bar(BAR_ACT_EMPTY + at), lane);
-            if (s & 1) mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
+            if (s % SPS == SPS - 1) mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
             done = s == nsb - 1;
         }
         if (done && row_ok) {
@@ -342,15 +405,77 @@ gemm_iq4xs_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const 
     }
 }
 
+// Q4_K's second term: dst[c][r] -= sum_sb dmin[r, sb] * d_x[c, sb] * sum_j m_j[r, sb] * bsum_j[c, sb], with
+// bsum_j the integer sum of the activation codes of sub-block j (written by the tiled quantizer
+// beside the chunks). One thread per weight row, MC columns per block; per super-block the row's
+// eight 6-bit mins are two packed words, the column's eight sums are split into two int8 digits
+// (bsum = 256 bh + bl) in shared memory, and the integer sum is four dp4a.
+constexpr int MC = 64;
+__global__ void __launch_bounds__(128)
+q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nsb, const uint8_t *__restrict__ act,
+                const int16_t *__restrict__ bsum, int N, float *__restrict__ dst, int64_t ldd) {
+    __shared__ __align__(16) uint32_t cs[2][MC][4];       // bl 0..3, bl 4..7, bh 0..3, bh 4..7
+    __shared__ float cdx[2][MC];
+    const int r = blockIdx.y * 128 + threadIdx.x, c0 = blockIdx.x * MC;
+    const bool row_ok = r < M;
+    const uint8_t *wrow = W + (size_t)(row_ok ? r : 0) * row_stride;
+    float acc[MC];
+#pragma unroll
+    for (int c = 0; c < MC; ++c) acc[c] = 0.f;
+    for (int sb = 0; sb < nsb; ++sb) {
+        const int pb = sb & 1;
+        if (threadIdx.x < MC) {
+            const int c = c0 + threadIdx.x, t = c / BN, cc = c % BN;
+            uint32_t w[4] = { 0, 0, 0, 0 };
+            float dx = 0.f;
+            if (c < N) {
+                const size_t chunk = (size_t)t * nsb + sb;
+                const int4 sv = *reinterpret_cast<const int4 *>(bsum + (chunk * BN + cc) * 8);
+                const int v[4] = { sv.x, sv.y, sv.z, sv.w };
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int s = (int)(int16_t)(((uint32_t)v[i >> 1] >> (16 * (i & 1))) & 0xFFFFu);
+                    const int bh = (s + 128) >> 8, bl = s - 256 * bh;
+                    w[i >> 2] |= (uint32_t)(bl & 0xFF) << (8 * (i & 3));
+                    w[2 + (i >> 2)] |= (uint32_t)(bh & 0xFF) << (8 * (i & 3));
+                }
+                dx = reinterpret_cast<const float *>(act + chunk * ACT_CHUNK + SB * OPER_BYTES)[cc];
+            }
+            *reinterpret_cast<uint4 *>(cs[pb][threadIdx.x]) = make_uint4(w[0], w[1], w[2], w[3]);
+            cdx[pb][threadIdx.x] = dx;
+        }
+        const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(wrow + (size_t)sb * 144));
+        uint32_t m03, m47;
+        q4k_mins8(hdr.y, hdr.z, hdr.w, &m03, &m47);
+        const float dmin = row_ok ? half_bits_to_float((uint16_t)(hdr.x >> 16)) : 0.f;
+        __syncthreads();                       // the other buffer is being read by nobody: two syncs apart
+#pragma unroll
+        for (int c = 0; c < MC; ++c) {
+            const uint4 b = *reinterpret_cast<const uint4 *>(cs[pb][c]);
+            const int lo = __dp4a((int)m47, (int)b.y, __dp4a((int)m03, (int)b.x, 0));
+            const int hi = __dp4a((int)m47, (int)b.w, __dp4a((int)m03, (int)b.z, 0));
+            acc[c] = fmaf(dmin * cdx[pb][c], (float)(lo + (hi << 8)), acc[c]);
+        }
+    }
+    if (row_ok) {
+#pragma unroll
+        for (int c = 0; c < MC; ++c)
+            if (c0 + c < N) dst[(int64_t)(c0 + c) * ldd + r] -= acc[c];
+    }
+}
+
 }  // namespace kq
 
+static size_t kq_chunks(int64_t K, int64_t N) { return (size_t)(((N + kq::BN - 1) / kq::BN) * (K / 256)); }
+
 size_t gemm_kq_act_bytes(int64_t K, int64_t N) {
-    return (size_t)(((N + kq::BN - 1) / kq::BN) * (K / 256)) * kq::ACT_CHUNK;
+    return kq_chunks(K, N) * (kq::ACT_CHUNK + kq::BN * 8 * sizeof(int16_t));      // chunks, then block sums
 }
 
 bool gemm_kq_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride) {
-    if (type != B200Q_TYPE_IQ4_XS) return false;
-    if (K <= 0 || K % 512 || M <= 0 || N <= 0) return false;          // raw stages hold two super-blocks (16-byte pieces)
+    if (type != B200Q_TYPE_IQ4_XS && type != B200Q_TYPE_Q4_K) return false;
+    // raw stages are whole super-blocks in 16-byte pieces: two per stage for IQ4_XS, one for Q4_K
+    if (K <= 0 || K % (type == B200Q_TYPE_IQ4_XS ? 512 : 256) || M <= 0 || N <= 0) return false;
     if ((uintptr_t)w % 16 || row_stride % 16) return false;
     if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return false;
     return true;
@@ -359,29 +484,47 @@ bool gemm_kq_supported(int type, int64_t M, int64_t K, int64_t N, const void *w,
 b200q_status launch_quantize_tiled256(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out) {
     const int64_t K = src1->ne[0], N = src1->ne[1] * src1->ne[2] * src1->ne[3];
     dim3 grid((unsigned)(K / 256), (unsigned)((N + kq::BN - 1) / kq::BN));
+    int16_t *bsum = reinterpret_cast<int16_t *>(out + kq_chunks(K, N) * kq::ACT_CHUNK);
     kq::quantize_tiled256_kernel<<<grid, 256, 0, ctx->stream>>>((const uint8_t *)src1->data, src1->ne[1], src1->ne[2],
-                                                               src1->nb[1], src1->nb[2], src1->nb[3], K, N, out);
+                                                               src1->nb[1], src1->nb[2], src1->nb[3], K, N, out, bsum);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC_QUANT);
     return B200Q_OK;
 }
 
-b200q_status launch_gemm_kq(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
-                            const uint8_t *act, int64_t N, float *dst, int64_t ldd) {
-    if (type != B200Q_TYPE_IQ4_XS) return fail(ctx, B200Q_UNSUPPORTED, "gemm_kq: type %d", type);
+template <int TYPE>
+static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K, const uint8_t *act,
+                                int64_t N, float *dst, int64_t ldd) {
+    typedef kq::Smem<TYPE> L;
+    auto kern = kq::gemm_kq_kernel<TYPE>;
     static bool attr_set = false;
     if (!attr_set) {
-        B200Q_CUDA(ctx, cudaFuncSetAttribute(kq::gemm_iq4xs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kq::SMEM_TOTAL));
+        B200Q_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::TOTAL));
         attr_set = true;
     }
     CUtensorMap wmap;
-    b200q_status st = make_weight_tmap(ctx, &wmap, w, row_stride, M, (K / 256) * kq::SBB, kq::ROWB);
+    b200q_status st = make_weight_tmap(ctx, &wmap, w, row_stride, M, (K / 256) * L::SBB, L::ROWB);
     if (st != B200Q_OK) return st;
     dim3 grid((unsigned)((N + kq::BN - 1) / kq::BN), (unsigned)((M + kq::BM - 1) / kq::BM));
-    kq::gemm_iq4xs_kernel<<<grid, kq::THREADS, kq::SMEM_TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd,
-                                                                              ctx->error_word);
+    kern<<<grid, kq::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd, ctx->error_word);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
+    return B200Q_OK;
+}
+
+b200q_status launch_gemm_kq(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
+                            const uint8_t *act, int64_t N, float *dst, int64_t ldd) {
+    if (type == B200Q_TYPE_IQ4_XS) return launch_kq_t<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, M, K, act, N, dst, ldd);
+    if (type != B200Q_TYPE_Q4_K) return fail(ctx, B200Q_UNSUPPORTED, "gemm_kq: type %d", type);
+    b200q_status st = launch_kq_t<B200Q_TYPE_Q4_K>(ctx, w, row_stride, M, K, act, N, dst, ldd);
+    if (st != B200Q_OK) return st;
+    // the mins term, subtracted in place
+    const int16_t *bsum = reinterpret_cast<const int16_t *>(act + kq_chunks(K, N) * kq::ACT_CHUNK);
+    dim3 grid((unsigned)((N + kq::MC - 1) / kq::MC), (unsigned)((M + 127) / 128));
+    kq::q4k_mins_kernel<<<grid, 128, 0, ctx->stream>>>((const uint8_t *)w, row_stride, (int)M, (int)(K / 256), act, bsum, (int)N,
+                                                      dst, ldd);
+    B200Q_CUDA(ctx, cudaGetLastError());
+    count(ctx, ST_GEMM_KQ_MINS);
     return B200Q_OK;
 }
 

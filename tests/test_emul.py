@@ -80,6 +80,36 @@ def test_iq4xs_two_limbs():
             assert out[3] == sum(los[i] << (8 * b) for b, i in enumerate(high))
 
 
+def test_q4k_two_limbs_and_packed_scales():
+    """Q4_K on the tensor cores: sc * q as 256 hi + lo with int8 limbs, four codes at a time; the packed
+    extraction of the eight scales and mins must agree with the scalar one."""
+    E = emul()
+    E.emul_q4k_limbs4.argtypes = [C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32)]
+    E.emul_q4k_scales_mins.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32)]
+    E.emul_q4k_scale_min.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    rng = np.random.default_rng(1)
+    for sc in range(64):
+        for idx4 in [np.arange(4) + 4 * g for g in range(4)] + [rng.integers(0, 16, 4) for _ in range(4)]:
+            idx = int(idx4[0]) | (int(idx4[1]) << 8) | (int(idx4[2]) << 16) | (int(idx4[3]) << 24)
+            out = (C.c_uint32 * 2)()
+            E.emul_q4k_limbs4(idx, sc, out)
+            for b, q in enumerate(idx4):
+                hi = (out[0] >> (8 * b)) & 0xFF
+                lo = (out[1] >> (8 * b)) & 0xFF
+                hi = hi - 256 if hi >= 128 else hi
+                lo = lo - 256 if lo >= 128 else lo
+                assert 256 * hi + lo == sc * int(q) and 0 <= hi <= 4
+    for _ in range(200):
+        s0, s1, s2 = (int(v) for v in rng.integers(0, 1 << 32, 3, dtype=np.uint64))
+        out = (C.c_uint32 * 4)()
+        E.emul_q4k_scales_mins(s0, s1, s2, out)
+        for j in range(8):
+            sc, m = C.c_int(), C.c_int()
+            E.emul_q4k_scale_min(s0, s1, s2, j, C.byref(sc), C.byref(m))
+            assert (out[j // 4] >> (8 * (j % 4))) & 0xFF == sc.value
+            assert (out[2 + j // 4] >> (8 * (j % 4))) & 0xFF == m.value
+
+
 @pytest.mark.parametrize("name,t", [("q4_0", O.Q4_0), ("q8_0", O.Q8_0), ("q4_K", O.Q4_K), ("q6_K", O.Q6_K), ("iq4_xs", O.IQ4_XS)])
 def test_device_decoder_text_matches_gguf_golden(golden, name, t):
     E = emul()

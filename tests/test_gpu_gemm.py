@@ -137,3 +137,57 @@ def test_config3_iq4_xs_full_size(ctx):
     rows = np.unique(np.concatenate([[0, 127, 128, m - 1], np.random.default_rng(1).integers(0, m, 28)]))
     assert rel_err(got[:, rows], O.mul_mat_f64(t, w[rows], k, x, True)) < TOL
     assert np.isfinite(got).all()
+
+
+# ---- Q4_K: sc * q as two int8 limbs on the tensor cores, mins term subtracted by a dp4a kernel ----
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (128, 16, 512), (300, 17, 1024), (300, 100, 1024), (512, 300, 2560),
+                                   (1023, 33, 4096), (77, 9, 768), (200, 130, 11008)])
+def test_gemm_q4_K_matches_oracle(ctx, m, n, k):
+    rng = np.random.default_rng(m * 5 + n)
+    t = A.Q4_K
+    w = O.random_blocks(t, m, k, rng)
+    x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1 and st.get("gemm_kq_mins", 0) == 1, st
+    assert np.isfinite(got).all()
+    assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
+
+
+def test_gemm_q4_K_extreme_codes(ctx):
+    """All scales and mins at 63, all codes 15, activations of one sign: the largest limb sums and block sums."""
+    t, m, n, k = A.Q4_K, 128, 32, 512
+    rng = np.random.default_rng(3)
+    w = O.random_blocks(t, m, k, rng).reshape(m, k // 256, 144)
+    w[:, :, 4:16] = 0xFF
+    w[: m // 2, :, 16:] = 0xFF
+    w[m // 2:, :, 16:] = 0x00
+    w = w.reshape(m, -1)
+    x = np.full((n, k), 2.5, dtype=np.float32)
+    x[1::2] *= -1
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1
+    assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
+
+
+def test_gemm_q4_K_nmse_and_gemv_agreement(ctx):
+    t, m, n, k = A.Q4_K, 384, 72, 2048
+    w = make_weights(t, m, k, 70)
+    x = O.fill_normal(n * k, 71, 1.0).reshape(n, k)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1
+    assert nmse(got, O.mul_mat_f64(t, w, k, x, False)) < 5e-4
+    parts = np.concatenate([ctx.run_mul_mat(t, w, k, x[i:i + 8]) for i in range(0, n, 8)])
+    assert rel_err(got, parts.astype(np.float64)) < TOL
+
+
+def test_config2_shape_q4_K_prompt(ctx):
+    """The decode config's gate/up shape at a prompt width: Q4_K 11008 x 4096, 512 tokens; sampled rows."""
+    t, m, n, k = A.Q4_K, 11008, 512, 4096
+    base = make_weights(t, 256, k, 0x5EED0003)
+    w = np.tile(base, (m // 256, 1))
+    x = O.fill_normal(n * k, 0x5EED0103, 1.0).reshape(n, k)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1
+    rows = np.unique(np.concatenate([[0, 127, 128, m - 1], np.random.default_rng(2).integers(0, m, 28)]))
+    assert rel_err(got[:, rows], O.mul_mat_f64(t, w[rows], k, x, True)) < TOL
