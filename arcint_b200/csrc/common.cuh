@@ -155,10 +155,24 @@ b200q_status launch_gemv_id(b200q_ctx *ctx, int type, const void *w, size_t row_
 struct RouteView {
     const int32_t *pairs;          // [n_pairs]
     const int32_t *tiles[4];       // class k: tiles of at most 1, 2, 4, 8 pairs (int4 each)
-    const int32_t *n_tiles;        // [4] device counters
+    const int32_t *tiles128;       // tiles of at most 128 pairs (tensor-core path), every pair once
+    const int32_t *n_tiles;        // [5] device counters: the four classes, then the 128-pair list
     int64_t        max_tiles;      // upper bound of every list
+    int64_t        max_tiles128;   // upper bound of the 128-pair list
     const int32_t *owner_counts;   // expert parallelism: pairs per owner rank (device), else unused
 };
+// MUL_MAT_ID view of the tensor-core GEMM: column c of tile n is pair pairs[first + c] of expert
+// tiles[4n] (tiles == nullptr: a dense product, column = token).
+struct TileRoute {
+    const int32_t *tiles;      // [n][4]: expert, first pair, count, -
+    const int32_t *n_tiles;    // device scalar
+    const int32_t *pairs;      // pairs sorted by expert
+    int            n_used, ne11;
+    size_t         nb1, nb2;   // src1: bytes between slot rows and between tokens
+    int64_t        ld1, ld2;   // dst: floats between slots and between tokens
+};
+b200q_status make_weight_tmap3(b200q_ctx *ctx, void *tmap_out, const void *w, size_t row_stride, int64_t M, int64_t row_bytes,
+                               int box_bytes, int64_t n_mat, size_t mat_stride);
 // tensor map of a packed weight matrix seen as [M rows][row_bytes / 4] 32-bit elements, box = 128 rows x box_bytes
 b200q_status make_weight_tmap(b200q_ctx *ctx, void *tmap_out, const void *w, size_t row_stride, int64_t M, int64_t row_bytes,
                               int box_bytes);
@@ -183,6 +197,9 @@ b200q_status launch_gemm_tc(b200q_ctx *ctx, int type, const void *w, size_t row_
 bool         gemm_kq_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride);
 size_t       gemm_kq_act_bytes(int64_t K, int64_t N);
 b200q_status launch_quantize_tiled256(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out);
+size_t       gemm_kq_id_act_bytes(int64_t K, int64_t max_tiles);
+b200q_status launch_gemm_kq_id(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1, const TileRoute &tr,
+                               int64_t max_tiles, uint8_t *act, float *dst);
 b200q_status launch_gemm_kq(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                             const uint8_t *act, int64_t N, float *dst, int64_t ldd);
 

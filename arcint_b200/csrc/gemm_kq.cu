@@ -100,16 +100,25 @@ __device__ __forceinline__ void umma_i8_acc(uint32_t tmem_d, uint64_t da, uint64
 //   scales [column < 128] f32
 __global__ void __launch_bounds__(256)
 quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t nb1, size_t nb2, size_t nb3, int64_t K,
-                         int64_t N, uint8_t *__restrict__ out, int16_t *__restrict__ bsum) {
+                         int64_t N, uint8_t *__restrict__ out, int16_t *__restrict__ bsum, TileRoute id) {
     __shared__ float part[256];
     const int t = blockIdx.y, s = blockIdx.x, nst = gridDim.x;
     const int col = threadIdx.x & 127, half = threadIdx.x >> 7;
-    const int64_t n = (int64_t)t * BN + col;
     uint8_t *chunk = out + ((size_t)t * nst + s) * ACT_CHUNK;
     const float *x = nullptr;
-    if (n < N) {
-        const int64_t c1 = n % ne1, c23 = n / ne1, c2 = c23 % ne2, c3 = c23 / ne2;
-        x = reinterpret_cast<const float *>(base + c1 * nb1 + c2 * nb2 + c3 * nb3) + (int64_t)s * 256 + 128 * half;
+    if (id.tiles) {
+        // MUL_MAT_ID: the tile's columns are routed pairs; pair p = (token, slot) reads src1 row slot % ne11
+        if (t >= __ldg(id.n_tiles)) return;
+        if (col < __ldg(id.tiles + 4 * t + 2)) {
+            const int p = __ldg(id.pairs + __ldg(id.tiles + 4 * t + 1) + col), tok = p / id.n_used, slot = p - tok * id.n_used;
+            x = reinterpret_cast<const float *>(base + (size_t)(slot % id.ne11) * id.nb1 + (size_t)tok * id.nb2) + (int64_t)s * 256 + 128 * half;
+        }
+    } else {
+        const int64_t n = (int64_t)t * BN + col;
+        if (n < N) {
+            const int64_t c1 = n % ne1, c23 = n / ne1, c2 = c23 % ne2, c3 = c23 / ne2;
+            x = reinterpret_cast<const float *>(base + c1 * nb1 + c2 * nb2 + c3 * nb3) + (int64_t)s * 256 + 128 * half;
+        }
     }
     float amax = 0.f;
     if (x)
@@ -198,7 +207,7 @@ __device__ __forceinline__ void unpack_group(const uint8_t *blk, int jg, int kh,
 template <int TYPE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
-               int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word) {
+               int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word, TileRoute id) {
     typedef Smem<TYPE> L;
     constexpr int SBB = L::SBB, SPS = L::SPS, NRAW = L::NRAW, ROWB = L::ROWB;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -212,6 +221,14 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     const uint32_t bars = sbase + L::BAR_OFF;
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
     const int valid_rows = min(BM, M - row0);
+    // the tile's matrix and columns: dense, tile_n-th run of 128 tokens; MUL_MAT_ID, a route tile
+    int expert = 0, first = 0, ncols = min(BN, N - tile_n * BN);
+    if (id.tiles) {
+        if (tile_n >= __ldg(id.n_tiles)) return;          // the whole block: nothing is set up yet
+        expert = __ldg(id.tiles + 4 * tile_n);
+        first = __ldg(id.tiles + 4 * tile_n + 1);
+        ncols = __ldg(id.tiles + 4 * tile_n + 2);
+    }
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -257,7 +274,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 if (lane == 0) {
                     // the whole [128 rows x ROWB] box in one tiled copy; rows past M arrive as zeros
                     mbar_expect_tx(bar(BAR_RAW_FULL + st), L::RAW_STAGE);
-                    tma_load_2d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, rs * (ROWB / 4), row0, bar(BAR_RAW_FULL + st));
+                    tma_load_3d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, rs * (ROWB / 4), row0, expert, bar(BAR_RAW_FULL + st));
                 }
             }
             const int at = s % NACT;
@@ -378,16 +395,30 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             done = s == nsb - 1;
         }
         if (done && row_ok) {
-            float *o = dst + (int64_t)(tile_n * BN + u * CW) * ldd + row0 + r;
-            const int ncol = N - (tile_n * BN + u * CW);
+            const int ncol = ncols - u * CW;                 // this thread's columns inside the tile
+            if (id.tiles) {
 #pragma unroll
-            for (int c = 0; c < CW; c += 2) {
-                float a0, a1;
-                f2_unpack(acc2[c / 2], a0, a1);
-                if (c < ncol) *o = a0;
-                o += ldd;
-                if (c + 1 < ncol) *o = a1;
-                o += ldd;
+                for (int c = 0; c < CW; c += 2) {
+                    float a[2];
+                    f2_unpack(acc2[c / 2], a[0], a[1]);
+#pragma unroll
+                    for (int d = 0; d < 2; ++d)
+                        if (c + d < ncol) {
+                            const int p = __ldg(id.pairs + first + u * CW + c + d), tok = p / id.n_used, slot = p - tok * id.n_used;
+                            dst[tok * id.ld2 + slot * id.ld1 + row0 + r] = a[d];
+                        }
+                }
+            } else {
+                float *o = dst + (int64_t)(tile_n * BN + u * CW) * ldd + row0 + r;
+#pragma unroll
+                for (int c = 0; c < CW; c += 2) {
+                    float a0, a1;
+                    f2_unpack(acc2[c / 2], a0, a1);
+                    if (c < ncol) *o = a0;
+                    o += ldd;
+                    if (c + 1 < ncol) *o = a1;
+                    o += ldd;
+                }
             }
         }
     }
@@ -412,24 +443,34 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
 // (bsum = 256 bh + bl) in shared memory, and the integer sum is four dp4a.
 constexpr int MC = 64;
 __global__ void __launch_bounds__(128)
-q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nsb, const uint8_t *__restrict__ act,
-                const int16_t *__restrict__ bsum, int N, float *__restrict__ dst, int64_t ldd) {
+q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_stride, int M, int nsb,
+                const uint8_t *__restrict__ act, const int16_t *__restrict__ bsum, int N, float *__restrict__ dst,
+                int64_t ldd, TileRoute id) {
     __shared__ __align__(16) uint32_t cs[2][MC][4];       // bl 0..3, bl 4..7, bh 0..3, bh 4..7
     __shared__ float cdx[2][MC];
-    const int r = blockIdx.y * 128 + threadIdx.x, c0 = blockIdx.x * MC;
+    const int tile = blockIdx.x / (BN / MC), cc0 = (blockIdx.x % (BN / MC)) * MC;   // columns cc0 .. cc0 + MC - 1 of the tile
+    int expert = 0, first = 0, ncols = min(BN, N - tile * BN);
+    if (id.tiles) {
+        if (tile >= __ldg(id.n_tiles)) return;
+        expert = __ldg(id.tiles + 4 * tile);
+        first = __ldg(id.tiles + 4 * tile + 1);
+        ncols = __ldg(id.tiles + 4 * tile + 2);
+    }
+    if (cc0 >= ncols) return;
+    const int r = blockIdx.y * 128 + threadIdx.x;
     const bool row_ok = r < M;
-    const uint8_t *wrow = W + (size_t)(row_ok ? r : 0) * row_stride;
+    const uint8_t *wrow = W + (size_t)expert * mat_stride + (size_t)(row_ok ? r : 0) * row_stride;
     float acc[MC];
 #pragma unroll
     for (int c = 0; c < MC; ++c) acc[c] = 0.f;
     for (int sb = 0; sb < nsb; ++sb) {
         const int pb = sb & 1;
         if (threadIdx.x < MC) {
-            const int c = c0 + threadIdx.x, t = c / BN, cc = c % BN;
+            const int cc = cc0 + threadIdx.x;
             uint32_t w[4] = { 0, 0, 0, 0 };
             float dx = 0.f;
-            if (c < N) {
-                const size_t chunk = (size_t)t * nsb + sb;
+            if (cc < ncols) {
+                const size_t chunk = (size_t)tile * nsb + sb;
                 const int4 sv = *reinterpret_cast<const int4 *>(bsum + (chunk * BN + cc) * 8);
                 const int v[4] = { sv.x, sv.y, sv.z, sv.w };
 #pragma unroll
@@ -448,7 +489,7 @@ q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nsb
         uint32_t m03, m47;
         q4k_mins8(hdr.y, hdr.z, hdr.w, &m03, &m47);
         const float dmin = row_ok ? half_bits_to_float((uint16_t)(hdr.x >> 16)) : 0.f;
-        __syncthreads();                       // the other buffer is being read by nobody: two syncs apart
+        __syncthreads();                       // the other buffer is read by nobody: its readers are two barriers back
 #pragma unroll
         for (int c = 0; c < MC; ++c) {
             const uint4 b = *reinterpret_cast<const uint4 *>(cs[pb][c]);
@@ -460,17 +501,26 @@ q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nsb
     if (row_ok) {
 #pragma unroll
         for (int c = 0; c < MC; ++c)
-            if (c0 + c < N) dst[(int64_t)(c0 + c) * ldd + r] -= acc[c];
+            if (cc0 + c < ncols) {
+                if (id.tiles) {
+                    const int p = __ldg(id.pairs + first + cc0 + c), tok = p / id.n_used, slot = p - tok * id.n_used;
+                    dst[tok * id.ld2 + slot * id.ld1 + r] -= acc[c];
+                } else {
+                    dst[(int64_t)(tile * BN + cc0 + c) * ldd + r] -= acc[c];
+                }
+            }
     }
 }
 
 }  // namespace kq
 
 static size_t kq_chunks(int64_t K, int64_t N) { return (size_t)(((N + kq::BN - 1) / kq::BN) * (K / 256)); }
+static const TileRoute NO_ROUTE = { nullptr, nullptr, nullptr, 1, 1, 0, 0, 0, 0 };
 
 size_t gemm_kq_act_bytes(int64_t K, int64_t N) {
     return kq_chunks(K, N) * (kq::ACT_CHUNK + kq::BN * 8 * sizeof(int16_t));      // chunks, then block sums
 }
+size_t gemm_kq_id_act_bytes(int64_t K, int64_t max_tiles) { return gemm_kq_act_bytes(K, max_tiles * kq::BN); }
 
 bool gemm_kq_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride) {
     if (type != B200Q_TYPE_IQ4_XS && type != B200Q_TYPE_Q4_K) return false;
@@ -481,20 +531,29 @@ bool gemm_kq_supported(int type, int64_t M, int64_t K, int64_t N, const void *w,
     return true;
 }
 
-b200q_status launch_quantize_tiled256(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out) {
-    const int64_t K = src1->ne[0], N = src1->ne[1] * src1->ne[2] * src1->ne[3];
-    dim3 grid((unsigned)(K / 256), (unsigned)((N + kq::BN - 1) / kq::BN));
-    int16_t *bsum = reinterpret_cast<int16_t *>(out + kq_chunks(K, N) * kq::ACT_CHUNK);
-    kq::quantize_tiled256_kernel<<<grid, 256, 0, ctx->stream>>>((const uint8_t *)src1->data, src1->ne[1], src1->ne[2],
-                                                               src1->nb[1], src1->nb[2], src1->nb[3], K, N, out, bsum);
+static b200q_status quantize256(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out, int64_t n_tiles, const TileRoute &tr) {
+    const int64_t K = src1->ne[0];
+    dim3 grid((unsigned)(K / 256), (unsigned)n_tiles);
+    int16_t *bsum = reinterpret_cast<int16_t *>(out + (size_t)(n_tiles * (K / 256)) * kq::ACT_CHUNK);
+    kq::quantize_tiled256_kernel<<<grid, 256, 0, ctx->stream>>>((const uint8_t *)src1->data, src1->ne[1], src1->ne[2], src1->nb[1],
+                                                               src1->nb[2], src1->nb[3], K, src1->ne[1] * src1->ne[2] * src1->ne[3],
+                                                               out, bsum, tr);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC_QUANT);
     return B200Q_OK;
 }
 
+b200q_status launch_quantize_tiled256(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out) {
+    const int64_t N = src1->ne[1] * src1->ne[2] * src1->ne[3];
+    return quantize256(ctx, src1, out, (N + kq::BN - 1) / kq::BN, NO_ROUTE);
+}
+
+// n_tiles: grid width (dense: the tiles of N; MUL_MAT_ID: the upper bound of the route's tile count,
+// blocks past the device-side count leave at once)
 template <int TYPE>
-static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K, const uint8_t *act,
-                                int64_t N, float *dst, int64_t ldd) {
+static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride, size_t mat_stride, int64_t n_mat, int64_t M,
+                                int64_t K, const uint8_t *act, int64_t N, int64_t n_tiles, float *dst, int64_t ldd,
+                                const TileRoute &tr) {
     typedef kq::Smem<TYPE> L;
     auto kern = kq::gemm_kq_kernel<TYPE>;
     static bool attr_set = false;
@@ -503,29 +562,45 @@ static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride
         attr_set = true;
     }
     CUtensorMap wmap;
-    b200q_status st = make_weight_tmap(ctx, &wmap, w, row_stride, M, (K / 256) * L::SBB, L::ROWB);
+    b200q_status st = make_weight_tmap3(ctx, &wmap, w, row_stride, M, (K / 256) * L::SBB, L::ROWB, n_mat, mat_stride);
     if (st != B200Q_OK) return st;
-    dim3 grid((unsigned)((N + kq::BN - 1) / kq::BN), (unsigned)((M + kq::BM - 1) / kq::BM));
-    kern<<<grid, kq::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd, ctx->error_word);
+    dim3 grid((unsigned)n_tiles, (unsigned)((M + kq::BM - 1) / kq::BM));
+    kern<<<grid, kq::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd, ctx->error_word, tr);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
+    if (TYPE == B200Q_TYPE_Q4_K) {
+        // the mins term, subtracted in place
+        const int16_t *bsum = reinterpret_cast<const int16_t *>(act + (size_t)(n_tiles * (K / 256)) * kq::ACT_CHUNK);
+        dim3 g2((unsigned)(n_tiles * (kq::BN / kq::MC)), (unsigned)((M + 127) / 128));
+        kq::q4k_mins_kernel<<<g2, 128, 0, ctx->stream>>>((const uint8_t *)w, row_stride, mat_stride, (int)M, (int)(K / 256), act, bsum,
+                                                        (int)N, dst, ldd, tr);
+        B200Q_CUDA(ctx, cudaGetLastError());
+        count(ctx, ST_GEMM_KQ_MINS);
+    }
     return B200Q_OK;
 }
 
 b200q_status launch_gemm_kq(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                             const uint8_t *act, int64_t N, float *dst, int64_t ldd) {
-    if (type == B200Q_TYPE_IQ4_XS) return launch_kq_t<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, M, K, act, N, dst, ldd);
-    if (type != B200Q_TYPE_Q4_K) return fail(ctx, B200Q_UNSUPPORTED, "gemm_kq: type %d", type);
-    b200q_status st = launch_kq_t<B200Q_TYPE_Q4_K>(ctx, w, row_stride, M, K, act, N, dst, ldd);
+    const int64_t n_tiles = (N + kq::BN - 1) / kq::BN;
+    const size_t ms = row_stride * (size_t)M;
+    if (type == B200Q_TYPE_IQ4_XS) return launch_kq_t<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
+    if (type == B200Q_TYPE_Q4_K) return launch_kq_t<B200Q_TYPE_Q4_K>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
+    return fail(ctx, B200Q_UNSUPPORTED, "gemm_kq: type %d", type);
+}
+
+// MUL_MAT_ID on the tensor cores: the route's 128-pair tiles are the column tiles; the activation of
+// every tile is gathered and quantized into `act` (gemm_kq_id_act_bytes) first.
+b200q_status launch_gemm_kq_id(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1, const TileRoute &tr,
+                               int64_t max_tiles, uint8_t *act, float *dst) {
+    const int64_t K = src0->ne[0], M = src0->ne[1];
+    b200q_status st = quantize256(ctx, src1, act, max_tiles, tr);
     if (st != B200Q_OK) return st;
-    // the mins term, subtracted in place
-    const int16_t *bsum = reinterpret_cast<const int16_t *>(act + kq_chunks(K, N) * kq::ACT_CHUNK);
-    dim3 grid((unsigned)((N + kq::MC - 1) / kq::MC), (unsigned)((M + 127) / 128));
-    kq::q4k_mins_kernel<<<grid, 128, 0, ctx->stream>>>((const uint8_t *)w, row_stride, (int)M, (int)(K / 256), act, bsum, (int)N,
-                                                      dst, ldd);
-    B200Q_CUDA(ctx, cudaGetLastError());
-    count(ctx, ST_GEMM_KQ_MINS);
-    return B200Q_OK;
+    if (src0->type == B200Q_TYPE_IQ4_XS)
+        return launch_kq_t<B200Q_TYPE_IQ4_XS>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
+    if (src0->type == B200Q_TYPE_Q4_K)
+        return launch_kq_t<B200Q_TYPE_Q4_K>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
+    return fail(ctx, B200Q_UNSUPPORTED, "gemm_kq_id: type %d", src0->type);
 }
 
 }  // namespace b200q

@@ -22,16 +22,16 @@ struct RouteEntry {
     uint64_t gen = 0;
     bool    valid = false;
     int     experts_per_owner = 0;
-    Workspace buf;               // pairs | 4 tile lists | 4 counters
+    Workspace buf;               // pairs | 5 tile lists | 8 counters | owner counts
     RouteView view;
 };
 
 __global__ void __launch_bounds__(1024)
 moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_expert, int32_t *pairs,
-                 int32_t *tiles0, int32_t *tiles1, int32_t *tiles2, int32_t *tiles3, int32_t *n_tiles,
+                 int32_t *tiles0, int32_t *tiles1, int32_t *tiles2, int32_t *tiles3, int32_t *tiles128, int32_t *n_tiles,
                  int32_t *owner_counts, int experts_per_owner) {
     extern __shared__ int sm[];
-    int *cnt = sm, *base = sm + n_expert, *fill = sm + 2 * n_expert, *toff = sm + 3 * n_expert;   // toff: [4][n_expert]
+    int *cnt = sm, *base = sm + n_expert, *fill = sm + 2 * n_expert, *toff = sm + 3 * n_expert;   // toff: [5][n_expert]
     const int tid = threadIdx.x, nth = blockDim.x;
     const int n_pairs = n_used * n_tok;
     auto expert_of = [&](int p) {
@@ -43,22 +43,24 @@ moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_ex
     __syncthreads();
     for (int p = tid; p < n_pairs; p += nth) atomicAdd(&cnt[expert_of(p)], 1);
     __syncthreads();
-    if (tid < 5) {
-        // five independent prefix sums over the experts, one thread each: the pair offsets and
-        // the tile offsets of the four size classes
+    if (tid < 6) {
+        // six independent prefix sums over the experts, one thread each: the pair offsets, the
+        // tile offsets of the four decode size classes, and of the 128-pair tiles of the
+        // tensor-core path (which covers every pair once more, in its own list)
         int acc = 0;
         for (int e = 0; e < n_expert; ++e) {
             const int c = cnt[e], rem = c & 7;
             int v;
-            if (tid == 4) v = c;
+            if (tid == 5) v = (c + 127) >> 7;
+            else if (tid == 4) v = c;
             else if (tid == 3) v = (c >> 3) + (rem >= 5);
             else if (tid == 2) v = rem == 3 || rem == 4;
             else if (tid == 1) v = rem == 2;
             else v = rem == 1;
-            if (tid == 4) base[e] = acc; else toff[tid * n_expert + e] = acc;
+            if (tid == 4) base[e] = acc; else toff[(tid == 5 ? 4 : tid) * n_expert + e] = acc;
             acc += v;
         }
-        if (tid < 4) n_tiles[tid] = acc;
+        if (tid != 4) n_tiles[tid == 5 ? 4 : tid] = acc;
     }
     __syncthreads();
     for (int e = tid; e < n_expert; e += nth) {
@@ -72,6 +74,8 @@ moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_ex
                                   : tiles0 + 4 * toff[e];
             t[0] = e; t[1] = first + 8 * full; t[2] = rem; t[3] = 0;
         }
+        int32_t *tb = tiles128 + 4 * toff[4 * n_expert + e];
+        for (int k = 0; 128 * k < c; ++k) { tb[4 * k] = e; tb[4 * k + 1] = first + 128 * k; tb[4 * k + 2] = min(128, c - 128 * k); tb[4 * k + 3] = 0; }
     }
     for (int p = tid; p < n_pairs; p += nth) {
         const int e = expert_of(p);
@@ -158,16 +162,16 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     RouteEntry &e = *ctx->routes[pick];
     e.valid = false;
     const int64_t max_tiles = (n_pairs + 7) / 8 + (n_expert < n_pairs ? n_expert : n_pairs);
-    const size_t bytes = sizeof(int32_t) * (size_t)(n_pairs + 4 * 4 * max_tiles + 4 + 4096) + 64;   // + owner counts
+    const size_t bytes = sizeof(int32_t) * (size_t)(n_pairs + 5 * 4 * max_tiles + 8 + 4096) + 64;   // + owner counts
     b200q_status st = ws_reserve(ctx, &e.buf, bytes);
     if (st != B200Q_OK) return st;
     int32_t *p = (int32_t *)e.buf.ptr;
     int32_t *pairs = p;
-    int32_t *tl[4];
-    for (int k = 0; k < 4; ++k) tl[k] = p + n_pairs + (size_t)k * 4 * max_tiles;
-    int32_t *n_tiles = p + n_pairs + (size_t)16 * max_tiles;
-    int32_t *owner_counts = n_tiles + 4;
-    const size_t smem = sizeof(int) * (size_t)n_expert * 7;
+    int32_t *tl[5];
+    for (int k = 0; k < 5; ++k) tl[k] = p + n_pairs + (size_t)k * 4 * max_tiles;
+    int32_t *n_tiles = p + n_pairs + (size_t)20 * max_tiles;
+    int32_t *owner_counts = n_tiles + 8;
+    const size_t smem = sizeof(int) * (size_t)n_expert * 8;
     if (smem > 200 * 1024) return fail(ctx, B200Q_UNSUPPORTED, "route: %d experts", n_expert);
     static bool attr = false;
     if (!attr) {
@@ -175,7 +179,7 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
         attr = true;
     }
     moe_route_kernel<<<1, 1024, smem, ctx->stream>>>((const uint8_t *)ids->data, ids->nb[1], n_used, n_tok, n_expert, pairs,
-                                                     tl[0], tl[1], tl[2], tl[3], n_tiles,
+                                                     tl[0], tl[1], tl[2], tl[3], tl[4], n_tiles,
                                                      experts_per_owner > 0 ? owner_counts : nullptr,
                                                      experts_per_owner > 0 ? experts_per_owner : 1);
     B200Q_CUDA(ctx, cudaGetLastError());
@@ -188,6 +192,8 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     e.gen = ctx->generation;
     e.view.pairs = pairs;
     for (int k = 0; k < 4; ++k) e.view.tiles[k] = tl[k];
+    e.view.tiles128 = tl[4];
+    e.view.max_tiles128 = (n_pairs + 127) / 128 + (n_expert < n_pairs ? n_expert : n_pairs);
     e.view.n_tiles = n_tiles;
     e.view.max_tiles = max_tiles;
     e.view.owner_counts = owner_counts;

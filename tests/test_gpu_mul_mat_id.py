@@ -131,3 +131,50 @@ def test_mul_mat_id_shape_errors(ctx):
     assert ctx.L.b200q_mul_mat_id(ctx.h, W, A.Tensor.f32(d, [256, 1, 3]), I, A.Tensor.f32(d, [8, 3, 3])) == A.INVALID
     assert ctx.supports(A.OP_MUL_MAT_ID, W, A.Tensor.f32(d, [256, 1, 3]), I, Y) == A.OK
     ctx.free(d)
+
+
+# ---- prompt-sized batches: the route's 128-pair tiles through the tensor-core GEMM ----
+
+@pytest.mark.parametrize("t", [A.Q4_K, A.IQ4_XS])
+@pytest.mark.parametrize("n_expert,n_used,n_tok,ne11_is_one", [(8, 2, 300, True), (8, 2, 300, False), (4, 4, 700, True),
+                                                               (32, 8, 64, False)])
+def test_mul_mat_id_tensor_core_tiles(ctx, t, n_expert, n_used, n_tok, ne11_is_one):
+    st = check(ctx, t, n_expert=n_expert, n_used=n_used, n_tok=n_tok, m=200, k=1024, ne11_is_one=ne11_is_one,
+               seed=n_tok + n_expert)
+    assert st.get("moe_gemm", 0) == 1 and st.get("gemm_tc", 0) == 1, st
+    assert st.get("gemv_id", 0) + st.get("gemv_id_unaligned", 0) == 0
+
+
+def test_mul_mat_id_tensor_core_skewed_route_duplicates_offset(ctx):
+    """Zipf-skewed routing (some experts with hundreds of pairs, some with none), the same expert in
+    several slots of a token, ids read through an offset view."""
+    t, n_expert, n_used, n_tok, m, k = A.Q4_K, 16, 4, 400, 136, 512
+    rng = np.random.default_rng(11)
+    w = np.stack([O.random_blocks(t, m, k, rng) for _ in range(n_expert)])
+    ids_full = np.concatenate([rng.integers(0, n_expert, (n_tok, 2)).astype(np.int32),
+                               O.route_ids(n_used, n_tok, n_expert, 5, 2.0)], axis=1)
+    ids_full[::3, 3] = ids_full[::3, 2]
+    ids_full[:, :][ids_full == 7] = 6                                     # expert 7 gets nothing
+    x = rng.normal(0, 1, size=(n_tok, n_used, k)).astype(np.float32)
+    got, st = run_id(ctx, t, w, m, k, x, ids_full, 2, n_used)
+    assert st.get("moe_gemm", 0) == 1
+    ref = O.mul_mat_id(t, w, m, k, x, ids_full[:, 2:2 + n_used], f64=True)
+    assert rel_err(got.reshape(-1, m), ref.reshape(-1, m)) < TOL
+
+
+def test_config5_moe_q4_K_prompt_batch(ctx):
+    """BASELINE config 5 at a prompt batch: 512 experts, top-10, 2048 tokens, gate shape 512 x 2048;
+    sampled tokens against the oracle."""
+    t, n_expert, n_used, n_tok, m, k = A.Q4_K, 512, 10, 2048, 512, 2048
+    rng = np.random.default_rng(12)
+    base = [O.random_blocks(t, m, k, rng) for _ in range(4)]
+    w = np.stack([base[e % 4] for e in range(n_expert)])
+    w[:, :, 0] = (np.arange(n_expert) % 251)[:, None]
+    ids = O.route_ids(n_used, n_tok, n_expert, 0x5EED0800)
+    x = O.fill_normal(n_tok * k, 13, 1.0).reshape(n_tok, 1, k)
+    got, st = run_id(ctx, t, w, m, k, x, ids, 0, n_used)
+    assert st.get("moe_gemm", 0) == 1
+    ts = np.arange(0, n_tok, 97)
+    ref = O.mul_mat_id(t, w, m, k, x[ts], np.ascontiguousarray(ids[ts]), f64=True)
+    assert rel_err(got[ts].reshape(-1, m), ref.reshape(-1, m)) < TOL
+    assert np.isfinite(got).all()
