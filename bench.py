@@ -428,6 +428,14 @@ def run_gpu(args, rank, world):
         dist = dist_mod
     device = int(os.environ.get("LOCAL_RANK", 0)) if world > 1 else 0
     ctx = A.Context(device)
+    if world > 1:
+        # the library's own communicator (tensor-parallel trace, expert-parallel MoE): rank 0's id to all
+        import torch
+        idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            idt = torch.frombuffer(bytearray(A.tp_unique_id()), dtype=torch.uint8).clone().cuda()
+        dist.broadcast(idt, 0)
+        ctx.tp_init(bytes(idt.cpu().numpy().tobytes()), rank, world)
     mats, xs = build_decode_inputs()
 
     # device copies: each shape rotates over enough copies to exceed 4x L2
@@ -578,7 +586,7 @@ def run_gpu(args, rank, world):
     moe = moe_section(ctx, world, rank, dist)
 
     cpu = None
-    if rank == 0:
+    if rank == 0 and world == 1:           # the CPU leg runs at N=1 only (idle ranks would spin on the host cores it needs)
         cpu_threads = len(os.sched_getaffinity(0))       # torchrun pins OMP_NUM_THREADS to 1: ask for the cores explicitly
         t0 = time.perf_counter()
         reps_cpu = 0
