@@ -54,6 +54,10 @@ constexpr int NA = 8;                                     // A-operand slots (bl
 constexpr int NBUF = 2;                                   // accumulator pairs (hi, lo)
 constexpr int NW = 2;
 constexpr int THREADS = 32 * (12 + 4 * NW);               // warp groups: {producer, MMA, 2 idle}, 2 x unpack, NW x scale-accumulate
+// Registers per thread by role (setmaxnreg): a warp group that asks for more waits until others have
+// given theirs back, so the sum must fit the pool the launch allocated (THREADS x LAUNCH_REGS).
+constexpr int LAUNCH_REGS = (65536 / THREADS) / 8 * 8;
+static_assert(128 * 40 + 256 * 72 + 128 * NW * 144 <= THREADS * LAUNCH_REGS, "register pool: 40 control, 72 unpack, 144 scale-accumulate");
 constexpr int OPER_BYTES = BM * KB;                       // 4096
 constexpr int ACT_CHUNK = SB * OPER_BYTES + BN * 4;       // codes of a super-block + one f32 scale per token
 constexpr int A_SLOT = 2 * OPER_BYTES;                    // hi limb, lo limb
@@ -85,13 +89,6 @@ constexpr int NG = NA / GB;                               // groups in the ring
 enum { BAR_RAW_FULL = 0, BAR_RAW_EMPTY = 4, BAR_ACT_FULL = 8, BAR_ACT_EMPTY = 10, BAR_A_FULL = 12, BAR_A_EMPTY = 14,
        BAR_ACC_FULL = 16, BAR_ACC_EMPTY = 18, BAR_COUNT = 20 };
 static_assert(NG == 2 && NACT == 2 && NBUF == 2, "barrier slots above");
-
-// D (+)= A x B^T with the accumulate flag as an operand
-__device__ __forceinline__ void umma_i8_acc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
 
 // After all chunks: the block sums, [chunk][column < 128][block < 8] int16.
 // Activation chunk (128-token tile t, super-block s), per-256 form (the reference's
@@ -204,31 +201,49 @@ __device__ __forceinline__ void unpack_group(const uint8_t *blk, int jg, int kh,
     }
 }
 
+// One unit of work: a 128-row x 128-column output tile. Dense: tile_n-th run of 128 tokens; MUL_MAT_ID:
+// route tile tile_n (one expert, up to 128 routed pairs).
+struct Unit {
+    int tile_n, row0, valid_rows, expert, first, ncols;
+};
+
 template <int TYPE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
-               int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word, TileRoute id) {
+               int N, int n_tiles_dense, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word, TileRoute id) {
     typedef Smem<TYPE> L;
     constexpr int SBB = L::SBB, SPS = L::SPS, NRAW = L::NRAW, ROWB = L::ROWB;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
-    const int row0 = tile_m * BM;
     const int nsb = K / 256;                    // super-blocks (a multiple of SPS: the host gate)
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bars = sbase + L::BAR_OFF;
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
-    const int valid_rows = min(BM, M - row0);
-    // the tile's matrix and columns: dense, tile_n-th run of 128 tokens; MUL_MAT_ID, a route tile
-    int expert = 0, first = 0, ncols = min(BN, N - tile_n * BN);
-    if (id.tiles) {
-        if (tile_n >= __ldg(id.n_tiles)) return;          // the whole block: nothing is set up yet
-        expert = __ldg(id.tiles + 4 * tile_n);
-        first = __ldg(id.tiles + 4 * tile_n + 1);
-        ncols = __ldg(id.tiles + 4 * tile_n + 2);
-    }
+    // The block is persistent: it walks the units blockIdx.x, blockIdx.x + gridDim.x, ... and every role
+    // keeps running counters for its rings, so the pipeline never drains between units (the loads,
+    // the unpacking and the MMAs of the next tile run while the last tile's results are stored).
+    // Units of one row tile are neighbours, so blocks running together share weight rows in L2.
+    const int tiles_m = (M + BM - 1) / BM;
+    const int tiles_n = id.tiles ? __ldg(id.n_tiles) : n_tiles_dense;
+    const int n_units = tiles_m * tiles_n;
+    auto unit_of = [&](int u) {
+        Unit U;
+        U.tile_n = u % tiles_n;
+        U.row0 = (u / tiles_n) * BM;
+        U.valid_rows = min(BM, M - U.row0);
+        U.expert = 0;
+        U.first = 0;
+        U.ncols = min(BN, N - U.tile_n * BN);
+        if (id.tiles) {
+            U.expert = __ldg(id.tiles + 4 * U.tile_n);
+            U.first = __ldg(id.tiles + 4 * U.tile_n + 1);
+            U.ncols = __ldg(id.tiles + 4 * U.tile_n + 2);
+        }
+        return U;
+    };
+    if ((int)blockIdx.x >= n_units) return;               // the whole block: nothing is set up yet
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -265,54 +280,64 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     if (warp == 0) {
         // ---- producer ----
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
-        const uint8_t *act_tile = act + (size_t)tile_n * nsb * ACT_CHUNK;
         if (lane == 0) tma_prefetch_desc(&wmap);
-        for (int s = 0; s < nsb; ++s) {
-            if (s % SPS == 0) {
-                const int rs = s / SPS, st = rs % NRAW;
-                if (!WAITP(1, bar(BAR_RAW_EMPTY + st), ((rs / NRAW) & 1) ^ 1)) break;
-                if (lane == 0) {
-                    // the whole [128 rows x ROWB] box in one tiled copy; rows past M arrive as zeros
-                    mbar_expect_tx(bar(BAR_RAW_FULL + st), L::RAW_STAGE);
-                    tma_load_3d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, rs * (ROWB / 4), row0, expert, bar(BAR_RAW_FULL + st));
+        int rs_run = 0, s_run = 0;                        // raw stages and super-blocks fetched so far
+        bool ok = true;
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            const Unit U = unit_of(u);
+            const uint8_t *act_tile = act + (size_t)U.tile_n * nsb * ACT_CHUNK;
+            for (int s = 0; s < nsb; ++s, ++s_run) {
+                if (s % SPS == 0) {
+                    const int st = rs_run % NRAW;
+                    if (!WAITP(1, bar(BAR_RAW_EMPTY + st), ((rs_run / NRAW) & 1) ^ 1)) { ok = false; break; }
+                    if (lane == 0) {
+                        // the whole [128 rows x ROWB] box in one tiled copy; rows past M arrive as zeros
+                        mbar_expect_tx(bar(BAR_RAW_FULL + st), L::RAW_STAGE);
+                        tma_load_3d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, (s / SPS) * (ROWB / 4), U.row0, U.expert,
+                                    bar(BAR_RAW_FULL + st));
+                    }
+                    ++rs_run;
                 }
+                const int at = s_run % NACT;
+                if (!WAITP(3, bar(BAR_ACT_EMPTY + at), ((s_run / NACT) & 1) ^ 1)) { ok = false; break; }
+                if (lane == 0) {
+                    mbar_expect_tx(bar(BAR_ACT_FULL + at), ACT_CHUNK);
+                    bulk_g2s(sbase + L::ACT_OFF + at * ACT_CHUNK, act_tile + (size_t)s * ACT_CHUNK, ACT_CHUNK, bar(BAR_ACT_FULL + at));
+                }
+                __syncwarp();
             }
-            const int at = s % NACT;
-            if (!WAITP(3, bar(BAR_ACT_EMPTY + at), ((s / NACT) & 1) ^ 1)) break;
-            if (lane == 0) {
-                mbar_expect_tx(bar(BAR_ACT_FULL + at), ACT_CHUNK);
-                bulk_g2s(sbase + L::ACT_OFF + at * ACT_CHUNK, act_tile + (size_t)s * ACT_CHUNK, ACT_CHUNK, bar(BAR_ACT_FULL + at));
-            }
-            __syncwarp();
         }
     } else if (warp == 1) {
         // ---- MMA issuer: per block one MMA per limb, accumulating over the super-block ----
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+        int s_run = 0;
         bool ok = true;
-        for (int s = 0; s < nsb && ok; ++s) {
-            const int at = s % NACT, buf = s % NBUF;
-            if (!WAITP(2, bar(BAR_ACT_FULL + at), (s / NACT) & 1)) break;
-            if (!WAITP(7, bar(BAR_ACC_EMPTY + buf), ((s / NBUF) & 1) ^ 1)) break;
-            for (int jg = 0; jg < SB / GB; ++jg) {
-                const int g = s * (SB / GB) + jg, gs = g % NG;          // group index, its place in the ring
-                if (!WAITP(4, bar(BAR_A_FULL + gs), (g / NG) & 1)) { ok = false; break; }
-                tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t d = tmem_base + (uint32_t)buf * (2 * BN);
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            for (int s = 0; s < nsb && ok; ++s, ++s_run) {
+                const int at = s_run % NACT, buf = s_run % NBUF;
+                if (!WAITP(2, bar(BAR_ACT_FULL + at), (s_run / NACT) & 1)) { ok = false; break; }
+                if (!WAITP(7, bar(BAR_ACC_EMPTY + buf), ((s_run / NBUF) & 1) ^ 1)) { ok = false; break; }
+                for (int jg = 0; jg < SB / GB; ++jg) {
+                    const int g = s_run * (SB / GB) + jg, gs = g % NG;          // group index, its place in the ring
+                    if (!WAITP(4, bar(BAR_A_FULL + gs), (g / NG) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t d = tmem_base + (uint32_t)buf * (2 * BN);
 #pragma unroll
-                    for (int jj = 0; jj < GB; ++jj) {
-                        const int j = jg * GB + jj, slot = gs * GB + jj;
-                        const uint64_t db = umma_desc(sbase + L::ACT_OFF + at * ACT_CHUNK + j * OPER_BYTES);
-                        umma_i8_acc(d, umma_desc(sbase + L::A_OFF + slot * A_SLOT), db, IDESC, j > 0);
-                        umma_i8_acc(d + BN, umma_desc(sbase + L::A_OFF + slot * A_SLOT + OPER_BYTES), db, IDESC, j > 0);
+                        for (int jj = 0; jj < GB; ++jj) {
+                            const int j = jg * GB + jj, slot = gs * GB + jj;
+                            const uint64_t db = umma_desc(sbase + L::ACT_OFF + at * ACT_CHUNK + j * OPER_BYTES);
+                            umma_i8_acc(d, umma_desc(sbase + L::A_OFF + slot * A_SLOT), db, IDESC, j > 0);
+                            umma_i8_acc(d + BN, umma_desc(sbase + L::A_OFF + slot * A_SLOT + OPER_BYTES), db, IDESC, j > 0);
+                        }
+                        tc_commit(bar(BAR_A_EMPTY + gs));
+                        if (jg == SB / GB - 1) {
+                            tc_commit(bar(BAR_ACC_FULL + buf));
+                            tc_commit(bar(BAR_ACT_EMPTY + at));
+                        }
                     }
-                    tc_commit(bar(BAR_A_EMPTY + gs));
-                    if (jg == SB / GB - 1) {
-                        tc_commit(bar(BAR_ACC_FULL + buf));
-                        tc_commit(bar(BAR_ACT_EMPTY + at));
-                    }
+                    __syncwarp();
                 }
-                __syncwarp();
             }
         }
     } else if (warp < 4) {
@@ -323,101 +348,110 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         // A half-warp holds eight rows times the two halves, so that the two threads of a row read
         // neighbouring shared-memory words and rows fall on distinct banks.
         const int r = (warp - 4) * 16 + (lane >> 4) * 8 + (lane & 7), kh = (lane >> 3) & 1;
-        const bool row_ok = r < valid_rows;
+        int rs_run = 0, g_run = 0;
         bool ok = true;
-        for (int rs = 0; rs < nsb / SPS && ok; ++rs) {
-            const int st = rs % NRAW;
-            if (!WAITP(0, bar(BAR_RAW_FULL + st), (rs / NRAW) & 1)) break;
-            const uint8_t *rowp = smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB;
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            const bool row_ok = r < unit_of(u).valid_rows;
+            for (int rs = 0; rs < nsb / SPS && ok; ++rs, ++rs_run) {
+                const int st = rs_run % NRAW;
+                if (!WAITP(0, bar(BAR_RAW_FULL + st), (rs_run / NRAW) & 1)) { ok = false; break; }
+                const uint8_t *rowp = smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB;
 #pragma unroll
-            for (int h = 0; h < SPS; ++h) {
+                for (int h = 0; h < SPS; ++h) {
 #pragma unroll
-                for (int jg = 0; jg < SB / GB; ++jg) {
-                    const int g = (SPS * rs + h) * (SB / GB) + jg, gs = g % NG;
-                    if (!WAITP(5, bar(BAR_A_EMPTY + gs), ((g / NG) & 1) ^ 1)) { ok = false; break; }
-                    unpack_group<TYPE>(rowp + SBB * h, jg, kh, row_ok,
-                                       smem + L::A_OFF + (gs * GB) * A_SLOT + (r >> 3) * 128 + (r & 7) * 16);
-                    fence_async_smem();                  // one proxy fence per group of blocks
-                    mbar_arrive_warp(bar(BAR_A_FULL + gs), lane);
+                    for (int jg = 0; jg < SB / GB; ++jg) {
+                        const int g = g_run + h * (SB / GB) + jg, gs = g % NG;
+                        if (!WAITP(5, bar(BAR_A_EMPTY + gs), ((g / NG) & 1) ^ 1)) { ok = false; break; }
+                        unpack_group<TYPE>(rowp + SBB * h, jg, kh, row_ok,
+                                           smem + L::A_OFF + (gs * GB) * A_SLOT + (r >> 3) * 128 + (r & 7) * 16);
+                        fence_async_smem();                  // one proxy fence per group of blocks
+                        mbar_arrive_warp(bar(BAR_A_FULL + gs), lane);
+                    }
+                    if (!ok) break;
                 }
-                if (!ok) break;
+                g_run += SPS * (SB / GB);
+                if (ok) mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
             }
-            if (ok) mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
         }
     } else {
         // ---- scale-accumulate, once per super-block ----
         asm volatile("setmaxnreg.inc.sync.aligned.u32 144;" ::: "memory");
         constexpr int CW = BN / NW;
-        const int q4 = warp & 3, u = (warp - 12) >> 2;
+        const int q4 = warp & 3, u4 = (warp - 12) >> 2;
         const int r = q4 * 32 + lane;
-        const bool row_ok = r < valid_rows;
-        f32x2 acc2[CW / 2];
+        int rs_run = 0, s_run = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            const Unit U = unit_of(u);
+            const bool row_ok = r < U.valid_rows;
+            f32x2 acc2[CW / 2];
 #pragma unroll
-        for (int c = 0; c < CW / 2; ++c) acc2[c] = 0ull;
-        bool done = false;
-        for (int s = 0; s < nsb; ++s) {
-            const int rs = s / SPS, st = rs % NRAW, at = s % NACT, buf = s % NBUF;
-            // stage barriers cannot advance past this thread: it releases both stages itself
-            if (s % SPS == 0 && !WAITP(0, bar(BAR_RAW_FULL + st), (rs / NRAW) & 1)) break;
-            if (!WAITP(2, bar(BAR_ACT_FULL + at), (s / NACT) & 1)) break;
-            if (!WAITP(6, bar(BAR_ACC_FULL + buf), (s / NBUF) & 1)) break;
-            tc_fence_after();
-            const float dwb = row_ok ? half_bits_to_float(*reinterpret_cast<const uint16_t *>(
-                                           smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + SBB * (s % SPS))) : 0.f;
-            const f32x2 dw2 = f2_pack(dwb, dwb);
-            const uint32_t dxa = sbase + L::ACT_OFF + at * ACT_CHUNK + SB * OPER_BYTES + (u * CW) * 4;
-            const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * (2 * BN) + (uint32_t)u * CW;
+            for (int c = 0; c < CW / 2; ++c) acc2[c] = 0ull;
+            for (int s = 0; s < nsb; ++s, ++s_run) {
+                if (s % SPS == 0 && s > 0) ++rs_run;
+                const int st = rs_run % NRAW, at = s_run % NACT, buf = s_run % NBUF;
+                // stage barriers cannot advance past this thread: it releases both stages itself
+                if (s % SPS == 0 && !WAITP(0, bar(BAR_RAW_FULL + st), (rs_run / NRAW) & 1)) { ok = false; break; }
+                if (!WAITP(2, bar(BAR_ACT_FULL + at), (s_run / NACT) & 1)) { ok = false; break; }
+                if (!WAITP(6, bar(BAR_ACC_FULL + buf), (s_run / NBUF) & 1)) { ok = false; break; }
+                tc_fence_after();
+                const float dwb = row_ok ? half_bits_to_float(*reinterpret_cast<const uint16_t *>(
+                                               smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + SBB * (s % SPS))) : 0.f;
+                const f32x2 dw2 = f2_pack(dwb, dwb);
+                const uint32_t dxa = sbase + L::ACT_OFF + at * ACT_CHUNK + SB * OPER_BYTES + (u4 * CW) * 4;
+                const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * (2 * BN) + (uint32_t)u4 * CW;
 #pragma unroll
-            for (int q = 0; q < CW / 16; ++q) {
-                uint32_t vh[16], vl[16];
-                tmem_ld16(taddr + q * 16, vh);
-                tmem_ld16(taddr + BN + q * 16, vl);
-                f32x2 dx[8];                             // sixteen activation scales, in flight under the tensor-memory loads
+                for (int q = 0; q < CW / 16; ++q) {
+                    uint32_t vh[16], vl[16];
+                    tmem_ld16(taddr + q * 16, vh);
+                    tmem_ld16(taddr + BN + q * 16, vl);
+                    f32x2 dx[8];                             // sixteen activation scales, in flight under the tensor-memory loads
 #pragma unroll
-                for (int c = 0; c < 4; ++c) lds128_f2(dxa + (q * 16 + 4 * c) * 4, dx[2 * c], dx[2 * c + 1]);
-                tmem_ld_wait();
-                if (q == CW / 16 - 1) {
-                    tc_fence_before();
-                    mbar_arrive_warp(bar(BAR_ACC_EMPTY + buf), lane);
+                    for (int c = 0; c < 4; ++c) lds128_f2(dxa + (q * 16 + 4 * c) * 4, dx[2 * c], dx[2 * c + 1]);
+                    tmem_ld_wait();
+                    if (q == CW / 16 - 1) {
+                        tc_fence_before();
+                        mbar_arrive_warp(bar(BAR_ACC_EMPTY + buf), lane);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 16; c += 4) {
+                        const int e = (q * 16 + c) / 2;
+                        // 256 hi + lo as an integer, one rounding to float (ggml's float(sumi))
+                        const f32x2 s01 = f2_pack(__int2float_rn((int)vl[c] + ((int)vh[c] << 8)), __int2float_rn((int)vl[c + 1] + ((int)vh[c + 1] << 8)));
+                        const f32x2 s23 = f2_pack(__int2float_rn((int)vl[c + 2] + ((int)vh[c + 2] << 8)), __int2float_rn((int)vl[c + 3] + ((int)vh[c + 3] << 8)));
+                        acc2[e]     = f2_fma(s01, f2_mul(dw2, dx[c / 2]), acc2[e]);
+                        acc2[e + 1] = f2_fma(s23, f2_mul(dw2, dx[c / 2 + 1]), acc2[e + 1]);
+                    }
                 }
-#pragma unroll
-                for (int c = 0; c < 16; c += 4) {
-                    const int e = (q * 16 + c) / 2;
-                    // 256 hi + lo as an integer, one rounding to float (ggml's float(sumi))
-                    const f32x2 s01 = f2_pack(__int2float_rn((int)vl[c] + ((int)vh[c] << 8)), __int2float_rn((int)vl[c + 1] + ((int)vh[c + 1] << 8)));
-                    const f32x2 s23 = f2_pack(__int2float_rn((int)vl[c + 2] + ((int)vh[c + 2] << 8)), __int2float_rn((int)vl[c + 3] + ((int)vh[c + 3] << 8)));
-                    acc2[e]     = f2_fma(s01, f2_mul(dw2, dx[c / 2]), acc2[e]);
-                    acc2[e + 1] = f2_fma(s23, f2_mul(dw2, dx[c / 2 + 1]), acc2[e + 1]);
-                }
+                mbar_arrive_warp(bar(BAR_ACT_EMPTY + at), lane);
+                if (s % SPS == SPS - 1) mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
             }
-            mbar_arrive_warp(bar(BAR_ACT_EMPTY + at), lane);
-            if (s % SPS == SPS - 1) mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
-            done = s == nsb - 1;
-        }
-        if (done && row_ok) {
-            const int ncol = ncols - u * CW;                 // this thread's columns inside the tile
-            if (id.tiles) {
+            ++rs_run;                                    // past the unit's last raw stage
+            if (ok && row_ok) {
+                const int ncol = U.ncols - u4 * CW;          // this thread's columns inside the tile
+                if (id.tiles) {
 #pragma unroll
-                for (int c = 0; c < CW; c += 2) {
-                    float a[2];
-                    f2_unpack(acc2[c / 2], a[0], a[1]);
+                    for (int c = 0; c < CW; c += 2) {
+                        float a[2];
+                        f2_unpack(acc2[c / 2], a[0], a[1]);
 #pragma unroll
-                    for (int d = 0; d < 2; ++d)
-                        if (c + d < ncol) {
-                            const int p = __ldg(id.pairs + first + u * CW + c + d), tok = p / id.n_used, slot = p - tok * id.n_used;
-                            dst[tok * id.ld2 + slot * id.ld1 + row0 + r] = a[d];
-                        }
-                }
-            } else {
-                float *o = dst + (int64_t)(tile_n * BN + u * CW) * ldd + row0 + r;
+                        for (int d = 0; d < 2; ++d)
+                            if (c + d < ncol) {
+                                const int p = __ldg(id.pairs + U.first + u4 * CW + c + d), tok = p / id.n_used, slot = p - tok * id.n_used;
+                                dst[tok * id.ld2 + slot * id.ld1 + U.row0 + r] = a[d];
+                            }
+                    }
+                } else {
+                    float *o = dst + (int64_t)(U.tile_n * BN + u4 * CW) * ldd + U.row0 + r;
 #pragma unroll
-                for (int c = 0; c < CW; c += 2) {
-                    float a0, a1;
-                    f2_unpack(acc2[c / 2], a0, a1);
-                    if (c < ncol) *o = a0;
-                    o += ldd;
-                    if (c + 1 < ncol) *o = a1;
-                    o += ldd;
+                    for (int c = 0; c < CW; c += 2) {
+                        float a0, a1;
+                        f2_unpack(acc2[c / 2], a0, a1);
+                        if (c < ncol) *o = a0;
+                        o += ldd;
+                        if (c + 1 < ncol) *o = a1;
+                        o += ldd;
+                    }
                 }
             }
         }
@@ -463,8 +497,11 @@ q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_str
     float acc[MC];
 #pragma unroll
     for (int c = 0; c < MC; ++c) acc[c] = 0.f;
+    uint4 hdr_next = __ldg(reinterpret_cast<const uint4 *>(wrow));          // d, dmin | 12 scale bytes of block 0
     for (int sb = 0; sb < nsb; ++sb) {
         const int pb = sb & 1;
+        const uint4 hdr = hdr_next;
+        if (sb + 1 < nsb) hdr_next = __ldg(reinterpret_cast<const uint4 *>(wrow + (size_t)(sb + 1) * 144));   // in flight under the math
         if (threadIdx.x < MC) {
             const int cc = cc0 + threadIdx.x;
             uint32_t w[4] = { 0, 0, 0, 0 };
@@ -485,7 +522,6 @@ q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_str
             *reinterpret_cast<uint4 *>(cs[pb][threadIdx.x]) = make_uint4(w[0], w[1], w[2], w[3]);
             cdx[pb][threadIdx.x] = dx;
         }
-        const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(wrow + (size_t)sb * 144));
         uint32_t m03, m47;
         q4k_mins8(hdr.y, hdr.z, hdr.w, &m03, &m47);
         const float dmin = row_ok ? half_bits_to_float((uint16_t)(hdr.x >> 16)) : 0.f;
@@ -564,8 +600,10 @@ static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride
     CUtensorMap wmap;
     b200q_status st = make_weight_tmap3(ctx, &wmap, w, row_stride, M, (K / 256) * L::SBB, L::ROWB, n_mat, mat_stride);
     if (st != B200Q_OK) return st;
-    dim3 grid((unsigned)n_tiles, (unsigned)((M + kq::BM - 1) / kq::BM));
-    kern<<<grid, kq::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd, ctx->error_word, tr);
+    // persistent blocks, one per SM, walking the (row tile, column tile) units
+    const int64_t units = n_tiles * ((M + kq::BM - 1) / kq::BM);
+    const unsigned grid = (unsigned)(units < ctx->sm_count ? units : ctx->sm_count);
+    kern<<<grid, kq::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, (int)n_tiles, dst, ldd, ctx->error_word, tr);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
     if (TYPE == B200Q_TYPE_Q4_K) {

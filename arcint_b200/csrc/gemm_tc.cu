@@ -48,8 +48,17 @@ constexpr int SB = 8;              // blocks per k-stage (256 weights)
 constexpr int NACC = 4;            // accumulators in tensor memory (4 x 128 = 512 columns)
 constexpr int OPER_BYTES = BM * KB;                         // one int8 operand block: 4096 B
 constexpr int ACT_CHUNK = SB * OPER_BYTES + SB * BN * 4;    // codes + f32 scales of a stage: 36864 B
-constexpr int NW = 2;              // scale-accumulate warps per tensor-memory lane quarter
+constexpr int NW = 2;              // scale-accumulate warps per tensor-memory lane quarter (4 measured no faster)
 constexpr int THREADS = 32 * (8 + 4 * NW);   // warp groups: {producer, MMA, 2 idle}, unpack, NW x scale-accumulate
+// Registers per thread by role (setmaxnreg). The launch gives every thread LAUNCH_REGS; a warp group that
+// asks for more WAITS until others have given theirs back, so the sum must fit the launch's pool or the
+// block never starts working.
+constexpr int LAUNCH_REGS = (65536 / THREADS) / 8 * 8;
+constexpr int REGS_CTRL = 64, REGS_UNPACK = 112, REGS_SCALE = 168;
+static_assert(128 * REGS_CTRL + 128 * REGS_UNPACK + 128 * NW * REGS_SCALE <= THREADS * LAUNCH_REGS, "register pool");
+static_assert(REGS_CTRL <= LAUNCH_REGS && REGS_UNPACK <= LAUNCH_REGS && REGS_SCALE >= LAUNCH_REGS, "dec / inc directions below");
+#define B200Q_STR2(x) #x
+#define B200Q_STR(x) B200Q_STR2(x)
 
 
 template <int TYPE> struct Raw;     // packed bytes of one row per stage
@@ -179,7 +188,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     // of theirs back, the scale-accumulate groups take them.
     if (warp == 0) {
         // ---- producer ----
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 " B200Q_STR(64) ";" ::: "memory");   // REGS_CTRL
         const uint8_t *act_tile = act + (size_t)tile_n * nst * ACT_CHUNK;
         if (lane == 0) tma_prefetch_desc(&wmap);
         for (int s = 0; s < nst; ++s) {
@@ -201,7 +210,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         }
     } else if (warp == 1) {
         // ---- MMA issuer ----
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 " B200Q_STR(64) ";" ::: "memory");   // REGS_CTRL
         for (int b = 0; b < nblk; ++b) {
             const int s = b / SB, j = b % SB, st = s % NSTAGE, acc = b % NACC;
             if (j == 0 && !WAITP(2, bar(BAR_ACT_FULL + st), (s / NSTAGE) & 1)) break;
@@ -219,10 +228,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         }
     } else if (warp < 4) {
         // idle warps of the first warp group
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 " B200Q_STR(64) ";" ::: "memory");   // REGS_CTRL
     } else if (warp < 8) {
         // ---- unpack: one thread per weight row ----
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 112;" ::: "memory");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 " B200Q_STR(112) ";" ::: "memory");  // REGS_UNPACK
         const int r = (warp - 4) * 32 + lane;
         const bool row_ok = r < valid_rows;
         bool ok = true;
@@ -267,7 +276,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         }
     } else {
         // ---- scale-accumulate: NW warps per tensor-memory lane quarter, BN/NW columns each ----
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 168;" ::: "memory");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 " B200Q_STR(168) ";" ::: "memory");  // REGS_SCALE
         constexpr int CW = BN / NW;                        // columns per thread
         const int q4 = warp & 3, u = (warp - 8) >> 2;      // lane quarter (fixed by warp id % 4), column part
         const int r = q4 * 32 + lane;
