@@ -59,7 +59,11 @@ constexpr int THREADS = 32 * (12 + 4 * NW);               // warp groups: {produ
 constexpr int LAUNCH_REGS = (65536 / THREADS) / 8 * 8;
 static_assert(128 * 40 + 256 * 72 + 128 * NW * 144 <= THREADS * LAUNCH_REGS, "register pool: 40 control, 72 unpack, 144 scale-accumulate");
 constexpr int OPER_BYTES = BM * KB;                       // 4096
-constexpr int ACT_CHUNK = SB * OPER_BYTES + BN * 4;       // codes of a super-block + one f32 scale per token
+// The activation chunk of a (column tile, super-block) is laid out by groups of eight columns, so a tile
+// with few columns (a route tile of a small expert) is a short prefix of it:
+//   group g < 16: [block j < 8][half c < 2][column r < 8][16 bytes] int8 codes (2048 B), then 8 f32 scales
+constexpr int ACT_GROUP = SB * 2 * 128 + 8 * 4;           // 2080
+constexpr int ACT_CHUNK = (BN / 8) * ACT_GROUP;           // 33280
 constexpr int A_SLOT = 2 * OPER_BYTES;                    // hi limb, lo limb
 
 // Per type: bytes of a super-block, super-blocks per raw stage (the stage's row piece must be a
@@ -92,9 +96,7 @@ static_assert(NG == 2 && NACT == 2 && NBUF == 2, "barrier slots above");
 
 // After all chunks: the block sums, [chunk][column < 128][block < 8] int16.
 // Activation chunk (128-token tile t, super-block s), per-256 form (the reference's
-// kernel_quant_i8 rule: scale bm/127, round to nearest even, zero below 1e-30):
-//   codes  [block j < 8][half c < 2][group g < 16][column r < 8][16 bytes]
-//   scales [column < 128] f32
+// kernel_quant_i8 rule: scale bm/127, round to nearest even, zero below 1e-30), in the group layout above.
 __global__ void __launch_bounds__(256)
 quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t nb1, size_t nb2, size_t nb3, int64_t K,
                          int64_t N, uint8_t *__restrict__ out, int16_t *__restrict__ bsum, TileRoute id) {
@@ -103,10 +105,13 @@ quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t n
     const int col = threadIdx.x & 127, half = threadIdx.x >> 7;
     uint8_t *chunk = out + ((size_t)t * nst + s) * ACT_CHUNK;
     const float *x = nullptr;
+    bool store = true;                                    // column groups past the tile's last one are never fetched
     if (id.tiles) {
         // MUL_MAT_ID: the tile's columns are routed pairs; pair p = (token, slot) reads src1 row slot % ne11
         if (t >= __ldg(id.n_tiles)) return;
-        if (col < __ldg(id.tiles + 4 * t + 2)) {
+        const int cnt = __ldg(id.tiles + 4 * t + 2);
+        store = (col >> 3) <= ((cnt - 1) >> 3);
+        if (col < cnt) {
             const int p = __ldg(id.pairs + __ldg(id.tiles + 4 * t + 1) + col), tok = p / id.n_used, slot = p - tok * id.n_used;
             x = reinterpret_cast<const float *>(base + (size_t)(slot % id.ne11) * id.nb1 + (size_t)tok * id.nb2) + (int64_t)s * 256 + 128 * half;
         }
@@ -127,6 +132,7 @@ quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t n
     __syncthreads();
     const float bm = fmaxf(part[col], part[col + 128]);
     const float iq = bm > 1e-30f ? __fdiv_rn(127.f, bm) : 0.f;
+    if (!store) return;
 #pragma unroll 1
     for (int jj = 0; jj < 4; ++jj) {
         const int j = 4 * half + jj;
@@ -137,16 +143,16 @@ quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t n
             w[i] = (uint32_t)(__float2int_rn(__fmul_rn(f.x, iq)) & 0xFF) | ((uint32_t)(__float2int_rn(__fmul_rn(f.y, iq)) & 0xFF) << 8) |
                    ((uint32_t)(__float2int_rn(__fmul_rn(f.z, iq)) & 0xFF) << 16) | ((uint32_t)(__float2int_rn(__fmul_rn(f.w, iq)) & 0xFF) << 24);
         }
-        uint8_t *o = chunk + j * OPER_BYTES + (col >> 3) * 128 + (col & 7) * 16;
+        uint8_t *o = chunk + (col >> 3) * ACT_GROUP + j * 256 + (col & 7) * 16;
         *reinterpret_cast<uint4 *>(o) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4 *>(o + LBO) = make_uint4(w[4], w[5], w[6], w[7]);
+        *reinterpret_cast<uint4 *>(o + 128) = make_uint4(w[4], w[5], w[6], w[7]);
         // the integer sum of the block's 32 codes (Q4_K's mins term): [chunk][column][block] int16
         int sum = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) sum = __dp4a((int)w[i], 0x01010101, sum);
         bsum[(((size_t)t * nst + s) * BN + col) * 8 + j] = (int16_t)sum;
     }
-    if (half == 0) reinterpret_cast<float *>(chunk + SB * OPER_BYTES)[col] = __fdiv_rn(bm, 127.f);
+    if (half == 0) reinterpret_cast<float *>(chunk + (col >> 3) * ACT_GROUP + 2048)[col & 7] = __fdiv_rn(bm, 127.f);
 }
 
 // The A-operand blocks of one group (GB = 4 blocks of 32 weights) of a super-block, written by the
@@ -301,8 +307,11 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 const int at = s_run % NACT;
                 if (!WAITP(3, bar(BAR_ACT_EMPTY + at), ((s_run / NACT) & 1) ^ 1)) { ok = false; break; }
                 if (lane == 0) {
-                    mbar_expect_tx(bar(BAR_ACT_FULL + at), ACT_CHUNK);
-                    bulk_g2s(sbase + L::ACT_OFF + at * ACT_CHUNK, act_tile + (size_t)s * ACT_CHUNK, ACT_CHUNK, bar(BAR_ACT_FULL + at));
+                    // only the column groups the tile has; the MMA still reads 128 columns, the rest of the
+                    // buffer holds older codes whose products land in accumulator columns nobody stores
+                    const uint32_t bytes = (uint32_t)((U.ncols + 7) >> 3) * ACT_GROUP;
+                    mbar_expect_tx(bar(BAR_ACT_FULL + at), bytes);
+                    bulk_g2s(sbase + L::ACT_OFF + at * ACT_CHUNK, act_tile + (size_t)s * ACT_CHUNK, bytes, bar(BAR_ACT_FULL + at));
                 }
                 __syncwarp();
             }
@@ -326,7 +335,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
 #pragma unroll
                         for (int jj = 0; jj < GB; ++jj) {
                             const int j = jg * GB + jj, slot = gs * GB + jj;
-                            const uint64_t db = umma_desc(sbase + L::ACT_OFF + at * ACT_CHUNK + j * OPER_BYTES);
+                            const uint64_t db = umma_desc2(sbase + L::ACT_OFF + at * ACT_CHUNK + j * 256, 128, ACT_GROUP);
                             umma_i8_acc(d, umma_desc(sbase + L::A_OFF + slot * A_SLOT), db, IDESC, j > 0);
                             umma_i8_acc(d + BN, umma_desc(sbase + L::A_OFF + slot * A_SLOT + OPER_BYTES), db, IDESC, j > 0);
                         }
@@ -398,16 +407,24 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 const float dwb = row_ok ? half_bits_to_float(*reinterpret_cast<const uint16_t *>(
                                                smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + SBB * (s % SPS))) : 0.f;
                 const f32x2 dw2 = f2_pack(dwb, dwb);
-                const uint32_t dxa = sbase + L::ACT_OFF + at * ACT_CHUNK + SB * OPER_BYTES + (u4 * CW) * 4;
+                const uint32_t dxa = sbase + L::ACT_OFF + at * ACT_CHUNK + (u4 * CW / 8) * ACT_GROUP + 2048;   // scales of this thread's first group
                 const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * (2 * BN) + (uint32_t)u4 * CW;
+                const int ncol = U.ncols - u4 * CW;          // this thread's columns inside the tile (warp-uniform)
 #pragma unroll
                 for (int q = 0; q < CW / 16; ++q) {
+                    if (q * 16 >= ncol) {                    // a short tile (the ragged end, a small expert): nothing to scale
+                        if (q == CW / 16 - 1) {
+                            tc_fence_before();
+                            mbar_arrive_warp(bar(BAR_ACC_EMPTY + buf), lane);
+                        }
+                        continue;
+                    }
                     uint32_t vh[16], vl[16];
                     tmem_ld16(taddr + q * 16, vh);
                     tmem_ld16(taddr + BN + q * 16, vl);
                     f32x2 dx[8];                             // sixteen activation scales, in flight under the tensor-memory loads
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) lds128_f2(dxa + (q * 16 + 4 * c) * 4, dx[2 * c], dx[2 * c + 1]);
+                    for (int c = 0; c < 4; ++c) lds128_f2(dxa + (2 * q + (c >> 1)) * ACT_GROUP + (c & 1) * 16, dx[2 * c], dx[2 * c + 1]);
                     tmem_ld_wait();
                     if (q == CW / 16 - 1) {
                         tc_fence_before();
@@ -427,21 +444,32 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 if (s % SPS == SPS - 1) mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
             }
             ++rs_run;                                    // past the unit's last raw stage
-            if (ok && row_ok) {
+            if (ok) {
                 const int ncol = U.ncols - u4 * CW;          // this thread's columns inside the tile
                 if (id.tiles) {
+                    // where the warp's 64 columns go: every lane looks up two of them (loads in flight
+                    // together), the store loop takes them by shuffle -- a load and a division per column
+                    // inside that loop would serialize 64 memory latencies
+                    long long off[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        off[h] = 0;
+                        if (lane + 32 * h < ncol) {
+                            const int p = __ldg(id.pairs + U.first + u4 * CW + lane + 32 * h), tok = p / id.n_used, slot = p - tok * id.n_used;
+                            off[h] = tok * id.ld2 + slot * id.ld1;
+                        }
+                    }
 #pragma unroll
                     for (int c = 0; c < CW; c += 2) {
                         float a[2];
                         f2_unpack(acc2[c / 2], a[0], a[1]);
 #pragma unroll
-                        for (int d = 0; d < 2; ++d)
-                            if (c + d < ncol) {
-                                const int p = __ldg(id.pairs + U.first + u4 * CW + c + d), tok = p / id.n_used, slot = p - tok * id.n_used;
-                                dst[tok * id.ld2 + slot * id.ld1 + U.row0 + r] = a[d];
-                            }
+                        for (int d = 0; d < 2; ++d) {
+                            const long long o = __shfl_sync(0xFFFFFFFFu, off[(c + d) >> 5], (c + d) & 31);
+                            if (row_ok && c + d < ncol) dst[o + U.row0 + r] = a[d];
+                        }
                     }
-                } else {
+                } else if (row_ok) {
                     float *o = dst + (int64_t)(U.tile_n * BN + u4 * CW) * ldd + U.row0 + r;
 #pragma unroll
                     for (int c = 0; c < CW; c += 2) {
@@ -517,7 +545,7 @@ q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_str
                     w[i >> 2] |= (uint32_t)(bl & 0xFF) << (8 * (i & 3));
                     w[2 + (i >> 2)] |= (uint32_t)(bh & 0xFF) << (8 * (i & 3));
                 }
-                dx = reinterpret_cast<const float *>(act + chunk * ACT_CHUNK + SB * OPER_BYTES)[cc];
+                dx = reinterpret_cast<const float *>(act + chunk * ACT_CHUNK + (cc >> 3) * ACT_GROUP + 2048)[cc & 7];
             }
             *reinterpret_cast<uint4 *>(cs[pb][threadIdx.x]) = make_uint4(w[0], w[1], w[2], w[3]);
             cdx[pb][threadIdx.x] = dx;
@@ -527,24 +555,48 @@ q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_str
         const float dmin = row_ok ? half_bits_to_float((uint16_t)(hdr.x >> 16)) : 0.f;
         __syncthreads();                       // the other buffer is read by nobody: its readers are two barriers back
 #pragma unroll
-        for (int c = 0; c < MC; ++c) {
-            const uint4 b = *reinterpret_cast<const uint4 *>(cs[pb][c]);
-            const int lo = __dp4a((int)m47, (int)b.y, __dp4a((int)m03, (int)b.x, 0));
-            const int hi = __dp4a((int)m47, (int)b.w, __dp4a((int)m03, (int)b.z, 0));
-            acc[c] = fmaf(dmin * cdx[pb][c], (float)(lo + (hi << 8)), acc[c]);
-        }
-    }
-    if (row_ok) {
+        for (int c8 = 0; c8 < MC; c8 += 8) {
+            if (cc0 + c8 < ncols) {                          // block-uniform: route tiles are mostly short
 #pragma unroll
-        for (int c = 0; c < MC; ++c)
-            if (cc0 + c < ncols) {
-                if (id.tiles) {
-                    const int p = __ldg(id.pairs + first + cc0 + c), tok = p / id.n_used, slot = p - tok * id.n_used;
-                    dst[tok * id.ld2 + slot * id.ld1 + r] -= acc[c];
-                } else {
-                    dst[(int64_t)(tile * BN + cc0 + c) * ldd + r] -= acc[c];
+                for (int c = c8; c < c8 + 8; ++c) {
+                    const uint4 b = *reinterpret_cast<const uint4 *>(cs[pb][c]);
+                    const int lo = __dp4a((int)m47, (int)b.y, __dp4a((int)m03, (int)b.x, 0));
+                    const int hi = __dp4a((int)m47, (int)b.w, __dp4a((int)m03, (int)b.z, 0));
+                    acc[c] = fmaf(dmin * cdx[pb][c], (float)(lo + (hi << 8)), acc[c]);
                 }
             }
+        }
+    }
+    // Read-modify-write of the outputs in two passes, all loads first: a load, a subtraction and a store
+    // per column in one loop would serialize 64 memory latencies. The destinations of the block's columns
+    // are looked up two per lane and handed round by shuffle.
+    long long off[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int c = (threadIdx.x & 31) + 32 * h;
+        off[h] = 0;
+        if (cc0 + c < ncols) {
+            if (id.tiles) {
+                const int p = __ldg(id.pairs + first + cc0 + c), tok = p / id.n_used, slot = p - tok * id.n_used;
+                off[h] = tok * id.ld2 + slot * id.ld1;
+            } else {
+                off[h] = (int64_t)(tile * BN + cc0 + c) * ldd;
+            }
+        }
+    }
+#pragma unroll
+    for (int c0 = 0; c0 < MC; c0 += 16) {
+        float old[16];
+#pragma unroll
+        for (int c = c0; c < c0 + 16; ++c) {
+            const long long o = __shfl_sync(0xFFFFFFFFu, off[c >> 5], c & 31);
+            old[c - c0] = row_ok && cc0 + c < ncols ? dst[o + r] : 0.f;
+        }
+#pragma unroll
+        for (int c = c0; c < c0 + 16; ++c) {
+            const long long o = __shfl_sync(0xFFFFFFFFu, off[c >> 5], c & 31);
+            if (row_ok && cc0 + c < ncols) dst[o + r] = old[c - c0] - acc[c];
+        }
     }
 }
 

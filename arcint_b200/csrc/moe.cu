@@ -41,26 +41,36 @@ moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_ex
     };
     for (int e = tid; e < n_expert; e += nth) { cnt[e] = 0; fill[e] = 0; }
     __syncthreads();
-    for (int p = tid; p < n_pairs; p += nth) atomicAdd(&cnt[expert_of(p)], 1);
+    // eight independent loads in flight per thread (the ids come from global memory)
+    for (int p0 = tid; p0 < n_pairs; p0 += 8 * nth) {
+        int e8[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) e8[k] = p0 + k * nth < n_pairs ? expert_of(p0 + k * nth) : -1;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (e8[k] >= 0) atomicAdd(&cnt[e8[k]], 1);
+    }
     __syncthreads();
-    if (tid < 6) {
-        // six independent prefix sums over the experts, one thread each: the pair offsets, the
-        // tile offsets of the four decode size classes, and of the 128-pair tiles of the
-        // tensor-core path (which covers every pair once more, in its own list)
+    if ((tid & 31) == 0 && tid < 6 * 32) {
+        // six independent prefix sums over the experts, one thread each, each in its own warp (in one
+        // warp the six branches would run one after the other): the pair offsets, the tile offsets
+        // of the four decode size classes, and of the 128-pair tiles of the tensor-core path (which
+        // covers every pair once more, in its own list)
+        const int which = tid >> 5;
         int acc = 0;
         for (int e = 0; e < n_expert; ++e) {
             const int c = cnt[e], rem = c & 7;
             int v;
-            if (tid == 5) v = (c + 127) >> 7;
-            else if (tid == 4) v = c;
-            else if (tid == 3) v = (c >> 3) + (rem >= 5);
-            else if (tid == 2) v = rem == 3 || rem == 4;
-            else if (tid == 1) v = rem == 2;
+            if (which == 5) v = (c + 127) >> 7;
+            else if (which == 4) v = c;
+            else if (which == 3) v = (c >> 3) + (rem >= 5);
+            else if (which == 2) v = rem == 3 || rem == 4;
+            else if (which == 1) v = rem == 2;
             else v = rem == 1;
-            if (tid == 4) base[e] = acc; else toff[(tid == 5 ? 4 : tid) * n_expert + e] = acc;
+            if (which == 4) base[e] = acc; else toff[(which == 5 ? 4 : which) * n_expert + e] = acc;
             acc += v;
         }
-        if (tid != 4) n_tiles[tid == 5 ? 4 : tid] = acc;
+        if (which != 4) n_tiles[which == 5 ? 4 : which] = acc;
     }
     __syncthreads();
     for (int e = tid; e < n_expert; e += nth) {
@@ -77,9 +87,13 @@ moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_ex
         int32_t *tb = tiles128 + 4 * toff[4 * n_expert + e];
         for (int k = 0; 128 * k < c; ++k) { tb[4 * k] = e; tb[4 * k + 1] = first + 128 * k; tb[4 * k + 2] = min(128, c - 128 * k); tb[4 * k + 3] = 0; }
     }
-    for (int p = tid; p < n_pairs; p += nth) {
-        const int e = expert_of(p);
-        pairs[base[e] + atomicAdd(&fill[e], 1)] = p;
+    for (int p0 = tid; p0 < n_pairs; p0 += 8 * nth) {
+        int e8[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) e8[k] = p0 + k * nth < n_pairs ? expert_of(p0 + k * nth) : -1;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (e8[k] >= 0) pairs[base[e8[k]] + atomicAdd(&fill[e8[k]], 1)] = p0 + k * nth;
     }
     // expert parallelism: how many pairs go to each owner (experts are owned in contiguous ranges)
     if (owner_counts) {

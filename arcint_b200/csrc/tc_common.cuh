@@ -81,6 +81,10 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 __device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
     return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)(LBO >> 4) << 16) | ((uint64_t)(SBO >> 4) << 32) | (1ull << 46);
 }
+// the same with the two strides given: lbo between the 16-byte halves of K, sbo between 8-row groups
+__device__ __forceinline__ uint64_t umma_desc2(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
+}
 // D[128 x 128] (int32, tensor memory) = A[128 x 32] (int8, K-major) x B[128 x 32]^T
 __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\t"
@@ -160,7 +164,7 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 #ifdef B200Q_TC_PROF
 #define PROF_DECL long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_t0_ = clock64();
 #define WAITP(slot, b, par) ([&]() { const long long t_ = clock64(); const bool r_ = mbar_wait_warp(b, par, abortp); prof_[slot] += clock64() - t_; return r_; }())
-#define PROF_DUMP(role) if (lane == 0 && blockIdx.x == 1 && blockIdx.y == 1) printf("%s warp %2d total %lld waits: rawF %lld rawE %lld actF %lld actE %lld aF %lld aE %lld accF %lld accE %lld\n", role, warp, clock64() - prof_t0_, prof_[0], prof_[1], prof_[2], prof_[3], prof_[4], prof_[5], prof_[6], prof_[7]);
+#define PROF_DUMP(role) if (lane == 0 && blockIdx.x == 1 && blockIdx.y == (gridDim.y > 1 ? 1 : 0)) printf("%s warp %2d total %lld waits: rawF %lld rawE %lld actF %lld actE %lld aF %lld aE %lld accF %lld accE %lld\n", role, warp, clock64() - prof_t0_, prof_[0], prof_[1], prof_[2], prof_[3], prof_[4], prof_[5], prof_[6], prof_[7]);
 #else
 #define PROF_DECL
 #define WAITP(slot, b, par) mbar_wait_warp(b, par, abortp)
