@@ -45,8 +45,8 @@ static b200q_status launch_one(b200q_ctx *ctx, const void *w, size_t row_stride,
     const int64_t cap = (int64_t)ctx->sm_count * occ[aligned];
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    kern<<<(unsigned)blocks, WARPS * 32, smem, ctx->stream>>>((const uint8_t *)w, row_stride, (int)M,
-                                                              (int)(K / GemvFmt<TYPE>::BLK_W), act, dst, (int)ldd, id);
+    B200Q_CUDA(ctx, launch_pdl(!ctx->no_pdl, kern, dim3((unsigned)blocks), dim3(WARPS * 32), smem, ctx->stream,
+                               (const uint8_t *)w, row_stride, (int)M, (int)(K / GemvFmt<TYPE>::BLK_W), act, dst, (int)ldd, id));
     B200Q_CUDA(ctx, cudaGetLastError());
     return B200Q_OK;
 }

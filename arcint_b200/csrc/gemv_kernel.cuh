@@ -2,6 +2,7 @@
 #pragma once
 
 #include "gemv_core.cuh"
+#include "pdl.cuh"
 
 namespace b200q {
 
@@ -58,6 +59,7 @@ gemv_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk, G
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint8_t *ring = smem + warp * (NSETS * B * S::SLOT);
+    if (ID) pdl_wait();                  // the route (tile lists, counts) comes from the kernel before
 
     const int row_bytes = nblk * F::BLK_B;
     const int nstages = (nblk + F::STAGE_BLOCKS - 1) / F::STAGE_BLOCKS;
@@ -108,6 +110,9 @@ gemv_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk, G
     float acc[B][NC];
 #pragma unroll
     for (int i = 0; i < NSETS - 1; ++i) issue();
+    // the first weight stages are in flight; the activation (the quantizer's output) and dst (which
+    // an earlier kernel may still be writing or reading) are touched only after this
+    if (!ID) pdl_wait();
     int c_set = 0;
     for (int u = gw; u < n_units; u += tw) {
         // this unit's columns: where each reads its activation and writes its result
@@ -184,6 +189,9 @@ gemv_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk, G
                 if (lane == 0 && row0 + r < M && c < ncol) dst[outs[c] + row0 + r] = v;
             }
     }
+    // this block's work is done: once every block is here the next kernel of the stream may be
+    // scheduled (any earlier and its blocks would take this wave's places on the SMs)
+    pdl_trigger();
     cp_async_wait<0>();
 }
 

@@ -14,6 +14,7 @@
 // Column c of src1 (flattened over dimensions 1..3) lands at codes + c*K.
 #include "formats.cuh"
 #include "common.cuh"
+#include "pdl.cuh"
 
 namespace b200q {
 
@@ -32,6 +33,8 @@ __device__ __forceinline__ const float *col_ptr(const ColAddr &a, int64_t c) {
 __global__ void __launch_bounds__(256)
 quantize_q8_0_kernel(ColAddr src, int64_t K, int64_t ncols, int8_t *__restrict__ codes, uint16_t *__restrict__ d16,
                      int16_t *__restrict__ sums32) {
+    pdl_trigger();
+    pdl_wait();                          // src1 may be the output of the kernel before, the scratch its input
     const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t per_col = K / 4;
     const int64_t c = gid / per_col, i4 = gid % per_col;
@@ -64,6 +67,8 @@ quantize_q8_0_kernel(ColAddr src, int64_t K, int64_t ncols, int8_t *__restrict__
 __global__ void __launch_bounds__(256)
 quantize_q8_256_kernel(ColAddr src, int64_t K, int64_t ncols, int8_t *__restrict__ codes, float *__restrict__ d32,
                        int16_t *__restrict__ bsums, int16_t *__restrict__ bsums16) {
+    pdl_trigger();
+    pdl_wait();                          // src1 may be the output of the kernel before, the scratch its input
     const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int64_t per_col = K / 256;
@@ -111,13 +116,13 @@ b200q_status launch_quantize_act(b200q_ctx *ctx, int form, const b200q_tensor *s
     a.nb3 = src1->nb[3];
     if (form == ACT_Q8_0) {
         const int64_t threads = ncols * (K / 4);
-        quantize_q8_0_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, ctx->stream>>>(a, K, ncols, codes,
-                                                                                       (uint16_t *)scales, bsums);
+        B200Q_CUDA(ctx, launch_pdl(!ctx->no_pdl, quantize_q8_0_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0,
+                                   ctx->stream, a, K, ncols, codes, (uint16_t *)scales, bsums));
         count(ctx, ST_QUANT_Q8_0);
     } else {
         const int64_t warps = ncols * (K / 256);
-        quantize_q8_256_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, ctx->stream>>>(
-            a, K, ncols, codes, (float *)scales, bsums, bsums16);
+        B200Q_CUDA(ctx, launch_pdl(!ctx->no_pdl, quantize_q8_256_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0,
+                                   ctx->stream, a, K, ncols, codes, (float *)scales, bsums, bsums16));
         count(ctx, ST_QUANT_Q8_256);
     }
     B200Q_CUDA(ctx, cudaGetLastError());
