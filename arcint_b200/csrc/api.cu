@@ -233,8 +233,8 @@ b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
     }
     const char *no_tc = getenv("B200Q_NO_TC");      // read once: force the CUDA-core path (tests, comparisons)
     ctx->no_tc = no_tc && no_tc[0] == '1';
-    const char *pdl = getenv("B200Q_PDL");           // programmatic dependent launch in the decode chain: opt-in
-    ctx->no_pdl = !(pdl && pdl[0] == '1');
+    const char *no_pdl = getenv("B200Q_NO_PDL");     // plain stream order in the decode chain (comparisons)
+    ctx->no_pdl = no_pdl && no_pdl[0] == '1';
     *out = ctx;
     return B200Q_OK;
 }

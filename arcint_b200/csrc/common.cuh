@@ -106,7 +106,7 @@ struct b200q_ctx {
     uint64_t     generation = 1;
     bool         capturing = false;
     bool         no_tc = false;           // B200Q_NO_TC=1: never take the tensor-core GEMM
-    bool         no_pdl = true;           // B200Q_PDL=1 switches programmatic dependent launch on in the decode chain
+    bool         no_pdl = false;          // B200Q_NO_PDL=1: plain stream order between the decode kernels
     std::string  last_error;
     std::string  stats_text;
     uint64_t     counters[b200q::ST_COUNT] = {};
