@@ -237,14 +237,18 @@ def tp_trace_section(ctx, world, rank, dist):
     n_layers = 32
     for label, n, reps in (("pp512", 512, 1), ("tg128", 1, 8)):
         kmax = 11008
+        # four activations per layer, as in the model's graph: the attention input feeds q, k and v, the
+        # attention output feeds o, the FFN input feeds gate and up, their product feeds down. One cache
+        # generation per layer, so the library quantizes each of them once (as under a ggml graph).
         x = O.fill_normal(n * kmax, 0x5EED0600 + n, 1.0).reshape(n, kmax)
-        dx = ctx.upload(x)
+        dxs = {key: ctx.upload(x) for key in ("attn_in", "attn_out", "ffn_in", "ffn_mid")}
+        feeds = {"q": "attn_in", "k": "attn_in", "v": "attn_in", "o": "attn_out", "gate": "ffn_in", "up": "ffn_in",
+                 "down": "ffn_mid", "head": "attn_in"}
         dy = ctx.alloc(n * 32000 * 4)
 
         def product(name, layer):
             mc, kc, how, copies = dev[name]
-            ctx.graph_begin()
-            xin = A.Tensor.make(A.F32, [kc, n, 1, 1], [4, 4 * kmax], dx)
+            xin = A.Tensor.make(A.F32, [kc, n, 1, 1], [4, 4 * kmax], dxs[feeds[name]])
             ctx.mul_mat(A.Tensor.weights(t, copies[layer % len(copies)], kc, mc), xin, A.Tensor.f32(dy, [mc, n]))
             if how == "row" and world > 1:
                 ctx.all_reduce_f32(dy, n * mc)
@@ -252,13 +256,17 @@ def tp_trace_section(ctx, world, rank, dist):
         def trace():
             for _ in range(reps):
                 for layer in range(n_layers):
+                    ctx.graph_begin()
                     for name, _, _, _ in shapes:
                         product(name, layer)
+                ctx.graph_begin()
                 product("head", 0)
 
         for layer in range(2):
+            ctx.graph_begin()
             for name, _, _, _ in shapes:
                 product(name, layer)
+        ctx.graph_begin()
         product("head", 0)
         ctx.sync()
         how_run = "CUDA-graph replay"
@@ -288,7 +296,8 @@ def tp_trace_section(ctx, world, rank, dist):
         else:
             rec["weight_gbs"] = bytes_w / (ms * 1e-3) / 1e9
         out.append(rec)
-        ctx.free(dx)
+        for ptr in dxs.values():
+            ctx.free(ptr)
         ctx.free(dy)
     for mc, kc, how, copies in dev.values():
         for ptr in copies:
