@@ -104,6 +104,7 @@ struct b200q_ctx {
     bool         own_stream = false;
     int          sm_count = 148;
     uint64_t     generation = 1;
+    uint64_t     private_generation = 0;  // expert-parallel calls: generations of their internal products
     bool         capturing = false;
     bool         no_tc = false;           // B200Q_NO_TC=1: never take the tensor-core GEMM
     bool         no_pdl = false;          // B200Q_NO_PDL=1: plain stream order between the decode kernels

@@ -203,8 +203,9 @@ b200q_status b200q_all_to_all_v(b200q_ctx *ctx, const void *dev_send, const size
 // exchanges the per-owner counts (one small all-gather and one host synchronisation: the send and receive
 // sizes must be known on the host), sends every pair's f32 activation row and owner-local expert index to
 // the owner (all-to-all), runs b200q_mul_mat_id over what it received, returns the result rows (all-to-all)
-// and scatters them into dst. It starts a new cache generation on the context (its receive buffers are
-// reused with other contents by the next call).
+// and scatters them into dst. The local product runs under a private cache generation (the receive
+// buffers are reused with other contents by the next call); the caller's caches, the route of `ids` among them,
+// stay valid across the gate, up and down calls of a layer.
 b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local, const b200q_tensor *src1,
                                  const b200q_tensor *ids, b200q_tensor *dst, int n_expert_total) {
     TpState *tp;
@@ -227,7 +228,6 @@ b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local,
         (src1->ne[1] != 1 && src1->ne[1] != n_used) || src1->ne[2] != n_tok)
         return fail(ctx, B200Q_INVALID, "expert-parallel MUL_MAT_ID shapes");
     B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
-    ++ctx->generation;
 
     // 1. route by global expert (which groups by owner) and count pairs per owner
     RouteView rv;
@@ -276,7 +276,15 @@ b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local,
         y1.type = B200Q_TYPE_F32; y1.data = out;
         y1.ne[0] = M; y1.ne[1] = 1; y1.ne[2] = (int64_t)n_recv; y1.ne[3] = 1;
         y1.nb[0] = 4; y1.nb[1] = rowy; y1.nb[2] = rowy; y1.nb[3] = rowy * n_recv;
-        if ((st = b200q_mul_mat_id(ctx, src0_local, &x1, &id1, &y1)) != B200Q_OK) return st;
+        // The receive buffers are reused with other contents by the next call, so what the local product
+        // caches about them (quantized activation, route) must not outlive it: it runs under a cache
+        // generation of its own, and the caller's generation -- with the route of `ids`, which gate, up and
+        // down of a layer share -- comes back afterwards.
+        const uint64_t caller_gen = ctx->generation;
+        ctx->generation = (1ull << 62) + ++ctx->private_generation;
+        st = b200q_mul_mat_id(ctx, src0_local, &x1, &id1, &y1);
+        ctx->generation = caller_gen;
+        if (st != B200Q_OK) return st;
     }
     // 5. combine: results travel back the way the activations came
     for (int g = 0; g < G; ++g) { zo[g] = ro[g] * rowy; zb[g] = rb[g] * rowy; wo[g] = so[g] * rowy; wb[g] = sb[g] * rowy; }
@@ -284,7 +292,6 @@ b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local,
     b200q::count(ctx, ST_EP_COMBINE);
     st = launch_ep_unpack(ctx, back, rv.pairs, n_used, n_pairs, (int)M, (float *)dst->data, (int64_t)(dst->nb[1] / 4),
                           (int64_t)(dst->nb[2] / 4));
-    ++ctx->generation;
     return st;
 }
 

@@ -146,7 +146,7 @@ B200Q_API b200q_status b200q_all_to_all_v(b200q_ctx *ctx, const void *dev_send, 
 /* MUL_MAT_ID with the experts split over the ranks: src0_local holds this rank's experts
  * [K, M, n_expert_total / nranks]; src1, ids (global expert ids) and dst are this rank's tokens.
  * Dispatch and combine are all-to-alls; the call synchronizes the stream once (the exchange sizes
- * must reach the host) and starts a new cache generation on the context. */
+ * must reach the host). */
 B200Q_API b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local, const b200q_tensor *src1,
                                            const b200q_tensor *ids, b200q_tensor *dst, int n_expert_total);
 B200Q_API b200q_status b200q_tp_check(b200q_ctx *ctx);
