@@ -133,6 +133,8 @@ def lib():
     L.b200q_buffer_free.argtypes = [vp, vp]
     L.b200q_tensor_set.argtypes = [vp, vp, vp, sz]
     L.b200q_tensor_get.argtypes = [vp, vp, vp, sz]
+    L.b200q_tensor_stage.argtypes = [vp, vp, vp, sz]
+    L.b200q_tensor_fetch.argtypes = [vp, vp, vp, sz]
     L.b200q_tensor_copy.argtypes = [vp, vp, vp, sz]
     L.b200q_synchronize.argtypes = [vp]
     L.b200q_host_alloc.argtypes = [sz, C.POINTER(vp)]
@@ -155,7 +157,7 @@ EXPORTS = [
     "b200q_mul_mat_id", "b200q_graph_begin", "b200q_capture_begin", "b200q_capture_end", "b200q_graph_launch",
     "b200q_graph_free", "b200q_tp_unique_id", "b200q_tp_init", "b200q_tp_rank", "b200q_tp_shard", "b200q_all_reduce_f32",
     "b200q_all_gather", "b200q_all_to_all_v", "b200q_tp_check", "b200q_mul_mat_id_ep", "b200q_mul_mat_noalloc", "b200q_noalloc_last_error", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
-    "b200q_tensor_get", "b200q_tensor_copy", "b200q_synchronize", "b200q_host_alloc", "b200q_host_free",
+    "b200q_tensor_get", "b200q_tensor_stage", "b200q_tensor_fetch", "b200q_tensor_copy", "b200q_synchronize", "b200q_host_alloc", "b200q_host_free",
     "b200q_stats", "b200q_stats_reset", "b200q_timer_start", "b200q_timer_stop", "b200q_flush_l2",
     "b200q_debug_quantize_act", "b200q_debug_dequantize",
 ]
@@ -239,6 +241,14 @@ class Context:
 
     def get_async(self, host_ptr, dev, nbytes):
         self.check(self.L.b200q_tensor_get(self.h, host_ptr, dev, nbytes))
+
+    def stage(self, dev, host_ptr, nbytes):
+        """host -> device on the copy stream; kernels queued afterwards wait for it"""
+        self.check(self.L.b200q_tensor_stage(self.h, dev, host_ptr, nbytes))
+
+    def fetch(self, host_ptr, dev, nbytes):
+        """device -> host on the copy stream, after the work queued so far; complete at the next sync()"""
+        self.check(self.L.b200q_tensor_fetch(self.h, host_ptr, dev, nbytes))
 
     def copy(self, dst, src, nbytes):
         self.check(self.L.b200q_tensor_copy(self.h, dst, src, nbytes))

@@ -227,6 +227,10 @@ b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
     }
     cudaEventCreate(&ctx->ev0);
     cudaEventCreate(&ctx->ev1);
+    cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking);
+    cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking);
+    cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming);
     if (cudaMalloc(&ctx->error_word, sizeof(int)) != cudaSuccess || cudaMemset(ctx->error_word, 0, sizeof(int)) != cudaSuccess) {
         b200q_free(ctx);
         return B200Q_NO_MEMORY;
@@ -255,6 +259,10 @@ void b200q_free(b200q_ctx *ctx) {
         if (w.ptr) cudaFree(w.ptr);
     moe_free(ctx);
     tp_free(ctx);
+    if (ctx->copy_in) { cudaStreamSynchronize(ctx->copy_in); cudaStreamDestroy(ctx->copy_in); }
+    if (ctx->copy_out) { cudaStreamSynchronize(ctx->copy_out); cudaStreamDestroy(ctx->copy_out); }
+    if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
+    if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
@@ -382,6 +390,8 @@ b200q_status b200q_mul_mat_id(b200q_ctx *ctx, const b200q_tensor *src0, const b2
     return B200Q_OK;
 }
 
+static b200q_status join_copy_stream(b200q_ctx *ctx);
+
 // ---- CUDA graphs ----------------------------------------------------------------------
 
 struct b200q_graph {
@@ -395,6 +405,11 @@ b200q_status b200q_capture_begin(b200q_ctx *ctx) {
     B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
     B200Q_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
     ctx->capturing = true;
+    // the copy stream joins the capture, so staged and fetched copies become nodes of the graph
+    B200Q_CUDA(ctx, cudaEventRecord(ctx->ev_fork, ctx->stream));
+    B200Q_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->ev_fork, 0));
+    B200Q_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->ev_fork, 0));
+    ctx->copy_pending = true;
     return B200Q_OK;
 }
 
@@ -403,6 +418,7 @@ b200q_status b200q_capture_end(b200q_ctx *ctx, b200q_graph **out) {
     *out = nullptr;
     if (!ctx->capturing) return fail(ctx, B200Q_INVALID, "no capture open");
     ctx->capturing = false;
+    join_copy_stream(ctx);                                  // every forked stream must be back before the capture ends
     b200q_graph *g = new b200q_graph();
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);
     if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
@@ -467,8 +483,44 @@ b200q_status b200q_tensor_copy(b200q_ctx *ctx, void *dev_dst, const void *dev_sr
     return B200Q_OK;
 }
 
+// Overlapped copies. They run on the context's two copy streams (one per direction, like the GPU's copy
+// engines), so they do not sit in the queue between two kernels of the compute stream: an upload runs while earlier kernels compute, a download while later ones do.
+// stage: host -> device; every kernel queued after the call waits for it. fetch: device -> host, after
+// everything queued before the call; complete at the next b200q_synchronize. The caller keeps the usual
+// double-buffering discipline: a device buffer being staged must not still be read by queued kernels, a
+// buffer being fetched must not be rewritten before the synchronize.
+b200q_status b200q_tensor_stage(b200q_ctx *ctx, void *dev_dst, const void *host_src, size_t bytes) {
+    if (!ctx || (bytes && (!dev_dst || !host_src))) return B200Q_INVALID;
+    B200Q_CUDA(ctx, cudaMemcpyAsync(dev_dst, host_src, bytes, cudaMemcpyHostToDevice, ctx->copy_in));
+    B200Q_CUDA(ctx, cudaEventRecord(ctx->ev_join, ctx->copy_in));
+    B200Q_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
+    return B200Q_OK;
+}
+
+b200q_status b200q_tensor_fetch(b200q_ctx *ctx, void *host_dst, const void *dev_src, size_t bytes) {
+    if (!ctx || (bytes && (!host_dst || !dev_src))) return B200Q_INVALID;
+    B200Q_CUDA(ctx, cudaEventRecord(ctx->ev_fork, ctx->stream));
+    B200Q_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->ev_fork, 0));
+    B200Q_CUDA(ctx, cudaMemcpyAsync(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost, ctx->copy_out));
+    ctx->copy_pending = true;
+    return B200Q_OK;
+}
+
+// the compute stream waits for what the copy stream still holds (before a capture ends, before a synchronize)
+static b200q_status join_copy_stream(b200q_ctx *ctx) {
+    if (!ctx->copy_pending) return B200Q_OK;
+    B200Q_CUDA(ctx, cudaEventRecord(ctx->ev_join, ctx->copy_out));
+    B200Q_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
+    B200Q_CUDA(ctx, cudaEventRecord(ctx->ev_join, ctx->copy_in));
+    B200Q_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
+    ctx->copy_pending = false;
+    return B200Q_OK;
+}
+
 b200q_status b200q_synchronize(b200q_ctx *ctx) {
     if (!ctx) return B200Q_INVALID;
+    b200q_status js = join_copy_stream(ctx);
+    if (js != B200Q_OK) return js;
     B200Q_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     // a kernel whose bounded wait ran out says so here
     int err = 0;

@@ -103,6 +103,9 @@ struct b200q_ctx {
     cudaStream_t stream = nullptr;
     bool         own_stream = false;
     int          sm_count = 148;
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;   // overlapped host copies (b200q_tensor_stage / _fetch), one stream per direction
+    cudaEvent_t  ev_fork = nullptr, ev_join = nullptr;
+    bool         copy_pending = false;    // the copy streams hold work the compute stream has not joined
     uint64_t     generation = 1;
     uint64_t     private_generation = 0;  // expert-parallel calls: generations of their internal products
     bool         capturing = false;

@@ -159,6 +159,13 @@ B200Q_API b200q_status b200q_tensor_set(b200q_ctx *ctx, void *dev_dst, const voi
 B200Q_API b200q_status b200q_tensor_get(b200q_ctx *ctx, void *host_dst, const void *dev_src, size_t bytes);
 B200Q_API b200q_status b200q_tensor_copy(b200q_ctx *ctx, void *dev_dst, const void *dev_src, size_t bytes);
 B200Q_API b200q_status b200q_synchronize(b200q_ctx *ctx);
+/* The same copies on a second stream of the context, so that they overlap kernels instead of queueing
+ * between them (ggml-cuda's copy-stream pattern for split buffers): _stage is host -> device and every
+ * kernel queued after the call waits for it; _fetch is device -> host after everything queued before the
+ * call and completes at the next b200q_synchronize. The caller double-buffers: a buffer being staged
+ * must not still be read by queued kernels, one being fetched must not be rewritten before the synchronize. */
+B200Q_API b200q_status b200q_tensor_stage(b200q_ctx *ctx, void *dev_dst, const void *host_src, size_t bytes);
+B200Q_API b200q_status b200q_tensor_fetch(b200q_ctx *ctx, void *host_dst, const void *dev_src, size_t bytes);
 /* page-locked host memory, so set/get copies run at full PCIe rate and asynchronously */
 B200Q_API b200q_status b200q_host_alloc(size_t bytes, void **host_ptr);
 B200Q_API b200q_status b200q_host_free(void *host_ptr);

@@ -225,3 +225,49 @@ def test_full_size_decode_shapes_sampled_rows(ctx, t, m, k):
         sub = got[:, rows]
         floor = 1e-2 * np.abs(ref).max(axis=-1, keepdims=True)
         assert float((np.abs(sub - ref) / np.maximum(np.abs(ref), floor)).max()) < TOL
+
+
+def test_overlapped_host_copies_eager_and_in_a_graph(ctx):
+    """b200q_tensor_stage / _fetch (uploads and downloads on the context's copy streams) around a chain of
+    products, each with its own buffers: the host results equal the plain upload / download path, called
+    eagerly and replayed as a CUDA graph with new inputs."""
+    t, m, k = A.Q4_K, 640, 1024
+    w = make_weights(t, m, k, 90)
+    dw = ctx.upload(w)
+    widths = [1, 3, 8, 5]
+    hin = [A.binding.PinnedArray((n, k), np.float32) for n in widths]
+    hout = [A.binding.PinnedArray((n, m), np.float32) for n in widths]
+    din = [ctx.alloc(4 * n * k) for n in widths]
+    dout = [ctx.alloc(4 * n * m) for n in widths]
+
+    def fill(seed):
+        for i, n in enumerate(widths):
+            hin[i].array[:] = O.fill_normal(n * k, seed + i, 1.0).reshape(n, k)
+            hout[i].array[:] = 0
+
+    def chain():
+        for i, n in enumerate(widths):
+            ctx.graph_begin()
+            ctx.stage(din[i], hin[i].ptr, 4 * n * k)
+            ctx.mul_mat(A.Tensor.weights(t, dw, k, m), A.Tensor.f32(din[i], [k, n]), A.Tensor.f32(dout[i], [m, n]))
+            ctx.fetch(hout[i].ptr, dout[i], 4 * n * m)
+
+    def check():
+        for i, n in enumerate(widths):
+            want = ctx.run_mul_mat(t, w, k, np.array(hin[i].array))
+            assert np.array_equal(hout[i].array, want), (i, n)
+
+    fill(100)
+    chain()
+    ctx.sync()
+    check()
+    g = ctx.capture(chain)
+    fill(200)
+    ctx.graph_launch(g)
+    ctx.sync()
+    check()
+    ctx.graph_free(g)
+    for p in din + dout + [dw]:
+        ctx.free(p)
+    for h in hin + hout:
+        h.free()
