@@ -157,6 +157,10 @@ b200q_status launch_gemv_id(b200q_ctx *ctx, int type, const void *w, size_t row_
                             const int32_t *n_tiles, int64_t max_tiles, const int32_t *pairs, const b200q_tensor *ids,
                             int n_expert, int n_used, int ne11, float *dst, int64_t ld1, int64_t ld2);
 // moe.cu: route (pairs sorted by expert, tile lists by size class)
+// Kernel attributes (dynamic shared memory opt-in, occupancy) belong to a device, and one process may hold
+// contexts on several: per-kernel tables indexed by device ordinal replace per-process flags.
+constexpr int B200Q_MAX_DEVICES = 64;
+
 struct RouteView {
     const int32_t *pairs;          // [n_pairs]
     const int32_t *tiles[4];       // class k: tiles of at most 1, 2, 4, 8 pairs (int4 each)

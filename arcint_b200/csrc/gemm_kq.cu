@@ -644,7 +644,8 @@ static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride
                                 const TileRoute &tr) {
     typedef kq::Smem<TYPE> L;
     auto kern = kq::gemm_kq_kernel<TYPE>;
-    static bool attr_set = false;
+    static bool attr_set_dev[B200Q_MAX_DEVICES] = {};
+    bool &attr_set = attr_set_dev[ctx->device % B200Q_MAX_DEVICES];
     if (!attr_set) {
         B200Q_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::TOTAL));
         attr_set = true;

@@ -396,7 +396,8 @@ static b200q_status launch_t(b200q_ctx *ctx, const void *w, size_t row_stride, i
                              int64_t N, float *dst, int64_t ldd) {
     typedef tc::Smem<TYPE> L;
     auto kern = tc::gemm_tc_kernel<TYPE>;
-    static bool attr_set = false;
+    static bool attr_set_dev[B200Q_MAX_DEVICES] = {};
+    bool &attr_set = attr_set_dev[ctx->device % B200Q_MAX_DEVICES];
     if (!attr_set) {
         B200Q_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::TOTAL));
         attr_set = true;

@@ -31,7 +31,8 @@ static b200q_status launch_one(b200q_ctx *ctx, const void *w, size_t row_stride,
     auto kern = aligned ? kern_a : kern_u;
     // resident CTAs per SM of this instantiation, asked once: the grid is one full wave of
     // persistent CTAs (or fewer when the work is small) and each warp strides over its units
-    static int occ[2] = { 0, 0 };
+    static int occ_dev[B200Q_MAX_DEVICES][2] = {};
+    int *occ = occ_dev[ctx->device % B200Q_MAX_DEVICES];
     if (occ[aligned] == 0) {
         if (smem > 48 * 1024)
             B200Q_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -187,7 +187,8 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     int32_t *owner_counts = n_tiles + 8;
     const size_t smem = sizeof(int) * (size_t)n_expert * 8;
     if (smem > 200 * 1024) return fail(ctx, B200Q_UNSUPPORTED, "route: %d experts", n_expert);
-    static bool attr = false;
+    static bool attr_dev[B200Q_MAX_DEVICES] = {};
+    bool &attr = attr_dev[ctx->device % B200Q_MAX_DEVICES];
     if (!attr) {
         B200Q_CUDA(ctx, cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr = true;
