@@ -105,7 +105,8 @@ class ClockSampler:
                 if len(r) > col and r[col].lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons),
+                "window": "warm-up, the timed steps, one more second of the same step, the end-to-end and roofline legs"}
 
 
 def build_decode_inputs(seed=0x5EED0001):
@@ -537,6 +538,15 @@ def run_gpu(args, rank, world):
         ctx.graph_launch(graphs[i % ROT])
     ms = timed(lambda i: ctx.graph_launch(graphs[i % ROT]), args.steps)
     ms_step = ms / args.steps
+    # the timed region lasts milliseconds, shorter than one nvidia-smi period: keep the same step running for
+    # about a second more (not timed) so that the clock samples are taken under this load
+    t_load = time.perf_counter()
+    i = 0
+    while time.perf_counter() - t_load < 1.0:
+        for _ in range(50):
+            ctx.graph_launch(graphs[i % ROT])
+            i += 1
+        ctx.sync()
     value = world * total_bytes / (ms_step * 1e-3) / 1e9
     launches = launches_per_step * args.steps
 
