@@ -361,15 +361,18 @@ b200q_status b200q_mul_mat_id(b200q_ctx *ctx, const b200q_tensor *src0, const b2
     // prompt-sized batches of the super-block types go to the tensor cores: the route's 128-pair tiles
     // are the GEMM's column tiles (an expert with few pairs pays a whole tile, so the batch must carry
     // enough pairs per expert on average to beat the per-tile GEMV below)
-    if ((int64_t)n_used * n_tok >= 8 * (int64_t)n_expert && (int64_t)n_used * n_tok >= 256 && !ctx->no_tc &&
-        gemm_kq_supported(src0->type, M, K, 1, src0->data, src0->nb[1]) && src0->nb[2] % 16 == 0 && src1->nb[1] % 16 == 0 &&
-        src1->nb[2] % 16 == 0 && (uintptr_t)src1->data % 16 == 0) {
+    const bool per32 = gemm_tc_supported(src0->type, M, K, 1, src0->data, src0->nb[1]);
+    const bool per256 = gemm_kq_supported(src0->type, M, K, 1, src0->data, src0->nb[1]);
+    if ((int64_t)n_used * n_tok >= 8 * (int64_t)n_expert && (int64_t)n_used * n_tok >= 256 && !ctx->no_tc && (per32 || per256) &&
+        src0->nb[2] % 16 == 0 && src1->nb[1] % 16 == 0 && src1->nb[2] % 16 == 0 && (uintptr_t)src1->data % 16 == 0) {
         RouteView rv;
         if ((st = moe_route(ctx, ids, n_expert, &rv)) != B200Q_OK) return st;
-        if ((st = ws_reserve(ctx, &ctx->moe_ws[7], gemm_kq_id_act_bytes(K, rv.max_tiles128))) != B200Q_OK) return st;
+        const size_t bytes = per32 ? gemm_tc_id_act_bytes(K, rv.max_tiles128) : gemm_kq_id_act_bytes(K, rv.max_tiles128);
+        if ((st = ws_reserve(ctx, &ctx->moe_ws[7], bytes)) != B200Q_OK) return st;
         TileRoute tr = { rv.tiles128, rv.n_tiles + 4, rv.pairs, n_used, ne11, src1->nb[1], src1->nb[2], ld1, ld2 };
         count(ctx, ST_MOE_GEMM);
-        return launch_gemm_kq_id(ctx, src0, src1, tr, rv.max_tiles128, (uint8_t *)ctx->moe_ws[7].ptr, (float *)dst->data);
+        return per32 ? launch_gemm_tc_id(ctx, src0, src1, tr, rv.max_tiles128, (uint8_t *)ctx->moe_ws[7].ptr, (float *)dst->data)
+                     : launch_gemm_kq_id(ctx, src0, src1, tr, rv.max_tiles128, (uint8_t *)ctx->moe_ws[7].ptr, (float *)dst->data);
     }
     ActView act;
     if ((st = get_activation(ctx, ti.act_form, src1, &act)) != B200Q_OK) return st;

@@ -199,6 +199,9 @@ void         tp_free(b200q_ctx *ctx);
 bool         gemm_tc_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride);
 size_t       gemm_tc_act_bytes(int64_t K, int64_t N);
 b200q_status launch_quantize_tiled(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out);
+size_t       gemm_tc_id_act_bytes(int64_t K, int64_t max_tiles);
+b200q_status launch_gemm_tc_id(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1, const TileRoute &tr,
+                               int64_t max_tiles, uint8_t *act, float *dst);
 b200q_status launch_gemm_tc(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                             const uint8_t *act, int64_t N, float *dst, int64_t ldd);
 

@@ -89,15 +89,24 @@ static_assert(BAR_COUNT <= 64, "the shared block reserves 64 mbarrier slots");
 //   scales [block j < 8][column < 128] f32 (the fp16-rounded block scale)
 __global__ void __launch_bounds__(256)
 quantize_tiled_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t nb1, size_t nb2, size_t nb3, int64_t K,
-                      int64_t N, uint8_t *__restrict__ out) {
+                      int64_t N, uint8_t *__restrict__ out, TileRoute id) {
     const int t = blockIdx.y, s = blockIdx.x, nst = gridDim.x;
     const int col = threadIdx.x & 127, half = threadIdx.x >> 7;
-    const int64_t n = (int64_t)t * BN + col;
     uint8_t *chunk = out + ((size_t)t * nst + s) * ACT_CHUNK;
     const float *x = nullptr;
-    if (n < N) {
-        const int64_t c1 = n % ne1, c23 = n / ne1, c2 = c23 % ne2, c3 = c23 / ne2;
-        x = reinterpret_cast<const float *>(base + c1 * nb1 + c2 * nb2 + c3 * nb3) + (int64_t)s * (SB * KB);
+    if (id.tiles) {
+        // MUL_MAT_ID: the tile's columns are routed pairs; pair p = (token, slot) reads src1 row slot % ne11
+        if (t >= __ldg(id.n_tiles)) return;
+        if (col < __ldg(id.tiles + 4 * t + 2)) {
+            const int p = __ldg(id.pairs + __ldg(id.tiles + 4 * t + 1) + col), tok = p / id.n_used, slot = p - tok * id.n_used;
+            x = reinterpret_cast<const float *>(base + (size_t)(slot % id.ne11) * id.nb1 + (size_t)tok * id.nb2) + (int64_t)s * (SB * KB);
+        }
+    } else {
+        const int64_t n = (int64_t)t * BN + col;
+        if (n < N) {
+            const int64_t c1 = n % ne1, c23 = n / ne1, c2 = c23 % ne2, c3 = c23 / ne2;
+            x = reinterpret_cast<const float *>(base + c1 * nb1 + c2 * nb2 + c3 * nb3) + (int64_t)s * (SB * KB);
+        }
     }
 #pragma unroll 1
     for (int jj = 0; jj < 4; ++jj) {
@@ -136,7 +145,7 @@ template <int N> __device__ __forceinline__ uint32_t word_at(const uint32_t (&w)
 template <int TYPE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
-               int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word) {
+               int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word, TileRoute id) {
     typedef Smem<TYPE> L;
     constexpr int ROWB = Raw<TYPE>::ROW;
     constexpr int NSTAGE = L::NSTAGE;
@@ -152,6 +161,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     const uint32_t bars = sbase + L::BAR_OFF;
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
     const int valid_rows = min(BM, M - row0);
+    // the tile's matrix and columns: dense, tile_n-th run of 128 tokens; MUL_MAT_ID, a route tile (one
+    // expert, up to 128 routed pairs)
+    int expert = 0, first = 0, ncols = min(BN, N - tile_n * BN);
+    if (id.tiles) {
+        if (tile_n >= __ldg(id.n_tiles)) return;          // the whole block: nothing is set up yet
+        expert = __ldg(id.tiles + 4 * tile_n);
+        first = __ldg(id.tiles + 4 * tile_n + 1);
+        ncols = __ldg(id.tiles + 4 * tile_n + 2);
+    }
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -198,7 +216,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             if (lane == 0) {
                 // the stage's [128 rows x ROWB] box in one tiled copy; rows past M arrive as zeros
                 mbar_expect_tx(bar(BAR_RAW_FULL + st), L::RAW_STAGE);
-                tma_load_2d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, s * (ROWB / 4), row0, bar(BAR_RAW_FULL + st));
+                tma_load_3d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, s * (ROWB / 4), row0, expert, bar(BAR_RAW_FULL + st));
             }
             if (!WAITP(3, bar(BAR_ACT_EMPTY + st), par)) break;
             if (lane == 0) {
@@ -336,9 +354,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             }
             done = b == nblk - 1;
         }
-        if (done && row_ok) {
+        const int ncol = ncols - u * CW;                         // this thread's columns inside the tile
+        if (done && id.tiles) {
+            // where the warp's columns go: every lane looks up some of them (loads in flight together), the
+            // store loop takes them by shuffle
+            long long off[(CW + 31) / 32];
+#pragma unroll
+            for (int h = 0; h < (CW + 31) / 32; ++h) {
+                off[h] = 0;
+                if (lane + 32 * h < ncol) {
+                    const int p = __ldg(id.pairs + first + u * CW + lane + 32 * h), tok = p / id.n_used, slot = p - tok * id.n_used;
+                    off[h] = tok * id.ld2 + slot * id.ld1;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < CW; c += 2) {
+                float a[2];
+                f2_unpack(acc2[c / 2], a[0], a[1]);
+#pragma unroll
+                for (int d = 0; d < 2; ++d) {
+                    const long long o = __shfl_sync(0xFFFFFFFFu, off[(c + d) >> 5], (c + d) & 31);
+                    if (row_ok && c + d < ncol) dst[o + row0 + r] = a[d];
+                }
+            }
+        } else if (done && row_ok) {
             float *o = dst + (int64_t)(tile_n * BN + u * CW) * ldd + row0 + r;
-            const int ncol = N - (tile_n * BN + u * CW);         // columns of this thread inside the matrix
 #pragma unroll
             for (int c = 0; c < CW; c += 2) {
                 float a0, a1;
@@ -381,19 +421,29 @@ bool gemm_tc_supported(int type, int64_t M, int64_t K, int64_t N, const void *w,
     return true;
 }
 
-b200q_status launch_quantize_tiled(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out) {
+static const TileRoute NO_ROUTE_TC = { nullptr, nullptr, nullptr, 1, 1, 0, 0, 0, 0 };
+
+static b200q_status quantize_tiled(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out, int64_t n_tiles, const TileRoute &tr) {
     const int64_t K = src1->ne[0], N = src1->ne[1] * src1->ne[2] * src1->ne[3];
-    dim3 grid((unsigned)(K / (tc::SB * tc::KB)), (unsigned)((N + tc::BN - 1) / tc::BN));
+    dim3 grid((unsigned)(K / (tc::SB * tc::KB)), (unsigned)n_tiles);
     tc::quantize_tiled_kernel<<<grid, 256, 0, ctx->stream>>>((const uint8_t *)src1->data, src1->ne[1], src1->ne[2],
-                                                            src1->nb[1], src1->nb[2], src1->nb[3], K, N, out);
+                                                            src1->nb[1], src1->nb[2], src1->nb[3], K, N, out, tr);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC_QUANT);
     return B200Q_OK;
 }
 
+b200q_status launch_quantize_tiled(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out) {
+    const int64_t N = src1->ne[1] * src1->ne[2] * src1->ne[3];
+    return quantize_tiled(ctx, src1, out, (N + tc::BN - 1) / tc::BN, NO_ROUTE_TC);
+}
+
+// n_tiles: grid width (dense: the tiles of N; MUL_MAT_ID: the upper bound of the route's tile count,
+// blocks past the device-side count leave at once)
 template <int TYPE>
-static b200q_status launch_t(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K, const uint8_t *act,
-                             int64_t N, float *dst, int64_t ldd) {
+static b200q_status launch_t(b200q_ctx *ctx, const void *w, size_t row_stride, size_t mat_stride, int64_t n_mat, int64_t M,
+                             int64_t K, const uint8_t *act, int64_t N, int64_t n_tiles, float *dst, int64_t ldd,
+                             const TileRoute &tr) {
     typedef tc::Smem<TYPE> L;
     auto kern = tc::gemm_tc_kernel<TYPE>;
     static bool attr_set_dev[B200Q_MAX_DEVICES] = {};
@@ -404,10 +454,10 @@ static b200q_status launch_t(b200q_ctx *ctx, const void *w, size_t row_stride, i
     }
     CUtensorMap wmap;
     constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
-    b200q_status st = make_weight_tmap(ctx, &wmap, w, row_stride, M, (K / 32) * BB, tc::Raw<TYPE>::ROW);
+    b200q_status st = make_weight_tmap3(ctx, &wmap, w, row_stride, M, (K / 32) * BB, tc::Raw<TYPE>::ROW, n_mat, mat_stride);
     if (st != B200Q_OK) return st;
-    dim3 grid((unsigned)((N + tc::BN - 1) / tc::BN), (unsigned)((M + tc::BM - 1) / tc::BM));
-    kern<<<grid, tc::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd, ctx->error_word);
+    dim3 grid((unsigned)n_tiles, (unsigned)((M + tc::BM - 1) / tc::BM));
+    kern<<<grid, tc::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd, ctx->error_word, tr);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
     return B200Q_OK;
@@ -415,9 +465,27 @@ static b200q_status launch_t(b200q_ctx *ctx, const void *w, size_t row_stride, i
 
 b200q_status launch_gemm_tc(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                             const uint8_t *act, int64_t N, float *dst, int64_t ldd) {
-    if (type == B200Q_TYPE_Q4_0) return launch_t<B200Q_TYPE_Q4_0>(ctx, w, row_stride, M, K, act, N, dst, ldd);
-    if (type == B200Q_TYPE_Q8_0) return launch_t<B200Q_TYPE_Q8_0>(ctx, w, row_stride, M, K, act, N, dst, ldd);
+    const int64_t n_tiles = (N + tc::BN - 1) / tc::BN;
+    const size_t ms = row_stride * (size_t)M;
+    if (type == B200Q_TYPE_Q4_0) return launch_t<B200Q_TYPE_Q4_0>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE_TC);
+    if (type == B200Q_TYPE_Q8_0) return launch_t<B200Q_TYPE_Q8_0>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE_TC);
     return fail(ctx, B200Q_UNSUPPORTED, "gemm_tc: type %d", type);
+}
+
+size_t gemm_tc_id_act_bytes(int64_t K, int64_t max_tiles) { return gemm_tc_act_bytes(K, max_tiles * tc::BN); }
+
+// MUL_MAT_ID on the tensor cores: the route's 128-pair tiles are the column tiles; the activation of
+// every tile is gathered and quantized into `act` (gemm_tc_id_act_bytes) first.
+b200q_status launch_gemm_tc_id(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1, const TileRoute &tr,
+                               int64_t max_tiles, uint8_t *act, float *dst) {
+    const int64_t K = src0->ne[0], M = src0->ne[1];
+    b200q_status st = quantize_tiled(ctx, src1, act, max_tiles, tr);
+    if (st != B200Q_OK) return st;
+    if (src0->type == B200Q_TYPE_Q4_0)
+        return launch_t<B200Q_TYPE_Q4_0>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
+    if (src0->type == B200Q_TYPE_Q8_0)
+        return launch_t<B200Q_TYPE_Q8_0>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
+    return fail(ctx, B200Q_UNSUPPORTED, "gemm_tc_id: type %d", src0->type);
 }
 
 }  // namespace b200q

@@ -135,7 +135,7 @@ def test_mul_mat_id_shape_errors(ctx):
 
 # ---- prompt-sized batches: the route's 128-pair tiles through the tensor-core GEMM ----
 
-@pytest.mark.parametrize("t", [A.Q4_K, A.IQ4_XS])
+@pytest.mark.parametrize("t", [A.Q4_K, A.IQ4_XS, A.Q4_0, A.Q8_0])
 @pytest.mark.parametrize("n_expert,n_used,n_tok,ne11_is_one", [(8, 2, 300, True), (8, 2, 300, False), (4, 4, 700, True),
                                                                (32, 8, 64, False)])
 def test_mul_mat_id_tensor_core_tiles(ctx, t, n_expert, n_used, n_tok, ne11_is_one):
