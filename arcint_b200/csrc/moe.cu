@@ -29,49 +29,100 @@ struct RouteEntry {
 __global__ void __launch_bounds__(1024)
 moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_expert, int32_t *pairs,
                  int32_t *tiles0, int32_t *tiles1, int32_t *tiles2, int32_t *tiles3, int32_t *tiles128, int32_t *n_tiles,
-                 int32_t *owner_counts, int experts_per_owner) {
+                 int32_t *owner_counts, int experts_per_owner, int n_groups) {
+    // Counters are kept once per group of warps (a skewed router sends a tenth of all pairs to one
+    // expert: one shared-memory counter would serialize them): cntg / fillg [n_groups][n_expert].
     extern __shared__ int sm[];
-    int *cnt = sm, *base = sm + n_expert, *fill = sm + 2 * n_expert, *toff = sm + 3 * n_expert;   // toff: [5][n_expert]
+    int *cnt = sm, *base = sm + n_expert, *toff = sm + 2 * n_expert;          // cnt: totals; toff: [5][n_expert]
+    int *cntg = sm + 7 * n_expert, *fillg = cntg + n_groups * n_expert;
     const int tid = threadIdx.x, nth = blockDim.x;
+    const int grp = (tid >> 5) * n_groups / (nth >> 5);                          // this warp's counter group
     const int n_pairs = n_used * n_tok;
     auto expert_of = [&](int p) {
         const int t = p / n_used, i = p - t * n_used;
         const int e = reinterpret_cast<const int32_t *>(ids + (size_t)t * nb1)[i];
         return min(max(e, 0), n_expert - 1);
     };
-    for (int e = tid; e < n_expert; e += nth) { cnt[e] = 0; fill[e] = 0; }
+    for (int i = tid; i < 2 * n_groups * n_expert; i += nth) cntg[i] = 0;      // cntg and fillg
     __syncthreads();
     // eight independent loads in flight per thread (the ids come from global memory)
+    const int lane = tid & 31;
     for (int p0 = tid; p0 < n_pairs; p0 += 8 * nth) {
         int e8[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) e8[k] = p0 + k * nth < n_pairs ? expert_of(p0 + k * nth) : -1;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-            if (e8[k] >= 0) atomicAdd(&cnt[e8[k]], 1);
+            if (e8[k] >= 0) atomicAdd(&cntg[grp * n_expert + e8[k]], 1);
     }
     __syncthreads();
-    if ((tid & 31) == 0 && tid < 6 * 32) {
-        // six independent prefix sums over the experts, one thread each, each in its own warp (in one
-        // warp the six branches would run one after the other): the pair offsets, the tile offsets
-        // of the four decode size classes, and of the 128-pair tiles of the tensor-core path (which
-        // covers every pair once more, in its own list)
-        const int which = tid >> 5;
-        int acc = 0;
-        for (int e = 0; e < n_expert; ++e) {
-            const int c = cnt[e], rem = c & 7;
-            int v;
-            if (which == 5) v = (c + 127) >> 7;
-            else if (which == 4) v = c;
-            else if (which == 3) v = (c >> 3) + (rem >= 5);
-            else if (which == 2) v = rem == 3 || rem == 4;
-            else if (which == 1) v = rem == 2;
-            else v = rem == 1;
-            if (which == 4) base[e] = acc; else toff[(which == 5 ? 4 : which) * n_expert + e] = acc;
-            acc += v;
+    // per expert: the groups' counts become the groups' offsets inside the expert's run; their sum is the count
+    for (int e = tid; e < n_expert; e += nth) {
+        int run = 0;
+        for (int g = 0; g < n_groups; ++g) {
+            const int t = cntg[g * n_expert + e];
+            cntg[g * n_expert + e] = run;
+            run += t;
         }
-        if (which != 4) n_tiles[which == 5 ? 4 : which] = acc;
+        cnt[e] = run;
     }
+    __syncthreads();
+    // six exclusive prefix sums over the experts at once (block-wide scan, 1024 experts per round): the pair
+    // offsets, the tile offsets of the four decode size classes, and of the 128-pair tiles of the tensor-core
+    // path (which covers every pair once more, in its own list)
+    __shared__ int warp_tot[6][32], carry[6], round_tot[6];
+    const int warp = tid >> 5, n_warps = nth >> 5;
+    if (tid < 6) carry[tid] = 0;
+    __syncthreads();
+    for (int e0 = 0; e0 < n_expert; e0 += nth) {
+        const int e = e0 + tid;
+        const int c = e < n_expert ? cnt[e] : 0, rem = c & 7;
+        int v[6], incl[6];
+        v[0] = rem == 1;
+        v[1] = rem == 2;
+        v[2] = rem == 3 || rem == 4;
+        v[3] = (c >> 3) + (rem >= 5);
+        v[4] = (c + 127) >> 7;
+        v[5] = c;
+#pragma unroll
+        for (int k = 0; k < 6; ++k) {
+            int x = v[k];
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int y = __shfl_up_sync(0xFFFFFFFFu, x, off);
+                if (lane >= off) x += y;
+            }
+            incl[k] = x;
+            if (lane == 31) warp_tot[k][warp] = x;
+        }
+        __syncthreads();
+        if (warp == 0) {
+#pragma unroll
+            for (int k = 0; k < 6; ++k) {
+                const int t = lane < n_warps ? warp_tot[k][lane] : 0;
+                int x = t;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int y = __shfl_up_sync(0xFFFFFFFFu, x, off);
+                    if (lane >= off) x += y;
+                }
+                warp_tot[k][lane] = x - t;                         // exclusive over the warps
+                if (lane == 31) round_tot[k] = x;
+            }
+        }
+        __syncthreads();
+        if (e < n_expert) {
+#pragma unroll
+            for (int k = 0; k < 6; ++k) {
+                const int ex = carry[k] + warp_tot[k][warp] + incl[k] - v[k];
+                if (k == 5) base[e] = ex; else toff[k * n_expert + e] = ex;
+            }
+        }
+        __syncthreads();
+        if (tid < 6) carry[tid] += round_tot[tid];
+        __syncthreads();
+    }
+    if (tid < 5) n_tiles[tid] = carry[tid];
     __syncthreads();
     for (int e = tid; e < n_expert; e += nth) {
         const int c = cnt[e], rem = c & 7, full = c >> 3, first = base[e];
@@ -87,13 +138,17 @@ moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_ex
         int32_t *tb = tiles128 + 4 * toff[4 * n_expert + e];
         for (int k = 0; 128 * k < c; ++k) { tb[4 * k] = e; tb[4 * k + 1] = first + 128 * k; tb[4 * k + 2] = min(128, c - 128 * k); tb[4 * k + 3] = 0; }
     }
+    // the same thread meets the same pairs as in the counting pass, so its group's share of the run is its own
     for (int p0 = tid; p0 < n_pairs; p0 += 8 * nth) {
         int e8[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) e8[k] = p0 + k * nth < n_pairs ? expert_of(p0 + k * nth) : -1;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-            if (e8[k] >= 0) pairs[base[e8[k]] + atomicAdd(&fill[e8[k]], 1)] = p0 + k * nth;
+            if (e8[k] >= 0) {
+                const int g = grp * n_expert + e8[k];
+                pairs[base[e8[k]] + cntg[g] + atomicAdd(&fillg[g], 1)] = p0 + k * nth;
+            }
     }
     // expert parallelism: how many pairs go to each owner (experts are owned in contiguous ranges)
     if (owner_counts) {
@@ -185,7 +240,10 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     for (int k = 0; k < 5; ++k) tl[k] = p + n_pairs + (size_t)k * 4 * max_tiles;
     int32_t *n_tiles = p + n_pairs + (size_t)20 * max_tiles;
     int32_t *owner_counts = n_tiles + 8;
-    const size_t smem = sizeof(int) * (size_t)n_expert * 8;
+    // counter groups: as many as fit beside the seven per-expert arrays (eight for up to ~1000 experts)
+    int n_groups = 8;
+    while (n_groups > 1 && sizeof(int) * (size_t)n_expert * (7 + 2 * n_groups) > 200 * 1024) n_groups >>= 1;
+    const size_t smem = sizeof(int) * (size_t)n_expert * (7 + 2 * n_groups);
     if (smem > 200 * 1024) return fail(ctx, B200Q_UNSUPPORTED, "route: %d experts", n_expert);
     static bool attr_dev[B200Q_MAX_DEVICES] = {};
     bool &attr = attr_dev[ctx->device % B200Q_MAX_DEVICES];
@@ -196,7 +254,7 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     moe_route_kernel<<<1, 1024, smem, ctx->stream>>>((const uint8_t *)ids->data, ids->nb[1], n_used, n_tok, n_expert, pairs,
                                                      tl[0], tl[1], tl[2], tl[3], tl[4], n_tiles,
                                                      experts_per_owner > 0 ? owner_counts : nullptr,
-                                                     experts_per_owner > 0 ? experts_per_owner : 1);
+                                                     experts_per_owner > 0 ? experts_per_owner : 1, n_groups);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_MOE_ROUTE);
     e.ids_data = ids->data;
