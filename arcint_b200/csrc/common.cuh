@@ -107,6 +107,7 @@ struct b200q_ctx {
     cudaEvent_t  ev_fork = nullptr, ev_join = nullptr;
     bool         copy_pending = false;    // the copy streams hold work the compute stream has not joined
     uint64_t     generation = 1;
+    int          route_pinned = -1;       // a route entry in use across a nested call: not a victim
     uint64_t     private_generation = 0;  // expert-parallel calls: generations of their internal products
     bool         capturing = false;
     bool         no_tc = false;           // B200Q_NO_TC=1: never take the tensor-core GEMM
@@ -168,6 +169,7 @@ struct RouteView {
     const int32_t *n_tiles;        // [5] device counters: the four classes, then the 128-pair list
     int64_t        max_tiles;      // upper bound of every list
     int64_t        max_tiles128;   // upper bound of the 128-pair list
+    int            slot;           // which of the context's route entries holds this view
     const int32_t *owner_counts;   // expert parallelism: pairs per owner rank (device), else unused
 };
 // MUL_MAT_ID view of the tensor-core GEMM: column c of tile n is pair pairs[first + c] of expert

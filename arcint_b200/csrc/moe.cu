@@ -222,11 +222,17 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
         *out = hit->view;
         return B200Q_OK;
     }
-    // victim: an entry of an older graph first, else round robin
+    // victim: an entry of an older graph first, else round robin; never the entry a caller up the stack
+    // still reads (the expert-parallel call keeps its route across the local product)
     size_t pick = 2;
     for (size_t i = 0; i < 2; ++i)
-        if (!ctx->routes[i] || !ctx->routes[i]->valid || ctx->routes[i]->gen != ctx->generation) { pick = i; break; }
-    if (pick == 2) { pick = ctx->route_next; ctx->route_next ^= 1; }
+        if ((int)i != ctx->route_pinned &&
+            (!ctx->routes[i] || !ctx->routes[i]->valid || ctx->routes[i]->gen != ctx->generation)) { pick = i; break; }
+    if (pick == 2) {
+        pick = ctx->route_next;
+        ctx->route_next ^= 1;
+        if ((int)pick == ctx->route_pinned) pick ^= 1;
+    }
     if (!ctx->routes[pick]) ctx->routes[pick] = new RouteEntry();
     RouteEntry &e = *ctx->routes[pick];
     e.valid = false;
@@ -270,6 +276,7 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     e.view.n_tiles = n_tiles;
     e.view.max_tiles = max_tiles;
     e.view.owner_counts = owner_counts;
+    e.view.slot = (int)pick;
     e.experts_per_owner = experts_per_owner;
     e.valid = true;
     *out = e.view;

@@ -282,7 +282,9 @@ b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local,
         // down of a layer share -- comes back afterwards.
         const uint64_t caller_gen = ctx->generation;
         ctx->generation = (1ull << 62) + ++ctx->private_generation;
+        ctx->route_pinned = rv.slot;                      // rv.pairs is read again after the local product
         st = b200q_mul_mat_id(ctx, src0_local, &x1, &id1, &y1);
+        ctx->route_pinned = -1;
         ctx->generation = caller_gen;
         if (st != B200Q_OK) return st;
     }
