@@ -351,12 +351,14 @@ def moe_section(ctx, world, rank, dist):
         block()
         got = ctx.download(dd, (n_tok, n_used, d_model), np.float32)
         err = None
-        if world == 1:                                    # parity of the last product on a sample of tokens
+        if True:                                          # parity of the last product on a sample of this rank's tokens
             ts = np.arange(0, n_tok, max(1, n_tok // 4))[:4]
             wfull = np.tile(mats["down"][2], (n_exp // 8, 1, 1))
             ref = O.mul_mat_id(t, wfull, d_model, d_ff, h[ts], np.ascontiguousarray(ids[ts]), f64=True)
             floor = 1e-2 * np.abs(ref).max(axis=-1, keepdims=True)
             err = float((np.abs(got[ts] - ref) / np.maximum(np.abs(ref), floor)).max())
+            if not err < 1e-3:
+                raise SystemExit("bench: MoE parity check failed on rank %d (max rel err %.3e)" % (rank, err))
         reps = 5
         g = None
         if world == 1:                                    # the expert-parallel call synchronizes: not capturable
