@@ -368,11 +368,25 @@ b200q_status b200q_mul_mat_id(b200q_ctx *ctx, const b200q_tensor *src0, const b2
         RouteView rv;
         if ((st = moe_route(ctx, ids, n_expert, &rv)) != B200Q_OK) return st;
         const size_t bytes = per32 ? gemm_tc_id_act_bytes(K, rv.max_tiles128) : gemm_kq_id_act_bytes(K, rv.max_tiles128);
+        const void *before = ctx->moe_ws[7].ptr;
         if ((st = ws_reserve(ctx, &ctx->moe_ws[7], bytes)) != B200Q_OK) return st;
+        const bool grew = ctx->moe_ws[7].ptr != before;
         TileRoute tr = { rv.tiles128, rv.n_tiles + 4, rv.pairs, n_used, ne11, src1->nb[1], src1->nb[2], ld1, ld2 };
         count(ctx, ST_MOE_GEMM);
-        return per32 ? launch_gemm_tc_id(ctx, src0, src1, tr, rv.max_tiles128, (uint8_t *)ctx->moe_ws[7].ptr, (float *)dst->data)
-                     : launch_gemm_kq_id(ctx, src0, src1, tr, rv.max_tiles128, (uint8_t *)ctx->moe_ws[7].ptr, (float *)dst->data);
+        // the scratch may already hold this very activation, gathered for these ids in this graph
+        auto &ma = ctx->moe_act;
+        bool ready = !grew && ma.src1 == src1->data && ma.ids == ids->data && ma.gen == ctx->generation && ma.per32 == (int)per32 &&
+                     ma.n_expert == n_expert;
+        for (int i = 0; i < 4 && ready; ++i) ready = ma.ne[i] == src1->ne[i] && ma.nb[i] == src1->nb[i];
+        if (ready) count(ctx, ST_ACT_CACHE_HIT);
+        ma.src1 = src1->data;
+        ma.ids = ids->data;
+        ma.gen = ctx->generation;
+        ma.per32 = (int)per32;
+        ma.n_expert = n_expert;
+        for (int i = 0; i < 4; ++i) { ma.ne[i] = src1->ne[i]; ma.nb[i] = src1->nb[i]; }
+        return per32 ? launch_gemm_tc_id(ctx, src0, src1, tr, rv.max_tiles128, (uint8_t *)ctx->moe_ws[7].ptr, (float *)dst->data, ready)
+                     : launch_gemm_kq_id(ctx, src0, src1, tr, rv.max_tiles128, (uint8_t *)ctx->moe_ws[7].ptr, (float *)dst->data, ready);
     }
     ActView act;
     if ((st = get_activation(ctx, ti.act_form, src1, &act)) != B200Q_OK) return st;
@@ -591,6 +605,7 @@ b200q_status b200q_debug_quantize_act(b200q_ctx *ctx, int weight_type, const b20
     if (!is_contiguous_f32(src1) || src1->ne[0] % ti.block) return fail(ctx, B200Q_UNSUPPORTED, "src1 layout");
     if (!dev_sums) return B200Q_INVALID;
     const int64_t K = src1->ne[0], N = src1->ne[1] * src1->ne[2] * src1->ne[3];
+    ctx->moe_act.src1 = nullptr;                            // the scratch below is shared with the MUL_MAT_ID activation
     b200q_status st = ws_reserve(ctx, &ctx->moe_ws[7], sizeof(int16_t) * (size_t)(N * (K / 16)) + 64);
     if (st != B200Q_OK) return st;
     return launch_quantize_act(ctx, ti.act_form, src1, (int8_t *)dev_codes, dev_scales, (int16_t *)dev_sums,

@@ -107,6 +107,9 @@ struct b200q_ctx {
     cudaEvent_t  ev_fork = nullptr, ev_join = nullptr;
     bool         copy_pending = false;    // the copy streams hold work the compute stream has not joined
     uint64_t     generation = 1;
+    // what the gathered, tiled activation scratch of the tensor-core MUL_MAT_ID holds (gate and up of a layer
+    // read the same src1 through the same ids: the second call finds it ready)
+    struct { const void *src1 = nullptr, *ids = nullptr; int64_t ne[4] = {0, 0, 0, 0}; size_t nb[4] = {0, 0, 0, 0}; uint64_t gen = 0; int per32 = -1, n_expert = 0; } moe_act;
     int          route_pinned = -1;       // a route entry in use across a nested call: not a victim
     uint64_t     private_generation = 0;  // expert-parallel calls: generations of their internal products
     bool         capturing = false;
@@ -203,7 +206,7 @@ size_t       gemm_tc_act_bytes(int64_t K, int64_t N);
 b200q_status launch_quantize_tiled(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out);
 size_t       gemm_tc_id_act_bytes(int64_t K, int64_t max_tiles);
 b200q_status launch_gemm_tc_id(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1, const TileRoute &tr,
-                               int64_t max_tiles, uint8_t *act, float *dst);
+                               int64_t max_tiles, uint8_t *act, float *dst, bool act_ready);
 b200q_status launch_gemm_tc(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                             const uint8_t *act, int64_t N, float *dst, int64_t ldd);
 
@@ -213,7 +216,7 @@ size_t       gemm_kq_act_bytes(int64_t K, int64_t N);
 b200q_status launch_quantize_tiled256(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out);
 size_t       gemm_kq_id_act_bytes(int64_t K, int64_t max_tiles);
 b200q_status launch_gemm_kq_id(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1, const TileRoute &tr,
-                               int64_t max_tiles, uint8_t *act, float *dst);
+                               int64_t max_tiles, uint8_t *act, float *dst, bool act_ready);
 b200q_status launch_gemm_kq(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                             const uint8_t *act, int64_t N, float *dst, int64_t ldd);
 

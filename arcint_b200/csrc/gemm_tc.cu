@@ -477,9 +477,9 @@ size_t gemm_tc_id_act_bytes(int64_t K, int64_t max_tiles) { return gemm_tc_act_b
 // MUL_MAT_ID on the tensor cores: the route's 128-pair tiles are the column tiles; the activation of
 // every tile is gathered and quantized into `act` (gemm_tc_id_act_bytes) first.
 b200q_status launch_gemm_tc_id(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1, const TileRoute &tr,
-                               int64_t max_tiles, uint8_t *act, float *dst) {
+                               int64_t max_tiles, uint8_t *act, float *dst, bool act_ready) {
     const int64_t K = src0->ne[0], M = src0->ne[1];
-    b200q_status st = quantize_tiled(ctx, src1, act, max_tiles, tr);
+    b200q_status st = act_ready ? B200Q_OK : quantize_tiled(ctx, src1, act, max_tiles, tr);
     if (st != B200Q_OK) return st;
     if (src0->type == B200Q_TYPE_Q4_0)
         return launch_t<B200Q_TYPE_Q4_0>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);

@@ -178,3 +178,34 @@ def test_config5_moe_q4_K_prompt_batch(ctx):
     ref = O.mul_mat_id(t, w, m, k, x[ts], np.ascontiguousarray(ids[ts]), f64=True)
     assert rel_err(got[ts].reshape(-1, m), ref.reshape(-1, m)) < TOL
     assert np.isfinite(got).all()
+
+
+def test_gate_and_up_share_the_gathered_activation(ctx):
+    """Two MUL_MAT_ID calls of one graph over the same src1 and ids (gate and up of a layer) gather and quantize the
+    activation once; a third with another src1 (down) does it again; results stay right."""
+    t, n_expert, n_used, n_tok, m, k = A.Q4_K, 8, 2, 300, 136, 512
+    rng = np.random.default_rng(21)
+    w1 = np.stack([O.random_blocks(t, m, k, rng) for _ in range(n_expert)])
+    w2 = np.stack([O.random_blocks(t, m, k, rng) for _ in range(n_expert)])
+    ids = rng.integers(0, n_expert, size=(n_tok, n_used)).astype(np.int32)
+    x = rng.normal(0, 1, size=(n_tok, 1, k)).astype(np.float32)
+    x2 = rng.normal(0, 1, size=(n_tok, n_used, k)).astype(np.float32)
+    rb = w1.shape[2]
+    d1, d2, dx, dx2, di = ctx.upload(w1), ctx.upload(w2), ctx.upload(x), ctx.upload(x2), ctx.upload(ids)
+    y1, y2, y3 = (ctx.alloc(n_tok * n_used * m * 4) for _ in range(3))
+    W = lambda d: A.Tensor.make(t, [k, m, n_expert, 1], [144, rb, rb * m, rb * m * n_expert], d)
+    I = A.Tensor.make(A.I32, [n_used, n_tok], [4, 4 * n_used], di)
+    Y = lambda d: A.Tensor.f32(d, [m, n_used, n_tok])
+    ctx.graph_begin()
+    ctx.stats_reset()
+    ctx.mul_mat_id(W(d1), A.Tensor.f32(dx, [k, 1, n_tok]), I, Y(y1))
+    ctx.mul_mat_id(W(d2), A.Tensor.f32(dx, [k, 1, n_tok]), I, Y(y2))
+    ctx.mul_mat_id(W(d1), A.Tensor.f32(dx2, [k, n_used, n_tok]), I, Y(y3))
+    st = ctx.stats()
+    assert st["moe_gemm"] == 3 and st["gemm_tc_quantize"] == 2 and st["moe_route"] == 1, st
+    for dy, w, xx in ((y1, w1, x), (y2, w2, x), (y3, w1, x2)):
+        got = ctx.download(dy, (n_tok, n_used, m), np.float32)
+        ref = O.mul_mat_id(t, w, m, k, xx, ids, f64=True)
+        assert rel_err(got.reshape(-1, m), ref.reshape(-1, m)) < TOL
+    for p in (d1, d2, dx, dx2, di, y1, y2, y3):
+        ctx.free(p)
