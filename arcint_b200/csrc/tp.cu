@@ -6,7 +6,7 @@
 // made by rank 0 and handed over by whatever launcher the caller uses.
 //
 // The reference has no tensor- or expert-parallel mode (its only multi-device mode is a
-// layer split through ggml's scheduler, marfrit/arcint DESIGN.md:782-788), so there is no
+// layer split through ggml's scheduler, lines 782-788 of the design notes at the root of marfrit/arcint), so there is no
 // reference behaviour to match here beyond the single-GPU op result.
 //
 // NCCL is opened at run time (dlopen "libnccl.so.2"): a single-GPU user never needs it, and a
