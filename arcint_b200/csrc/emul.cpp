@@ -128,6 +128,7 @@ uint32_t emul_lookup4_tab(const uint32_t *t, uint32_t idx) {
 }
 
 void emul_iq4xs_limbs(int ls, int n, int *hi, int *lo) { iq4xs_limbs(ls, n, hi, lo); }
+void emul_q6k_limbs4(uint32_t q6, int sc, uint32_t *out2) { q6k_limbs4(q6, sc, out2, out2 + 1); }
 void emul_q4k_limbs4(uint32_t idx, uint32_t sc, uint32_t *out2) { q4k_limbs4(idx, sc, out2, out2 + 1); }
 void emul_q4k_scales_mins(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t *out4) {
     q4k_scales8(s0, s1, s2, out4, out4 + 1);

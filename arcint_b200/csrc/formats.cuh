@@ -148,6 +148,17 @@ B200Q_HD void q4k_limbs4(uint32_t idx, uint32_t sc, uint32_t *hi4, uint32_t *lo4
     *lo4 = hd_byte_perm(za, zb, 0x6420) ^ 0x80808080u;
 }
 
+// Q6_K for the int8 tensor cores: p = sc * (q - 32) with the int8 sub-block scale and the 6-bit code
+// (|p| <= 4096) as two int8 limbs, p = 256 * hi + lo, for four codes (one per byte, 0..63) at once:
+// half = q * sc + (32896 - 32 sc) = p + 128 + 32768 stays inside 0..65535, the rest as for IQ4_XS.
+B200Q_HD void q6k_limbs4(uint32_t q6, int sc, uint32_t *hi4, uint32_t *lo4) {
+    const uint32_t c = (uint32_t)(32896 - 32 * sc) * 0x10001u, us = (uint32_t)sc;
+    const uint32_t za = (hd_byte_perm(q6, 0, 0x4140) * us + c) ^ 0x80808080u;
+    const uint32_t zb = (hd_byte_perm(q6, 0, 0x4342) * us + c) ^ 0x80808080u;
+    *hi4 = hd_byte_perm(za, zb, 0x7531);
+    *lo4 = hd_byte_perm(za, zb, 0x6420);
+}
+
 // the eight 6-bit mins (or scales) of a Q4_K block as two words of four bytes
 B200Q_HD void q4k_mins8(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t *m03, uint32_t *m47) {
     *m03 = s1 & 0x3F3F3F3Fu;

@@ -69,12 +69,16 @@ constexpr int A_SLOT = 2 * OPER_BYTES;                    // hi limb, lo limb
 // Per type: bytes of a super-block, super-blocks per raw stage (the stage's row piece must be a
 // multiple of 16 bytes: 2 x 136 for IQ4_XS, 144 for Q4_K), raw stages in flight.
 template <int TYPE> struct Fmt;
-template <> struct Fmt<B200Q_TYPE_IQ4_XS> { enum { SBB = 136, SPS = 2, NRAW = 2 }; };
-template <> struct Fmt<B200Q_TYPE_Q4_K>   { enum { SBB = 144, SPS = 1, NRAW = 4 }; };
+// BOX: bytes per row of the staged box. Q6_K's 210-byte blocks start on 2-byte boundaries only, so its box
+// starts at the 16-byte boundary below the block and is 224 bytes wide; the block begins (210 s) % 16 bytes in.
+// D_OFF: where the block's fp16 super-scale sits.
+template <> struct Fmt<B200Q_TYPE_IQ4_XS> { enum { SBB = 136, SPS = 2, NRAW = 2, BOX = 272, D_OFF = 0 }; };
+template <> struct Fmt<B200Q_TYPE_Q4_K>   { enum { SBB = 144, SPS = 1, NRAW = 4, BOX = 144, D_OFF = 0 }; };
+template <> struct Fmt<B200Q_TYPE_Q6_K>   { enum { SBB = 210, SPS = 1, NRAW = 2, BOX = 224, D_OFF = 208 }; };
 template <int TYPE> struct Smem {
     enum {
         SBB = Fmt<TYPE>::SBB, SPS = Fmt<TYPE>::SPS, NRAW = Fmt<TYPE>::NRAW,
-        ROWB = SPS * SBB,
+        ROWB = Fmt<TYPE>::BOX,
         RAW_STAGE = BM * ROWB,
         RAW_OFF = 0,
         ACT_OFF = RAW_OFF + NRAW * RAW_STAGE,
@@ -178,6 +182,40 @@ __device__ __forceinline__ void unpack_group(const uint8_t *blk, int jg, int kh,
             *reinterpret_cast<uint2 *>(a + LBO) = make_uint2(hh[0], hh[1]);
             *reinterpret_cast<uint2 *>(a + OPER_BYTES) = make_uint2(ll[0], ll[1]);
             *reinterpret_cast<uint2 *>(a + OPER_BYTES + LBO) = make_uint2(lh[0], lh[1]);
+        }
+    } else if (TYPE == B200Q_TYPE_Q6_K) {
+        // Q6_K: ql[128] | qh[64] | 16 int8 scales | d. Half n = jg of the block holds sub-blocks 4 jg .. + 3 ("parts"
+        // p = 0..3): part p takes the low (p < 2) or high nibbles of ql[64 n + 32 (p & 1) + t] and bits 2p, 2p + 1 of
+        // qh[32 n + t]; its scale is scales[8 n + 2 p + (t >= 16)]. The thread takes t = 16 kh .. + 15. The block is
+        // only 2-byte aligned in the stage: words are read aligned and funnel-shifted.
+        const int n = jg;
+        auto words4 = [&](int byte_off, uint32_t (&out)[4]) {
+            const uintptr_t p = (uintptr_t)(blk + byte_off);
+            const uint32_t *w = reinterpret_cast<const uint32_t *>(p & ~(uintptr_t)3);
+            const uint32_t sh = (uint32_t)(p & 3) * 8;
+            uint32_t a[5];
+#pragma unroll
+            for (int i = 0; i < 5; ++i) a[i] = w[i];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) out[i] = __funnelshift_r(a[i], a[i + 1], sh);
+        };
+        uint32_t qa[4], qb[4], qh[4];
+        words4(64 * n + 16 * kh, qa);
+        words4(64 * n + 32 + 16 * kh, qb);
+        words4(128 + 32 * n + 16 * kh, qh);
+#pragma unroll
+        for (int pp = 0; pp < GB; ++pp) {
+            const int sc = row_ok ? (int)(int8_t)blk[192 + 8 * n + 2 * pp + kh] : 0;       // 0: every limb zero
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t ql = (pp & 1) ? qb[i] : qa[i];
+                const uint32_t q6 = (((pp & 2) ? ql >> 4 : ql) & 0x0F0F0F0Fu) | (((qh[i] >> (2 * pp)) & 0x03030303u) << 4);
+                q6k_limbs4(q6, sc, &hi[i], &lo[i]);
+            }
+            uint8_t *a = a0 + pp * A_SLOT + kh * LBO;
+            *reinterpret_cast<uint4 *>(a) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4 *>(a + OPER_BYTES) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
         }
     } else {
         // Q4_K: d, dmin | 12 scale bytes | 4 x 32 bytes; bytes 32 g .. 32 g + 31 hold sub-block 2g in
@@ -299,7 +337,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                     if (lane == 0) {
                         // the whole [128 rows x ROWB] box in one tiled copy; rows past M arrive as zeros
                         mbar_expect_tx(bar(BAR_RAW_FULL + st), L::RAW_STAGE);
-                        tma_load_3d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, (s / SPS) * (ROWB / 4), U.row0, U.expert,
+                        tma_load_3d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, ((s / SPS) * SPS * SBB / 16) * 4, U.row0, U.expert,
                                     bar(BAR_RAW_FULL + st));
                     }
                     ++rs_run;
@@ -364,7 +402,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             for (int rs = 0; rs < nsb / SPS && ok; ++rs, ++rs_run) {
                 const int st = rs_run % NRAW;
                 if (!WAITP(0, bar(BAR_RAW_FULL + st), (rs_run / NRAW) & 1)) { ok = false; break; }
-                const uint8_t *rowp = smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB;
+                const uint8_t *rowp = smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + (rs * SPS * SBB) % 16;
 #pragma unroll
                 for (int h = 0; h < SPS; ++h) {
 #pragma unroll
@@ -405,7 +443,8 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 if (!WAITP(6, bar(BAR_ACC_FULL + buf), (s_run / NBUF) & 1)) { ok = false; break; }
                 tc_fence_after();
                 const float dwb = row_ok ? half_bits_to_float(*reinterpret_cast<const uint16_t *>(
-                                               smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + SBB * (s % SPS))) : 0.f;
+                                               smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + ((s / SPS) * SPS * SBB) % 16 +
+                                               SBB * (s % SPS) + Fmt<TYPE>::D_OFF)) : 0.f;
                 const f32x2 dw2 = f2_pack(dwb, dwb);
                 const uint32_t dxa = sbase + L::ACT_OFF + at * ACT_CHUNK + (u4 * CW / 8) * ACT_GROUP + 2048;   // scales of this thread's first group
                 const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * (2 * BN) + (uint32_t)u4 * CW;
@@ -752,9 +791,10 @@ size_t gemm_kq_act_bytes(int64_t K, int64_t N) {
 size_t gemm_kq_id_act_bytes(int64_t K, int64_t max_tiles) { return gemm_kq_act_bytes(K, max_tiles * kq::BN); }
 
 bool gemm_kq_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride) {
-    if (type != B200Q_TYPE_IQ4_XS && type != B200Q_TYPE_Q4_K) return false;
+    if (type != B200Q_TYPE_IQ4_XS && type != B200Q_TYPE_Q4_K && type != B200Q_TYPE_Q6_K) return false;
     // raw stages are whole super-blocks in 16-byte pieces: two per stage for IQ4_XS, one for Q4_K
-    if (K <= 0 || K % (type == B200Q_TYPE_IQ4_XS ? 512 : 256) || M <= 0 || N <= 0) return false;
+    // (Q6_K: rows of 210-byte blocks are a multiple of 16 bytes, as the tensor map needs, every 8 blocks)
+    if (K <= 0 || K % (type == B200Q_TYPE_IQ4_XS ? 512 : type == B200Q_TYPE_Q6_K ? 2048 : 256) || M <= 0 || N <= 0) return false;
     if ((uintptr_t)w % 16 || row_stride % 16) return false;
     if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return false;
     return true;
@@ -824,6 +864,7 @@ b200q_status launch_gemm_kq(b200q_ctx *ctx, int type, const void *w, size_t row_
     const size_t ms = row_stride * (size_t)M;
     if (type == B200Q_TYPE_IQ4_XS) return launch_kq_t<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
     if (type == B200Q_TYPE_Q4_K) return launch_kq_t<B200Q_TYPE_Q4_K>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
+    if (type == B200Q_TYPE_Q6_K) return launch_kq_t<B200Q_TYPE_Q6_K>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
     return fail(ctx, B200Q_UNSUPPORTED, "gemm_kq: type %d", type);
 }
 
@@ -838,6 +879,8 @@ b200q_status launch_gemm_kq_id(b200q_ctx *ctx, const b200q_tensor *src0, const b
         return launch_kq_t<B200Q_TYPE_IQ4_XS>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
     if (src0->type == B200Q_TYPE_Q4_K)
         return launch_kq_t<B200Q_TYPE_Q4_K>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
+    if (src0->type == B200Q_TYPE_Q6_K)
+        return launch_kq_t<B200Q_TYPE_Q6_K>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
     return fail(ctx, B200Q_UNSUPPORTED, "gemm_kq_id: type %d", src0->type);
 }
 

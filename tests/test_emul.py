@@ -80,6 +80,23 @@ def test_iq4xs_two_limbs():
             assert out[3] == sum(los[i] << (8 * b) for b, i in enumerate(high))
 
 
+def test_q6k_two_limbs():
+    """Q6_K on the tensor cores: sc * (q - 32) as 256 hi + lo with int8 limbs, for every scale and code."""
+    E = emul()
+    E.emul_q6k_limbs4.argtypes = [C.c_uint32, C.c_int, C.POINTER(C.c_uint32)]
+    for sc in range(-128, 128):
+        for q0 in range(0, 64, 4):
+            q6 = q0 | ((q0 + 1) << 8) | ((q0 + 2) << 16) | ((q0 + 3) << 24)
+            out = (C.c_uint32 * 2)()
+            E.emul_q6k_limbs4(q6, sc, out)
+            for b in range(4):
+                hi = (out[0] >> (8 * b)) & 0xFF
+                lo = (out[1] >> (8 * b)) & 0xFF
+                hi = hi - 256 if hi >= 128 else hi
+                lo = lo - 256 if lo >= 128 else lo
+                assert 256 * hi + lo == sc * (q0 + b - 32) and -16 <= hi <= 16
+
+
 def test_q4k_two_limbs_and_packed_scales():
     """Q4_K on the tensor cores: sc * q as 256 hi + lo with int8 limbs, four codes at a time; the packed
     extraction of the eight scales and mins must agree with the scalar one."""

@@ -191,3 +191,54 @@ def test_config2_shape_q4_K_prompt(ctx):
     assert st.get("gemm_tc", 0) == 1
     rows = np.unique(np.concatenate([[0, 127, 128, m - 1], np.random.default_rng(2).integers(0, m, 28)]))
     assert rel_err(got[:, rows], O.mul_mat_f64(t, w[rows], k, x, True)) < TOL
+
+
+# ---- Q6_K: sc * (q - 32) as two int8 limbs; 210-byte blocks staged through a 224-byte box (K % 2048 == 0) ----
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 2048), (300, 17, 2048), (300, 100, 4096), (77, 9, 4096), (1023, 33, 6144),
+                                   (512, 300, 2048)])
+def test_gemm_q6_K_matches_oracle(ctx, m, n, k):
+    rng = np.random.default_rng(m * 11 + n)
+    t = A.Q6_K
+    w = O.random_blocks(t, m, k, rng)
+    x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1 and st.get("gemm_kq_mins", 0) == 0, st
+    assert np.isfinite(got).all()
+    assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
+
+
+def test_gemm_q6_K_extreme_codes_and_other_k_fall_back(ctx):
+    """Scales at -128 / 127 with codes 0 / 63 (the largest limb sums); a K that is not a multiple of 2048 walks the GEMV."""
+    t, m, n, k = A.Q6_K, 128, 32, 2048
+    rng = np.random.default_rng(4)
+    w = O.random_blocks(t, m, k, rng).reshape(m, k // 256, 210)
+    w[:, :, 192:208] = 0x80                               # every scale -128
+    w[m // 2:, :, 192:208] = 0x7F                         # ... and 127 in the other half of the rows
+    w[:, :, :192] = 0x00                                  # code 0 (q - 32 = -32)
+    w[::2, :, :192] = 0xFF                                # code 63 in every other row
+    w = w.reshape(m, -1)
+    x = np.full((n, k), 1.5, dtype=np.float32)
+    x[::2] *= -1
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1
+    assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
+    k2 = 1280
+    w2 = O.random_blocks(t, 64, k2, rng)
+    x2 = rng.normal(0, 1, size=(20, k2)).astype(np.float32)
+    got2, st2 = run(ctx, t, w2, k2, x2)
+    assert st2.get("gemm_tc", 0) == 0 and st2.get("gemm_fallback_shape", 0) == 1
+    assert rel_err(got2, O.mul_mat_f64(t, w2, k2, x2, True)) < TOL
+
+
+def test_config2_head_q6_K_prompt(ctx):
+    """The decode config's LM head at a prompt width: Q6_K 32000 x 4096, 128 tokens; sampled rows, NMSE against f32 activations."""
+    t, m, n, k = A.Q6_K, 32000, 128, 4096
+    base = make_weights(t, 256, k, 0x5EED0004)
+    w = np.tile(base, (m // 256, 1))
+    x = O.fill_normal(n * k, 0x5EED0104, 1.0).reshape(n, k)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1
+    rows = np.unique(np.concatenate([[0, 127, 128, m - 1], np.random.default_rng(3).integers(0, m, 28)]))
+    assert rel_err(got[:, rows], O.mul_mat_f64(t, w[rows], k, x, True)) < TOL
+    assert nmse(got[:, rows], O.mul_mat_f64(t, w[rows], k, x, False)) < 5e-4

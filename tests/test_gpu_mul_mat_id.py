@@ -180,6 +180,11 @@ def test_config5_moe_q4_K_prompt_batch(ctx):
     assert np.isfinite(got).all()
 
 
+def test_mul_mat_id_tensor_core_q6_K(ctx):
+    st = check(ctx, A.Q6_K, n_expert=8, n_used=2, n_tok=300, m=200, k=2048, ne11_is_one=True, seed=77)
+    assert st.get("moe_gemm", 0) == 1 and st.get("gemm_tc", 0) == 1, st
+
+
 def test_gate_and_up_share_the_gathered_activation(ctx):
     """Two MUL_MAT_ID calls of one graph over the same src1 and ids (gate and up of a layer) gather and quantize the
     activation once; a third with another src1 (down) does it again; results stay right."""
