@@ -143,7 +143,10 @@ def prefill_section(ctx, world, rank, dist):
              ("config3 iq4_xs 17408x5120 x 512" + tag, A.IQ4_XS, 17408, 5120, 512, True),
              ("config3 iq4_xs 5120x17408 x 512" + tag, A.IQ4_XS, 5120, 17408, 512, True),
              ("config3 iq4_xs 17408x5120 x 2048" + tag, A.IQ4_XS, 17408, 5120, 2048, True),
-             ("config3 iq4_xs 5120x17408 x 2048" + tag, A.IQ4_XS, 5120, 17408, 2048, True)]
+             ("config3 iq4_xs 5120x17408 x 2048" + tag, A.IQ4_XS, 5120, 17408, 2048, True),
+             # beyond the listed configs: the decode config's matrices at a prompt width (Q4_K and Q6_K on the tensor cores)
+             ("extra q4_K 11008x4096 x 512" + tag, A.Q4_K, 11008, 4096, 512, True),
+             ("extra q6_K 32000x4096 x 512" + tag, A.Q6_K, 32000, 4096, 512, True)]
     out = []
     for name, t, m, k, n, split in cases:
         if world > 1 and not split:
