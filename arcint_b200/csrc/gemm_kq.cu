@@ -248,13 +248,14 @@ __device__ __forceinline__ void unpack_group(const uint8_t *blk, int jg, int kh,
 // One unit of work: a 128-row x 128-column output tile. Dense: tile_n-th run of 128 tokens; MUL_MAT_ID:
 // route tile tile_n (one expert, up to 128 routed pairs).
 struct Unit {
-    int tile_n, row0, valid_rows, expert, first, ncols;
+    int tile_n, row0, valid_rows, expert, first, ncols, sb0;      // sb0: first super-block (split K)
 };
 
 template <int TYPE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
-               int N, int n_tiles_dense, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word, TileRoute id) {
+               int N, int n_tiles_dense, int ksplit, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word,
+               TileRoute id) {
     typedef Smem<TYPE> L;
     constexpr int SBB = L::SBB, SPS = L::SPS, NRAW = L::NRAW, ROWB = L::ROWB;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -262,6 +263,9 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nsb = K / 256;                    // super-blocks (a multiple of SPS: the host gate)
+    // A dense product whose tiles fill the SMs badly (a last, nearly empty wave) is cut in two along K: a unit is
+    // then half the super-blocks of a tile and adds its result to a zeroed dst (two addends: the order cannot matter).
+    const int nsu = nsb / ksplit;               // super-blocks per unit
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bars = sbase + L::BAR_OFF;
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
@@ -271,9 +275,11 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     // Units of one row tile are neighbours, so blocks running together share weight rows in L2.
     const int tiles_m = (M + BM - 1) / BM;
     const int tiles_n = id.tiles ? __ldg(id.n_tiles) : n_tiles_dense;
-    const int n_units = tiles_m * tiles_n;
+    const int n_units = tiles_m * tiles_n * ksplit;
     auto unit_of = [&](int u) {
         Unit U;
+        U.sb0 = (u % ksplit) * nsu;
+        u /= ksplit;
         U.tile_n = u % tiles_n;
         U.row0 = (u / tiles_n) * BM;
         U.valid_rows = min(BM, M - U.row0);
@@ -330,7 +336,8 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
             const Unit U = unit_of(u);
             const uint8_t *act_tile = act + (size_t)U.tile_n * nsb * ACT_CHUNK;
-            for (int s = 0; s < nsb; ++s, ++s_run) {
+            for (int su = 0; su < nsu; ++su, ++s_run) {
+                const int s = U.sb0 + su;                 // the super-block inside the row
                 if (s % SPS == 0) {
                     const int st = rs_run % NRAW;
                     if (!WAITP(1, bar(BAR_RAW_EMPTY + st), ((rs_run / NRAW) & 1) ^ 1)) { ok = false; break; }
@@ -360,7 +367,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         int s_run = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-            for (int s = 0; s < nsb && ok; ++s, ++s_run) {
+            for (int su = 0; su < nsu && ok; ++su, ++s_run) {
                 const int at = s_run % NACT, buf = s_run % NBUF;
                 if (!WAITP(2, bar(BAR_ACT_FULL + at), (s_run / NACT) & 1)) { ok = false; break; }
                 if (!WAITP(7, bar(BAR_ACC_EMPTY + buf), ((s_run / NBUF) & 1) ^ 1)) { ok = false; break; }
@@ -398,8 +405,10 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         int rs_run = 0, g_run = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-            const bool row_ok = r < unit_of(u).valid_rows;
-            for (int rs = 0; rs < nsb / SPS && ok; ++rs, ++rs_run) {
+            const Unit U = unit_of(u);
+            const bool row_ok = r < U.valid_rows;
+            for (int rsu = 0; rsu < nsu / SPS && ok; ++rsu, ++rs_run) {
+                const int rs = U.sb0 / SPS + rsu;         // the raw stage inside the row
                 const int st = rs_run % NRAW;
                 if (!WAITP(0, bar(BAR_RAW_FULL + st), (rs_run / NRAW) & 1)) { ok = false; break; }
                 const uint8_t *rowp = smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + (rs * SPS * SBB) % 16;
@@ -434,8 +443,9 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             f32x2 acc2[CW / 2];
 #pragma unroll
             for (int c = 0; c < CW / 2; ++c) acc2[c] = 0ull;
-            for (int s = 0; s < nsb; ++s, ++s_run) {
-                if (s % SPS == 0 && s > 0) ++rs_run;
+            for (int su = 0; su < nsu; ++su, ++s_run) {
+                const int s = U.sb0 + su;
+                if (s % SPS == 0 && su > 0) ++rs_run;
                 const int st = rs_run % NRAW, at = s_run % NACT, buf = s_run % NBUF;
                 // stage barriers cannot advance past this thread: it releases both stages itself
                 if (s % SPS == 0 && !WAITP(0, bar(BAR_RAW_FULL + st), (rs_run / NRAW) & 1)) { ok = false; break; }
@@ -514,10 +524,14 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                     for (int c = 0; c < CW; c += 2) {
                         float a0, a1;
                         f2_unpack(acc2[c / 2], a0, a1);
-                        if (c < ncol) *o = a0;
-                        o += ldd;
-                        if (c + 1 < ncol) *o = a1;
-                        o += ldd;
+                        if (ksplit > 1) {
+                            if (c < ncol) atomicAdd(o, a0);
+                            if (c + 1 < ncol) atomicAdd(o + ldd, a1);
+                        } else {
+                            if (c < ncol) *o = a0;
+                            if (c + 1 < ncol) o[ldd] = a1;
+                        }
+                        o += 2 * ldd;
                     }
                 }
             }
@@ -835,9 +849,18 @@ static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride
     b200q_status st = make_weight_tmap3(ctx, &wmap, w, row_stride, M, (K / 256) * L::SBB, L::ROWB, n_mat, mat_stride);
     if (st != B200Q_OK) return st;
     // persistent blocks, one per SM, walking the (row tile, column tile) units
-    const int64_t units = n_tiles * ((M + kq::BM - 1) / kq::BM);
-    const unsigned grid = (unsigned)(units < ctx->sm_count ? units : ctx->sm_count);
-    kern<<<grid, kq::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, (int)n_tiles, dst, ldd, ctx->error_word, tr);
+    int64_t units = n_tiles * ((M + kq::BM - 1) / kq::BM);
+    // split K in two when that shortens the schedule: rounds of whole units against rounds of half units
+    int ksplit = 1;
+    const int64_t S = ctx->sm_count, nsb = K / 256;
+    if (!tr.tiles && nsb % (2 * L::SPS) == 0 && nsb >= 8 && 2 * ((units + S - 1) / S) > (2 * units + S - 1) / S) {
+        ksplit = 2;
+        B200Q_CUDA(ctx, cudaMemset2DAsync(dst, (size_t)ldd * sizeof(float), 0, (size_t)M * sizeof(float), (size_t)N, ctx->stream));
+        units *= 2;
+    }
+    const unsigned grid = (unsigned)(units < S ? units : S);
+    kern<<<grid, kq::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, (int)n_tiles, ksplit, dst, ldd,
+                                                       ctx->error_word, tr);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
     if (TYPE == B200Q_TYPE_Q4_K) {
