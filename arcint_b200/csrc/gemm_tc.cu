@@ -155,7 +155,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x, tile_m = blockIdx.y;
     const int row0 = tile_m * BM;
-    const int nst = K / (SB * KB);              // k-stages
+    // gridDim.z > 1: the product is cut along K (a launch whose whole tiles would leave a nearly empty last round);
+    // this block takes nst of the K / 256 stages, from s_off, and adds its result to a zeroed dst
+    const int nst_all = K / (SB * KB);
+    const int nst = nst_all / (int)gridDim.z;   // k-stages of this block
+    const int s_off = (int)blockIdx.z * nst;
     const int nblk = nst * SB;
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bars = sbase + L::BAR_OFF;
@@ -207,7 +211,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     if (warp == 0) {
         // ---- producer ----
         asm volatile("setmaxnreg.dec.sync.aligned.u32 " B200Q_STR(64) ";" ::: "memory");   // REGS_CTRL
-        const uint8_t *act_tile = act + (size_t)tile_n * nst * ACT_CHUNK;
+        const uint8_t *act_tile = act + ((size_t)tile_n * nst_all + s_off) * ACT_CHUNK;
         if (lane == 0) tma_prefetch_desc(&wmap);
         for (int s = 0; s < nst; ++s) {
             const int st = s % NSTAGE;
@@ -216,7 +220,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             if (lane == 0) {
                 // the stage's [128 rows x ROWB] box in one tiled copy; rows past M arrive as zeros
                 mbar_expect_tx(bar(BAR_RAW_FULL + st), L::RAW_STAGE);
-                tma_load_3d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, s * (ROWB / 4), row0, expert, bar(BAR_RAW_FULL + st));
+                tma_load_3d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, (s_off + s) * (ROWB / 4), row0, expert, bar(BAR_RAW_FULL + st));
             }
             if (!WAITP(3, bar(BAR_ACT_EMPTY + st), par)) break;
             if (lane == 0) {
@@ -383,10 +387,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             for (int c = 0; c < CW; c += 2) {
                 float a0, a1;
                 f2_unpack(acc2[c / 2], a0, a1);
-                if (c < ncol) *o = a0;
-                o += ldd;
-                if (c + 1 < ncol) *o = a1;
-                o += ldd;
+                if (gridDim.z > 1) {                     // two addends per element: the order cannot matter
+                    if (c < ncol) atomicAdd(o, a0);
+                    if (c + 1 < ncol) atomicAdd(o + ldd, a1);
+                } else {
+                    if (c < ncol) *o = a0;
+                    if (c + 1 < ncol) o[ldd] = a1;
+                }
+                o += 2 * ldd;
             }
         }
     }
@@ -456,7 +464,14 @@ static b200q_status launch_t(b200q_ctx *ctx, const void *w, size_t row_stride, s
     constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
     b200q_status st = make_weight_tmap3(ctx, &wmap, w, row_stride, M, (K / 32) * BB, tc::Raw<TYPE>::ROW, n_mat, mat_stride);
     if (st != B200Q_OK) return st;
-    dim3 grid((unsigned)n_tiles, (unsigned)((M + tc::BM - 1) / tc::BM));
+    // split K in two when that shortens the schedule: rounds of whole tiles against rounds of half tiles
+    const int64_t units = n_tiles * ((M + tc::BM - 1) / tc::BM), S = ctx->sm_count, nst = K / 256;
+    unsigned ksplit = 1;
+    if (!tr.tiles && nst % 2 == 0 && nst >= 8 && 2 * ((units + S - 1) / S) > (2 * units + S - 1) / S) {
+        ksplit = 2;
+        B200Q_CUDA(ctx, cudaMemset2DAsync(dst, (size_t)ldd * sizeof(float), 0, (size_t)M * sizeof(float), (size_t)N, ctx->stream));
+    }
+    dim3 grid((unsigned)n_tiles, (unsigned)((M + tc::BM - 1) / tc::BM), ksplit);
     kern<<<grid, tc::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd, ctx->error_word, tr);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
