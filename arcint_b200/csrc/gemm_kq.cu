@@ -600,16 +600,24 @@ q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_str
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
     uint4 h0n = __ldg(reinterpret_cast<const uint4 *>(w0)), h1n = __ldg(reinterpret_cast<const uint4 *>(w1));
+    // the staging threads (one per column) keep the next super-block's sums and scale in flight while this one's
+    // MMAs run: a load consumed at once would stall them, and everybody else at the barrier behind them
+    const int cc = cc0 + (int)threadIdx.x;
+    const bool stager = threadIdx.x < MC, col_ok = stager && cc < ncols;
+    int4 sv = make_int4(0, 0, 0, 0);
+    float dxv = 0.f;
+    auto fetch = [&](int sb) {
+        const size_t chunk = (size_t)tile * nsb + sb;
+        sv = __ldg(reinterpret_cast<const int4 *>(bsum + (chunk * BN + cc) * 8));
+        dxv = __ldg(reinterpret_cast<const float *>(act + chunk * ACT_CHUNK + (cc >> 3) * ACT_GROUP + 2048) + (cc & 7));
+    };
+    if (col_ok) fetch(0);
     for (int sb = 0; sb < nsb; ++sb) {
         const int pb = sb & 1;
-        if (threadIdx.x < MC) {
+        if (stager) {
             // stage the column's eight block sums as the B operand's f16 digits, and its scale
-            const int cc = cc0 + threadIdx.x;
             uint32_t w[8] = { 0, 0, 0, 0, 0, 0, 0, 0 };
-            float dx = 0.f;
-            if (cc < ncols) {
-                const size_t chunk = (size_t)tile * nsb + sb;
-                const int4 sv = *reinterpret_cast<const int4 *>(bsum + (chunk * BN + cc) * 8);
+            if (col_ok) {
                 const int v[4] = { sv.x, sv.y, sv.z, sv.w };
 #pragma unroll
                 for (int qq = 0; qq < 4; ++qq) {
@@ -620,11 +628,11 @@ q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_str
                     w[2 * qq] = *reinterpret_cast<const uint32_t *>(&lo);
                     w[2 * qq + 1] = *reinterpret_cast<const uint32_t *>(&hi);
                 }
-                dx = reinterpret_cast<const float *>(act + chunk * ACT_CHUNK + (cc >> 3) * ACT_GROUP + 2048)[cc & 7];
             }
             *reinterpret_cast<uint4 *>(&cb[pb][threadIdx.x][0]) = make_uint4(w[0], w[1], w[2], w[3]);
             *reinterpret_cast<uint4 *>(&cb[pb][threadIdx.x][4]) = make_uint4(w[4], w[5], w[6], w[7]);
-            cdx[pb][threadIdx.x] = dx;
+            cdx[pb][threadIdx.x] = col_ok ? dxv : 0.f;
+            if (col_ok && sb + 1 < nsb) fetch(sb + 1);
         }
         const uint4 h0 = h0n, h1 = h1n;                      // d, dmin | 12 scale bytes of the two rows' blocks
         if (sb + 1 < nsb) {
