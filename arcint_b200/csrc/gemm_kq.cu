@@ -126,24 +126,26 @@ quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t n
             x = reinterpret_cast<const float *>(base + c1 * nb1 + c2 * nb2 + c3 * nb3) + (int64_t)s * 256 + 128 * half;
         }
     }
+    // the thread's 128 values stay in registers between the maximum and the rounding pass
+    float4 v[32];
     float amax = 0.f;
-    if (x)
-        for (int i = 0; i < 32; ++i) {
-            const float4 f = *reinterpret_cast<const float4 *>(x + 4 * i);
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
-        }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        v[i] = x ? __ldg(reinterpret_cast<const float4 *>(x) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+    }
     part[threadIdx.x] = amax;
     __syncthreads();
     const float bm = fmaxf(part[col], part[col + 128]);
     const float iq = bm > 1e-30f ? __fdiv_rn(127.f, bm) : 0.f;
     if (!store) return;
-#pragma unroll 1
+#pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
         const int j = 4 * half + jj;
         uint32_t w[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const float4 f = x ? *reinterpret_cast<const float4 *>(x + 32 * jj + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 f = v[8 * jj + i];
             w[i] = (uint32_t)(__float2int_rn(__fmul_rn(f.x, iq)) & 0xFF) | ((uint32_t)(__float2int_rn(__fmul_rn(f.y, iq)) & 0xFF) << 8) |
                    ((uint32_t)(__float2int_rn(__fmul_rn(f.z, iq)) & 0xFF) << 16) | ((uint32_t)(__float2int_rn(__fmul_rn(f.w, iq)) & 0xFF) << 24);
         }
