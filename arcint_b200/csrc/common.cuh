@@ -210,7 +210,7 @@ b200q_status launch_gemm_tc_id(b200q_ctx *ctx, const b200q_tensor *src0, const b
 b200q_status launch_gemm_tc(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                             const uint8_t *act, int64_t N, float *dst, int64_t ldd);
 
-// gemm_kq.cu: tensor-core prefill GEMM for IQ4_XS (integer sub-scales folded into two int8 limbs)
+// gemm_kq.cu: tensor-core prefill GEMM for the super-block types IQ4_XS, Q4_K and Q6_K (integer sub-scales folded into two int8 limbs)
 bool         gemm_kq_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride);
 size_t       gemm_kq_act_bytes(int64_t K, int64_t N);
 b200q_status launch_quantize_tiled256(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out);

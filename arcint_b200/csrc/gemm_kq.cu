@@ -1,7 +1,7 @@
-// gemm_kq.cu -- prefill GEMM for the 256-weight super-block types IQ4_XS and Q4_K on the tensor cores
+// gemm_kq.cu -- prefill GEMM for the 256-weight super-block types IQ4_XS, Q4_K and Q6_K on the tensor cores
 // (tcgen05 int8 MMA).
 //
-//   dst[M, N] = W[M, K] (136-byte IQ4_XS / 144-byte Q4_K super-blocks) x X[K, N] (f32), N > 8 tokens
+//   dst[M, N] = W[M, K] (136-byte IQ4_XS / 144-byte Q4_K / 210-byte Q6_K super-blocks) x X[K, N] (f32), N > 8 tokens
 //
 // ggml's form for this type is integer inside a 256-weight super-block and float once per
 // super-block: out += d_w * d_x * sum_sb (ls_sb - 32) * I_sb, with I_sb the exact dot of the
