@@ -56,11 +56,13 @@ class B200QError(RuntimeError):
 
 class Tensor(C.Structure):
     """b200q_tensor: the ggml_tensor fields the path reads."""
-    _fields_ = [("type", C.c_int32), ("ne", C.c_int64 * 4), ("nb", C.c_size_t * 4), ("data", C.c_void_p)]
+    _fields_ = [("type", C.c_int32), ("ne", C.c_int64 * 4), ("nb", C.c_size_t * 4), ("data", C.c_void_p),
+                ("id", C.c_void_p)]
 
     @staticmethod
-    def make(type_, ne, nb, data):
+    def make(type_, ne, nb, data, ident=None):
         t = Tensor()
+        t.id = ident
         t.type = type_
         ne = list(ne) + [1] * (4 - len(ne))
         nb = list(nb)
@@ -129,6 +131,7 @@ def lib():
     L.b200q_mul_mat_id_ep.argtypes = [vp, TP, TP, TP, TP, C.c_int]
     L.b200q_mul_mat_noalloc.argtypes = [C.c_int, vp, TP, TP, TP]
     L.b200q_noalloc_last_error.restype = C.c_char_p
+    L.b200q_noalloc_device_error.argtypes = [C.c_int, C.POINTER(C.c_int)]
     L.b200q_buffer_alloc.argtypes = [vp, sz, C.POINTER(vp)]
     L.b200q_buffer_free.argtypes = [vp, vp]
     L.b200q_tensor_set.argtypes = [vp, vp, vp, sz]
@@ -156,7 +159,7 @@ EXPORTS = [
     "b200q_init", "b200q_free", "b200q_last_error", "b200q_get_stream", "b200q_version", "b200q_supports", "b200q_mul_mat",
     "b200q_mul_mat_id", "b200q_graph_begin", "b200q_capture_begin", "b200q_capture_end", "b200q_graph_launch",
     "b200q_graph_free", "b200q_tp_unique_id", "b200q_tp_init", "b200q_tp_rank", "b200q_tp_shard", "b200q_all_reduce_f32",
-    "b200q_all_gather", "b200q_all_to_all_v", "b200q_tp_check", "b200q_mul_mat_id_ep", "b200q_mul_mat_noalloc", "b200q_noalloc_last_error", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
+    "b200q_all_gather", "b200q_all_to_all_v", "b200q_tp_check", "b200q_mul_mat_id_ep", "b200q_mul_mat_noalloc", "b200q_noalloc_last_error", "b200q_noalloc_device_error", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
     "b200q_tensor_get", "b200q_tensor_stage", "b200q_tensor_fetch", "b200q_tensor_copy", "b200q_synchronize", "b200q_host_alloc", "b200q_host_free",
     "b200q_stats", "b200q_stats_reset", "b200q_timer_start", "b200q_timer_stop", "b200q_flush_l2",
     "b200q_debug_quantize_act", "b200q_debug_dequantize",

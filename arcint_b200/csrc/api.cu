@@ -27,7 +27,7 @@ const char *stat_name(int s) {
     }
     static const char *rest[] = { "gemv_id", "gemv_id_unaligned", "moe_route", "route_cache_hit", "moe_gemm", "moe_pack",
                                   "gemm_tc", "gemm_tc_quantize", "gemm_fallback_shape", "tp_allreduce", "tp_allgather",
-                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins" };
+                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins", "gemv_stream" };
     return rest[s - ST_GEMV_ID];
 }
 
@@ -124,6 +124,7 @@ static b200q_status check_ids(b200q_ctx *ctx, const b200q_tensor *src0, const b2
 static b200q_status get_activation(b200q_ctx *ctx, int form, const b200q_tensor *src1, ActView *out) {
     ActKey key;
     key.data = src1->data;
+    key.id = src1->id;
     key.form = form;
     key.gen = ctx->generation;
     for (int i = 0; i < 4; ++i) { key.ne[i] = src1->ne[i]; key.nb[i] = src1->nb[i]; }
@@ -225,12 +226,14 @@ b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
         }
         ctx->own_stream = true;
     }
-    cudaEventCreate(&ctx->ev0);
-    cudaEventCreate(&ctx->ev1);
-    cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking);
-    cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking);
-    cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming);
-    cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming);
+    if (cudaEventCreate(&ctx->ev0) != cudaSuccess || cudaEventCreate(&ctx->ev1) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+        b200q_free(ctx);
+        return B200Q_CUDA_ERROR;
+    }
     if (cudaMalloc(&ctx->error_word, sizeof(int)) != cudaSuccess || cudaMemset(ctx->error_word, 0, sizeof(int)) != cudaSuccess) {
         b200q_free(ctx);
         return B200Q_NO_MEMORY;
@@ -239,6 +242,8 @@ b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
     ctx->no_tc = no_tc && no_tc[0] == '1';
     const char *no_pdl = getenv("B200Q_NO_PDL");     // plain stream order in the decode chain (comparisons)
     ctx->no_pdl = no_pdl && no_pdl[0] == '1';
+    const char *no_stream = getenv("B200Q_NO_STREAM");   // the older GEMV kernel for every shape (comparisons)
+    ctx->no_stream = no_stream && no_stream[0] == '1';
     *out = ctx;
     return B200Q_OK;
 }
@@ -375,12 +380,14 @@ b200q_status b200q_mul_mat_id(b200q_ctx *ctx, const b200q_tensor *src0, const b2
         count(ctx, ST_MOE_GEMM);
         // the scratch may already hold this very activation, gathered for these ids in this graph
         auto &ma = ctx->moe_act;
-        bool ready = !grew && ma.src1 == src1->data && ma.ids == ids->data && ma.gen == ctx->generation && ma.per32 == (int)per32 &&
+        bool ready = !grew && ma.src1 == src1->data && ma.ids == ids->data && ma.src1_id == src1->id && ma.ids_id == ids->id && ma.gen == ctx->generation && ma.per32 == (int)per32 &&
                      ma.n_expert == n_expert;
         for (int i = 0; i < 4 && ready; ++i) ready = ma.ne[i] == src1->ne[i] && ma.nb[i] == src1->nb[i];
         if (ready) count(ctx, ST_ACT_CACHE_HIT);
         ma.src1 = src1->data;
         ma.ids = ids->data;
+        ma.src1_id = src1->id;
+        ma.ids_id = ids->id;
         ma.gen = ctx->generation;
         ma.per32 = (int)per32;
         ma.n_expert = n_expert;
@@ -422,6 +429,11 @@ b200q_status b200q_capture_begin(b200q_ctx *ctx) {
     B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
     B200Q_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
     ctx->capturing = true;
+    // a recorded sequence must contain its own quantizers, routes and gathers: nothing cached by the
+    // warm-up run before the capture may be reused inside it, or every replay would multiply by the
+    // warm-up's activation
+    ++ctx->generation;
+    ctx->moe_act.src1 = nullptr;
     // the copy stream joins the capture, so staged and fetched copies become nodes of the graph
     B200Q_CUDA(ctx, cudaEventRecord(ctx->ev_fork, ctx->stream));
     B200Q_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->ev_fork, 0));
@@ -435,6 +447,8 @@ b200q_status b200q_capture_end(b200q_ctx *ctx, b200q_graph **out) {
     *out = nullptr;
     if (!ctx->capturing) return fail(ctx, B200Q_INVALID, "no capture open");
     ctx->capturing = false;
+    ++ctx->generation;                                      // and nothing cached inside the capture outlives it
+    ctx->moe_act.src1 = nullptr;
     join_copy_stream(ctx);                                  // every forked stream must be back before the capture ends
     b200q_graph *g = new b200q_graph();
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);

@@ -64,12 +64,13 @@ struct Workspace {
 
 struct ActKey {
     const void *data;
+    const void *id;          // the caller's tensor identity (NULL: unknown)
     int64_t ne[4];
     size_t  nb[4];
     int     form;
     uint64_t gen;
     bool operator==(const ActKey &o) const {
-        if (data != o.data || form != o.form || gen != o.gen) return false;
+        if (data != o.data || id != o.id || form != o.form || gen != o.gen) return false;
         for (int i = 0; i < 4; ++i) if (ne[i] != o.ne[i] || nb[i] != o.nb[i]) return false;
         return true;
     }
@@ -91,7 +92,7 @@ enum Stat {
     ST_GEMV_UNALIGNED_COL0 = ST_GEMV_COL0 + 9,    // + ncols
     ST_GEMV_ID = ST_GEMV_UNALIGNED_COL0 + 9, ST_GEMV_ID_UNALIGNED, ST_MOE_ROUTE, ST_ROUTE_CACHE_HIT, ST_MOE_GEMM,
     ST_MOE_PACK, ST_GEMM_TC, ST_GEMM_TC_QUANT, ST_GEMM_FALLBACK_SHAPE, ST_TP_ALLREDUCE, ST_TP_ALLGATHER,
-    ST_EP_DISPATCH, ST_EP_COMBINE, ST_GRAPH_LAUNCH, ST_NO_ALLOC, ST_GEMM_KQ_MINS,
+    ST_EP_DISPATCH, ST_EP_COMBINE, ST_GRAPH_LAUNCH, ST_NO_ALLOC, ST_GEMM_KQ_MINS, ST_GEMV_STREAM,
     ST_COUNT
 };
 const char *stat_name(int s);
@@ -109,12 +110,13 @@ struct b200q_ctx {
     uint64_t     generation = 1;
     // what the gathered, tiled activation scratch of the tensor-core MUL_MAT_ID holds (gate and up of a layer
     // read the same src1 through the same ids: the second call finds it ready)
-    struct { const void *src1 = nullptr, *ids = nullptr; int64_t ne[4] = {0, 0, 0, 0}; size_t nb[4] = {0, 0, 0, 0}; uint64_t gen = 0; int per32 = -1, n_expert = 0; } moe_act;
+    struct { const void *src1 = nullptr, *ids = nullptr, *src1_id = nullptr, *ids_id = nullptr; int64_t ne[4] = {0, 0, 0, 0}; size_t nb[4] = {0, 0, 0, 0}; uint64_t gen = 0; int per32 = -1, n_expert = 0; } moe_act;
     int          route_pinned = -1;       // a route entry in use across a nested call: not a victim
     uint64_t     private_generation = 0;  // expert-parallel calls: generations of their internal products
     bool         capturing = false;
     bool         no_tc = false;           // B200Q_NO_TC=1: never take the tensor-core GEMM
     bool         no_pdl = false;          // B200Q_NO_PDL=1: plain stream order between the decode kernels
+    bool         no_stream = false;       // B200Q_NO_STREAM=1: every GEMV through the per-warp ring kernel (comparisons)
     std::string  last_error;
     std::string  stats_text;
     uint64_t     counters[b200q::ST_COUNT] = {};

@@ -12,6 +12,7 @@
 // (marfrit/arcint contrib/llama.cpp/patches/0000-01-kquant-integer-dpas.patch:3882-3915,
 // host side ggml_cl_mul_mv_kq_q8_1 at :817-857).
 #include "gemv_kernel.cuh"
+#include "gemv_stream.cuh"
 #include "common.cuh"
 
 #include <limits.h>
@@ -52,12 +53,84 @@ static b200q_status launch_one(b200q_ctx *ctx, const void *w, size_t row_stride,
     return B200Q_OK;
 }
 
+// The slice-resident kernel (gemv_stream.cuh) for rows that bulk copies can fetch (16-byte aligned
+// start, stride and length). Returns false when the shape does not fit it: more than 16 warps per
+// group (K beyond 16 slices, or 8 for more than four columns) or a ring beyond shared memory.
+template <int TYPE, int NC, int R>
+static bool try_launch_stream(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K, const GemvAct &act,
+                              float *dst, int64_t ldd, b200q_status *st) {
+    typedef GemvFmt<TYPE> F;
+    constexpr int CW = NC > 4 ? 2 : 1, NSETS = 3;
+    const int nblk = (int)(K / F::BLK_W), nsl = (nblk + F::STAGE_BLOCKS - 1) / F::STAGE_BLOCKS, nw = nsl * CW;
+    if (nw > GEMV_STREAM_MAX_THREADS / 32) return false;
+    const int row_bytes = nblk * F::BLK_B;
+    const size_t gb = (gemv_stream_group_smem(row_bytes, R, NSETS, nw) + 15) / 16 * 16;
+    if (gb > 200 * 1024) return false;
+    int groups = 4 / nw < 1 ? 1 : 4 / nw;                  // blocks of about four warps measured best
+    while (groups > 1 && groups * gb > 200 * 1024) --groups;
+    const size_t smem = groups * gb;
+    const int threads = groups * nw * 32;
+    auto kern = gemv_stream_kernel<TYPE, NC, R, NSETS>;
+    // resident blocks per SM for this block shape, asked once per (device, shape)
+    struct Occ { int threads; size_t smem; int blocks; bool attr; };
+    static Occ occ_dev[B200Q_MAX_DEVICES] = {};
+    Occ &o = occ_dev[ctx->device % B200Q_MAX_DEVICES];
+    if (!o.attr) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) { *st = fail(ctx, B200Q_CUDA_ERROR, "gemv_stream attribute: %s", cudaGetErrorString(e)); return true; }
+        o.attr = true;
+    }
+    if (o.threads != threads || o.smem != smem) {
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem);
+        if (e != cudaSuccess) { *st = fail(ctx, B200Q_CUDA_ERROR, "gemv_stream occupancy: %s", cudaGetErrorString(e)); return true; }
+        o.threads = threads;
+        o.smem = smem;
+        o.blocks = n > 0 ? n : 1;
+    }
+    const int64_t n_units = (M + R - 1) / R;
+    int64_t blocks = (n_units + groups - 1) / groups;
+    const int64_t cap = (int64_t)ctx->sm_count * o.blocks;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    cudaError_t e = launch_pdl(!ctx->no_pdl, kern, dim3((unsigned)blocks), dim3(threads), smem, ctx->stream, (const uint8_t *)w,
+                               row_stride, (int)M, nblk, act, dst, (int)ldd, groups, ctx->error_word);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    *st = e == cudaSuccess ? B200Q_OK : fail(ctx, B200Q_CUDA_ERROR, "gemv_stream launch: %s", cudaGetErrorString(e));
+    return true;
+}
+
+// Which kernel takes a dense, aligned product of NC columns (measured on B200, CUDA-graph replay over
+// rotating weight copies): the slice-resident kernel wins at one column and from four columns on
+// (20-25 % at 4 and 8 columns); at two and three columns, and for the 210-byte Q6_K blocks at one
+// column, the per-warp ring kernel is a few percent faster.
+template <int TYPE, int NC>
+static bool stream_preferred() {
+    if (NC == 2 || NC == 3) return false;
+    if (NC == 1 && TYPE == B200Q_TYPE_Q6_K) return false;
+    return true;
+}
+
 template <int TYPE, int NC>
 static b200q_status launch_nc(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K,
                               const GemvAct &act, float *dst, int64_t ldd, bool aligned) {
     // rows per warp batch: four; eight for three or four columns of a small-block type, where
     // the activation registers are worth sharing further (measured on B200)
     constexpr bool wide = (NC == 3 || NC == 4) && GemvStage<TYPE>::BYTES <= 1152;
+    if (aligned && !ctx->no_stream && M <= INT32_MAX / 2 && ldd <= INT32_MAX && stream_preferred<TYPE, NC>()) {
+        typedef GemvFmt<TYPE> F;
+        const int row_bytes = (int)(K / F::BLK_W) * F::BLK_B;
+        // rows per ring stage: four, two when a stage of four long rows would crowd shared memory or a
+        // single column leaves little work per row
+        const bool two = NC == 1 || (size_t)12 * gemv_stream_slot(row_bytes) > 36 * 1024;
+        b200q_status st = B200Q_OK;
+        const bool took = two ? try_launch_stream<TYPE, NC, 2>(ctx, w, row_stride, M, K, act, dst, ldd, &st)
+                              : try_launch_stream<TYPE, NC, 4>(ctx, w, row_stride, M, K, act, dst, ldd, &st);
+        if (took) {
+            if (st == B200Q_OK) count(ctx, ST_GEMV_STREAM);
+            return st;
+        }
+    }
     GemvId none = {};
     return launch_one<TYPE, NC, wide ? 8 : 4, 4, 2, false>(ctx, w, row_stride, M, K, act, dst, ldd, aligned, none, 0);
 }

@@ -63,6 +63,17 @@ B200Q_HD int dp4a_us(uint32_t a, int b, int c) {
 #endif
 }
 
+// two signed 16-bit halves of a times the two low unsigned bytes of b, summed into c
+B200Q_HD int dp2a_lo_su(uint32_t a, uint32_t b, int c) {
+#ifdef __CUDA_ARCH__
+    int d;
+    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+#else
+    return c + (int)(int16_t)(a & 0xFFFFu) * (int)(b & 0xFFu) + (int)(int16_t)(a >> 16) * (int)((b >> 8) & 0xFFu);
+#endif
+}
+
 B200Q_HD int ld_s16(const int16_t *p) {
 #ifdef __CUDA_ARCH__
     return (int)__ldg(p);
@@ -151,12 +162,9 @@ B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, const i
             const int8_t *xp = act.q + (size_t)cols[c] * K + 256 * blk + 64 * g;
 #pragma unroll
             for (int j = 0; j < 4; ++j) X.x[c][j] = hd_ld16(xp + 16 * j);
-            const float dx = ld_f32(act.d32 + (size_t)cols[c] * (K / 256) + blk);
-            X.f0[c] = dx * 0.0625f;      // both nibble dots are kept x16
-            X.f1[c] = dx;
-            const uint32_t bp = ld_u32(act.s32 + (size_t)cols[c] * (K / 32) + 8 * blk + 2 * g);
-            X.i0[c] = sext16(bp);
-            X.i1[c] = sext16(bp >> 16);
+            X.f0[c] = ld_f32(act.d32 + (size_t)cols[c] * (K / 256) + blk);
+            // the sums of the lane's two sub-blocks, kept as the pair of 16-bit halves they are stored as
+            X.i0[c] = (int)ld_u32(act.s32 + (size_t)cols[c] * (K / 32) + 8 * blk + 2 * g);
         }
     } else if (TYPE == B200Q_TYPE_IQ4_XS) {
         // lane -> block sb and sub-block pair pp: 32 bytes = sub-blocks 2pp and 2pp+1
@@ -195,8 +203,9 @@ B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, const i
 
 // sw: the staged words of one weight row for the stage X was loaded for. acc[c] += partial.
 template <int TYPE, int NC>
-B200Q_HD void gemv_lane_row(const uint32_t *sw, int lane, const GemvX<NC> &X, float (&acc)[NC]) {
+B200Q_HD void gemv_lane_row(const uint32_t *sw_ptr, int lane, const GemvX<NC> &X, float (&acc)[NC]) {
     typedef GemvFmt<TYPE> F;
+    const Stage sw(sw_ptr);
     if (TYPE == B200Q_TYPE_Q4_0) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
@@ -214,7 +223,7 @@ B200Q_HD void gemv_lane_row(const uint32_t *sw, int lane, const GemvX<NC> &X, fl
                 int hi0 = dp4a_us(q[0] & 0xF0F0F0F0u, xb.x, u ? X.i1[c] : X.i0[c]);
                 int hi1 = dp4a_us(q[1] & 0xF0F0F0F0u, xb.y, 0);
                 hi0 = dp4a_us(q[2] & 0xF0F0F0F0u, xb.z, hi0);   hi1 = dp4a_us(q[3] & 0xF0F0F0F0u, xb.w, hi1);
-                const int si = 16 * (lo0 + lo1) + hi0 + hi1;                  // 16 * sum((n - 8) x)
+                const int si = 16 * (lo0 + lo1) + (hi0 + hi1);                // 16 * sum((n - 8) x)
                 acc[c] += (float)si * (d * (u ? X.f1[c] : X.f0[c]));
             }
         }
@@ -239,48 +248,64 @@ B200Q_HD void gemv_lane_row(const uint32_t *sw, int lane, const GemvX<NC> &X, fl
     } else if (TYPE == B200Q_TYPE_Q4_K) {
         if (!X.live) return;
         const int sb = lane >> 2, g = lane & 3;
-        const uint32_t *bw = sw + sb * (144 / 4);
-        const uint32_t hd = bw[0], s0 = bw[1], s1 = bw[2], s2 = bw[3];
-        const float d = hd_half_bits((uint16_t)hd), dmin = hd_half_bits((uint16_t)(hd >> 16));
+        const uint32_t bw = sb * (144 / 4);                 // word index; blocks are 16-byte aligned inside the stage
+        const U4 h = sw.ld16(bw);                           // d | dmin, then the 12 scale bytes
+        const float d16 = hd_half_bits((uint16_t)h.x) * 0.0625f;     // both nibble dots are kept x16
+        const float dmin = hd_half_bits((uint16_t)(h.x >> 16));
         // the 6-bit scales / mins of sub-blocks 0..3 and 4..7 as four bytes each
-        const uint32_t scw = g < 2 ? (s0 & 0x3F3F3F3Fu) : ((s2 & 0x0F0F0F0Fu) | ((s0 >> 2) & 0x30303030u));
-        const uint32_t mnw = g < 2 ? (s1 & 0x3F3F3F3Fu) : (((s2 >> 4) & 0x0F0F0F0Fu) | ((s1 >> 2) & 0x30303030u));
+        const uint32_t scw = g < 2 ? (h.y & 0x3F3F3F3Fu) : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
+        const uint32_t mnw = g < 2 ? (h.z & 0x3F3F3F3Fu) : (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u));
         const int sh = 16 * (g & 1);
         const int sc0 = (int)((scw >> sh) & 0xFFu) * 16, sc1 = (int)((scw >> (sh + 8)) & 0xFFu);
-        const int m0 = (int)((mnw >> sh) & 0xFFu), m1 = (int)((mnw >> (sh + 8)) & 0xFFu);
-        const uint32_t *qp = bw + 4 + 8 * g;
-        uint32_t q[8];
+        const uint32_t mw = mnw >> sh;                      // the mins of the lane's two sub-blocks in bytes 0 and 1
+        const U4 qa = sw.ld16(bw + 4 + 8 * g), qb = sw.ld16(bw + 8 + 8 * g);
+        const uint32_t q[8] = { qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w };
+        uint32_t ql[8], qh[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) q[j] = qp[j];
+        for (int j = 0; j < 8; ++j) { ql[j] = q[j] & 0x0F0F0F0Fu; qh[j] = q[j] & 0xF0F0F0F0u; }
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
             const I4 a0 = X.x[c][0], a1 = X.x[c][1], b0 = X.x[c][2], b1 = X.x[c][3];
-            int il0 = dp4a_ss(q[0] & 0x0F0F0F0Fu, a0.x, 0), il1 = dp4a_ss(q[1] & 0x0F0F0F0Fu, a0.y, 0);
-            il0 = dp4a_ss(q[2] & 0x0F0F0F0Fu, a0.z, il0); il1 = dp4a_ss(q[3] & 0x0F0F0F0Fu, a0.w, il1);
-            il0 = dp4a_ss(q[4] & 0x0F0F0F0Fu, a1.x, il0); il1 = dp4a_ss(q[5] & 0x0F0F0F0Fu, a1.y, il1);
-            il0 = dp4a_ss(q[6] & 0x0F0F0F0Fu, a1.z, il0); il1 = dp4a_ss(q[7] & 0x0F0F0F0Fu, a1.w, il1);
-            int ih0 = dp4a_us(q[0] & 0xF0F0F0F0u, b0.x, 0), ih1 = dp4a_us(q[1] & 0xF0F0F0F0u, b0.y, 0);
-            ih0 = dp4a_us(q[2] & 0xF0F0F0F0u, b0.z, ih0); ih1 = dp4a_us(q[3] & 0xF0F0F0F0u, b0.w, ih1);
-            ih0 = dp4a_us(q[4] & 0xF0F0F0F0u, b1.x, ih0); ih1 = dp4a_us(q[5] & 0xF0F0F0F0u, b1.y, ih1);
-            ih0 = dp4a_us(q[6] & 0xF0F0F0F0u, b1.z, ih0); ih1 = dp4a_us(q[7] & 0xF0F0F0F0u, b1.w, ih1);
-            const int si = sc0 * (il0 + il1) + sc1 * (ih0 + ih1);            // 16 * sum_sb sc * dot
-            const int sm = m0 * X.i0[c] + m1 * X.i1[c];
-            acc[c] += (d * X.f0[c]) * (float)si - (dmin * X.f1[c]) * (float)sm;
+            int il, ih;
+            if (NC <= 2) {       // few columns: two chains per dot so the dependent latency is covered
+                int il1 = dp4a_ss(ql[1], a0.y, 0), ih1 = dp4a_us(qh[1], b0.y, 0);
+                il = dp4a_ss(ql[0], a0.x, 0);    ih = dp4a_us(qh[0], b0.x, 0);
+                il = dp4a_ss(ql[2], a0.z, il);   il1 = dp4a_ss(ql[3], a0.w, il1);
+                ih = dp4a_us(qh[2], b0.z, ih);   ih1 = dp4a_us(qh[3], b0.w, ih1);
+                il = dp4a_ss(ql[4], a1.x, il);   il1 = dp4a_ss(ql[5], a1.y, il1);
+                ih = dp4a_us(qh[4], b1.x, ih);   ih1 = dp4a_us(qh[5], b1.y, ih1);
+                il = dp4a_ss(ql[6], a1.z, il);   il1 = dp4a_ss(ql[7], a1.w, il1);
+                ih = dp4a_us(qh[6], b1.z, ih);   ih1 = dp4a_us(qh[7], b1.w, ih1);
+                il += il1;
+                ih += ih1;
+            } else {
+                il = dp4a_ss(ql[0], a0.x, 0);    ih = dp4a_us(qh[0], b0.x, 0);
+                il = dp4a_ss(ql[1], a0.y, il);   ih = dp4a_us(qh[1], b0.y, ih);
+                il = dp4a_ss(ql[2], a0.z, il);   ih = dp4a_us(qh[2], b0.z, ih);
+                il = dp4a_ss(ql[3], a0.w, il);   ih = dp4a_us(qh[3], b0.w, ih);
+                il = dp4a_ss(ql[4], a1.x, il);   ih = dp4a_us(qh[4], b1.x, ih);
+                il = dp4a_ss(ql[5], a1.y, il);   ih = dp4a_us(qh[5], b1.y, ih);
+                il = dp4a_ss(ql[6], a1.z, il);   ih = dp4a_us(qh[6], b1.z, ih);
+                il = dp4a_ss(ql[7], a1.w, il);   ih = dp4a_us(qh[7], b1.w, ih);
+            }
+            const int si = sc0 * il + sc1 * ih;                           // 16 * sum_sb sc * dot
+            const int sm = dp2a_lo_su((uint32_t)X.i0[c], mw, 0);          // sum_sb m * sum(x)
+            acc[c] += X.f0[c] * (d16 * (float)si - dmin * (float)sm);
         }
     } else if (TYPE == B200Q_TYPE_IQ4_XS) {
         if (!X.live) return;
         const int sb = lane >> 2, pp = lane & 3;
-        const uint32_t *bw = sw + sb * (136 / 4);
-        const uint32_t hd = bw[0];
+        const uint32_t bw = sb * (136 / 4);                 // word index; blocks are 8-byte aligned inside the stage
+        const uint32_t hd = sw.w(bw), sl = sw.w(bw + 1);
         const float d = hd_half_bits((uint16_t)hd);
-        const int ls0 = iq4xs_ls(hd >> 16, bw[1], 2 * pp) - 32, ls1 = iq4xs_ls(hd >> 16, bw[1], 2 * pp + 1) - 32;
-        const uint32_t *qp = bw + 2 + 8 * pp;
+        const int ls0 = iq4xs_ls(hd >> 16, sl, 2 * pp) - 32, ls1 = iq4xs_ls(hd >> 16, sl, 2 * pp + 1) - 32;
+        const uint32_t qp = bw + 2 + 8 * pp;
         uint32_t w[16];      // sub-block 2pp: w[0..3] weights 0..15, w[4..7] weights 16..31; then 2pp+1
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint32_t q = qp[4 * h + j];
+                const uint32_t q = sw.w(qp + 4 * h + j);
                 w[8 * h + j]     = iq4nl_lookup4(q & 0x0F0F0F0Fu);
                 w[8 * h + j + 4] = iq4nl_lookup4((q >> 4) & 0x0F0F0F0Fu);
             }

@@ -1,0 +1,265 @@
+// gemv_stream.cuh -- the decode GEMV for dense products whose rows are 16-byte aligned.
+//
+// HBM-bound by intent: every packed weight byte crosses HBM once for all columns. What bounds it in
+// practice is instruction issue and the load/store pipe, so the kernel keeps both out of the inner loop:
+//   - a row is cut into slices of 2048 weights (64 per lane) and a warp owns ONE slice for the whole
+//     launch: its activation codes, scales and block sums for that slice are loaded into registers once,
+//     never again. A warp holds at most four columns (the form in which the lane code of gemv_core.cuh
+//     needs about 120 registers); 5..8 columns are split over two warps per slice;
+//   - the S slices x 1 or 2 column halves of a row are a "group" of warps. A group takes R consecutive
+//     rows at a time; the R whole rows arrive in a shared-memory ring by bulk asynchronous copies
+//     (cp.async.bulk, one instruction per row, issued by one lane of the group) that complete on an
+//     mbarrier; a second mbarrier per ring stage hands the space back. All warps of the group read the
+//     same staged bytes, so the weights are fetched once;
+//   - the R x columns partial sums of a lane are reduced across the warp by a transposing butterfly
+//     (half of the values change hands at each step: 31 shuffles for 32 values instead of 160), the
+//     slices' partial sums meet in shared memory and one warp of the group (they take turns) adds them
+//     in a fixed order and stores the results, while the others go on with the next rows.
+// Every mbarrier wait is bounded; a wait that runs out sets the context's error word and the warp ends.
+//
+// Stands in for the reference's kernel_mul_mv_*_q8_1 family (marfrit/arcint contrib/llama.cpp/patches/
+// 0000-01-kquant-integer-dpas.patch:3882-3915) at 1..8 columns and for its few-column kernels
+// (0115-opencl-few-column-int8-q4_0-q8_0-iq4.patch:904-984), without tensor cores.
+#pragma once
+
+#include "gemv_core.cuh"
+#include "pdl.cuh"
+#include "tc_common.cuh"
+
+namespace b200q {
+
+constexpr uint32_t GEMV_SPIN_LIMIT = 1u << 22;
+constexpr int GEMV_STREAM_MAX_THREADS = 512;      // 16 warps: the compiler may use up to 128 registers per thread
+
+// bounded wait of one thread on an mbarrier phase; false when the limit ran out
+__device__ __forceinline__ bool gemv_mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < GEMV_SPIN_LIMIT; ++i)
+        if (tc::mbar_try(bar, parity)) return true;
+    return false;
+}
+
+// Weights are read once per product: their lines are marked evict-first in L2 so that the stream does
+// not push out what is read again (the quantized activation, the next product's inputs).
+__device__ __forceinline__ uint64_t gemv_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void gemv_bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+}
+
+// Sum of v[i] over the 32 lanes for every i < V (V a power of two up to 32). On return v[0] of lane l
+// holds the total of index l >> (5 - log2 V); lanes that share an index hold the same total.
+template <int V>
+__device__ __forceinline__ void warp_reduce_transposed(float (&v)[V], int lane) {
+    int n = V;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        if (n > 1) {
+            const int half = n / 2;
+            const bool upper = (lane & o) != 0;
+#pragma unroll
+            for (int i = 0; i < V / 2; ++i) {
+                if (i < half) {
+                    const float keep = upper ? v[i + half] : v[i];
+                    const float send = upper ? v[i] : v[i + half];
+                    v[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, o);
+                }
+            }
+            n = half;
+        } else {
+            v[0] += __shfl_xor_sync(0xFFFFFFFFu, v[0], o);
+        }
+    }
+}
+
+constexpr int gemv_pow2_at_least(int v) { return v <= 1 ? 1 : v <= 2 ? 2 : v <= 4 ? 4 : v <= 8 ? 8 : v <= 16 ? 16 : 32; }
+
+// Shared memory of one group: the ring of NSETS stages of R rows, the slices' partial sums of two
+// row batches in flight, and the barriers.
+struct GemvGroupSmem {
+    uint32_t ring, part, bar_full, bar_empty, bar_done, bar_free;   // shared-space addresses
+    uint8_t *ring_ptr;
+    float   *part_ptr;
+};
+
+__host__ __device__ inline int gemv_stream_slot(int row_bytes) { return ((row_bytes + 15) / 16) * 16 + 16; }
+// bytes of shared memory per group of nw warps
+__host__ __device__ inline size_t gemv_stream_group_smem(int row_bytes, int R, int nsets, int nw) {
+    return (size_t)nsets * R * gemv_stream_slot(row_bytes) + (size_t)2 * nw * 32 * sizeof(float) + (size_t)(2 * nsets + 4) * 8;
+}
+
+// What one warp of a group does: slice `slice` of every row, columns [col0, col0 + NCW) of the launch.
+// wi: the warp's index in its group of nw warps; warp 0 of the group also runs the producer side.
+template <int TYPE, int NC, int NCW, int R, int NSETS>
+__device__ __forceinline__ void gemv_stream_warp(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk,
+                                                 const GemvAct &act, float *__restrict__ dst, int ldd, const GemvGroupSmem &sm,
+                                                 int gg, int tg, int lane, int wi, int nw, int slice, int col0,
+                                                 int *error_word) {
+    constexpr int CW = NC > 4 ? 2 : 1;                             // warps per slice (column halves)
+    typedef GemvFmt<TYPE> F;
+    typedef GemvStage<TYPE> S;
+    const int row_bytes = nblk * F::BLK_B;
+    const int slot = gemv_stream_slot(row_bytes);
+    const int n_units = (M + R - 1) / R;
+    const bool leader = wi == 0;
+    bool ok = true;
+    const uint64_t policy = gemv_policy_evict_first();
+
+    // producer cursor (lane 0 of the group's first warp acts): the next row batch to request
+    int p_n = 0, p_set = 0;
+    auto issue = [&]() {
+        const int u = gg + p_n * tg;
+        if (u < n_units && lane == 0) {
+            // the stage's previous rows must have been released by every warp of the group
+            if (p_n >= NSETS && !gemv_mbar_wait(sm.bar_empty + 8 * p_set, (uint32_t)((p_n / NSETS - 1) & 1))) ok = false;
+            if (ok) {
+                const int row0 = u * R, rows = min(R, M - row0);
+                const uint8_t *src = W + (size_t)row0 * row_stride;
+                const uint32_t d = sm.ring + p_set * (R * slot);
+                tc::mbar_expect_tx(sm.bar_full + 8 * p_set, (uint32_t)row_bytes * (uint32_t)rows);
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                    if (r < rows) gemv_bulk_g2s(d + r * slot, src + (size_t)r * row_stride, (uint32_t)row_bytes, sm.bar_full + 8 * p_set, policy);
+            }
+        }
+        p_set = p_set + 1 == NSETS ? 0 : p_set + 1;
+        ++p_n;
+    };
+    // The producer runs NSETS - 2 batches ahead of the consumers, not NSETS - 1: the stage it refills was
+    // read one batch earlier than the newest finished one, so its wait for the other warps' release is
+    // normally over before it begins and the warps of a group do not fall into lockstep.
+    static_assert(NSETS >= 3, "the ring needs a stage being read, one draining and at least one in flight");
+    if (leader) {
+#pragma unroll
+        for (int i = 0; i < NSETS - 2; ++i) issue();
+    }
+    // the first rows are in flight; the activation (the quantizer's output) and dst (which an earlier
+    // kernel may still be using) are touched only after this
+    pdl_wait();
+
+    int cols[NCW];
+#pragma unroll
+    for (int c = 0; c < NCW; ++c) cols[c] = col0 + c;
+    GemvX<NCW> X;
+    gemv_load_x<TYPE, NCW>(lane, slice, nblk, act, cols, X);      // once: this warp's slice of every column
+
+    constexpr int V = gemv_pow2_at_least(R * NCW);
+    constexpr int SHARE = 32 / V;                                  // lanes that end up with the same value
+    const int slice_off = slice * S::BYTES;
+    int c_set = 0;
+    for (int n = 0, u = gg; u < n_units; u += tg, ++n) {
+        if (leader) issue();
+        float acc[R][NCW];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int c = 0; c < NCW; ++c) acc[r][c] = 0.f;
+        ok = ok && gemv_mbar_wait(sm.bar_full + 8 * c_set, (uint32_t)((n / NSETS) & 1));
+        if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+        const uint8_t *set = sm.ring_ptr + c_set * (R * slot) + slice_off;
+#pragma unroll
+        for (int r = 0; r < R; ++r) gemv_lane_row<TYPE, NCW>(reinterpret_cast<const uint32_t *>(set + r * slot), lane, X, acc[r]);
+        __syncwarp();                                              // every lane has read the stage
+        if (lane == 0) tc::mbar_arrive(sm.bar_empty + 8 * c_set);
+        c_set = c_set + 1 == NSETS ? 0 : c_set + 1;
+
+        // value index i = c * R + r, so neighbouring lanes hold neighbouring rows
+        float v[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) v[i] = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int c = 0; c < NCW; ++c) v[c * R + r] = acc[r][c];
+        warp_reduce_transposed<V>(v, lane);
+        const int i = lane / SHARE;
+        if (nw == 1) {
+            const int c = i / R, r = i - c * R, row = u * R + r;
+            if ((lane & (SHARE - 1)) == 0 && c < NCW && row < M) dst[(size_t)(col0 + c) * ldd + row] = v[0];
+            continue;
+        }
+        // the slices meet in shared memory: part[par][warp][i]
+        const int par = n & 1;
+        if (n >= 2) {                                              // the batch two back has been added up and stored
+            ok = gemv_mbar_wait(sm.bar_free + 8 * par, (uint32_t)((n / 2 - 1) & 1));
+            if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+        }
+        float *part = sm.part_ptr + (size_t)par * nw * 32;
+        if ((lane & (SHARE - 1)) == 0) part[wi * 32 + i] = v[0];
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(sm.bar_done + 8 * par);
+        if (wi == n % nw) {                                        // this batch's finisher
+            ok = gemv_mbar_wait(sm.bar_done + 8 * par, (uint32_t)((n / 2) & 1));
+            if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+            // warps of a group: wi = slice * CW + half; every lane adds up one (column, row) of a half
+#pragma unroll
+            for (int h = 0; h < CW; ++h) {
+                const int hcol0 = h == 0 ? 0 : (NC + 1) / 2, hn = CW == 1 ? NC : (h == 0 ? (NC + 1) / 2 : NC / 2);
+                const int c = lane / R, r = lane - c * R, row = u * R + r;
+                if (c < hn && row < M) {
+                    float t = 0.f;
+                    for (int s = h; s < nw; s += CW) t += part[s * 32 + lane];
+                    dst[(size_t)(hcol0 + c) * ldd + row] = t;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(sm.bar_free + 8 * par);
+        }
+    }
+    if (!ok && lane == 0 && error_word) atomicExch(error_word, 2);
+}
+
+// dst[m + c*ldd] = sum_k W[m][k] x_c[k] for c < NC (1..8), rows [0, M). A block holds `groups` groups of
+// nslices * (NC > 4 ? 2 : 1) warps; the grid is one wave of persistent blocks and group number gg takes the
+// row batches gg, gg + (all groups), ...
+template <int TYPE, int NC, int R, int NSETS>
+__global__ void __launch_bounds__(GEMV_STREAM_MAX_THREADS)
+gemv_stream_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk, GemvAct act, float *__restrict__ dst,
+                   int ldd, int groups, int *__restrict__ error_word) {
+    typedef GemvFmt<TYPE> F;
+    constexpr int CW = NC > 4 ? 2 : 1;
+    constexpr int NCA = CW == 2 ? (NC + 1) / 2 : NC, NCB = NC - NCA;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int nslices = (nblk + F::STAGE_BLOCKS - 1) / F::STAGE_BLOCKS, nw = nslices * CW;
+    const int row_bytes = nblk * F::BLK_B, slot = gemv_stream_slot(row_bytes);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = warp / nw, wi = warp - g * nw;
+    const int slice = wi / CW, sub = wi - slice * CW;
+    const size_t gbytes = (gemv_stream_group_smem(row_bytes, R, NSETS, nw) + 15) / 16 * 16;
+    GemvGroupSmem sm;
+    sm.ring_ptr = smem + g * gbytes;
+    sm.part_ptr = reinterpret_cast<float *>(sm.ring_ptr + (size_t)NSETS * R * slot);
+    sm.ring = tc::smem_u32(sm.ring_ptr);
+    sm.part = tc::smem_u32(sm.part_ptr);
+    sm.bar_full = sm.part + 2 * nw * 32 * (uint32_t)sizeof(float);
+    sm.bar_empty = sm.bar_full + 8 * NSETS;
+    sm.bar_done = sm.bar_empty + 8 * NSETS;
+    sm.bar_free = sm.bar_done + 16;
+    if (wi == 0 && lane == 0) {
+#pragma unroll
+        for (int i = 0; i < NSETS; ++i) {
+            tc::mbar_init(sm.bar_full + 8 * i, 1);
+            tc::mbar_init(sm.bar_empty + 8 * i, (uint32_t)nw);
+        }
+        tc::mbar_init(sm.bar_done, (uint32_t)nw);
+        tc::mbar_init(sm.bar_done + 8, (uint32_t)nw);
+        tc::mbar_init(sm.bar_free, 1);
+        tc::mbar_init(sm.bar_free + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int gg = blockIdx.x * groups + g, tg = gridDim.x * groups;
+    if (g < groups) {
+        if (CW == 1 || sub == 0)
+            gemv_stream_warp<TYPE, NC, NCA, R, NSETS>(W, row_stride, M, nblk, act, dst, ldd, sm, gg, tg, lane, wi, nw, slice, 0, error_word);
+        else
+            gemv_stream_warp<TYPE, NC, (NCB > 0 ? NCB : 1), R, NSETS>(W, row_stride, M, nblk, act, dst, ldd, sm, gg, tg, lane, wi, nw, slice,
+                                                                      NCA, error_word);
+    }
+    // this block's rows are done: once every block is here the next kernel of the stream may be scheduled
+    pdl_trigger();
+}
+
+}  // namespace b200q

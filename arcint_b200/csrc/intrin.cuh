@@ -87,25 +87,45 @@ B200Q_HD I2 hd_ld8(const void *p) {
 #endif
 }
 
-// Reads from a staged (shared-memory) row chunk held as 32-bit words. The packed
-// blocks are only 2-byte aligned inside a row (18-, 34- and 210-byte blocks), so a run
+// A staged (shared-memory) row chunk held as 32-bit words. Plain loads through the pointer: the
+// compiler sees that it points into shared memory and may hoist and pair the loads as it likes
+// (explicit ld.shared in volatile asm measured slower: it pins the loads' order).
+struct alignas(16) U4 { uint32_t x, y, z, w; };
+struct Stage {
+    const uint32_t *p;
+    B200Q_HD explicit Stage(const uint32_t *q) : p(q) {}
+    B200Q_HD uint32_t w(uint32_t i) const { return p[i]; }
+    // four words at a 16-byte aligned place (word index i a multiple of 4 from an aligned chunk)
+    B200Q_HD U4 ld16(uint32_t i) const {
+#ifdef __CUDA_ARCH__
+        const uint4 v = *reinterpret_cast<const uint4 *>(p + i);
+        return U4{ v.x, v.y, v.z, v.w };
+#else
+        U4 v;
+        memcpy(&v, p + i, 16);
+        return v;
+#endif
+    }
+};
+
+// The packed blocks are only 2-byte aligned inside a row (18-, 34- and 210-byte blocks), so a run
 // of N words at byte offset `off` (even) is N+1 aligned words and a funnel shift each.
 template <int N>
-B200Q_HD void stage_words(const uint32_t *sw, uint32_t off, uint32_t (&out)[N]) {
+B200Q_HD void stage_words(const Stage &st, uint32_t off, uint32_t (&out)[N]) {
     const uint32_t w = off >> 2, sh = (off & 2u) * 8u;
     uint32_t a[N + 1];
 #pragma unroll
-    for (int i = 0; i <= N; ++i) a[i] = sw[w + i];
+    for (int i = 0; i <= N; ++i) a[i] = st.w(w + i);
 #pragma unroll
     for (int i = 0; i < N; ++i) out[i] = hd_funnelshift_r(a[i], a[i + 1], sh);
 }
 
-B200Q_HD uint16_t stage_u16(const uint32_t *sw, uint32_t off) {
-    return (uint16_t)(sw[off >> 2] >> ((off & 2u) * 8u));
+B200Q_HD uint16_t stage_u16(const Stage &st, uint32_t off) {
+    return (uint16_t)(st.w(off >> 2) >> ((off & 2u) * 8u));
 }
 
-B200Q_HD uint32_t stage_u8(const uint32_t *sw, uint32_t off) {
-    return (sw[off >> 2] >> ((off & 3u) * 8u)) & 0xFFu;
+B200Q_HD uint32_t stage_u8(const Stage &st, uint32_t off) {
+    return (st.w(off >> 2) >> ((off & 3u) * 8u)) & 0xFFu;
 }
 
 }  // namespace b200q

@@ -16,6 +16,7 @@ namespace b200q {
 
 struct RouteEntry {
     const void *ids_data = nullptr;
+    const void *ids_id = nullptr;      // the caller's tensor identity (NULL: unknown)
     int64_t ne[2] = { 0, 0 };
     size_t  nb1 = 0;
     int     n_expert = 0;
@@ -214,7 +215,7 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     const int64_t n_pairs = (int64_t)n_used * n_tok;
     RouteEntry *hit = nullptr;
     for (RouteEntry *e : ctx->routes)
-        if (e && e->valid && e->ids_data == ids->data && e->ne[0] == ids->ne[0] && e->ne[1] == ids->ne[1] &&
+        if (e && e->valid && e->ids_data == ids->data && e->ids_id == ids->id && e->ne[0] == ids->ne[0] && e->ne[1] == ids->ne[1] &&
             e->nb1 == ids->nb[1] && e->n_expert == n_expert && e->gen == ctx->generation &&
             e->experts_per_owner == experts_per_owner) { hit = e; break; }
     if (hit) {
@@ -264,6 +265,7 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_MOE_ROUTE);
     e.ids_data = ids->data;
+    e.ids_id = ids->id;
     e.ne[0] = ids->ne[0];
     e.ne[1] = ids->ne[1];
     e.nb1 = ids->nb[1];

@@ -7,7 +7,7 @@
 // b200q context either, because a context grows its scratch with cudaMalloc. This entry point
 // takes no context and allocates nothing: the quantized activation it needs between its two
 // kernels lives in a fixed array that is part of the library image. The price is a size limit
-// (at most 8 activation columns of at most 32768 values) and 352 KiB of device memory held by
+// (at most 8 activation columns of at most 32768 values) and 320 KiB of device memory held by
 // every GPU that loads the library, until the process exits.
 //
 // The array is shared by every call and keeps what the last call left in it. Nothing has to
@@ -18,7 +18,15 @@
 //
 // In host code the array's name is only a stand-in; the address kernels can use comes from
 // cudaGetSymbolAddress, asked once per device with that device current. The first call on a
-// device does this, so it should happen before any stream capture is opened.
+// device does this, so it should happen before any stream capture is opened. The first call for
+// a weight type and column count also asks the driver for that kernel's attributes (and, with lazy
+// module loading, makes the driver load the kernel's code): a host that is about to hand all device
+// memory to its own pool should make one call per weight type and column count it will use first.
+//
+// The last 256 bytes of the array hold the word a GEMV kernel sets when one of its bounded waits runs
+// out (it starts at zero and nothing clears it; b200q_noalloc_device_error reads it).
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -33,7 +41,9 @@ constexpr size_t NOALLOC_CODES = (size_t)NOALLOC_MAX_COLS * NOALLOC_MAX_K;
 constexpr size_t NOALLOC_SCALES = (size_t)NOALLOC_MAX_COLS * (NOALLOC_MAX_K / 32) * 2;
 constexpr size_t NOALLOC_SUMS32 = (size_t)NOALLOC_MAX_COLS * (NOALLOC_MAX_K / 32) * 2;
 constexpr size_t NOALLOC_SUMS16 = (size_t)NOALLOC_MAX_COLS * (NOALLOC_MAX_K / 16) * 2;
-constexpr size_t NOALLOC_BYTES = NOALLOC_CODES + NOALLOC_SCALES + NOALLOC_SUMS32 + NOALLOC_SUMS16;
+constexpr size_t NOALLOC_ERROR = 256;       // the kernels' error word, on its own 256 bytes
+constexpr size_t NOALLOC_BYTES = NOALLOC_CODES + NOALLOC_SCALES + NOALLOC_SUMS32 + NOALLOC_SUMS16 + NOALLOC_ERROR;
+static_assert(NOALLOC_BYTES == 320 * 1024 + 256, "the documented size of the fixed array");
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
 
@@ -94,11 +104,16 @@ b200q_status b200q_mul_mat_noalloc(int device, void *stream, const b200q_tensor 
         }
     }
     ctx.sm_count = g_sm_count[device];
+    static const bool no_pdl = [] { const char *v = getenv("B200Q_NO_PDL"); return v && v[0] == '1'; }();
+    static const bool no_stream = [] { const char *v = getenv("B200Q_NO_STREAM"); return v && v[0] == '1'; }();
+    ctx.no_pdl = no_pdl;
+    ctx.no_stream = no_stream;
     unsigned char *base = g_scratch_ptr[device];
     int8_t *codes = (int8_t *)base;
     void *scales = base + NOALLOC_CODES;
     int16_t *sums32 = (int16_t *)(base + NOALLOC_CODES + NOALLOC_SCALES);
     int16_t *sums16 = (int16_t *)(base + NOALLOC_CODES + NOALLOC_SCALES + NOALLOC_SUMS32);
+    ctx.error_word = (int *)(base + NOALLOC_BYTES - NOALLOC_ERROR);
     // kernel 1 writes the activation of this call's N columns into the array, kernel 2 reads it
     st = launch_quantize_act(&ctx, ti.act_form, src1, codes, scales, sums32, sums16);
     if (st != B200Q_OK) return bad(st, ctx.last_error);
@@ -114,6 +129,18 @@ b200q_status b200q_mul_mat_noalloc(int device, void *stream, const b200q_tensor 
     st = launch_gemv(&ctx, src0->type, src0->data, src0->nb[1], M, K, act, 0, (int)N, (float *)dst->data,
                      (int64_t)(s1 / sizeof(float)));
     if (st != B200Q_OK) return bad(st, ctx.last_error);
+    return B200Q_OK;
+}
+
+// Nonzero when a kernel of an earlier b200q_mul_mat_noalloc call on `device` gave up a bounded wait
+// (its results are then incomplete). Synchronizes the device's default stream copy; not for hot paths.
+b200q_status b200q_noalloc_device_error(int device, int *error) {
+    if (!error || device < 0 || device >= NOALLOC_MAX_DEVICES) return B200Q_INVALID;
+    *error = 0;
+    if (!g_scratch_ptr[device]) return B200Q_OK;             // no call has run on this device yet
+    if (cudaSetDevice(device) != cudaSuccess) return B200Q_CUDA_ERROR;
+    if (cudaMemcpy(error, g_scratch_ptr[device] + NOALLOC_BYTES - NOALLOC_ERROR, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return B200Q_CUDA_ERROR;
     return B200Q_OK;
 }
 

@@ -267,6 +267,7 @@ b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local,
     // 4. the local experts over everything received: one slot per received pair
     if (n_recv) {
         b200q_tensor x1, id1, y1;
+        x1.id = id1.id = y1.id = nullptr;
         x1.type = B200Q_TYPE_F32; x1.data = recv_x;
         x1.ne[0] = K; x1.ne[1] = 1; x1.ne[2] = (int64_t)n_recv; x1.ne[3] = 1;
         x1.nb[0] = 4; x1.nb[1] = rowx; x1.nb[2] = rowx; x1.nb[3] = rowx * n_recv;

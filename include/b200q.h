@@ -63,12 +63,19 @@ enum { B200Q_OP_MUL_MAT = 0, B200Q_OP_MUL_MAT_ID = 1 };
  * The fields of ggml_tensor this path reads (P01:817-857, 1174-1219): type, ne[4]
  * (elements per dimension, ne[0] fastest), nb[4] (strides in bytes) and the device
  * address of element 0 (ggml: extra->data_device + offset + view_offs).
+ * `id` is the tensor's identity for the per-graph caches (ggml: the ggml_tensor pointer
+ * itself, as the reference keys its caches: `c.src1 == src1`, P01:683-688; `rc.ids == ids`,
+ * P01:1264-1287): ggml-alloc gives one address to several tensors of a graph in turn, so an
+ * address alone does not say whose contents a buffer holds. NULL: no identity is known and the
+ * caches compare address, shape and strides only -- then the caller must start a new
+ * generation (b200q_graph_begin) whenever a buffer's contents may have changed.
  */
 typedef struct {
     int32_t type;
     int64_t ne[4];
     size_t  nb[4];
     void   *data;
+    const void *id;
 } b200q_tensor;
 
 typedef struct b200q_ctx b200q_ctx;
@@ -106,8 +113,9 @@ B200Q_API b200q_status b200q_mul_mat_id(b200q_ctx *ctx, const b200q_tensor *src0
 /* ggml_backend_opencl_graph_compute's generation bump (P01:609-611): starts a new
  * graph. Within one graph an activation tensor that feeds several products (q/k/v,
  * gate/up) is quantized once (P01:670-688) and a MoE route is computed once per ids
- * tensor (P01:1264-1287); both caches are keyed by (address, shape, strides,
- * generation), so the caller must call this whenever tensor contents may have changed. */
+ * tensor (P01:1264-1287); both caches are keyed by (identity, address, shape, strides,
+ * generation): call this once per graph when tensors carry their `id`, and whenever tensor
+ * contents may have changed when they do not. */
 B200Q_API b200q_status b200q_graph_begin(b200q_ctx *ctx);
 
 /* CUDA-graph replay of a recorded call sequence (what ggml's CUDA backend does for its
@@ -116,7 +124,9 @@ B200Q_API b200q_status b200q_graph_begin(b200q_ctx *ctx);
  * then replays them on the context's stream with one launch. Scratch must already be large
  * enough (run the sequence once before capturing: growth inside a capture is refused), and
  * a graph is stale once the context's scratch has grown ("workspace_grow" in b200q_stats)
- * or any tensor it touched has moved. */
+ * or any tensor it touched has moved. capture_begin and capture_end each start a new cache
+ * generation, so a recorded sequence always holds its own quantize / route kernels and a replay
+ * sees the tensors' current contents. */
 typedef struct b200q_graph b200q_graph;
 B200Q_API b200q_status b200q_capture_begin(b200q_ctx *ctx);
 B200Q_API b200q_status b200q_capture_end(b200q_ctx *ctx, b200q_graph **graph);
@@ -188,16 +198,21 @@ B200Q_API b200q_status b200q_flush_l2(b200q_ctx *ctx);
  * that cannot allocate device memory: a host whose own pool took all of the GPU's memory at
  * start-up, or a serving loop that must not meet the device-wide synchronisation of
  * cudaMalloc / cudaFree. It needs no context and allocates nothing; the quantized activation
- * passes through a fixed 352 KiB array inside the library image (held by every GPU that loads
+ * passes through a fixed 320 KiB array inside the library image (held by every GPU that loads
  * the library until the process exits). Larger shapes are refused with B200Q_UNSUPPORTED and a
  * message in b200q_noalloc_last_error(). All calls share that array and it keeps the last
  * call's contents (each call overwrites what it reads, so nothing needs clearing); calls that
  * overlap on one GPU race on it, so keep them ordered. The first call on a device looks up the
- * array's device address, so make that call before opening any stream capture. `stream` is a
- * cudaStream_t (NULL: the default stream); work is enqueued, not waited for. */
+ * array's device address, so make that call before opening any stream capture; the first call for a
+ * weight type and column count asks the driver for that kernel's attributes (and may make it load the
+ * kernel's code), so a host about to take all device memory should first make one call per weight type
+ * and column count it will use. `stream` is a cudaStream_t (NULL: the default stream); work is
+ * enqueued, not waited for. b200q_noalloc_device_error reads (with a blocking copy) the word a kernel
+ * of an earlier call set when one of its bounded waits gave up; zero means none did. */
 B200Q_API b200q_status b200q_mul_mat_noalloc(int device, void *stream, const b200q_tensor *src0,
                                              const b200q_tensor *src1, b200q_tensor *dst);
 B200Q_API const char  *b200q_noalloc_last_error(void);
+B200Q_API b200q_status b200q_noalloc_device_error(int device, int *error);
 
 /* Debug views of what the kernels see, for bit-exact parity tests: the quantized
  * activation (codes [N][K] int8; scales fp16 [N][K/32] for Q4_0/Q8_0 weights or f32

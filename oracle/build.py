@@ -6,14 +6,18 @@
 
 kq_i8_ops.inc only exists as an added file inside a patch of the reference tree
 (contrib/llama.cpp/patches/0000-09-moe-routing-gemm-tiles.patch), so its '+' lines are
-extracted into oracle/_ref/ (git-ignored: no reference source is committed) and compiled
-together with ref_shim.cpp.
+extracted into a temporary directory, compiled together with ref_shim.cpp and deleted: only
+the built library stays in oracle/_ref/ (git-ignored), no reference source is kept.
+
+The reference tree is looked for in $B200Q_REFERENCE_ROOT, else in a directory named
+`reference` beside the repository.
 """
 import argparse
 import os
 import shutil
 import subprocess
 import sys
+import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 PATCH = "contrib/llama.cpp/patches/0000-09-moe-routing-gemm-tiles.patch"
@@ -72,29 +76,37 @@ def _extract(patch_path):
     return "".join(out)
 
 
-def build_ref(ref_root="/root/reference"):
+def default_ref_root():
+    return os.environ.get("B200Q_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build_ref(ref_root=None):
     """Compile _ref/libkqref.so from the reference tree; None when the tree is absent."""
-    patch = os.path.join(ref_root, PATCH)
+    patch = os.path.join(ref_root or default_ref_root(), PATCH)
     if not os.path.isfile(patch):
         return None
     dst = os.path.join(HERE, "_ref")
     os.makedirs(dst, exist_ok=True)
-    with open(os.path.join(dst, "kq_i8_ops.inc"), "w") as f:
-        f.write(_extract(patch))
+    stale = os.path.join(dst, "kq_i8_ops.inc")           # an earlier layout kept the extracted text here
+    if os.path.exists(stale):
+        os.remove(stale)
     so = os.path.join(dst, "libkqref.so")
     errs = []
-    for cxx in _compilers(["/usr/bin/g++", os.environ.get("CXX", "g++"), "g++"]):
-        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-I", dst, os.path.join(HERE, "ref_shim.cpp"), "-o", so]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode == 0:
-            return so
-        errs.append(r.stderr[-400:])
+    with tempfile.TemporaryDirectory() as tmp:
+        with open(os.path.join(tmp, "kq_i8_ops.inc"), "w") as f:
+            f.write(_extract(patch))
+        for cxx in _compilers(["/usr/bin/g++", os.environ.get("CXX", "g++"), "g++"]):
+            cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-I", tmp, os.path.join(HERE, "ref_shim.cpp"), "-o", so]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode == 0:
+                return so
+            errs.append(r.stderr[-400:])
     raise RuntimeError("could not build _ref:\n" + "\n".join(errs))
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=None)
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     print(build_oracle(force=a.force))

@@ -33,7 +33,7 @@ def test_version_and_block_tables():
 
 def test_tensor_struct_layout():
     t = A.Tensor.weights(A.Q4_K, 0x1000, 4096, 11008)
-    assert C.sizeof(A.Tensor) == 80
+    assert C.sizeof(A.Tensor) == 88 and A.Tensor.id.offset == 80      # type, ne[4], nb[4], data, id
     assert list(t.ne) == [4096, 11008, 1, 1] and list(t.nb)[:2] == [144, 2304]
     f = A.Tensor.f32(0x2000, [4096, 8])
     assert list(f.nb) == [4, 16384, 131072, 131072]
