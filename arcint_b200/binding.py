@@ -151,6 +151,7 @@ def lib():
     L.b200q_flush_l2.argtypes = [vp]
     L.b200q_debug_quantize_act.argtypes = [vp, C.c_int, TP, vp, vp, vp]
     L.b200q_debug_dequantize.argtypes = [vp, TP, vp]
+    L.b200q_debug_wait_timeout.argtypes = [vp, C.c_uint]
     _lib = L
     return L
 
@@ -162,7 +163,7 @@ EXPORTS = [
     "b200q_all_gather", "b200q_all_to_all_v", "b200q_tp_check", "b200q_mul_mat_id_ep", "b200q_mul_mat_noalloc", "b200q_noalloc_last_error", "b200q_noalloc_device_error", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
     "b200q_tensor_get", "b200q_tensor_stage", "b200q_tensor_fetch", "b200q_tensor_copy", "b200q_synchronize", "b200q_host_alloc", "b200q_host_free",
     "b200q_stats", "b200q_stats_reset", "b200q_timer_start", "b200q_timer_stop", "b200q_flush_l2",
-    "b200q_debug_quantize_act", "b200q_debug_dequantize",
+    "b200q_debug_quantize_act", "b200q_debug_dequantize", "b200q_debug_wait_timeout",
 ]
 
 

@@ -77,11 +77,14 @@ def _extra_link():
     return ["-ldl"]
 
 
-def build_emul(force=False):
-    """Host build of the kernels' per-lane text (device-free tests): g++ on emul.cpp."""
+def build_emul(force=False, define=None):
+    """Host build of the kernels' per-lane text (device-free tests): g++ on emul.cpp. `define` names a
+    red-case switch (e.g. "B200Q_RED_Q40"): the mutant is built beside the real library."""
     src = os.path.join(CSRC, "emul.cpp")
     if not os.path.exists(src):
         return None
+    os.makedirs(LIBDIR, exist_ok=True)
+    EMUL = os.path.join(LIBDIR, "libb200q_emul%s.so" % ("_" + define.lower() if define else ""))
     if not force and not _stale(EMUL, [src] + _deps()):
         return EMUL
     cuda_inc = os.path.join(os.path.dirname(os.path.dirname(nvcc())), "include")
@@ -89,7 +92,8 @@ def build_emul(force=False):
         cxx = cxx if os.path.isabs(cxx) else shutil.which(cxx)
         if not cxx or not os.path.exists(cxx):
             continue
-        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-I", cuda_inc, src, "-o", EMUL]
+        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-I", cuda_inc, src, "-o", EMUL] + \
+            (["-D" + define] if define else [])
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode == 0:
             return EMUL

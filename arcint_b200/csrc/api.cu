@@ -10,8 +10,23 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace b200q {
+
+// A wait that cannot succeed, for the failure-path test: one thread polls a shared-memory mbarrier that
+// nobody ever arrives at, at most `polls` times, then does what every kernel of the library does when a
+// bounded wait runs out -- it records the fact in the context's error word and returns. No trap, no
+// fault, no unbounded loop: the context stays usable.
+__global__ void debug_wait_timeout_kernel(unsigned polls, int *error_word) {
+    __shared__ __align__(8) uint64_t bar;
+    const uint32_t b = tc::smem_u32(&bar);
+    tc::mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    bool done = false;
+    for (unsigned i = 0; i < polls && !done; ++i) done = tc::mbar_try(b, 0);
+    if (!done) atomicExch(error_word, 3);
+}
 
 const char *stat_name(int s) {
     static const char *fixed[] = { "quantize_act_q8_0", "quantize_act_q8_256", "act_cache_hit", "workspace_grow",
@@ -27,7 +42,7 @@ const char *stat_name(int s) {
     }
     static const char *rest[] = { "gemv_id", "gemv_id_unaligned", "moe_route", "route_cache_hit", "moe_gemm", "moe_pack",
                                   "gemm_tc", "gemm_tc_quantize", "gemm_fallback_shape", "tp_allreduce", "tp_allgather",
-                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins", "gemv_stream" };
+                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins", "gemv_stream", "tp_allreduce_peer" };
     return rest[s - ST_GEMV_ID];
 }
 
@@ -624,6 +639,15 @@ b200q_status b200q_debug_quantize_act(b200q_ctx *ctx, int weight_type, const b20
     if (st != B200Q_OK) return st;
     return launch_quantize_act(ctx, ti.act_form, src1, (int8_t *)dev_codes, dev_scales, (int16_t *)dev_sums,
                                (int16_t *)ctx->moe_ws[7].ptr);
+}
+
+b200q_status b200q_debug_wait_timeout(b200q_ctx *ctx, unsigned polls) {
+    if (!ctx) return B200Q_INVALID;
+    if (polls > (1u << 20)) polls = 1u << 20;
+    B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+    debug_wait_timeout_kernel<<<1, 1, 0, ctx->stream>>>(polls, ctx->error_word);
+    B200Q_CUDA(ctx, cudaGetLastError());
+    return B200Q_OK;
 }
 
 b200q_status b200q_debug_dequantize(b200q_ctx *ctx, const b200q_tensor *src0, float *dev_out) {

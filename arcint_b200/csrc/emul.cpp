@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "gemv_core.cuh"
+#include "peer_ar.cuh"
 
 using namespace b200q;
 
@@ -136,6 +137,38 @@ void emul_q4k_scales_mins(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t *out4)
 }
 void emul_q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int j, int *sc, int *m) { q4k_scale_min(s0, s1, s2, j, sc, m); }
 void emul_iq4xs_limbs8(uint32_t q, int m, uint32_t *out4) { iq4xs_limbs8(q, m, out4, out4 + 1, out4 + 2, out4 + 3); }
+// Host replay of the one-shot all-reduce's slot protocol (peer_ar.cuh): nranks receive buffers, two
+// all-reduces in a row (both sets of slots), every rank writes its vector into every buffer and then reads
+// its own. Rank `silent` (if >= 0) writes nothing in the second all-reduce: the readers' bounded waits must
+// then give up (gave_up[r] = 1) instead of spinning, having taken the stale element they found.
+// in: [2][nranks][count] floats, out: [2][nranks][count]. Returns 0.
+int emul_peer_allreduce(int nranks, int count, const float *in, float *out, int silent, unsigned limit, int *gave_up) {
+    if (nranks < 1 || nranks > PEER_AR_MAX_RANKS || count < 0 || count > PEER_AR_MAX_FLOATS) return -1;
+    std::vector<std::vector<uint64_t>> buf(nranks, std::vector<uint64_t>(PEER_AR_BUFFER_BYTES / 8, 0));
+    auto load = [](const uint64_t *p) { return *p; };
+    for (int r = 0; r < nranks; ++r) gave_up[r] = 0;
+    for (uint32_t call = 0; call < 2; ++call) {
+        const uint32_t seq = call + 1;
+        const int set = (int)(seq & 1u);
+        for (int r = 0; r < nranks; ++r) {
+            if (call == 1 && r == silent) continue;
+            for (int e = 0; e < count; ++e)
+                for (int p = 0; p < nranks; ++p)
+                    buf[p][peer_ar_index(set, r, e)] = peer_ar_pack(in[((size_t)call * nranks + r) * count + e], seq);
+        }
+        for (int r = 0; r < nranks; ++r)
+            for (int e = 0; e < count; ++e) {
+                float sum = 0.f;
+                bool ok = true;
+                for (int q = 0; q < nranks; ++q)
+                    sum += peer_ar_value(peer_ar_wait(&buf[r][peer_ar_index(set, q, e)], seq, limit, load, &ok));
+                if (!ok) gave_up[r] = 1;
+                out[((size_t)call * nranks + r) * count + e] = sum;
+            }
+    }
+    return 0;
+}
+
 uint32_t emul_nib_minus8(uint32_t t) { return nib_minus8(t); }
 uint32_t emul_six_minus32(uint32_t t) { return six_minus32(t); }
 

@@ -22,6 +22,11 @@
 // mv_q4_0 / mv_iq (marfrit/arcint contrib/llama.cpp/patches/
 // 0000-01-kquant-integer-dpas.patch:3740-3874, 0000-02-lowbit-iq-types.patch:5947-5955,
 // 6100-6130) without their residual term.
+//
+// Red cases (the reference ships a mutant switch with every kernel patch that must turn its suite red:
+// -DQ40_RED 0099-opencl-q4_0-q8_0-int8-gemm.patch:304-310, -DID_RED 0103-opencl-id-int8-sg8.patch:338-343,
+// -DFEWQ_RED 0115-...patch:742-746): -DB200Q_RED_Q40 takes the Q4_0 codes as n - 4, -DB200Q_RED_SCALE negates
+// the Q4_K block scale, -DB200Q_RED_DROP skips every eighth 32-block of Q4_0 / Q8_0. Test builds only.
 #pragma once
 
 #include "formats.cuh"
@@ -137,7 +142,11 @@ B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, const i
                 X.x[c][1] = hd_ld16(xp + 32 * b0 + 16);
                 X.f0[c] = hd_half_bits(ld_u16(act.d16 + sc + b0));
                 if (TYPE == B200Q_TYPE_Q4_0) {
+#ifdef B200Q_RED_Q40
+                    X.i0[c] = -64 * ld_s16(act.s32 + sc + b0);
+#else
                     X.i0[c] = -128 * ld_s16(act.s32 + sc + b0);      // -8 * 16 * sum(x)
+#endif
                     X.f0[c] *= 0.0625f;                              // the nibble dot is kept x16
                 }
             }
@@ -210,6 +219,9 @@ B200Q_HD void gemv_lane_row(const uint32_t *sw_ptr, int lane, const GemvX<NC> &X
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             if (!(u ? X.live2 : X.live)) continue;
+#ifdef B200Q_RED_DROP
+            if (((32 * u + lane) & 7) == 7) continue;
+#endif
             const uint32_t off = (uint32_t)F::BLK_B * (uint32_t)(32 * u + lane);
             const float d = hd_half_bits(stage_u16(sw, off));
             uint32_t q[4];
@@ -231,6 +243,9 @@ B200Q_HD void gemv_lane_row(const uint32_t *sw_ptr, int lane, const GemvX<NC> &X
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             if (!(u ? X.live2 : X.live)) continue;
+#ifdef B200Q_RED_DROP
+            if (((32 * u + lane) & 7) == 7) continue;
+#endif
             const uint32_t off = (uint32_t)F::BLK_B * (uint32_t)(32 * u + lane);
             const float d = hd_half_bits(stage_u16(sw, off));
             uint32_t w[8];
@@ -290,7 +305,11 @@ B200Q_HD void gemv_lane_row(const uint32_t *sw_ptr, int lane, const GemvX<NC> &X
             }
             const int si = sc0 * il + sc1 * ih;                           // 16 * sum_sb sc * dot
             const int sm = dp2a_lo_su((uint32_t)X.i0[c], mw, 0);          // sum_sb m * sum(x)
+#ifdef B200Q_RED_SCALE
+            acc[c] += X.f0[c] * (-d16 * (float)si - dmin * (float)sm);
+#else
             acc[c] += X.f0[c] * (d16 * (float)si - dmin * (float)sm);
+#endif
         }
     } else if (TYPE == B200Q_TYPE_IQ4_XS) {
         if (!X.live) return;

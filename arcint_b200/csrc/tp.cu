@@ -11,14 +11,18 @@
 //
 // NCCL is opened at run time (dlopen "libnccl.so.2"): a single-GPU user never needs it, and a
 // process that already carries an NCCL (PyTorch's) shares that copy instead of loading a
-// second one. No kernel here touches a peer's memory itself; every byte crosses in NCCL.
+// second one. One kernel here touches peers' memory itself: the one-shot all-reduce of decode-sized
+// vectors (peer_ar.cuh), with plain loads and stores; every other byte crosses in NCCL.
 #include <dlfcn.h>
 #include <nccl.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <vector>
 
 #include "common.cuh"
+#include "pdl.cuh"
+#include "peer_ar.cuh"
 
 namespace b200q {
 
@@ -64,7 +68,58 @@ static Nccl *nccl_api(std::string *err) {
 struct TpState {
     ncclComm_t comm = nullptr;
     int rank = 0, nranks = 1;
+    // one-shot all-reduce over peer memory (peer_ar.cuh): this rank's receive buffer, the peers' buffers as
+    // mapped into this process, and the device words the kernel keeps its sequence number and block count in
+    bool      peer_ok = false;
+    uint64_t *ar_local = nullptr;
+    uint64_t *ar_peer[PEER_AR_MAX_RANKS] = {};
+    uint32_t *ar_state = nullptr;            // [0] sequence number of the last all-reduce, [1] blocks finished
 };
+
+struct PeerArArgs {
+    uint64_t *peer[PEER_AR_MAX_RANKS];       // every rank's receive buffer (this rank's own at [rank])
+    int       rank, nranks;
+};
+
+// One all-reduce: buf[0..count) += the other ranks' buf, in place, the same sum on every rank.
+__global__ void __launch_bounds__(512)
+peer_allreduce_kernel(float *__restrict__ buf, int count, PeerArArgs a, uint32_t *state, int *error_word) {
+    pdl_wait();                                                   // buf comes from the kernel before
+    const uint32_t seq = *(volatile uint32_t *)state + 1;
+    const int set = (int)(seq & 1u);
+    const int stride = gridDim.x * blockDim.x, first = blockIdx.x * blockDim.x + threadIdx.x;
+    for (int e = first; e < count; e += stride) {
+        const uint64_t w = peer_ar_pack(buf[e], seq);
+        for (int p = 0; p < a.nranks; ++p) {
+            const int q = (a.rank + p) % a.nranks;                // ranks start on different peers
+            asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(a.peer[q] + peer_ar_index(set, a.rank, e)), "l"(w) : "memory");
+        }
+    }
+    bool ok = true;
+    auto load = [](const uint64_t *p) {
+        uint64_t v;
+        asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+        return v;
+    };
+    const uint64_t *mine = a.peer[a.rank];
+    for (int e = first; e < count; e += stride) {
+        float sum = 0.f;
+        for (int r = 0; r < a.nranks; ++r)
+            sum += peer_ar_value(peer_ar_wait(mine + peer_ar_index(set, r, e), seq, PEER_AR_SPIN_LIMIT, load, &ok));
+        buf[e] = sum;
+    }
+    if (!ok && error_word) atomicExch(error_word, 4);
+    // the last block to finish advances the sequence number for the next all-reduce (a later launch)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(state + 1, 1u) == gridDim.x - 1) {
+            state[1] = 0;
+            *(volatile uint32_t *)state = seq;
+        }
+    }
+    pdl_trigger();
+}
 
 #define B200Q_NCCL(ctx, api, expr)                                                                     \
     do {                                                                                               \
@@ -74,9 +129,72 @@ struct TpState {
                         (api)->GetErrorString ? (api)->GetErrorString(r_) : "nccl error");             \
     } while (0)
 
+static void peer_ar_close(b200q_ctx *ctx, TpState *tp) {
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (int p = 0; p < tp->nranks && p < PEER_AR_MAX_RANKS; ++p)
+        if (p != tp->rank && tp->ar_peer[p]) cudaIpcCloseMemHandle(tp->ar_peer[p]);
+    if (tp->ar_local) cudaFree(tp->ar_local);
+    if (tp->ar_state) cudaFree(tp->ar_state);
+    tp->ar_local = nullptr;
+    tp->ar_state = nullptr;
+    tp->peer_ok = false;
+}
+
+// Maps every rank's receive buffer into every rank (cudaIpc handles travel through one NCCL all-gather).
+// The fast path is switched on only when every rank mapped every peer; otherwise all ranks stay on NCCL.
+static void peer_ar_setup(b200q_ctx *ctx, TpState *tp, Nccl *api) {
+    const char *off = getenv("B200Q_NO_PEER_AR");
+    if ((off && off[0] == '1') || tp->nranks < 2 || tp->nranks > PEER_AR_MAX_RANKS) return;
+    const int G = tp->nranks;
+    bool mine = cudaMalloc(&tp->ar_local, PEER_AR_BUFFER_BYTES) == cudaSuccess &&
+                cudaMemset(tp->ar_local, 0, PEER_AR_BUFFER_BYTES) == cudaSuccess &&
+                cudaMalloc(&tp->ar_state, 2 * sizeof(uint32_t)) == cudaSuccess &&
+                cudaMemset(tp->ar_state, 0, 2 * sizeof(uint32_t)) == cudaSuccess;
+    cudaIpcMemHandle_t h;
+    memset(&h, 0, sizeof(h));
+    if (mine) mine = cudaIpcGetMemHandle(&h, tp->ar_local) == cudaSuccess;
+    // record: [handle 64 B][ok 1 B] padded to 80 bytes per rank
+    constexpr size_t REC = 80;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is passed as 64 bytes");
+    std::vector<uint8_t> all(REC * G), rec(REC, 0);
+    memcpy(rec.data(), &h, 64);
+    rec[64] = mine ? 1 : 0;
+    uint8_t *d = nullptr;
+    bool ok = cudaMalloc(&d, REC * (G + 1)) == cudaSuccess;
+    auto gather = [&]() {
+        return ok && cudaMemcpyAsync(d + REC * G, rec.data(), REC, cudaMemcpyHostToDevice, ctx->stream) == cudaSuccess &&
+               api->AllGather(d + REC * G, d, REC, ncclInt8, tp->comm, ctx->stream) == ncclSuccess &&
+               cudaMemcpyAsync(all.data(), d, REC * G, cudaMemcpyDeviceToHost, ctx->stream) == cudaSuccess &&
+               cudaStreamSynchronize(ctx->stream) == cudaSuccess;
+    };
+    bool agreed = gather();
+    for (int p = 0; agreed && p < G; ++p) agreed = all[REC * p + 64] == 1;
+    bool mapped = agreed;
+    if (agreed) {
+        for (int p = 0; p < G && mapped; ++p) {
+            if (p == tp->rank) { tp->ar_peer[p] = tp->ar_local; continue; }
+            cudaIpcMemHandle_t hp;
+            memcpy(&hp, all.data() + REC * p, 64);
+            void *ptr = nullptr;
+            mapped = cudaIpcOpenMemHandle(&ptr, hp, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+            tp->ar_peer[p] = (uint64_t *)ptr;
+        }
+        if (!mapped) cudaGetLastError();                           // a refused mapping is not a sticky error
+    }
+    // second round: did every rank map every peer?
+    rec[64] = mapped ? 1 : 0;
+    bool all_mapped = gather();
+    for (int p = 0; all_mapped && p < G; ++p) all_mapped = all[REC * p + 64] == 1;
+    if (d) cudaFree(d);
+    tp->peer_ok = all_mapped;
+    if (!all_mapped) peer_ar_close(ctx, tp);
+}
+
 void tp_free(b200q_ctx *ctx) {
     TpState *tp = (TpState *)ctx->tp;
     if (!tp) return;
+    peer_ar_close(ctx, tp);
     Nccl *api = nccl_api(nullptr);
     if (api && tp->comm && api->CommDestroy) api->CommDestroy(tp->comm);
     delete tp;
@@ -128,6 +246,7 @@ b200q_status b200q_tp_init(b200q_ctx *ctx, const void *id128, int rank, int nran
         return fail(ctx, B200Q_NCCL_ERROR, "ncclCommInitRank: %s", api->GetErrorString ? api->GetErrorString(r) : "error");
     }
     ctx->tp = tp;
+    peer_ar_setup(ctx, tp, api);
     return B200Q_OK;
 }
 
@@ -158,6 +277,23 @@ b200q_status b200q_all_reduce_f32(b200q_ctx *ctx, void *dev_buf, size_t count) {
     if (st != B200Q_OK) return st;
     if (!dev_buf && count) return B200Q_INVALID;
     if (count == 0 || tp->nranks == 1) return B200Q_OK;
+    // decode-sized vectors: one kernel over peer memory instead of a library collective
+    if (tp->peer_ok && count <= (size_t)PEER_AR_MAX_FLOATS && (uintptr_t)dev_buf % 4 == 0) {
+        PeerArArgs a;
+        for (int p = 0; p < PEER_AR_MAX_RANKS; ++p) a.peer[p] = tp->ar_peer[p];
+        a.rank = tp->rank;
+        a.nranks = tp->nranks;
+        const int threads = 512;
+        int blocks = (int)((count + threads - 1) / threads);
+        if (blocks > 16) blocks = 16;                             // all blocks of all ranks must be resident together: far below one wave
+        B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+        B200Q_CUDA(ctx, launch_pdl(!ctx->no_pdl, peer_allreduce_kernel, dim3(blocks), dim3(threads), 0, ctx->stream, (float *)dev_buf,
+                                   (int)count, a, tp->ar_state, ctx->error_word));
+        B200Q_CUDA(ctx, cudaGetLastError());
+        b200q::count(ctx, ST_TP_ALLREDUCE);
+        b200q::count(ctx, ST_TP_ALLREDUCE_PEER);
+        return B200Q_OK;
+    }
     B200Q_NCCL(ctx, api, api->AllReduce(dev_buf, dev_buf, count, ncclFloat32, ncclSum, tp->comm, ctx->stream));
     b200q::count(ctx, ST_TP_ALLREDUCE);
     return B200Q_OK;

@@ -165,6 +165,8 @@ def prefill_section(ctx, world, rank, dist):
         ref = O.mul_mat_f64(t, w[rows], k, x[:32], True)
         floor = 1e-2 * np.abs(ref).max(axis=-1, keepdims=True)
         err = float((np.abs(got[:32][:, rows] - ref) / np.maximum(np.abs(ref), floor)).max())
+        if not err < 1e-3:
+            raise SystemExit("bench: prefill parity check failed on rank %d, %s (max rel err %.3e)" % (rank, name, err))
         reps = 5
 
         def seq():
@@ -222,7 +224,16 @@ def tp_trace_section(ctx, world, rank, dist):
     head = ("head", 32000, 4096, "col")
     bs, bb = A.block_size(t), A.block_bytes(t)
     dev = {}
+    seed_of = {}
+
+    def wfull_shard(name, r, kc_r):
+        """the 256 distinct rows rank r tiles its shard of `name` from (row-split ranks differ in K range
+        only by length: every rank draws its own block from the same seed, so the unsharded weight of the
+        parity check is the ranks' blocks side by side)"""
+        return O.quantize(t, O.fill_normal(256 * kc_r, seed_of[name], 0.02).reshape(256, kc_r))
+
     for name, m, k, how in shapes + [head]:
+        seed_of[name] = 0x5EED0500 + len(dev)
         if how == "col":
             _, mc = A.tp_shard(m, 1, world, rank)
             kc = k
@@ -273,6 +284,38 @@ def tp_trace_section(ctx, world, rank, dist):
         ctx.graph_begin()
         product("head", 0)
         ctx.sync()
+        # parity before timing, on every rank: the row-split products (o, down) after their all-reduce and one
+        # column-split product (q) against the oracle's product with the unsharded weight, sampled rows
+        errs = {}
+        for name in ("o", "down", "q"):
+            mc, kc, how, copies = dev[name]
+            m_full, k_full = [(m, k) for nm, m, k, _ in shapes if nm == name][0]
+            ctx.graph_begin()
+            product(name, 0)
+            got = ctx.download(dy, (n, mc), np.float32)
+            nchk = min(n, 4)
+            if how == "row":
+                rows = np.arange(0, m_full, max(1, m_full // 24))
+                # the full weight is the ranks' K shards side by side, each the seeded block of its rank
+                parts = []
+                for r in range(world):
+                    _, kr = A.tp_shard(k_full, 256, world, r)
+                    parts.append(wfull_shard(name, r, kr)[rows % 256])
+                ref, k0 = 0.0, 0
+                for r, pw in enumerate(parts):
+                    _, kr = A.tp_shard(k_full, 256, world, r)
+                    ref = ref + O.mul_mat_f64(t, pw, kr, np.ascontiguousarray(x[:nchk, :kr]), True)
+                    k0 += kr
+                sub = got[:nchk][:, rows]
+            else:
+                rows = np.arange(0, mc, max(1, mc // 24))
+                ref = O.mul_mat_f64(t, wfull_shard(name, rank, kc)[rows % 256], kc, np.ascontiguousarray(x[:nchk, :kc]), True)
+                sub = got[:nchk][:, rows]
+            floor = 1e-2 * np.abs(ref).max(axis=-1, keepdims=True)
+            errs[name] = float((np.abs(sub - ref) / np.maximum(np.abs(ref), floor)).max())
+            if not errs[name] < 1e-3:
+                raise SystemExit("bench: tensor-parallel parity check failed on rank %d, %s %s (max rel err %.3e)"
+                                 % (rank, label, name, errs[name]))
         how_run = "CUDA-graph replay"
         g = None
         try:
@@ -294,7 +337,8 @@ def tp_trace_section(ctx, world, rank, dist):
         bytes_w = (n_layers * sum(m * k for _, m, k, _ in shapes) + head[1] * head[2]) // bs * bb
         rec = {"workload": "config4 llama-2-7b q4_0 %s" % label, "tokens": n, "ms_per_pass": ms,
                "tokens_per_s": n / (ms * 1e-3), "parallelism": "tp%d column/row split, all-reduce of row-split outputs" % world
-               if world > 1 else "single GPU", "timed": how_run + " of 32 layers x 7 mat-muls + LM head"}
+               if world > 1 else "single GPU", "timed": how_run + " of 32 layers x 7 mat-muls + LM head",
+               "parity_max_rel_err": max(errs.values())}
         if n > 8:
             rec["tops"] = ops / (ms * 1e-3) / 1e12
         else:
@@ -393,6 +437,68 @@ def moe_section(ctx, world, rank, dist):
     for m, k, base, dw, rb in mats.values():
         ctx.free(dw)
     return out
+
+
+def run_case(args):
+    """One product, a few times, for profiling and tile sweeps: --case <type>:<M>x<K>x<N>[:id].
+    Seeded tensors are uploaded, every repeat is one b200q_mul_mat (or, with :id, one b200q_mul_mat_id over
+    512 experts, top-10 routing, N tokens) in a cache generation of its own, over rotating weight copies
+    beyond L2; the CUDA-event time per call and the path counters are printed as one JSON line. This is
+    the command line the summaries under profiles/ give."""
+    import arcint_b200 as A
+    import oracle as O
+    parts = args.case.split(":")
+    tname, dims = parts[0], [int(v) for v in parts[1].lower().split("x")]
+    is_id = len(parts) > 2 and parts[2] == "id"
+    t = {v: k for k, v in O.TYPE_NAMES.items()}[tname]
+    m, k, n = dims
+    ctx = A.Context(0)
+    base = O.quantize(t, O.fill_normal(256 * k, 0x5EED0C00 + t, 0.02).reshape(256, k))
+    if is_id:
+        n_exp, n_used = 512, 10
+        w = np.tile(base, (-(-m // 256), 1))[:m]
+        w = np.tile(w[None], (n_exp, 1, 1))
+        rb = w.shape[-1]
+        ids = O.route_ids(n_used, n, n_exp, 0x5EED0C10)
+        x = O.fill_normal(n * k, 0x5EED0C20, 1.0).reshape(n, 1, k)
+        dw, dx, di, dy = ctx.upload(w), ctx.upload(x), ctx.upload(ids), ctx.alloc(n * n_used * m * 4)
+        W = [A.Tensor.make(t, [k, m, n_exp, 1], [A.block_bytes(t), rb, rb * m, rb * m * n_exp], dw)]
+        X, I = A.Tensor.f32(dx, [k, 1, n]), A.Tensor.make(A.I32, [n_used, n, 1, 1], [4, 4 * n_used], di)
+        Y = A.Tensor.f32(dy, [m, n_used, n])
+        call = lambda i: ctx.mul_mat_id(W[0], X, I, Y)
+        ops = 2.0 * m * k * n * n_used
+    else:
+        w = np.tile(base, (-(-m // 256), 1))[:m]
+        copies = max(2, min(16, -(-3 * L2_BYTES // w.nbytes)))
+        first = ctx.upload(w)
+        ptrs = [first]
+        for _ in range(copies - 1):
+            p2 = ctx.alloc(w.nbytes)
+            ctx.copy(p2, first, w.nbytes)
+            ptrs.append(p2)
+        x = O.fill_normal(min(n, 256) * k, 0x5EED0C20, 1.0).reshape(min(n, 256), k)
+        x = np.tile(x, (-(-n // 256), 1))[:n]
+        dx, dy = ctx.upload(x), ctx.alloc(n * m * 4)
+        W = [A.Tensor.weights(t, p2, k, m) for p2 in ptrs]
+        X, Y = A.Tensor.f32(dx, [k, n]), A.Tensor.f32(dy, [m, n])
+        call = lambda i: ctx.mul_mat(W[i % len(W)], X, Y)
+        ops = 2.0 * m * k * n
+    ctx.graph_begin()
+    call(0)
+    ctx.sync()
+    ctx.stats_reset()
+    times = []
+    for i in range(args.reps):
+        ctx.graph_begin()
+        ctx.timer_start()
+        call(i + 1)
+        times.append(ctx.timer_stop())
+    ms = float(np.median(times))
+    wbytes = m * A.row_bytes(t, k)
+    print(json.dumps({"case": args.case, "reps": args.reps, "ms_per_call_median": ms, "ms_all": [round(v, 4) for v in times],
+                      "tops": ops / (ms * 1e-3) / 1e12, "weight_gbs": wbytes / (ms * 1e-3) / 1e9, "stats": ctx.stats(),
+                      "timed": "one eager call (activation quantize + product), CUDA events"}))
+    ctx.close()
 
 
 def run_reference(args, rank):
@@ -639,6 +745,19 @@ def run_gpu(args, rank, world):
     if dist:
         dist.barrier()
     if rank == 0:
+        # one short line per section first, so a truncated tail of the output still carries the sharded numbers
+        for r in prefill:
+            print("# prefill %-44s %8.4f ms %7.1f TOP/s frac %.3f err %.1e" % (r["workload"], r["ms"], r["tops"], r["roofline"]["frac"],
+                                                                             r["parity_max_rel_err"]), file=sys.stderr)
+        for r in tp_trace:
+            print("# tp_trace %-34s %8.3f ms/pass %10.1f tok/s err %.1e (%s)" % (r["workload"], r["ms_per_pass"], r["tokens_per_s"],
+                                                                                 r["parity_max_rel_err"], r["parallelism"][:24]), file=sys.stderr)
+        for r in moe:
+            print("# moe %-52s %8.4f ms err %.1e (%s)" % (r["workload"], r["ms"], r["parity_max_rel_err"], r["parallelism"][:24]),
+                  file=sys.stderr)
+        summary = {"prefill": {r["workload"]: [round(r["ms"], 4), round(r["tops"], 1)] for r in prefill},
+                   "tp_trace_ms": {r["workload"].split()[-1]: round(r["ms_per_pass"], 3) for r in tp_trace},
+                   "moe_ms": {("%d tok" % (1 if " 1 token" in r["workload"] else 2048)): round(r["ms"], 4) for r in moe}}
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -648,8 +767,8 @@ def run_gpu(args, rank, world):
                        "launch": "each step is one CUDA-graph replay of 12 x (quantize, GEMV)",
                        "parallelism": "replicas" if world > 1 else "single GPU", "parity_max_rel_err": err},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         # DRAM bytes per GEMV launch, mean over the 12 products: ncu read 25.38 MB for the 25.36 MB
-                         # Q4_K matrix and 107.5 MB for the 107.52 MB Q6_K head (profiles/gemv_decode_q4_K_q6_K.md)
+                         # DRAM bytes per GEMV launch, mean over the 12 products: an ncu capture read 25.38 MB for the
+                         # 25.36 MB Q4_K matrix and 107.5 MB for the 107.52 MB Q6_K head (1.001 x algorithmic)
                          "traffic": 1.001 * tot_b / len(detail), "algorithmic_bytes_per_launch": tot_b / len(detail),
                          "peak_source": peak_src, "kernel": "gemv_kernel (activation pre-quantized), back-to-back launches in a CUDA graph",
                          "detail": detail},
@@ -662,6 +781,7 @@ def run_gpu(args, rank, world):
                     "mul_mat, tensor_fetch (device -> pinned host, copy stream); one synchronize per step", "graph_replay_value": world * total_bytes / (ms_e2e_graph * 1e-3) / 1e9},
             "gpu_launches": launches,
             "clocks": clocks,
+            "sections_ms": summary,
         }
         print(json.dumps(line))
     ctx.close()
@@ -675,10 +795,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200q", choices=["b200q", "reference"])
+    ap.add_argument("--case", default=None, help="<type>:<M>x<K>x<N>[:id] -- one product a few times (profiling)")
+    ap.add_argument("--reps", type=int, default=4)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args, rank)
     else:
         run_gpu(args, rank, world)

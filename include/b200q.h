@@ -221,6 +221,10 @@ B200Q_API b200q_status b200q_noalloc_device_error(int device, int *error);
 B200Q_API b200q_status b200q_debug_quantize_act(b200q_ctx *ctx, int weight_type, const b200q_tensor *src1,
                                                 void *dev_codes, void *dev_scales, void *dev_sums);
 B200Q_API b200q_status b200q_debug_dequantize(b200q_ctx *ctx, const b200q_tensor *src0, float *dev_out);
+/* Failure-path check: enqueues a one-thread kernel whose bounded wait (at most `polls` polls of a barrier
+ * nobody arrives at) must run out; like every kernel of the library it then sets the context's error word
+ * and returns, so the next b200q_synchronize answers B200Q_TIMEOUT and the context stays usable. */
+B200Q_API b200q_status b200q_debug_wait_timeout(b200q_ctx *ctx, unsigned polls);
 
 #ifdef __cplusplus
 }

@@ -66,6 +66,37 @@ def main():
         errs.append(rel_err(got, O.mul_mat_f64(t, w, k, x, True)))
         assert errs[-1] < TOL, ("row split", t, errs[-1])
 
+    # the one-shot all-reduce over peer memory, many times in a row (both sets of slots, the device-side sequence
+    # number), eagerly and replayed from a CUDA graph: every rank must end with the same, exact sums
+    # (small integers: any order of the additions gives the same float)
+    cnt = 3000
+    vals = (np.arange(cnt, dtype=np.float32) % 97) + rank
+    dv = ctx.alloc(cnt * 4)
+    want = sum(((np.arange(cnt, dtype=np.float32) % 97) + r) for r in range(world))
+    for rep in range(5):
+        ctx.upload(vals, dv)
+        ctx.all_reduce_f32(dv, cnt)
+        assert np.array_equal(ctx.download(dv, (cnt,), np.float32), want), ("peer all-reduce", rep)
+    ctx.upload(vals, dv)
+    ctx.sync()
+    dist.barrier()
+
+    def three():
+        for _ in range(3):
+            ctx.all_reduce_f32(dv, cnt)
+
+    g = ctx.capture(three)
+    for rep in range(2):
+        ctx.graph_launch(g)
+        ctx.sync()
+        dist.barrier()
+    ctx.graph_free(g)
+    # six all-reduces of the running sums: value * world^6 (exact in f32 for these sizes)
+    got6 = ctx.download(dv, (cnt,), np.float32)
+    # after the first all-reduce every rank holds `want`; each further one multiplies by world
+    assert np.array_equal(got6, want * float(world) ** 5), "peer all-reduce in a graph"
+    peer_used = ctx.stats().get("tp_allreduce_peer", 0)
+
     # variable all-to-all: rank r sends (r + p + 1) floats of value 100 r + p to peer p
     send_counts = [rank + p + 1 for p in range(world)]
     recv_counts = [p + rank + 1 for p in range(world)]
@@ -97,10 +128,12 @@ def main():
         assert ep_errs[-1] < TOL, ("expert parallel", t, ep_errs[-1])
 
     st = ctx.stats()
-    assert st.get("tp_allgather") == 1 and st.get("tp_allreduce") == 2 and st.get("gemm_tc") == 1, st
+    assert st.get("tp_allgather") == 1 and st.get("tp_allreduce") == 2 + 5 + 3 and st.get("gemm_tc") == 1, st
+    # the decode-sized all-reduces went over peer memory unless the mapping was refused or switched off
+    assert peer_used in (0, st.get("tp_allreduce")) or os.environ.get("B200Q_NO_PEER_AR") == "1", st
     dist.barrier()
-    print("MGPU_OK rank %d/%d colsplit %.2e rowsplit %s ep %s" % (rank, world, e1, ["%.2e" % e for e in errs],
-                                                                     ["%.2e" % e for e in ep_errs]), flush=True)
+    print("MGPU_OK rank %d/%d colsplit %.2e rowsplit %s ep %s peer_allreduce %d" % (rank, world, e1, ["%.2e" % e for e in errs],
+                                                                                       ["%.2e" % e for e in ep_errs], peer_used), flush=True)
     ctx.close()
     dist.destroy_process_group()
 

@@ -12,6 +12,20 @@ import oracle as O
 from arcint_b200 import build as B
 
 _emul = None
+_mutants = {}
+
+
+def _load(so):
+    E = C.CDLL(so)
+    vp, i64 = C.c_void_p, C.c_int64
+    E.emul_gemv.argtypes = [C.c_int, vp, C.c_size_t, i64, i64, vp, vp, vp, vp, vp, C.c_int, C.c_int, vp, i64]
+    return E
+
+
+def mutant(define):
+    if define not in _mutants:
+        _mutants[define] = _load(B.build_emul(define=define))
+    return _mutants[define]
 
 
 def emul():
@@ -138,8 +152,8 @@ def test_device_decoder_text_matches_gguf_golden(golden, name, t):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
-def _run_emul(t, w, k, x, R):
-    E = emul()
+def _run_emul(t, w, k, x, R, E=None):
+    E = E or emul()
     m, n = w.shape[0], x.shape[0]
     if O.act_form(t) == O.ACT_Q8_0:
         q, d = O.quantize_act_q8_0(x)
@@ -191,3 +205,49 @@ def test_gemv_lane_code_red_case():
     x2 = x.copy()
     x2[0, 700] += 0.5
     assert rel_err(_run_emul(t, w, k, x2, 4), ref) > 1e-3
+
+
+@pytest.mark.parametrize("define,t", [("B200Q_RED_Q40", O.Q4_0), ("B200Q_RED_SCALE", O.Q4_K), ("B200Q_RED_DROP", O.Q8_0),
+                                      ("B200Q_RED_DROP", O.Q4_0)])
+def test_kernel_mutants_turn_the_suite_red(define, t):
+    """The reference ships a mutant switch with every kernel patch and records that the suite fails under it
+    (0099-opencl-q4_0-q8_0-int8-gemm.patch:304-310, 576-581; 0103-opencl-id-int8-sg8.patch:338-343;
+    0115-...patch:742-746). The same lane text, built with the switch, must miss the tolerance the real build
+    meets on every case here."""
+    E = mutant(define)
+    rng = np.random.default_rng(7)
+    red = green = 0
+    for k in (1024, 4096):
+        for n in (1, 4, 8):
+            w = O.random_blocks(t, 7, k, rng)
+            x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
+            ref = O.mul_mat_f64(t, w, k, x, True)
+            green += rel_err(_run_emul(t, w, k, x, 4), ref) < 1e-4
+            red += rel_err(_run_emul(t, w, k, x, 4, E), ref) > 1e-3
+    assert green == 6 and red == 6, (define, green, red)
+
+
+@pytest.mark.parametrize("nranks", [2, 4, 8])
+def test_peer_allreduce_slot_protocol_and_give_up(nranks):
+    """The one-shot all-reduce's slot protocol (sequence number beside each float, two alternating sets of
+    slots, sum in rank order) replayed on the host from the kernel's own text: two all-reduces in a row give
+    the same sum on every rank; with one rank silent in the second, every reader's bounded wait gives up
+    after its poll limit instead of spinning."""
+    E = emul()
+    E.emul_peer_allreduce.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_uint, C.c_void_p]
+    rng = np.random.default_rng(nranks)
+    count = 1000
+    x = rng.normal(0, 1, size=(2, nranks, count)).astype(np.float32)
+    out = np.empty_like(x)
+    gave = np.zeros(nranks, dtype=np.int32)
+    assert E.emul_peer_allreduce(nranks, count, x.ctypes.data, out.ctypes.data, -1, 100, gave.ctypes.data) == 0
+    assert not gave.any()
+    for call in range(2):
+        want = np.zeros(count, dtype=np.float32)
+        for r in range(nranks):                                  # the kernel's order: rank 0 first
+            want = want + x[call, r]
+        for r in range(nranks):
+            assert np.array_equal(out[call, r], want)
+    assert E.emul_peer_allreduce(nranks, count, x.ctypes.data, out.ctypes.data, nranks - 1, 50, gave.ctypes.data) == 0
+    assert gave.all()                                            # nobody hung: every rank gave up and said so
+    assert np.array_equal(out[0, 0], x[0].sum(axis=0, dtype=np.float32)) or np.allclose(out[0, 0], x[0].sum(axis=0), atol=1e-5)

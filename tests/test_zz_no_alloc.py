@@ -54,6 +54,43 @@ def test_two_calls_in_a_row_match_mul_mat(ctx, t, k):
         assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
 
 
+@pytest.mark.parametrize("t", [A.Q4_0, A.Q8_0, A.Q4_K, A.Q6_K, A.IQ4_XS])
+def test_the_array_filled_to_its_limits(ctx, t):
+    """8 columns of 32768 values fill every part of the fixed array exactly (codes, scales, both kinds of
+    block sums): a part one element short would overwrite its neighbour. Then a narrow call with other
+    values on the same array."""
+    k, m = 32768, 8
+    rng = np.random.default_rng(900 + t)
+    w = O.random_blocks(t, m, k, rng)
+    for n, scale in ((8, 1.0), (1, 0.25)):
+        x = (rng.normal(0, 1, size=(n, k)) * scale).astype(np.float32)
+        want, got = both_ways(ctx, t, w, k, x)
+        assert np.array_equal(got, want)
+        assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
+    err = A.binding.C.c_int(-1)
+    assert ctx.L.b200q_noalloc_device_error(0, A.binding.C.byref(err)) == A.OK and err.value == 0
+
+
+def test_rows_that_are_not_16_byte_multiples(ctx):
+    """Q6_K with K = 2816 (11 blocks of 210 bytes): the rows take the kernel's 2-byte loader."""
+    t, k, m = A.Q6_K, 2816, 37
+    rng = np.random.default_rng(12)
+    w = O.random_blocks(t, m, k, rng)
+    x = rng.normal(0, 1, size=(5, k)).astype(np.float32)
+    want, got = both_ways(ctx, t, w, k, x)
+    assert np.array_equal(got, want) and rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
+
+
+def test_unevenly_spaced_dst_columns_are_refused(ctx):
+    d = ctx.alloc(1 << 20)
+    W = A.Tensor.weights(A.Q4_0, d, 1024, 4)
+    X = A.Tensor.make(A.F32, [1024, 2, 2, 1], [4, 4096, 8192, 16384], d)
+    Y = A.Tensor.make(A.F32, [4, 2, 2, 1], [4, 16, 48, 96], d)        # columns 0,1 | gap | 2,3
+    assert ctx.L.b200q_mul_mat_noalloc(0, None, W, X, Y) == A.UNSUPPORTED
+    assert b"evenly spaced" in ctx.L.b200q_noalloc_last_error()
+    ctx.free(d)
+
+
 def test_limits_are_refused_with_a_message(ctx):
     d = ctx.alloc(1 << 20)
     W = A.Tensor.weights(A.Q4_0, d, 1024, 4)
