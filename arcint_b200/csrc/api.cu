@@ -42,7 +42,7 @@ const char *stat_name(int s) {
     }
     static const char *rest[] = { "gemv_id", "gemv_id_unaligned", "moe_route", "route_cache_hit", "moe_gemm", "moe_pack",
                                   "gemm_tc", "gemm_tc_quantize", "gemm_fallback_shape", "tp_allreduce", "tp_allgather",
-                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins", "gemv_stream", "tp_allreduce_peer" };
+                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins", "gemv_stream", "tp_allreduce_peer", "gemm_tc_f16" };
     return rest[s - ST_GEMV_ID];
 }
 
@@ -257,6 +257,8 @@ b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
     ctx->no_tc = no_tc && no_tc[0] == '1';
     const char *no_pdl = getenv("B200Q_NO_PDL");     // plain stream order in the decode chain (comparisons)
     ctx->no_pdl = no_pdl && no_pdl[0] == '1';
+    const char *tc_i8 = getenv("B200Q_TC_I8");           // the int8 arm of the per-32 prompt GEMM (comparisons)
+    ctx->tc_f16 = !(tc_i8 && tc_i8[0] == '1');
     const char *no_stream = getenv("B200Q_NO_STREAM");   // the older GEMV kernel for every shape (comparisons)
     ctx->no_stream = no_stream && no_stream[0] == '1';
     *out = ctx;

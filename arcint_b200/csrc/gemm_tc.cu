@@ -46,8 +46,13 @@ constexpr int BN = 128;            // tokens per tile (MMA N, tensor-memory colu
 constexpr int KB = 32;             // weights per MMA (one quantization block)
 constexpr int SB = 8;              // blocks per k-stage (256 weights)
 constexpr int NACC = 4;            // accumulators in tensor memory (4 x 128 = 512 columns)
-constexpr int OPER_BYTES = BM * KB;                         // one int8 operand block: 4096 B
-constexpr int ACT_CHUNK = SB * OPER_BYTES + SB * BN * 4;    // codes + f32 scales of a stage: 36864 B
+// One operand block (128 rows or columns x 32 k) is 4096 B as int8 and 8192 B as fp16; both are K-major
+// core matrices (8 rows x 16 bytes) with the 16-byte K pieces LBO apart: two pieces per block as int8,
+// four as fp16 (an fp16 MMA covers K = 16, so a block is two of them).
+template <bool F16> struct Oper {
+    enum { BYTES = BM * KB * (F16 ? 2 : 1),
+           ACT_CHUNK = SB * BYTES + SB * BN * 4 };          // codes + f32 scales of a stage: 36864 / 69632 B
+};
 constexpr int NW = 2;              // scale-accumulate warps per tensor-memory lane quarter (4 measured no faster)
 constexpr int THREADS = 32 * (8 + 4 * NW);   // warp groups: {producer, MMA, 2 idle}, unpack, NW x scale-accumulate
 // Registers per thread by role (setmaxnreg). The launch gives every thread LAUNCH_REGS; a warp group that
@@ -62,22 +67,28 @@ static_assert(REGS_CTRL <= LAUNCH_REGS && REGS_UNPACK <= LAUNCH_REGS && REGS_SCA
 
 
 template <int TYPE> struct Raw;     // packed bytes of one row per stage
-template <> struct Raw<B200Q_TYPE_Q4_0> { enum { ROW = SB * 18, NSTAGE = 3 }; };     // 144 B per row and stage
-template <> struct Raw<B200Q_TYPE_Q8_0> { enum { ROW = SB * 34, NSTAGE = 2 }; };     // 272 B: two stages fit
+template <> struct Raw<B200Q_TYPE_Q4_0> { enum { ROW = SB * 18, NSTAGE = 3, A_SLOTS_F16 = 4 }; };     // 144 B per row and stage
+template <> struct Raw<B200Q_TYPE_Q8_0> { enum { ROW = SB * 34, NSTAGE = 2, A_SLOTS_F16 = 2 }; };     // 272 B: two stages fit
 
-template <int TYPE> struct Smem {
+template <int TYPE, bool F16> struct Smem {
     enum {
-        NSTAGE = Raw<TYPE>::NSTAGE,         // raw-weight / activation stages in flight
+        NSTAGE = F16 ? 2 : Raw<TYPE>::NSTAGE,     // raw-weight / activation stages in flight
+        A_SLOTS = F16 ? Raw<TYPE>::A_SLOTS_F16 : SB,      // unpacked A operand blocks in flight
         RAW_STAGE = BM * Raw<TYPE>::ROW,
         RAW_OFF = 0,
         ACT_OFF = RAW_OFF + NSTAGE * RAW_STAGE,
-        A_OFF = ACT_OFF + NSTAGE * ACT_CHUNK,
-        BAR_OFF = A_OFF + SB * OPER_BYTES,
+        A_OFF = ACT_OFF + NSTAGE * Oper<F16>::ACT_CHUNK,
+        BAR_OFF = A_OFF + A_SLOTS * Oper<F16>::BYTES,
         TOTAL = BAR_OFF + 8 * 64             // room for up to 64 mbarriers (BAR_COUNT of them are used)
     };
 };
+static_assert(Smem<B200Q_TYPE_Q4_0, true>::TOTAL <= 227 * 1024 && Smem<B200Q_TYPE_Q8_0, true>::TOTAL <= 227 * 1024, "shared memory");
 
 constexpr uint32_t IDESC_I8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// fp16 operands, f32 accumulator: integer-valued halves (|v| <= 255) multiply and add exactly (every
+// partial sum of a 32-block stays far below 2^24), so the accumulator holds float(I_b) with the bits the
+// int8 MMA's result would convert to -- without the conversion
+constexpr uint32_t IDESC_F16 = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
 // barrier slots inside the shared block
 enum { BAR_RAW_FULL = 0, BAR_RAW_EMPTY = 3, BAR_ACT_FULL = 6, BAR_ACT_EMPTY = 9, BAR_A_FULL = 12, BAR_A_EMPTY = 20,
@@ -85,13 +96,16 @@ enum { BAR_RAW_FULL = 0, BAR_RAW_EMPTY = 3, BAR_ACT_FULL = 6, BAR_ACT_EMPTY = 9,
 static_assert(BAR_COUNT <= 64, "the shared block reserves 64 mbarrier slots");
 
 // Activation chunk (n-tile t, k-stage s) in global memory, written by quantize_tiled_kernel:
-//   codes  [block j < 8][half c < 2][group g < 16][column r < 8][16 bytes]   column 8g + r, k = 32j + 16c + byte
+//   codes  [block j < 8][piece c][group g < 16][column r < 8][16 bytes]   column 8g + r; int8: two pieces of 16 k
+//          (k = 32j + 16c + byte), fp16: four pieces of 8 k (k = 32j + 8c + half), the codes as exact halves
 //   scales [block j < 8][column < 128] f32 (the fp16-rounded block scale)
+template <bool F16>
 __global__ void __launch_bounds__(256)
 quantize_tiled_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t nb1, size_t nb2, size_t nb3, int64_t K,
                       int64_t N, uint8_t *__restrict__ out, TileRoute id) {
     const int t = blockIdx.y, s = blockIdx.x, nst = gridDim.x;
     const int col = threadIdx.x & 127, half = threadIdx.x >> 7;
+    constexpr int OPER_BYTES = Oper<F16>::BYTES, ACT_CHUNK = Oper<F16>::ACT_CHUNK;
     uint8_t *chunk = out + ((size_t)t * nst + s) * ACT_CHUNK;
     const float *x = nullptr;
     if (id.tiles) {
@@ -121,17 +135,29 @@ quantize_tiled_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t nb1,
         }
         const float d = __fdiv_rn(amax, 127.f);
         const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;
-        uint32_t w[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            uint32_t p = 0;
-#pragma unroll
-            for (int b = 0; b < 4; ++b) p |= (uint32_t)((int)roundf(__fmul_rn(v[4 * i + b], id)) & 0xFF) << (8 * b);
-            w[i] = p;
-        }
         uint8_t *o = chunk + j * OPER_BYTES + (col >> 3) * 128 + (col & 7) * 16;
-        *reinterpret_cast<uint4 *>(o) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4 *>(o + LBO) = make_uint4(w[4], w[5], w[6], w[7]);
+        if (F16) {
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const __half2 h = __floats2half2_rn(roundf(__fmul_rn(v[2 * i], id)), roundf(__fmul_rn(v[2 * i + 1], id)));
+                w[i] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4 *>(o + c * LBO) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+        } else {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                uint32_t p = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) p |= (uint32_t)((int)roundf(__fmul_rn(v[4 * i + b], id)) & 0xFF) << (8 * b);
+                w[i] = p;
+            }
+            *reinterpret_cast<uint4 *>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4 *>(o + LBO) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
         reinterpret_cast<float *>(chunk + SB * OPER_BYTES)[j * BN + col] = __half2float(__float2half_rn(d));
     }
 }
@@ -142,13 +168,31 @@ template <int N> __device__ __forceinline__ uint32_t word_at(const uint32_t (&w)
     return sh == 0 ? w[i] : __funnelshift_r(w[i], w[i + 1], sh);
 }
 
-template <int TYPE>
+// four int8 bytes -> their values as exact fp16 halves: a byte b becomes the half 0x6400 | b = 1024 + b (byte
+// permute with the constant 0x64), and one packed subtraction removes 1024 and the code's own offset
+__device__ __forceinline__ void bytes_to_halves(uint32_t b4, uint32_t bias2, uint32_t &h01, uint32_t &h23) {
+    const uint32_t a = __byte_perm(b4, 0x64646464u, 0x4140), b = __byte_perm(b4, 0x64646464u, 0x4342);
+    const __half2 bias = *reinterpret_cast<const __half2 *>(&bias2);
+    const __half2 ra = __hsub2(*reinterpret_cast<const __half2 *>(&a), bias), rb = __hsub2(*reinterpret_cast<const __half2 *>(&b), bias);
+    h01 = *reinterpret_cast<const uint32_t *>(&ra);
+    h23 = *reinterpret_cast<const uint32_t *>(&rb);
+}
+
+__device__ __forceinline__ void umma_f16_acc(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <int TYPE, bool F16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
                int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word, TileRoute id) {
-    typedef Smem<TYPE> L;
+    typedef Smem<TYPE, F16> L;
     constexpr int ROWB = Raw<TYPE>::ROW;
     constexpr int NSTAGE = L::NSTAGE;
+    constexpr int A_SLOTS = L::A_SLOTS;
+    constexpr int OPER_BYTES = Oper<F16>::BYTES, ACT_CHUNK = Oper<F16>::ACT_CHUNK;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -183,7 +227,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             mbar_init(bar(BAR_ACT_FULL + i), 1);
             mbar_init(bar(BAR_ACT_EMPTY + i), 1 + 4 * NW);     // MMA commit + every scaling warp
         }
-        for (int i = 0; i < SB; ++i) {
+        for (int i = 0; i < A_SLOTS; ++i) {
             mbar_init(bar(BAR_A_FULL + i), 4);                  // unpack warps
             mbar_init(bar(BAR_A_EMPTY + i), 1);
         }
@@ -234,16 +278,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         // ---- MMA issuer ----
         asm volatile("setmaxnreg.dec.sync.aligned.u32 " B200Q_STR(64) ";" ::: "memory");   // REGS_CTRL
         for (int b = 0; b < nblk; ++b) {
-            const int s = b / SB, j = b % SB, st = s % NSTAGE, acc = b % NACC;
+            const int s = b / SB, j = b % SB, st = s % NSTAGE, acc = b % NACC, slot = b % A_SLOTS;
             if (j == 0 && !WAITP(2, bar(BAR_ACT_FULL + st), (s / NSTAGE) & 1)) break;
-            if (!WAITP(4, bar(BAR_A_FULL + j), (b / SB) & 1)) break;
+            if (!WAITP(4, bar(BAR_A_FULL + slot), (b / A_SLOTS) & 1)) break;
             if (!WAITP(7, bar(BAR_ACC_EMPTY + acc), ((b / NACC) & 1) ^ 1)) break;
             tc_fence_after();
             if (lane == 0) {
-                umma_i8(tmem_base + (uint32_t)acc * BN, umma_desc(sbase + L::A_OFF + j * OPER_BYTES),
-                        umma_desc(sbase + L::ACT_OFF + st * ACT_CHUNK + j * OPER_BYTES), IDESC_I8);
+                const uint32_t a_addr = sbase + L::A_OFF + slot * OPER_BYTES, b_addr = sbase + L::ACT_OFF + st * ACT_CHUNK + j * OPER_BYTES;
+                if (F16) {
+                    // K = 16 per fp16 MMA: the block's first two 16-byte K pieces, then the other two
+                    umma_f16_acc(tmem_base + (uint32_t)acc * BN, umma_desc(a_addr), umma_desc(b_addr), IDESC_F16, 0u);
+                    umma_f16_acc(tmem_base + (uint32_t)acc * BN, umma_desc(a_addr + 2 * LBO), umma_desc(b_addr + 2 * LBO), IDESC_F16, 1u);
+                } else {
+                    umma_i8(tmem_base + (uint32_t)acc * BN, umma_desc(a_addr), umma_desc(b_addr), IDESC_I8);
+                }
                 tc_commit(bar(BAR_ACC_FULL + acc));
-                tc_commit(bar(BAR_A_EMPTY + j));
+                tc_commit(bar(BAR_A_EMPTY + slot));
                 if (j == SB - 1) tc_commit(bar(BAR_ACT_EMPTY + st));
             }
             __syncwarp();
@@ -271,9 +321,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
 #pragma unroll
             for (int j = 0; j < SB; ++j) {
-                const int b = s * SB + j;
-                if (!WAITP(5, bar(BAR_A_EMPTY + j), ((b / SB) & 1) ^ 1)) { ok = false; break; }
+                const int b = s * SB + j, slot = b % A_SLOTS;
+                if (!WAITP(5, bar(BAR_A_EMPTY + slot), ((b / A_SLOTS) & 1) ^ 1)) { ok = false; break; }
                 constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
+                uint8_t *a = smem + L::A_OFF + slot * OPER_BYTES + (r >> 3) * 128 + (r & 7) * 16;
+                if (F16) {
+                    // the block's 32 weights as exact fp16 integers, four pieces of eight
+                    uint32_t h[16];
+                    if (TYPE == B200Q_TYPE_Q4_0) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const uint32_t q = word_at(rw, BB * j + 2 + 4 * i);
+                            bytes_to_halves(q & 0x0F0F0F0Fu, 0x64086408u, h[2 * i], h[2 * i + 1]);               // 1024 + n - 1032
+                            bytes_to_halves((q >> 4) & 0x0F0F0F0Fu, 0x64086408u, h[8 + 2 * i], h[8 + 2 * i + 1]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)                                                               // 1024 + (q + 128) - 1152
+                            bytes_to_halves(word_at(rw, BB * j + 2 + 4 * i) ^ 0x80808080u, 0x64806480u, h[2 * i], h[2 * i + 1]);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        *reinterpret_cast<uint4 *>(a + c * LBO) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+                    fence_async_smem();
+                    mbar_arrive_warp(bar(BAR_A_FULL + slot), lane);
+                    continue;
+                }
                 uint32_t lo[4], hi[4];
                 if (TYPE == B200Q_TYPE_Q4_0) {
 #pragma unroll
@@ -289,11 +362,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                         hi[i] = word_at(rw, BB * j + 18 + 4 * i);
                     }
                 }
-                uint8_t *a = smem + L::A_OFF + j * OPER_BYTES + (r >> 3) * 128 + (r & 7) * 16;
                 *reinterpret_cast<uint4 *>(a) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 *reinterpret_cast<uint4 *>(a + LBO) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                 fence_async_smem();
-                mbar_arrive_warp(bar(BAR_A_FULL + j), lane);
+                mbar_arrive_warp(bar(BAR_A_FULL + slot), lane);
             }
         }
     } else {
@@ -322,32 +394,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                                            smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + BB * j)) : 0.f;
             const f32x2 dw2 = f2_pack(dwb, dwb), negc2 = f2_pack(-12582912.f, -12582912.f);
             const uint32_t dxa = sbase + L::ACT_OFF + st * ACT_CHUNK + SB * OPER_BYTES + (j * BN + u * CW) * 4;
-            // sixteen columns at a time, the next sixteen in flight while these are scaled
-            uint32_t v[2][16];
-            tmem_ld16(taddr, v[0]);
+            // the whole accumulator slice in one go: the CW/16 tensor-memory loads are issued back to back and
+            // waited for once (one load latency per block, not one per sixteen columns), then the accumulator
+            // is free for the MMA three blocks ahead while these registers are scaled
+            uint32_t v[CW / 16][16];
+#pragma unroll
+            for (int q = 0; q < CW / 16; ++q) tmem_ld16(taddr + q * 16, v[q]);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive_warp(bar(BAR_ACC_EMPTY + acc), lane);
 #pragma unroll
             for (int q = 0; q < CW / 16; ++q) {
-                // the sixteen activation scales: four loads in flight together, under the wait for the
-                // tensor-memory load
                 f32x2 dx[8];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) lds128_f2(dxa + (q * 16 + 4 * c) * 4, dx[2 * c], dx[2 * c + 1]);
-                tmem_ld_wait();
-                if (q + 1 < CW / 16) {
-                    tmem_ld16(taddr + (q + 1) * 16, v[(q + 1) & 1]);
-                } else {
-                    tc_fence_before();
-                    mbar_arrive_warp(bar(BAR_ACC_EMPTY + acc), lane);     // the accumulator is in registers: free it
-                }
 #pragma unroll
                 for (int c = 0; c < 16; c += 4) {
                     const int e = (q * 16 + c) / 2;
-                    // exact int -> float without the conversion pipe (|I| < 2^22): add the
-                    // magic exponent as an integer, subtract it as a float
-                    const f32x2 x01 = f2_add(f2_pack(__int_as_float((int)v[q & 1][c] + 0x4B400000),
-                                                     __int_as_float((int)v[q & 1][c + 1] + 0x4B400000)), negc2);
-                    const f32x2 x23 = f2_add(f2_pack(__int_as_float((int)v[q & 1][c + 2] + 0x4B400000),
-                                                     __int_as_float((int)v[q & 1][c + 3] + 0x4B400000)), negc2);
+                    // int8 arm: exact int -> float without the conversion pipe (|I| < 2^22): add the magic
+                    // exponent as an integer, subtract it as a float; the fp16 arm's accumulator already holds floats
+                    const f32x2 x01 = F16 ? f2_pack(__uint_as_float(v[q][c]), __uint_as_float(v[q][c + 1]))
+                                          : f2_add(f2_pack(__int_as_float((int)v[q][c] + 0x4B400000),
+                                                           __int_as_float((int)v[q][c + 1] + 0x4B400000)), negc2);
+                    const f32x2 x23 = F16 ? f2_pack(__uint_as_float(v[q][c + 2]), __uint_as_float(v[q][c + 3]))
+                                          : f2_add(f2_pack(__int_as_float((int)v[q][c + 2] + 0x4B400000),
+                                                           __int_as_float((int)v[q][c + 3] + 0x4B400000)), negc2);
                     acc2[e]     = f2_fma(x01, f2_mul(dw2, dx[c / 2]), acc2[e]);
                     acc2[e + 1] = f2_fma(x23, f2_mul(dw2, dx[c / 2 + 1]), acc2[e + 1]);
                 }
@@ -416,9 +487,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
 
 }  // namespace tc
 
+// sized for the larger (fp16) form, so one scratch serves either arm
 size_t gemm_tc_act_bytes(int64_t K, int64_t N) {
     const int64_t ntile = (N + tc::BN - 1) / tc::BN, nst = K / (tc::SB * tc::KB);
-    return (size_t)(ntile * nst) * tc::ACT_CHUNK;
+    return (size_t)(ntile * nst) * tc::Oper<true>::ACT_CHUNK;
 }
 
 bool gemm_tc_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride) {
@@ -434,8 +506,12 @@ static const TileRoute NO_ROUTE_TC = { nullptr, nullptr, nullptr, 1, 1, 0, 0, 0,
 static b200q_status quantize_tiled(b200q_ctx *ctx, const b200q_tensor *src1, uint8_t *out, int64_t n_tiles, const TileRoute &tr) {
     const int64_t K = src1->ne[0], N = src1->ne[1] * src1->ne[2] * src1->ne[3];
     dim3 grid((unsigned)(K / (tc::SB * tc::KB)), (unsigned)n_tiles);
-    tc::quantize_tiled_kernel<<<grid, 256, 0, ctx->stream>>>((const uint8_t *)src1->data, src1->ne[1], src1->ne[2],
-                                                            src1->nb[1], src1->nb[2], src1->nb[3], K, N, out, tr);
+    if (ctx->tc_f16)
+        tc::quantize_tiled_kernel<true><<<grid, 256, 0, ctx->stream>>>((const uint8_t *)src1->data, src1->ne[1], src1->ne[2],
+                                                                      src1->nb[1], src1->nb[2], src1->nb[3], K, N, out, tr);
+    else
+        tc::quantize_tiled_kernel<false><<<grid, 256, 0, ctx->stream>>>((const uint8_t *)src1->data, src1->ne[1], src1->ne[2],
+                                                                       src1->nb[1], src1->nb[2], src1->nb[3], K, N, out, tr);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC_QUANT);
     return B200Q_OK;
@@ -448,12 +524,12 @@ b200q_status launch_quantize_tiled(b200q_ctx *ctx, const b200q_tensor *src1, uin
 
 // n_tiles: grid width (dense: the tiles of N; MUL_MAT_ID: the upper bound of the route's tile count,
 // blocks past the device-side count leave at once)
-template <int TYPE>
-static b200q_status launch_t(b200q_ctx *ctx, const void *w, size_t row_stride, size_t mat_stride, int64_t n_mat, int64_t M,
-                             int64_t K, const uint8_t *act, int64_t N, int64_t n_tiles, float *dst, int64_t ldd,
-                             const TileRoute &tr) {
-    typedef tc::Smem<TYPE> L;
-    auto kern = tc::gemm_tc_kernel<TYPE>;
+template <int TYPE, bool F16>
+static b200q_status launch_tf(b200q_ctx *ctx, const void *w, size_t row_stride, size_t mat_stride, int64_t n_mat, int64_t M,
+                              int64_t K, const uint8_t *act, int64_t N, int64_t n_tiles, float *dst, int64_t ldd,
+                              const TileRoute &tr) {
+    typedef tc::Smem<TYPE, F16> L;
+    auto kern = tc::gemm_tc_kernel<TYPE, F16>;
     static bool attr_set_dev[B200Q_MAX_DEVICES] = {};
     bool &attr_set = attr_set_dev[ctx->device % B200Q_MAX_DEVICES];
     if (!attr_set) {
@@ -475,7 +551,18 @@ static b200q_status launch_t(b200q_ctx *ctx, const void *w, size_t row_stride, s
     kern<<<grid, tc::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd, ctx->error_word, tr);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
+    if (F16) count(ctx, ST_GEMM_TC_F16);
     return B200Q_OK;
+}
+
+// The arm: fp16 operands (integer-valued, exact) by default; B200Q_TC_I8=1 keeps the int8 MMA. Both give the
+// same block dots bit for bit; the fp16 arm's accumulator needs no int -> float conversion.
+template <int TYPE>
+static b200q_status launch_t(b200q_ctx *ctx, const void *w, size_t row_stride, size_t mat_stride, int64_t n_mat, int64_t M,
+                             int64_t K, const uint8_t *act, int64_t N, int64_t n_tiles, float *dst, int64_t ldd,
+                             const TileRoute &tr) {
+    return ctx->tc_f16 ? launch_tf<TYPE, true>(ctx, w, row_stride, mat_stride, n_mat, M, K, act, N, n_tiles, dst, ldd, tr)
+                       : launch_tf<TYPE, false>(ctx, w, row_stride, mat_stride, n_mat, M, K, act, N, n_tiles, dst, ldd, tr);
 }
 
 b200q_status launch_gemm_tc(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,

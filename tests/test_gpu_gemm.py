@@ -242,3 +242,26 @@ def test_config2_head_q6_K_prompt(ctx):
     rows = np.unique(np.concatenate([[0, 127, 128, m - 1], np.random.default_rng(3).integers(0, m, 28)]))
     assert rel_err(got[:, rows], O.mul_mat_f64(t, w[rows], k, x, True)) < TOL
     assert nmse(got[:, rows], O.mul_mat_f64(t, w[rows], k, x, False)) < 5e-4
+
+
+@pytest.mark.parametrize("t,m,k,n", [(A.Q4_0, 300, 1024, 100), (A.Q8_0, 256, 2048, 129), (A.Q4_0, 128, 4096, 16)])
+def test_fp16_and_int8_arms_give_identical_results(t, m, k, n):
+    """The per-32 prompt GEMM has two arms: int8 operands (tcgen05 kind::i8, int32 block dots converted to float)
+    and integer-valued fp16 operands (kind::f16, f32 block dots). Every product and partial sum of a 32-block is
+    an integer below 2^24, so both give the same float for every block dot and the outputs must match bit for bit."""
+    import os
+    w = make_weights(t, m, k, 700 + t)
+    x = np.random.default_rng(n).normal(0, 1, size=(n, k)).astype(np.float32)
+    outs = {}
+    for arm in ("f16", "i8"):
+        if arm == "i8":
+            os.environ["B200Q_TC_I8"] = "1"
+        try:
+            with A.Context(0) as c:
+                outs[arm] = c.run_mul_mat(t, w, k, x)
+                st = c.stats()
+                assert st.get("gemm_tc") == 1 and (st.get("gemm_tc_f16", 0) == 1) == (arm == "f16"), st
+        finally:
+            os.environ.pop("B200Q_TC_I8", None)
+    assert np.array_equal(outs["f16"], outs["i8"])
+    assert rel_err(outs["f16"], O.mul_mat_f64(t, w, k, x, True)) < TOL
