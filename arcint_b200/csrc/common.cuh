@@ -92,7 +92,7 @@ enum Stat {
     ST_GEMV_UNALIGNED_COL0 = ST_GEMV_COL0 + 9,    // + ncols
     ST_GEMV_ID = ST_GEMV_UNALIGNED_COL0 + 9, ST_GEMV_ID_UNALIGNED, ST_MOE_ROUTE, ST_ROUTE_CACHE_HIT, ST_MOE_GEMM,
     ST_MOE_PACK, ST_GEMM_TC, ST_GEMM_TC_QUANT, ST_GEMM_FALLBACK_SHAPE, ST_TP_ALLREDUCE, ST_TP_ALLGATHER,
-    ST_EP_DISPATCH, ST_EP_COMBINE, ST_GRAPH_LAUNCH, ST_NO_ALLOC, ST_GEMM_KQ_MINS, ST_GEMV_STREAM, ST_TP_ALLREDUCE_PEER, ST_GEMM_TC_F16,
+    ST_EP_DISPATCH, ST_EP_COMBINE, ST_GRAPH_LAUNCH, ST_NO_ALLOC, ST_GEMM_KQ_MINS, ST_GEMV_STREAM, ST_TP_ALLREDUCE_PEER, ST_GEMM_TC_F16, ST_EP_PEER, ST_EP_DISPATCH_CACHED,
     ST_COUNT
 };
 const char *stat_name(int s);
@@ -111,6 +111,7 @@ struct b200q_ctx {
     // what the gathered, tiled activation scratch of the tensor-core MUL_MAT_ID holds (gate and up of a layer
     // read the same src1 through the same ids: the second call finds it ready)
     struct { const void *src1 = nullptr, *ids = nullptr, *src1_id = nullptr, *ids_id = nullptr; int64_t ne[4] = {0, 0, 0, 0}; size_t nb[4] = {0, 0, 0, 0}; uint64_t gen = 0; int per32 = -1, n_expert = 0; } moe_act;
+    bool         route_skip_negative = false;   // expert-parallel local product: negative ids are empty slots
     int          route_pinned = -1;       // a route entry in use across a nested call: not a victim
     uint64_t     private_generation = 0;  // expert-parallel calls: generations of their internal products
     bool         capturing = false;

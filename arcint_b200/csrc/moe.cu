@@ -23,6 +23,7 @@ struct RouteEntry {
     uint64_t gen = 0;
     bool    valid = false;
     int     experts_per_owner = 0;
+    bool    skip_negative = false;
     Workspace buf;               // pairs | 5 tile lists | 8 counters | owner counts
     RouteView view;
 };
@@ -30,7 +31,7 @@ struct RouteEntry {
 __global__ void __launch_bounds__(1024)
 moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_expert, int32_t *pairs,
                  int32_t *tiles0, int32_t *tiles1, int32_t *tiles2, int32_t *tiles3, int32_t *tiles128, int32_t *n_tiles,
-                 int32_t *owner_counts, int experts_per_owner, int n_groups) {
+                 int32_t *owner_counts, int experts_per_owner, int n_groups, int skip_negative) {
     // Counters are kept once per group of warps (a skewed router sends a tenth of all pairs to one
     // expert: one shared-memory counter would serialize them): cntg / fillg [n_groups][n_expert].
     extern __shared__ int sm[];
@@ -42,6 +43,9 @@ moe_route_kernel(const uint8_t *ids, size_t nb1, int n_used, int n_tok, int n_ex
     auto expert_of = [&](int p) {
         const int t = p / n_used, i = p - t * n_used;
         const int e = reinterpret_cast<const int32_t *>(ids + (size_t)t * nb1)[i];
+        // skip_negative: a negative id marks an empty slot (expert-parallel receive regions are only partly
+        // filled) and takes no part in the route; otherwise ids are clamped like the reference's route kernel
+        if (skip_negative && e < 0) return -1;
         return min(max(e, 0), n_expert - 1);
     };
     for (int i = tid; i < 2 * n_groups * n_expert; i += nth) cntg[i] = 0;      // cntg and fillg
@@ -217,7 +221,7 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     for (RouteEntry *e : ctx->routes)
         if (e && e->valid && e->ids_data == ids->data && e->ids_id == ids->id && e->ne[0] == ids->ne[0] && e->ne[1] == ids->ne[1] &&
             e->nb1 == ids->nb[1] && e->n_expert == n_expert && e->gen == ctx->generation &&
-            e->experts_per_owner == experts_per_owner) { hit = e; break; }
+            e->experts_per_owner == experts_per_owner && e->skip_negative == ctx->route_skip_negative) { hit = e; break; }
     if (hit) {
         count(ctx, ST_ROUTE_CACHE_HIT);
         *out = hit->view;
@@ -261,7 +265,8 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     moe_route_kernel<<<1, 1024, smem, ctx->stream>>>((const uint8_t *)ids->data, ids->nb[1], n_used, n_tok, n_expert, pairs,
                                                      tl[0], tl[1], tl[2], tl[3], tl[4], n_tiles,
                                                      experts_per_owner > 0 ? owner_counts : nullptr,
-                                                     experts_per_owner > 0 ? experts_per_owner : 1, n_groups);
+                                                     experts_per_owner > 0 ? experts_per_owner : 1, n_groups,
+                                                     ctx->route_skip_negative ? 1 : 0);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_MOE_ROUTE);
     e.ids_data = ids->data;
@@ -280,6 +285,7 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     e.view.owner_counts = owner_counts;
     e.view.slot = (int)pick;
     e.experts_per_owner = experts_per_owner;
+    e.skip_negative = ctx->route_skip_negative;
     e.valid = true;
     *out = e.view;
     return B200Q_OK;

@@ -15,6 +15,7 @@
 // vectors (peer_ar.cuh), with plain loads and stores; every other byte crosses in NCCL.
 #include <dlfcn.h>
 #include <nccl.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -23,6 +24,7 @@
 #include "common.cuh"
 #include "pdl.cuh"
 #include "peer_ar.cuh"
+#include "ep_peer.cuh"
 
 namespace b200q {
 
@@ -74,6 +76,17 @@ struct TpState {
     uint64_t *ar_local = nullptr;
     uint64_t *ar_peer[PEER_AR_MAX_RANKS] = {};
     uint32_t *ar_state = nullptr;            // [0] sequence number of the last all-reduce, [1] blocks finished
+    // expert parallelism over peer memory (ep_peer.cuh), after b200q_ep_reserve
+    bool      ep_ok = false;
+    int64_t   ep_cap = 0, ep_k = 0, ep_m = 0;          // reserved: pairs per region, longest rows in floats
+    size_t    ep_off_e = 0, ep_off_y = 0, ep_off_flags = 0;
+    uint8_t  *ep_local = nullptr, *ep_peer[EP_MAX_RANKS] = {};
+    float    *ep_out = nullptr;              // local product's results, one row per slot
+    int32_t  *ep_ids = nullptr, *ep_counts = nullptr;
+    uint32_t *ep_state = nullptr;
+    // what the owners hold from this rank's last dispatch (gate and up of a layer share it)
+    struct { const void *src1 = nullptr, *src1_id = nullptr, *ids = nullptr, *ids_id = nullptr; uint64_t gen = 0; int64_t ne[4] = {0, 0, 0, 0};
+             size_t nb[4] = {0, 0, 0, 0}; uint64_t private_gen = 0; } ep_sent;
 };
 
 struct PeerArArgs {
@@ -191,9 +204,27 @@ static void peer_ar_setup(b200q_ctx *ctx, TpState *tp, Nccl *api) {
     if (!all_mapped) peer_ar_close(ctx, tp);
 }
 
+static void ep_close(b200q_ctx *ctx, TpState *tp) {
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (int p = 0; p < tp->nranks && p < EP_MAX_RANKS; ++p)
+        if (p != tp->rank && tp->ep_peer[p]) cudaIpcCloseMemHandle(tp->ep_peer[p]);
+    for (int p = 0; p < EP_MAX_RANKS; ++p) tp->ep_peer[p] = nullptr;
+    if (tp->ep_local) cudaFree(tp->ep_local);
+    if (tp->ep_out) cudaFree(tp->ep_out);
+    if (tp->ep_ids) cudaFree(tp->ep_ids);
+    if (tp->ep_state) cudaFree(tp->ep_state);
+    tp->ep_local = nullptr;
+    tp->ep_out = nullptr;
+    tp->ep_ids = nullptr;
+    tp->ep_state = nullptr;
+    tp->ep_ok = false;
+}
+
 void tp_free(b200q_ctx *ctx) {
     TpState *tp = (TpState *)ctx->tp;
     if (!tp) return;
+    ep_close(ctx, tp);
     peer_ar_close(ctx, tp);
     Nccl *api = nccl_api(nullptr);
     if (api && tp->comm && api->CommDestroy) api->CommDestroy(tp->comm);
@@ -333,6 +364,83 @@ b200q_status b200q_all_to_all_v(b200q_ctx *ctx, const void *dev_send, const size
     return B200Q_OK;
 }
 
+// Collective: every rank calls it with the same bounds, before its expert-parallel products (and again when the
+// bounds grow): the largest number of (token, expert) pairs one rank brings to a call, and the longest
+// activation and result rows. It allocates the symmetric regions of ep_peer.cuh, exchanges their cudaIpc
+// handles through one NCCL all-gather and maps the peers' regions. After it, b200q_mul_mat_id_ep runs without
+// any host synchronisation; without it (or when a mapping was refused) the call uses NCCL send/receive.
+b200q_status b200q_ep_reserve(b200q_ctx *ctx, int64_t max_pairs, int64_t max_k, int64_t max_m) {
+    TpState *tp;
+    Nccl *api;
+    b200q_status st = tp_get(ctx, &tp, &api);
+    if (st != B200Q_OK) return st;
+    if (max_pairs <= 0 || max_k <= 0 || max_m <= 0 || max_k % 4 || max_m % 4) return fail(ctx, B200Q_INVALID, "ep_reserve bounds");
+    const int G = tp->nranks;
+    const char *off = getenv("B200Q_NO_PEER_EP");
+    if ((off && off[0] == '1') || G < 2 || G > EP_MAX_RANKS) return B200Q_OK;        // stays on NCCL
+    if (tp->ep_ok && max_pairs <= tp->ep_cap && max_k <= tp->ep_k && max_m <= tp->ep_m) return B200Q_OK;
+    B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+    ep_close(ctx, tp);
+    const int64_t cap = (max_pairs + 3) / 4 * 4;
+    const size_t x_bytes = (size_t)G * cap * max_k * 4, e_bytes = (size_t)G * cap * 4, y_bytes = (size_t)G * cap * max_m * 4;
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    tp->ep_off_e = up(x_bytes);
+    tp->ep_off_y = tp->ep_off_e + up(e_bytes);
+    tp->ep_off_flags = tp->ep_off_y + up(y_bytes);
+    const size_t total = tp->ep_off_flags + 4 * 2 * EP_MAX_RANKS * 8;
+    bool mine = cudaMalloc(&tp->ep_local, total) == cudaSuccess &&
+                cudaMemset(tp->ep_local + tp->ep_off_flags, 0, total - tp->ep_off_flags) == cudaSuccess &&
+                cudaMalloc(&tp->ep_out, (size_t)G * cap * max_m * 4) == cudaSuccess &&
+                cudaMalloc(&tp->ep_ids, ((size_t)G * cap + EP_MAX_RANKS) * 4) == cudaSuccess &&
+                cudaMalloc(&tp->ep_state, 4 * sizeof(uint32_t)) == cudaSuccess &&
+                cudaMemset(tp->ep_state, 0, 4 * sizeof(uint32_t)) == cudaSuccess;
+    if (!mine) cudaGetLastError();
+    tp->ep_counts = tp->ep_ids ? tp->ep_ids + (size_t)G * cap : nullptr;
+    cudaIpcMemHandle_t h;
+    memset(&h, 0, sizeof(h));
+    if (mine) mine = cudaIpcGetMemHandle(&h, tp->ep_local) == cudaSuccess;
+    constexpr size_t REC = 80;
+    std::vector<uint8_t> all(REC * G), rec(REC, 0);
+    memcpy(rec.data(), &h, 64);
+    rec[64] = mine ? 1 : 0;
+    uint8_t *d = nullptr;
+    bool ok = cudaMalloc(&d, REC * (G + 1)) == cudaSuccess;
+    auto gather = [&]() {
+        return ok && cudaMemcpyAsync(d + REC * G, rec.data(), REC, cudaMemcpyHostToDevice, ctx->stream) == cudaSuccess &&
+               api->AllGather(d + REC * G, d, REC, ncclInt8, tp->comm, ctx->stream) == ncclSuccess &&
+               cudaMemcpyAsync(all.data(), d, REC * G, cudaMemcpyDeviceToHost, ctx->stream) == cudaSuccess &&
+               cudaStreamSynchronize(ctx->stream) == cudaSuccess;
+    };
+    bool agreed = gather();
+    for (int p = 0; agreed && p < G; ++p) agreed = all[REC * p + 64] == 1;
+    bool mapped = agreed;
+    if (agreed) {
+        for (int p = 0; p < G && mapped; ++p) {
+            if (p == tp->rank) { tp->ep_peer[p] = tp->ep_local; continue; }
+            cudaIpcMemHandle_t hp;
+            memcpy(&hp, all.data() + REC * p, 64);
+            void *ptr = nullptr;
+            mapped = cudaIpcOpenMemHandle(&ptr, hp, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+            tp->ep_peer[p] = (uint8_t *)ptr;
+        }
+        if (!mapped) cudaGetLastError();
+    }
+    rec[64] = mapped ? 1 : 0;
+    bool all_mapped = gather();
+    for (int p = 0; all_mapped && p < G; ++p) all_mapped = all[REC * p + 64] == 1;
+    if (d) cudaFree(d);
+    if (!all_mapped) {
+        ep_close(ctx, tp);
+        return B200Q_OK;                                                       // every rank stays on NCCL
+    }
+    tp->ep_ok = true;
+    tp->ep_cap = cap;
+    tp->ep_k = max_k;
+    tp->ep_m = max_m;
+    tp->ep_sent.src1 = nullptr;
+    return B200Q_OK;
+}
+
 // Expert-parallel MUL_MAT_ID. Every rank holds its own tokens (src1 [K, ne11, n_tok], ids [n_used, n_tok]
 // with GLOBAL expert ids, dst [M, n_used, n_tok]) and the experts [rank * n_local, (rank + 1) * n_local)
 // as src0 [K, M, n_local]; n_expert_total = n_local * nranks. The call routes the local pairs by owner,
@@ -368,6 +476,96 @@ b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local,
     // 1. route by global expert (which groups by owner) and count pairs per owner
     RouteView rv;
     if ((st = moe_route(ctx, ids, n_expert_total, &rv, n_local)) != B200Q_OK) return st;
+    // device-initiated exchange over peer memory when the regions are reserved and this call fits them
+    if (tp->ep_ok && n_pairs <= tp->ep_cap && K <= tp->ep_k && M <= tp->ep_m && K % 4 == 0 && M % 4 == 0 &&
+        (uintptr_t)dst->data % 16 == 0 && dst->nb[1] % 16 == 0 && dst->nb[2] % 16 == 0 && G <= EP_MAX_RANKS) {
+        EpLayout L;
+        L.cap = tp->ep_cap;
+        L.K = K;
+        L.M = M;
+        L.off_e = tp->ep_off_e;
+        L.off_y = tp->ep_off_y;
+        L.off_flags = tp->ep_off_flags;
+        L.G = G;
+        L.rank = tp->rank;
+        for (int p = 0; p < EP_MAX_RANKS; ++p) L.base[p] = tp->ep_peer[p];
+        // B200Q_EP_TRACE=1: time the phases of this call with events and print them (synchronizes: debugging only)
+        static const bool trace = [] { const char *v = getenv("B200Q_EP_TRACE"); return v && v[0] == '1'; }();
+        cudaEvent_t ev[6] = {};
+        int nev = 0;
+        auto mark = [&]() { if (trace && nev < 6) { cudaEventCreate(&ev[nev]); cudaEventRecord(ev[nev], ctx->stream); ++nev; } };
+        mark();
+        // persistent copy kernels: eight rows per block at a time, at most four blocks per SM
+        auto copy_blocks = [&](int64_t rows) {
+            int64_t b = (rows + 7) / 8;
+            const int64_t cap_b = (int64_t)ctx->sm_count * 4;
+            return (unsigned)(b < 1 ? 1 : b > cap_b ? cap_b : b);
+        };
+        auto &sent = tp->ep_sent;
+        bool cached = sent.src1 == src1->data && sent.src1_id == src1->id && sent.ids == ids->data && sent.ids_id == ids->id &&
+                      sent.gen == ctx->generation;
+        for (int i = 0; i < 4 && cached; ++i) cached = sent.ne[i] == src1->ne[i] && sent.nb[i] == src1->nb[i];
+        if (!cached) {
+            ep_dispatch_kernel<<<copy_blocks(n_pairs), EP_COPY_THREADS, 0, ctx->stream>>>(
+                (const uint8_t *)src1->data, src1->nb[1], src1->nb[2], (int)src1->ne[1], (const uint8_t *)ids->data, ids->nb[1], n_used,
+                n_pairs, n_expert_total, n_local, rv.pairs, rv.owner_counts, L, tp->ep_state);
+            B200Q_CUDA(ctx, cudaGetLastError());
+            ep_wait_build_kernel<<<1, 256, 0, ctx->stream>>>(L, tp->ep_state, tp->ep_ids, tp->ep_counts, ctx->error_word);
+            B200Q_CUDA(ctx, cudaGetLastError());
+            sent.src1 = src1->data; sent.src1_id = src1->id; sent.ids = ids->data; sent.ids_id = ids->id; sent.gen = ctx->generation;
+            for (int i = 0; i < 4; ++i) { sent.ne[i] = src1->ne[i]; sent.nb[i] = src1->nb[i]; }
+            sent.private_gen = (1ull << 62) + ++ctx->private_generation;
+            count(ctx, ST_EP_DISPATCH);
+        } else {
+            count(ctx, ST_EP_DISPATCH_CACHED);
+        }
+        mark();
+        // the local experts over all slots: slot = one token with one used expert (-1: empty, skipped by the route)
+        const int64_t slots = (int64_t)G * L.cap;
+        b200q_tensor x1, id1, y1;
+        x1.id = id1.id = y1.id = nullptr;
+        x1.type = B200Q_TYPE_F32; x1.data = tp->ep_local;
+        x1.ne[0] = K; x1.ne[1] = 1; x1.ne[2] = slots; x1.ne[3] = 1;
+        x1.nb[0] = 4; x1.nb[1] = (size_t)K * 4; x1.nb[2] = (size_t)K * 4; x1.nb[3] = (size_t)K * 4 * slots;
+        id1.type = B200Q_TYPE_I32; id1.data = tp->ep_ids;
+        id1.ne[0] = 1; id1.ne[1] = slots; id1.ne[2] = 1; id1.ne[3] = 1;
+        id1.nb[0] = 4; id1.nb[1] = 4; id1.nb[2] = 4 * (size_t)slots; id1.nb[3] = 4 * (size_t)slots;
+        y1.type = B200Q_TYPE_F32; y1.data = tp->ep_out;
+        y1.ne[0] = M; y1.ne[1] = 1; y1.ne[2] = slots; y1.ne[3] = 1;
+        y1.nb[0] = 4; y1.nb[1] = (size_t)M * 4; y1.nb[2] = (size_t)M * 4; y1.nb[3] = (size_t)M * 4 * slots;
+        // The regions are refilled by the next dispatch, so what the local product caches about them lives under a
+        // private generation: a new one per dispatch, the same one for the calls that share a dispatch (their
+        // route and gathered activation are reused).
+        const uint64_t caller_gen = ctx->generation;
+        ctx->generation = sent.private_gen;
+        ctx->route_pinned = rv.slot;
+        ctx->route_skip_negative = true;
+        st = b200q_mul_mat_id(ctx, src0_local, &x1, &id1, &y1);
+        ctx->route_skip_negative = false;
+        ctx->route_pinned = -1;
+        ctx->generation = caller_gen;
+        if (st != B200Q_OK) return st;
+        mark();
+        ep_combine_kernel<<<copy_blocks(slots), EP_COPY_THREADS, 0, ctx->stream>>>(tp->ep_out, tp->ep_counts, L, tp->ep_state);
+        B200Q_CUDA(ctx, cudaGetLastError());
+        mark();
+        ep_unpack_kernel2<<<copy_blocks(n_pairs), EP_COPY_THREADS, 0, ctx->stream>>>(rv.pairs, rv.owner_counts, n_pairs, n_used, (float *)dst->data,
+                                                           (int64_t)(dst->nb[1] / 4), (int64_t)(dst->nb[2] / 4), L, tp->ep_state,
+                                                           ctx->error_word);
+        B200Q_CUDA(ctx, cudaGetLastError());
+        mark();
+        if (trace && !ctx->capturing) {
+            cudaStreamSynchronize(ctx->stream);
+            float ms[4] = {0, 0, 0, 0};
+            for (int i = 0; i + 1 < nev; ++i) cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1]);
+            fprintf(stderr, "ep_trace rank %d M=%lld K=%lld pairs=%d%s: dispatch+wait %.3f product %.3f combine %.3f unpack %.3f ms\n", tp->rank,
+                    (long long)M, (long long)K, n_pairs, cached ? " (dispatch cached)" : "", ms[0], ms[1], ms[2], ms[3]);
+        }
+        for (int i = 0; i < nev; ++i) cudaEventDestroy(ev[i]);
+        count(ctx, ST_EP_PEER);
+        count(ctx, ST_EP_COMBINE);
+        return B200Q_OK;
+    }
     // 2. everyone learns everyone's counts
     if ((st = ws_reserve(ctx, &ctx->moe_ws[0], sizeof(int32_t) * (size_t)G * G)) != B200Q_OK) return st;
     int32_t *all_counts = (int32_t *)ctx->moe_ws[0].ptr;

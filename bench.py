@@ -383,6 +383,9 @@ def moe_section(ctx, world, rank, dist):
             m, k, _, dw, rb = mats[name]
             return A.Tensor.make(t, [k, m, per, 1], [A.block_bytes(t), rb, rb * m, rb * m * per], dw)
 
+        if world > 1:
+            ctx.ep_reserve(n_tok * n_used, d_model, d_model)        # collective; maps the peer regions (no-op when refused)
+
         def block():
             # gate and up read the token's activation (ne11 = 1), down reads one row per used expert
             ctx.graph_begin()
@@ -408,12 +411,14 @@ def moe_section(ctx, world, rank, dist):
                 raise SystemExit("bench: MoE parity check failed on rank %d (max rel err %.3e)" % (rank, err))
         reps = 5
         g = None
-        if world == 1:                                    # the expert-parallel call synchronizes: not capturable
+        peer_ep = world > 1 and ctx.stats().get("ep_peer", 0) > 0
+        if world == 1 or peer_ep:                         # over NCCL the expert-parallel call synchronizes: not capturable
             g = ctx.capture(lambda: [block() for _ in range(reps)])
             ctx.graph_launch(g)
         ctx.sync()
         if dist:
             dist.barrier()
+        g_used = g is not None
         ctx.timer_start()
         if g is not None:
             for _ in range(3):
@@ -431,7 +436,8 @@ def moe_section(ctx, world, rank, dist):
                     "ms": ms, "tokens_per_s": tokens / (ms * 1e-3), "tops": ops / (ms * 1e-3) / 1e12,
                     "parallelism": ("ep%d: %d experts per GPU, all-to-all dispatch/combine" % (world, per)) if world > 1 else "single GPU",
                     "parity_max_rel_err": err,
-                    "timed": "gate + up + down MUL_MAT_ID" + (", CUDA-graph replay" if world == 1 else ", eager (one host synchronisation per call)")})
+                    "timed": "gate + up + down MUL_MAT_ID" + (", CUDA-graph replay" if g_used else ", eager (one host synchronisation per call)"),
+                    "exchange": "none" if world == 1 else ("own kernels over peer memory" if peer_ep else "NCCL send/receive")})
         for ptr in (dxi, dh, di, dg, dd):
             ctx.free(ptr)
     for m, k, base, dw, rb in mats.values():

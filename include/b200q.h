@@ -155,10 +155,17 @@ B200Q_API b200q_status b200q_all_to_all_v(b200q_ctx *ctx, const void *dev_send, 
                                           const size_t *recv_bytes);
 /* MUL_MAT_ID with the experts split over the ranks: src0_local holds this rank's experts
  * [K, M, n_expert_total / nranks]; src1, ids (global expert ids) and dst are this rank's tokens.
- * Dispatch and combine are all-to-alls; the call synchronizes the stream once (the exchange sizes
- * must reach the host). */
+ * After b200q_ep_reserve dispatch and combine are the library's own kernels over peer memory; otherwise they are
+ * NCCL all-to-alls and the call synchronizes the stream once (the exchange sizes must reach the host).
+ * Every rank must make the same sequence of calls (the ranks wait for one another inside them). */
 B200Q_API b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local, const b200q_tensor *src1,
                                            const b200q_tensor *ids, b200q_tensor *dst, int n_expert_total);
+/* Collective (every rank, same arguments): reserves and maps, on every rank, the regions of peer memory that let
+ * b200q_mul_mat_id_ep dispatch and combine from its own kernels, with no host synchronisation, so that the call
+ * can be captured in a CUDA graph. max_pairs: the most (token, expert) pairs one rank brings to a call;
+ * max_k / max_m: the longest activation / result rows (multiples of 4). Calls beyond the reserved bounds, and
+ * every call when the mapping was refused or B200Q_NO_PEER_EP=1 is set, take the NCCL send/receive route. */
+B200Q_API b200q_status b200q_ep_reserve(b200q_ctx *ctx, int64_t max_pairs, int64_t max_k, int64_t max_m);
 B200Q_API b200q_status b200q_tp_check(b200q_ctx *ctx);
 
 /* ggml backend buffer interface (buffer alloc, set_tensor, get_tensor, synchronize):

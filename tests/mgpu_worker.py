@@ -111,29 +111,51 @@ def main():
     # expert parallelism: 8 experts split over the ranks, every rank brings its own tokens (a different
     # count per rank) with global expert ids; against the oracle's MUL_MAT_ID over all experts
     ep_errs = []
-    for t, m, k, n_tok, ne11 in ((A.Q4_K, 192, 512, 5 + 3 * rank, 1), (A.Q4_0, 96, 256, 37 + rank, 2), (A.Q6_K, 64, 256, 1, 1)):
-        n_exp, n_used = 4 * world, 2
-        per = n_exp // world
-        w = np.stack([O.quantize(t, O.fill_normal(m * k, 500 + 10 * t + e, 0.05).reshape(m, k)) for e in range(n_exp)])
-        x = O.fill_normal(n_tok * ne11 * k, 600 + rank, 1.0).reshape(n_tok, ne11, k)
-        ids = O.route_ids(n_used, n_tok, n_exp, 700 + rank)
-        dw = ctx.upload(np.ascontiguousarray(w[rank * per:(rank + 1) * per]))
-        dx, di, dy = ctx.upload(x), ctx.upload(ids), ctx.alloc(n_tok * n_used * m * 4)
-        rb = w.shape[-1]
-        src0 = A.Tensor.make(t, [k, m, per, 1], [A.block_bytes(t), rb, rb * m, rb * m * per], dw)
-        ctx.mul_mat_id_ep(src0, A.Tensor.f32(dx, [k, ne11, n_tok]), A.Tensor.make(A.I32, [n_used, n_tok, 1, 1], [4, 4 * n_used], di),
-                          A.Tensor.f32(dy, [m, n_used, n_tok]), n_exp)
-        got = ctx.download(dy, (n_tok, n_used, m), np.float32)
-        ep_errs.append(rel_err(got.reshape(-1, m), O.mul_mat_id(t, w, m, k, x, ids, f64=True).reshape(-1, m)))
-        assert ep_errs[-1] < TOL, ("expert parallel", t, ep_errs[-1])
+    cases = ((A.Q4_K, 192, 512, 5 + 3 * rank, 1), (A.Q4_0, 96, 256, 37 + rank, 2), (A.Q6_K, 64, 256, 1, 1),
+             (A.Q4_K, 128, 1024, 150 + 7 * rank, 1))
+    for mode in ("nccl", "peer"):
+        if mode == "peer":
+            # collective, same bounds on every rank: the largest pair count, the longest rows
+            ctx.ep_reserve(2 * (150 + 7 * (world - 1)), 1024, 192)
+        for t, m, k, n_tok, ne11 in cases:
+            n_exp, n_used = 4 * world, 2
+            per = n_exp // world
+            w = np.stack([O.quantize(t, O.fill_normal(m * k, 500 + 10 * t + e, 0.05).reshape(m, k)) for e in range(n_exp)])
+            x = O.fill_normal(n_tok * ne11 * k, 600 + rank, 1.0).reshape(n_tok, ne11, k)
+            ids = O.route_ids(n_used, n_tok, n_exp, 700 + rank)
+            dw = ctx.upload(np.ascontiguousarray(w[rank * per:(rank + 1) * per]))
+            dx, di, dy = ctx.upload(x), ctx.upload(ids), ctx.alloc(n_tok * n_used * m * 4)
+            rb = w.shape[-1]
+            src0 = A.Tensor.make(t, [k, m, per, 1], [A.block_bytes(t), rb, rb * m, rb * m * per], dw)
+            X, I = A.Tensor.f32(dx, [k, ne11, n_tok]), A.Tensor.make(A.I32, [n_used, n_tok, 1, 1], [4, 4 * n_used], di)
+            Y = A.Tensor.f32(dy, [m, n_used, n_tok])
+            want = O.mul_mat_id(t, w, m, k, x, ids, f64=True).reshape(-1, m)
+            ctx.graph_begin()
+            for rep in range(2):          # twice in one graph generation: the second finds the dispatch done (gate, up)
+                ctx.upload(np.zeros((n_tok, n_used, m), dtype=np.float32), dy)
+                ctx.mul_mat_id_ep(src0, X, I, Y, n_exp)
+                got = ctx.download(dy, (n_tok, n_used, m), np.float32)
+                ep_errs.append(rel_err(got.reshape(-1, m), want))
+                assert ep_errs[-1] < TOL, ("expert parallel", mode, t, rep, ep_errs[-1])
+            for ptr in (dw, dx, di, dy):
+                ctx.free(ptr)
+        dist.barrier()
+    ep_stats = ctx.stats()
+    peer_ep = ep_stats.get("ep_peer", 0)
+    # when the peer regions could be mapped every call of the second round went through them, half of them
+    # on a cached dispatch
+    assert peer_ep in (0, 2 * len(cases)), ep_stats
+    if peer_ep:
+        assert ep_stats.get("ep_dispatch_cached") == len(cases), ep_stats
+    ctx.sync()
 
     st = ctx.stats()
-    assert st.get("tp_allgather") == 1 and st.get("tp_allreduce") == 2 + 5 + 3 and st.get("gemm_tc") == 1, st
+    assert st.get("tp_allgather") == 1 and st.get("tp_allreduce") == 2 + 5 + 3 and st.get("gemm_tc", 0) >= 1, st
     # the decode-sized all-reduces went over peer memory unless the mapping was refused or switched off
     assert peer_used in (0, st.get("tp_allreduce")) or os.environ.get("B200Q_NO_PEER_AR") == "1", st
     dist.barrier()
     print("MGPU_OK rank %d/%d colsplit %.2e rowsplit %s ep %s peer_allreduce %d" % (rank, world, e1, ["%.2e" % e for e in errs],
-                                                                                       ["%.2e" % e for e in ep_errs], peer_used), flush=True)
+                                                                                       ["%.2e" % max(ep_errs)], peer_used) + " peer_ep %d" % peer_ep, flush=True)
     ctx.close()
     dist.destroy_process_group()
 
