@@ -130,6 +130,8 @@ def lib():
     L.b200q_tp_check.argtypes = [vp]
     L.b200q_mul_mat_id_ep.argtypes = [vp, TP, TP, TP, TP, C.c_int]
     L.b200q_ep_reserve.argtypes = [vp, C.c_int64, C.c_int64, C.c_int64]
+    L.b200q_moe_router.argtypes = [vp, TP, C.c_int, C.c_float, C.c_float, TP, TP]
+    L.b200q_moe_ffn.argtypes = [vp, TP, TP, TP, TP, TP, C.c_int, C.c_float, C.c_float, TP, TP, TP]
     L.b200q_mul_mat_noalloc.argtypes = [C.c_int, vp, TP, TP, TP]
     L.b200q_noalloc_last_error.restype = C.c_char_p
     L.b200q_noalloc_device_error.argtypes = [C.c_int, C.POINTER(C.c_int)]
@@ -161,7 +163,7 @@ EXPORTS = [
     "b200q_init", "b200q_free", "b200q_last_error", "b200q_get_stream", "b200q_version", "b200q_supports", "b200q_mul_mat",
     "b200q_mul_mat_id", "b200q_graph_begin", "b200q_capture_begin", "b200q_capture_end", "b200q_graph_launch",
     "b200q_graph_free", "b200q_tp_unique_id", "b200q_tp_init", "b200q_tp_rank", "b200q_tp_shard", "b200q_all_reduce_f32",
-    "b200q_all_gather", "b200q_all_to_all_v", "b200q_tp_check", "b200q_mul_mat_id_ep", "b200q_ep_reserve", "b200q_mul_mat_noalloc", "b200q_noalloc_last_error", "b200q_noalloc_device_error", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
+    "b200q_all_gather", "b200q_all_to_all_v", "b200q_tp_check", "b200q_mul_mat_id_ep", "b200q_ep_reserve", "b200q_moe_router", "b200q_moe_ffn", "b200q_mul_mat_noalloc", "b200q_noalloc_last_error", "b200q_noalloc_device_error", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
     "b200q_tensor_get", "b200q_tensor_stage", "b200q_tensor_fetch", "b200q_tensor_copy", "b200q_synchronize", "b200q_host_alloc", "b200q_host_free",
     "b200q_stats", "b200q_stats_reset", "b200q_timer_start", "b200q_timer_stop", "b200q_flush_l2",
     "b200q_debug_quantize_act", "b200q_debug_dequantize", "b200q_debug_wait_timeout",
@@ -303,6 +305,12 @@ class Context:
         self.check(self.L.b200q_mul_mat_id_ep(self.h, src0_local, src1, ids, dst, n_expert_total))
 
     # ---- CUDA graphs ----
+    def moe_router(self, logits, n_used, cmin, cmax, ids, weights):
+        self.check(self.L.b200q_moe_router(self.h, logits, n_used, cmin, cmax, ids, weights))
+
+    def moe_ffn(self, gate_w, up_w, down_w, x, logits, n_used, cmin, cmax, y, ids_out=None, weights_out=None):
+        self.check(self.L.b200q_moe_ffn(self.h, gate_w, up_w, down_w, x, logits, n_used, cmin, cmax, y, ids_out, weights_out))
+
     def ep_reserve(self, max_pairs, max_k, max_m):
         self.check(self.L.b200q_ep_reserve(self.h, max_pairs, max_k, max_m))
 

@@ -42,7 +42,7 @@ const char *stat_name(int s) {
     }
     static const char *rest[] = { "gemv_id", "gemv_id_unaligned", "moe_route", "route_cache_hit", "moe_gemm", "moe_pack",
                                   "gemm_tc", "gemm_tc_quantize", "gemm_fallback_shape", "tp_allreduce", "tp_allgather",
-                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins", "gemv_stream", "tp_allreduce_peer", "gemm_tc_f16", "ep_peer", "ep_dispatch_cached" };
+                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins", "gemv_stream", "tp_allreduce_peer", "gemm_tc_f16", "ep_peer", "ep_dispatch_cached", "moe_router", "moe_ffn", "gemv_knob_ignored" };
     return rest[s - ST_GEMV_ID];
 }
 
@@ -259,6 +259,11 @@ b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
     ctx->no_pdl = no_pdl && no_pdl[0] == '1';
     const char *tc_i8 = getenv("B200Q_TC_I8");           // the int8 arm of the per-32 prompt GEMM (comparisons)
     ctx->tc_f16 = !(tc_i8 && tc_i8[0] == '1');
+    // tile knobs for the tuner (arcint_b200/tune.py): each is validated where it is used, a value the kernels do
+    // not take falls back to the default and is counted as "gemv_knob_ignored"
+    if (const char *v = getenv("B200Q_GEMV_ROWS")) ctx->gemv_rows = atoi(v);
+    if (const char *v = getenv("B200Q_GEMV_BLOCK_WARPS")) ctx->gemv_block_warps = atoi(v);
+    if (const char *v = getenv("B200Q_GEMV_STREAM_MASK")) ctx->gemv_stream_mask = (int)strtol(v, nullptr, 0);
     const char *no_stream = getenv("B200Q_NO_STREAM");   // the older GEMV kernel for every shape (comparisons)
     ctx->no_stream = no_stream && no_stream[0] == '1';
     *out = ctx;

@@ -92,7 +92,7 @@ enum Stat {
     ST_GEMV_UNALIGNED_COL0 = ST_GEMV_COL0 + 9,    // + ncols
     ST_GEMV_ID = ST_GEMV_UNALIGNED_COL0 + 9, ST_GEMV_ID_UNALIGNED, ST_MOE_ROUTE, ST_ROUTE_CACHE_HIT, ST_MOE_GEMM,
     ST_MOE_PACK, ST_GEMM_TC, ST_GEMM_TC_QUANT, ST_GEMM_FALLBACK_SHAPE, ST_TP_ALLREDUCE, ST_TP_ALLGATHER,
-    ST_EP_DISPATCH, ST_EP_COMBINE, ST_GRAPH_LAUNCH, ST_NO_ALLOC, ST_GEMM_KQ_MINS, ST_GEMV_STREAM, ST_TP_ALLREDUCE_PEER, ST_GEMM_TC_F16, ST_EP_PEER, ST_EP_DISPATCH_CACHED,
+    ST_EP_DISPATCH, ST_EP_COMBINE, ST_GRAPH_LAUNCH, ST_NO_ALLOC, ST_GEMM_KQ_MINS, ST_GEMV_STREAM, ST_TP_ALLREDUCE_PEER, ST_GEMM_TC_F16, ST_EP_PEER, ST_EP_DISPATCH_CACHED, ST_MOE_ROUTER, ST_MOE_FFN, ST_GEMV_KNOB_IGNORED,
     ST_COUNT
 };
 const char *stat_name(int s);
@@ -118,6 +118,9 @@ struct b200q_ctx {
     bool         no_tc = false;           // B200Q_NO_TC=1: never take the tensor-core GEMM
     bool         no_pdl = false;          // B200Q_NO_PDL=1: plain stream order between the decode kernels
     bool         tc_f16 = true;           // B200Q_TC_I8=1: the per-32 prompt GEMM on the int8 MMA instead of exact fp16 operands
+    // decode GEMV tile knobs (read once from the environment; 0 / -1: the measured defaults): rows per ring stage,
+    // warps per block, and which column counts take the slice-resident kernel (bit c = c columns)
+    int          gemv_rows = 0, gemv_block_warps = 0, gemv_stream_mask = -1;
     bool         no_stream = false;       // B200Q_NO_STREAM=1: every GEMV through the per-warp ring kernel (comparisons)
     std::string  last_error;
     std::string  stats_text;
@@ -126,7 +129,7 @@ struct b200q_ctx {
     std::vector<b200q::ActEntry> act_cache;
     size_t       act_next = 0;
     b200q::Workspace flush_buf;
-    b200q::Workspace moe_ws[8];
+    b200q::Workspace moe_ws[10];
     b200q::RouteEntry *routes[2] = { nullptr, nullptr };
     size_t       route_next = 0;
     cudaEvent_t  ev0 = nullptr, ev1 = nullptr;

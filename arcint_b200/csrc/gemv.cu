@@ -66,7 +66,13 @@ static bool try_launch_stream(b200q_ctx *ctx, const void *w, size_t row_stride, 
     const int row_bytes = nblk * F::BLK_B;
     const size_t gb = (gemv_stream_group_smem(row_bytes, R, NSETS, nw) + 15) / 16 * 16;
     if (gb > 200 * 1024) return false;
-    int groups = 4 / nw < 1 ? 1 : 4 / nw;                  // blocks of about four warps measured best
+    int target_warps = 4;                                  // blocks of about four warps measured best
+    if (ctx->gemv_block_warps) {
+        if (ctx->gemv_block_warps >= 1 && ctx->gemv_block_warps <= GEMV_STREAM_MAX_THREADS / 32) target_warps = ctx->gemv_block_warps;
+        else count(ctx, ST_GEMV_KNOB_IGNORED);
+    }
+    int groups = target_warps / nw < 1 ? 1 : target_warps / nw;
+    if (groups * nw > GEMV_STREAM_MAX_THREADS / 32) groups = (GEMV_STREAM_MAX_THREADS / 32) / nw;
     while (groups > 1 && groups * gb > 200 * 1024) --groups;
     const size_t smem = groups * gb;
     const int threads = groups * nw * 32;
@@ -117,12 +123,15 @@ static b200q_status launch_nc(b200q_ctx *ctx, const void *w, size_t row_stride, 
     // rows per warp batch: four; eight for three or four columns of a small-block type, where
     // the activation registers are worth sharing further (measured on B200)
     constexpr bool wide = (NC == 3 || NC == 4) && GemvStage<TYPE>::BYTES <= 1152;
-    if (aligned && !ctx->no_stream && M <= INT32_MAX / 2 && ldd <= INT32_MAX && stream_preferred<TYPE, NC>()) {
+    const bool want_stream = ctx->gemv_stream_mask >= 0 ? ((ctx->gemv_stream_mask >> NC) & 1) != 0 : stream_preferred<TYPE, NC>();
+    if (aligned && !ctx->no_stream && M <= INT32_MAX / 2 && ldd <= INT32_MAX && want_stream) {
         typedef GemvFmt<TYPE> F;
         const int row_bytes = (int)(K / F::BLK_W) * F::BLK_B;
         // rows per ring stage: four, two when a stage of four long rows would crowd shared memory or a
         // single column leaves little work per row
-        const bool two = NC == 1 || (size_t)12 * gemv_stream_slot(row_bytes) > 36 * 1024;
+        bool two = NC == 1 || (size_t)12 * gemv_stream_slot(row_bytes) > 36 * 1024;
+        if (ctx->gemv_rows == 2 || ctx->gemv_rows == 4) two = ctx->gemv_rows == 2;
+        else if (ctx->gemv_rows) count(ctx, ST_GEMV_KNOB_IGNORED);
         b200q_status st = B200Q_OK;
         const bool took = two ? try_launch_stream<TYPE, NC, 2>(ctx, w, row_stride, M, K, act, dst, ldd, &st)
                               : try_launch_stream<TYPE, NC, 4>(ctx, w, row_stride, M, K, act, dst, ldd, &st);

@@ -110,6 +110,22 @@ B200Q_API b200q_status b200q_mul_mat_id(b200q_ctx *ctx, const b200q_tensor *src0
                                         const b200q_tensor *src1, const b200q_tensor *ids,
                                         b200q_tensor *dst);
 
+/* The steps either side of MUL_MAT_ID in a mixture-of-experts feed-forward block.
+ * b200q_moe_router: the reference's fused router kernel_topk_moe_softmax_norm_n* (P09:928-987): per token, softmax over
+ * logits [n_expert, n_tok] f32, the n_used largest in descending order (ties: the lower expert id) into ids [n_used, n_tok]
+ * i32, and their probabilities divided by clamp(their sum, cmin, cmax) into weights [n_used, n_tok] f32. At most 1024
+ * experts and 32 used.
+ * b200q_moe_ffn: router, gate and up MUL_MAT_ID over x [d_model, n_tok] (one route, one gathered activation), SwiGLU
+ * h = silu(gate) * up, down MUL_MAT_ID over h, and y[:, t] = sum_i weights[i, t] * down[:, i, t] into y [d_model, n_tok],
+ * as one launch sequence on the context's stream (scratch from the context, no host synchronisation). gate_w, up_w:
+ * [d_model, d_ff, n_expert]; down_w: [d_ff, d_model, n_expert]. ids_out / weights_out may be NULL. The reference runs
+ * these as separate graph nodes (no matmul + GLU fusion on its Intel path, P01:65). */
+B200Q_API b200q_status b200q_moe_router(b200q_ctx *ctx, const b200q_tensor *logits, int n_used, float cmin, float cmax,
+                                        b200q_tensor *ids, b200q_tensor *weights);
+B200Q_API b200q_status b200q_moe_ffn(b200q_ctx *ctx, const b200q_tensor *gate_w, const b200q_tensor *up_w, const b200q_tensor *down_w,
+                                     const b200q_tensor *x, const b200q_tensor *logits, int n_used, float cmin, float cmax,
+                                     b200q_tensor *y, b200q_tensor *ids_out, b200q_tensor *weights_out);
+
 /* ggml_backend_opencl_graph_compute's generation bump (P01:609-611): starts a new
  * graph. Within one graph an activation tensor that feeds several products (q/k/v,
  * gate/up) is quantized once (P01:670-688) and a MoE route is computed once per ids

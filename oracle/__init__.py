@@ -238,3 +238,30 @@ def random_blocks(t, rows, k, rng):
     elif t == Q6_K:
         put_half(208, 1e-5, 5e-4)
     return raw.reshape(rows, nb * bb)
+
+
+def moe_router(logits, n_used, cmin, cmax):
+    """The MoE router as the reference's fused kernel computes it (kernel_topk_moe_softmax_norm_n*,
+    0000-09-moe-routing-gemm-tiles.patch:928-987): per token p = exp(x - max x), s = sum p, the n_used
+    largest p in descending order (ties: the lower expert id), w_j = p_j / s, then w_j / clamp(sum_j w_j,
+    cmin, cmax). logits: f32 [n_tok, n_expert] -> ids int32 [n_tok, n_used], weights f32 [n_tok, n_used]."""
+    x = np.asarray(logits, dtype=np.float32)
+    p = np.exp(x - x.max(axis=1, keepdims=True)).astype(np.float32)
+    s = p.sum(axis=1, dtype=np.float64).astype(np.float32)
+    order = np.argsort(-p, axis=1, kind="stable")[:, :n_used]          # stable: equal values keep the lower id first
+    w = (np.take_along_axis(p, order, axis=1) / s[:, None]).astype(np.float32)
+    denom = np.clip(w.sum(axis=1, dtype=np.float32), np.float32(cmin), np.float32(cmax))
+    return order.astype(np.int32), (w / denom[:, None]).astype(np.float32)
+
+
+def moe_ffn(t, gate_w, up_w, down_w, d_model, d_ff, x, logits, n_used, cmin, cmax):
+    """The feed-forward block around MUL_MAT_ID in fp64 on the library's quantized operands: router, gate and up
+    over x [n_tok, d_model], h = silu(gate) * up (rounded to f32, as the block hands it to the down projection),
+    down, and the weighted sum over the used experts -> (y [n_tok, d_model] f64, ids, weights)."""
+    ids, w = moe_router(logits, n_used, cmin, cmax)
+    x3 = np.ascontiguousarray(x, dtype=np.float32)[:, None, :]
+    g = mul_mat_id(t, gate_w, d_ff, d_model, x3, ids, f64=True)
+    u = mul_mat_id(t, up_w, d_ff, d_model, x3, ids, f64=True)
+    h = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+    d = mul_mat_id(t, down_w, d_model, d_ff, h, ids, f64=True)
+    return (d * w[:, :, None].astype(np.float64)).sum(axis=1), ids, w
