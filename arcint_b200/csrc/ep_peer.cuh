@@ -62,8 +62,14 @@ __device__ __forceinline__ uint64_t ep_load_flag(const uint64_t *p) {
     asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
-// bounded wait for a flag of this sequence number; false when the limit ran out
-__device__ __forceinline__ bool ep_wait_flag(const uint64_t *p, uint32_t seq, uint32_t *count) {
+// Bounded wait for a flag of this sequence number; false when it gave up: after EP_WAIT_NS, after the poll limit,
+// or at once when an earlier wait of this context already gave up (its error word is set) -- a peer that has gone
+// away costs the others two seconds once, not per flag and per kernel.
+constexpr unsigned long long EP_WAIT_NS = 2000000000ull;
+__device__ __forceinline__ bool ep_wait_flag(const uint64_t *p, uint32_t seq, uint32_t *count, const int *error_word) {
+    *count = 0;
+    if (error_word && *(volatile const int *)error_word) return false;
+    unsigned long long t0 = 0;
     for (uint32_t i = 0; i < EP_SPIN_LIMIT; ++i) {
         const uint64_t v = ep_load_flag(p);
         if ((uint32_t)(v >> 32) == seq) {
@@ -72,8 +78,13 @@ __device__ __forceinline__ bool ep_wait_flag(const uint64_t *p, uint32_t seq, ui
             return true;
         }
         if (i > 256) __nanosleep(100);
+        if ((i & 1023u) == 1023u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > EP_WAIT_NS) break;
+        }
     }
-    *count = 0;
     return false;
 }
 
@@ -134,7 +145,7 @@ ep_wait_build_kernel(EpLayout L, const uint32_t *state, int32_t *ids_local, int3
     __syncthreads();
     if ((int)threadIdx.x < L.G) {
         uint32_t c;
-        if (!ep_wait_flag(ep_flag(L, L.rank, 0, (int)(seq & 1u), threadIdx.x), seq, &c)) bad = 1;
+        if (!ep_wait_flag(ep_flag(L, L.rank, 0, (int)(seq & 1u), threadIdx.x), seq, &c, error_word)) bad = 1;
         cnt[threadIdx.x] = c > (uint32_t)L.cap ? (uint32_t)L.cap : c;
         counts[threadIdx.x] = (int32_t)cnt[threadIdx.x];
     }
@@ -187,7 +198,7 @@ ep_unpack_kernel2(const int32_t *pairs, const int32_t *owner_counts, int n_pairs
     __syncthreads();
     if ((int)threadIdx.x < L.G) {
         uint32_t c;
-        if (!ep_wait_flag(ep_flag(L, L.rank, 1, (int)(seq & 1u), threadIdx.x), seq, &c)) bad = 1;
+        if (!ep_wait_flag(ep_flag(L, L.rank, 1, (int)(seq & 1u), threadIdx.x), seq, &c, error_word)) bad = 1;
     }
     __syncthreads();
     if (!bad) {

@@ -30,6 +30,10 @@ namespace b200q {
 constexpr int      PEER_AR_MAX_RANKS = 8;
 constexpr int      PEER_AR_MAX_FLOATS = 64 * 1024;          // per all-reduce: 8 decode columns of 8192 rows
 constexpr uint32_t PEER_AR_SPIN_LIMIT = 1u << 22;
+// a wait on another GPU also ends after this long, and once one wait of a context has given up (its error word is
+// set) no later wait of that context spins at all: a peer that has gone away costs the others two seconds once,
+// not per element and per kernel
+constexpr unsigned long long PEER_WAIT_NS = 2000000000ull;
 
 // element e of rank r's slot in set s of a receive buffer (8-byte elements)
 B200Q_HD size_t peer_ar_index(int set, int r, int e) {
@@ -55,7 +59,20 @@ B200Q_HD float peer_ar_value(uint64_t w) {
 template <typename Load>
 B200Q_HD uint64_t peer_ar_wait(const uint64_t *slot, uint32_t seq, uint32_t limit, Load load, bool *ok) {
     uint64_t w = load(slot);
+#ifdef __CUDA_ARCH__
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0; (uint32_t)(w >> 32) != seq && i < limit && *ok; ++i) {
+        w = load(slot);
+        if ((i & 1023u) == 1023u) {                              // the clock every thousand polls
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > PEER_WAIT_NS) break;
+        }
+    }
+#else
     for (uint32_t i = 0; (uint32_t)(w >> 32) != seq && i < limit; ++i) w = load(slot);
+#endif
     if ((uint32_t)(w >> 32) != seq) *ok = false;
     return w;
 }

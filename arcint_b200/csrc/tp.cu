@@ -108,7 +108,8 @@ peer_allreduce_kernel(float *__restrict__ buf, int count, PeerArArgs a, uint32_t
             asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(a.peer[q] + peer_ar_index(set, a.rank, e)), "l"(w) : "memory");
         }
     }
-    bool ok = true;
+    // a context whose earlier wait gave up does not wait again (the host has not yet looked at the error word)
+    bool ok = !(error_word && *(volatile int *)error_word);
     auto load = [](const uint64_t *p) {
         uint64_t v;
         asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
