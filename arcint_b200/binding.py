@@ -126,6 +126,7 @@ def lib():
     L.b200q_tp_shard.argtypes = [C.c_int64, C.c_int64, C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
     L.b200q_all_reduce_f32.argtypes = [vp, vp, sz]
     L.b200q_all_gather.argtypes = [vp, vp, vp, sz]
+    L.b200q_mul_mat_allreduce.argtypes = [vp, TP, TP, TP]
     L.b200q_all_to_all_v.argtypes = [vp, vp, C.POINTER(sz), C.POINTER(sz), vp, C.POINTER(sz), C.POINTER(sz)]
     L.b200q_tp_check.argtypes = [vp]
     L.b200q_mul_mat_id_ep.argtypes = [vp, TP, TP, TP, TP, C.c_int]
@@ -163,7 +164,7 @@ EXPORTS = [
     "b200q_init", "b200q_free", "b200q_last_error", "b200q_get_stream", "b200q_version", "b200q_supports", "b200q_mul_mat",
     "b200q_mul_mat_id", "b200q_graph_begin", "b200q_capture_begin", "b200q_capture_end", "b200q_graph_launch",
     "b200q_graph_free", "b200q_tp_unique_id", "b200q_tp_init", "b200q_tp_rank", "b200q_tp_shard", "b200q_all_reduce_f32",
-    "b200q_all_gather", "b200q_all_to_all_v", "b200q_tp_check", "b200q_mul_mat_id_ep", "b200q_ep_reserve", "b200q_moe_router", "b200q_moe_ffn", "b200q_mul_mat_noalloc", "b200q_noalloc_last_error", "b200q_noalloc_device_error", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
+    "b200q_all_gather", "b200q_mul_mat_allreduce", "b200q_all_to_all_v", "b200q_tp_check", "b200q_mul_mat_id_ep", "b200q_ep_reserve", "b200q_moe_router", "b200q_moe_ffn", "b200q_mul_mat_noalloc", "b200q_noalloc_last_error", "b200q_noalloc_device_error", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
     "b200q_tensor_get", "b200q_tensor_stage", "b200q_tensor_fetch", "b200q_tensor_copy", "b200q_synchronize", "b200q_host_alloc", "b200q_host_free",
     "b200q_stats", "b200q_stats_reset", "b200q_timer_start", "b200q_timer_stop", "b200q_flush_l2",
     "b200q_debug_quantize_act", "b200q_debug_dequantize", "b200q_debug_wait_timeout",
@@ -292,6 +293,9 @@ class Context:
 
     def all_reduce_f32(self, dev, count):
         self.check(self.L.b200q_all_reduce_f32(self.h, dev, count))
+
+    def mul_mat_allreduce(self, src0, src1, dst):
+        self.check(self.L.b200q_mul_mat_allreduce(self.h, src0, src1, dst))
 
     def all_gather(self, send, recv, bytes_per_rank):
         self.check(self.L.b200q_all_gather(self.h, send, recv, bytes_per_rank))

@@ -42,7 +42,7 @@ const char *stat_name(int s) {
     }
     static const char *rest[] = { "gemv_id", "gemv_id_unaligned", "moe_route", "route_cache_hit", "moe_gemm", "moe_pack",
                                   "gemm_tc", "gemm_tc_quantize", "gemm_fallback_shape", "tp_allreduce", "tp_allgather",
-                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins", "gemv_stream", "tp_allreduce_peer", "gemm_tc_f16", "ep_peer", "ep_dispatch_cached", "moe_router", "moe_ffn", "gemv_knob_ignored" };
+                                  "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins", "gemv_stream", "tp_allreduce_peer", "gemm_tc_f16", "ep_peer", "ep_dispatch_cached", "moe_router", "moe_ffn", "gemv_knob_ignored", "gemm_ksplit", "gemv_fused_quant", "gemv_allreduce_fused" };
     return rest[s - ST_GEMV_ID];
 }
 
@@ -202,6 +202,12 @@ static b200q_status get_activation(b200q_ctx *ctx, int form, const b200q_tensor 
     return B200Q_OK;
 }
 
+b200q_status get_decode_activation(b200q_ctx *ctx, int weight_type, const b200q_tensor *src1, ActView *out) {
+    TypeInfo ti;
+    if (!type_info(weight_type, &ti)) return fail(ctx, B200Q_UNSUPPORTED, "weight type %d", weight_type);
+    return get_activation(ctx, ti.act_form, src1, out);
+}
+
 // dst column c (flattened like src1) -> element offset; the kernels take a single column
 // stride, so a dst whose flattened columns are not evenly spaced is walked in runs
 static bool dst_uniform(const b200q_tensor *dst, int64_t *ldd) {
@@ -264,6 +270,9 @@ b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
     if (const char *v = getenv("B200Q_GEMV_ROWS")) ctx->gemv_rows = atoi(v);
     if (const char *v = getenv("B200Q_GEMV_BLOCK_WARPS")) ctx->gemv_block_warps = atoi(v);
     if (const char *v = getenv("B200Q_GEMV_STREAM_MASK")) ctx->gemv_stream_mask = (int)strtol(v, nullptr, 0);
+    if (const char *v = getenv("B200Q_FUSE_QUANT_BYTES")) ctx->fuse_quant_bytes = atoll(v);
+    const char *no_ks = getenv("B200Q_NO_KSPLIT");
+    ctx->no_ksplit = no_ks && no_ks[0] == '1';
     const char *no_stream = getenv("B200Q_NO_STREAM");   // the older GEMV kernel for every shape (comparisons)
     ctx->no_stream = no_stream && no_stream[0] == '1';
     *out = ctx;
@@ -353,6 +362,12 @@ b200q_status b200q_mul_mat(b200q_ctx *ctx, const b200q_tensor *src0, const b200q
                               (float *)dst->data, ldd);
     }
     if (N > 8) count(ctx, ST_GEMM_FALLBACK_SHAPE);
+    // small per-32 products at one or two columns: the GEMV quantizes its own slice of the activation, one launch
+    // instead of two (what matters once a tensor-parallel shard is a microsecond of weights)
+    if (N <= 2 && uniform) {
+        st = launch_gemv_fused(ctx, src0->type, src0->data, src0->nb[1], M, K, src1, (int)N, (float *)dst->data, ldd);
+        if (st != B200Q_UNSUPPORTED) return st;
+    }
     if ((st = get_activation(ctx, ti.act_form, src1, &act)) != B200Q_OK) return st;
     // decode widths go to the GEMV; wider products walk it in groups of eight columns
     // until the tensor-core GEMM takes them

@@ -92,7 +92,7 @@ enum Stat {
     ST_GEMV_UNALIGNED_COL0 = ST_GEMV_COL0 + 9,    // + ncols
     ST_GEMV_ID = ST_GEMV_UNALIGNED_COL0 + 9, ST_GEMV_ID_UNALIGNED, ST_MOE_ROUTE, ST_ROUTE_CACHE_HIT, ST_MOE_GEMM,
     ST_MOE_PACK, ST_GEMM_TC, ST_GEMM_TC_QUANT, ST_GEMM_FALLBACK_SHAPE, ST_TP_ALLREDUCE, ST_TP_ALLGATHER,
-    ST_EP_DISPATCH, ST_EP_COMBINE, ST_GRAPH_LAUNCH, ST_NO_ALLOC, ST_GEMM_KQ_MINS, ST_GEMV_STREAM, ST_TP_ALLREDUCE_PEER, ST_GEMM_TC_F16, ST_EP_PEER, ST_EP_DISPATCH_CACHED, ST_MOE_ROUTER, ST_MOE_FFN, ST_GEMV_KNOB_IGNORED,
+    ST_EP_DISPATCH, ST_EP_COMBINE, ST_GRAPH_LAUNCH, ST_NO_ALLOC, ST_GEMM_KQ_MINS, ST_GEMV_STREAM, ST_TP_ALLREDUCE_PEER, ST_GEMM_TC_F16, ST_EP_PEER, ST_EP_DISPATCH_CACHED, ST_MOE_ROUTER, ST_MOE_FFN, ST_GEMV_KNOB_IGNORED, ST_GEMM_KSPLIT, ST_GEMV_FUSED_QUANT, ST_GEMV_ALLREDUCE_FUSED,
     ST_COUNT
 };
 const char *stat_name(int s);
@@ -121,6 +121,8 @@ struct b200q_ctx {
     // decode GEMV tile knobs (read once from the environment; 0 / -1: the measured defaults): rows per ring stage,
     // warps per block, and which column counts take the slice-resident kernel (bit c = c columns)
     int          gemv_rows = 0, gemv_block_warps = 0, gemv_stream_mask = -1;
+    int64_t      fuse_quant_bytes = 4 << 20;   // B200Q_FUSE_QUANT_BYTES: per-32 decode products up to this many weight bytes quantize their activation inside the GEMV (0: never)
+    bool         no_ksplit = false;       // B200Q_NO_KSPLIT=1: never cut a prompt product along K
     bool         no_stream = false;       // B200Q_NO_STREAM=1: every GEMV through the per-warp ring kernel (comparisons)
     std::string  last_error;
     std::string  stats_text;
@@ -160,6 +162,10 @@ b200q_status launch_dequantize(b200q_ctx *ctx, int type, const void *w, int64_t 
 // gemv.cu: dst[m + c*ldd] for c < ncols (<= 8), rows [0, M)
 b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                          const ActView &act, int64_t col0, int ncols, float *dst, int64_t ldd);
+// the same for one or two columns of a small Q4_0 / Q8_0 product, quantizing src1 inside the kernel;
+// B200Q_UNSUPPORTED: not that case, take the quantizer + launch_gemv
+b200q_status launch_gemv_fused(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
+                               const b200q_tensor *src1, int ncols, float *dst, int64_t ldd);
 
 // MUL_MAT_ID over route tiles of at most tile_pairs (1, 2, 4 or 8) pairs of one expert; tiles == NULL:
 // direct mode, one pair per unit with its expert read from ids on the device (small token counts)
@@ -167,6 +173,15 @@ b200q_status launch_gemv_id(b200q_ctx *ctx, int type, const void *w, size_t row_
                             int64_t M, int64_t K, const ActView &av, int tile_pairs, const int32_t *tiles,
                             const int32_t *n_tiles, int64_t max_tiles, const int32_t *pairs, const b200q_tensor *ids,
                             int n_expert, int n_used, int ne11, float *dst, int64_t ld1, int64_t ld2);
+// the product of a K shard and the all-reduce of the ranks' partial results in one kernel (gemv_stream.cuh); av: the
+// quantized activation, or NULL with src1 to quantize inside the kernel; peers / state: the all-reduce's mapped
+// buffers and device words (tp.cu). B200Q_UNSUPPORTED: the shape does not qualify.
+b200q_status launch_gemv_allreduce(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K, const ActView *av,
+                                   const b200q_tensor *src1, int ncols, float *dst, int64_t ldd, uint64_t *const *peers, uint32_t *state,
+                                   int rank, int nranks);
+bool gemv_ar_shape_ok(int type, const void *w, size_t row_stride, int64_t M, int64_t K, int ncols, int64_t ldd);
+// api.cu: the quantized activation of src1 in the decode layout of the weight type's form (cached per graph)
+b200q_status get_decode_activation(b200q_ctx *ctx, int weight_type, const b200q_tensor *src1, ActView *out);
 // moe.cu: route (pairs sorted by expert, tile lists by size class)
 // Kernel attributes (dynamic shared memory opt-in, occupancy) belong to a device, and one process may hold
 // contexts on several: per-kernel tables indexed by device ordinal replace per-process flags.

@@ -162,6 +162,18 @@ quantize_tiled_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t nb1,
     }
 }
 
+// dst[n][m] = sum over the K parts, part 0 first
+__global__ void __launch_bounds__(256)
+ksplit_sum_kernel(const float *__restrict__ parts, int ksplit, int64_t part_stride, int M, int64_t N, float *__restrict__ dst, int64_t ldd) {
+    const int64_t total = N * M;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        float acc = parts[i];
+        for (int z = 1; z < ksplit; ++z) acc += parts[(int64_t)z * part_stride + i];
+        const int64_t n = i / M, m = i - n * M;
+        dst[n * ldd + m] = acc;
+    }
+}
+
 template <int N> __device__ __forceinline__ uint32_t word_at(const uint32_t (&w)[N], int byte_off) {
     // 32-bit word at a compile-time even byte offset of a register array
     const int i = byte_off >> 2, sh = (byte_off & 3) * 8;
@@ -187,7 +199,7 @@ __device__ __forceinline__ void umma_f16_acc(uint32_t tmem_d, uint64_t da, uint6
 template <int TYPE, bool F16>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
-               int N, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word, TileRoute id) {
+               int N, float *__restrict__ dst, int64_t ldd, int64_t part_stride, int *__restrict__ error_word, TileRoute id) {
     typedef Smem<TYPE, F16> L;
     constexpr int ROWB = Raw<TYPE>::ROW;
     constexpr int NSTAGE = L::NSTAGE;
@@ -199,8 +211,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x, tile_m = blockIdx.y;
     const int row0 = tile_m * BM;
-    // gridDim.z > 1: the product is cut along K (a launch whose whole tiles would leave a nearly empty last round);
-    // this block takes nst of the K / 256 stages, from s_off, and adds its result to a zeroed dst
+    // gridDim.z > 1: the product is cut along K (few tiles on many SMs); this block takes nst of the K / 256
+    // stages, from s_off, and writes its partial result to part blockIdx.z of a scratch buffer
     const int nst_all = K / (SB * KB);
     const int nst = nst_all / (int)gridDim.z;   // k-stages of this block
     const int s_off = (int)blockIdx.z * nst;
@@ -453,18 +465,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 }
             }
         } else if (done && row_ok) {
-            float *o = dst + (int64_t)(tile_n * BN + u * CW) * ldd + row0 + r;
+            float *o = dst + (int64_t)blockIdx.z * part_stride + (int64_t)(tile_n * BN + u * CW) * ldd + row0 + r;
 #pragma unroll
             for (int c = 0; c < CW; c += 2) {
                 float a0, a1;
                 f2_unpack(acc2[c / 2], a0, a1);
-                if (gridDim.z > 1) {                     // two addends per element: the order cannot matter
-                    if (c < ncol) atomicAdd(o, a0);
-                    if (c + 1 < ncol) atomicAdd(o + ldd, a1);
-                } else {
-                    if (c < ncol) *o = a0;
-                    if (c + 1 < ncol) o[ldd] = a1;
-                }
+                // (with the product cut along K, dst is this K part's own [N][ldd] scratch: plain stores, added up
+                // afterwards in a fixed order)
+                if (c < ncol) *o = a0;
+                if (c + 1 < ncol) o[ldd] = a1;
                 o += 2 * ldd;
             }
         }
@@ -540,16 +549,41 @@ static b200q_status launch_tf(b200q_ctx *ctx, const void *w, size_t row_stride, 
     constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
     b200q_status st = make_weight_tmap3(ctx, &wmap, w, row_stride, M, (K / 32) * BB, tc::Raw<TYPE>::ROW, n_mat, mat_stride);
     if (st != B200Q_OK) return st;
-    // split K in two when that shortens the schedule: rounds of whole tiles against rounds of half tiles
+    // Cut K into 2, 4 or 8 parts when the tiles alone leave SMs idle (a 512-row shard of a tensor-parallel product is
+    // 16 tiles on 148 SMs and every tile walks all of K): the schedule's length is rounds of blocks x stages per
+    // block. Parts write their own scratch and a second kernel adds them in a fixed order, so the result does not
+    // depend on which block finishes first.
     const int64_t units = n_tiles * ((M + tc::BM - 1) / tc::BM), S = ctx->sm_count, nst = K / 256;
     unsigned ksplit = 1;
-    if (!tr.tiles && nst % 2 == 0 && nst >= 8 && 2 * ((units + S - 1) / S) > (2 * units + S - 1) / S) {
-        ksplit = 2;
-        B200Q_CUDA(ctx, cudaMemset2DAsync(dst, (size_t)ldd * sizeof(float), 0, (size_t)M * sizeof(float), (size_t)N, ctx->stream));
+    if (!tr.tiles && !ctx->no_ksplit) {
+        // in stages: a block costs about three stages' time beyond its K walk (set-up, drain, stores), the adding pass one
+        constexpr int64_t FIXED = 3;
+        int64_t best = ((units + S - 1) / S) * (nst + FIXED);
+        for (unsigned ks = 2; ks <= 8; ks *= 2) {
+            if (nst % ks || nst / ks < 2) break;
+            const int64_t len = ((units * ks + S - 1) / S) * (nst / ks + FIXED) + 1;
+            if (len < best) { best = len; ksplit = ks; }
+        }
+    }
+    float *out = dst;
+    int64_t out_ld = ldd, part_stride = 0;
+    if (ksplit > 1) {
+        part_stride = N * M;
+        if ((st = ws_reserve(ctx, &ctx->moe_ws[9], sizeof(float) * (size_t)part_stride * ksplit)) != B200Q_OK) return st;
+        out = (float *)ctx->moe_ws[9].ptr;
+        out_ld = M;
     }
     dim3 grid((unsigned)n_tiles, (unsigned)((M + tc::BM - 1) / tc::BM), ksplit);
-    kern<<<grid, tc::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, dst, ldd, ctx->error_word, tr);
+    kern<<<grid, tc::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, out, out_ld, part_stride, ctx->error_word, tr);
     B200Q_CUDA(ctx, cudaGetLastError());
+    if (ksplit > 1) {
+        const int64_t total = N * M;
+        int64_t blocks = (total + 255) / 256;
+        if (blocks > (int64_t)S * 8) blocks = (int64_t)S * 8;
+        tc::ksplit_sum_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(out, (int)ksplit, part_stride, (int)M, N, dst, ldd);
+        B200Q_CUDA(ctx, cudaGetLastError());
+        count(ctx, ST_GEMM_KSPLIT);
+    }
     count(ctx, ST_GEMM_TC);
     if (F16) count(ctx, ST_GEMM_TC_F16);
     return B200Q_OK;

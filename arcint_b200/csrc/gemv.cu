@@ -56,9 +56,9 @@ static b200q_status launch_one(b200q_ctx *ctx, const void *w, size_t row_stride,
 // The slice-resident kernel (gemv_stream.cuh) for rows that bulk copies can fetch (16-byte aligned
 // start, stride and length). Returns false when the shape does not fit it: more than 16 warps per
 // group (K beyond 16 slices, or 8 for more than four columns) or a ring beyond shared memory.
-template <int TYPE, int NC, int R>
+template <int TYPE, int NC, int R, bool QX = false, bool AR = false>
 static bool try_launch_stream(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K, const GemvAct &act,
-                              float *dst, int64_t ldd, b200q_status *st) {
+                              float *dst, int64_t ldd, b200q_status *st, const GemvAr *ar = nullptr) {
     typedef GemvFmt<TYPE> F;
     constexpr int CW = NC > 4 ? 2 : 1, NSETS = 3;
     const int nblk = (int)(K / F::BLK_W), nsl = (nblk + F::STAGE_BLOCKS - 1) / F::STAGE_BLOCKS, nw = nsl * CW;
@@ -76,7 +76,9 @@ static bool try_launch_stream(b200q_ctx *ctx, const void *w, size_t row_stride, 
     while (groups > 1 && groups * gb > 200 * 1024) --groups;
     const size_t smem = groups * gb;
     const int threads = groups * nw * 32;
-    auto kern = gemv_stream_kernel<TYPE, NC, R, NSETS>;
+    auto kern = gemv_stream_kernel<TYPE, NC, R, NSETS, QX, AR>;
+    GemvAr ar_args = {};
+    if (ar) ar_args = *ar;
     // resident blocks per SM for this block shape, asked once per (device, shape)
     struct Occ { int threads; size_t smem; int blocks; bool attr; };
     static Occ occ_dev[B200Q_MAX_DEVICES] = {};
@@ -100,7 +102,7 @@ static bool try_launch_stream(b200q_ctx *ctx, const void *w, size_t row_stride, 
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     cudaError_t e = launch_pdl(!ctx->no_pdl, kern, dim3((unsigned)blocks), dim3(threads), smem, ctx->stream, (const uint8_t *)w,
-                               row_stride, (int)M, nblk, act, dst, (int)ldd, groups, ctx->error_word);
+                               row_stride, (int)M, nblk, act, dst, (int)ldd, groups, ctx->error_word, ar_args);
     if (e == cudaSuccess) e = cudaGetLastError();
     *st = e == cudaSuccess ? B200Q_OK : fail(ctx, B200Q_CUDA_ERROR, "gemv_stream launch: %s", cudaGetErrorString(e));
     return true;
@@ -217,6 +219,115 @@ b200q_status launch_gemv_id(b200q_ctx *ctx, int type, const void *w, size_t row_
     case B200Q_TYPE_IQ4_XS: return launch_id_type<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
     }
     return fail(ctx, B200Q_UNSUPPORTED, "gemv_id: type %d", type);
+}
+
+static GemvAct make_act(const ActView &av, int64_t col0, int64_t K);
+
+// One or two columns of a small per-32 product with the activation quantized inside the GEMV (no quantizer launch):
+// B200Q_UNSUPPORTED when the shape does not qualify and the caller should take the two-kernel route.
+template <int TYPE>
+static b200q_status launch_fused_t(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K, const GemvAct &act, int nc,
+                                   float *dst, int64_t ldd) {
+    b200q_status st = B200Q_OK;
+    bool took = false;
+    if (nc == 1) took = try_launch_stream<TYPE, 1, 2, true>(ctx, w, row_stride, M, K, act, dst, ldd, &st);
+    else if (nc == 2) took = try_launch_stream<TYPE, 2, 4, true>(ctx, w, row_stride, M, K, act, dst, ldd, &st);
+    if (!took) return B200Q_UNSUPPORTED;
+    if (st == B200Q_OK) { count(ctx, ST_GEMV_STREAM); count(ctx, ST_GEMV_FUSED_QUANT); count(ctx, ST_GEMV_COL0 + nc); }
+    return st;
+}
+
+b200q_status launch_gemv_fused(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
+                               const b200q_tensor *src1, int ncols, float *dst, int64_t ldd) {
+    if (type != B200Q_TYPE_Q4_0 && type != B200Q_TYPE_Q8_0) return B200Q_UNSUPPORTED;
+    if (ncols < 1 || ncols > 2 || ctx->no_stream || ctx->fuse_quant_bytes <= 0) return B200Q_UNSUPPORTED;
+    TypeInfo ti;
+    type_info(type, &ti);
+    const size_t row_bytes = (size_t)(K / ti.block) * ti.bytes;
+    if ((uintptr_t)w % 16 || row_stride % 16 || row_bytes % 16) return B200Q_UNSUPPORTED;
+    if ((int64_t)(row_bytes * (size_t)M) > ctx->fuse_quant_bytes || M > INT32_MAX / 2 || ldd > INT32_MAX) return B200Q_UNSUPPORTED;
+    // the activation as plain columns of f32
+    if (src1->ne[2] != 1 || src1->ne[3] != 1 || src1->nb[0] != 4 || src1->nb[1] % 16 || (uintptr_t)src1->data % 16) return B200Q_UNSUPPORTED;
+    GemvAct act = {};
+    act.K = (int)K;
+    act.xf = (const float *)src1->data;
+    act.xf_stride = (int64_t)(src1->nb[1] / 4);
+    return type == B200Q_TYPE_Q4_0 ? launch_fused_t<B200Q_TYPE_Q4_0>(ctx, w, row_stride, M, K, act, ncols, dst, ldd)
+                                   : launch_fused_t<B200Q_TYPE_Q8_0>(ctx, w, row_stride, M, K, act, ncols, dst, ldd);
+}
+
+// Product + all-reduce in one kernel (row split over several GPUs): 1, 2, 4 or 8 columns of a shape the slice-resident
+// kernel takes, NC * M results within the all-reduce buffer. src1 != NULL: quantize inside the kernel (per-32 types,
+// 1-2 columns). B200Q_UNSUPPORTED: not that case.
+template <int TYPE, int NC, bool QX>
+static b200q_status launch_ar_t(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K, const GemvAct &act, float *dst,
+                                int64_t ldd, const GemvAr &ar) {
+    typedef GemvFmt<TYPE> F;
+    const int row_bytes = (int)(K / F::BLK_W) * F::BLK_B;
+    const bool two = NC == 1 || (size_t)12 * gemv_stream_slot(row_bytes) > 36 * 1024;
+    b200q_status st = B200Q_OK;
+    const bool took = two ? try_launch_stream<TYPE, NC, 2, QX, true>(ctx, w, row_stride, M, K, act, dst, ldd, &st, &ar)
+                          : try_launch_stream<TYPE, NC, 4, QX, true>(ctx, w, row_stride, M, K, act, dst, ldd, &st, &ar);
+    if (!took) return B200Q_UNSUPPORTED;
+    if (st == B200Q_OK) { count(ctx, ST_GEMV_STREAM); count(ctx, ST_GEMV_ALLREDUCE_FUSED); count(ctx, ST_GEMV_COL0 + NC); if (QX) count(ctx, ST_GEMV_FUSED_QUANT); }
+    return st;
+}
+
+template <int TYPE>
+static b200q_status launch_ar_type(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K, const GemvAct &act, int nc,
+                                   bool qx, float *dst, int64_t ldd, const GemvAr &ar) {
+    constexpr bool per32 = TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_Q8_0;
+    if constexpr (per32) {
+        if (qx && nc == 1) return launch_ar_t<TYPE, 1, true>(ctx, w, row_stride, M, K, act, dst, ldd, ar);
+        if (qx && nc == 2) return launch_ar_t<TYPE, 2, true>(ctx, w, row_stride, M, K, act, dst, ldd, ar);
+    }
+    if (qx) return B200Q_UNSUPPORTED;
+    switch (nc) {
+    case 1: return launch_ar_t<TYPE, 1, false>(ctx, w, row_stride, M, K, act, dst, ldd, ar);
+    case 2: return launch_ar_t<TYPE, 2, false>(ctx, w, row_stride, M, K, act, dst, ldd, ar);
+    case 4: return launch_ar_t<TYPE, 4, false>(ctx, w, row_stride, M, K, act, dst, ldd, ar);
+    case 8: return launch_ar_t<TYPE, 8, false>(ctx, w, row_stride, M, K, act, dst, ldd, ar);
+    }
+    return B200Q_UNSUPPORTED;
+}
+
+bool gemv_ar_shape_ok(int type, const void *w, size_t row_stride, int64_t M, int64_t K, int ncols, int64_t ldd) {
+    TypeInfo ti;
+    if (!type_info(type, &ti)) return false;
+    const size_t row_bytes = (size_t)(K / ti.block) * ti.bytes;
+    if ((uintptr_t)w % 16 || row_stride % 16 || row_bytes % 16) return false;
+    if (ncols != 1 && ncols != 2 && ncols != 4 && ncols != 8) return false;
+    return (int64_t)ncols * M <= PEER_AR_MAX_FLOATS && M <= INT32_MAX / 2 && ldd <= INT32_MAX;
+}
+
+b200q_status launch_gemv_allreduce(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K, const ActView *av,
+                                   const b200q_tensor *src1, int ncols, float *dst, int64_t ldd, uint64_t *const *peers, uint32_t *state,
+                                   int rank, int nranks) {
+    if (ctx->no_stream || !gemv_ar_shape_ok(type, w, row_stride, M, K, ncols, ldd)) return B200Q_UNSUPPORTED;
+    GemvAr ar = {};
+    for (int p = 0; p < nranks && p < PEER_AR_MAX_RANKS; ++p) ar.peer[p] = peers[p];
+    ar.state = state;
+    ar.rank = rank;
+    ar.nranks = nranks;
+    GemvAct act = {};
+    bool qx = false;
+    if (av) {
+        act = make_act(*av, 0, K);
+    } else {
+        if (!src1 || src1->ne[2] != 1 || src1->ne[3] != 1 || src1->nb[0] != 4 || src1->nb[1] % 16 || (uintptr_t)src1->data % 16) return B200Q_UNSUPPORTED;
+        act.K = (int)K;
+        act.xf = (const float *)src1->data;
+        act.xf_stride = (int64_t)(src1->nb[1] / 4);
+        qx = true;
+    }
+    switch (type) {
+    case B200Q_TYPE_Q4_0:   return launch_ar_type<B200Q_TYPE_Q4_0>(ctx, w, row_stride, M, K, act, ncols, qx, dst, ldd, ar);
+    case B200Q_TYPE_Q8_0:   return launch_ar_type<B200Q_TYPE_Q8_0>(ctx, w, row_stride, M, K, act, ncols, qx, dst, ldd, ar);
+    case B200Q_TYPE_Q4_K:   return launch_ar_type<B200Q_TYPE_Q4_K>(ctx, w, row_stride, M, K, act, ncols, qx, dst, ldd, ar);
+    case B200Q_TYPE_Q6_K:   return launch_ar_type<B200Q_TYPE_Q6_K>(ctx, w, row_stride, M, K, act, ncols, qx, dst, ldd, ar);
+    case B200Q_TYPE_IQ4_XS: return launch_ar_type<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, M, K, act, ncols, qx, dst, ldd, ar);
+    }
+    return B200Q_UNSUPPORTED;
 }
 
 b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,

@@ -53,6 +53,9 @@ struct GemvAct {
     const int16_t  *s32;   // [ ][K/32]   sums of each 32 codes (both forms)
     const int16_t  *s16;   // [ ][K/16]   sums of each 16 codes (per-256 form)
     int             K;
+    // the f32 activation itself, for the kernels that quantize their slice on the fly: column c at xf + c * xf_stride
+    const float    *xf;
+    int64_t         xf_stride;
 };
 
 // signed x signed and unsigned x signed 4-way byte dot products

@@ -25,6 +25,7 @@
 #include "gemv_core.cuh"
 #include "pdl.cuh"
 #include "tc_common.cuh"
+#include "peer_ar.cuh"
 
 namespace b200q {
 
@@ -91,13 +92,82 @@ __host__ __device__ inline size_t gemv_stream_group_smem(int row_bytes, int R, i
     return (size_t)nsets * R * gemv_stream_slot(row_bytes) + (size_t)2 * nw * 32 * sizeof(float) + (size_t)(2 * nsets + 4) * 8;
 }
 
+// Row split over several GPUs: the product and the all-reduce of its partial results as ONE kernel. Instead of
+// storing a finished partial sum to dst, a warp stores it (with the all-reduce's sequence number, peer_ar.cuh)
+// into its rank's slot of EVERY rank's mapped receive buffer -- plain 8-byte stores over NVLink, issued while the
+// other rows are still being computed; after its last row batch a group goes back over its outputs, polls the G
+// slots of each element in its own buffer (bounded), adds them in rank order and writes dst. The last block
+// advances the sequence number. nranks == 0: a plain product.
+struct GemvAr {
+    uint64_t *peer[PEER_AR_MAX_RANKS];
+    uint32_t *state;                   // [0] sequence number of the last all-reduce, [1] blocks finished
+    int       rank, nranks;
+};
+
+__device__ __forceinline__ void gemv_ar_emit(const GemvAr &ar, uint32_t seq, int e, float v) {
+    const uint64_t w = peer_ar_pack(v, seq);
+    const int set = (int)(seq & 1u);
+    for (int p = 0; p < ar.nranks; ++p) {
+        const int q = (ar.rank + p) % ar.nranks;
+        asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(ar.peer[q] + peer_ar_index(set, ar.rank, e)), "l"(w) : "memory");
+    }
+}
+
+// The lane's activation registers for its slice straight from the f32 activation, for the per-32 weight types
+// (Q4_0, Q8_0): the lane's two 32-blocks (numbers 64 slice + lane and + 32) are whole quantization blocks, so ggml's
+// block_q8_0 rule needs nothing from other lanes. Same arithmetic as quantize_q8_0_kernel, operation for operation
+// (d = amax / 127, codes roundf(x * (1 / d)), the scale rounded to fp16), so the product is bit-identical to the one
+// over the separately quantized activation. For small products this removes the quantizer's launch from the chain.
+template <int TYPE, int NC>
+__device__ __forceinline__ void gemv_quant_x(int lane, int slice, int nblk, const GemvAct &act, const int (&cols)[NC], GemvX<NC> &X) {
+    static_assert(TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_Q8_0, "per-32 activation form only");
+    const int b0 = slice * 64 + lane, b1 = b0 + 32;
+    X.live = b0 < nblk;
+    X.live2 = b1 < nblk;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+        const float *xp = act.xf + (int64_t)cols[c] * act.xf_stride;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (!(u ? X.live2 : X.live)) continue;
+            const float4 *p = reinterpret_cast<const float4 *>(xp + 32 * (u ? b1 : b0));
+            float4 v[8];
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[i] = __ldg(p + i);
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+            }
+            const float d = __fdiv_rn(amax, 127.f);
+            const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;
+            int w[8], sum = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int q0 = (int)roundf(__fmul_rn(v[i].x, id)), q1 = (int)roundf(__fmul_rn(v[i].y, id));
+                const int q2 = (int)roundf(__fmul_rn(v[i].z, id)), q3 = (int)roundf(__fmul_rn(v[i].w, id));
+                sum += q0 + q1 + q2 + q3;
+                w[i] = (int)((uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24));
+            }
+            X.x[c][2 * u] = I4{ w[0], w[1], w[2], w[3] };
+            X.x[c][2 * u + 1] = I4{ w[4], w[5], w[6], w[7] };
+            float f = __half2float(__float2half_rn(d));
+            int off = 0;
+            if (TYPE == B200Q_TYPE_Q4_0) {
+                off = -128 * sum;                      // -8 * 16 * sum(x)
+                f *= 0.0625f;                          // the nibble dot is kept x16
+            }
+            if (u) { X.f1[c] = f; X.i1[c] = off; } else { X.f0[c] = f; X.i0[c] = off; }
+        }
+    }
+}
+
 // What one warp of a group does: slice `slice` of every row, columns [col0, col0 + NCW) of the launch.
 // wi: the warp's index in its group of nw warps; warp 0 of the group also runs the producer side.
-template <int TYPE, int NC, int NCW, int R, int NSETS>
+template <int TYPE, int NC, int NCW, int R, int NSETS, bool QX, bool AR>
 __device__ __forceinline__ void gemv_stream_warp(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk,
                                                  const GemvAct &act, float *__restrict__ dst, int ldd, const GemvGroupSmem &sm,
                                                  int gg, int tg, int lane, int wi, int nw, int slice, int col0,
-                                                 int *error_word) {
+                                                 int *error_word, const GemvAr &ar, uint32_t seq) {
     constexpr int CW = NC > 4 ? 2 : 1;                             // warps per slice (column halves)
     typedef GemvFmt<TYPE> F;
     typedef GemvStage<TYPE> S;
@@ -144,7 +214,8 @@ __device__ __forceinline__ void gemv_stream_warp(const uint8_t *__restrict__ W, 
 #pragma unroll
     for (int c = 0; c < NCW; ++c) cols[c] = col0 + c;
     GemvX<NCW> X;
-    gemv_load_x<TYPE, NCW>(lane, slice, nblk, act, cols, X);      // once: this warp's slice of every column
+    if constexpr (QX) gemv_quant_x<TYPE, NCW>(lane, slice, nblk, act, cols, X);      // ... quantized here from the f32 activation
+    else gemv_load_x<TYPE, NCW>(lane, slice, nblk, act, cols, X);                    // once: this warp's slice of every column
 
     constexpr int V = gemv_pow2_at_least(R * NCW);
     constexpr int SHARE = 32 / V;                                  // lanes that end up with the same value
@@ -178,7 +249,10 @@ __device__ __forceinline__ void gemv_stream_warp(const uint8_t *__restrict__ W, 
         const int i = lane / SHARE;
         if (nw == 1) {
             const int c = i / R, r = i - c * R, row = u * R + r;
-            if ((lane & (SHARE - 1)) == 0 && c < NCW && row < M) dst[(size_t)(col0 + c) * ldd + row] = v[0];
+            if ((lane & (SHARE - 1)) == 0 && c < NCW && row < M) {
+                if (AR) gemv_ar_emit(ar, seq, (col0 + c) * M + row, v[0]);
+                else dst[(size_t)(col0 + c) * ldd + row] = v[0];
+            }
             continue;
         }
         // the slices meet in shared memory: part[par][warp][i]
@@ -202,12 +276,37 @@ __device__ __forceinline__ void gemv_stream_warp(const uint8_t *__restrict__ W, 
                 if (c < hn && row < M) {
                     float t = 0.f;
                     for (int s = h; s < nw; s += CW) t += part[s * 32 + lane];
-                    dst[(size_t)(hcol0 + c) * ldd + row] = t;
+                    if (AR) gemv_ar_emit(ar, seq, (hcol0 + c) * M + row, t);
+                    else dst[(size_t)(hcol0 + c) * ldd + row] = t;
                 }
             }
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(sm.bar_free + 8 * par);
         }
+    }
+    if (AR && ok) {
+        // second pass over this group's row batches: every lane takes one (column, row) of a batch, waits for the G
+        // ranks' partial sums of it in this rank's own buffer and adds them in rank order
+        bool got = !(error_word && *(volatile int *)error_word);
+        auto load = [](const uint64_t *p) {
+            uint64_t w;
+            asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+            return w;
+        };
+        const uint64_t *mine = ar.peer[ar.rank];
+        const int set = (int)(seq & 1u);
+        for (int n = wi, u = gg + wi * tg; u < n_units; u += nw * tg, n += nw) {
+            for (int j = lane; j < R * NC; j += 32) {
+                const int c = j / R, r = j - c * R, row = u * R + r;
+                if (row >= M) continue;
+                const int e = c * M + row;
+                float sum = 0.f;
+                for (int q = 0; q < ar.nranks; ++q)
+                    sum += peer_ar_value(peer_ar_wait(mine + peer_ar_index(set, q, e), seq, PEER_AR_SPIN_LIMIT, load, &got));
+                dst[(size_t)c * ldd + row] = sum;
+            }
+        }
+        if (!got && error_word) atomicExch(error_word, 4);
     }
     if (!ok && lane == 0 && error_word) atomicExch(error_word, 2);
 }
@@ -215,10 +314,10 @@ __device__ __forceinline__ void gemv_stream_warp(const uint8_t *__restrict__ W, 
 // dst[m + c*ldd] = sum_k W[m][k] x_c[k] for c < NC (1..8), rows [0, M). A block holds `groups` groups of
 // nslices * (NC > 4 ? 2 : 1) warps; the grid is one wave of persistent blocks and group number gg takes the
 // row batches gg, gg + (all groups), ...
-template <int TYPE, int NC, int R, int NSETS>
+template <int TYPE, int NC, int R, int NSETS, bool QX = false, bool AR = false>
 __global__ void __launch_bounds__(GEMV_STREAM_MAX_THREADS)
 gemv_stream_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk, GemvAct act, float *__restrict__ dst,
-                   int ldd, int groups, int *__restrict__ error_word) {
+                   int ldd, int groups, int *__restrict__ error_word, GemvAr ar) {
     typedef GemvFmt<TYPE> F;
     constexpr int CW = NC > 4 ? 2 : 1;
     constexpr int NCA = CW == 2 ? (NC + 1) / 2 : NC, NCB = NC - NCA;
@@ -251,12 +350,26 @@ gemv_stream_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int 
     }
     __syncthreads();
     const int gg = blockIdx.x * groups + g, tg = gridDim.x * groups;
+    uint32_t seq = 0;
+    if (AR) seq = *(volatile uint32_t *)ar.state + 1;
     if (g < groups) {
         if (CW == 1 || sub == 0)
-            gemv_stream_warp<TYPE, NC, NCA, R, NSETS>(W, row_stride, M, nblk, act, dst, ldd, sm, gg, tg, lane, wi, nw, slice, 0, error_word);
+            gemv_stream_warp<TYPE, NC, NCA, R, NSETS, QX, AR>(W, row_stride, M, nblk, act, dst, ldd, sm, gg, tg, lane, wi, nw, slice, 0, error_word, ar,
+                                                              seq);
         else
-            gemv_stream_warp<TYPE, NC, (NCB > 0 ? NCB : 1), R, NSETS>(W, row_stride, M, nblk, act, dst, ldd, sm, gg, tg, lane, wi, nw, slice,
-                                                                      NCA, error_word);
+            gemv_stream_warp<TYPE, NC, (NCB > 0 ? NCB : 1), R, NSETS, QX, AR>(W, row_stride, M, nblk, act, dst, ldd, sm, gg, tg, lane, wi, nw,
+                                                                              slice, NCA, error_word, ar, seq);
+    }
+    if (AR) {
+        // the last block to finish advances the all-reduce's sequence number (for the next launch)
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(ar.state + 1, 1u) == gridDim.x - 1) {
+                ar.state[1] = 0;
+                *(volatile uint32_t *)ar.state = seq;
+            }
+        }
     }
     // this block's rows are done: once every block is here the next kernel of the stream may be scheduled
     pdl_trigger();

@@ -331,6 +331,41 @@ b200q_status b200q_all_reduce_f32(b200q_ctx *ctx, void *dev_buf, size_t count) {
     return B200Q_OK;
 }
 
+// Row split, decode widths: dst = sum over the ranks of src0 (this rank's K shard) x src1 (its K range), the same on
+// every rank. When the shape allows (1, 2, 4 or 8 columns, rows the slice-resident GEMV takes, at most 65536 results,
+// peer buffers mapped) the product and the all-reduce are ONE kernel: partial sums go straight from the GEMV's
+// registers into every rank's receive buffer over NVLink and are added up by the same kernel (gemv_stream.cuh).
+// Otherwise b200q_mul_mat followed by b200q_all_reduce_f32.
+b200q_status b200q_mul_mat_allreduce(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1, b200q_tensor *dst) {
+    TpState *tp;
+    Nccl *api;
+    b200q_status st = tp_get(ctx, &tp, &api);
+    if (st != B200Q_OK) return st;
+    if (!src0 || !src1 || !dst) return B200Q_INVALID;
+    const int64_t N = src1->ne[1] * src1->ne[2] * src1->ne[3], M = src0->ne[1], K = src0->ne[0];
+    const bool plain = b200q_supports(nullptr, B200Q_OP_MUL_MAT, src0, src1, nullptr, dst) == B200Q_OK && dst->ne[2] == 1 && dst->ne[3] == 1 &&
+                       src1->ne[2] == 1 && src1->ne[3] == 1 && dst->nb[1] == (size_t)M * 4;      // packed [M, N] result: element c * M + m
+    static const bool off = [] { const char *v = getenv("B200Q_NO_FUSED_AR"); return v && v[0] == '1'; }();
+    if (plain && !off && tp->peer_ok && tp->nranks > 1 && N >= 1 && N <= 8 && M > 0 &&
+        gemv_ar_shape_ok(src0->type, src0->data, src0->nb[1], M, K, (int)N, M)) {
+        B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+        // small per-32 products quantize inside the kernel; the rest take the cached quantized activation
+        TypeInfo ti;
+        type_info(src0->type, &ti);
+        const bool qx = ti.act_form == ACT_Q8_0 && N <= 2 && ctx->fuse_quant_bytes > 0 &&
+                        (int64_t)((size_t)(K / ti.block) * ti.bytes * (size_t)M) <= ctx->fuse_quant_bytes;
+        ActView av;
+        if (!qx && (st = get_decode_activation(ctx, src0->type, src1, &av)) != B200Q_OK) return st;
+        st = launch_gemv_allreduce(ctx, src0->type, src0->data, src0->nb[1], M, K, qx ? nullptr : &av, src1, (int)N, (float *)dst->data, M,
+                                   tp->ar_peer, tp->ar_state, tp->rank, tp->nranks);
+        if (st == B200Q_OK) count(ctx, ST_TP_ALLREDUCE);
+        if (st != B200Q_UNSUPPORTED) return st;
+    }
+    if ((st = b200q_mul_mat(ctx, src0, src1, dst)) != B200Q_OK) return st;
+    if (!plain) return fail(ctx, B200Q_UNSUPPORTED, "mul_mat_allreduce needs a packed 2-D result");
+    return b200q_all_reduce_f32(ctx, dst->data, (size_t)(M * N));
+}
+
 b200q_status b200q_all_gather(b200q_ctx *ctx, const void *dev_send, void *dev_recv, size_t bytes_per_rank) {
     TpState *tp;
     Nccl *api;

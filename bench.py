@@ -264,9 +264,11 @@ def tp_trace_section(ctx, world, rank, dist):
         def product(name, layer):
             mc, kc, how, copies = dev[name]
             xin = A.Tensor.make(A.F32, [kc, n, 1, 1], [4, 4 * kmax], dxs[feeds[name]])
-            ctx.mul_mat(A.Tensor.weights(t, copies[layer % len(copies)], kc, mc), xin, A.Tensor.f32(dy, [mc, n]))
             if how == "row" and world > 1:
-                ctx.all_reduce_f32(dy, n * mc)
+                # product + all-reduce: one kernel at decode widths, product then collective at prompt widths
+                ctx.mul_mat_allreduce(A.Tensor.weights(t, copies[layer % len(copies)], kc, mc), xin, A.Tensor.f32(dy, [mc, n]))
+            else:
+                ctx.mul_mat(A.Tensor.weights(t, copies[layer % len(copies)], kc, mc), xin, A.Tensor.f32(dy, [mc, n]))
 
         def trace():
             for _ in range(reps):

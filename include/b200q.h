@@ -166,6 +166,11 @@ B200Q_API b200q_status b200q_tp_rank(const b200q_ctx *ctx, int *rank, int *nrank
 B200Q_API b200q_status b200q_tp_shard(int64_t total, int64_t unit, int nranks, int rank, int64_t *first, int64_t *count);
 B200Q_API b200q_status b200q_all_reduce_f32(b200q_ctx *ctx, void *dev_buf, size_t count);
 B200Q_API b200q_status b200q_all_gather(b200q_ctx *ctx, const void *dev_send, void *dev_recv, size_t bytes_per_rank);
+/* Row split in one call: dst [M, N] (packed) = the sum over the ranks of src0 (this rank's K shard) x src1 (its K range),
+ * the same on every rank. At decode widths (1, 2, 4 or 8 columns) the product and the all-reduce are one kernel: the
+ * partial sums leave the GEMV's registers as stores into every rank's mapped receive buffer over NVLink and the same
+ * kernel adds them up in rank order; otherwise b200q_mul_mat followed by b200q_all_reduce_f32. Collective. */
+B200Q_API b200q_status b200q_mul_mat_allreduce(b200q_ctx *ctx, const b200q_tensor *src0, const b200q_tensor *src1, b200q_tensor *dst);
 B200Q_API b200q_status b200q_all_to_all_v(b200q_ctx *ctx, const void *dev_send, const size_t *send_offsets,
                                           const size_t *send_bytes, void *dev_recv, const size_t *recv_offsets,
                                           const size_t *recv_bytes);

@@ -65,6 +65,21 @@ def main():
         got = ctx.download(dy, (n, m), np.float32)
         errs.append(rel_err(got, O.mul_mat_f64(t, w, k, x, True)))
         assert errs[-1] < TOL, ("row split", t, errs[-1])
+        # the same as one call (at 1, 2, 4, 8 columns product and all-reduce are one kernel), twice in a row
+        if kc:
+            for nn in (1, 2, 4):
+                xs = np.ascontiguousarray(x[:nn, k0:k0 + kc]) if nn <= n else np.ascontiguousarray(np.tile(x, (2, 1))[:nn, k0:k0 + kc])
+                xfull = x[:nn] if nn <= n else np.tile(x, (2, 1))[:nn]
+                dxs, dy2 = ctx.upload(xs), ctx.alloc(nn * m * 4)
+                for rep in range(2):
+                    ctx.graph_begin()
+                    ctx.upload(np.full((nn, m), np.nan, dtype=np.float32), dy2)
+                    ctx.mul_mat_allreduce(A.Tensor.weights(t, dw, kc, m), A.Tensor.f32(dxs, [kc, nn]), A.Tensor.f32(dy2, [m, nn]))
+                    got = ctx.download(dy2, (nn, m), np.float32)
+                    e = rel_err(got, O.mul_mat_f64(t, w, k, xfull, True))
+                    assert e < TOL, ("fused row split", t, nn, rep, e)
+                ctx.free(dxs)
+                ctx.free(dy2)
 
     # the one-shot all-reduce over peer memory, many times in a row (both sets of slots, the device-side sequence
     # number), eagerly and replayed from a CUDA graph: every rank must end with the same, exact sums
@@ -150,9 +165,11 @@ def main():
     ctx.sync()
 
     st = ctx.stats()
-    assert st.get("tp_allgather") == 1 and st.get("tp_allreduce") == 2 + 5 + 3 and st.get("gemm_tc", 0) >= 1, st
+    assert st.get("tp_allgather") == 1 and st.get("tp_allreduce", 0) >= 2 + 5 + 3 and st.get("gemm_tc", 0) >= 1, st
     # the decode-sized all-reduces went over peer memory unless the mapping was refused or switched off
-    assert peer_used in (0, st.get("tp_allreduce")) or os.environ.get("B200Q_NO_PEER_AR") == "1", st
+    assert peer_used in (0, 10) or os.environ.get("B200Q_NO_PEER_AR") == "1", st
+    if peer_used:
+        assert st.get("gemv_allreduce_fused", 0) >= 6, st
     dist.barrier()
     print("MGPU_OK rank %d/%d colsplit %.2e rowsplit %s ep %s peer_allreduce %d" % (rank, world, e1, ["%.2e" % e for e in errs],
                                                                                        ["%.2e" % max(ep_errs)], peer_used) + " peer_ep %d" % peer_ep, flush=True)
