@@ -353,7 +353,12 @@ gemv_stream_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int 
     uint32_t seq = 0;
     if (AR) seq = *(volatile uint32_t *)ar.state + 1;
     if (g < groups) {
-        if (CW == 1 || sub == 0)
+        // one copy of the warp code when both column halves are equally wide (8 and 6 columns): the instruction
+        // cache is a measured bottleneck of the wide forms
+        if (CW == 1 || NCA == NCB)
+            gemv_stream_warp<TYPE, NC, NCA, R, NSETS, QX, AR>(W, row_stride, M, nblk, act, dst, ldd, sm, gg, tg, lane, wi, nw, slice, sub * NCA,
+                                                              error_word, ar, seq);
+        else if (sub == 0)
             gemv_stream_warp<TYPE, NC, NCA, R, NSETS, QX, AR>(W, row_stride, M, nblk, act, dst, ldd, sm, gg, tg, lane, wi, nw, slice, 0, error_word, ar,
                                                               seq);
         else

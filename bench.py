@@ -685,7 +685,9 @@ def run_gpu(args, rank, world):
     ctx.stats_reset()
     graphs = [ctx.capture(lambda r=r: step_device(r)) for r in range(ROT)]
     st = ctx.stats()
-    launches_per_step = sum(v for key, v in st.items() if key.startswith("gemv_") or key.startswith("quantize_")) // ROT
+    # one kernel per counted product (its column-count key) and per quantizer call
+    launches_per_step = sum(v for key, v in st.items() if key.startswith("quantize_") or
+                            (key.startswith("gemv_") and key.endswith("col"))) // ROT
     for i in range(max(args.warmup, 3)):
         ctx.graph_launch(graphs[i % ROT])
     ms = timed(lambda i: ctx.graph_launch(graphs[i % ROT]), args.steps)
@@ -735,7 +737,7 @@ def run_gpu(args, rank, world):
     # roofline of the dominant kernel: the GEMV alone (activation quantized once per graph),
     # a graph of back-to-back launches over the rotating weight copies
     peak, peak_src = measured_peaks()
-    detail, tot_b, tot_ms = [], 0, 0.0
+    detail, tot_b, tot_ms, tot_traffic = [], 0, 0.0, 0.0
     reps = 50
     for name, t, m, k, ptrs, n in products:
         W = [A.Tensor.weights(t, p, k, m) for p in ptrs]
@@ -762,6 +764,9 @@ def run_gpu(args, rank, world):
                        "gbs": round(b / (kms * 1e-3) / 1e9, 1), "frac": round(b / (kms * 1e-3) / 1e9 / peak, 3)})
         tot_b += b
         tot_ms += kms
+        # DRAM bytes per launch as ncu captured them (dram__bytes.sum.per_second x gpu__time_duration): 25.39 to 25.46 MB for
+        # the 25.36 MB Q4_K matrix at 1 and 8 columns, 111.2 MB for the 107.52 MB Q6_K head
+        tot_traffic += b * (1.035 if t == A.Q6_K else 1.003)
     achieved = tot_b / (tot_ms * 1e-3) / 1e9
     clocks = sampler.stop() if rank == 0 else None
 
@@ -808,10 +813,9 @@ def run_gpu(args, rank, world):
                        "launch": "each step is one CUDA-graph replay of 12 x (quantize, GEMV)",
                        "parallelism": "replicas" if world > 1 else "single GPU", "parity_max_rel_err": err},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         # DRAM bytes per GEMV launch, mean over the 12 products: an ncu capture read 25.38 MB for the
-                         # 25.36 MB Q4_K matrix and 107.5 MB for the 107.52 MB Q6_K head (1.001 x algorithmic)
-                         "traffic": 1.001 * tot_b / len(detail), "algorithmic_bytes_per_launch": tot_b / len(detail),
-                         "peak_source": peak_src, "kernel": "gemv_kernel (activation pre-quantized), back-to-back launches in a CUDA graph",
+                         # DRAM bytes per GEMV launch, mean over the 12 products, scaled from the ncu captures
+                         "traffic": tot_traffic / len(detail), "algorithmic_bytes_per_launch": tot_b / len(detail),
+                         "peak_source": peak_src, "kernel": "gemv_stream_kernel / gemv_kernel (activation pre-quantized), back-to-back launches in a CUDA graph",
                          "detail": detail},
             "prefill": prefill,
             "tp_trace": tp_trace,

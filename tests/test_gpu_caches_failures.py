@@ -26,7 +26,7 @@ def _x(dev, k, n, ident):
     return A.Tensor.make(A.F32, [k, n, 1, 1], [4, 4 * k], dev, ident)
 
 
-@pytest.mark.parametrize("t,n", [(A.Q4_0, 1), (A.Q4_K, 3), (A.Q4_0, 40), (A.IQ4_XS, 24)])
+@pytest.mark.parametrize("t,n", [(A.Q4_0, 1), (A.Q4_0, 5), (A.Q4_K, 3), (A.Q4_0, 40), (A.IQ4_XS, 24)])
 def test_two_tensors_at_one_address_in_one_graph(ctx, t, n):
     """Layer L+1's activation lands where layer L's was (same address, shape and generation): with the
     tensors' identities in the descriptors both products must use their own contents."""
@@ -42,11 +42,13 @@ def test_two_tensors_at_one_address_in_one_graph(ctx, t, n):
     ctx.mul_mat(W, _x(dx, k, n, 0x1000), Y)
     ga = ctx.download(dy, (n, m), np.float32)
     ctx.mul_mat(W, _x(dx, k, n, 0x1000), Y)                 # the same tensor again: cached
-    assert ctx.stats()["act_cache_hit"] == 1
+    # (a small per-32 product at one or two columns quantizes inside the GEMV and has no cache entry at all)
+    fused = ctx.stats().get("gemv_fused_quant", 0) > 0
+    assert ctx.stats().get("act_cache_hit", 0) == (0 if fused else 1)
     ctx.upload(xb, dx)                                      # another tensor of the graph at the same address
     ctx.mul_mat(W, _x(dx, k, n, 0x2000), Y)
     gb = ctx.download(dy, (n, m), np.float32)
-    assert ctx.stats()["act_cache_hit"] == 1
+    assert ctx.stats().get("act_cache_hit", 0) == (0 if fused else 1)
     assert rel_err(ga, O.mul_mat_f64(t, w, k, xa, True)) < TOL
     assert rel_err(gb, O.mul_mat_f64(t, w, k, xb, True)) < TOL
     for p in (dw, dx, dy):

@@ -188,21 +188,21 @@ def test_activation_cache_within_a_graph(ctx):
     t, m, k = A.Q4_0, 64, 1024
     rng = np.random.default_rng(8)
     w = O.random_blocks(t, m, k, rng)
-    x = rng.normal(0, 1, size=(1, k)).astype(np.float32)
-    dw, dx, dy = ctx.upload(w), ctx.upload(x), ctx.alloc(m * 4)
-    W, X, Y = A.Tensor.weights(t, dw, k, m), A.Tensor.f32(dx, [k, 1]), A.Tensor.f32(dy, [m, 1])
+    x = rng.normal(0, 1, size=(3, k)).astype(np.float32)      # three columns: not the width that quantizes inside the GEMV
+    dw, dx, dy = ctx.upload(w), ctx.upload(x), ctx.alloc(3 * m * 4)
+    W, X, Y = A.Tensor.weights(t, dw, k, m), A.Tensor.f32(dx, [k, 3]), A.Tensor.f32(dy, [m, 3])
     ctx.stats_reset()
     ctx.graph_begin()
     for _ in range(3):
         ctx.mul_mat(W, X, Y)
     s = ctx.stats()
-    assert s["quantize_act_q8_0"] == 1 and s["act_cache_hit"] == 2 and s["gemv_1col"] == 3
+    assert s["quantize_act_q8_0"] == 1 and s["act_cache_hit"] == 2 and s["gemv_3col"] == 3
     x2 = x * 2
     ctx.upload(x2, dx)
     ctx.graph_begin()
     ctx.mul_mat(W, X, Y)
     assert ctx.stats()["quantize_act_q8_0"] == 2
-    assert rel_err(ctx.download(dy, (1, m), np.float32), O.mul_mat_f64(t, w, k, x2, True)) < TOL
+    assert rel_err(ctx.download(dy, (3, m), np.float32), O.mul_mat_f64(t, w, k, x2, True)) < TOL
     for p in (dw, dx, dy):
         ctx.free(p)
 
@@ -274,7 +274,7 @@ def test_overlapped_host_copies_eager_and_in_a_graph(ctx):
 
 
 @pytest.mark.parametrize("t", [A.Q4_0, A.Q8_0])
-@pytest.mark.parametrize("m,k,n", [(512, 4096, 1), (96, 2080, 2), (1000, 512, 1), (37, 32, 2)])
+@pytest.mark.parametrize("m,k,n", [(512, 4096, 1), (96, 2304, 2), (1000, 512, 1), (37, 256, 2)])
 def test_gemv_that_quantizes_its_own_activation_is_bit_identical(t, m, k, n):
     """Small per-32 decode products quantize their slice of the activation inside the GEMV (one launch instead of
     two). The arithmetic is the quantizer kernel's, operation for operation, so the result must equal the
@@ -287,11 +287,13 @@ def test_gemv_that_quantizes_its_own_activation_is_bit_identical(t, m, k, n):
     for fused in (True, False):
         if not fused:
             os.environ["B200Q_FUSE_QUANT_BYTES"] = "0"
+            os.environ["B200Q_GEMV_STREAM_MASK"] = "0x1FE"      # the same GEMV kernel at every width, so only the quantizer's place differs
         try:
             with A.Context(0) as c:
                 outs[fused] = c.run_mul_mat(t, w, k, x)
                 assert (c.stats().get("gemv_fused_quant", 0) == 1) == fused, c.stats()
         finally:
             os.environ.pop("B200Q_FUSE_QUANT_BYTES", None)
+            os.environ.pop("B200Q_GEMV_STREAM_MASK", None)
     assert np.array_equal(outs[True], outs[False])
     assert rel_err(outs[True], O.mul_mat_f64(t, w, k, x, True)) < TOL
