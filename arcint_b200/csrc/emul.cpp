@@ -14,6 +14,7 @@
 
 #include "gemv_core.cuh"
 #include "peer_ar.cuh"
+#include "ep_agree.h"
 
 using namespace b200q;
 
@@ -167,6 +168,12 @@ int emul_peer_allreduce(int nranks, int count, const float *in, float *out, int 
             }
     }
     return 0;
+}
+
+// The exit rule of the NCCL form of expert parallelism (ep_agree.h): G records of `stride` int32, status at
+// `status_at`; what rank `rank` returns (0, its own status, or peer_failed) and the lowest failing rank.
+int emul_ep_agree(const int32_t *records, int G, int stride, int status_at, int rank, int peer_failed, int *who) {
+    return ep_agree_decide(records, G, stride, status_at, rank, peer_failed, who);
 }
 
 uint32_t emul_nib_minus8(uint32_t t) { return nib_minus8(t); }

@@ -25,6 +25,7 @@
 #include "pdl.cuh"
 #include "peer_ar.cuh"
 #include "ep_peer.cuh"
+#include "ep_agree.h"
 
 namespace b200q {
 
@@ -76,6 +77,11 @@ struct TpState {
     uint64_t *ar_local = nullptr;
     uint64_t *ar_peer[PEER_AR_MAX_RANKS] = {};
     uint32_t *ar_state = nullptr;            // [0] sequence number of the last all-reduce, [1] blocks finished
+    // status agreement of the NCCL form of expert parallelism (ep_agree.h): G gathered records of G counts and a
+    // status word, then this rank's own record; allocated with the communicator so that no later failure can keep a
+    // rank out of the agreement
+    int32_t  *agree_dev = nullptr;
+    int32_t   agree_host = 0;                // the status word on its way to the device
     // expert parallelism over peer memory (ep_peer.cuh), after b200q_ep_reserve
     bool      ep_ok = false;
     int64_t   ep_cap = 0, ep_k = 0, ep_m = 0;          // reserved: pairs per region, longest rows in floats
@@ -227,6 +233,7 @@ void tp_free(b200q_ctx *ctx) {
     if (!tp) return;
     ep_close(ctx, tp);
     peer_ar_close(ctx, tp);
+    if (tp->agree_dev) cudaFree(tp->agree_dev);
     Nccl *api = nccl_api(nullptr);
     if (api && tp->comm && api->CommDestroy) api->CommDestroy(tp->comm);
     delete tp;
@@ -276,6 +283,12 @@ b200q_status b200q_tp_init(b200q_ctx *ctx, const void *id128, int rank, int nran
     if (r != ncclSuccess) {
         delete tp;
         return fail(ctx, B200Q_NCCL_ERROR, "ncclCommInitRank: %s", api->GetErrorString ? api->GetErrorString(r) : "error");
+    }
+    if (cudaMalloc(&tp->agree_dev, sizeof(int32_t) * (size_t)(nranks + 1) * (nranks + 1)) != cudaSuccess) {
+        cudaGetLastError();
+        if (api->CommDestroy) api->CommDestroy(tp->comm);
+        delete tp;
+        return fail(ctx, B200Q_NO_MEMORY, "status records of %d ranks", nranks);
     }
     ctx->tp = tp;
     peer_ar_setup(ctx, tp, api);
@@ -389,13 +402,18 @@ b200q_status b200q_all_to_all_v(b200q_ctx *ctx, const void *dev_send, const size
     if (st != B200Q_OK) return st;
     if (!send_offsets || !send_bytes || !recv_offsets || !recv_bytes) return B200Q_INVALID;
     B200Q_NCCL(ctx, api, api->GroupStart());
-    for (int p = 0; p < tp->nranks; ++p) {
+    // a group that was opened is always closed, also after a refused send or receive: the first error is kept
+    ncclResult_t first = ncclSuccess;
+    for (int p = 0; p < tp->nranks && first == ncclSuccess; ++p) {
         if (send_bytes[p])
-            B200Q_NCCL(ctx, api, api->Send((const uint8_t *)dev_send + send_offsets[p], send_bytes[p], ncclInt8, p, tp->comm, ctx->stream));
-        if (recv_bytes[p])
-            B200Q_NCCL(ctx, api, api->Recv((uint8_t *)dev_recv + recv_offsets[p], recv_bytes[p], ncclInt8, p, tp->comm, ctx->stream));
+            first = api->Send((const uint8_t *)dev_send + send_offsets[p], send_bytes[p], ncclInt8, p, tp->comm, ctx->stream);
+        if (recv_bytes[p] && first == ncclSuccess)
+            first = api->Recv((uint8_t *)dev_recv + recv_offsets[p], recv_bytes[p], ncclInt8, p, tp->comm, ctx->stream);
     }
-    B200Q_NCCL(ctx, api, api->GroupEnd());
+    const ncclResult_t end = api->GroupEnd();
+    if (first == ncclSuccess) first = end;
+    if (first != ncclSuccess)
+        return fail(ctx, B200Q_NCCL_ERROR, "all-to-all: %s", api->GetErrorString ? api->GetErrorString(first) : "nccl error");
     b200q::count(ctx, ST_EP_DISPATCH);
     return B200Q_OK;
 }
@@ -479,42 +497,75 @@ b200q_status b200q_ep_reserve(b200q_ctx *ctx, int64_t max_pairs, int64_t max_k, 
 
 // Expert-parallel MUL_MAT_ID. Every rank holds its own tokens (src1 [K, ne11, n_tok], ids [n_used, n_tok]
 // with GLOBAL expert ids, dst [M, n_used, n_tok]) and the experts [rank * n_local, (rank + 1) * n_local)
-// as src0 [K, M, n_local]; n_expert_total = n_local * nranks. The call routes the local pairs by owner,
-// exchanges the per-owner counts (one small all-gather and one host synchronisation: the send and receive
-// sizes must be known on the host), sends every pair's f32 activation row and owner-local expert index to
-// the owner (all-to-all), runs b200q_mul_mat_id over what it received, returns the result rows (all-to-all)
-// and scatters them into dst. The local product runs under a private cache generation (the receive
-// buffers are reused with other contents by the next call); the caller's caches, the route of `ids` among them,
-// stay valid across the gate, up and down calls of a layer.
+// as src0 [K, M, n_local]; n_expert_total = n_local * nranks. After b200q_ep_reserve the exchange is
+// device-initiated over peer memory (ep_peer.cuh) and the call neither synchronises nor allocates. Without it
+// the call routes the local pairs by owner, exchanges the per-owner counts (one small all-gather and one host
+// synchronisation: the send and receive sizes must be known on the host), sends every pair's f32 activation row
+// and owner-local expert index to the owner (all-to-all), runs b200q_mul_mat_id over what it received, returns
+// the result rows (all-to-all) and scatters them into dst. The local product runs under a private cache
+// generation (the receive buffers are reused with other contents by the next call); the caller's caches, the
+// route of `ids` among them, stay valid across the gate, up and down calls of a layer.
+//
+// Errors. In the NCCL form no rank leaves between collectives alone: a rank-local error (a refused argument, no
+// memory for the scratch, a failed launch or local product) travels as a status word beside the counts and again
+// before the dispatch and before the combine (ep_agree.h), and every rank returns from the same point -- the
+// failing rank with its own error, the others with B200Q_PEER_FAILED. In the peer-memory form a rank that fails
+// returns at once; the others' bounded waits for its rows run out and they report B200Q_TIMEOUT.
 b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local, const b200q_tensor *src1,
                                  const b200q_tensor *ids, b200q_tensor *dst, int n_expert_total) {
     TpState *tp;
     Nccl *api;
     b200q_status st = tp_get(ctx, &tp, &api);
     if (st != B200Q_OK) return st;
-    if (!src0_local || !src1 || !ids || !dst) return B200Q_INVALID;
     const int G = tp->nranks;
-    if (n_expert_total <= 0 || n_expert_total % G || src0_local->ne[2] != n_expert_total / G)
-        return fail(ctx, B200Q_INVALID, "experts: %d in total over %d ranks, %lld here", n_expert_total, G,
-                    (long long)src0_local->ne[2]);
-    if (n_expert_total > 4096 || G > 64) return fail(ctx, B200Q_UNSUPPORTED, "expert-parallel limits: 4096 experts, 64 ranks");
-    if (ids->type != B200Q_TYPE_I32 || src1->type != B200Q_TYPE_F32 || dst->type != B200Q_TYPE_F32 || src1->nb[0] != 4 ||
-        dst->nb[0] != 4 || (uintptr_t)src1->data % 16 || src1->nb[1] % 16 || src1->nb[2] % 16 || src1->ne[0] % 4)
-        return fail(ctx, B200Q_UNSUPPORTED, "expert-parallel MUL_MAT_ID needs packed f32 activations and i32 ids");
-    const int n_local = n_expert_total / G, n_used = (int)ids->ne[0], n_tok = (int)ids->ne[1];
-    const int64_t K = src0_local->ne[0], M = src0_local->ne[1];
-    const int n_pairs = n_used * n_tok;
-    if (src1->ne[0] != K || dst->ne[0] != M || dst->ne[1] != n_used || dst->ne[2] != n_tok ||
-        (src1->ne[1] != 1 && src1->ne[1] != n_used) || src1->ne[2] != n_tok)
-        return fail(ctx, B200Q_INVALID, "expert-parallel MUL_MAT_ID shapes");
-    B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+    int n_local = 0, n_used = 0, n_tok = 0, n_pairs = 0;
+    int64_t K = 0, M = 0;
+    // everything this rank can refuse by itself
+    auto validate = [&]() -> b200q_status {
+        if (!src0_local || !src1 || !ids || !dst) return fail(ctx, B200Q_INVALID, "expert-parallel MUL_MAT_ID: null tensor");
+        if (n_expert_total <= 0 || n_expert_total % G || src0_local->ne[2] != n_expert_total / G)
+            return fail(ctx, B200Q_INVALID, "experts: %d in total over %d ranks, %lld here", n_expert_total, G,
+                        (long long)src0_local->ne[2]);
+        if (n_expert_total > 4096 || G > 64) return fail(ctx, B200Q_UNSUPPORTED, "expert-parallel limits: 4096 experts, 64 ranks");
+        if (ids->type != B200Q_TYPE_I32 || src1->type != B200Q_TYPE_F32 || dst->type != B200Q_TYPE_F32 || src1->nb[0] != 4 ||
+            dst->nb[0] != 4 || (uintptr_t)src1->data % 16 || src1->nb[1] % 16 || src1->nb[2] % 16 || src1->ne[0] % 4)
+            return fail(ctx, B200Q_UNSUPPORTED, "expert-parallel MUL_MAT_ID needs packed f32 activations and i32 ids");
+        n_local = n_expert_total / G;
+        n_used = (int)ids->ne[0];
+        n_tok = (int)ids->ne[1];
+        K = src0_local->ne[0];
+        M = src0_local->ne[1];
+        n_pairs = n_used * n_tok;
+        if (src1->ne[0] != K || dst->ne[0] != M || dst->ne[1] != n_used || dst->ne[2] != n_tok ||
+            (src1->ne[1] != 1 && src1->ne[1] != n_used) || src1->ne[2] != n_tok)
+            return fail(ctx, B200Q_INVALID, "expert-parallel MUL_MAT_ID shapes");
+        if (cudaSetDevice(ctx->device) != cudaSuccess) return fail(ctx, B200Q_CUDA_ERROR, "cudaSetDevice(%d)", ctx->device);
+        return B200Q_OK;
+    };
+    // B200Q_EP_INJECT_FAIL=<rank>:<stage> makes that rank report a host-side error at agreement <stage> (0 counts,
+    // 1 dispatch, 2 combine): how the multi-GPU test exercises the joint exit without any device fault
+    auto injected = [&](int stage, b200q_status s) -> b200q_status {
+        int r = -1, g = -1;
+        const char *inj = getenv("B200Q_EP_INJECT_FAIL");                 // read per call: the NCCL form synchronises anyway
+        if (s == B200Q_OK && inj && sscanf(inj, "%d:%d", &r, &g) == 2 && r == tp->rank && g == stage)
+            return fail(ctx, B200Q_INVALID, "injected failure at stage %d", stage);
+        return s;
+    };
+    b200q_status local = validate();
 
-    // 1. route by global expert (which groups by owner) and count pairs per owner
     RouteView rv;
-    if ((st = moe_route(ctx, ids, n_expert_total, &rv, n_local)) != B200Q_OK) return st;
-    // device-initiated exchange over peer memory when the regions are reserved and this call fits them
-    if (tp->ep_ok && n_pairs <= tp->ep_cap && K <= tp->ep_k && M <= tp->ep_m && K % 4 == 0 && M % 4 == 0 &&
-        (uintptr_t)dst->data % 16 == 0 && dst->nb[1] % 16 == 0 && dst->nb[2] % 16 == 0 && G <= EP_MAX_RANKS) {
+    if (local == B200Q_OK) local = moe_route(ctx, ids, n_expert_total, &rv, n_local);
+    if (tp->ep_ok) {
+        if (local != B200Q_OK) return local;
+        // regions are reserved: a call that does not fit them is refused here, on this rank alone, rather than sent
+        // down the NCCL form while the peers run the peer-memory form
+        if (!(n_pairs <= tp->ep_cap && K <= tp->ep_k && M <= tp->ep_m && K % 4 == 0 && M % 4 == 0 && (uintptr_t)dst->data % 16 == 0 &&
+              dst->nb[1] % 16 == 0 && dst->nb[2] % 16 == 0 && G <= EP_MAX_RANKS))
+            return fail(ctx, B200Q_INVALID, "expert-parallel call outside the reserved bounds (%lld pairs, rows %lld / %lld): b200q_ep_reserve again",
+                        (long long)tp->ep_cap, (long long)tp->ep_k, (long long)tp->ep_m);
+    }
+    // device-initiated exchange over peer memory when the regions are reserved
+    if (tp->ep_ok) {
         EpLayout L;
         L.cap = tp->ep_cap;
         L.K = K;
@@ -602,39 +653,66 @@ b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local,
         count(ctx, ST_EP_COMBINE);
         return B200Q_OK;
     }
-    // 2. everyone learns everyone's counts
-    if ((st = ws_reserve(ctx, &ctx->moe_ws[0], sizeof(int32_t) * (size_t)G * G)) != B200Q_OK) return st;
-    int32_t *all_counts = (int32_t *)ctx->moe_ws[0].ptr;
-    B200Q_NCCL(ctx, api, api->AllGather(rv.owner_counts, all_counts, (size_t)G, ncclInt32, tp->comm, ctx->stream));
-    std::vector<int32_t> h((size_t)G * G);
-    B200Q_CUDA(ctx, cudaMemcpyAsync(h.data(), all_counts, sizeof(int32_t) * h.size(), cudaMemcpyDeviceToHost, ctx->stream));
-    B200Q_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // 2. everyone learns everyone's counts, and whether every rank got this far (ep_agree.h)
+    const int REC = G + 1;
+    int32_t *gathered = tp->agree_dev, *mine = tp->agree_dev + (size_t)G * REC;
+    std::vector<int32_t> h((size_t)G * REC);
+    // One agreement round: this rank's record (its per-owner counts when it has them, its status word) goes to every
+    // rank; B200Q_OK only when all ranks reported B200Q_OK. A CUDA or NCCL failure inside the round itself cannot be
+    // agreed on and is returned as it is.
+    auto agree = [&](int stage, b200q_status mine_st, const int32_t *dev_counts) -> b200q_status {
+        mine_st = injected(stage, mine_st);
+        tp->agree_host = (int32_t)mine_st;
+        if (dev_counts) B200Q_CUDA(ctx, cudaMemcpyAsync(mine, dev_counts, sizeof(int32_t) * G, cudaMemcpyDeviceToDevice, ctx->stream));
+        else B200Q_CUDA(ctx, cudaMemsetAsync(mine, 0, sizeof(int32_t) * G, ctx->stream));
+        B200Q_CUDA(ctx, cudaMemcpyAsync(mine + G, &tp->agree_host, sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream));
+        B200Q_NCCL(ctx, api, api->AllGather(mine, gathered, (size_t)REC, ncclInt32, tp->comm, ctx->stream));
+        B200Q_CUDA(ctx, cudaMemcpyAsync(h.data(), gathered, sizeof(int32_t) * h.size(), cudaMemcpyDeviceToHost, ctx->stream));
+        B200Q_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        int who = -1;
+        const int verdict = ep_agree_decide(h.data(), G, REC, G, tp->rank, (int)B200Q_PEER_FAILED, &who);
+        if (verdict == 0) return B200Q_OK;
+        count(ctx, ST_EP_AGREED_EXIT);
+        if (verdict == (int)B200Q_PEER_FAILED)
+            return fail(ctx, B200Q_PEER_FAILED, "rank %d reported status %d at stage %d of the expert-parallel call; every rank leaves", who,
+                        (int)h[(size_t)who * REC + G], stage);
+        return (b200q_status)verdict;                        // this rank's own error: its message is already recorded
+    };
+    if (ctx->capturing) local = local != B200Q_OK ? local : fail(ctx, B200Q_UNSUPPORTED, "the NCCL form of expert parallelism synchronises: not capturable");
+    if ((st = agree(0, local, local == B200Q_OK ? rv.owner_counts : nullptr)) != B200Q_OK) return st;
     std::vector<size_t> so(G), sb(G), ro(G), rb(G), zo(G), zb(G), wo(G), wb(G);
     size_t n_send = 0, n_recv = 0;
     for (int g = 0; g < G; ++g) {
-        const size_t cs = (size_t)h[(size_t)tp->rank * G + g], cr = (size_t)h[(size_t)g * G + tp->rank];
+        const size_t cs = (size_t)h[(size_t)tp->rank * REC + g], cr = (size_t)h[(size_t)g * REC + tp->rank];
         so[g] = n_send; sb[g] = cs; ro[g] = n_recv; rb[g] = cr;
         n_send += cs;
         n_recv += cr;
     }
-    if ((int64_t)n_send != n_pairs) return fail(ctx, B200Q_INVALID, "route counted %zu of %d pairs", n_send, n_pairs);
-    // 3. pack and dispatch
+    // 3. scratch and packing are rank-local too: agree again before the first exchange
     const size_t rowx = (size_t)K * 4, rowy = (size_t)M * 4;
-    if ((st = ws_reserve(ctx, &ctx->moe_ws[1], rowx * (n_send ? n_send : 1))) != B200Q_OK) return st;
-    if ((st = ws_reserve(ctx, &ctx->moe_ws[2], 4 * (n_send ? n_send : 1))) != B200Q_OK) return st;
-    if ((st = ws_reserve(ctx, &ctx->moe_ws[3], rowx * (n_recv ? n_recv : 1))) != B200Q_OK) return st;
-    if ((st = ws_reserve(ctx, &ctx->moe_ws[4], 4 * (n_recv ? n_recv : 1))) != B200Q_OK) return st;
-    if ((st = ws_reserve(ctx, &ctx->moe_ws[5], rowy * (n_recv ? n_recv : 1))) != B200Q_OK) return st;
-    if ((st = ws_reserve(ctx, &ctx->moe_ws[6], rowy * (n_send ? n_send : 1))) != B200Q_OK) return st;
-    float *send_x = (float *)ctx->moe_ws[1].ptr, *recv_x = (float *)ctx->moe_ws[3].ptr;
-    int32_t *send_e = (int32_t *)ctx->moe_ws[2].ptr, *recv_e = (int32_t *)ctx->moe_ws[4].ptr;
-    float *out = (float *)ctx->moe_ws[5].ptr, *back = (float *)ctx->moe_ws[6].ptr;
-    if ((st = launch_ep_pack(ctx, src1, ids, n_expert_total, n_local, rv.pairs, send_x, send_e)) != B200Q_OK) return st;
+    float *send_x = nullptr, *recv_x = nullptr, *out = nullptr, *back = nullptr;
+    int32_t *send_e = nullptr, *recv_e = nullptr;
+    auto prepare = [&]() -> b200q_status {
+        if ((int64_t)n_send != n_pairs) return fail(ctx, B200Q_INVALID, "route counted %zu of %d pairs", n_send, n_pairs);
+        b200q_status r;
+        if ((r = ws_reserve(ctx, &ctx->moe_ws[1], rowx * (n_send ? n_send : 1))) != B200Q_OK) return r;
+        if ((r = ws_reserve(ctx, &ctx->moe_ws[2], 4 * (n_send ? n_send : 1))) != B200Q_OK) return r;
+        if ((r = ws_reserve(ctx, &ctx->moe_ws[3], rowx * (n_recv ? n_recv : 1))) != B200Q_OK) return r;
+        if ((r = ws_reserve(ctx, &ctx->moe_ws[4], 4 * (n_recv ? n_recv : 1))) != B200Q_OK) return r;
+        if ((r = ws_reserve(ctx, &ctx->moe_ws[5], rowy * (n_recv ? n_recv : 1))) != B200Q_OK) return r;
+        if ((r = ws_reserve(ctx, &ctx->moe_ws[6], rowy * (n_send ? n_send : 1))) != B200Q_OK) return r;
+        send_x = (float *)ctx->moe_ws[1].ptr; recv_x = (float *)ctx->moe_ws[3].ptr;
+        send_e = (int32_t *)ctx->moe_ws[2].ptr; recv_e = (int32_t *)ctx->moe_ws[4].ptr;
+        out = (float *)ctx->moe_ws[5].ptr; back = (float *)ctx->moe_ws[6].ptr;
+        return launch_ep_pack(ctx, src1, ids, n_expert_total, n_local, rv.pairs, send_x, send_e);
+    };
+    if ((st = agree(1, prepare(), nullptr)) != B200Q_OK) return st;
     for (int g = 0; g < G; ++g) { zo[g] = so[g] * rowx; zb[g] = sb[g] * rowx; wo[g] = ro[g] * rowx; wb[g] = rb[g] * rowx; }
     if ((st = b200q_all_to_all_v(ctx, send_x, zo.data(), zb.data(), recv_x, wo.data(), wb.data())) != B200Q_OK) return st;
     for (int g = 0; g < G; ++g) { zo[g] = so[g] * 4; zb[g] = sb[g] * 4; wo[g] = ro[g] * 4; wb[g] = rb[g] * 4; }
     if ((st = b200q_all_to_all_v(ctx, send_e, zo.data(), zb.data(), recv_e, wo.data(), wb.data())) != B200Q_OK) return st;
     // 4. the local experts over everything received: one slot per received pair
+    b200q_status prod = B200Q_OK;
     if (n_recv) {
         b200q_tensor x1, id1, y1;
         x1.id = id1.id = y1.id = nullptr;
@@ -654,12 +732,12 @@ b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local,
         const uint64_t caller_gen = ctx->generation;
         ctx->generation = (1ull << 62) + ++ctx->private_generation;
         ctx->route_pinned = rv.slot;                      // rv.pairs is read again after the local product
-        st = b200q_mul_mat_id(ctx, src0_local, &x1, &id1, &y1);
+        prod = b200q_mul_mat_id(ctx, src0_local, &x1, &id1, &y1);
         ctx->route_pinned = -1;
         ctx->generation = caller_gen;
-        if (st != B200Q_OK) return st;
     }
-    // 5. combine: results travel back the way the activations came
+    // 5. combine: results travel back the way the activations came -- if every rank's product went through
+    if ((st = agree(2, prod, nullptr)) != B200Q_OK) return st;
     for (int g = 0; g < G; ++g) { zo[g] = ro[g] * rowy; zb[g] = rb[g] * rowy; wo[g] = so[g] * rowy; wb[g] = sb[g] * rowy; }
     if ((st = b200q_all_to_all_v(ctx, out, zo.data(), zb.data(), back, wo.data(), wb.data())) != B200Q_OK) return st;
     b200q::count(ctx, ST_EP_COMBINE);

@@ -43,7 +43,8 @@ typedef enum {
     B200Q_CUDA_ERROR = 3,
     B200Q_NO_MEMORY = 4,
     B200Q_NCCL_ERROR = 5,
-    B200Q_TIMEOUT = 6        /* a bounded device-side wait gave up                   */
+    B200Q_TIMEOUT = 6,       /* a bounded device-side wait gave up                   */
+    B200Q_PEER_FAILED = 7    /* a collective call that every rank left together because another rank reported an error */
 } b200q_status;
 
 /* ggml type ids (ggml.h enum ggml_type) */
@@ -178,7 +179,12 @@ B200Q_API b200q_status b200q_all_to_all_v(b200q_ctx *ctx, const void *dev_send, 
  * [K, M, n_expert_total / nranks]; src1, ids (global expert ids) and dst are this rank's tokens.
  * After b200q_ep_reserve dispatch and combine are the library's own kernels over peer memory; otherwise they are
  * NCCL all-to-alls and the call synchronizes the stream once (the exchange sizes must reach the host).
- * Every rank must make the same sequence of calls (the ranks wait for one another inside them). */
+ * Every rank must make the same sequence of calls (the ranks wait for one another inside them).
+ * Errors: in the NCCL form no rank leaves between collectives alone -- a rank-local error travels as a status word
+ * beside the exchange sizes, and again before dispatch and combine, and every rank returns from the same point, the
+ * failing rank with its own status, the others with B200Q_PEER_FAILED; the communicator stays usable. In the peer-memory
+ * form a failing rank returns at once and the others' bounded waits end in B200Q_TIMEOUT; a call outside the reserved
+ * bounds is B200Q_INVALID on the rank that made it. */
 B200Q_API b200q_status b200q_mul_mat_id_ep(b200q_ctx *ctx, const b200q_tensor *src0_local, const b200q_tensor *src1,
                                            const b200q_tensor *ids, b200q_tensor *dst, int n_expert_total);
 /* Collective (every rank, same arguments): reserves and maps, on every rank, the regions of peer memory that let

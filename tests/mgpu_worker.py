@@ -152,6 +152,26 @@ def main():
                 got = ctx.download(dy, (n_tok, n_used, m), np.float32)
                 ep_errs.append(rel_err(got.reshape(-1, m), want))
                 assert ep_errs[-1] < TOL, ("expert parallel", mode, t, rep, ep_errs[-1])
+            if mode == "nccl" and (t, n_tok) == (A.Q4_0, 37 + rank):
+                # a host-injected error on the last rank at each of the three agreement points: every rank must come
+                # back from the call (nobody waits in a collective for a rank that left), the failing rank with its
+                # own status, the others with PEER_FAILED; the next call is an ordinary one and must be right
+                for stage in range(3):
+                    os.environ["B200Q_EP_INJECT_FAIL"] = "%d:%d" % (world - 1, stage)
+                    try:
+                        ctx.mul_mat_id_ep(src0, X, I, Y, n_exp)
+                        status = A.binding.OK
+                    except A.B200QError as e:
+                        status = e.status
+                    finally:
+                        del os.environ["B200Q_EP_INJECT_FAIL"]
+                    assert status == (A.binding.INVALID if rank == world - 1 else A.binding.PEER_FAILED), (stage, rank, status)
+                    ctx.graph_begin()
+                    ctx.upload(np.zeros((n_tok, n_used, m), dtype=np.float32), dy)
+                    ctx.mul_mat_id_ep(src0, X, I, Y, n_exp)
+                    got = ctx.download(dy, (n_tok, n_used, m), np.float32)
+                    assert rel_err(got.reshape(-1, m), want) < TOL, ("after an agreed exit", stage)
+                assert ctx.stats().get("ep_agreed_exit") == 3, ctx.stats()
             for ptr in (dw, dx, di, dy):
                 ctx.free(ptr)
         dist.barrier()

@@ -104,3 +104,66 @@ def test_splits_world_size_2_gloo():
         assert p.exitcode == 0
     res = dict(q.get(timeout=5) for _ in range(2))
     assert res == {0: True, 1: True}
+
+
+def _agree_worker(rank, world, port, q, fail_rank, fail_stage):
+    """A replay of the NCCL form of b200q_mul_mat_id_ep's control flow on gloo ranks: three agreement rounds
+    (after the counts, before the dispatch, before the combine) decided by the library's own rule
+    (ep_agree_decide, through the host replay). One rank reports a host-side error at one stage."""
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    from arcint_b200 import build as B
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        E = C.CDLL(B.build_emul())
+        E.emul_ep_agree.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int)]
+        rec = world + 1
+        left_at, status, exchanges = None, A.binding.OK, 0
+        for stage in range(3):
+            mine = torch.zeros(rec, dtype=torch.int32)
+            mine[:world] = torch.arange(world, dtype=torch.int32) + 10 * rank          # the per-owner counts
+            mine[world] = A.binding.INVALID if (rank == fail_rank and stage == fail_stage) else A.binding.OK
+            allr = [torch.empty(rec, dtype=torch.int32) for _ in range(world)]
+            dist.all_gather(allr, mine)
+            flat = torch.cat(allr).numpy().copy()
+            who = C.c_int(-2)
+            v = E.emul_ep_agree(flat.ctypes.data, world, rec, world, rank, A.binding.PEER_FAILED, C.byref(who))
+            if v != 0:
+                left_at, status = stage, v
+                assert who.value == fail_rank
+                break
+            # the collective that follows the agreement: every rank that got here must find all the others here
+            t = torch.ones(1)
+            dist.all_reduce(t)
+            assert int(t.item()) == world
+            exchanges += 1
+        q.put((rank, left_at, int(status), exchanges))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fail_rank,fail_stage", [(1, 0), (0, 1), (1, 2), (-1, -1)])
+def test_ep_ranks_leave_together_gloo(fail_rank, fail_stage):
+    """No rank of an expert-parallel call leaves between collectives alone: with a host-injected error on one rank
+    at one stage, both ranks stop at that stage -- the failing rank with its own status, the other with PEER_FAILED --
+    and every collective before it saw both ranks."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + (os.getpid() + 7 * (fail_rank + 2) + 3 * (fail_stage + 2)) % 2000
+    procs = [ctx.Process(target=_agree_worker, args=(r, 2, port, q, fail_rank, fail_stage)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+        assert p.exitcode == 0
+    res = {r: (at, st, ex) for r, at, st, ex in (q.get(timeout=5) for _ in range(2))}
+    if fail_rank < 0:
+        assert res == {0: (None, A.binding.OK, 3), 1: (None, A.binding.OK, 3)}
+    else:
+        other = 1 - fail_rank
+        assert res[fail_rank] == (fail_stage, A.binding.INVALID, fail_stage)
+        assert res[other] == (fail_stage, A.binding.PEER_FAILED, fail_stage)
