@@ -61,9 +61,14 @@ static_assert(128 * 40 + 256 * 72 + 128 * NW * 144 <= THREADS * LAUNCH_REGS, "re
 constexpr int OPER_BYTES = BM * KB;                       // 4096
 // The activation chunk of a (column tile, super-block) is laid out by groups of eight columns, so a tile
 // with few columns (a route tile of a small expert) is a short prefix of it:
-//   group g < 16: [block j < 8][half c < 2][column r < 8][16 bytes] int8 codes (2048 B), then 8 f32 scales
-constexpr int ACT_GROUP = SB * 2 * 128 + 8 * 4;           // 2080
-constexpr int ACT_CHUNK = (BN / 8) * ACT_GROUP;           // 33280
+//   group g < 16: [block j < 8][half c < 2][column r < 8][16 bytes] int8 codes (2048 B), then 8 f32 scales, then per
+//   column the eight block sums as int8 digit pairs, bsum_j = 256 bh_j + bl_j: [column r < 8][bl_0..7, bh_0..7]
+//   (what Q4_K's mins term needs when it is taken inside the GEMM: route tiles)
+constexpr int ACT_SCALES = SB * 2 * 128;                  // 2048: offset of the scales in a group
+constexpr int ACT_DIGITS = ACT_SCALES + 8 * 4;            // 2080: offset of the block-sum digits
+constexpr int ACT_GROUP = ACT_DIGITS + 8 * 16;            // 2208
+constexpr int ACT_CHUNK = (BN / 8) * ACT_GROUP;           // 35328
+static_assert(ACT_GROUP % 16 == 0 && ACT_CHUNK % 128 == 0, "bulk copies and MMA descriptors");
 constexpr int A_SLOT = 2 * OPER_BYTES;                    // hi limb, lo limb
 
 // Per type: bytes of a super-block, super-blocks per raw stage (the stage's row piece must be a
@@ -139,6 +144,7 @@ quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t n
     const float bm = fmaxf(part[col], part[col + 128]);
     const float iq = bm > 1e-30f ? __fdiv_rn(127.f, bm) : 0.f;
     if (!store) return;
+    uint32_t dig_l = 0, dig_h = 0;
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
         const int j = 4 * half + jj;
@@ -157,8 +163,15 @@ quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t n
 #pragma unroll
         for (int i = 0; i < 8; ++i) sum = __dp4a((int)w[i], 0x01010101, sum);
         bsum[(((size_t)t * nst + s) * BN + col) * 8 + j] = (int16_t)sum;
+        // ... and as two int8 digits inside the chunk: bh = round(sum / 256), bl = sum - 256 bh in [-128, 127]
+        const int bh = (sum + 128) >> 8, bl = sum - 256 * bh;
+        dig_l |= (uint32_t)(bl & 0xFF) << (8 * jj);
+        dig_h |= (uint32_t)(bh & 0xFF) << (8 * jj);
     }
-    if (half == 0) reinterpret_cast<float *>(chunk + (col >> 3) * ACT_GROUP + 2048)[col & 7] = __fdiv_rn(bm, 127.f);
+    uint8_t *dg = chunk + (col >> 3) * ACT_GROUP + ACT_DIGITS + (col & 7) * 16;
+    reinterpret_cast<uint32_t *>(dg)[half] = dig_l;                      // bl of blocks 4 half .. 4 half + 3
+    reinterpret_cast<uint32_t *>(dg)[2 + half] = dig_h;
+    if (half == 0) reinterpret_cast<float *>(chunk + (col >> 3) * ACT_GROUP + ACT_SCALES)[col & 7] = __fdiv_rn(bm, 127.f);
 }
 
 // The A-operand blocks of one group (GB = 4 blocks of 32 weights) of a super-block, written by the
@@ -257,7 +270,7 @@ template <int TYPE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
                int N, int n_tiles_dense, int ksplit, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word,
-               TileRoute id) {
+               TileRoute id, int fold) {
     typedef Smem<TYPE> L;
     constexpr int SBB = L::SBB, SPS = L::SPS, NRAW = L::NRAW, ROWB = L::ROWB;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -265,6 +278,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nsb = K / 256;                    // super-blocks (a multiple of SPS: the host gate)
+    const bool fold_mins = fold != 0;           // MUL_MAT_ID: Q4_K's mins term is taken in the scale-accumulate warps
     // A dense product whose tiles fill the SMs badly (a last, nearly empty wave) is cut in two along K: a unit is
     // then half the super-blocks of a tile and adds its result to a zeroed dst (two addends: the order cannot matter).
     const int nsu = nsb / ksplit;               // super-blocks per unit
@@ -442,6 +456,10 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
             const Unit U = unit_of(u);
             const bool row_ok = r < U.valid_rows;
+            // The tile's columns are shared out between the two warps of a row quadrant: 64 each for a full tile, and
+            // for a short one (the ragged end, a route tile of a small expert) half of what there is, in steps of 16.
+            const int cw_eff = U.ncols > CW ? CW : max(16, (((U.ncols + 1) >> 1) + 15) & ~15);
+            const int cbase = u4 * cw_eff;
             f32x2 acc2[CW / 2];
 #pragma unroll
             for (int c = 0; c < CW / 2; ++c) acc2[c] = 0ull;
@@ -458,9 +476,19 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                                                smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + ((s / SPS) * SPS * SBB) % 16 +
                                                SBB * (s % SPS) + Fmt<TYPE>::D_OFF)) : 0.f;
                 const f32x2 dw2 = f2_pack(dwb, dwb);
-                const uint32_t dxa = sbase + L::ACT_OFF + at * ACT_CHUNK + (u4 * CW / 8) * ACT_GROUP + 2048;   // scales of this thread's first group
-                const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * (2 * BN) + (uint32_t)u4 * CW;
-                const int ncol = U.ncols - u4 * CW;          // this thread's columns inside the tile (warp-uniform)
+                // Q4_K route tiles take the mins term here (a short tile leaves these warps idle most of the time, and
+                // a separate pass would read and write all of dst again): the row's eight mins and -dmin
+                uint32_t m03 = 0, m47 = 0;
+                f32x2 ndm2 = 0ull;
+                if (TYPE == B200Q_TYPE_Q4_K && fold_mins) {
+                    const uint4 hdr = *reinterpret_cast<const uint4 *>(smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB);
+                    q4k_mins8(hdr.y, hdr.z, hdr.w, &m03, &m47);
+                    const float ndm = row_ok ? -half_bits_to_float((uint16_t)(hdr.x >> 16)) : 0.f;
+                    ndm2 = f2_pack(ndm, ndm);
+                }
+                const uint32_t dxa = sbase + L::ACT_OFF + at * ACT_CHUNK + (cbase / 8) * ACT_GROUP + ACT_SCALES;   // scales of this thread's first group
+                const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * (2 * BN) + (uint32_t)cbase;
+                const int ncol = min(cw_eff, U.ncols - cbase);   // this thread's columns inside the tile (warp-uniform)
 #pragma unroll
                 for (int q = 0; q < CW / 16; ++q) {
                     if (q * 16 >= ncol) {                    // a short tile (the ragged end, a small expert): nothing to scale
@@ -490,13 +518,39 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                         acc2[e]     = f2_fma(s01, f2_mul(dw2, dx[c / 2]), acc2[e]);
                         acc2[e + 1] = f2_fma(s23, f2_mul(dw2, dx[c / 2 + 1]), acc2[e + 1]);
                     }
+                    if (TYPE == B200Q_TYPE_Q4_K && fold_mins) {
+                        // - dmin d_x sum_j m_j bsum_j per live column: the digits come by broadcast loads from the
+                        // chunk, four dp4a per column (as q4k_mins_rows_kernel, without its pass over dst). Eight
+                        // columns' loads are issued together and their chains are independent, so the latencies overlap.
+                        const uint32_t dga = dxa - ACT_SCALES + ACT_DIGITS + (2 * q) * ACT_GROUP;
+#pragma unroll
+                        for (int g8 = 0; g8 < 2; ++g8) {
+                            if (q * 16 + 8 * g8 < ncol) {        // warp-uniform
+                                uint4 dg[8];
+#pragma unroll
+                                for (int c = 0; c < 8; ++c) dg[c] = *reinterpret_cast<const uint4 *>(smem + (dga - sbase) + g8 * ACT_GROUP + c * 16);
+                                float t[8];
+#pragma unroll
+                                for (int c = 0; c < 8; ++c) {
+                                    const int lo = __dp4a((int)m47, (int)dg[c].y, __dp4a((int)m03, (int)dg[c].x, 0));
+                                    const int hi = __dp4a((int)m47, (int)dg[c].w, __dp4a((int)m03, (int)dg[c].z, 0));
+                                    t[c] = __int2float_rn(lo + (hi << 8));
+                                }
+#pragma unroll
+                                for (int c = 0; c < 8; c += 2) {
+                                    const int e = (q * 16 + 8 * g8 + c) / 2;
+                                    acc2[e] = f2_fma(f2_pack(t[c], t[c + 1]), f2_mul(ndm2, dx[(8 * g8 + c) / 2]), acc2[e]);
+                                }
+                            }
+                        }
+                    }
                 }
                 mbar_arrive_warp(bar(BAR_ACT_EMPTY + at), lane);
                 if (s % SPS == SPS - 1) mbar_arrive_warp(bar(BAR_RAW_EMPTY + st), lane);
             }
             ++rs_run;                                    // past the unit's last raw stage
             if (ok) {
-                const int ncol = U.ncols - u4 * CW;          // this thread's columns inside the tile
+                const int ncol = min(cw_eff, U.ncols - cbase);   // this thread's columns inside the tile
                 if (id.tiles) {
                     // where the warp's 64 columns go: every lane looks up two of them (loads in flight
                     // together), the store loop takes them by shuffle -- a load and a division per column
@@ -506,7 +560,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                     for (int h = 0; h < 2; ++h) {
                         off[h] = 0;
                         if (lane + 32 * h < ncol) {
-                            const int p = __ldg(id.pairs + U.first + u4 * CW + lane + 32 * h), tok = p / id.n_used, slot = p - tok * id.n_used;
+                            const int p = __ldg(id.pairs + U.first + cbase + lane + 32 * h), tok = p / id.n_used, slot = p - tok * id.n_used;
                             off[h] = tok * id.ld2 + slot * id.ld1;
                         }
                     }
@@ -521,7 +575,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                         }
                     }
                 } else if (row_ok) {
-                    float *o = dst + (int64_t)(U.tile_n * BN + u4 * CW) * ldd + U.row0 + r;
+                    float *o = dst + (int64_t)(U.tile_n * BN + cbase) * ldd + U.row0 + r;
 #pragma unroll
                     for (int c = 0; c < CW; c += 2) {
                         float a0, a1;
@@ -611,7 +665,7 @@ q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_str
     auto fetch = [&](int sb) {
         const size_t chunk = (size_t)tile * nsb + sb;
         sv = __ldg(reinterpret_cast<const int4 *>(bsum + (chunk * BN + cc) * 8));
-        dxv = __ldg(reinterpret_cast<const float *>(act + chunk * ACT_CHUNK + (cc >> 3) * ACT_GROUP + 2048) + (cc & 7));
+        dxv = __ldg(reinterpret_cast<const float *>(act + chunk * ACT_CHUNK + (cc >> 3) * ACT_GROUP + ACT_SCALES) + (cc & 7));
     };
     if (col_ok) fetch(0);
     for (int sb = 0; sb < nsb; ++sb) {
@@ -749,7 +803,7 @@ q4k_mins_rows_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t ma
                     w[i >> 2] |= (uint32_t)(bl & 0xFF) << (8 * (i & 3));
                     w[2 + (i >> 2)] |= (uint32_t)(bh & 0xFF) << (8 * (i & 3));
                 }
-                dx = reinterpret_cast<const float *>(act + chunk * ACT_CHUNK + (cc >> 3) * ACT_GROUP + 2048)[cc & 7];
+                dx = reinterpret_cast<const float *>(act + chunk * ACT_CHUNK + (cc >> 3) * ACT_GROUP + ACT_SCALES)[cc & 7];
             }
             *reinterpret_cast<uint4 *>(cs[pb][threadIdx.x]) = make_uint4(w[0], w[1], w[2], w[3]);
             cdx[pb][threadIdx.x] = dx;
@@ -869,17 +923,21 @@ static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride
         units *= 2;
     }
     const unsigned grid = (unsigned)(units < S ? units : S);
+    // route tiles of Q4_K: the mins term inside the GEMM (B200Q_MOE_MINS_PASS=1 keeps the separate pass, for comparison)
+    const int fold = TYPE == B200Q_TYPE_Q4_K && tr.tiles && !ctx->moe_mins_pass;
     kern<<<grid, kq::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, (int)n_tiles, ksplit, dst, ldd,
-                                                       ctx->error_word, tr);
+                                                       ctx->error_word, tr, fold);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
     if (TYPE == B200Q_TYPE_Q4_K) {
         // the mins term, subtracted in place
         const int16_t *bsum = reinterpret_cast<const int16_t *>(act + (size_t)(n_tiles * (K / 256)) * kq::ACT_CHUNK);
-        if (tr.tiles) {
+        if (tr.tiles && ctx->moe_mins_pass) {
             dim3 g2((unsigned)(n_tiles * (kq::BN / kq::MC)), (unsigned)((M + 127) / 128));
             kq::q4k_mins_rows_kernel<<<g2, 128, 0, ctx->stream>>>((const uint8_t *)w, row_stride, mat_stride, (int)M, (int)(K / 256), act,
                                                                  bsum, (int)N, dst, ldd, tr);
+        } else if (tr.tiles) {
+            return B200Q_OK;                     // route tiles: the term was taken inside the GEMM
         } else {
             dim3 g2((unsigned)(n_tiles * (kq::BN / kq::MC)), (unsigned)((M + kq::MR - 1) / kq::MR));
             kq::q4k_mins_kernel<<<g2, 128, 0, ctx->stream>>>((const uint8_t *)w, row_stride, mat_stride, (int)M, (int)(K / 256), act, bsum,
