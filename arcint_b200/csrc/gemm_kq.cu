@@ -109,69 +109,73 @@ static_assert(NG == 2 && NACT == 2 && NBUF == 2, "barrier slots above");
 __global__ void __launch_bounds__(256)
 quantize_tiled256_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t nb1, size_t nb2, size_t nb3, int64_t K,
                          int64_t N, uint8_t *__restrict__ out, int16_t *__restrict__ bsum, TileRoute id) {
-    __shared__ float part[256];
+    // One block per (tile, super-block); a half-warp per column at a time: its sixteen lanes read the column's 256
+    // floats as one contiguous kilobyte (lane l: elements 16 l .. 16 l + 15, i.e. half c = l & 1 of block j = l >> 1),
+    // take the maximum by shuffles and store one 16-byte piece each. Columns of groups past the tile's last one are
+    // never fetched by the GEMM and are skipped; the dead columns of the last live group are written as zeros.
     const int t = blockIdx.y, s = blockIdx.x, nst = gridDim.x;
-    const int col = threadIdx.x & 127, half = threadIdx.x >> 7;
+    const int hw = threadIdx.x >> 4, l = threadIdx.x & 15;
     uint8_t *chunk = out + ((size_t)t * nst + s) * ACT_CHUNK;
-    const float *x = nullptr;
-    bool store = true;                                    // column groups past the tile's last one are never fetched
+    int cnt, first = 0;
     if (id.tiles) {
         // MUL_MAT_ID: the tile's columns are routed pairs; pair p = (token, slot) reads src1 row slot % ne11
         if (t >= __ldg(id.n_tiles)) return;
-        const int cnt = __ldg(id.tiles + 4 * t + 2);
-        store = (col >> 3) <= ((cnt - 1) >> 3);
-        if (col < cnt) {
-            const int p = __ldg(id.pairs + __ldg(id.tiles + 4 * t + 1) + col), tok = p / id.n_used, slot = p - tok * id.n_used;
-            x = reinterpret_cast<const float *>(base + (size_t)(slot % id.ne11) * id.nb1 + (size_t)tok * id.nb2) + (int64_t)s * 256 + 128 * half;
-        }
+        first = __ldg(id.tiles + 4 * t + 1);
+        cnt = __ldg(id.tiles + 4 * t + 2);
     } else {
-        const int64_t n = (int64_t)t * BN + col;
-        if (n < N) {
-            const int64_t c1 = n % ne1, c23 = n / ne1, c2 = c23 % ne2, c3 = c23 / ne2;
-            x = reinterpret_cast<const float *>(base + c1 * nb1 + c2 * nb2 + c3 * nb3) + (int64_t)s * 256 + 128 * half;
+        const int64_t left = N - (int64_t)t * BN;
+        cnt = left < BN ? (int)left : BN;
+    }
+    const int live = ((cnt + 7) >> 3) << 3;
+    for (int col = hw; col < live; col += 16) {
+        const float *x = nullptr;
+        if (col < cnt) {
+            if (id.tiles) {
+                const int p = __ldg(id.pairs + first + col), tok = p / id.n_used, slot = p - tok * id.n_used;
+                x = reinterpret_cast<const float *>(base + (size_t)(slot % id.ne11) * id.nb1 + (size_t)tok * id.nb2);
+            } else {
+                const int64_t n = (int64_t)t * BN + col;
+                const int64_t c1 = n % ne1, c23 = n / ne1, c2 = c23 % ne2, c3 = c23 / ne2;
+                x = reinterpret_cast<const float *>(base + c1 * nb1 + c2 * nb2 + c3 * nb3);
+            }
+            x += (int64_t)s * 256 + 16 * l;
         }
-    }
-    // the thread's 128 values stay in registers between the maximum and the rounding pass
-    float4 v[32];
-    float amax = 0.f;
+        float4 v[4];
+        float amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        v[i] = x ? __ldg(reinterpret_cast<const float4 *>(x) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
-    }
-    part[threadIdx.x] = amax;
-    __syncthreads();
-    const float bm = fmaxf(part[col], part[col + 128]);
-    const float iq = bm > 1e-30f ? __fdiv_rn(127.f, bm) : 0.f;
-    if (!store) return;
-    uint32_t dig_l = 0, dig_h = 0;
+        for (int i = 0; i < 4; ++i) {
+            v[i] = x ? __ldg(reinterpret_cast<const float4 *>(x) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+        }
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {
-        const int j = 4 * half + jj;
-        uint32_t w[8];
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        const float bm = amax;
+        const float iq = bm > 1e-30f ? __fdiv_rn(127.f, bm) : 0.f;
+        uint32_t w[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float4 f = v[8 * jj + i];
+        for (int i = 0; i < 4; ++i) {
+            const float4 f = v[i];
             w[i] = (uint32_t)(__float2int_rn(__fmul_rn(f.x, iq)) & 0xFF) | ((uint32_t)(__float2int_rn(__fmul_rn(f.y, iq)) & 0xFF) << 8) |
                    ((uint32_t)(__float2int_rn(__fmul_rn(f.z, iq)) & 0xFF) << 16) | ((uint32_t)(__float2int_rn(__fmul_rn(f.w, iq)) & 0xFF) << 24);
         }
-        uint8_t *o = chunk + (col >> 3) * ACT_GROUP + j * 256 + (col & 7) * 16;
-        *reinterpret_cast<uint4 *>(o) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4 *>(o + 128) = make_uint4(w[4], w[5], w[6], w[7]);
-        // the integer sum of the block's 32 codes (Q4_K's mins term): [chunk][column][block] int16
+        uint8_t *grp = chunk + (col >> 3) * ACT_GROUP;
+        const int j = l >> 1;
+        *reinterpret_cast<uint4 *>(grp + j * 256 + (l & 1) * 128 + (col & 7) * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        // the integer sum of the block's 32 codes (Q4_K's mins term): [chunk][column][block] int16 beside the chunks, and
+        // as two int8 digits inside the chunk: bh = round(sum / 256), bl = sum - 256 bh in [-128, 127]
         int sum = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sum = __dp4a((int)w[i], 0x01010101, sum);
-        bsum[(((size_t)t * nst + s) * BN + col) * 8 + j] = (int16_t)sum;
-        // ... and as two int8 digits inside the chunk: bh = round(sum / 256), bl = sum - 256 bh in [-128, 127]
-        const int bh = (sum + 128) >> 8, bl = sum - 256 * bh;
-        dig_l |= (uint32_t)(bl & 0xFF) << (8 * jj);
-        dig_h |= (uint32_t)(bh & 0xFF) << (8 * jj);
+        for (int i = 0; i < 4; ++i) sum = __dp4a((int)w[i], 0x01010101, sum);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+        if ((l & 1) == 0) {
+            bsum[(((size_t)t * nst + s) * BN + col) * 8 + j] = (int16_t)sum;
+            const int bh = (sum + 128) >> 8, bl = sum - 256 * bh;
+            uint8_t *dg = grp + ACT_DIGITS + (col & 7) * 16;
+            dg[j] = (uint8_t)(bl & 0xFF);
+            dg[8 + j] = (uint8_t)(bh & 0xFF);
+        }
+        if (l == 0) reinterpret_cast<float *>(grp + ACT_SCALES)[col & 7] = __fdiv_rn(bm, 127.f);
     }
-    uint8_t *dg = chunk + (col >> 3) * ACT_GROUP + ACT_DIGITS + (col & 7) * 16;
-    reinterpret_cast<uint32_t *>(dg)[half] = dig_l;                      // bl of blocks 4 half .. 4 half + 3
-    reinterpret_cast<uint32_t *>(dg)[2 + half] = dig_h;
-    if (half == 0) reinterpret_cast<float *>(chunk + (col >> 3) * ACT_GROUP + ACT_SCALES)[col & 7] = __fdiv_rn(bm, 127.f);
 }
 
 // The A-operand blocks of one group (GB = 4 blocks of 32 weights) of a super-block, written by the
@@ -288,7 +292,11 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     // The block is persistent: it walks the units blockIdx.x, blockIdx.x + gridDim.x, ... and every role
     // keeps running counters for its rings, so the pipeline never drains between units (the loads,
     // the unpacking and the MMAs of the next tile run while the last tile's results are stored).
-    // Units of one row tile are neighbours, so blocks running together share weight rows in L2.
+    // Units of one row tile are neighbours, so blocks running together share weight rows in L2 (MUL_MAT_ID: the
+    // tiles of one expert). Measured slower on the 512-expert configuration, on the same GPU: a contiguous run of
+    // units per block (+18 %: the full tiles of busy experts pile up on a few blocks), groups of four row tiles of
+    // one column tile so that its activation chunks stay in the ring (+10 % at K = 512), and fetching the next
+    // unit's description and the column destinations one unit ahead in the scale-accumulate warps (+4 / +10 %).
     const int tiles_m = (M + BM - 1) / BM;
     const int tiles_n = id.tiles ? __ldg(id.n_tiles) : n_tiles_dense;
     const int n_units = tiles_m * tiles_n * ksplit;
