@@ -103,62 +103,72 @@ template <bool F16>
 __global__ void __launch_bounds__(256)
 quantize_tiled_kernel(const uint8_t *base, int64_t ne1, int64_t ne2, size_t nb1, size_t nb2, size_t nb3, int64_t K,
                       int64_t N, uint8_t *__restrict__ out, TileRoute id) {
+    // One block per (tile, k-stage of 256); a half-warp per column at a time: its sixteen lanes read the column's 256
+    // floats as one contiguous kilobyte (lane l: k = 16 l .. 16 l + 15, i.e. half l & 1 of block j = l >> 1), the two
+    // lanes of a block share their maximum by one shuffle, and every lane stores its 16 codes as one piece (int8) or
+    // two (fp16). Columns past the tile's last one are written as zeros.
     const int t = blockIdx.y, s = blockIdx.x, nst = gridDim.x;
-    const int col = threadIdx.x & 127, half = threadIdx.x >> 7;
+    const int hw = threadIdx.x >> 4, l = threadIdx.x & 15;
     constexpr int OPER_BYTES = Oper<F16>::BYTES, ACT_CHUNK = Oper<F16>::ACT_CHUNK;
     uint8_t *chunk = out + ((size_t)t * nst + s) * ACT_CHUNK;
-    const float *x = nullptr;
+    int cnt, first = 0;
     if (id.tiles) {
         // MUL_MAT_ID: the tile's columns are routed pairs; pair p = (token, slot) reads src1 row slot % ne11
         if (t >= __ldg(id.n_tiles)) return;
-        if (col < __ldg(id.tiles + 4 * t + 2)) {
-            const int p = __ldg(id.pairs + __ldg(id.tiles + 4 * t + 1) + col), tok = p / id.n_used, slot = p - tok * id.n_used;
-            x = reinterpret_cast<const float *>(base + (size_t)(slot % id.ne11) * id.nb1 + (size_t)tok * id.nb2) + (int64_t)s * (SB * KB);
-        }
+        first = __ldg(id.tiles + 4 * t + 1);
+        cnt = __ldg(id.tiles + 4 * t + 2);
     } else {
-        const int64_t n = (int64_t)t * BN + col;
-        if (n < N) {
-            const int64_t c1 = n % ne1, c23 = n / ne1, c2 = c23 % ne2, c3 = c23 / ne2;
-            x = reinterpret_cast<const float *>(base + c1 * nb1 + c2 * nb2 + c3 * nb3) + (int64_t)s * (SB * KB);
-        }
+        const int64_t left = N - (int64_t)t * BN;
+        cnt = left < BN ? (int)left : BN;
     }
+    const int j = l >> 1;
 #pragma unroll 1
-    for (int jj = 0; jj < 4; ++jj) {
-        const int j = 4 * half + jj;
-        float v[32];
+    for (int col = hw; col < BN; col += 16) {
+        const float *x = nullptr;
+        if (col < cnt) {
+            if (id.tiles) {
+                const int p = __ldg(id.pairs + first + col), tok = p / id.n_used, slot = p - tok * id.n_used;
+                x = reinterpret_cast<const float *>(base + (size_t)(slot % id.ne11) * id.nb1 + (size_t)tok * id.nb2);
+            } else {
+                const int64_t n = (int64_t)t * BN + col;
+                const int64_t c1 = n % ne1, c23 = n / ne1, c2 = c23 % ne2, c3 = c23 / ne2;
+                x = reinterpret_cast<const float *>(base + c1 * nb1 + c2 * nb2 + c3 * nb3);
+            }
+            x += (int64_t)s * (SB * KB) + 16 * l;
+        }
+        float v[16];
         float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float4 f = x ? *reinterpret_cast<const float4 *>(x + 32 * j + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < 4; ++i) {
+            const float4 f = x ? *reinterpret_cast<const float4 *>(x + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
             v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
             amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
         }
+        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
         const float d = __fdiv_rn(amax, 127.f);
         const float id = d != 0.f ? __fdiv_rn(1.f, d) : 0.f;
         uint8_t *o = chunk + j * OPER_BYTES + (col >> 3) * 128 + (col & 7) * 16;
         if (F16) {
-            uint32_t w[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const __half2 h = __floats2half2_rn(roundf(__fmul_rn(v[2 * i], id)), roundf(__fmul_rn(v[2 * i + 1], id)));
-                w[i] = *reinterpret_cast<const uint32_t *>(&h);
-            }
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                *reinterpret_cast<uint4 *>(o + c * LBO) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
-        } else {
             uint32_t w[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
+                const __half2 h = __floats2half2_rn(roundf(__fmul_rn(v[2 * i], id)), roundf(__fmul_rn(v[2 * i + 1], id)));
+                w[i] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+            *reinterpret_cast<uint4 *>(o + (2 * (l & 1)) * LBO) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4 *>(o + (2 * (l & 1) + 1) * LBO) = make_uint4(w[4], w[5], w[6], w[7]);
+        } else {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
                 uint32_t p = 0;
 #pragma unroll
                 for (int b = 0; b < 4; ++b) p |= (uint32_t)((int)roundf(__fmul_rn(v[4 * i + b], id)) & 0xFF) << (8 * b);
                 w[i] = p;
             }
-            *reinterpret_cast<uint4 *>(o) = make_uint4(w[0], w[1], w[2], w[3]);
-            *reinterpret_cast<uint4 *>(o + LBO) = make_uint4(w[4], w[5], w[6], w[7]);
+            *reinterpret_cast<uint4 *>(o + (l & 1) * LBO) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        reinterpret_cast<float *>(chunk + SB * OPER_BYTES)[j * BN + col] = __half2float(__float2half_rn(d));
+        if ((l & 1) == 0) reinterpret_cast<float *>(chunk + SB * OPER_BYTES)[j * BN + col] = __half2float(__float2half_rn(d));
     }
 }
 
