@@ -43,7 +43,7 @@ const char *stat_name(int s) {
     static const char *rest[] = { "gemv_id", "gemv_id_unaligned", "moe_route", "route_cache_hit", "moe_gemm", "moe_pack",
                                   "gemm_tc", "gemm_tc_quantize", "gemm_fallback_shape", "tp_allreduce", "tp_allgather",
                                   "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins", "gemv_stream", "tp_allreduce_peer", "gemm_tc_f16", "ep_peer", "ep_dispatch_cached", "moe_router", "moe_ffn", "gemv_knob_ignored", "gemm_ksplit", "gemv_fused_quant", "gemv_allreduce_fused",
-                                  "ep_agreed_exit" };
+                                  "ep_agreed_exit", "gemm_kq_rowcopy" };
     return rest[s - ST_GEMV_ID];
 }
 

@@ -93,7 +93,7 @@ enum Stat {
     ST_GEMV_ID = ST_GEMV_UNALIGNED_COL0 + 9, ST_GEMV_ID_UNALIGNED, ST_MOE_ROUTE, ST_ROUTE_CACHE_HIT, ST_MOE_GEMM,
     ST_MOE_PACK, ST_GEMM_TC, ST_GEMM_TC_QUANT, ST_GEMM_FALLBACK_SHAPE, ST_TP_ALLREDUCE, ST_TP_ALLGATHER,
     ST_EP_DISPATCH, ST_EP_COMBINE, ST_GRAPH_LAUNCH, ST_NO_ALLOC, ST_GEMM_KQ_MINS, ST_GEMV_STREAM, ST_TP_ALLREDUCE_PEER, ST_GEMM_TC_F16, ST_EP_PEER, ST_EP_DISPATCH_CACHED, ST_MOE_ROUTER, ST_MOE_FFN, ST_GEMV_KNOB_IGNORED, ST_GEMM_KSPLIT, ST_GEMV_FUSED_QUANT, ST_GEMV_ALLREDUCE_FUSED,
-    ST_EP_AGREED_EXIT,
+    ST_EP_AGREED_EXIT, ST_GEMM_KQ_ROWCOPY,
     ST_COUNT
 };
 const char *stat_name(int s);

@@ -80,6 +80,10 @@ template <int TYPE> struct Fmt;
 template <> struct Fmt<B200Q_TYPE_IQ4_XS> { enum { SBB = 136, SPS = 2, NRAW = 2, BOX = 272, D_OFF = 0 }; };
 template <> struct Fmt<B200Q_TYPE_Q4_K>   { enum { SBB = 144, SPS = 1, NRAW = 4, BOX = 144, D_OFF = 0 }; };
 template <> struct Fmt<B200Q_TYPE_Q6_K>   { enum { SBB = 210, SPS = 1, NRAW = 2, BOX = 224, D_OFF = 208 }; };
+// IQ4_XS rows with an odd number of super-blocks (K = 11008: 5848-byte rows) are 8-byte multiples only: they are staged
+// row by row, one super-block per stage, the slot 8 bytes wider than the block (format variant FMT_IQ4_XS_ROWS).
+constexpr int FMT_IQ4_XS_ROWS = 1000 + B200Q_TYPE_IQ4_XS;
+template <> struct Fmt<FMT_IQ4_XS_ROWS>   { enum { SBB = 136, SPS = 1, NRAW = 4, BOX = 144, D_OFF = 0 }; };
 template <int TYPE> struct Smem {
     enum {
         SBB = Fmt<TYPE>::SBB, SPS = Fmt<TYPE>::SPS, NRAW = Fmt<TYPE>::NRAW,
@@ -270,12 +274,12 @@ struct Unit {
     int tile_n, row0, valid_rows, expert, first, ncols, sb0;      // sb0: first super-block (split K)
 };
 
-template <int TYPE>
+template <int TYPE, int FV = TYPE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uint8_t *__restrict__ act,
                int N, int n_tiles_dense, int ksplit, float *__restrict__ dst, int64_t ldd, int *__restrict__ error_word,
-               TileRoute id, int fold) {
-    typedef Smem<TYPE> L;
+               TileRoute id, int fold, const uint8_t *__restrict__ wraw, size_t row_stride, size_t mat_stride, int rowcopy) {
+    typedef Smem<FV> L;                         // FV: the staging variant of the type's format
     constexpr int SBB = L::SBB, SPS = L::SPS, NRAW = L::NRAW, ROWB = L::ROWB;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint32_t tmem_base_slot;
@@ -354,7 +358,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     if (warp == 0) {
         // ---- producer ----
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
-        if (lane == 0) tma_prefetch_desc(&wmap);
+        if (lane == 0 && !rowcopy) tma_prefetch_desc(&wmap);
         int rs_run = 0, s_run = 0;                        // raw stages and super-blocks fetched so far
         bool ok = true;
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
@@ -365,7 +369,21 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 if (s % SPS == 0) {
                     const int st = rs_run % NRAW;
                     if (!WAITP(1, bar(BAR_RAW_EMPTY + st), ((rs_run / NRAW) & 1) ^ 1)) { ok = false; break; }
-                    if (lane == 0) {
+                    if (rowcopy) {
+                        // Rows that are not 16-byte multiples (Q6_K with K = 11008: 9030-byte rows) cannot be described by a
+                        // tensor map. Every row's piece is copied by itself, from the 16-byte boundary below it: the block
+                        // then begins (address % 16) bytes into the row's slot, which the readers add (row_shift below).
+                        // A slot is 16 bytes wider than a block, so the copy never reads past the 16-byte unit that holds
+                        // the block's last byte. Rows past M are not copied; their threads multiply by a zero scale.
+                        if (lane == 0) mbar_expect_tx(bar(BAR_RAW_FULL + st), (uint32_t)U.valid_rows * ROWB);
+                        __syncwarp();
+                        for (int rr = lane; rr < U.valid_rows; rr += 32) {
+                            const uintptr_t src = (uintptr_t)(wraw + (size_t)U.expert * mat_stride + (size_t)(U.row0 + rr) * row_stride +
+                                                              (size_t)(s / SPS) * SPS * SBB);
+                            bulk_g2s(sbase + L::RAW_OFF + st * L::RAW_STAGE + rr * ROWB, (const void *)(src & ~(uintptr_t)15), ROWB,
+                                     bar(BAR_RAW_FULL + st));
+                        }
+                    } else if (lane == 0) {
                         // the whole [128 rows x ROWB] box in one tiled copy; rows past M arrive as zeros
                         mbar_expect_tx(bar(BAR_RAW_FULL + st), L::RAW_STAGE);
                         tma_load_3d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, ((s / SPS) * SPS * SBB / 16) * 4, U.row0, U.expert,
@@ -431,11 +449,13 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
             const Unit U = unit_of(u);
             const bool row_ok = r < U.valid_rows;
+            // where the row's bytes begin inside a 16-byte unit (0 unless rows are copied one by one, see the producer)
+            const int row_shift = rowcopy ? (int)(((uintptr_t)wraw + (size_t)U.expert * mat_stride + (size_t)(U.row0 + r) * row_stride) & 15) : 0;
             for (int rsu = 0; rsu < nsu / SPS && ok; ++rsu, ++rs_run) {
                 const int rs = U.sb0 / SPS + rsu;         // the raw stage inside the row
                 const int st = rs_run % NRAW;
                 if (!WAITP(0, bar(BAR_RAW_FULL + st), (rs_run / NRAW) & 1)) { ok = false; break; }
-                const uint8_t *rowp = smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + (rs * SPS * SBB) % 16;
+                const uint8_t *rowp = smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + ((row_shift + rs * SPS * SBB) & 15);
 #pragma unroll
                 for (int h = 0; h < SPS; ++h) {
 #pragma unroll
@@ -466,6 +486,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             const bool row_ok = r < U.valid_rows;
             // The tile's columns are shared out between the two warps of a row quadrant: 64 each for a full tile, and
             // for a short one (the ragged end, a route tile of a small expert) half of what there is, in steps of 16.
+            const int row_shift = rowcopy ? (int)(((uintptr_t)wraw + (size_t)U.expert * mat_stride + (size_t)(U.row0 + r) * row_stride) & 15) : 0;
             const int cw_eff = U.ncols > CW ? CW : max(16, (((U.ncols + 1) >> 1) + 15) & ~15);
             const int cbase = u4 * cw_eff;
             f32x2 acc2[CW / 2];
@@ -481,8 +502,8 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 if (!WAITP(6, bar(BAR_ACC_FULL + buf), (s_run / NBUF) & 1)) { ok = false; break; }
                 tc_fence_after();
                 const float dwb = row_ok ? half_bits_to_float(*reinterpret_cast<const uint16_t *>(
-                                               smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + ((s / SPS) * SPS * SBB) % 16 +
-                                               SBB * (s % SPS) + Fmt<TYPE>::D_OFF)) : 0.f;
+                                               smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + ((row_shift + (s / SPS) * SPS * SBB) & 15) +
+                                               SBB * (s % SPS) + Fmt<FV>::D_OFF)) : 0.f;
                 const f32x2 dw2 = f2_pack(dwb, dwb);
                 // Q4_K route tiles take the mins term here (a short tile leaves these warps idle most of the time, and
                 // a separate pass would read and write all of dst again): the row's eight mins and -dmin
@@ -878,10 +899,13 @@ size_t gemm_kq_id_act_bytes(int64_t K, int64_t max_tiles) { return gemm_kq_act_b
 
 bool gemm_kq_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride) {
     if (type != B200Q_TYPE_IQ4_XS && type != B200Q_TYPE_Q4_K && type != B200Q_TYPE_Q6_K) return false;
-    // raw stages are whole super-blocks in 16-byte pieces: two per stage for IQ4_XS, one for Q4_K
-    // (Q6_K: rows of 210-byte blocks are a multiple of 16 bytes, as the tensor map needs, every 8 blocks)
-    if (K <= 0 || K % (type == B200Q_TYPE_IQ4_XS ? 512 : type == B200Q_TYPE_Q6_K ? 2048 : 256) || M <= 0 || N <= 0) return false;
-    if ((uintptr_t)w % 16 || row_stride % 16) return false;
+    // raw stages are whole super-blocks in 16-byte pieces: two per stage for IQ4_XS, one for Q4_K. Q6_K rows of 210-byte
+    // blocks are 16-byte multiples only every 8 blocks: other lengths (K = 11008) take the row-by-row staging, which
+    // needs an even row stride only.
+    // IQ4_XS stages two 136-byte super-blocks at a time through a tensor map when K is a multiple of 512, and row by row,
+    // one at a time, otherwise (8-byte row stride).
+    if (K <= 0 || K % 256 || M <= 0 || N <= 0) return false;
+    if ((uintptr_t)w % 16 || row_stride % (type == B200Q_TYPE_Q6_K ? 2 : type == B200Q_TYPE_IQ4_XS ? 8 : 16)) return false;
     if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return false;
     return true;
 }
@@ -905,21 +929,28 @@ b200q_status launch_quantize_tiled256(b200q_ctx *ctx, const b200q_tensor *src1, 
 
 // n_tiles: grid width (dense: the tiles of N; MUL_MAT_ID: the upper bound of the route's tile count,
 // blocks past the device-side count leave at once)
-template <int TYPE>
+template <int TYPE, int FV = TYPE>
 static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride, size_t mat_stride, int64_t n_mat, int64_t M,
                                 int64_t K, const uint8_t *act, int64_t N, int64_t n_tiles, float *dst, int64_t ldd,
                                 const TileRoute &tr) {
-    typedef kq::Smem<TYPE> L;
-    auto kern = kq::gemm_kq_kernel<TYPE>;
+    typedef kq::Smem<FV> L;
+    auto kern = kq::gemm_kq_kernel<TYPE, FV>;
     static bool attr_set_dev[B200Q_MAX_DEVICES] = {};
     bool &attr_set = attr_set_dev[ctx->device % B200Q_MAX_DEVICES];
     if (!attr_set) {
         B200Q_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::TOTAL));
         attr_set = true;
     }
+    // rows a tensor map cannot describe (Q6_K whose row length is not a 16-byte multiple) are staged row by row
+    const int rowcopy = FV != TYPE || (TYPE == B200Q_TYPE_Q6_K && (row_stride % 16 != 0 || K % 2048 != 0 || mat_stride % 16 != 0));
     CUtensorMap wmap;
-    b200q_status st = make_weight_tmap3(ctx, &wmap, w, row_stride, M, (K / 256) * L::SBB, L::ROWB, n_mat, mat_stride);
-    if (st != B200Q_OK) return st;
+    memset(&wmap, 0, sizeof(wmap));
+    if (!rowcopy) {
+        b200q_status st = make_weight_tmap3(ctx, &wmap, w, row_stride, M, (K / 256) * L::SBB, L::ROWB, n_mat, mat_stride);
+        if (st != B200Q_OK) return st;
+    } else {
+        count(ctx, ST_GEMM_KQ_ROWCOPY);
+    }
     // persistent blocks, one per SM, walking the (row tile, column tile) units
     int64_t units = n_tiles * ((M + kq::BM - 1) / kq::BM);
     // split K in two when that shortens the schedule: rounds of whole units against rounds of half units
@@ -934,7 +965,7 @@ static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride
     // route tiles of Q4_K: the mins term inside the GEMM (B200Q_MOE_MINS_PASS=1 keeps the separate pass, for comparison)
     const int fold = TYPE == B200Q_TYPE_Q4_K && tr.tiles && !ctx->moe_mins_pass;
     kern<<<grid, kq::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, (int)n_tiles, ksplit, dst, ldd,
-                                                       ctx->error_word, tr, fold);
+                                                       ctx->error_word, tr, fold, (const uint8_t *)w, row_stride, mat_stride, rowcopy);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
     if (TYPE == B200Q_TYPE_Q4_K) {
@@ -957,10 +988,16 @@ static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride
     return B200Q_OK;
 }
 
+// IQ4_XS shapes the two-super-block tensor-map staging cannot take: an odd super-block count, or strides that are not
+// 16-byte multiples
+static bool iq4_rows(int64_t K, size_t row_stride, size_t mat_stride) { return K % 512 != 0 || row_stride % 16 != 0 || mat_stride % 16 != 0; }
+
 b200q_status launch_gemm_kq(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
                             const uint8_t *act, int64_t N, float *dst, int64_t ldd) {
     const int64_t n_tiles = (N + kq::BN - 1) / kq::BN;
     const size_t ms = row_stride * (size_t)M;
+    if (type == B200Q_TYPE_IQ4_XS && iq4_rows(K, row_stride, ms))
+        return launch_kq_t<B200Q_TYPE_IQ4_XS, kq::FMT_IQ4_XS_ROWS>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
     if (type == B200Q_TYPE_IQ4_XS) return launch_kq_t<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
     if (type == B200Q_TYPE_Q4_K) return launch_kq_t<B200Q_TYPE_Q4_K>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
     if (type == B200Q_TYPE_Q6_K) return launch_kq_t<B200Q_TYPE_Q6_K>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
@@ -975,7 +1012,10 @@ b200q_status launch_gemm_kq_id(b200q_ctx *ctx, const b200q_tensor *src0, const b
     b200q_status st = act_ready ? B200Q_OK : quantize256(ctx, src1, act, max_tiles, tr);
     if (st != B200Q_OK) return st;
     if (src0->type == B200Q_TYPE_IQ4_XS)
-        return launch_kq_t<B200Q_TYPE_IQ4_XS>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
+        return iq4_rows(K, src0->nb[1], src0->nb[2])
+                   ? launch_kq_t<B200Q_TYPE_IQ4_XS, kq::FMT_IQ4_XS_ROWS>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0,
+                                                                         max_tiles, dst, 0, tr)
+                   : launch_kq_t<B200Q_TYPE_IQ4_XS>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
     if (src0->type == B200Q_TYPE_Q4_K)
         return launch_kq_t<B200Q_TYPE_Q4_K>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
     if (src0->type == B200Q_TYPE_Q6_K)

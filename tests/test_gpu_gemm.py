@@ -116,13 +116,16 @@ def test_gemm_iq4_xs_extreme_codes(ctx):
     assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
 
 
-def test_gemm_iq4_xs_odd_superblock_count_falls_back(ctx):
-    t, m, n, k = A.IQ4_XS, 64, 20, 768                    # three super-blocks: not a multiple of 512
-    rng = np.random.default_rng(2)
+@pytest.mark.parametrize("m,k,n", [(64, 768, 20), (200, 11008, 40), (129, 256, 9), (1000, 1280, 128)])
+def test_gemm_iq4_xs_odd_superblock_count(ctx, m, k, n):
+    """An odd number of 136-byte super-blocks makes rows 8-byte multiples only (K = 11008: the down projection of the 7B
+    models): staged row by row, one super-block per stage, still on the tensor cores."""
+    t = A.IQ4_XS
+    rng = np.random.default_rng(2 + m + k)
     w = O.random_blocks(t, m, k, rng)
     x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
     got, st = run(ctx, t, w, k, x)
-    assert st.get("gemm_tc", 0) == 0 and st.get("gemm_fallback_shape", 0) == 1
+    assert st.get("gemm_tc", 0) == 1 and st.get("gemm_kq_rowcopy", 0) == 1 and st.get("gemm_fallback_shape", 0) == 0, st
     assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
 
 
@@ -227,8 +230,23 @@ def test_gemm_q6_K_extreme_codes_and_other_k_fall_back(ctx):
     w2 = O.random_blocks(t, 64, k2, rng)
     x2 = rng.normal(0, 1, size=(20, k2)).astype(np.float32)
     got2, st2 = run(ctx, t, w2, k2, x2)
-    assert st2.get("gemm_tc", 0) == 0 and st2.get("gemm_fallback_shape", 0) == 1
+    # five super-blocks: 1050-byte rows, not a 16-byte multiple -- staged row by row, still on the tensor cores
+    assert st2.get("gemm_tc", 0) == 1 and st2.get("gemm_kq_rowcopy", 0) == 1 and st2.get("gemm_fallback_shape", 0) == 0
     assert rel_err(got2, O.mul_mat_f64(t, w2, k2, x2, True)) < TOL
+
+
+@pytest.mark.parametrize("m,k,n", [(200, 11008, 40), (129, 256, 9), (64, 3328, 300), (1000, 1280, 128)])
+def test_gemm_q6_k_rows_that_are_not_16_byte_multiples(ctx, m, k, n):
+    """Q6_K rows of 210-byte blocks are 16-byte multiples only when K is a multiple of 2048. Other lengths (K = 11008, the
+    down projection of the 7B models) are staged row by row from the 16-byte boundary below each row's block; every row
+    then sits at its own offset inside its slot. Ragged M and N, one and many super-blocks, odd block counts."""
+    t = A.Q6_K
+    rng = np.random.default_rng(m + k + n)
+    w = O.random_blocks(t, m, k, rng)
+    x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
+    got, st = run(ctx, t, w, k, x)
+    assert st.get("gemm_tc", 0) == 1 and st.get("gemm_kq_rowcopy", 0) == 1 and st.get("gemm_fallback_shape", 0) == 0, st
+    assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
 
 
 def test_config2_head_q6_K_prompt(ctx):

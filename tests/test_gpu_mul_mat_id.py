@@ -185,6 +185,17 @@ def test_mul_mat_id_tensor_core_q6_K(ctx):
     assert st.get("moe_gemm", 0) == 1 and st.get("gemm_tc", 0) == 1, st
 
 
+def test_mul_mat_id_tensor_core_q6_K_rows_not_16_byte_multiples(ctx):
+    """Five super-blocks per row (1050 bytes): the experts' rows are staged one by one, each at its own offset."""
+    st = check(ctx, A.Q6_K, n_expert=8, n_used=2, n_tok=300, m=200, k=1280, ne11_is_one=True, seed=78)
+    assert st.get("moe_gemm", 0) == 1 and st.get("gemm_tc", 0) == 1 and st.get("gemm_kq_rowcopy", 0) == 1, st
+
+
+def test_mul_mat_id_tensor_core_iq4_xs_odd_superblock_count(ctx):
+    st = check(ctx, A.IQ4_XS, n_expert=8, n_used=2, n_tok=300, m=200, k=768, ne11_is_one=True, seed=79)
+    assert st.get("moe_gemm", 0) == 1 and st.get("gemm_tc", 0) == 1 and st.get("gemm_kq_rowcopy", 0) == 1, st
+
+
 def test_gate_and_up_share_the_gathered_activation(ctx):
     """Two MUL_MAT_ID calls of one graph over the same src1 and ids (gate and up of a layer) gather and quantize the
     activation once; a third with another src1 (down) does it again; results stay right."""
