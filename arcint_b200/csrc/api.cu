@@ -274,6 +274,8 @@ b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
     if (const char *v = getenv("B200Q_FUSE_QUANT_BYTES")) ctx->fuse_quant_bytes = atoll(v);
     const char *no_ks = getenv("B200Q_NO_KSPLIT");
     ctx->no_ksplit = no_ks && no_ks[0] == '1';
+    const char *no_small = getenv("B200Q_GEMV_NO_SMALL");
+    ctx->gemv_no_small = no_small && no_small[0] == '1';
     const char *mins_pass = getenv("B200Q_MOE_MINS_PASS");
     ctx->moe_mins_pass = mins_pass && mins_pass[0] == '1';
     const char *no_stream = getenv("B200Q_NO_STREAM");   // the older GEMV kernel for every shape (comparisons)

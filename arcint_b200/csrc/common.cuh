@@ -124,6 +124,7 @@ struct b200q_ctx {
     int          gemv_rows = 0, gemv_block_warps = 0, gemv_stream_mask = -1;
     int64_t      fuse_quant_bytes = 4 << 20;   // B200Q_FUSE_QUANT_BYTES: per-32 decode products up to this many weight bytes quantize their activation inside the GEMV (0: never)
     bool         no_ksplit = false;       // B200Q_NO_KSPLIT=1: never cut a prompt product along K
+    bool         gemv_no_small = false;   // B200Q_GEMV_NO_SMALL=1: never the 128-thread, 170-register build of the wide Q6_K GEMV
     bool         moe_mins_pass = false;   // B200Q_MOE_MINS_PASS=1: Q4_K route tiles take the mins term in a separate pass
     bool         no_stream = false;       // B200Q_NO_STREAM=1: every GEMV through the per-warp ring kernel (comparisons)
     std::string  last_error;

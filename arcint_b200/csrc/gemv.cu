@@ -53,6 +53,39 @@ static b200q_status launch_one(b200q_ctx *ctx, const void *w, size_t row_stride,
     return B200Q_OK;
 }
 
+// One launch of the slice-resident kernel built with the launch bounds (MAXT, MINB); resident blocks per SM for the
+// block shape are asked once per (device, shape).
+template <int TYPE, int NC, int R, int NSETS, bool QX, bool AR, int MAXT, int MINB>
+static b200q_status launch_stream_kernel(b200q_ctx *ctx, int threads, size_t smem, int groups, const void *w, size_t row_stride, int64_t M,
+                                         int nblk, const GemvAct &act, float *dst, int64_t ldd, const GemvAr &ar_args) {
+    auto kern = gemv_stream_kernel<TYPE, NC, R, NSETS, QX, AR, MAXT, MINB>;
+    struct Occ { int threads; size_t smem; int blocks; bool attr; };
+    static Occ occ_dev[B200Q_MAX_DEVICES] = {};
+    Occ &o = occ_dev[ctx->device % B200Q_MAX_DEVICES];
+    if (!o.attr) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return fail(ctx, B200Q_CUDA_ERROR, "gemv_stream attribute: %s", cudaGetErrorString(e));
+        o.attr = true;
+    }
+    if (o.threads != threads || o.smem != smem) {
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem);
+        if (e != cudaSuccess) return fail(ctx, B200Q_CUDA_ERROR, "gemv_stream occupancy: %s", cudaGetErrorString(e));
+        o.threads = threads;
+        o.smem = smem;
+        o.blocks = n > 0 ? n : 1;
+    }
+    const int64_t n_units = (M + R - 1) / R;
+    int64_t blocks = (n_units + groups - 1) / groups;
+    const int64_t cap = (int64_t)ctx->sm_count * o.blocks;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    cudaError_t e = launch_pdl(!ctx->no_pdl, kern, dim3((unsigned)blocks), dim3(threads), smem, ctx->stream, (const uint8_t *)w,
+                               row_stride, (int)M, nblk, act, dst, (int)ldd, groups, ctx->error_word, ar_args);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return e == cudaSuccess ? B200Q_OK : fail(ctx, B200Q_CUDA_ERROR, "gemv_stream launch: %s", cudaGetErrorString(e));
+}
+
 // The slice-resident kernel (gemv_stream.cuh) for rows that bulk copies can fetch (16-byte aligned
 // start, stride and length). Returns false when the shape does not fit it: more than 16 warps per
 // group (K beyond 16 slices, or 8 for more than four columns) or a ring beyond shared memory.
@@ -76,35 +109,18 @@ static bool try_launch_stream(b200q_ctx *ctx, const void *w, size_t row_stride, 
     while (groups > 1 && groups * gb > 200 * 1024) --groups;
     const size_t smem = groups * gb;
     const int threads = groups * nw * 32;
-    auto kern = gemv_stream_kernel<TYPE, NC, R, NSETS, QX, AR>;
     GemvAr ar_args = {};
     if (ar) ar_args = *ar;
-    // resident blocks per SM for this block shape, asked once per (device, shape)
-    struct Occ { int threads; size_t smem; int blocks; bool attr; };
-    static Occ occ_dev[B200Q_MAX_DEVICES] = {};
-    Occ &o = occ_dev[ctx->device % B200Q_MAX_DEVICES];
-    if (!o.attr) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) { *st = fail(ctx, B200Q_CUDA_ERROR, "gemv_stream attribute: %s", cudaGetErrorString(e)); return true; }
-        o.attr = true;
+    // Q6_K at four and more columns in blocks of one 128-thread group: the build with room for 170 registers
+    constexpr bool has_small = (TYPE == B200Q_TYPE_Q6_K || TYPE == B200Q_TYPE_Q4_K) && NC >= 4 && !QX && !AR;
+    if constexpr (has_small) {
+        if (threads <= 128 && !ctx->gemv_no_small) {
+            *st = launch_stream_kernel<TYPE, NC, R, NSETS, QX, AR, 128, 3>(ctx, threads, smem, groups, w, row_stride, M, nblk, act, dst, ldd, ar_args);
+            return true;
+        }
     }
-    if (o.threads != threads || o.smem != smem) {
-        int n = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem);
-        if (e != cudaSuccess) { *st = fail(ctx, B200Q_CUDA_ERROR, "gemv_stream occupancy: %s", cudaGetErrorString(e)); return true; }
-        o.threads = threads;
-        o.smem = smem;
-        o.blocks = n > 0 ? n : 1;
-    }
-    const int64_t n_units = (M + R - 1) / R;
-    int64_t blocks = (n_units + groups - 1) / groups;
-    const int64_t cap = (int64_t)ctx->sm_count * o.blocks;
-    if (blocks > cap) blocks = cap;
-    if (blocks < 1) blocks = 1;
-    cudaError_t e = launch_pdl(!ctx->no_pdl, kern, dim3((unsigned)blocks), dim3(threads), smem, ctx->stream, (const uint8_t *)w,
-                               row_stride, (int)M, nblk, act, dst, (int)ldd, groups, ctx->error_word, ar_args);
-    if (e == cudaSuccess) e = cudaGetLastError();
-    *st = e == cudaSuccess ? B200Q_OK : fail(ctx, B200Q_CUDA_ERROR, "gemv_stream launch: %s", cudaGetErrorString(e));
+    *st = launch_stream_kernel<TYPE, NC, R, NSETS, QX, AR, GEMV_STREAM_MAX_THREADS, 0>(ctx, threads, smem, groups, w, row_stride, M, nblk, act, dst,
+                                                                                      ldd, ar_args);
     return true;
 }
 

@@ -314,8 +314,10 @@ __device__ __forceinline__ void gemv_stream_warp(const uint8_t *__restrict__ W, 
 // dst[m + c*ldd] = sum_k W[m][k] x_c[k] for c < NC (1..8), rows [0, M). A block holds `groups` groups of
 // nslices * (NC > 4 ? 2 : 1) warps; the grid is one wave of persistent blocks and group number gg takes the
 // row batches gg, gg + (all groups), ...
-template <int TYPE, int NC, int R, int NSETS, bool QX = false, bool AR = false>
-__global__ void __launch_bounds__(GEMV_STREAM_MAX_THREADS)
+// MAXT, MINB: the launch bounds. The default (512 threads) caps a thread at 128 registers, which the wide Q6_K forms
+// reach: they are also built for blocks of at most 128 threads, three to an SM (170 registers).
+template <int TYPE, int NC, int R, int NSETS, bool QX = false, bool AR = false, int MAXT = GEMV_STREAM_MAX_THREADS, int MINB = 0>
+__global__ void __launch_bounds__(MAXT, MINB)
 gemv_stream_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk, GemvAct act, float *__restrict__ dst,
                    int ldd, int groups, int *__restrict__ error_word, GemvAr ar) {
     typedef GemvFmt<TYPE> F;
