@@ -145,14 +145,15 @@ static b200q_status launch_nc(b200q_ctx *ctx, const void *w, size_t row_stride, 
     if (aligned && !ctx->no_stream && M <= INT32_MAX / 2 && ldd <= INT32_MAX && want_stream) {
         typedef GemvFmt<TYPE> F;
         const int row_bytes = (int)(K / F::BLK_W) * F::BLK_B;
-        // rows per ring stage: four, two when a stage of four long rows would crowd shared memory or a
-        // single column leaves little work per row
-        bool two = NC == 1 || (size_t)12 * gemv_stream_slot(row_bytes) > 36 * 1024;
+        // rows per ring stage: four; two at a single column unless the rows are long (measured: Q4_K 11008x4096 at one
+        // column 7.4 us with two and 7.6 with four, 4096x11008 7.55 with two and 7.1 with four; at 4 and 8 columns four rows
+        // win everywhere, by up to 25 % on the long rows), and two when a ring of four rows does not fit shared memory
+        bool two = NC == 1 && row_bytes <= 4096;
         if (ctx->gemv_rows == 2 || ctx->gemv_rows == 4) two = ctx->gemv_rows == 2;
         else if (ctx->gemv_rows) count(ctx, ST_GEMV_KNOB_IGNORED);
         b200q_status st = B200Q_OK;
-        const bool took = two ? try_launch_stream<TYPE, NC, 2>(ctx, w, row_stride, M, K, act, dst, ldd, &st)
-                              : try_launch_stream<TYPE, NC, 4>(ctx, w, row_stride, M, K, act, dst, ldd, &st);
+        bool took = !two && try_launch_stream<TYPE, NC, 4>(ctx, w, row_stride, M, K, act, dst, ldd, &st);
+        if (!took) took = try_launch_stream<TYPE, NC, 2>(ctx, w, row_stride, M, K, act, dst, ldd, &st);
         if (took) {
             if (st == B200Q_OK) count(ctx, ST_GEMV_STREAM);
             return st;
@@ -280,10 +281,10 @@ static b200q_status launch_ar_t(b200q_ctx *ctx, const void *w, size_t row_stride
                                 int64_t ldd, const GemvAr &ar) {
     typedef GemvFmt<TYPE> F;
     const int row_bytes = (int)(K / F::BLK_W) * F::BLK_B;
-    const bool two = NC == 1 || (size_t)12 * gemv_stream_slot(row_bytes) > 36 * 1024;
+    const bool two = NC == 1 && row_bytes <= 4096;              // as in launch_nc
     b200q_status st = B200Q_OK;
-    const bool took = two ? try_launch_stream<TYPE, NC, 2, QX, true>(ctx, w, row_stride, M, K, act, dst, ldd, &st, &ar)
-                          : try_launch_stream<TYPE, NC, 4, QX, true>(ctx, w, row_stride, M, K, act, dst, ldd, &st, &ar);
+    bool took = !two && try_launch_stream<TYPE, NC, 4, QX, true>(ctx, w, row_stride, M, K, act, dst, ldd, &st, &ar);
+    if (!took) took = try_launch_stream<TYPE, NC, 2, QX, true>(ctx, w, row_stride, M, K, act, dst, ldd, &st, &ar);
     if (!took) return B200Q_UNSUPPORTED;
     if (st == B200Q_OK) { count(ctx, ST_GEMV_STREAM); count(ctx, ST_GEMV_ALLREDUCE_FUSED); count(ctx, ST_GEMV_COL0 + NC); if (QX) count(ctx, ST_GEMV_FUSED_QUANT); }
     return st;
