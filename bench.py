@@ -765,8 +765,8 @@ def run_gpu(args, rank, world):
         tot_b += b
         tot_ms += kms
         # DRAM bytes per launch as ncu captured them (dram__bytes.sum.per_second x gpu__time_duration): 25.39 to 25.46 MB for
-        # the 25.36 MB Q4_K matrix at 1 and 8 columns, 111.2 MB for the 107.52 MB Q6_K head
-        tot_traffic += b * (1.035 if t == A.Q6_K else 1.003)
+        # the 25.36 MB Q4_K matrix at 1 and 8 columns, 111.7 to 114.2 MB for the 107.52 MB Q6_K head
+        tot_traffic += b * (1.05 if t == A.Q6_K else 1.003)
     achieved = tot_b / (tot_ms * 1e-3) / 1e9
     clocks = sampler.stop() if rank == 0 else None
 
