@@ -122,7 +122,11 @@ struct b200q_ctx {
     // decode GEMV tile knobs (read once from the environment; 0 / -1: the measured defaults): rows per ring stage,
     // warps per block, and which column counts take the slice-resident kernel (bit c = c columns)
     int          gemv_rows = 0, gemv_block_warps = 0, gemv_stream_mask = -1;
-    int64_t      fuse_quant_bytes = 4 << 20;   // B200Q_FUSE_QUANT_BYTES: per-32 decode products up to this many weight bytes quantize their activation inside the GEMV (0: never)
+    // B200Q_FUSE_QUANT_BYTES: per-32 decode products up to this many weight bytes quantize their activation inside the GEMV.
+    // Off (0) by default: it saves a launch, but every warp then starts with two dependent global loads and the quantizer's
+    // arithmetic in front of its first row, where the separate quantizer runs under the previous GEMV's tail (programmatic
+    // dependent launch). Measured on the 7B decode trace: -2 % at two GPUs, +38 % at eight (1.48 against 1.08 ms).
+    int64_t      fuse_quant_bytes = 0;
     bool         no_ksplit = false;       // B200Q_NO_KSPLIT=1: never cut a prompt product along K
     bool         gemv_no_small = false;   // B200Q_GEMV_NO_SMALL=1: never the 128-thread, 170-register build of the wide Q6_K GEMV
     bool         moe_mins_pass = false;   // B200Q_MOE_MINS_PASS=1: Q4_K route tiles take the mins term in a separate pass

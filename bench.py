@@ -770,9 +770,11 @@ def run_gpu(args, rank, world):
     achieved = tot_b / (tot_ms * 1e-3) / 1e9
     clocks = sampler.stop() if rank == 0 else None
 
-    prefill = prefill_section(ctx, world, rank, dist)
-    tp_trace = tp_trace_section(ctx, world, rank, dist)
-    moe = moe_section(ctx, world, rank, dist)
+    # the sections beside the headline (all by default; --sections picks some, e.g. to compare one of them across builds)
+    want = set(args.sections.split(",")) if args.sections else {"prefill", "tp_trace", "moe"}
+    prefill = prefill_section(ctx, world, rank, dist) if "prefill" in want else []
+    tp_trace = tp_trace_section(ctx, world, rank, dist) if "tp_trace" in want else []
+    moe = moe_section(ctx, world, rank, dist) if "moe" in want else []
 
     cpu = None
     if rank == 0 and world == 1:           # the CPU leg runs at N=1 only (idle ranks would spin on the host cores it needs)
@@ -842,6 +844,7 @@ def main():
     ap.add_argument("--impl", default="b200q", choices=["b200q", "reference"])
     ap.add_argument("--case", default=None, help="<type>:<M>x<K>x<N>[:id] -- one product a few times (profiling)")
     ap.add_argument("--reps", type=int, default=4)
+    ap.add_argument("--sections", default=None, help="comma list of prefill,tp_trace,moe (default: all)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))

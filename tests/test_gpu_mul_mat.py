@@ -276,18 +276,17 @@ def test_overlapped_host_copies_eager_and_in_a_graph(ctx):
 @pytest.mark.parametrize("t", [A.Q4_0, A.Q8_0])
 @pytest.mark.parametrize("m,k,n", [(512, 4096, 1), (96, 2304, 2), (1000, 512, 1), (37, 256, 2)])
 def test_gemv_that_quantizes_its_own_activation_is_bit_identical(t, m, k, n):
-    """Small per-32 decode products quantize their slice of the activation inside the GEMV (one launch instead of
-    two). The arithmetic is the quantizer kernel's, operation for operation, so the result must equal the
-    two-kernel route bit for bit (B200Q_FUSE_QUANT_BYTES=0 switches the fusion off)."""
+    """With B200Q_FUSE_QUANT_BYTES set, small per-32 decode products quantize their slice of the activation inside the
+    GEMV (one launch instead of two; off by default). The arithmetic is the quantizer kernel's, operation for
+    operation, so the result must equal the two-kernel route bit for bit."""
     import os
     w = make_weights(t, m, k, 60 + t)
     x = np.random.default_rng(m + k).normal(0, 1, size=(n, k)).astype(np.float32)
     x[0, :32] = 0.0                                        # an all-zero block: scale 0, codes 0
     outs = {}
     for fused in (True, False):
-        if not fused:
-            os.environ["B200Q_FUSE_QUANT_BYTES"] = "0"
-            os.environ["B200Q_GEMV_STREAM_MASK"] = "0x1FE"      # the same GEMV kernel at every width, so only the quantizer's place differs
+        os.environ["B200Q_FUSE_QUANT_BYTES"] = str(4 << 20) if fused else "0"
+        os.environ["B200Q_GEMV_STREAM_MASK"] = "0x1FE"          # the same GEMV kernel at every width, so only the quantizer's place differs
         try:
             with A.Context(0) as c:
                 outs[fused] = c.run_mul_mat(t, w, k, x)
