@@ -8,6 +8,8 @@
 //   Q4_K  144 B: fp16 d, fp16 dmin, 12 B of 6-bit scales/mins, 128 B nibbles; group g of
 //          32 bytes: low -> sub-block 2g, high -> 2g+1; w = d sc q - dmin m
 //          (0000-01-kquant-integer-dpas.patch:1562-1576, 3735-3739)
+//   Q5_K  176 B: Q4_K's header, then 32 B of fifth bits (bit j of byte t: weight t of sub-block j), then Q4_K's
+//          128 B of nibbles; w = d sc (n + 16 bit) - dmin m      (0000-01-...:1734-1735, 3735-3739)
 //   Q6_K  210 B: ql[128], qh[64], int8 scales[16], fp16 d; w = d sc (q - 32)
 //          (0000-01-...:1789-1794, 3798-3802, 3849-3860)
 //   IQ4_XS 136 B: fp16 d, u16 scales_h, scales_l[4], 128 B nibbles indexing kvalues_iq4nl;
@@ -201,6 +203,21 @@ __host__ __device__ inline float decode_weight(int type, const uint8_t *row, int
         q4k_scale_min(s0, s1, s2, j, &sc, &m);
         const uint8_t qb = b[16 + 32 * (j / 2) + t];
         const int q = (j & 1) ? (qb >> 4) : (qb & 0xF);
+        return sub_rn(mul_rn(mul_rn(d, (float)sc), (float)q), mul_rn(dmin, (float)m));
+    }
+    case B200Q_TYPE_Q5_K: {
+        const uint8_t *b = row + (i / 256) * 176;
+        const int r = (int)(i % 256), j = r / 32, t = r % 32;
+        const float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
+        const float dmin = half_bits_to_float((uint16_t)(b[2] | (b[3] << 8)));
+        const uint8_t *s = b + 4;
+        const uint32_t s0 = s[0] | (s[1] << 8) | (s[2] << 16) | ((uint32_t)s[3] << 24);
+        const uint32_t s1 = s[4] | (s[5] << 8) | (s[6] << 16) | ((uint32_t)s[7] << 24);
+        const uint32_t s2 = s[8] | (s[9] << 8) | (s[10] << 16) | ((uint32_t)s[11] << 24);
+        int sc, m;
+        q4k_scale_min(s0, s1, s2, j, &sc, &m);
+        const uint8_t qb = b[48 + 32 * (j / 2) + t];
+        const int q = ((j & 1) ? (qb >> 4) : (qb & 0xF)) | (((b[16 + t] >> j) & 1) << 4);
         return sub_rn(mul_rn(mul_rn(d, (float)sc), (float)q), mul_rn(dmin, (float)m));
     }
     case B200Q_TYPE_Q6_K: {

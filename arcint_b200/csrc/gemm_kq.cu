@@ -79,6 +79,7 @@ template <int TYPE> struct Fmt;
 // D_OFF: where the block's fp16 super-scale sits.
 template <> struct Fmt<B200Q_TYPE_IQ4_XS> { enum { SBB = 136, SPS = 2, NRAW = 2, BOX = 272, D_OFF = 0 }; };
 template <> struct Fmt<B200Q_TYPE_Q4_K>   { enum { SBB = 144, SPS = 1, NRAW = 4, BOX = 144, D_OFF = 0 }; };
+template <> struct Fmt<B200Q_TYPE_Q5_K>   { enum { SBB = 176, SPS = 1, NRAW = 3, BOX = 176, D_OFF = 0 }; };
 template <> struct Fmt<B200Q_TYPE_Q6_K>   { enum { SBB = 210, SPS = 1, NRAW = 2, BOX = 224, D_OFF = 208 }; };
 // IQ4_XS rows with an odd number of super-blocks (K = 11008: 5848-byte rows) are 8-byte multiples only: they are staged
 // row by row, one super-block per stage, the slot 8 bytes wider than the block (format variant FMT_IQ4_XS_ROWS).
@@ -239,6 +240,34 @@ __device__ __forceinline__ void unpack_group(const uint8_t *blk, int jg, int kh,
             uint8_t *a = a0 + pp * A_SLOT + kh * LBO;
             *reinterpret_cast<uint4 *>(a) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
             *reinterpret_cast<uint4 *>(a + OPER_BYTES) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+    } else if (TYPE == B200Q_TYPE_Q5_K) {
+        // Q5_K: Q4_K's header | 32 bytes of fifth bits | 4 x 32 bytes of nibbles. Bit 2G of high-bit byte t goes with
+        // the low nibble of byte t of group G, bit 2G + 1 with the high one. p = sc * q5 <= 63 * 31: the same limbs.
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+        uint32_t c03, c47;
+        q4k_scales8(hdr.y, hdr.z, hdr.w, &c03, &c47);
+        const uint32_t cw = row_ok ? (jg ? c47 : c03) : 0u;                  // scales of sub-blocks 4 jg .. + 3
+        const uint4 hv = *reinterpret_cast<const uint4 *>(blk + 16 + 16 * kh);
+        const uint32_t hb[4] = { hv.x, hv.y, hv.z, hv.w };
+#pragma unroll
+        for (int gg = 0; gg < 2; ++gg) {
+            const int G = 2 * jg + gg;
+            const uint4 qv = *reinterpret_cast<const uint4 *>(blk + 48 + 32 * G + 16 * kh);
+            const uint32_t q[4] = { qv.x, qv.y, qv.z, qv.w };
+            const uint32_t sc_lo = (cw >> (16 * gg)) & 0xFFu, sc_hi = (cw >> (16 * gg + 8)) & 0xFFu;
+            uint32_t hl[4], ll[4], hh[4], lh[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t u = hb[i] >> (2 * G);
+                q4k_limbs4((q[i] & 0x0F0F0F0Fu) | ((u << 4) & 0x10101010u), sc_lo, &hl[i], &ll[i]);
+                q4k_limbs4(((q[i] >> 4) & 0x0F0F0F0Fu) | ((u << 3) & 0x10101010u), sc_hi, &hh[i], &lh[i]);
+            }
+            uint8_t *a = a0 + (2 * gg) * A_SLOT + kh * LBO;
+            *reinterpret_cast<uint4 *>(a) = make_uint4(hl[0], hl[1], hl[2], hl[3]);
+            *reinterpret_cast<uint4 *>(a + OPER_BYTES) = make_uint4(ll[0], ll[1], ll[2], ll[3]);
+            *reinterpret_cast<uint4 *>(a + A_SLOT) = make_uint4(hh[0], hh[1], hh[2], hh[3]);
+            *reinterpret_cast<uint4 *>(a + A_SLOT + OPER_BYTES) = make_uint4(lh[0], lh[1], lh[2], lh[3]);
         }
     } else {
         // Q4_K: d, dmin | 12 scale bytes | 4 x 32 bytes; bytes 32 g .. 32 g + 31 hold sub-block 2g in
@@ -509,7 +538,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                 // a separate pass would read and write all of dst again): the row's eight mins and -dmin
                 uint32_t m03 = 0, m47 = 0;
                 f32x2 ndm2 = 0ull;
-                if (TYPE == B200Q_TYPE_Q4_K && fold_mins) {
+                if ((TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K) && fold_mins) {
                     const uint4 hdr = *reinterpret_cast<const uint4 *>(smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB);
                     q4k_mins8(hdr.y, hdr.z, hdr.w, &m03, &m47);
                     const float ndm = row_ok ? -half_bits_to_float((uint16_t)(hdr.x >> 16)) : 0.f;
@@ -547,7 +576,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                         acc2[e]     = f2_fma(s01, f2_mul(dw2, dx[c / 2]), acc2[e]);
                         acc2[e + 1] = f2_fma(s23, f2_mul(dw2, dx[c / 2 + 1]), acc2[e + 1]);
                     }
-                    if (TYPE == B200Q_TYPE_Q4_K && fold_mins) {
+                    if ((TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K) && fold_mins) {
                         // - dmin d_x sum_j m_j bsum_j per live column: the digits come by broadcast loads from the
                         // chunk, four dp4a per column (as q4k_mins_rows_kernel, without its pass over dst). Eight
                         // columns' loads are issued together and their chains are independent, so the latencies overlap.
@@ -661,7 +690,7 @@ __device__ __forceinline__ uint32_t u8x2_to_h2(uint32_t two_bytes) {
 __global__ void __launch_bounds__(128)
 q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_stride, int M, int nsb,
                 const uint8_t *__restrict__ act, const int16_t *__restrict__ bsum, int N, float *__restrict__ dst,
-                int64_t ldd, TileRoute id) {
+                int64_t ldd, TileRoute id, int blk_bytes) {
     __shared__ __align__(16) uint32_t cb[2][MC][8];       // per column: for q < 4 the f16 pairs (bl_2q, bl_2q+1), 256 (bh_2q, bh_2q+1)
     __shared__ __align__(8) float cdx[2][MC];
     const int tile = blockIdx.x / (BN / MC), cc0 = (blockIdx.x % (BN / MC)) * MC;   // columns cc0 .. cc0 + MC - 1 of the tile
@@ -721,8 +750,8 @@ q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_str
         }
         const uint4 h0 = h0n, h1 = h1n;                      // d, dmin | 12 scale bytes of the two rows' blocks
         if (sb + 1 < nsb) {
-            h0n = __ldg(reinterpret_cast<const uint4 *>(w0 + (size_t)(sb + 1) * 144));
-            h1n = __ldg(reinterpret_cast<const uint4 *>(w1 + (size_t)(sb + 1) * 144));
+            h0n = __ldg(reinterpret_cast<const uint4 *>(w0 + (size_t)(sb + 1) * blk_bytes));      // 144 Q4_K, 176 Q5_K: the same header
+            h1n = __ldg(reinterpret_cast<const uint4 *>(w1 + (size_t)(sb + 1) * blk_bytes));
         }
         uint32_t m03, m47, a[4];
         q4k_mins8(h0.y, h0.z, h0.w, &m03, &m47);
@@ -794,7 +823,7 @@ q4k_mins_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_str
 __global__ void __launch_bounds__(128)
 q4k_mins_rows_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t mat_stride, int M, int nsb,
                 const uint8_t *__restrict__ act, const int16_t *__restrict__ bsum, int N, float *__restrict__ dst,
-                int64_t ldd, TileRoute id) {
+                int64_t ldd, TileRoute id, int blk_bytes) {
     __shared__ __align__(16) uint32_t cs[2][MC][4];       // bl 0..3, bl 4..7, bh 0..3, bh 4..7
     __shared__ float cdx[2][MC];
     const int tile = blockIdx.x / (BN / MC), cc0 = (blockIdx.x % (BN / MC)) * MC;   // columns cc0 .. cc0 + MC - 1 of the tile
@@ -816,7 +845,7 @@ q4k_mins_rows_kernel(const uint8_t *__restrict__ W, size_t row_stride, size_t ma
     for (int sb = 0; sb < nsb; ++sb) {
         const int pb = sb & 1;
         const uint4 hdr = hdr_next;
-        if (sb + 1 < nsb) hdr_next = __ldg(reinterpret_cast<const uint4 *>(wrow + (size_t)(sb + 1) * 144));   // in flight under the math
+        if (sb + 1 < nsb) hdr_next = __ldg(reinterpret_cast<const uint4 *>(wrow + (size_t)(sb + 1) * blk_bytes));   // in flight under the math
         if (threadIdx.x < MC) {
             const int cc = cc0 + threadIdx.x;
             uint32_t w[4] = { 0, 0, 0, 0 };
@@ -898,7 +927,7 @@ size_t gemm_kq_act_bytes(int64_t K, int64_t N) {
 size_t gemm_kq_id_act_bytes(int64_t K, int64_t max_tiles) { return gemm_kq_act_bytes(K, max_tiles * kq::BN); }
 
 bool gemm_kq_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride) {
-    if (type != B200Q_TYPE_IQ4_XS && type != B200Q_TYPE_Q4_K && type != B200Q_TYPE_Q6_K) return false;
+    if (type != B200Q_TYPE_IQ4_XS && type != B200Q_TYPE_Q4_K && type != B200Q_TYPE_Q5_K && type != B200Q_TYPE_Q6_K) return false;
     // raw stages are whole super-blocks in 16-byte pieces: two per stage for IQ4_XS, one for Q4_K. Q6_K rows of 210-byte
     // blocks are 16-byte multiples only every 8 blocks: other lengths (K = 11008) take the row-by-row staging, which
     // needs an even row stride only.
@@ -963,24 +992,24 @@ static b200q_status launch_kq_t(b200q_ctx *ctx, const void *w, size_t row_stride
     }
     const unsigned grid = (unsigned)(units < S ? units : S);
     // route tiles of Q4_K: the mins term inside the GEMM (B200Q_MOE_MINS_PASS=1 keeps the separate pass, for comparison)
-    const int fold = TYPE == B200Q_TYPE_Q4_K && tr.tiles && !ctx->moe_mins_pass;
+    const int fold = (TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K) && tr.tiles && !ctx->moe_mins_pass;
     kern<<<grid, kq::THREADS, L::TOTAL, ctx->stream>>>(wmap, (int)M, (int)K, act, (int)N, (int)n_tiles, ksplit, dst, ldd,
                                                        ctx->error_word, tr, fold, (const uint8_t *)w, row_stride, mat_stride, rowcopy);
     B200Q_CUDA(ctx, cudaGetLastError());
     count(ctx, ST_GEMM_TC);
-    if (TYPE == B200Q_TYPE_Q4_K) {
+    if (TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K) {
         // the mins term, subtracted in place
         const int16_t *bsum = reinterpret_cast<const int16_t *>(act + (size_t)(n_tiles * (K / 256)) * kq::ACT_CHUNK);
         if (tr.tiles && ctx->moe_mins_pass) {
             dim3 g2((unsigned)(n_tiles * (kq::BN / kq::MC)), (unsigned)((M + 127) / 128));
             kq::q4k_mins_rows_kernel<<<g2, 128, 0, ctx->stream>>>((const uint8_t *)w, row_stride, mat_stride, (int)M, (int)(K / 256), act,
-                                                                 bsum, (int)N, dst, ldd, tr);
+                                                                 bsum, (int)N, dst, ldd, tr, (int)L::SBB);
         } else if (tr.tiles) {
             return B200Q_OK;                     // route tiles: the term was taken inside the GEMM
         } else {
             dim3 g2((unsigned)(n_tiles * (kq::BN / kq::MC)), (unsigned)((M + kq::MR - 1) / kq::MR));
             kq::q4k_mins_kernel<<<g2, 128, 0, ctx->stream>>>((const uint8_t *)w, row_stride, mat_stride, (int)M, (int)(K / 256), act, bsum,
-                                                            (int)N, dst, ldd, tr);
+                                                            (int)N, dst, ldd, tr, (int)L::SBB);
         }
         B200Q_CUDA(ctx, cudaGetLastError());
         count(ctx, ST_GEMM_KQ_MINS);
@@ -1000,6 +1029,7 @@ b200q_status launch_gemm_kq(b200q_ctx *ctx, int type, const void *w, size_t row_
         return launch_kq_t<B200Q_TYPE_IQ4_XS, kq::FMT_IQ4_XS_ROWS>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
     if (type == B200Q_TYPE_IQ4_XS) return launch_kq_t<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
     if (type == B200Q_TYPE_Q4_K) return launch_kq_t<B200Q_TYPE_Q4_K>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
+    if (type == B200Q_TYPE_Q5_K) return launch_kq_t<B200Q_TYPE_Q5_K>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
     if (type == B200Q_TYPE_Q6_K) return launch_kq_t<B200Q_TYPE_Q6_K>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE);
     return fail(ctx, B200Q_UNSUPPORTED, "gemm_kq: type %d", type);
 }
@@ -1018,6 +1048,8 @@ b200q_status launch_gemm_kq_id(b200q_ctx *ctx, const b200q_tensor *src0, const b
                    : launch_kq_t<B200Q_TYPE_IQ4_XS>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
     if (src0->type == B200Q_TYPE_Q4_K)
         return launch_kq_t<B200Q_TYPE_Q4_K>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
+    if (src0->type == B200Q_TYPE_Q5_K)
+        return launch_kq_t<B200Q_TYPE_Q5_K>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
     if (src0->type == B200Q_TYPE_Q6_K)
         return launch_kq_t<B200Q_TYPE_Q6_K>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
     return fail(ctx, B200Q_UNSUPPORTED, "gemm_kq_id: type %d", src0->type);

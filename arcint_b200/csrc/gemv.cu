@@ -231,6 +231,7 @@ b200q_status launch_gemv_id(b200q_ctx *ctx, int type, const void *w, size_t row_
     case B200Q_TYPE_Q4_0:   return launch_id_type<B200Q_TYPE_Q4_0>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
     case B200Q_TYPE_Q8_0:   return launch_id_type<B200Q_TYPE_Q8_0>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
     case B200Q_TYPE_Q4_K:   return launch_id_type<B200Q_TYPE_Q4_K>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
+    case B200Q_TYPE_Q5_K:   return launch_id_type<B200Q_TYPE_Q5_K>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
     case B200Q_TYPE_Q6_K:   return launch_id_type<B200Q_TYPE_Q6_K>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
     case B200Q_TYPE_IQ4_XS: return launch_id_type<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
     }
@@ -343,7 +344,7 @@ b200q_status launch_gemv_allreduce(b200q_ctx *ctx, int type, const void *w, size
     case B200Q_TYPE_Q6_K:   return launch_ar_type<B200Q_TYPE_Q6_K>(ctx, w, row_stride, M, K, act, ncols, qx, dst, ldd, ar);
     case B200Q_TYPE_IQ4_XS: return launch_ar_type<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, M, K, act, ncols, qx, dst, ldd, ar);
     }
-    return B200Q_UNSUPPORTED;
+    return B200Q_UNSUPPORTED;                 // other types (Q5_K): the caller runs the product and the all-reduce one after the other
 }
 
 b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_stride, int64_t M, int64_t K,
@@ -358,6 +359,7 @@ b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_str
     case B200Q_TYPE_Q4_0:   return launch_type<B200Q_TYPE_Q4_0>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);
     case B200Q_TYPE_Q8_0:   return launch_type<B200Q_TYPE_Q8_0>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);
     case B200Q_TYPE_Q4_K:   return launch_type<B200Q_TYPE_Q4_K>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);
+    case B200Q_TYPE_Q5_K:   return launch_type<B200Q_TYPE_Q5_K>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);
     case B200Q_TYPE_Q6_K:   return launch_type<B200Q_TYPE_Q6_K>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);
     case B200Q_TYPE_IQ4_XS: return launch_type<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);
     }

@@ -5,7 +5,7 @@
 // A "stage" is 2048 weights of a row (64 per lane); its byte size is a multiple of 16 for
 // every type, so stages are fetched with 16-byte copies:
 //   Q4_0 64 blocks = 1152 B   Q8_0 64 blocks = 2176 B   Q4_K 8 blocks = 1152 B
-//   IQ4_XS 8 blocks = 1088 B  Q6_K 8 blocks = 1680 B
+//   IQ4_XS 8 blocks = 1088 B  Q6_K 8 blocks = 1680 B    Q5_K 8 blocks = 1408 B
 // Work is split in two so the activation side is paid once per stage, not once per row:
 //   gemv_load_x   loads the lane's 64 activation codes, scales and block sums of NC columns
 //                 for stage s into registers (GemvX);
@@ -37,6 +37,7 @@ template <int TYPE> struct GemvFmt;
 template <> struct GemvFmt<B200Q_TYPE_Q4_0>   { enum { BLK_W = 32,  BLK_B = 18,  STAGE_BLOCKS = 64 }; };
 template <> struct GemvFmt<B200Q_TYPE_Q8_0>   { enum { BLK_W = 32,  BLK_B = 34,  STAGE_BLOCKS = 64 }; };
 template <> struct GemvFmt<B200Q_TYPE_Q4_K>   { enum { BLK_W = 256, BLK_B = 144, STAGE_BLOCKS = 8 }; };
+template <> struct GemvFmt<B200Q_TYPE_Q5_K>   { enum { BLK_W = 256, BLK_B = 176, STAGE_BLOCKS = 8 }; };
 template <> struct GemvFmt<B200Q_TYPE_IQ4_XS> { enum { BLK_W = 256, BLK_B = 136, STAGE_BLOCKS = 8 }; };
 template <> struct GemvFmt<B200Q_TYPE_Q6_K>   { enum { BLK_W = 256, BLK_B = 210, STAGE_BLOCKS = 8 }; };
 
@@ -163,7 +164,7 @@ B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, const i
                 }
             }
         }
-    } else if (TYPE == B200Q_TYPE_Q4_K) {
+    } else if (TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K) {
         // lane -> block sb of the stage and 32-byte group g: sub-blocks 2g (low nibbles) and
         // 2g+1 (high nibbles), 64 weights
         const int sb = lane >> 2, g = lane & 3, blk = s * F::STAGE_BLOCKS + sb;
@@ -313,6 +314,46 @@ B200Q_HD void gemv_lane_row(const uint32_t *sw_ptr, int lane, const GemvX<NC> &X
 #else
             acc[c] += X.f0[c] * (d16 * (float)si - dmin * (float)sm);
 #endif
+        }
+    } else if (TYPE == B200Q_TYPE_Q5_K) {
+        // Q4_K's lane with the fifth bits: bit 2g of byte t of qh[32] belongs to weight t of sub-block 2g (the low
+        // nibbles of the lane's 32 bytes), bit 2g + 1 to sub-block 2g + 1 (the high ones)
+        if (!X.live) return;
+        const int sb = lane >> 2, g = lane & 3;
+        const uint32_t bw = sb * (176 / 4);                 // word index; blocks are 16-byte aligned inside the stage
+        const U4 h = sw.ld16(bw);                           // d | dmin, then the 12 scale bytes
+        const float d = hd_half_bits((uint16_t)h.x);
+        const float dmin = hd_half_bits((uint16_t)(h.x >> 16));
+        const uint32_t scw = g < 2 ? (h.y & 0x3F3F3F3Fu) : ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u));
+        const uint32_t mnw = g < 2 ? (h.z & 0x3F3F3F3Fu) : (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u));
+        const int sh = 16 * (g & 1);
+        const int sc0 = (int)((scw >> sh) & 0xFFu), sc1 = (int)((scw >> (sh + 8)) & 0xFFu);
+        const uint32_t mw = mnw >> sh;                      // the mins of the lane's two sub-blocks in bytes 0 and 1
+        const U4 ha = sw.ld16(bw + 4), hb = sw.ld16(bw + 8);
+        const U4 qa = sw.ld16(bw + 12 + 8 * g), qb = sw.ld16(bw + 16 + 8 * g);
+        const uint32_t q[8] = { qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w };
+        const uint32_t hq[8] = { ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w };
+        uint32_t ql[8], qh[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t u = hq[j] >> (2 * g);            // bit 0: low sub-block's fifth bit, bit 1: the high one's
+            ql[j] = (q[j] & 0x0F0F0F0Fu) | ((u << 4) & 0x10101010u);
+            qh[j] = ((q[j] >> 4) & 0x0F0F0F0Fu) | ((u << 3) & 0x10101010u);
+        }
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            const I4 a0 = X.x[c][0], a1 = X.x[c][1], b0 = X.x[c][2], b1 = X.x[c][3];
+            int il = dp4a_ss(ql[0], a0.x, 0), ih = dp4a_ss(qh[0], b0.x, 0);
+            il = dp4a_ss(ql[1], a0.y, il);   ih = dp4a_ss(qh[1], b0.y, ih);
+            il = dp4a_ss(ql[2], a0.z, il);   ih = dp4a_ss(qh[2], b0.z, ih);
+            il = dp4a_ss(ql[3], a0.w, il);   ih = dp4a_ss(qh[3], b0.w, ih);
+            il = dp4a_ss(ql[4], a1.x, il);   ih = dp4a_ss(qh[4], b1.x, ih);
+            il = dp4a_ss(ql[5], a1.y, il);   ih = dp4a_ss(qh[5], b1.y, ih);
+            il = dp4a_ss(ql[6], a1.z, il);   ih = dp4a_ss(qh[6], b1.z, ih);
+            il = dp4a_ss(ql[7], a1.w, il);   ih = dp4a_ss(qh[7], b1.w, ih);
+            const int si = sc0 * il + sc1 * ih;                           // sum_sb sc * dot
+            const int sm = dp2a_lo_su((uint32_t)X.i0[c], mw, 0);          // sum_sb m * sum(x)
+            acc[c] += X.f0[c] * (d * (float)si - dmin * (float)sm);
         }
     } else if (TYPE == B200Q_TYPE_IQ4_XS) {
         if (!X.live) return;

@@ -13,9 +13,9 @@ from . import build as _build
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-F32, Q4_0, Q8_0, Q4_K, Q6_K, IQ4_XS, I32 = 0, 2, 8, 12, 14, 23, 26
-QUANT_TYPES = (Q4_0, Q8_0, Q4_K, Q6_K, IQ4_XS)
-TYPE_NAMES = {Q4_0: "q4_0", Q8_0: "q8_0", Q4_K: "q4_K", Q6_K: "q6_K", IQ4_XS: "iq4_xs"}
+F32, Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS, I32 = 0, 2, 8, 12, 13, 14, 23, 26
+QUANT_TYPES = (Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS)
+TYPE_NAMES = {Q4_0: "q4_0", Q8_0: "q8_0", Q4_K: "q4_K", Q5_K: "q5_K", Q6_K: "q6_K", IQ4_XS: "iq4_xs"}
 ACT_Q8_0, ACT_Q8_256 = 0, 1
 KVALUES_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.int8)
 
@@ -232,7 +232,7 @@ def random_blocks(t, rows, k, rng):
 
     if t in (Q4_0, Q8_0, IQ4_XS):
         put_half(0, 1e-3, 2e-2)
-    elif t == Q4_K:
+    elif t in (Q4_K, Q5_K):
         put_half(0, 1e-4, 2e-3, signed=False)
         put_half(2, 1e-4, 2e-3, signed=False)
     elif t == Q6_K:

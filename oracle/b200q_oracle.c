@@ -78,7 +78,7 @@ uint16_t orc_fp32_to_fp16(float f) {
 int orc_block_size(int type) {
     switch (type) {
         case ORC_TYPE_Q4_0: case ORC_TYPE_Q8_0: return QK;
-        case ORC_TYPE_Q4_K: case ORC_TYPE_Q6_K: case ORC_TYPE_IQ4_XS: return QK_K;
+        case ORC_TYPE_Q4_K: case ORC_TYPE_Q5_K: case ORC_TYPE_Q6_K: case ORC_TYPE_IQ4_XS: return QK_K;
         default: return 0;
     }
 }
@@ -88,6 +88,7 @@ size_t orc_block_bytes(int type) {
         case ORC_TYPE_Q4_0:   return 18;
         case ORC_TYPE_Q8_0:   return 34;
         case ORC_TYPE_Q4_K:   return 144;
+        case ORC_TYPE_Q5_K:   return 176;
         case ORC_TYPE_Q6_K:   return 210;
         case ORC_TYPE_IQ4_XS: return 136;
         default: return 0;
@@ -151,6 +152,17 @@ static void q4_K_codes(const uint8_t *blk, uint8_t *q /*256, 0..15*/) {
         }
 }
 
+/* Q5_K (P01:1734-1735, 3735-3739): Q4_K's nibble order behind 32 bytes of fifth bits; bit j of byte t belongs to
+ * weight t of sub-block j. Block: d, dmin, 12 scale bytes, qh[32], qs[128] (176 bytes). */
+static void q5_K_codes(const uint8_t *blk, uint8_t *q /*256, 0..31*/) {
+    const uint8_t *qh = blk + 16, *qs = blk + 48;
+    for (int g = 0; g < 4; ++g)
+        for (int i = 0; i < 32; ++i) {
+            q[64 * g + i]      = (uint8_t)((qs[32 * g + i] & 0xF) | (((qh[i] >> (2 * g)) & 1) << 4));
+            q[64 * g + 32 + i] = (uint8_t)((qs[32 * g + i] >> 4)  | (((qh[i] >> (2 * g + 1)) & 1) << 4));
+        }
+}
+
 /* Q6_K (P01:1789-1794, 3798-3802, 3849-3860): q - 32 in -32..31; scale index 8n + 2p + (t >= 16) */
 static void q6_K_codes(const uint8_t *blk, int8_t *q /*256*/) {
     const uint8_t *ql = blk, *qh = blk + 128;
@@ -195,6 +207,17 @@ int orc_dequantize_row(int type, const void *src, float *dst, int64_t k) {
         case ORC_TYPE_Q4_K: {       /* w = (d sc) q - (dmin m) */
             uint8_t q[256];
             q4_K_codes(b, q);
+            const float d = orc_fp16_to_fp32(rd16(b)), dmin = orc_fp16_to_fp32(rd16(b + 2));
+            for (int j = 0; j < 8; ++j) {
+                int sc, m;
+                q4k_scale_min(b + 4, j, &sc, &m);
+                const float dl = d * (float)sc, ml = dmin * (float)m;
+                for (int i = 0; i < 32; ++i) dst[32 * j + i] = dl * (float)q[32 * j + i] - ml;
+            }
+        } break;
+        case ORC_TYPE_Q5_K: {       /* w = (d sc) q - (dmin m), q in 0..31 */
+            uint8_t q[256];
+            q5_K_codes(b, q);
             const float d = orc_fp16_to_fp32(rd16(b)), dmin = orc_fp16_to_fp32(rd16(b + 2));
             for (int j = 0; j < 8; ++j) {
                 int sc, m;
@@ -269,12 +292,13 @@ static void quantize_q8_0(const float *x, uint8_t *b) {
  */
 static inline int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
 
-static void quantize_q4_K_standin(const float *x, uint8_t *b) {
+/* levels = 15: Q4_K (codes 0..15, 144-byte block); levels = 31: Q5_K (codes 0..31, the fifth bits in qh, 176 bytes) */
+static void quantize_q45_K_standin(const float *x, uint8_t *b, int levels) {
     float scale[8], mn[8], smax = 0.f, mmax = 0.f;
     for (int j = 0; j < 8; ++j) {
         float lo = 0.f, hi = 0.f;
         for (int i = 0; i < 32; ++i) { const float v = x[32 * j + i]; if (v < lo) lo = v; if (v > hi) hi = v; }
-        scale[j] = (hi - lo) / 15.f;
+        scale[j] = (hi - lo) / (float)levels;
         mn[j] = -lo;
         if (scale[j] > smax) smax = scale[j];
         if (mn[j] > mmax) mmax = mn[j];
@@ -304,11 +328,21 @@ static void quantize_q4_K_standin(const float *x, uint8_t *b) {
     for (int j = 0; j < 8; ++j) {
         const float dl = d * (float)sc[j], ml = dmin * (float)m[j];
         for (int i = 0; i < 32; ++i)
-            q[32 * j + i] = (uint8_t)(dl > 0.f ? clampi(nearest_away((x[32 * j + i] + ml) / dl), 0, 15) : 0);
+            q[32 * j + i] = (uint8_t)(dl > 0.f ? clampi(nearest_away((x[32 * j + i] + ml) / dl), 0, levels) : 0);
     }
+    uint8_t *qs = b + (levels == 31 ? 48 : 16);
     for (int g = 0; g < 4; ++g)
-        for (int i = 0; i < 32; ++i) b[16 + 32 * g + i] = (uint8_t)(q[64 * g + i] | (q[64 * g + 32 + i] << 4));
+        for (int i = 0; i < 32; ++i) qs[32 * g + i] = (uint8_t)((q[64 * g + i] & 0xF) | ((q[64 * g + 32 + i] & 0xF) << 4));
+    if (levels == 31) {
+        memset(b + 16, 0, 32);
+        for (int j = 0; j < 8; ++j)
+            for (int i = 0; i < 32; ++i) b[16 + i] |= (uint8_t)((q[32 * j + i] >> 4) << j);
+    }
 }
+static void quantize_q4_K_standin(const float *x, uint8_t *b) { quantize_q45_K_standin(x, b, 15); }
+static void quantize_q5_K_standin(const float *x, uint8_t *b) { quantize_q45_K_standin(x, b, 31); }
+
+
 
 static void quantize_q6_K_standin(const float *x, uint8_t *b) {
     float scale[16], smax = 0.f;
@@ -387,6 +421,7 @@ int orc_quantize_row(int type, const float *src, void *dst, int64_t k) {
         case ORC_TYPE_Q4_0:   quantize_q4_0(src, b); break;
         case ORC_TYPE_Q8_0:   quantize_q8_0(src, b); break;
         case ORC_TYPE_Q4_K:   quantize_q4_K_standin(src, b); break;
+        case ORC_TYPE_Q5_K:   quantize_q5_K_standin(src, b); break;
         case ORC_TYPE_Q6_K:   quantize_q6_K_standin(src, b); break;
         case ORC_TYPE_IQ4_XS: quantize_iq4_xs_standin(src, b); break;
         default: return -1;
@@ -543,7 +578,9 @@ static void rowx_expand(rowx_t *r, int type, const uint8_t *row, int64_t k) {
             r->f0[ib] = orc_fp16_to_fp32(rd16(b));
             break;
         case ORC_TYPE_Q4_K:
-            q4_K_codes(b, (uint8_t *)r->q + 256 * ib);
+        case ORC_TYPE_Q5_K:
+            if (type == ORC_TYPE_Q4_K) q4_K_codes(b, (uint8_t *)r->q + 256 * ib);
+            else q5_K_codes(b, (uint8_t *)r->q + 256 * ib);
             r->f0[ib] = orc_fp16_to_fp32(rd16(b));
             r->f1[ib] = orc_fp16_to_fp32(rd16(b + 2));
             for (int j = 0; j < 8; ++j) {
@@ -586,7 +623,8 @@ static float rowx_dot(const rowx_t *r, int type, const act_t *a, int64_t col) {
             sum += ((float)si * r->f0[ib]) * orc_fp16_to_fp32(xd[ib]);
         }
     } break;
-    case ORC_TYPE_Q4_K: {
+    case ORC_TYPE_Q4_K:
+    case ORC_TYPE_Q5_K: {
         const float *xd = a->d32 + col * (k / 256);
         const int16_t *bs = a->bsums + col * (k / 32);
         for (int64_t ib = 0; ib < k / 256; ++ib) {

@@ -4,7 +4,7 @@ implementation of the block formats, gguf/quants.py).
 Run in a container that has the `gguf` package:  python tests/golden/make_golden.py
 The tests only read the .npz, so they do not need gguf at run time.
 
-Contents, per block type T in {q4_0, q8_0, q4_K, q6_K, iq4_xs}:
+Contents, per block type T in {q4_0, q8_0, q4_K, q6_K, iq4_xs, q5_K}:
   T_blocks  uint8 [rows, row_bytes]  random-field blocks with sane fp16 scales
   T_deq     f32   [rows, k]          gguf.quants.dequantize(T_blocks)
 and for the two types gguf-py can quantize bit-exactly like ggml-quants.c:
@@ -20,14 +20,16 @@ from gguf import quants
 from gguf.constants import GGML_QUANT_SIZES, GGMLQuantizationType as T
 
 TYPES = {"q4_0": T.Q4_0, "q8_0": T.Q8_0, "q4_K": T.Q4_K, "q6_K": T.Q6_K, "iq4_xs": T.IQ4_XS}
+MORE_TYPES = {"q5_K": T.Q5_K}
 HALF_FIELDS = {  # byte offset of each fp16 field, (lo, hi) magnitude, signed?
     "q4_0": [(0, 1e-3, 2e-2, True)], "q8_0": [(0, 1e-3, 2e-2, True)], "iq4_xs": [(0, 1e-3, 2e-2, True)],
     "q4_K": [(0, 1e-4, 2e-3, False), (2, 1e-4, 2e-3, False)], "q6_K": [(208, 1e-5, 5e-4, True)],
+    "q5_K": [(0, 1e-4, 2e-3, False), (2, 1e-4, 2e-3, False)],
 }
 
 
 def random_blocks(name, rows, k, rng):
-    bs, bb = GGML_QUANT_SIZES[TYPES[name]]
+    bs, bb = GGML_QUANT_SIZES[TYPES[name] if name in TYPES else MORE_TYPES[name]]
     nb = k // bs
     raw = rng.integers(0, 256, size=(rows, nb, bb), dtype=np.uint8)
     for off, lo, hi, signed in HALF_FIELDS[name]:
@@ -75,6 +77,12 @@ def main():
     out["act_src"] = act
     out["act_d"] = qb[:, :, :2].copy().view(np.uint16).reshape(6, 16)
     out["act_q"] = qb[:, :, 2:].copy().view(np.int8).reshape(6, 512)
+    # types added later draw from a generator of their own, so the entries above keep their values
+    rng2 = np.random.default_rng(0xB201)
+    for name, t in MORE_TYPES.items():
+        blocks = random_blocks(name, 6, k, rng2)
+        out[name + "_blocks"] = blocks
+        out[name + "_deq"] = quants.dequantize(blocks, t).astype(np.float32)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "quant_golden.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes")

@@ -146,9 +146,10 @@ def test_config3_iq4_xs_full_size(ctx):
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 256), (128, 16, 512), (300, 17, 1024), (300, 100, 1024), (512, 300, 2560),
                                    (1023, 33, 4096), (77, 9, 768), (200, 130, 11008)])
-def test_gemm_q4_K_matches_oracle(ctx, m, n, k):
-    rng = np.random.default_rng(m * 5 + n)
-    t = A.Q4_K
+@pytest.mark.parametrize("t", [A.Q4_K, A.Q5_K])
+def test_gemm_q4_K_matches_oracle(ctx, t, m, n, k):
+    """Q4_K and Q5_K (the same block with a fifth code bit): two-limb tensor-core product plus the mins term."""
+    rng = np.random.default_rng(m * 5 + n + t)
     w = O.random_blocks(t, m, k, rng)
     x = rng.normal(0, 1, size=(n, k)).astype(np.float32)
     got, st = run(ctx, t, w, k, x)
@@ -157,11 +158,13 @@ def test_gemm_q4_K_matches_oracle(ctx, m, n, k):
     assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
 
 
-def test_gemm_q4_K_extreme_codes(ctx):
-    """All scales and mins at 63, all codes 15, activations of one sign: the largest limb sums and block sums."""
-    t, m, n, k = A.Q4_K, 128, 32, 512
+@pytest.mark.parametrize("t,bb", [(A.Q4_K, 144), (A.Q5_K, 176)])
+def test_gemm_q4_K_extreme_codes(ctx, t, bb):
+    """All scales and mins at 63, all codes at their maximum (15, 31), activations of one sign: the largest limb sums
+    and block sums."""
+    m, n, k = 128, 32, 512
     rng = np.random.default_rng(3)
-    w = O.random_blocks(t, m, k, rng).reshape(m, k // 256, 144)
+    w = O.random_blocks(t, m, k, rng).reshape(m, k // 256, bb)
     w[:, :, 4:16] = 0xFF
     w[: m // 2, :, 16:] = 0xFF
     w[m // 2:, :, 16:] = 0x00
@@ -173,8 +176,9 @@ def test_gemm_q4_K_extreme_codes(ctx):
     assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
 
 
-def test_gemm_q4_K_nmse_and_gemv_agreement(ctx):
-    t, m, n, k = A.Q4_K, 384, 72, 2048
+@pytest.mark.parametrize("t", [A.Q4_K, A.Q5_K])
+def test_gemm_q4_K_nmse_and_gemv_agreement(ctx, t):
+    m, n, k = 384, 72, 2048
     w = make_weights(t, m, k, 70)
     x = O.fill_normal(n * k, 71, 1.0).reshape(n, k)
     got, st = run(ctx, t, w, k, x)
