@@ -7,7 +7,7 @@
 // repository, so the glue is written against the FIELDS of ggml_tensor the path reads (type, ne, nb, data,
 // src[], op) as templates: include ggml.h first and instantiate with ggml_tensor, or -- as this repository's
 // device-free test does -- with any struct that has those members. ggml_type ids are used as they are
-// (Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ4_XS = 23, F32 = 0, I32 = 26).
+// (Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ4_NL = 20, IQ4_XS = 23, F32 = 0, I32 = 26).
 //
 // What a backend built on this does:
 //   supports_op(op)        -> b200q_ggml::supports_op(op, GGML_OP_MUL_MAT, GGML_OP_MUL_MAT_ID)

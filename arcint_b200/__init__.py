@@ -6,6 +6,6 @@ fallback: importing `binding` fails loudly when the library is missing.
 """
 from .binding import (  # noqa: F401
     B200QError, Context, Tensor, lib, lib_path,
-    F32, Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS, I32, OP_MUL_MAT, OP_MUL_MAT_ID,
+    F32, Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS, I32, OP_MUL_MAT, OP_MUL_MAT_ID,
     OK, UNSUPPORTED, INVALID, block_size, block_bytes, row_bytes, tp_unique_id, tp_shard,
 )

@@ -10,10 +10,10 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-F32, Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS, I32 = 0, 2, 8, 12, 13, 14, 23, 26
+F32, Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS, I32 = 0, 2, 8, 12, 13, 14, 20, 23, 26
 OP_MUL_MAT, OP_MUL_MAT_ID = 0, 1
 OK, UNSUPPORTED, INVALID, CUDA_ERROR, NO_MEMORY, NCCL_ERROR, TIMEOUT, PEER_FAILED = range(8)
-_BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_XS: (256, 136)}
+_BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_XS: (256, 136), IQ4_NL: (32, 18)}
 STATUS_NAMES = ["OK", "UNSUPPORTED", "INVALID", "CUDA_ERROR", "NO_MEMORY", "NCCL_ERROR", "TIMEOUT", "PEER_FAILED"]
 
 

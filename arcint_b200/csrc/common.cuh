@@ -33,6 +33,7 @@ __host__ __device__ inline bool type_info(int type, TypeInfo *ti) {
         case B200Q_TYPE_Q5_K:   *ti = { 256, 176, 1, "q5_K" };  return true;
         case B200Q_TYPE_Q6_K:   *ti = { 256, 210, 1, "q6_K" };  return true;
         case B200Q_TYPE_IQ4_XS: *ti = { 256, 136, 1, "iq4_xs" }; return true;
+        case B200Q_TYPE_IQ4_NL: *ti = { 32, 18, 0, "iq4_nl" };   return true;
         default: return false;
     }
 }

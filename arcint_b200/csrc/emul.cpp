@@ -113,6 +113,7 @@ int emul_gemv(int type, const uint8_t *W, size_t row_stride, int64_t M, int64_t 
     case B200Q_TYPE_Q5_K:   return emul_gemv_nc<B200Q_TYPE_Q5_K>(ncols, R, W, row_stride, M, K, a, dst, ldd);
     case B200Q_TYPE_Q6_K:   return emul_gemv_nc<B200Q_TYPE_Q6_K>(ncols, R, W, row_stride, M, K, a, dst, ldd);
     case B200Q_TYPE_IQ4_XS: return emul_gemv_nc<B200Q_TYPE_IQ4_XS>(ncols, R, W, row_stride, M, K, a, dst, ldd);
+    case B200Q_TYPE_IQ4_NL: return emul_gemv_nc<B200Q_TYPE_IQ4_NL>(ncols, R, W, row_stride, M, K, a, dst, ldd);
     }
     return -1;
 }

@@ -5,6 +5,7 @@
 //   Q4_0   18 B: fp16 d, 16 B nibbles; byte j low -> weight j, high -> j+16; w = d (n - 8)
 //          (0099-opencl-q4_0-q8_0-int8-gemm.patch:323-326)
 //   Q8_0   34 B: fp16 d, 32 int8; w = d q                      (0099-...:575-576)
+//   IQ4_NL 18 B: Q4_0's block; the nibbles index kvalues_iq4nl; w = d kv[n]   (0000-01-...:2143-2145)
 //   Q4_K  144 B: fp16 d, fp16 dmin, 12 B of 6-bit scales/mins, 128 B nibbles; group g of
 //          32 bytes: low -> sub-block 2g, high -> 2g+1; w = d sc q - dmin m
 //          (0000-01-kquant-integer-dpas.patch:1562-1576, 3735-3739)
@@ -184,6 +185,14 @@ __host__ __device__ inline float decode_weight(int type, const uint8_t *row, int
         const float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
         const int n = j < 16 ? (b[2 + j] & 0xF) : (b[2 + j - 16] >> 4);
         return mul_rn(d, (float)(n - 8));
+    }
+    case B200Q_TYPE_IQ4_NL: {
+        const uint8_t *b = row + (i / 32) * 18;
+        const int j = (int)(i % 32);
+        const float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
+        const int n = j < 16 ? (b[2 + j] & 0xF) : (b[2 + j - 16] >> 4);
+        const uint32_t kv = iq4nl_lookup4((uint32_t)n);
+        return mul_rn(d, (float)(int8_t)(kv & 0xFFu));
     }
     case B200Q_TYPE_Q8_0: {
         const uint8_t *b = row + (i / 32) * 34;

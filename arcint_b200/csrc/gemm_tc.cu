@@ -1,4 +1,4 @@
-// gemm_tc.cu -- prefill GEMM for Q4_0 / Q8_0 weights on the 5th-generation tensor cores.
+// gemm_tc.cu -- prefill GEMM for the per-32 types (Q4_0, Q8_0, IQ4_NL) on the 5th-generation tensor cores.
 //
 //   dst[M, N] = W[M, K] (packed GGUF blocks) x X[K, N] (f32), N > 8 tokens
 //
@@ -69,6 +69,7 @@ static_assert(REGS_CTRL <= LAUNCH_REGS && REGS_UNPACK <= LAUNCH_REGS && REGS_SCA
 template <int TYPE> struct Raw;     // packed bytes of one row per stage
 template <> struct Raw<B200Q_TYPE_Q4_0> { enum { ROW = SB * 18, NSTAGE = 3, A_SLOTS_F16 = 4 }; };     // 144 B per row and stage
 template <> struct Raw<B200Q_TYPE_Q8_0> { enum { ROW = SB * 34, NSTAGE = 2, A_SLOTS_F16 = 2 }; };     // 272 B: two stages fit
+template <> struct Raw<B200Q_TYPE_IQ4_NL> { enum { ROW = SB * 18, NSTAGE = 3, A_SLOTS_F16 = 4 }; };   // Q4_0's block
 
 template <int TYPE, bool F16> struct Smem {
     enum {
@@ -345,7 +346,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             for (int j = 0; j < SB; ++j) {
                 const int b = s * SB + j, slot = b % A_SLOTS;
                 if (!WAITP(5, bar(BAR_A_EMPTY + slot), ((b / A_SLOTS) & 1) ^ 1)) { ok = false; break; }
-                constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
+                constexpr int BB = TYPE == B200Q_TYPE_Q8_0 ? 34 : 18;
                 uint8_t *a = smem + L::A_OFF + slot * OPER_BYTES + (r >> 3) * 128 + (r & 7) * 16;
                 if (F16) {
                     // the block's 32 weights as exact fp16 integers, four pieces of eight
@@ -356,6 +357,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                             const uint32_t q = word_at(rw, BB * j + 2 + 4 * i);
                             bytes_to_halves(q & 0x0F0F0F0Fu, 0x64086408u, h[2 * i], h[2 * i + 1]);               // 1024 + n - 1032
                             bytes_to_halves((q >> 4) & 0x0F0F0F0Fu, 0x64086408u, h[8 + 2 * i], h[8 + 2 * i + 1]);
+                        }
+                    } else if (TYPE == B200Q_TYPE_IQ4_NL) {
+                        // the nibbles index kvalues_iq4nl (signed bytes, |v| <= 127: exact halves), then as for Q8_0
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const uint32_t q = word_at(rw, BB * j + 2 + 4 * i);
+                            bytes_to_halves(iq4nl_lookup4(q & 0x0F0F0F0Fu) ^ 0x80808080u, 0x64806480u, h[2 * i], h[2 * i + 1]);
+                            bytes_to_halves(iq4nl_lookup4((q >> 4) & 0x0F0F0F0Fu) ^ 0x80808080u, 0x64806480u, h[8 + 2 * i], h[8 + 2 * i + 1]);
                         }
                     } else {
 #pragma unroll
@@ -376,6 +385,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
                         const uint32_t q = word_at(rw, BB * j + 2 + 4 * i);
                         lo[i] = nib_minus8(q & 0x0F0F0F0Fu);           // weights 4i..4i+3
                         hi[i] = nib_minus8((q >> 4) & 0x0F0F0F0Fu);    // weights 16+4i..
+                    }
+                } else if (TYPE == B200Q_TYPE_IQ4_NL) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t q = word_at(rw, BB * j + 2 + 4 * i);
+                        lo[i] = iq4nl_lookup4(q & 0x0F0F0F0Fu);
+                        hi[i] = iq4nl_lookup4((q >> 4) & 0x0F0F0F0Fu);
                     }
                 } else {
 #pragma unroll
@@ -411,7 +427,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)acc * BN + (uint32_t)u * CW;
             // the block's fp16 weight scale, straight from the packed row in the raw stage
-            constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
+            constexpr int BB = TYPE == B200Q_TYPE_Q8_0 ? 34 : 18;
             const float dwb = row_ok ? half_bits_to_float(*reinterpret_cast<const uint16_t *>(
                                            smem + L::RAW_OFF + st * L::RAW_STAGE + r * ROWB + BB * j)) : 0.f;
             const f32x2 dw2 = f2_pack(dwb, dwb), negc2 = f2_pack(-12582912.f, -12582912.f);
@@ -513,7 +529,7 @@ size_t gemm_tc_act_bytes(int64_t K, int64_t N) {
 }
 
 bool gemm_tc_supported(int type, int64_t M, int64_t K, int64_t N, const void *w, size_t row_stride) {
-    if (type != B200Q_TYPE_Q4_0 && type != B200Q_TYPE_Q8_0) return false;
+    if (type != B200Q_TYPE_Q4_0 && type != B200Q_TYPE_Q8_0 && type != B200Q_TYPE_IQ4_NL) return false;
     if (K % (tc::SB * tc::KB) || K <= 0 || M <= 0 || N <= 0) return false;
     if ((uintptr_t)w % 16 || row_stride % 16) return false;          // bulk copies of row pieces
     if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return false;
@@ -556,7 +572,7 @@ static b200q_status launch_tf(b200q_ctx *ctx, const void *w, size_t row_stride, 
         attr_set = true;
     }
     CUtensorMap wmap;
-    constexpr int BB = TYPE == B200Q_TYPE_Q4_0 ? 18 : 34;
+    constexpr int BB = TYPE == B200Q_TYPE_Q8_0 ? 34 : 18;
     b200q_status st = make_weight_tmap3(ctx, &wmap, w, row_stride, M, (K / 32) * BB, tc::Raw<TYPE>::ROW, n_mat, mat_stride);
     if (st != B200Q_OK) return st;
     // Cut K into 2, 4 or 8 parts when the tiles alone leave SMs idle (a 512-row shard of a tensor-parallel product is
@@ -615,6 +631,7 @@ b200q_status launch_gemm_tc(b200q_ctx *ctx, int type, const void *w, size_t row_
     const size_t ms = row_stride * (size_t)M;
     if (type == B200Q_TYPE_Q4_0) return launch_t<B200Q_TYPE_Q4_0>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE_TC);
     if (type == B200Q_TYPE_Q8_0) return launch_t<B200Q_TYPE_Q8_0>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE_TC);
+    if (type == B200Q_TYPE_IQ4_NL) return launch_t<B200Q_TYPE_IQ4_NL>(ctx, w, row_stride, ms, 1, M, K, act, N, n_tiles, dst, ldd, NO_ROUTE_TC);
     return fail(ctx, B200Q_UNSUPPORTED, "gemm_tc: type %d", type);
 }
 
@@ -631,6 +648,8 @@ b200q_status launch_gemm_tc_id(b200q_ctx *ctx, const b200q_tensor *src0, const b
         return launch_t<B200Q_TYPE_Q4_0>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
     if (src0->type == B200Q_TYPE_Q8_0)
         return launch_t<B200Q_TYPE_Q8_0>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
+    if (src0->type == B200Q_TYPE_IQ4_NL)
+        return launch_t<B200Q_TYPE_IQ4_NL>(ctx, src0->data, src0->nb[1], src0->nb[2], src0->ne[2], M, K, act, 0, max_tiles, dst, 0, tr);
     return fail(ctx, B200Q_UNSUPPORTED, "gemm_tc_id: type %d", src0->type);
 }
 

@@ -234,6 +234,7 @@ b200q_status launch_gemv_id(b200q_ctx *ctx, int type, const void *w, size_t row_
     case B200Q_TYPE_Q5_K:   return launch_id_type<B200Q_TYPE_Q5_K>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
     case B200Q_TYPE_Q6_K:   return launch_id_type<B200Q_TYPE_Q6_K>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
     case B200Q_TYPE_IQ4_XS: return launch_id_type<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
+    case B200Q_TYPE_IQ4_NL: return launch_id_type<B200Q_TYPE_IQ4_NL>(ctx, w, row_stride, M, K, act, tile_pairs, dst, aligned, id, max_tiles);
     }
     return fail(ctx, B200Q_UNSUPPORTED, "gemv_id: type %d", type);
 }
@@ -362,6 +363,7 @@ b200q_status launch_gemv(b200q_ctx *ctx, int type, const void *w, size_t row_str
     case B200Q_TYPE_Q5_K:   return launch_type<B200Q_TYPE_Q5_K>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);
     case B200Q_TYPE_Q6_K:   return launch_type<B200Q_TYPE_Q6_K>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);
     case B200Q_TYPE_IQ4_XS: return launch_type<B200Q_TYPE_IQ4_XS>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);
+    case B200Q_TYPE_IQ4_NL: return launch_type<B200Q_TYPE_IQ4_NL>(ctx, w, row_stride, M, K, act, ncols, dst, ldd, aligned);
     }
     return fail(ctx, B200Q_UNSUPPORTED, "gemv: type %d", type);
 }

@@ -36,6 +36,7 @@ namespace b200q {
 template <int TYPE> struct GemvFmt;
 template <> struct GemvFmt<B200Q_TYPE_Q4_0>   { enum { BLK_W = 32,  BLK_B = 18,  STAGE_BLOCKS = 64 }; };
 template <> struct GemvFmt<B200Q_TYPE_Q8_0>   { enum { BLK_W = 32,  BLK_B = 34,  STAGE_BLOCKS = 64 }; };
+template <> struct GemvFmt<B200Q_TYPE_IQ4_NL> { enum { BLK_W = 32,  BLK_B = 18,  STAGE_BLOCKS = 64 }; };
 template <> struct GemvFmt<B200Q_TYPE_Q4_K>   { enum { BLK_W = 256, BLK_B = 144, STAGE_BLOCKS = 8 }; };
 template <> struct GemvFmt<B200Q_TYPE_Q5_K>   { enum { BLK_W = 256, BLK_B = 176, STAGE_BLOCKS = 8 }; };
 template <> struct GemvFmt<B200Q_TYPE_IQ4_XS> { enum { BLK_W = 256, BLK_B = 136, STAGE_BLOCKS = 8 }; };
@@ -132,7 +133,7 @@ template <int TYPE, int NC>
 B200Q_HD void gemv_load_x(int lane, int s, int nblk, const GemvAct &act, const int (&cols)[NC], GemvX<NC> &X) {
     typedef GemvFmt<TYPE> F;
     const int K = act.K;
-    if (TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_Q8_0) {
+    if (TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_Q8_0 || TYPE == B200Q_TYPE_IQ4_NL) {
         // two 32-blocks per lane: lane and lane + 32 of the stage
         const int b0 = s * F::STAGE_BLOCKS + lane, b1 = b0 + 32;
         X.live = b0 < nblk;
@@ -241,6 +242,31 @@ B200Q_HD void gemv_lane_row(const uint32_t *sw_ptr, int lane, const GemvX<NC> &X
                 hi0 = dp4a_us(q[2] & 0xF0F0F0F0u, xb.z, hi0);   hi1 = dp4a_us(q[3] & 0xF0F0F0F0u, xb.w, hi1);
                 const int si = 16 * (lo0 + lo1) + (hi0 + hi1);                // 16 * sum((n - 8) x)
                 acc[c] += (float)si * (d * (u ? X.f1[c] : X.f0[c]));
+            }
+        }
+    } else if (TYPE == B200Q_TYPE_IQ4_NL) {
+        // Q4_0's block with the nibbles as indices into kvalues_iq4nl: the codebook values are signed bytes, so no
+        // offset term; the lookup (byte permutes) is shared by all columns
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (!(u ? X.live2 : X.live)) continue;
+            const uint32_t off = (uint32_t)F::BLK_B * (uint32_t)(32 * u + lane);
+            const float d = hd_half_bits(stage_u16(sw, off));
+            uint32_t q[4], lo[4], hi[4];
+            stage_words<4>(sw, off + 2, q);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                lo[j] = iq4nl_lookup4(q[j] & 0x0F0F0F0Fu);              // weights 4j .. 4j + 3
+                hi[j] = iq4nl_lookup4((q[j] >> 4) & 0x0F0F0F0Fu);       // weights 16 + 4j ..
+            }
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const I4 xa = X.x[c][2 * u], xb = X.x[c][2 * u + 1];
+                int s0 = dp4a_ss(lo[0], xa.x, 0), s1 = dp4a_ss(lo[1], xa.y, 0);
+                s0 = dp4a_ss(lo[2], xa.z, s0); s1 = dp4a_ss(lo[3], xa.w, s1);
+                s0 = dp4a_ss(hi[0], xb.x, s0); s1 = dp4a_ss(hi[1], xb.y, s1);
+                s0 = dp4a_ss(hi[2], xb.z, s0); s1 = dp4a_ss(hi[3], xb.w, s1);
+                acc[c] += (float)(s0 + s1) * (d * (u ? X.f1[c] : X.f0[c]));
             }
         }
     } else if (TYPE == B200Q_TYPE_Q8_0) {

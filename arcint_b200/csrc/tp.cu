@@ -365,7 +365,7 @@ b200q_status b200q_mul_mat_allreduce(b200q_ctx *ctx, const b200q_tensor *src0, c
         // small per-32 products quantize inside the kernel; the rest take the cached quantized activation
         TypeInfo ti;
         type_info(src0->type, &ti);
-        const bool qx = ti.act_form == ACT_Q8_0 && N <= 2 && ctx->fuse_quant_bytes > 0 &&
+        const bool qx = (src0->type == B200Q_TYPE_Q4_0 || src0->type == B200Q_TYPE_Q8_0) && N <= 2 && ctx->fuse_quant_bytes > 0 &&
                         (int64_t)((size_t)(K / ti.block) * ti.bytes * (size_t)M) <= ctx->fuse_quant_bytes;
         ActView av;
         if (!qx && (st = get_decode_activation(ctx, src0->type, src1, &av)) != B200Q_OK) return st;

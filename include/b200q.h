@@ -1,6 +1,6 @@
 /*
  * b200q.h -- C ABI of the B200 (sm_100a) quantized weight mat-mul: ggml's
- * GGML_OP_MUL_MAT and GGML_OP_MUL_MAT_ID over Q4_0, Q8_0, Q4_K, Q5_K, Q6_K and IQ4_XS
+ * GGML_OP_MUL_MAT and GGML_OP_MUL_MAT_ID over Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL and IQ4_XS
  * weights with f32 activations and f32 results.
  *
  * The entry points are what a ggml backend binds for this path. Each one names the
@@ -55,6 +55,7 @@ enum {
     B200Q_TYPE_Q4_K = 12,
     B200Q_TYPE_Q5_K = 13,
     B200Q_TYPE_Q6_K = 14,
+    B200Q_TYPE_IQ4_NL = 20,
     B200Q_TYPE_IQ4_XS = 23,
     B200Q_TYPE_I32 = 26
 };

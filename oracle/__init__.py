@@ -13,9 +13,9 @@ from . import build as _build
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-F32, Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS, I32 = 0, 2, 8, 12, 13, 14, 23, 26
-QUANT_TYPES = (Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS)
-TYPE_NAMES = {Q4_0: "q4_0", Q8_0: "q8_0", Q4_K: "q4_K", Q5_K: "q5_K", Q6_K: "q6_K", IQ4_XS: "iq4_xs"}
+F32, Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS, I32 = 0, 2, 8, 12, 13, 14, 20, 23, 26
+QUANT_TYPES = (Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS, IQ4_NL)
+TYPE_NAMES = {Q4_0: "q4_0", Q8_0: "q8_0", Q4_K: "q4_K", Q5_K: "q5_K", Q6_K: "q6_K", IQ4_XS: "iq4_xs", IQ4_NL: "iq4_nl"}
 ACT_Q8_0, ACT_Q8_256 = 0, 1
 KVALUES_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.int8)
 
@@ -89,7 +89,7 @@ def row_bytes(t, k):
 
 
 def act_form(t):
-    return ACT_Q8_0 if t in (Q4_0, Q8_0) else ACT_Q8_256
+    return ACT_Q8_0 if t in (Q4_0, Q8_0, IQ4_NL) else ACT_Q8_256
 
 
 def num_threads():
@@ -230,7 +230,7 @@ def random_blocks(t, rows, k, rng):
         raw[:, :, off] = (h & 0xFF).astype(np.uint8)
         raw[:, :, off + 1] = (h >> 8).astype(np.uint8)
 
-    if t in (Q4_0, Q8_0, IQ4_XS):
+    if t in (Q4_0, Q8_0, IQ4_XS, IQ4_NL):
         put_half(0, 1e-3, 2e-2)
     elif t in (Q4_K, Q5_K):
         put_half(0, 1e-4, 2e-3, signed=False)

@@ -77,7 +77,7 @@ uint16_t orc_fp32_to_fp16(float f) {
 
 int orc_block_size(int type) {
     switch (type) {
-        case ORC_TYPE_Q4_0: case ORC_TYPE_Q8_0: return QK;
+        case ORC_TYPE_Q4_0: case ORC_TYPE_Q8_0: case ORC_TYPE_IQ4_NL: return QK;
         case ORC_TYPE_Q4_K: case ORC_TYPE_Q5_K: case ORC_TYPE_Q6_K: case ORC_TYPE_IQ4_XS: return QK_K;
         default: return 0;
     }
@@ -86,6 +86,7 @@ int orc_block_size(int type) {
 size_t orc_block_bytes(int type) {
     switch (type) {
         case ORC_TYPE_Q4_0:   return 18;
+        case ORC_TYPE_IQ4_NL: return 18;
         case ORC_TYPE_Q8_0:   return 34;
         case ORC_TYPE_Q4_K:   return 144;
         case ORC_TYPE_Q5_K:   return 176;
@@ -101,7 +102,7 @@ size_t orc_row_bytes(int type, int64_t k) {
 }
 
 int orc_act_form(int type) {
-    return (type == ORC_TYPE_Q4_0 || type == ORC_TYPE_Q8_0) ? ORC_ACT_Q8_0 : ORC_ACT_Q8_256;
+    return (type == ORC_TYPE_Q4_0 || type == ORC_TYPE_Q8_0 || type == ORC_TYPE_IQ4_NL) ? ORC_ACT_Q8_0 : ORC_ACT_Q8_256;
 }
 
 static inline uint16_t rd16(const uint8_t *p) { return (uint16_t)(p[0] | (p[1] << 8)); }
@@ -139,6 +140,15 @@ static void q4_0_codes(const uint8_t *blk, int8_t *q /*32*/) {
     for (int j = 0; j < 16; ++j) {
         q[j]      = (int8_t)((blk[2 + j] & 0xF) - 8);
         q[j + 16] = (int8_t)((blk[2 + j] >> 4) - 8);
+    }
+}
+
+/* IQ4_NL (P01:2143-2145 the codebook; P115:1057-1085 lists the type beside Q4_0): Q4_0's 18-byte block and nibble order,
+ * the nibbles index kvalues_iq4nl; w = d kv[n] */
+static void iq4_nl_codes(const uint8_t *blk, int8_t *q /*32, codebook values*/) {
+    for (int j = 0; j < 16; ++j) {
+        q[j]      = KV_IQ4NL[blk[2 + j] & 0xF];
+        q[j + 16] = KV_IQ4NL[blk[2 + j] >> 4];
     }
 }
 
@@ -197,6 +207,12 @@ int orc_dequantize_row(int type, const void *src, float *dst, int64_t k) {
         case ORC_TYPE_Q4_0: {
             int8_t q[32];
             q4_0_codes(b, q);
+            const float d = orc_fp16_to_fp32(rd16(b));
+            for (int i = 0; i < 32; ++i) dst[i] = d * (float)q[i];
+        } break;
+        case ORC_TYPE_IQ4_NL: {
+            int8_t q[32];
+            iq4_nl_codes(b, q);
             const float d = orc_fp16_to_fp32(rd16(b));
             for (int i = 0; i < 32; ++i) dst[i] = d * (float)q[i];
         } break;
@@ -411,6 +427,29 @@ static void quantize_iq4_xs_standin(const float *x, uint8_t *b) {
     memcpy(b + 4, sl, 4);
 }
 
+/* stand-in: d = amax / 127 with the sign of the largest element's partner value (kv[0] = -127), nearest codebook entry */
+static void quantize_iq4_nl_standin(const float *x, uint8_t *b) {
+    float amax = 0.f, vmax = 0.f;
+    for (int i = 0; i < 32; ++i) { const float a = fabsf(x[i]); if (a > amax) { amax = a; vmax = x[i]; } }
+    const uint16_t dh = orc_fp32_to_fp16(vmax / -127.f);        /* the largest element lands on kv[0] = -127 */
+    const float d = orc_fp16_to_fp32(dh);
+    uint8_t q[32];
+    for (int i = 0; i < 32; ++i) {
+        int best = 8;
+        if (d != 0.f) {
+            const float v = x[i] / d;
+            float be = INFINITY;
+            for (int c = 0; c < 16; ++c) {
+                const float e = fabsf(v - (float)KV_IQ4NL[c]);
+                if (e < be) { be = e; best = c; }
+            }
+        }
+        q[i] = (uint8_t)best;
+    }
+    wr16(b, dh);
+    for (int j = 0; j < 16; ++j) b[2 + j] = (uint8_t)(q[j] | (q[j + 16] << 4));
+}
+
 int orc_quantize_row(int type, const float *src, void *dst, int64_t k) {
     const int bs = orc_block_size(type);
     if (!bs || k % bs) return -1;
@@ -424,6 +463,7 @@ int orc_quantize_row(int type, const float *src, void *dst, int64_t k) {
         case ORC_TYPE_Q5_K:   quantize_q5_K_standin(src, b); break;
         case ORC_TYPE_Q6_K:   quantize_q6_K_standin(src, b); break;
         case ORC_TYPE_IQ4_XS: quantize_iq4_xs_standin(src, b); break;
+        case ORC_TYPE_IQ4_NL: quantize_iq4_nl_standin(src, b); break;
         default: return -1;
         }
     }
@@ -577,6 +617,10 @@ static void rowx_expand(rowx_t *r, int type, const uint8_t *row, int64_t k) {
             memcpy(r->q + 32 * ib, b + 2, 32);
             r->f0[ib] = orc_fp16_to_fp32(rd16(b));
             break;
+        case ORC_TYPE_IQ4_NL:
+            iq4_nl_codes(b, r->q + 32 * ib);
+            r->f0[ib] = orc_fp16_to_fp32(rd16(b));
+            break;
         case ORC_TYPE_Q4_K:
         case ORC_TYPE_Q5_K:
             if (type == ORC_TYPE_Q4_K) q4_K_codes(b, (uint8_t *)r->q + 256 * ib);
@@ -616,7 +660,8 @@ static float rowx_dot(const rowx_t *r, int type, const act_t *a, int64_t col) {
     float sum = 0.f;
     switch (type) {
     case ORC_TYPE_Q4_0:
-    case ORC_TYPE_Q8_0: {
+    case ORC_TYPE_Q8_0:
+    case ORC_TYPE_IQ4_NL: {
         const uint16_t *xd = a->d16 + col * (k / 32);
         for (int64_t ib = 0; ib < k / 32; ++ib) {
             const int si = dot_s8(r->q + 32 * ib, xq + 32 * ib, 32);

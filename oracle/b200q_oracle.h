@@ -35,6 +35,7 @@ enum {
     ORC_TYPE_Q4_K   = 12,
     ORC_TYPE_Q5_K   = 13,
     ORC_TYPE_Q6_K   = 14,
+    ORC_TYPE_IQ4_NL = 20,
     ORC_TYPE_IQ4_XS = 23,
     ORC_TYPE_I32    = 26
 };

@@ -4,7 +4,7 @@ implementation of the block formats, gguf/quants.py).
 Run in a container that has the `gguf` package:  python tests/golden/make_golden.py
 The tests only read the .npz, so they do not need gguf at run time.
 
-Contents, per block type T in {q4_0, q8_0, q4_K, q6_K, iq4_xs, q5_K}:
+Contents, per block type T in {q4_0, q8_0, q4_K, q6_K, iq4_xs, q5_K, iq4_nl}:
   T_blocks  uint8 [rows, row_bytes]  random-field blocks with sane fp16 scales
   T_deq     f32   [rows, k]          gguf.quants.dequantize(T_blocks)
 and for the two types gguf-py can quantize bit-exactly like ggml-quants.c:
@@ -20,11 +20,11 @@ from gguf import quants
 from gguf.constants import GGML_QUANT_SIZES, GGMLQuantizationType as T
 
 TYPES = {"q4_0": T.Q4_0, "q8_0": T.Q8_0, "q4_K": T.Q4_K, "q6_K": T.Q6_K, "iq4_xs": T.IQ4_XS}
-MORE_TYPES = {"q5_K": T.Q5_K}
+MORE_TYPES = {"q5_K": T.Q5_K, "iq4_nl": T.IQ4_NL}
 HALF_FIELDS = {  # byte offset of each fp16 field, (lo, hi) magnitude, signed?
     "q4_0": [(0, 1e-3, 2e-2, True)], "q8_0": [(0, 1e-3, 2e-2, True)], "iq4_xs": [(0, 1e-3, 2e-2, True)],
     "q4_K": [(0, 1e-4, 2e-3, False), (2, 1e-4, 2e-3, False)], "q6_K": [(208, 1e-5, 5e-4, True)],
-    "q5_K": [(0, 1e-4, 2e-3, False), (2, 1e-4, 2e-3, False)],
+    "q5_K": [(0, 1e-4, 2e-3, False), (2, 1e-4, 2e-3, False)], "iq4_nl": [(0, 1e-3, 2e-2, True)],
 }
 
 

@@ -178,7 +178,7 @@ def rel_err(got, ref):
 # K values: one full stage, several stages, a ragged last stage, a single block
 KS = {O.Q4_0: [32, 96, 1024, 2080, 4096, 6176], O.Q8_0: [32, 96, 1024, 2080, 4128], O.Q4_K: [256, 1024, 2816, 4096, 5120],
       O.Q5_K: [256, 1024, 2816, 4096, 5120],
-      O.Q6_K: [256, 2048, 2816, 4096, 4352], O.IQ4_XS: [256, 1024, 2816, 5120]}
+      O.Q6_K: [256, 2048, 2816, 4096, 4352], O.IQ4_XS: [256, 1024, 2816, 5120], O.IQ4_NL: [32, 96, 1024, 2080, 4096, 6176]}
 
 
 @pytest.mark.parametrize("t", O.QUANT_TYPES)

@@ -27,7 +27,7 @@ def run(ctx, t, w, k, x):
     return got, ctx.stats()
 
 
-@pytest.mark.parametrize("t", [A.Q4_0, A.Q8_0])
+@pytest.mark.parametrize("t", [A.Q4_0, A.Q8_0, A.IQ4_NL])
 @pytest.mark.parametrize("m,n,k", [(128, 128, 256), (128, 16, 256), (256, 128, 512), (300, 17, 1024), (300, 40, 1024),
                                    (300, 64, 1024), (300, 100, 1024), (1023, 33, 4096), (77, 9, 4096), (512, 300, 2560)])
 def test_gemm_tc_matches_oracle(ctx, t, m, n, k):
@@ -40,7 +40,7 @@ def test_gemm_tc_matches_oracle(ctx, t, m, n, k):
     assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
 
 
-@pytest.mark.parametrize("t", [A.Q4_0, A.Q8_0])
+@pytest.mark.parametrize("t", [A.Q4_0, A.Q8_0, A.IQ4_NL])
 def test_gemm_tc_nmse_against_f32_activations(ctx, t):
     m, n, k = 384, 200, 2048
     w = make_weights(t, m, k, 60 + t)

@@ -13,8 +13,8 @@ from gpu_util import TOL, make_weights, nmse, rel_err
 
 pytestmark = pytest.mark.gpu
 
-TYPES = [A.Q4_0, A.Q8_0, A.Q4_K, A.Q5_K, A.Q6_K, A.IQ4_XS]
-NAMES = {A.Q4_0: "q4_0", A.Q8_0: "q8_0", A.Q4_K: "q4_K", A.Q5_K: "q5_K", A.Q6_K: "q6_K", A.IQ4_XS: "iq4_xs"}
+TYPES = [A.Q4_0, A.Q8_0, A.Q4_K, A.Q5_K, A.Q6_K, A.IQ4_XS, A.IQ4_NL]
+NAMES = {A.Q4_0: "q4_0", A.Q8_0: "q8_0", A.Q4_K: "q4_K", A.Q5_K: "q5_K", A.Q6_K: "q6_K", A.IQ4_XS: "iq4_xs", A.IQ4_NL: "iq4_nl"}
 
 
 @pytest.fixture(scope="module")

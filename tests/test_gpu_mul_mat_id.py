@@ -61,7 +61,7 @@ def check(ctx, t, n_expert, n_used, n_tok, m, k, ne11_is_one, seed, off=0, dup=F
     return st
 
 
-@pytest.mark.parametrize("t", [A.Q4_K, A.Q5_K, A.Q4_0, A.IQ4_XS, A.Q6_K, A.Q8_0])
+@pytest.mark.parametrize("t", [A.Q4_K, A.Q5_K, A.Q4_0, A.IQ4_XS, A.IQ4_NL, A.Q6_K, A.Q8_0])
 @pytest.mark.parametrize("n_tok", [1, 2, 4, 5, 16, 33])
 def test_mul_mat_id_types_and_token_counts(ctx, t, n_tok):
     st = check(ctx, t, n_expert=16, n_used=4, n_tok=n_tok, m=72, k=512, ne11_is_one=(n_tok % 2 == 1), seed=n_tok + t)
@@ -135,7 +135,7 @@ def test_mul_mat_id_shape_errors(ctx):
 
 # ---- prompt-sized batches: the route's 128-pair tiles through the tensor-core GEMM ----
 
-@pytest.mark.parametrize("t", [A.Q4_K, A.Q5_K, A.IQ4_XS, A.Q4_0, A.Q8_0])
+@pytest.mark.parametrize("t", [A.Q4_K, A.Q5_K, A.IQ4_XS, A.IQ4_NL, A.Q4_0, A.Q8_0])
 @pytest.mark.parametrize("n_expert,n_used,n_tok,ne11_is_one", [(8, 2, 300, True), (8, 2, 300, False), (4, 4, 700, True),
                                                                (32, 8, 64, False)])
 def test_mul_mat_id_tensor_core_tiles(ctx, t, n_expert, n_used, n_tok, ne11_is_one):

@@ -8,8 +8,8 @@ import pytest
 
 import oracle as O
 
-NAMES = {"q4_0": O.Q4_0, "q8_0": O.Q8_0, "q4_K": O.Q4_K, "q5_K": O.Q5_K, "q6_K": O.Q6_K, "iq4_xs": O.IQ4_XS}
-SIZES = {O.Q4_0: (32, 18), O.Q8_0: (32, 34), O.Q4_K: (256, 144), O.Q5_K: (256, 176), O.Q6_K: (256, 210), O.IQ4_XS: (256, 136)}
+NAMES = {"q4_0": O.Q4_0, "q8_0": O.Q8_0, "q4_K": O.Q4_K, "q5_K": O.Q5_K, "q6_K": O.Q6_K, "iq4_xs": O.IQ4_XS, "iq4_nl": O.IQ4_NL}
+SIZES = {O.Q4_0: (32, 18), O.Q8_0: (32, 34), O.Q4_K: (256, 144), O.Q5_K: (256, 176), O.Q6_K: (256, 210), O.IQ4_XS: (256, 136), O.IQ4_NL: (32, 18)}
 
 
 def test_block_sizes():
@@ -67,13 +67,13 @@ def test_act_q8_0_matches_gguf_golden(golden):
     assert np.array_equal(q, golden["act_q"]) and np.array_equal(d, golden["act_d"])
 
 
-@pytest.mark.parametrize("t", [O.Q4_K, O.Q5_K, O.Q6_K, O.IQ4_XS, O.Q4_0, O.Q8_0])
+@pytest.mark.parametrize("t", [O.Q4_K, O.Q5_K, O.Q6_K, O.IQ4_XS, O.IQ4_NL, O.Q4_0, O.Q8_0])
 def test_standin_quantizers_are_close(t):
     """The stand-in quantizers must produce valid blocks whose decode is near the input."""
     w = O.fill_normal(8 * 1024, 7, 0.02).reshape(8, 1024)
     deq = O.dequantize(t, O.quantize(t, w), 1024)
     rel = np.sqrt(np.mean((deq - w) ** 2)) / np.sqrt(np.mean(w ** 2))
-    assert rel < {O.Q4_0: 0.12, O.Q8_0: 0.01, O.Q4_K: 0.09, O.Q5_K: 0.05, O.Q6_K: 0.03, O.IQ4_XS: 0.09}[t]
+    assert rel < {O.Q4_0: 0.12, O.Q8_0: 0.01, O.Q4_K: 0.09, O.Q5_K: 0.05, O.Q6_K: 0.03, O.IQ4_XS: 0.09, O.IQ4_NL: 0.09}[t]
 
 
 def test_act_q8_256_rule():

@@ -54,7 +54,7 @@ def test_two_calls_in_a_row_match_mul_mat(ctx, t, k):
         assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
 
 
-@pytest.mark.parametrize("t", [A.Q4_0, A.Q8_0, A.Q4_K, A.Q5_K, A.Q6_K, A.IQ4_XS])
+@pytest.mark.parametrize("t", [A.Q4_0, A.Q8_0, A.Q4_K, A.Q5_K, A.Q6_K, A.IQ4_XS, A.IQ4_NL])
 def test_the_array_filled_to_its_limits(ctx, t):
     """8 columns of 32768 values fill every part of the fixed array exactly (codes, scales, both kinds of
     block sums): a part one element short would overwrite its neighbour. Then a narrow call with other
