@@ -101,6 +101,23 @@ def build_emul(force=False, define=None):
     raise RuntimeError("emul build failed:\n" + err[-2000:])
 
 
+def build_gguf(force=False):
+    """The GGUF reader of adapters/gguf (plain C++, no CUDA): g++ into lib/libb200q_gguf.so."""
+    src = os.path.join(HERE, "..", "adapters", "gguf", "b200q_gguf.cpp")
+    hdr = os.path.join(HERE, "..", "adapters", "gguf", "b200q_gguf.h")
+    if not os.path.exists(src):
+        return None
+    os.makedirs(LIBDIR, exist_ok=True)
+    out = os.path.join(LIBDIR, "libb200q_gguf.so")
+    if not force and not _stale(out, [src, hdr, os.path.join(HERE, "..", "include", "b200q.h")]):
+        return out
+    cxx = shutil.which(os.environ.get("CXX", "g++")) or "/usr/bin/g++"
+    r = subprocess.run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", src, "-o", out], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("gguf reader build failed:\n" + r.stderr[-2000:])
+    return out
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
