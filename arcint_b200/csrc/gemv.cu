@@ -112,9 +112,10 @@ static bool try_launch_stream(b200q_ctx *ctx, const void *w, size_t row_stride, 
     GemvAr ar_args = {};
     if (ar) ar_args = *ar;
     // Q6_K at four and more columns in blocks of one 128-thread group: the build with room for 170 registers
-    constexpr bool has_small = (TYPE == B200Q_TYPE_Q6_K || TYPE == B200Q_TYPE_Q4_K) && NC >= 4 && !QX && !AR;
+    constexpr bool has_small = ((TYPE == B200Q_TYPE_Q6_K && NC >= 2) || (TYPE == B200Q_TYPE_Q4_K && NC >= 4)) && !QX && !AR;
     if constexpr (has_small) {
         if (threads <= 128 && !ctx->gemv_no_small) {
+            // (two blocks per SM with up to 255 registers measured slower: Q6_K 8 columns 60.4 against 55.5 us)
             *st = launch_stream_kernel<TYPE, NC, R, NSETS, QX, AR, 128, 3>(ctx, threads, smem, groups, w, row_stride, M, nblk, act, dst, ldd, ar_args);
             return true;
         }
