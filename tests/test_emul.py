@@ -120,7 +120,8 @@ def test_q4k_two_limbs_and_packed_scales():
     E.emul_q4k_scale_min.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]
     rng = np.random.default_rng(1)
     for sc in range(64):
-        for idx4 in [np.arange(4) + 4 * g for g in range(4)] + [rng.integers(0, 16, 4) for _ in range(4)]:
+        # codes 0..15 (Q4_K) and 0..31 (Q5_K: the same limbs, sc * q <= 63 * 31)
+        for idx4 in [np.arange(4) + 4 * g for g in range(8)] + [rng.integers(0, 32, 4) for _ in range(4)]:
             idx = int(idx4[0]) | (int(idx4[1]) << 8) | (int(idx4[2]) << 16) | (int(idx4[3]) << 24)
             out = (C.c_uint32 * 2)()
             E.emul_q4k_limbs4(idx, sc, out)
@@ -129,7 +130,7 @@ def test_q4k_two_limbs_and_packed_scales():
                 lo = (out[1] >> (8 * b)) & 0xFF
                 hi = hi - 256 if hi >= 128 else hi
                 lo = lo - 256 if lo >= 128 else lo
-                assert 256 * hi + lo == sc * int(q) and 0 <= hi <= 4
+                assert 256 * hi + lo == sc * int(q) and 0 <= hi <= 8 and -128 <= lo <= 127
     for _ in range(200):
         s0, s1, s2 = (int(v) for v in rng.integers(0, 1 << 32, 3, dtype=np.uint64))
         out = (C.c_uint32 * 4)()
@@ -141,7 +142,8 @@ def test_q4k_two_limbs_and_packed_scales():
             assert (out[2 + j // 4] >> (8 * (j % 4))) & 0xFF == m.value
 
 
-@pytest.mark.parametrize("name,t", [("q4_0", O.Q4_0), ("q8_0", O.Q8_0), ("q4_K", O.Q4_K), ("q6_K", O.Q6_K), ("iq4_xs", O.IQ4_XS)])
+@pytest.mark.parametrize("name,t", [("q4_0", O.Q4_0), ("q8_0", O.Q8_0), ("q4_K", O.Q4_K), ("q5_K", O.Q5_K), ("q6_K", O.Q6_K), ("iq4_xs", O.IQ4_XS),
+                                    ("iq4_nl", O.IQ4_NL)])
 def test_device_decoder_text_matches_gguf_golden(golden, name, t):
     E = emul()
     blocks, want = golden[name + "_blocks"], golden[name + "_deq"]
