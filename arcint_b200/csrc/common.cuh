@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "../../include/b200q.h"
+#include "../../include/b200q_test.h"
 
 #define QK   32
 #define QK_K 256

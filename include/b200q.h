@@ -223,12 +223,6 @@ B200Q_API b200q_status b200q_host_free(void *host_ptr);
 B200Q_API const char  *b200q_stats(b200q_ctx *ctx);
 B200Q_API void         b200q_stats_reset(b200q_ctx *ctx);
 
-/* Device timing for benchmarks: cudaEvent pairs on the context's stream. */
-B200Q_API b200q_status b200q_timer_start(b200q_ctx *ctx);
-B200Q_API b200q_status b200q_timer_stop(b200q_ctx *ctx, float *elapsed_ms);  /* synchronizes */
-/* writes a buffer larger than L2 so the next launch starts cold */
-B200Q_API b200q_status b200q_flush_l2(b200q_ctx *ctx);
-
 /* No counterpart in the reference (its backend always owns scratch buffers it may grow).
  * b200q_mul_mat for at most 8 activation columns of at most 32768 values each, for callers
  * that cannot allocate device memory: a host whose own pool took all of the GPU's memory at
@@ -250,17 +244,9 @@ B200Q_API b200q_status b200q_mul_mat_noalloc(int device, void *stream, const b20
 B200Q_API const char  *b200q_noalloc_last_error(void);
 B200Q_API b200q_status b200q_noalloc_device_error(int device, int *error);
 
-/* Debug views of what the kernels see, for bit-exact parity tests: the quantized
- * activation (codes [N][K] int8; scales fp16 [N][K/32] for Q4_0/Q8_0 weights or f32
- * [N][K/256] for the 256-block types; sums int16 [N][K/32] of each 32 codes) and
- * the dequantized weight rows the device decoders produce (f32 [M][K]). */
-B200Q_API b200q_status b200q_debug_quantize_act(b200q_ctx *ctx, int weight_type, const b200q_tensor *src1,
-                                                void *dev_codes, void *dev_scales, void *dev_sums);
-B200Q_API b200q_status b200q_debug_dequantize(b200q_ctx *ctx, const b200q_tensor *src0, float *dev_out);
-/* Failure-path check: enqueues a one-thread kernel whose bounded wait (at most `polls` polls of a barrier
- * nobody arrives at) must run out; like every kernel of the library it then sets the context's error word
- * and returns, so the next b200q_synchronize answers B200Q_TIMEOUT and the context stays usable. */
-B200Q_API b200q_status b200q_debug_wait_timeout(b200q_ctx *ctx, unsigned polls);
+/* Measurement and test helpers (device timers, an L2 flush, debug views of the kernels' operands, the failure-path
+ * check) are declared in b200q_test.h: they are exported by the same library but are not part of the boundary a
+ * backend binds. */
 
 #ifdef __cplusplus
 }

@@ -1,4 +1,4 @@
-"""The C-ABI library loads and exports every symbol include/b200q.h declares (no compute)."""
+"""The C-ABI library loads and exports every symbol include/b200q.h and include/b200q_test.h declare (no compute)."""
 import ctypes as C
 import os
 import re
@@ -12,7 +12,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "b200q.h")).read()
+    # the boundary (b200q.h) and the measurement / test helpers exported beside it (b200q_test.h)
+    text = open(os.path.join(ROOT, "include", "b200q.h")).read() + open(os.path.join(ROOT, "include", "b200q_test.h")).read()
     return sorted(set(re.findall(r"B200Q_API\s+[\w\s\*]+?\b(b200q_\w+)\s*\(", text)))
 
 
