@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """bench.py -- the path's headline measurement on B200.
 
-Default workload ("decode_gemv", BASELINE config 2): the decode GEMV over a Llama-7B-shaped
+Default workload ("decode_gemv", benchmark config 2): the decode GEMV over a Llama-7B-shaped
 set of quantized weights -- Q4_K gate/up 11008x4096, Q4_K down 4096x11008, Q6_K LM head
 32000x4096 -- at batch 1, 2, 4 and 8 f32 activation columns. One step = all twelve
 products once, each through b200q_mul_mat (activation quantize + GEMV).
@@ -16,7 +16,7 @@ products once, each through b200q_mul_mat (activation quantize + GEMV).
 
 Weights rotate over distinct device copies whose total footprint is several times the
 126 MB L2, so no product finds its weights in cache. Under torchrun each rank runs a
-replica (the decode config is single-GPU in BASELINE; it does not shard).
+replica (the decode configuration of the benchmark definition is single-GPU; it does not shard).
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
 """

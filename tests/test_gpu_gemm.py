@@ -73,7 +73,7 @@ def test_gemm_shapes_outside_the_tensor_core_gate_fall_back(ctx):
 
 
 def test_config1_full_size(ctx):
-    """BASELINE config 1: Q4_0 4096 x 4096 weights, 512 tokens; sampled rows against the oracle."""
+    """benchmark config 1: Q4_0 4096 x 4096 weights, 512 tokens; sampled rows against the oracle."""
     t, m, n, k = A.Q4_0, 4096, 512, 4096
     w = make_weights(t, m, k, 0x5EED0000)
     x = O.fill_normal(n * k, 0x5EED0100, 1.0).reshape(n, k)
@@ -130,7 +130,7 @@ def test_gemm_iq4_xs_odd_superblock_count(ctx, m, k, n):
 
 
 def test_config3_iq4_xs_full_size(ctx):
-    """BASELINE config 3: IQ4_XS 17408 x 5120 at 512 tokens; sampled rows against the oracle."""
+    """benchmark config 3: IQ4_XS 17408 x 5120 at 512 tokens; sampled rows against the oracle."""
     t, m, n, k = A.IQ4_XS, 17408, 512, 5120
     base = make_weights(t, 512, k, 0x5EED0002)
     w = np.tile(base, (m // 512, 1))

@@ -210,7 +210,7 @@ def test_activation_cache_within_a_graph(ctx):
 @pytest.mark.parametrize("t,m,k", [(A.Q4_K, 11008, 4096), (A.Q4_K, 4096, 11008), (A.Q6_K, 32000, 4096),
                                    (A.Q4_0, 4096, 4096), (A.Q8_0, 3072, 3072), (A.IQ4_XS, 5120, 17408)])
 def test_full_size_decode_shapes_sampled_rows(ctx, t, m, k):
-    """BASELINE decode shapes at batch 1 and 8: every output is produced, sampled rows are
+    """The benchmark's decode shapes at batch 1 and 8: every output is produced, sampled rows are
     checked against the oracle (rows are independent, so a row subset is a valid oracle case)."""
     rng = np.random.default_rng(m + k)
     base = make_weights(t, 512, k, 40 + t)

@@ -84,7 +84,7 @@ def test_mul_mat_id_duplicates_and_offset_view(ctx):
 
 @pytest.mark.parametrize("n_tok,ne11_is_one", [(1, True), (3, False), (64, True), (64, False)])
 def test_mul_mat_id_512_experts_top10(ctx, n_tok, ne11_is_one):
-    """BASELINE config 5's shapes: 512 experts, top-10, gate/up 512 x 2048 and down 2048 x 512 (fewer rows here)."""
+    """benchmark config 5's shapes: 512 experts, top-10, gate/up 512 x 2048 and down 2048 x 512 (fewer rows here)."""
     rng = np.random.default_rng(7)
     t, n_expert, n_used, m, k = A.Q4_K, 512, 10, 64, 2048
     base = [O.random_blocks(t, m, k, rng) for _ in range(8)]
@@ -163,7 +163,7 @@ def test_mul_mat_id_tensor_core_skewed_route_duplicates_offset(ctx):
 
 
 def test_config5_moe_q4_K_prompt_batch(ctx):
-    """BASELINE config 5 at a prompt batch: 512 experts, top-10, 2048 tokens, gate shape 512 x 2048;
+    """benchmark config 5 at a prompt batch: 512 experts, top-10, 2048 tokens, gate shape 512 x 2048;
     sampled tokens against the oracle."""
     t, n_expert, n_used, n_tok, m, k = A.Q4_K, 512, 10, 2048, 512, 2048
     rng = np.random.default_rng(12)
