@@ -95,3 +95,41 @@ def test_ggml_glue_compiles_and_gates(tmp_path):
     A.lib()
     out = _run(tmp_path, "glue.cpp", CPP_SRC, "g++", ["-std=c++17", "-Wall", "-Wextra", "-Werror"])
     assert out.startswith("ok")
+
+
+GGUF_C_SRC = r'''
+#include <stdio.h>
+#include <string.h>
+#include "adapters/gguf/b200q_gguf.h"
+#include "b200q_test.h"
+int main(int argc, char **argv) {
+    b200q_gguf *g = b200q_gguf_open(argc > 1 ? argv[1] : "");
+    b200q_gguf_tensor t;
+    b200q_tensor d;
+    if (!g) { printf("open failed: %s\n", b200q_gguf_error()); return 1; }
+    if (b200q_gguf_find(g, "blk.0.q4_K.weight", &t) != 0) return 2;
+    if (b200q_gguf_describe(&t, (void *)0x1000, &d) != B200Q_OK || d.type != B200Q_TYPE_Q4_K || d.nb[1] != 288) return 3;
+    printf("%d tensors, %s: %d x %d, %d bytes\n", (int)b200q_gguf_tensor_count(g), t.name, (int)t.ne[0], (int)t.ne[1], (int)t.nbytes);
+    b200q_gguf_close(g);
+    return 0;
+}
+'''
+
+
+def test_gguf_reader_header_is_plain_c(tmp_path):
+    """adapters/gguf/b200q_gguf.h (and include/b200q_test.h) compile as C99; a C program reads the fixture through the reader."""
+    from arcint_b200 import build as B
+    cc = shutil.which("gcc")
+    if not cc:
+        pytest.skip("gcc not found")
+    so = B.build_gguf()
+    f = tmp_path / "reader.c"
+    f.write_text(GGUF_C_SRC)
+    exe = tmp_path / "reader.exe"
+    libdir = os.path.dirname(so)
+    r = subprocess.run([cc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"), "-I", ROOT, str(f), "-o",
+                        str(exe), "-L", libdir, "-lb200q_gguf", "-Wl,-rpath," + libdir], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    r = subprocess.run([str(exe), os.path.join(ROOT, "tests", "golden", "tiny.gguf")], capture_output=True, text=True)
+    assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
+    assert "blk.0.q4_K.weight: 512 x 16, 4608 bytes" in r.stdout
