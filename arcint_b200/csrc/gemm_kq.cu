@@ -80,7 +80,7 @@ template <int TYPE> struct Fmt;
 template <> struct Fmt<B200Q_TYPE_IQ4_XS> { enum { SBB = 136, SPS = 2, NRAW = 2, BOX = 272, D_OFF = 0 }; };
 template <> struct Fmt<B200Q_TYPE_Q4_K>   { enum { SBB = 144, SPS = 1, NRAW = 4, BOX = 144, D_OFF = 0 }; };
 template <> struct Fmt<B200Q_TYPE_Q5_K>   { enum { SBB = 176, SPS = 1, NRAW = 3, BOX = 176, D_OFF = 0 }; };
-template <> struct Fmt<B200Q_TYPE_Q6_K>   { enum { SBB = 210, SPS = 1, NRAW = 2, BOX = 224, D_OFF = 208 }; };
+template <> struct Fmt<B200Q_TYPE_Q6_K>   { enum { SBB = 210, SPS = 1, NRAW = 3, BOX = 224, D_OFF = 208 }; };
 // IQ4_XS rows with an odd number of super-blocks (K = 11008: 5848-byte rows) are 8-byte multiples only: they are staged
 // row by row, one super-block per stage, the slot 8 bytes wider than the block (format variant FMT_IQ4_XS_ROWS).
 constexpr int FMT_IQ4_XS_ROWS = 1000 + B200Q_TYPE_IQ4_XS;
@@ -355,7 +355,7 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int i = 0; i < NRAW; ++i) {
-            mbar_init(bar(BAR_RAW_FULL + i), 1);
+            mbar_init(bar(BAR_RAW_FULL + i), rowcopy ? 64 : 1);        // row by row: the 64 threads of the two row-copy warps
             mbar_init(bar(BAR_RAW_EMPTY + i), 8 + 4 * NW);          // unpack warps + scaling warps (d_w)
         }
         for (int i = 0; i < NACT; ++i) {
@@ -395,24 +395,10 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
             const uint8_t *act_tile = act + (size_t)U.tile_n * nsb * ACT_CHUNK;
             for (int su = 0; su < nsu; ++su, ++s_run) {
                 const int s = U.sb0 + su;                 // the super-block inside the row
-                if (s % SPS == 0) {
+                if (s % SPS == 0 && !rowcopy) {               // (row by row: warps 2 and 3 fetch the raw rows, see below)
                     const int st = rs_run % NRAW;
                     if (!WAITP(1, bar(BAR_RAW_EMPTY + st), ((rs_run / NRAW) & 1) ^ 1)) { ok = false; break; }
-                    if (rowcopy) {
-                        // Rows that are not 16-byte multiples (Q6_K with K = 11008: 9030-byte rows) cannot be described by a
-                        // tensor map. Every row's piece is copied by itself, from the 16-byte boundary below it: the block
-                        // then begins (address % 16) bytes into the row's slot, which the readers add (row_shift below).
-                        // A slot is 16 bytes wider than a block, so the copy never reads past the 16-byte unit that holds
-                        // the block's last byte. Rows past M are not copied; their threads multiply by a zero scale.
-                        if (lane == 0) mbar_expect_tx(bar(BAR_RAW_FULL + st), (uint32_t)U.valid_rows * ROWB);
-                        __syncwarp();
-                        for (int rr = lane; rr < U.valid_rows; rr += 32) {
-                            const uintptr_t src = (uintptr_t)(wraw + (size_t)U.expert * mat_stride + (size_t)(U.row0 + rr) * row_stride +
-                                                              (size_t)(s / SPS) * SPS * SBB);
-                            bulk_g2s(sbase + L::RAW_OFF + st * L::RAW_STAGE + rr * ROWB, (const void *)(src & ~(uintptr_t)15), ROWB,
-                                     bar(BAR_RAW_FULL + st));
-                        }
-                    } else if (lane == 0) {
+                    if (lane == 0) {
                         // the whole [128 rows x ROWB] box in one tiled copy; rows past M arrive as zeros
                         mbar_expect_tx(bar(BAR_RAW_FULL + st), L::RAW_STAGE);
                         tma_load_3d(sbase + L::RAW_OFF + st * L::RAW_STAGE, &wmap, ((s / SPS) * SPS * SBB / 16) * 4, U.row0, U.expert,
@@ -467,6 +453,43 @@ gemm_kq_kernel(const __grid_constant__ CUtensorMap wmap, int M, int K, const uin
         }
     } else if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+        // Idle with a tensor map. Rows that are not 16-byte multiples (Q6_K with K = 11008: 9030-byte rows; IQ4_XS with an odd
+        // super-block count) cannot be described by one: these two warps then fetch the raw rows, thread t rows t and
+        // t + 64, in 16-byte cp.async pieces from the 16-byte boundary below the row's block. The block begins
+        // (address % 16) bytes into the row's slot, which the readers add (row_shift); a slot is 8 or 14 bytes wider than a
+        // block, so a piece never reaches past the 16-byte unit that holds the block's last byte. Rows past M are not
+        // copied (their threads multiply by a zero scale). 128 bulk copies of 224 bytes per stage were tried first: the
+        // copy engine's issue rate, not memory, set the pace (4.8 us per stage).
+        if (rowcopy) {
+            const int t = (int)threadIdx.x - 64;
+            int rs_run = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                const Unit U = unit_of(u);
+                for (int su = 0; su < nsu; ++su) {
+                    const int s = U.sb0 + su;
+                    if (s % SPS != 0) continue;
+                    const int st = rs_run % NRAW;
+                    if (!WAITP(1, bar(BAR_RAW_EMPTY + st), ((rs_run / NRAW) & 1) ^ 1)) { ok = false; break; }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int rr = t + 64 * h;
+                        if (rr < U.valid_rows) {
+                            const uintptr_t src = ((uintptr_t)(wraw + (size_t)U.expert * mat_stride + (size_t)(U.row0 + rr) * row_stride +
+                                                               (size_t)(s / SPS) * SPS * SBB)) & ~(uintptr_t)15;
+                            const uint32_t dstp = sbase + L::RAW_OFF + st * L::RAW_STAGE + rr * ROWB;
+#pragma unroll
+                            for (int i = 0; i < ROWB / 16; ++i)
+                                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dstp + 16 * i), "l"(src + 16 * i) : "memory");
+                        }
+                    }
+                    // one arrival per thread once its copies have landed (none: at once)
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar(BAR_RAW_FULL + st)) : "memory");
+                    ++rs_run;
+                }
+            }
+            asm volatile("cp.async.wait_all;" ::: "memory");      // nothing of this thread is in flight when the block ends
+        }
     } else if (warp < 12) {
         // ---- unpack: two threads per weight row ----
         asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
