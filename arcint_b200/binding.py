@@ -156,6 +156,7 @@ def lib():
     L.b200q_debug_quantize_act.argtypes = [vp, C.c_int, TP, vp, vp, vp]
     L.b200q_debug_dequantize.argtypes = [vp, TP, vp]
     L.b200q_debug_wait_timeout.argtypes = [vp, C.c_uint]
+    L.b200q_debug_check_guards.argtypes = [vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]
     _lib = L
     return L
 
@@ -167,7 +168,7 @@ EXPORTS = [
     "b200q_all_gather", "b200q_mul_mat_allreduce", "b200q_all_to_all_v", "b200q_tp_check", "b200q_mul_mat_id_ep", "b200q_ep_reserve", "b200q_moe_router", "b200q_moe_ffn", "b200q_mul_mat_noalloc", "b200q_noalloc_last_error", "b200q_noalloc_device_error", "b200q_buffer_alloc", "b200q_buffer_free", "b200q_tensor_set",
     "b200q_tensor_get", "b200q_tensor_stage", "b200q_tensor_fetch", "b200q_tensor_copy", "b200q_synchronize", "b200q_host_alloc", "b200q_host_free",
     "b200q_stats", "b200q_stats_reset", "b200q_timer_start", "b200q_timer_stop", "b200q_flush_l2",
-    "b200q_debug_quantize_act", "b200q_debug_dequantize", "b200q_debug_wait_timeout",
+    "b200q_debug_quantize_act", "b200q_debug_dequantize", "b200q_debug_wait_timeout", "b200q_debug_check_guards",
 ]
 
 
@@ -356,6 +357,12 @@ class Context:
 
     def flush_l2(self):
         self.check(self.L.b200q_flush_l2(self.h))
+
+    def check_guards(self):
+        """(blocks looked at, blocks whose guard words were overwritten); needs B200Q_CANARY=1 at Context creation."""
+        blocks, bad = C.c_int(0), C.c_int(0)
+        self.check(self.L.b200q_debug_check_guards(self.h, C.byref(blocks), C.byref(bad)))
+        return blocks.value, bad.value
 
     # ---- numpy conveniences for tests ----
     def run_mul_mat(self, type_, w_bytes, k, x):

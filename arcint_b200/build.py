@@ -77,6 +77,16 @@ def _extra_link():
     return ["-ldl"]
 
 
+def _sanitize():
+    """B200Q_SANITIZE=1: the host-only libraries (the lane-code replay, the GGUF reader) are built with
+    AddressSanitizer and UndefinedBehaviorSanitizer under names of their own; the process that loads them needs
+    the ASan runtime preloaded (tests/test_sanitizers.py does that)."""
+    return os.environ.get("B200Q_SANITIZE") == "1"
+
+
+SAN_FLAGS = ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer", "-g1", "-O0"]
+
+
 def build_emul(force=False, define=None):
     """Host build of the kernels' per-lane text (device-free tests): g++ on emul.cpp. `define` names a
     red-case switch (e.g. "B200Q_RED_Q40"): the mutant is built beside the real library."""
@@ -84,7 +94,7 @@ def build_emul(force=False, define=None):
     if not os.path.exists(src):
         return None
     os.makedirs(LIBDIR, exist_ok=True)
-    EMUL = os.path.join(LIBDIR, "libb200q_emul%s.so" % ("_" + define.lower() if define else ""))
+    EMUL = os.path.join(LIBDIR, "libb200q_emul%s%s.so" % ("_" + define.lower() if define else "", "_san" if _sanitize() else ""))
     if not force and not _stale(EMUL, [src] + _deps()):
         return EMUL
     cuda_inc = os.path.join(os.path.dirname(os.path.dirname(nvcc())), "include")
@@ -93,7 +103,7 @@ def build_emul(force=False, define=None):
         if not cxx or not os.path.exists(cxx):
             continue
         cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-I", cuda_inc, src, "-o", EMUL] + \
-            (["-D" + define] if define else [])
+            (["-D" + define] if define else []) + (SAN_FLAGS if _sanitize() else [])
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode == 0:
             return EMUL
@@ -108,11 +118,12 @@ def build_gguf(force=False):
     if not os.path.exists(src):
         return None
     os.makedirs(LIBDIR, exist_ok=True)
-    out = os.path.join(LIBDIR, "libb200q_gguf.so")
+    out = os.path.join(LIBDIR, "libb200q_gguf%s.so" % ("_san" if _sanitize() else ""))
     if not force and not _stale(out, [src, hdr, os.path.join(HERE, "..", "include", "b200q.h")]):
         return out
-    cxx = shutil.which(os.environ.get("CXX", "g++")) or "/usr/bin/g++"
-    r = subprocess.run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", src, "-o", out], capture_output=True, text=True)
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else shutil.which(os.environ.get("CXX", "g++"))
+    r = subprocess.run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", src, "-o", out] + (SAN_FLAGS if _sanitize() else []),
+                       capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("gguf reader build failed:\n" + r.stderr[-2000:])
     return out

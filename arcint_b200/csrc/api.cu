@@ -67,19 +67,36 @@ b200q_status ws_reserve(b200q_ctx *ctx, Workspace *ws, size_t bytes) {
     if (ws->ptr) {
         // the old block may still be in use by work already enqueued on the stream
         B200Q_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        B200Q_CUDA(ctx, cudaFree(ws->ptr));
-        ws->ptr = nullptr;
+        B200Q_CUDA(ctx, cudaFree(ws->base));
+        ws->ptr = ws->base = nullptr;
         ws->cap = 0;
     }
-    const size_t want = (bytes + (1u << 20) - 1) & ~(size_t)((1u << 20) - 1);
-    cudaError_t e = cudaMalloc(&ws->ptr, want);
+    // Normally whole megabytes, so that a slowly growing request does not reallocate every time. With guard words the block
+    // has the size asked for (to 256 bytes), so that a write past the request lands in the guard and not in rounding slack.
+    const size_t guard = ctx->canary ? WS_GUARD : 0;
+    const size_t unit = ctx->canary ? 256 : (size_t)1 << 20;
+    const size_t want = (bytes + unit - 1) / unit * unit;
+    // (behind the tail guard another 64 KiB, so that a read past the block -- which no guard can see -- stays inside the allocation)
+    const size_t total = want + 2 * guard + (guard ? (size_t)64 << 10 : 0);
+    cudaError_t e = cudaMalloc(&ws->base, total);
     if (e != cudaSuccess) {
-        ws->ptr = nullptr;
-        return fail(ctx, B200Q_NO_MEMORY, "cudaMalloc(%zu): %s", want, cudaGetErrorString(e));
+        ws->base = nullptr;
+        return fail(ctx, B200Q_NO_MEMORY, "cudaMalloc(%zu): %s", total, cudaGetErrorString(e));
     }
+    ws->ptr = (uint8_t *)ws->base + guard;
     ws->cap = want;
+    if (guard) {
+        B200Q_CUDA(ctx, cudaMemsetAsync(ws->base, WS_GUARD_BYTE, guard, ctx->stream));
+        B200Q_CUDA(ctx, cudaMemsetAsync((uint8_t *)ws->ptr + want, WS_GUARD_BYTE, guard, ctx->stream));
+    }
     count(ctx, ST_WORKSPACE_GROW);
     return B200Q_OK;
+}
+
+void ws_release(Workspace *ws) {
+    if (ws->base) cudaFree(ws->base);
+    ws->ptr = ws->base = nullptr;
+    ws->cap = 0;
 }
 
 static bool is_contiguous_f32(const b200q_tensor *t) {
@@ -276,6 +293,8 @@ b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
     ctx->no_ksplit = no_ks && no_ks[0] == '1';
     const char *no_small = getenv("B200Q_GEMV_NO_SMALL");
     ctx->gemv_no_small = no_small && no_small[0] == '1';
+    const char *canary = getenv("B200Q_CANARY");         // debugging: guard words around every scratch block
+    ctx->canary = canary && canary[0] == '1';
     const char *mins_pass = getenv("B200Q_MOE_MINS_PASS");
     ctx->moe_mins_pass = mins_pass && mins_pass[0] == '1';
     const char *no_stream = getenv("B200Q_NO_STREAM");   // the older GEMV kernel for every shape (comparisons)
@@ -289,15 +308,14 @@ void b200q_free(b200q_ctx *ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     for (auto &e : ctx->act_cache) {
-        if (e.codes.ptr) cudaFree(e.codes.ptr);
-        if (e.scales.ptr) cudaFree(e.scales.ptr);
-        if (e.sums.ptr) cudaFree(e.sums.ptr);
-        if (e.sums16.ptr) cudaFree(e.sums16.ptr);
+        ws_release(&e.codes);
+        ws_release(&e.scales);
+        ws_release(&e.sums);
+        ws_release(&e.sums16);
     }
-    if (ctx->flush_buf.ptr) cudaFree(ctx->flush_buf.ptr);
+    ws_release(&ctx->flush_buf);
     if (ctx->error_word) cudaFree(ctx->error_word);
-    for (auto &w : ctx->moe_ws)
-        if (w.ptr) cudaFree(w.ptr);
+    for (auto &w : ctx->moe_ws) ws_release(&w);
     moe_free(ctx);
     tp_free(ctx);
     if (ctx->copy_in) { cudaStreamSynchronize(ctx->copy_in); cudaStreamDestroy(ctx->copy_in); }
@@ -674,6 +692,45 @@ b200q_status b200q_debug_wait_timeout(b200q_ctx *ctx, unsigned polls) {
     B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
     debug_wait_timeout_kernel<<<1, 1, 0, ctx->stream>>>(polls, ctx->error_word);
     B200Q_CUDA(ctx, cudaGetLastError());
+    return B200Q_OK;
+}
+
+b200q_status b200q_debug_check_guards(b200q_ctx *ctx, int *blocks, int *violated) {
+    if (!ctx || !blocks || !violated) return B200Q_INVALID;
+    *blocks = *violated = 0;
+    if (!ctx->canary) return fail(ctx, B200Q_INVALID, "guard words are off: create the context with B200Q_CANARY=1");
+    B200Q_CUDA(ctx, cudaSetDevice(ctx->device));
+    B200Q_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    Workspace *list[64];
+    const char *names[64];
+    int n = 0;
+    for (auto &e : ctx->act_cache) {
+        list[n] = &e.codes;  names[n++] = "activation codes";
+        list[n] = &e.scales; names[n++] = "activation scales";
+        list[n] = &e.sums;   names[n++] = "activation sums";
+        list[n] = &e.sums16; names[n++] = "activation sums16";
+    }
+    static const char *ws_names[10] = { "moe_ws[0]", "moe_ws[1]", "moe_ws[2]", "moe_ws[3]", "moe_ws[4]",
+                                        "moe_ws[5]", "moe_ws[6]", "moe_ws[7]", "moe_ws[8]", "moe_ws[9]" };
+    for (int i = 0; i < 10; ++i) { list[n] = &ctx->moe_ws[i]; names[n++] = ws_names[i]; }
+    list[n] = &ctx->flush_buf; names[n++] = "flush buffer";
+    n += moe_route_workspaces(ctx, list + n, names + n);
+    uint8_t host[2 * WS_GUARD];
+    for (int i = 0; i < n; ++i) {
+        const Workspace *w = list[i];
+        if (!w->base) continue;
+        ++*blocks;
+        B200Q_CUDA(ctx, cudaMemcpy(host, w->base, WS_GUARD, cudaMemcpyDeviceToHost));
+        B200Q_CUDA(ctx, cudaMemcpy(host + WS_GUARD, (const uint8_t *)w->ptr + w->cap, WS_GUARD, cudaMemcpyDeviceToHost));
+        for (size_t b = 0; b < 2 * WS_GUARD; ++b)
+            if (host[b] != (uint8_t)WS_GUARD_BYTE) {
+                if (!*violated)
+                    fail(ctx, B200Q_INVALID, "%s (%zu bytes): guard byte %zu %s the block was overwritten", names[i], w->cap,
+                         b % WS_GUARD, b < WS_GUARD ? "before" : "after");
+                ++*violated;
+                break;
+            }
+    }
     return B200Q_OK;
 }
 

@@ -63,7 +63,11 @@ struct ActView {
 struct Workspace {
     void  *ptr = nullptr;
     size_t cap = 0;
+    void  *base = nullptr;   // start of the allocation: ptr, or WS_GUARD bytes before it when guard words surround the block
 };
+
+constexpr size_t WS_GUARD = 256;          // bytes of guard words on each side of a scratch block (B200Q_CANARY=1)
+constexpr int    WS_GUARD_BYTE = 0xC5;
 
 struct ActKey {
     const void *data;
@@ -131,6 +135,7 @@ struct b200q_ctx {
     // dependent launch). Measured on the 7B decode trace: -2 % at two GPUs, +38 % at eight (1.48 against 1.08 ms).
     int64_t      fuse_quant_bytes = 0;
     bool         no_ksplit = false;       // B200Q_NO_KSPLIT=1: never cut a prompt product along K
+    bool         canary = false;          // B200Q_CANARY=1: guard words around every scratch block, exact sizes (b200q_debug_check_guards)
     bool         gemv_no_small = false;   // B200Q_GEMV_NO_SMALL=1: never the 128-thread, 170-register build of the wide Q6_K GEMV
     bool         moe_mins_pass = false;   // B200Q_MOE_MINS_PASS=1: Q4_K route tiles take the mins term in a separate pass
     bool         no_stream = false;       // B200Q_NO_STREAM=1: every GEMV through the per-warp ring kernel (comparisons)
@@ -153,6 +158,8 @@ namespace b200q {
 
 b200q_status fail(b200q_ctx *ctx, b200q_status st, const char *fmt, ...);
 b200q_status ws_reserve(b200q_ctx *ctx, Workspace *ws, size_t bytes);
+void ws_release(Workspace *ws);
+int moe_route_workspaces(b200q_ctx *ctx, Workspace **out, const char **names);   // the route caches' blocks, for the guard check
 inline void  count(b200q_ctx *ctx, int stat) { ++ctx->counters[stat]; }
 
 #define B200Q_CUDA(ctx, expr)                                                                       \

@@ -291,10 +291,17 @@ b200q_status moe_route(b200q_ctx *ctx, const b200q_tensor *ids, int n_expert, Ro
     return B200Q_OK;
 }
 
+int moe_route_workspaces(b200q_ctx *ctx, Workspace **out, const char **names) {
+    int n = 0;
+    for (RouteEntry *e : ctx->routes)
+        if (e) { out[n] = &e->buf; names[n++] = "route tables"; }
+    return n;
+}
+
 void moe_free(b200q_ctx *ctx) {
     for (RouteEntry *&e : ctx->routes) {
         if (e) {
-            if (e->buf.ptr) cudaFree(e->buf.ptr);
+            ws_release(&e->buf);
             delete e;
             e = nullptr;
         }

@@ -29,6 +29,12 @@ B200Q_API b200q_status b200q_debug_dequantize(b200q_ctx *ctx, const b200q_tensor
  * and returns, so the next b200q_synchronize answers B200Q_TIMEOUT and the context stays usable. */
 B200Q_API b200q_status b200q_debug_wait_timeout(b200q_ctx *ctx, unsigned polls);
 
+/* Guard words. A context created with B200Q_CANARY=1 in the environment allocates every scratch block (quantized
+ * activations, route tables, MoE and split-K scratch) at the size asked for, with 256 guard bytes before and after it.
+ * This call synchronizes and checks them on the host: *blocks = blocks looked at, *violated = blocks whose guard was
+ * overwritten (the first one is named in b200q_last_error). Without B200Q_CANARY: B200Q_INVALID. */
+B200Q_API b200q_status b200q_debug_check_guards(b200q_ctx *ctx, int *blocks, int *violated);
+
 #ifdef __cplusplus
 }
 #endif
