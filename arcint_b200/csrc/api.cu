@@ -43,7 +43,7 @@ const char *stat_name(int s) {
     static const char *rest[] = { "gemv_id", "gemv_id_unaligned", "moe_route", "route_cache_hit", "moe_gemm", "moe_pack",
                                   "gemm_tc", "gemm_tc_quantize", "gemm_fallback_shape", "tp_allreduce", "tp_allgather",
                                   "ep_dispatch", "ep_combine", "graph_launch", "no_alloc", "gemm_kq_mins", "gemv_stream", "tp_allreduce_peer", "gemm_tc_f16", "ep_peer", "ep_dispatch_cached", "moe_router", "moe_ffn", "gemv_knob_ignored", "gemm_ksplit", "gemv_fused_quant", "gemv_allreduce_fused",
-                                  "ep_agreed_exit", "gemm_kq_rowcopy" };
+                                  "ep_agreed_exit", "gemm_kq_rowcopy", "gemv_mma" };
     return rest[s - ST_GEMV_ID];
 }
 
@@ -293,6 +293,14 @@ b200q_status b200q_init(b200q_ctx **out, int device, void *stream) {
     ctx->no_ksplit = no_ks && no_ks[0] == '1';
     const char *no_small = getenv("B200Q_GEMV_NO_SMALL");
     ctx->gemv_no_small = no_small && no_small[0] == '1';
+    const char *mma_min = getenv("B200Q_GEMV_MMA_MIN");  // fewest columns for the warp-MMA GEMV (99: never)
+    if (mma_min && mma_min[0]) ctx->gemv_mma_min = atoi(mma_min);
+    const char *mma_sets = getenv("B200Q_GEMV_MMA_SETS");
+    ctx->gemv_mma_sets3 = mma_sets && mma_sets[0] == '3';
+    const char *mma_groups = getenv("B200Q_GEMV_MMA_GROUPS");
+    if (mma_groups && mma_groups[0]) ctx->gemv_mma_groups = atoi(mma_groups);
+    const char *mma_slice = getenv("B200Q_GEMV_MMA_SLICE");
+    if (mma_slice && mma_slice[0]) ctx->gemv_mma_slice = atoi(mma_slice);
     const char *canary = getenv("B200Q_CANARY");         // debugging: guard words around every scratch block
     ctx->canary = canary && canary[0] == '1';
     const char *mins_pass = getenv("B200Q_MOE_MINS_PASS");

@@ -100,7 +100,7 @@ enum Stat {
     ST_GEMV_ID = ST_GEMV_UNALIGNED_COL0 + 9, ST_GEMV_ID_UNALIGNED, ST_MOE_ROUTE, ST_ROUTE_CACHE_HIT, ST_MOE_GEMM,
     ST_MOE_PACK, ST_GEMM_TC, ST_GEMM_TC_QUANT, ST_GEMM_FALLBACK_SHAPE, ST_TP_ALLREDUCE, ST_TP_ALLGATHER,
     ST_EP_DISPATCH, ST_EP_COMBINE, ST_GRAPH_LAUNCH, ST_NO_ALLOC, ST_GEMM_KQ_MINS, ST_GEMV_STREAM, ST_TP_ALLREDUCE_PEER, ST_GEMM_TC_F16, ST_EP_PEER, ST_EP_DISPATCH_CACHED, ST_MOE_ROUTER, ST_MOE_FFN, ST_GEMV_KNOB_IGNORED, ST_GEMM_KSPLIT, ST_GEMV_FUSED_QUANT, ST_GEMV_ALLREDUCE_FUSED,
-    ST_EP_AGREED_EXIT, ST_GEMM_KQ_ROWCOPY,
+    ST_EP_AGREED_EXIT, ST_GEMM_KQ_ROWCOPY, ST_GEMV_MMA,
     ST_COUNT
 };
 const char *stat_name(int s);
@@ -136,6 +136,10 @@ struct b200q_ctx {
     int64_t      fuse_quant_bytes = 0;
     bool         no_ksplit = false;       // B200Q_NO_KSPLIT=1: never cut a prompt product along K
     bool         canary = false;          // B200Q_CANARY=1: guard words around every scratch block, exact sizes (b200q_debug_check_guards)
+    bool         gemv_mma_sets3 = false;  // B200Q_GEMV_MMA_SETS=3: a three-stage ring for the warp-MMA GEMV even where four stages fit
+    int          gemv_mma_groups = 0;     // B200Q_GEMV_MMA_GROUPS=1: blocks of one group (several blocks per SM) instead of one block per SM
+    int          gemv_mma_slice = 0;      // B200Q_GEMV_MMA_SLICE=2|3|4: super-blocks per warp of the warp-MMA GEMV (0: by row length)
+    int          gemv_mma_min = 3;        // B200Q_GEMV_MMA_MIN: fewest columns at which Q4_K takes the warp-MMA GEMV (99: never)
     bool         gemv_no_small = false;   // B200Q_GEMV_NO_SMALL=1: never the 128-thread, 170-register build of the wide Q6_K GEMV
     bool         moe_mins_pass = false;   // B200Q_MOE_MINS_PASS=1: Q4_K route tiles take the mins term in a separate pass
     bool         no_stream = false;       // B200Q_NO_STREAM=1: every GEMV through the per-warp ring kernel (comparisons)

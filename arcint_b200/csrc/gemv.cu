@@ -13,6 +13,7 @@
 // host side ggml_cl_mul_mv_kq_q8_1 at :817-857).
 #include "gemv_kernel.cuh"
 #include "gemv_stream.cuh"
+#include "gemv_mma.cuh"
 #include "common.cuh"
 
 #include <limits.h>
@@ -125,6 +126,46 @@ static bool try_launch_stream(b200q_ctx *ctx, const void *w, size_t row_stride, 
     return true;
 }
 
+// The warp-MMA kernel (gemv_mma.cuh) for rows that bulk copies can fetch. Returns false when the shape does not fit it:
+// more than twelve warps per group (K beyond 12288) or a ring beyond shared memory.
+template <int TYPE, int NSETS, int SLICE>
+static bool try_launch_mma(b200q_ctx *ctx, const void *w, size_t row_stride, int64_t M, int64_t K, const GemvAct &act, int ncols,
+                           float *dst, int64_t ldd, b200q_status *st) {
+    typedef GemvFmt<TYPE> F;
+    constexpr int MAX_WARPS = gemv_mma_max_threads(SLICE) / 32;
+    constexpr size_t SMEM_CAP = 227 * 1024;
+    const int nblk = (int)(K / F::BLK_W), nw = (nblk + SLICE - 1) / SLICE;
+    if (nw > MAX_WARPS) return false;
+    const size_t gb = (gemv_mma_group_smem(nblk * F::BLK_B, NSETS, nw) + 127) / 128 * 128;
+    if (gb > SMEM_CAP || gemv_mma_xstages((int)K, nblk * F::BLK_B) > NSETS - 1) return false;
+    int groups = MAX_WARPS / nw;
+    while (groups > 1 && groups * gb > SMEM_CAP) --groups;
+    const int per_sm = groups;                                     // groups an SM holds
+    if (ctx->gemv_mma_groups == 1) groups = 1;                     // ... as blocks of one group each
+    const int64_t n_units = (M + GEMV_MMA_ROWS - 1) / GEMV_MMA_ROWS;
+    // few rows: rather more blocks than full ones
+    while (groups > 1 && n_units < (int64_t)groups * ctx->sm_count) --groups;
+    const size_t smem = groups * gb;
+    const int threads = groups * nw * 32;
+    auto kern = gemv_mma_kernel<TYPE, NSETS, SLICE>;
+    static bool attr_dev[B200Q_MAX_DEVICES] = {};
+    bool &attr = attr_dev[ctx->device % B200Q_MAX_DEVICES];
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_CAP);
+        if (e != cudaSuccess) { *st = fail(ctx, B200Q_CUDA_ERROR, "gemv_mma attribute: %s", cudaGetErrorString(e)); return true; }
+        attr = true;
+    }
+    int64_t blocks = (n_units + groups - 1) / groups;
+    const int64_t cap = (int64_t)ctx->sm_count * (per_sm / groups);
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    cudaError_t e = launch_pdl(!ctx->no_pdl, kern, dim3((unsigned)blocks), dim3(threads), smem, ctx->stream, (const uint8_t *)w, row_stride,
+                               (int)M, nblk, act, ncols, dst, (int)ldd, groups, ctx->error_word);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    *st = e == cudaSuccess ? B200Q_OK : fail(ctx, B200Q_CUDA_ERROR, "gemv_mma launch: %s", cudaGetErrorString(e));
+    return true;
+}
+
 // Which kernel takes a dense, aligned product of NC columns (measured on B200, CUDA-graph replay over
 // rotating weight copies): the slice-resident kernel everywhere except the 210-byte Q6_K blocks at one
 // column, where the per-warp ring kernel is 10 % faster (23.1 against 25.9 us on the 32000x4096 head). With four
@@ -142,6 +183,31 @@ static b200q_status launch_nc(b200q_ctx *ctx, const void *w, size_t row_stride, 
     // the activation registers are worth sharing further (measured on B200)
     constexpr bool wide = (NC == 3 || NC == 4) && GemvStage<TYPE>::BYTES <= 1152;
     const bool want_stream = ctx->gemv_stream_mask >= 0 ? ((ctx->gemv_stream_mask >> NC) & 1) != 0 : stream_preferred<TYPE, NC>();
+    if constexpr (TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q6_K) {
+        if (aligned && !ctx->no_stream && M <= INT32_MAX / 2 && ldd <= INT32_MAX && NC >= ctx->gemv_mma_min) {
+            b200q_status st = B200Q_OK;
+            // the narrowest slice per warp that covers a row with sixteen warps (twelve at four super-blocks)
+            const int nblk = (int)(K / 256);
+            int slice = nblk <= 32 ? 2 : nblk <= 48 ? 3 : 4;
+            if (ctx->gemv_mma_slice >= 2 && ctx->gemv_mma_slice <= 4) slice = ctx->gemv_mma_slice;
+            if (TYPE == B200Q_TYPE_Q6_K && slice == 3) slice = 4;      // Q6_K: even slices only
+            const bool four = !ctx->gemv_mma_sets3;
+            bool took = false;
+            if (slice == 2) took = (four && try_launch_mma<TYPE, 4, 2>(ctx, w, row_stride, M, K, act, NC, dst, ldd, &st)) ||
+                                   try_launch_mma<TYPE, 3, 2>(ctx, w, row_stride, M, K, act, NC, dst, ldd, &st);
+            else if (slice == 3) {
+                if constexpr (TYPE == B200Q_TYPE_Q4_K)
+                    took = (four && try_launch_mma<TYPE, 4, 3>(ctx, w, row_stride, M, K, act, NC, dst, ldd, &st)) ||
+                           try_launch_mma<TYPE, 3, 3>(ctx, w, row_stride, M, K, act, NC, dst, ldd, &st);
+            }
+            else took = (four && try_launch_mma<TYPE, 4, 4>(ctx, w, row_stride, M, K, act, NC, dst, ldd, &st)) ||
+                        try_launch_mma<TYPE, 3, 4>(ctx, w, row_stride, M, K, act, NC, dst, ldd, &st);
+            if (took) {
+                if (st == B200Q_OK) count(ctx, ST_GEMV_MMA);
+                return st;
+            }
+        }
+    }
     if (aligned && !ctx->no_stream && M <= INT32_MAX / 2 && ldd <= INT32_MAX && want_stream) {
         typedef GemvFmt<TYPE> F;
         const int row_bytes = (int)(K / F::BLK_W) * F::BLK_B;
