@@ -184,7 +184,7 @@ static b200q_status launch_nc(b200q_ctx *ctx, const void *w, size_t row_stride, 
     constexpr bool wide = (NC == 3 || NC == 4) && GemvStage<TYPE>::BYTES <= 1152;
     const bool want_stream = ctx->gemv_stream_mask >= 0 ? ((ctx->gemv_stream_mask >> NC) & 1) != 0 : stream_preferred<TYPE, NC>();
     if constexpr (TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q6_K) {
-        if (aligned && !ctx->no_stream && M <= INT32_MAX / 2 && ldd <= INT32_MAX && NC >= ctx->gemv_mma_min) {
+        if (aligned && !ctx->no_stream && M <= INT32_MAX / 2 && ldd <= INT32_MAX && NC >= (ctx->gemv_mma_min ? ctx->gemv_mma_min : (TYPE == B200Q_TYPE_Q6_K ? 3 : 4))) {
             b200q_status st = B200Q_OK;
             // the narrowest slice per warp that covers a row with sixteen warps (twelve at four super-blocks)
             const int nblk = (int)(K / 256);

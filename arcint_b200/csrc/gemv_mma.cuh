@@ -41,7 +41,7 @@ __host__ __device__ constexpr int gemv_mma_max_threads(int slice) { return slice
 // a half-warp touches fall into different banks
 __host__ __device__ inline int gemv_mma_slot(int row_bytes) { return (row_bytes + 95) / 128 * 128 + 32; }
 __host__ __device__ inline size_t gemv_mma_group_smem(int row_bytes, int nsets, int nw) {
-    return (size_t)nsets * GEMV_MMA_ROWS * gemv_mma_slot(row_bytes) + (size_t)2 * nw * 64 * sizeof(float) + (size_t)(2 * nsets + 5) * 8;
+    return (size_t)nsets * GEMV_MMA_ROWS * gemv_mma_slot(row_bytes) + (size_t)2 * nw * 64 * sizeof(float) + (size_t)(2 * nsets + 6) * 8;
 }
 // bytes between the columns of the activation while it sits in the ring: 32 modulo 128, as for the rows
 __host__ __device__ inline int gemv_mma_xstride(int K) { return K + 32; }
@@ -94,7 +94,7 @@ __device__ __forceinline__ int gemv_dp2a_hi_su(uint32_t a, uint32_t b, int c) {
 template <int TYPE, int NSETS, int SLICE>
 __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk, const GemvAct &act,
                                               int ncols, float *__restrict__ dst, int ldd, const GemvGroupSmem &sm, int gg, int tg,
-                                              int lane, int wi, int nw, int *error_word) {
+                                              int lane, int wi, int nw, int *error_word, int g, uint8_t *ring0, uint32_t bar_x) {
     static_assert(TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q6_K, "built for Q4_K and Q6_K");
     static_assert(TYPE != B200Q_TYPE_Q6_K || SLICE % 2 == 0, "Q6_K: a block's alignment in the row must be known at compile time");
     constexpr bool Q4 = TYPE == B200Q_TYPE_Q4_K;
@@ -113,16 +113,19 @@ __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, siz
     int p_n = 0, p_set = 0;
     auto issue = [&]() {
         const int u = gg + p_n * tg;
-        if (u < n_units && lane == 0) {
-            // the stage's previous rows must have been released by every warp of the group
-            // (the last xs stages held the activation first: one more phase of their barrier, the warps' arrival after
-            // they have taken their fragments out)
-            const bool xst = p_set >= NSETS - xs;
-            if ((xst || p_n >= NSETS) && !gemv_mbar_wait(sm.bar_empty + 8 * p_set, (uint32_t)((p_n / NSETS - (xst ? 0 : 1)) & 1))) ok = false;
-            if (ok) {
-                const int row0 = u * R, rows = min(R, M - row0);
-                const uint8_t *src = W + (size_t)row0 * row_stride;
-                const uint32_t d = sm.ring + p_set * (R * slot);
+        if (u < n_units) {
+            if (lane == 0) {
+                // the stage's previous rows must have been released by every warp of the group
+                // (the last xs stages of the block's first group hold the activation at first: every warp of the block
+                // arrives at a barrier of its own once it has taken its fragments out)
+                if (g == 0 && p_n < NSETS && p_set >= NSETS - xs && !gemv_mbar_wait(bar_x + 8, 0)) ok = false;
+                if (p_n >= NSETS && !gemv_mbar_wait(sm.bar_empty + 8 * p_set, (uint32_t)((p_n / NSETS - 1) & 1))) ok = false;
+            }
+            const int row0 = u * R, rows = min(R, M - row0);
+            const uint8_t *src = W + (size_t)row0 * row_stride;
+            const uint32_t d = sm.ring + p_set * (R * slot);
+            // (16-byte cp.async copies by all lanes instead of the bulk copies measured 7-12 % slower)
+            if (lane == 0 && ok) {
                 int mine = 0;
                 for (int r = wi; r < rows; r += nw) ++mine;
                 tc::mbar_expect_tx(sm.bar_full + 8 * p_set, (uint32_t)row_bytes * (uint32_t)mine);     // one arrival per warp
@@ -148,13 +151,13 @@ __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, siz
     pt_pdl = now();
 #endif
 
-    // The activation codes come into the ring's last xs stages by one bulk copy per column (every block reads all of
-    // them: plain loads of eight bytes per lane kept the load pipe of every SM busy for microseconds), and each warp
+    // The activation codes come into the last xs ring stages of the block's first group by one bulk copy per column,
+    // once for all groups of the block (every SM reads all of them, which at eight columns is a third of the weight
+    // bytes it streams: plain loads of eight bytes per lane, per group, cost microseconds), and each warp
     // takes its slice out as B fragments of column lane / 4 (the last column again beyond ncols). The scale and block
     // sums of the two columns this lane's results belong to are few: plain loads.
-    const uint32_t bar_x = sm.bar_free + 16;
-    uint8_t *xs_ptr = sm.ring_ptr + (size_t)(NSETS - xs) * (R * slot);
-    if (wi == 0 && lane == 0) {
+    uint8_t *xs_ptr = ring0 + (size_t)(NSETS - xs) * (R * slot);
+    if (g == 0 && wi == 0 && lane == 0) {
         tc::mbar_expect_tx(bar_x, (uint32_t)ncols * (uint32_t)K);
         for (int cc = 0; cc < ncols; ++cc)
             gemv_bulk_g2s_plain(tc::smem_u32(xs_ptr) + cc * xstride, act.q + (size_t)cc * K, (uint32_t)K, bar_x);
@@ -203,11 +206,10 @@ __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, siz
         }
     }
     __syncwarp();                                                  // every lane has its fragments: the stages may take weights
-    if (lane == 0)
-        for (int st = NSETS - xs; st < NSETS; ++st) tc::mbar_arrive(sm.bar_empty + 8 * st);
+    if (lane == 0) tc::mbar_arrive(bar_x + 8);
 
 #pragma unroll
-    for (int i = 1; i < NSETS - 2 && i < NSETS - xs; ++i) issue();
+    for (int i = 1; i < NSETS - 2 && (g != 0 || i < NSETS - xs); ++i) issue();
 #ifdef B200Q_MMA_PROF
     pt_x = now();
 #endif
@@ -371,12 +373,16 @@ gemv_mma_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nbl
         tc::mbar_init(sm.bar_done + 8, (uint32_t)nw);
         tc::mbar_init(sm.bar_free, 1);
         tc::mbar_init(sm.bar_free + 8, 1);
-        tc::mbar_init(sm.bar_free + 16, 1);                        // the activation's arrival
+        tc::mbar_init(sm.bar_free + 16, 1);                        // the activation's arrival (the first group's is used)
+        tc::mbar_init(sm.bar_free + 24, (uint32_t)(groups * nw));  // ... and every warp of the block having taken its part
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     const int gg = blockIdx.x * groups + g, tg = gridDim.x * groups;
-    if (g < groups) gemv_mma_warp<TYPE, NSETS, SLICE>(W, row_stride, M, nblk, act, ncols, dst, ldd, sm, gg, tg, lane, wi, nw, error_word);
+    // group 0's barrier block sits at the same offset as every group's
+    const uint32_t bar_x0 = tc::smem_u32(smem) + (sm.bar_free + 16 - sm.ring);
+    if (g < groups)
+        gemv_mma_warp<TYPE, NSETS, SLICE>(W, row_stride, M, nblk, act, ncols, dst, ldd, sm, gg, tg, lane, wi, nw, error_word, g, smem, bar_x0);
     pdl_trigger();
 }
 
