@@ -9,6 +9,8 @@ Genome = the library's environment knobs, read once when a context is made:
   B200Q_GEMV_BLOCK_WARPS   warps per block (2..16; 0 = default 4)
   B200Q_GEMV_STREAM_MASK   which column counts take the slice-resident kernel (bit c; -1 = default rule)
   B200Q_GEMV_NO_SMALL      1: never the 128-thread / 170-register build of the wide Q4_K / Q6_K forms
+  B200Q_GEMV_MMA_MIN       fewest columns at which Q4_K / Q6_K take the warp-MMA GEMV (0 = measured rule: 4 / 3; 99 = never)
+  B200Q_GEMV_MMA_SLICE     super-blocks per warp of the warp-MMA GEMV (2, 3, 4; 0 = by row length)
 Fitness = sum over the cases of the median CUDA-event time of `bench.py --case` (lower is better), each case in
 its own process. A genome the library ignored (stats key "gemv_knob_ignored") scores nothing, so a fallback to
 the defaults is never credited to the genome that asked for something else; the default genome is re-measured
@@ -26,8 +28,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DEFAULT_CASES = ["q4_K:11008x4096x1", "q4_K:11008x4096x4", "q4_K:11008x4096x8", "q4_K:4096x11008x1", "q4_K:4096x11008x8",
                  "q6_K:32000x4096x1", "q6_K:32000x4096x8", "q4_0:4096x4096x1"]
 GENES = {"B200Q_GEMV_ROWS": [0, 2, 4], "B200Q_GEMV_BLOCK_WARPS": [0, 2, 4, 8, 16],
-         "B200Q_GEMV_STREAM_MASK": [-1, 0x1F2, 0x1FE, 0x1F0, 0x112], "B200Q_GEMV_NO_SMALL": [0, 1]}
-DEFAULT = {"B200Q_GEMV_ROWS": 0, "B200Q_GEMV_BLOCK_WARPS": 0, "B200Q_GEMV_STREAM_MASK": -1, "B200Q_GEMV_NO_SMALL": 0}
+         "B200Q_GEMV_STREAM_MASK": [-1, 0x1F2, 0x1FE, 0x1F0, 0x112], "B200Q_GEMV_NO_SMALL": [0, 1],
+         "B200Q_GEMV_MMA_MIN": [0, 2, 3, 4, 5, 99], "B200Q_GEMV_MMA_SLICE": [0, 2, 4]}
+DEFAULT = {"B200Q_GEMV_ROWS": 0, "B200Q_GEMV_BLOCK_WARPS": 0, "B200Q_GEMV_STREAM_MASK": -1, "B200Q_GEMV_NO_SMALL": 0,
+           "B200Q_GEMV_MMA_MIN": 0, "B200Q_GEMV_MMA_SLICE": 0}
 
 
 def key(g):
