@@ -777,9 +777,10 @@ def run_gpu(args, rank, world):
                        "gbs": round(b / (kms * 1e-3) / 1e9, 1), "frac": round(b / (kms * 1e-3) / 1e9 / peak, 3)})
         tot_b += b
         tot_ms += kms
-        # DRAM bytes per launch as ncu captured them (dram__bytes.sum.per_second x gpu__time_duration): 25.39 to 25.46 MB for
-        # the 25.36 MB Q4_K matrix at 1 and 8 columns, 111.7 to 114.2 MB for the 107.52 MB Q6_K head
-        tot_traffic += b * (1.05 if t == A.Q6_K else 1.003)
+        # DRAM bytes per launch as ncu captured them (dram__bytes_read.sum + dram__bytes_write.sum): 25.39 to 25.46 MB for
+        # the 25.36 MB Q4_K matrix at 1 and 8 columns; for the 107.52 MB Q6_K head 111.7 to 114.2 MB from the dp4a
+        # kernels (1 and 2 columns) and 107.83 MB from the warp-MMA kernel (4 and 8 columns)
+        tot_traffic += b * ((1.05 if n < 3 else 1.003) if t == A.Q6_K else 1.003)
     achieved = tot_b / (tot_ms * 1e-3) / 1e9
     clocks = sampler.stop() if rank == 0 else None
 
@@ -822,7 +823,7 @@ def run_gpu(args, rank, world):
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int8 block dots (dp4a), f32 accumulate", "data": "synthetic",
+            "vs_baseline": None, "dtype": "int8 block dots (dp4a; warp MMA from 3-4 columns), f32 accumulate", "data": "synthetic",
             "config": {"workload": "decode_gemv: Q4_K 11008x4096 + Q4_K 4096x11008 + Q6_K 32000x4096, batch 1/2/4/8",
                        "l2": "weights rotate over device copies totalling >= 4x L2 per shape",
                        "launch": "each step is one CUDA-graph replay of 12 x (quantize, GEMV)",
@@ -830,7 +831,7 @@ def run_gpu(args, rank, world):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          # DRAM bytes per GEMV launch, mean over the 12 products, scaled from the ncu captures
                          "traffic": tot_traffic / len(detail), "algorithmic_bytes_per_launch": tot_b / len(detail),
-                         "peak_source": peak_src, "kernel": "gemv_stream_kernel / gemv_kernel (activation pre-quantized), back-to-back launches in a CUDA graph",
+                         "peak_source": peak_src, "kernel": "gemv_stream_kernel / gemv_kernel at 1-2 (Q4_K: 1-3) columns, gemv_mma_kernel above (activation pre-quantized), back-to-back launches in a CUDA graph",
                          "detail": detail},
             "prefill": prefill,
             "tp_trace": tp_trace,
