@@ -183,7 +183,8 @@ static b200q_status launch_nc(b200q_ctx *ctx, const void *w, size_t row_stride, 
     // the activation registers are worth sharing further (measured on B200)
     constexpr bool wide = (NC == 3 || NC == 4) && GemvStage<TYPE>::BYTES <= 1152;
     const bool want_stream = ctx->gemv_stream_mask >= 0 ? ((ctx->gemv_stream_mask >> NC) & 1) != 0 : stream_preferred<TYPE, NC>();
-    if constexpr (TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q6_K) {
+    if constexpr (TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K || TYPE == B200Q_TYPE_Q6_K || TYPE == B200Q_TYPE_IQ4_XS) {
+        // from how many columns the warp-MMA kernel wins (measured): Q6_K 3, the others 4
         if (aligned && !ctx->no_stream && M <= INT32_MAX / 2 && ldd <= INT32_MAX && NC >= (ctx->gemv_mma_min ? ctx->gemv_mma_min : (TYPE == B200Q_TYPE_Q6_K ? 3 : 4))) {
             b200q_status st = B200Q_OK;
             // the narrowest slice per warp that covers a row with sixteen warps (twelve at four super-blocks)
@@ -196,7 +197,7 @@ static b200q_status launch_nc(b200q_ctx *ctx, const void *w, size_t row_stride, 
             if (slice == 2) took = (four && try_launch_mma<TYPE, 4, 2>(ctx, w, row_stride, M, K, act, NC, dst, ldd, &st)) ||
                                    try_launch_mma<TYPE, 3, 2>(ctx, w, row_stride, M, K, act, NC, dst, ldd, &st);
             else if (slice == 3) {
-                if constexpr (TYPE == B200Q_TYPE_Q4_K)
+                if constexpr (TYPE != B200Q_TYPE_Q6_K)
                     took = (four && try_launch_mma<TYPE, 4, 3>(ctx, w, row_stride, M, K, act, NC, dst, ldd, &st)) ||
                            try_launch_mma<TYPE, 3, 3>(ctx, w, row_stride, M, K, act, NC, dst, ldd, &st);
             }

@@ -23,6 +23,9 @@
 //     partial sums meet in shared memory and the warps of the group take turns adding them up.
 // Fewer than eight columns run with the last column repeated in the unused B columns; nothing is stored for them.
 //
+// Q5_K adds the fifth bits to Q4_K's fragment; Q6_K works per scale group of sixteen weights (m16n8k16, signed q - 32);
+// IQ4_XS looks its nibbles up in the codebook into a signed fragment and has no mins term.
+//
 // Stands in for the reference's kernel_mul_mv_q4_K_q8_1 at several columns (marfrit/arcint contrib/llama.cpp/patches/
 // 0000-01-kquant-integer-dpas.patch:3740-3796, 3882-3915) and its few-column int8 kernels
 // (0115-opencl-few-column-int8-q4_0-q8_0-iq4.patch:904-984).
@@ -62,6 +65,14 @@ __device__ __forceinline__ void gemv_mma_u8s8(uint32_t a0, uint32_t a1, uint32_t
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
+// the same with signed weights (IQ4_XS: codebook values)
+__device__ __forceinline__ void gemv_mma_s8s8(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1, int &c0,
+                                              int &c1, int &c2, int &c3) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c0), "=r"(c1), "=r"(c2), "=r"(c3)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 // One m16n8k16 MMA, signed weights x signed codes, for Q6_K's scale groups of 16 weights: rows 0..7 (a0) carry one
 // group of the lane's eight weight rows and rows 8..15 (a1) another group made from the same loaded words; issued
 // once against each group's codes, each time one half of C is the wanted one.
@@ -95,9 +106,10 @@ template <int TYPE, int NSETS, int SLICE>
 __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk, const GemvAct &act,
                                               int ncols, float *__restrict__ dst, int ldd, const GemvGroupSmem &sm, int gg, int tg,
                                               int lane, int wi, int nw, int *error_word, int g, uint8_t *ring0, uint32_t bar_x) {
-    static_assert(TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q6_K, "built for Q4_K and Q6_K");
+    static_assert(TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K || TYPE == B200Q_TYPE_Q6_K || TYPE == B200Q_TYPE_IQ4_XS,
+                  "built for the 256-weight block types Q4_K, Q5_K, Q6_K and IQ4_XS");
     static_assert(TYPE != B200Q_TYPE_Q6_K || SLICE % 2 == 0, "Q6_K: a block's alignment in the row must be known at compile time");
-    constexpr bool Q4 = TYPE == B200Q_TYPE_Q4_K;
+    constexpr bool Q5 = TYPE == B200Q_TYPE_Q5_K, Q4 = TYPE == B200Q_TYPE_Q4_K || Q5, IQ = TYPE == B200Q_TYPE_IQ4_XS;
     typedef GemvFmt<TYPE> F;
     constexpr int R = GEMV_MMA_ROWS;
     const int row_bytes = nblk * F::BLK_B;
@@ -198,6 +210,7 @@ __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, siz
                         xb[sb][2 * j + 1] = v.y;
                     }
                 } else {
+                    // Q6_K: group G's codes 4c..; IQ4_XS: the same sixteen pieces are the sub-blocks' codes 4c.. and 16 + 4c..
                     const uint8_t *xp = xs_ptr + (size_t)bcol * xstride + 256 * blk + 4 * c;
 #pragma unroll
                     for (int G = 0; G < 16; ++G) xb[sb][G] = *reinterpret_cast<const uint32_t *>(xp + 16 * G);
@@ -227,18 +240,26 @@ __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, siz
         for (int sb = 0; sb < SLICE; ++sb) {
             if (blk0 + sb >= nblk) break;
             if constexpr (Q4) {
-                const uint8_t *b = rowp + (blk0 + sb) * 144;
+                const uint8_t *b = rowp + (blk0 + sb) * (Q5 ? 176 : 144);
                 const uint4 h = *reinterpret_cast<const uint4 *>(b);        // d | dmin, then the 12 scale bytes
+                // Q5_K: qh[32] follows; bit j of byte t is the fifth bit of weight t of sub-block j. The lane's bytes 8c..
+                uint2 hb = make_uint2(0u, 0u);
+                if (Q5) hb = *reinterpret_cast<const uint2 *>(b + 16 + 8 * c);
+                const uint8_t *qs = b + (Q5 ? 48 : 16);
                 const float d = hd_half_bits((uint16_t)h.x), dmin = hd_half_bits((uint16_t)(h.x >> 16));
                 const uint32_t sc_lo = h.y & 0x3F3F3F3Fu, sc_hi = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
                 const uint32_t mn_lo = h.z & 0x3F3F3F3Fu, mn_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
                 int i0 = 0, i1 = 0;
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
-                    const uint2 q = *reinterpret_cast<const uint2 *>(b + 16 + 32 * g + 8 * c);
+                    const uint2 q = *reinterpret_cast<const uint2 *>(qs + 32 * g + 8 * c);
                     const uint32_t scw = g < 2 ? sc_lo : sc_hi;
                     const int s_even = (int)((scw >> (16 * (g & 1))) & 0xFFu), s_odd = (int)((scw >> (16 * (g & 1) + 8)) & 0xFFu);
-                    const uint32_t l0 = q.x & 0x0F0F0F0Fu, h0 = (q.x >> 4) & 0x0F0F0F0Fu, l1 = q.y & 0x0F0F0F0Fu, h1 = (q.y >> 4) & 0x0F0F0F0Fu;
+                    uint32_t l0 = q.x & 0x0F0F0F0Fu, h0 = (q.x >> 4) & 0x0F0F0F0Fu, l1 = q.y & 0x0F0F0F0Fu, h1 = (q.y >> 4) & 0x0F0F0F0Fu;
+                    if (Q5) {
+                        l0 |= ((hb.x >> (2 * g)) << 4) & 0x10101010u;      h0 |= ((hb.x >> (2 * g + 1)) << 4) & 0x10101010u;
+                        l1 |= ((hb.y >> (2 * g)) << 4) & 0x10101010u;      h1 |= ((hb.y >> (2 * g + 1)) << 4) & 0x10101010u;
+                    }
                     int e0, e1, o0, o1, unused0, unused1;
                     gemv_mma_u8s8(l0, h0, l1, h1, xb[sb][4 * g], xb[sb][4 * g + 1], e0, e1, unused0, unused1);
                     gemv_mma_u8s8(l0, h0, l1, h1, xb[sb][4 * g + 2], xb[sb][4 * g + 3], unused0, unused1, o0, o1);
@@ -252,6 +273,31 @@ __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, siz
                 j0 = gemv_dp2a_hi_su(bs0[sb].w, mn_hi, j0);  j1 = gemv_dp2a_hi_su(bs1[sb].w, mn_hi, j1);
                 acc0 += dx0[sb] * (d * (float)i0 - dmin * (float)j0);
                 acc1 += dx1[sb] * (d * (float)i1 - dmin * (float)j1);
+            } else if constexpr (IQ) {
+                // IQ4_XS: d | scales_h | scales_l[4] | qs[128]; sub-block j is sixteen bytes, weights t in the low nibbles and
+                // 16 + t in the high ones, values kvalues_iq4nl[nibble], scale ls_j - 32 with ls_j six bits
+                const uint8_t *b = rowp + (blk0 + sb) * 136;
+                const uint2 h = *reinterpret_cast<const uint2 *>(b);        // d, scales_h | scales_l
+                const float d = hd_half_bits((uint16_t)h.x);
+                const uint32_t sh = h.x >> 16, sl = h.y;
+                int i0 = 0, i1 = 0;
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {                            // sub-blocks 2 jj (rows 0..7 of A) and 2 jj + 1 (rows 8..15)
+                    const uint32_t qa = *reinterpret_cast<const uint32_t *>(b + 8 + 32 * jj + 4 * c);
+                    const uint32_t qb = *reinterpret_cast<const uint32_t *>(b + 8 + 32 * jj + 16 + 4 * c);
+                    const uint32_t a0 = iq4nl_lookup4(qa & 0x0F0F0F0Fu), a2 = iq4nl_lookup4((qa >> 4) & 0x0F0F0F0Fu);
+                    const uint32_t a1 = iq4nl_lookup4(qb & 0x0F0F0F0Fu), a3 = iq4nl_lookup4((qb >> 4) & 0x0F0F0F0Fu);
+                    int e0, e1, o0, o1, u0, u1;
+                    gemv_mma_s8s8(a0, a1, a2, a3, xb[sb][4 * jj], xb[sb][4 * jj + 1], e0, e1, u0, u1);
+                    gemv_mma_s8s8(a0, a1, a2, a3, xb[sb][4 * jj + 2], xb[sb][4 * jj + 3], u0, u1, o0, o1);
+                    const uint32_t lb = sl >> (8 * jj);                     // the byte with both sub-blocks' low four scale bits
+                    const int s_even = (int)((lb & 0xFu) | (((sh >> (4 * jj)) & 3u) << 4)) - 32;
+                    const int s_odd = (int)(((lb >> 4) & 0xFu) | (((sh >> (4 * jj + 2)) & 3u) << 4)) - 32;
+                    i0 += s_even * e0 + s_odd * o0;
+                    i1 += s_even * e1 + s_odd * o1;
+                }
+                acc0 += (dx0[sb] * d) * (float)i0;
+                acc1 += (dx1[sb] * d) * (float)i1;
             } else {
                 // Q6_K: ql[128] | qh[64] | scales[16] | d; the 210-byte blocks alternate between 4-byte aligned and not
                 const bool odd = (sb & 1) != 0;                             // blk0 is even: 210 (blk0 + sb) is 2 modulo 4 for odd sb
