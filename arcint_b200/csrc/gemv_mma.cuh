@@ -1,13 +1,13 @@
 // gemv_mma.cuh -- the decode GEMV at several columns with the block dots on warp-level integer MMAs.
 //
-// At one column the dp4a kernel of gemv_stream.cuh is bound by memory latency; from three or four columns on it is
-// bound by instruction issue: every column costs sixteen dp4a per 64 weights and lane, and the decode of the packed
+// At one column the dp4a kernel of gemv_stream.cuh is bound by the row stream and a launch's start-up; from three or
+// four columns on it is bound by instruction issue: every column costs sixteen dp4a per 64 weights and lane, and the decode of the packed
 // block is repeated by the second warp that holds columns 5..8. Here one mma.sync.m16n8k32 (u8 x s8 -> s32) takes
 // the dot products of EIGHT weight rows x one 32-weight sub-block x EIGHT columns at once, so the instruction count
 // per weight no longer grows with the columns:
-//   - a warp owns a slice of four super-blocks (1024 weights) of every row for the whole launch and keeps the
-//     activation codes of that slice for all eight columns in registers as B fragments (64 registers), plus the
-//     scales and block sums of the two columns whose results it ends up with;
+//   - a warp owns a slice of two to four super-blocks (512 to 1024 weights) of every row for the whole launch and
+//     keeps the activation codes of that slice for all eight columns in registers as B fragments (sixteen registers
+//     per super-block), plus the scales and block sums of the two columns whose results it ends up with;
 //   - the warps that cover a row are a group; a group takes eight consecutive rows at a time, which arrive in a
 //     shared-memory ring by bulk asynchronous copies exactly as in gemv_stream.cuh (same barriers, same bounded
 //     waits). Lane l reads row l / 4 of the stage: eight bytes of packed nibbles per pair of sub-blocks, masked
