@@ -134,10 +134,12 @@ static bool try_launch_mma(b200q_ctx *ctx, const void *w, size_t row_stride, int
     typedef GemvFmt<TYPE> F;
     constexpr int MAX_WARPS = gemv_mma_max_threads(SLICE) / 32;
     constexpr size_t SMEM_CAP = 227 * 1024;
-    const int nblk = (int)(K / F::BLK_W), nw = (nblk + SLICE - 1) / SLICE;
+    if (K % 256) return false;                                     // the kernel counts in chunks of 256 weights
+    const int nblk = (int)(K / 256), nw = (nblk + SLICE - 1) / SLICE;
     if (nw > MAX_WARPS) return false;
-    const size_t gb = (gemv_mma_group_smem(nblk * F::BLK_B, NSETS, nw) + 127) / 128 * 128;
-    if (gb > SMEM_CAP || gemv_mma_xstages((int)K, nblk * F::BLK_B) > NSETS - 1) return false;
+    const int row_bytes = nblk * gemv_mma_chunk_bytes<TYPE>();
+    const size_t gb = (gemv_mma_group_smem(row_bytes, NSETS, nw) + 127) / 128 * 128;
+    if (gb > SMEM_CAP || gemv_mma_xstages((int)K, row_bytes) > NSETS - 1) return false;
     int groups = MAX_WARPS / nw;
     while (groups > 1 && groups * gb > SMEM_CAP) --groups;
     const int per_sm = groups;                                     // groups an SM holds
@@ -183,8 +185,9 @@ static b200q_status launch_nc(b200q_ctx *ctx, const void *w, size_t row_stride, 
     // the activation registers are worth sharing further (measured on B200)
     constexpr bool wide = (NC == 3 || NC == 4) && GemvStage<TYPE>::BYTES <= 1152;
     const bool want_stream = ctx->gemv_stream_mask >= 0 ? ((ctx->gemv_stream_mask >> NC) & 1) != 0 : stream_preferred<TYPE, NC>();
-    if constexpr (TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K || TYPE == B200Q_TYPE_Q6_K || TYPE == B200Q_TYPE_IQ4_XS) {
-        // from how many columns the warp-MMA kernel wins (measured): Q6_K 3, the others 4
+    if constexpr (TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K || TYPE == B200Q_TYPE_Q6_K || TYPE == B200Q_TYPE_IQ4_XS ||
+                  TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_IQ4_NL) {
+        // from how many columns the warp-MMA kernel wins (measured): Q6_K 3, the others 4 (Q8_0 is not built for it)
         if (aligned && !ctx->no_stream && M <= INT32_MAX / 2 && ldd <= INT32_MAX && NC >= (ctx->gemv_mma_min ? ctx->gemv_mma_min : (TYPE == B200Q_TYPE_Q6_K ? 3 : 4))) {
             b200q_status st = B200Q_OK;
             // the narrowest slice per warp that covers a row with sixteen warps (twelve at four super-blocks)

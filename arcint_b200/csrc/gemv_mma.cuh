@@ -24,7 +24,8 @@
 // Fewer than eight columns run with the last column repeated in the unused B columns; nothing is stored for them.
 //
 // Q5_K adds the fifth bits to Q4_K's fragment; Q6_K works per scale group of sixteen weights (m16n8k16, signed q - 32);
-// IQ4_XS looks its nibbles up in the codebook into a signed fragment and has no mins term.
+// IQ4_XS looks its nibbles up in the codebook into a signed fragment and has no mins term; the 18-byte blocks of Q4_0
+// and IQ4_NL are counted eight to a chunk of 256 weights and go a pair per fragment, with float per block (d_w d_x).
 //
 // Stands in for the reference's kernel_mul_mv_q4_K_q8_1 at several columns (marfrit/arcint contrib/llama.cpp/patches/
 // 0000-01-kquant-integer-dpas.patch:3740-3796, 3882-3915) and its few-column int8 kernels
@@ -36,6 +37,8 @@
 namespace b200q {
 
 constexpr int GEMV_MMA_ROWS = 8;              // rows per ring stage
+// bytes of 256 weights of a row: one super-block, or eight blocks of the per-32 types (the kernel counts in these chunks)
+template <int TYPE> __host__ __device__ constexpr int gemv_mma_chunk_bytes() { return GemvFmt<TYPE>::BLK_B * (256 / GemvFmt<TYPE>::BLK_W); }
 // SLICE = super-blocks of a row that one warp owns (2, 3 or 4): the fewer, the more warps share a row and the fewer
 // registers hold activations. Sixteen warps (128 registers) for slices of 2 and 3, twelve (170 registers) for 4.
 __host__ __device__ constexpr int gemv_mma_max_threads(int slice) { return slice >= 4 ? 384 : 512; }
@@ -106,13 +109,15 @@ template <int TYPE, int NSETS, int SLICE>
 __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, size_t row_stride, int M, int nblk, const GemvAct &act,
                                               int ncols, float *__restrict__ dst, int ldd, const GemvGroupSmem &sm, int gg, int tg,
                                               int lane, int wi, int nw, int *error_word, int g, uint8_t *ring0, uint32_t bar_x) {
-    static_assert(TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K || TYPE == B200Q_TYPE_Q6_K || TYPE == B200Q_TYPE_IQ4_XS,
-                  "built for the 256-weight block types Q4_K, Q5_K, Q6_K and IQ4_XS");
+    static_assert(TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K || TYPE == B200Q_TYPE_Q6_K || TYPE == B200Q_TYPE_IQ4_XS ||
+                  TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_IQ4_NL,
+                  "built for Q4_K, Q5_K, Q6_K, IQ4_XS and the 18-byte blocks Q4_0 and IQ4_NL");
+    constexpr bool P32 = TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_IQ4_NL;      // per-32 activation form: fp16 scale per block
     static_assert(TYPE != B200Q_TYPE_Q6_K || SLICE % 2 == 0, "Q6_K: a block's alignment in the row must be known at compile time");
     constexpr bool Q5 = TYPE == B200Q_TYPE_Q5_K, Q4 = TYPE == B200Q_TYPE_Q4_K || Q5, IQ = TYPE == B200Q_TYPE_IQ4_XS;
     typedef GemvFmt<TYPE> F;
     constexpr int R = GEMV_MMA_ROWS;
-    const int row_bytes = nblk * F::BLK_B;
+    const int row_bytes = nblk * gemv_mma_chunk_bytes<TYPE>();
     const int slot = gemv_mma_slot(row_bytes);
     const int n_units = (M + R - 1) / R;
     bool ok = true;
@@ -182,6 +187,7 @@ __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, siz
     uint32_t xb[SLICE][16];
     uint4 bs0[Q4 ? SLICE : 1], bs1[Q4 ? SLICE : 1];
     float dx0[SLICE], dx1[SLICE];
+    uint32_t dxp[P32 ? SLICE : 1][8];
 #pragma unroll
     for (int sb = 0; sb < SLICE; ++sb) {
         const int blk = blk0 + sb;
@@ -190,8 +196,20 @@ __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, siz
                 bs0[sb] = __ldg(reinterpret_cast<const uint4 *>(act.s32 + (size_t)oc0 * (K / 32) + 8 * blk));
                 bs1[sb] = __ldg(reinterpret_cast<const uint4 *>(act.s32 + (size_t)oc1 * (K / 32) + 8 * blk));
             }
-            dx0[sb] = __ldg(act.d32 + (size_t)oc0 * (K / 256) + blk);
-            dx1[sb] = __ldg(act.d32 + (size_t)oc1 * (K / 256) + blk);
+            if (P32) {
+                // the eight blocks' fp16 activation scales of both columns, packed as pairs (column oc0 low, oc1 high)
+                const uint4 a = __ldg(reinterpret_cast<const uint4 *>(act.d16 + (size_t)oc0 * (K / 32) + 8 * blk));
+                const uint4 b = __ldg(reinterpret_cast<const uint4 *>(act.d16 + (size_t)oc1 * (K / 32) + 8 * blk));
+                const uint32_t av[4] = { a.x, a.y, a.z, a.w }, bv[4] = { b.x, b.y, b.z, b.w };
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    dxp[sb][2 * i] = (av[i] & 0xFFFFu) | (bv[i] << 16);
+                    dxp[sb][2 * i + 1] = (av[i] >> 16) | (bv[i] & 0xFFFF0000u);
+                }
+            } else {
+                dx0[sb] = __ldg(act.d32 + (size_t)oc0 * (K / 256) + blk);
+                dx1[sb] = __ldg(act.d32 + (size_t)oc1 * (K / 256) + blk);
+            }
         }
     }
     ok = gemv_mbar_wait(bar_x, 0);
@@ -273,6 +291,31 @@ __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, siz
                 j0 = gemv_dp2a_hi_su(bs0[sb].w, mn_hi, j0);  j1 = gemv_dp2a_hi_su(bs1[sb].w, mn_hi, j1);
                 acc0 += dx0[sb] * (d * (float)i0 - dmin * (float)j0);
                 acc1 += dx1[sb] * (d * (float)i1 - dmin * (float)j1);
+            } else if constexpr (P32) {
+                // eight 18-byte blocks: d | qs[16], weight t in the low nibble of byte t and 16 + t in the high one. A pair of
+                // blocks per fragment: the even block in rows 0..7, the odd one in rows 8..15. The even block's codes are
+                // 2 modulo 4 in the row (two words and a funnel shift), the odd block's 4-byte aligned.
+                const uint8_t *b = rowp + (blk0 + sb) * 144;
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const uint8_t *be = b + 36 * jj, *bo = be + 18;
+                    const uint32_t qe = gemv_mma_word(be + 2 + 4 * c, true), qo = gemv_mma_word(bo + 2 + 4 * c, false);
+                    const float de = hd_half_bits(*reinterpret_cast<const uint16_t *>(be)), dd = hd_half_bits(*reinterpret_cast<const uint16_t *>(bo));
+                    uint32_t a0, a1, a2, a3;
+                    if (TYPE == B200Q_TYPE_Q4_0) {
+                        a0 = nib_minus8(qe & 0x0F0F0F0Fu); a2 = nib_minus8((qe >> 4) & 0x0F0F0F0Fu);
+                        a1 = nib_minus8(qo & 0x0F0F0F0Fu); a3 = nib_minus8((qo >> 4) & 0x0F0F0F0Fu);
+                    } else {
+                        a0 = iq4nl_lookup4(qe & 0x0F0F0F0Fu); a2 = iq4nl_lookup4((qe >> 4) & 0x0F0F0F0Fu);
+                        a1 = iq4nl_lookup4(qo & 0x0F0F0F0Fu); a3 = iq4nl_lookup4((qo >> 4) & 0x0F0F0F0Fu);
+                    }
+                    int e0, e1, o0, o1, u0, u1;
+                    gemv_mma_s8s8(a0, a1, a2, a3, xb[sb][4 * jj], xb[sb][4 * jj + 1], e0, e1, u0, u1);
+                    gemv_mma_s8s8(a0, a1, a2, a3, xb[sb][4 * jj + 2], xb[sb][4 * jj + 3], u0, u1, o0, o1);
+                    const uint32_t pe = dxp[sb][2 * jj], po = dxp[sb][2 * jj + 1];
+                    acc0 += (float)e0 * (de * hd_half_bits((uint16_t)pe)) + (float)o0 * (dd * hd_half_bits((uint16_t)po));
+                    acc1 += (float)e1 * (de * hd_half_bits((uint16_t)(pe >> 16))) + (float)o1 * (dd * hd_half_bits((uint16_t)(po >> 16)));
+                }
             } else if constexpr (IQ) {
                 // IQ4_XS: d | scales_h | scales_l[4] | qs[128]; sub-block j is sixteen bytes, weights t in the low nibbles and
                 // 16 + t in the high ones, values kvalues_iq4nl[nibble], scale ls_j - 32 with ls_j six bits
@@ -397,7 +440,7 @@ gemv_mma_kernel(const uint8_t *__restrict__ W, size_t row_stride, int M, int nbl
     typedef GemvFmt<TYPE> F;
     extern __shared__ __align__(128) uint8_t smem[];
     const int nw = (nblk + SLICE - 1) / SLICE;
-    const int row_bytes = nblk * F::BLK_B, slot = gemv_mma_slot(row_bytes);
+    const int row_bytes = nblk * gemv_mma_chunk_bytes<TYPE>(), slot = gemv_mma_slot(row_bytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = warp / nw, wi = warp - g * nw;
     const size_t gbytes = (gemv_mma_group_smem(row_bytes, NSETS, nw) + 127) / 128 * 128;
     GemvGroupSmem sm;

@@ -1,5 +1,5 @@
-"""The decode GEMV on warp-level integer MMAs (gemv_mma.cuh: Q6_K from three columns, Q4_K, Q5_K and IQ4_XS from four)
-against the oracle.
+"""The decode GEMV on warp-level integer MMAs (gemv_mma.cuh: Q6_K from three columns, Q4_K, Q5_K, IQ4_XS, Q4_0 and IQ4_NL
+from four) against the oracle.
 
 The kernel keeps the arithmetic of the reference's mv_q45_K / mv_q6_K bodies (marfrit/arcint contrib/llama.cpp/patches/
 0000-01-kquant-integer-dpas.patch:3740-3874): exact integer dots per sub-block, integer sub-scales, float once per
@@ -47,7 +47,8 @@ def _run(ctx, t, w, k, x):
 # K: Q6_K rows are 16-byte multiples (the aligned path) only when K is a multiple of 2048
 @pytest.mark.parametrize("t,k", [(A.Q4_K, 256), (A.Q4_K, 1280), (A.Q4_K, 4096), (A.Q4_K, 8448), (A.Q4_K, 11008), (A.Q4_K, 12288),
                                  (A.Q6_K, 2048), (A.Q6_K, 4096), (A.Q6_K, 6144), (A.Q6_K, 8192),
-                                 (A.Q5_K, 256), (A.Q5_K, 4352), (A.Q5_K, 11008), (A.IQ4_XS, 512), (A.IQ4_XS, 5120), (A.IQ4_XS, 11264)])
+                                 (A.Q5_K, 256), (A.Q5_K, 4352), (A.Q5_K, 11008), (A.IQ4_XS, 512), (A.IQ4_XS, 5120), (A.IQ4_XS, 11264),
+                                 (A.Q4_0, 256), (A.Q4_0, 4096), (A.Q4_0, 11008), (A.IQ4_NL, 768), (A.IQ4_NL, 4096), (A.IQ4_NL, 8448)])
 @pytest.mark.parametrize("n", [3, 4, 5, 6, 7, 8])
 def test_every_column_count_and_row_length(ctx, t, k, n):
     if t != A.Q6_K and n == 3:
@@ -62,7 +63,7 @@ def test_every_column_count_and_row_length(ctx, t, k, n):
     assert rel_err(got, O.mul_mat(t, w, k, x)) < 1e-4      # the float form of the oracle: same integers, other summation order
 
 
-@pytest.mark.parametrize("t,k", [(A.Q4_K, 4096), (A.Q6_K, 4096), (A.Q5_K, 2048), (A.IQ4_XS, 2048)])
+@pytest.mark.parametrize("t,k", [(A.Q4_K, 4096), (A.Q6_K, 4096), (A.Q5_K, 2048), (A.IQ4_XS, 2048), (A.Q4_0, 2048), (A.IQ4_NL, 1024)])
 @pytest.mark.parametrize("m", [1, 7, 8, 9, 1000, 2371])
 def test_row_counts(ctx, t, k, m):
     n = 8
@@ -91,7 +92,7 @@ def test_slice_widths_and_the_dp4a_kernel_agree(ctx, slice_):
     other = _ctx_with(B200Q_GEMV_MMA_SLICE=slice_)
     plain = _ctx_with(B200Q_GEMV_MMA_MIN=99)
     try:
-        for t in (A.Q4_K, A.Q6_K, A.Q5_K, A.IQ4_XS):
+        for t in (A.Q4_K, A.Q6_K, A.Q5_K, A.IQ4_XS, A.Q4_0, A.IQ4_NL):
             if t == A.Q6_K and slice_ == 3:
                 continue                                    # Q6_K: even widths only (a request for 3 runs 4)
             m, k, n = 203, 6144, 8
@@ -131,3 +132,15 @@ def test_inside_a_captured_graph_with_column_offsets(ctx):
         ctx.free(p)
     assert np.array_equal(a, b)
     assert rel_err(a, O.mul_mat_f64(t, w, k, x, True)) < TOL
+
+
+def test_per32_rows_that_are_not_whole_chunks_fall_back(ctx):
+    """The kernel counts in chunks of 256 weights. For the 18-byte blocks a row is a 16-byte multiple exactly when it is
+    whole chunks, so every aligned row qualifies and the others take the kernel for unaligned rows."""
+    t, m, n = A.Q4_0, 40, 8
+    for k, want in ((4352, 1), (4736, 0)):
+        w = make_weights(t, m, k, 3)
+        x = np.random.default_rng(4).normal(0, 1, size=(n, k)).astype(np.float32)
+        got, st = _run(ctx, t, w, k, x)
+        assert st.get("gemv_mma", 0) == want, (k, st)
+        assert rel_err(got, O.mul_mat_f64(t, w, k, x, True)) < TOL
