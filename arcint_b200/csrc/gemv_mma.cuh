@@ -24,8 +24,8 @@
 // Fewer than eight columns run with the last column repeated in the unused B columns; nothing is stored for them.
 //
 // Q5_K adds the fifth bits to Q4_K's fragment; Q6_K works per scale group of sixteen weights (m16n8k16, signed q - 32);
-// IQ4_XS looks its nibbles up in the codebook into a signed fragment and has no mins term; the 18-byte blocks of Q4_0
-// and IQ4_NL are counted eight to a chunk of 256 weights and go a pair per fragment, with float per block (d_w d_x).
+// IQ4_XS looks its nibbles up in the codebook into a signed fragment and has no mins term; the 32-weight blocks of Q4_0,
+// IQ4_NL and Q8_0 are counted eight to a chunk of 256 weights and go a pair per fragment, with float per block (d_w d_x).
 //
 // Stands in for the reference's kernel_mul_mv_q4_K_q8_1 at several columns (marfrit/arcint contrib/llama.cpp/patches/
 // 0000-01-kquant-integer-dpas.patch:3740-3796, 3882-3915) and its few-column int8 kernels
@@ -110,9 +110,10 @@ __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, siz
                                               int ncols, float *__restrict__ dst, int ldd, const GemvGroupSmem &sm, int gg, int tg,
                                               int lane, int wi, int nw, int *error_word, int g, uint8_t *ring0, uint32_t bar_x) {
     static_assert(TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K || TYPE == B200Q_TYPE_Q6_K || TYPE == B200Q_TYPE_IQ4_XS ||
-                  TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_IQ4_NL,
-                  "built for Q4_K, Q5_K, Q6_K, IQ4_XS and the 18-byte blocks Q4_0 and IQ4_NL");
-    constexpr bool P32 = TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_IQ4_NL;      // per-32 activation form: fp16 scale per block
+                  TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_IQ4_NL || TYPE == B200Q_TYPE_Q8_0,
+                  "built for Q4_K, Q5_K, Q6_K, IQ4_XS and the 32-weight blocks Q4_0, IQ4_NL and Q8_0");
+    constexpr bool P8 = TYPE == B200Q_TYPE_Q8_0;
+    constexpr bool P32 = TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_IQ4_NL || P8;      // per-32 activation form: fp16 scale per block
     static_assert(TYPE != B200Q_TYPE_Q6_K || SLICE % 2 == 0, "Q6_K: a block's alignment in the row must be known at compile time");
     constexpr bool Q5 = TYPE == B200Q_TYPE_Q5_K, Q4 = TYPE == B200Q_TYPE_Q4_K || Q5, IQ = TYPE == B200Q_TYPE_IQ4_XS;
     typedef GemvFmt<TYPE> F;
@@ -295,14 +296,19 @@ __device__ __forceinline__ void gemv_mma_warp(const uint8_t *__restrict__ W, siz
                 // eight 18-byte blocks: d | qs[16], weight t in the low nibble of byte t and 16 + t in the high one. A pair of
                 // blocks per fragment: the even block in rows 0..7, the odd one in rows 8..15. The even block's codes are
                 // 2 modulo 4 in the row (two words and a funnel shift), the odd block's 4-byte aligned.
-                const uint8_t *b = rowp + (blk0 + sb) * 144;
+                // (Q8_0: d | 32 signed bytes, 34-byte blocks with the same alternation; weights 4c.. and 16 + 4c.. as they are)
+                constexpr int BB = P8 ? 34 : 18;
+                const uint8_t *b = rowp + (blk0 + sb) * (8 * BB);
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj) {
-                    const uint8_t *be = b + 36 * jj, *bo = be + 18;
+                    const uint8_t *be = b + 2 * BB * jj, *bo = be + BB;
                     const uint32_t qe = gemv_mma_word(be + 2 + 4 * c, true), qo = gemv_mma_word(bo + 2 + 4 * c, false);
                     const float de = hd_half_bits(*reinterpret_cast<const uint16_t *>(be)), dd = hd_half_bits(*reinterpret_cast<const uint16_t *>(bo));
                     uint32_t a0, a1, a2, a3;
-                    if (TYPE == B200Q_TYPE_Q4_0) {
+                    if (P8) {
+                        a0 = qe; a2 = gemv_mma_word(be + 18 + 4 * c, true);
+                        a1 = qo; a3 = gemv_mma_word(bo + 18 + 4 * c, false);
+                    } else if (TYPE == B200Q_TYPE_Q4_0) {
                         a0 = nib_minus8(qe & 0x0F0F0F0Fu); a2 = nib_minus8((qe >> 4) & 0x0F0F0F0Fu);
                         a1 = nib_minus8(qo & 0x0F0F0F0Fu); a3 = nib_minus8((qo >> 4) & 0x0F0F0F0Fu);
                     } else {

@@ -1,5 +1,5 @@
 """The decode GEMV on warp-level integer MMAs (gemv_mma.cuh: Q6_K from three columns, Q4_K, Q5_K, IQ4_XS, Q4_0 and IQ4_NL
-from four) against the oracle.
+from four, Q8_0 from six) against the oracle.
 
 The kernel keeps the arithmetic of the reference's mv_q45_K / mv_q6_K bodies (marfrit/arcint contrib/llama.cpp/patches/
 0000-01-kquant-integer-dpas.patch:3740-3874): exact integer dots per sub-block, integer sub-scales, float once per
@@ -48,11 +48,12 @@ def _run(ctx, t, w, k, x):
 @pytest.mark.parametrize("t,k", [(A.Q4_K, 256), (A.Q4_K, 1280), (A.Q4_K, 4096), (A.Q4_K, 8448), (A.Q4_K, 11008), (A.Q4_K, 12288),
                                  (A.Q6_K, 2048), (A.Q6_K, 4096), (A.Q6_K, 6144), (A.Q6_K, 8192),
                                  (A.Q5_K, 256), (A.Q5_K, 4352), (A.Q5_K, 11008), (A.IQ4_XS, 512), (A.IQ4_XS, 5120), (A.IQ4_XS, 11264),
-                                 (A.Q4_0, 256), (A.Q4_0, 4096), (A.Q4_0, 11008), (A.IQ4_NL, 768), (A.IQ4_NL, 4096), (A.IQ4_NL, 8448)])
+                                 (A.Q4_0, 256), (A.Q4_0, 4096), (A.Q4_0, 11008), (A.IQ4_NL, 768), (A.IQ4_NL, 4096), (A.IQ4_NL, 8448),
+                                 (A.Q8_0, 256), (A.Q8_0, 3072), (A.Q8_0, 8448)])
 @pytest.mark.parametrize("n", [3, 4, 5, 6, 7, 8])
 def test_every_column_count_and_row_length(ctx, t, k, n):
-    if t != A.Q6_K and n == 3:
-        pytest.skip("only Q6_K takes this kernel at three columns")
+    if n < {A.Q6_K: 3, A.Q8_0: 6}.get(t, 4):
+        pytest.skip("the dp4a kernel is the faster one at this column count")
     m = 77                                                  # nine batches of eight rows and one of five
     w = make_weights(t, m, k, 60 + n)
     x = np.random.default_rng(k + n).normal(0, 1, size=(n, k)).astype(np.float32)
@@ -63,7 +64,7 @@ def test_every_column_count_and_row_length(ctx, t, k, n):
     assert rel_err(got, O.mul_mat(t, w, k, x)) < 1e-4      # the float form of the oracle: same integers, other summation order
 
 
-@pytest.mark.parametrize("t,k", [(A.Q4_K, 4096), (A.Q6_K, 4096), (A.Q5_K, 2048), (A.IQ4_XS, 2048), (A.Q4_0, 2048), (A.IQ4_NL, 1024)])
+@pytest.mark.parametrize("t,k", [(A.Q4_K, 4096), (A.Q6_K, 4096), (A.Q5_K, 2048), (A.IQ4_XS, 2048), (A.Q4_0, 2048), (A.IQ4_NL, 1024), (A.Q8_0, 1024)])
 @pytest.mark.parametrize("m", [1, 7, 8, 9, 1000, 2371])
 def test_row_counts(ctx, t, k, m):
     n = 8
@@ -92,7 +93,7 @@ def test_slice_widths_and_the_dp4a_kernel_agree(ctx, slice_):
     other = _ctx_with(B200Q_GEMV_MMA_SLICE=slice_)
     plain = _ctx_with(B200Q_GEMV_MMA_MIN=99)
     try:
-        for t in (A.Q4_K, A.Q6_K, A.Q5_K, A.IQ4_XS, A.Q4_0, A.IQ4_NL):
+        for t in (A.Q4_K, A.Q6_K, A.Q5_K, A.IQ4_XS, A.Q4_0, A.IQ4_NL, A.Q8_0):
             if t == A.Q6_K and slice_ == 3:
                 continue                                    # Q6_K: even widths only (a request for 3 runs 4)
             m, k, n = 203, 6144, 8
