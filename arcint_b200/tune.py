@@ -9,7 +9,7 @@ Genome = the library's environment knobs, read once when a context is made:
   B200Q_GEMV_BLOCK_WARPS   warps per block (2..16; 0 = default 4)
   B200Q_GEMV_STREAM_MASK   which column counts take the slice-resident kernel (bit c; -1 = default rule)
   B200Q_GEMV_NO_SMALL      1: never the 128-thread / 170-register build of the wide Q4_K / Q6_K forms
-  B200Q_GEMV_MMA_MIN       fewest columns at which Q4_K / Q6_K take the warp-MMA GEMV (0 = measured rule: 4 / 3; 99 = never)
+  B200Q_GEMV_MMA_MIN       fewest columns at which a product takes the warp-MMA GEMV (0 = measured rule per type: 3 to 6; 99 = never)
   B200Q_GEMV_MMA_SLICE     super-blocks per warp of the warp-MMA GEMV (2, 3, 4; 0 = by row length)
 Fitness = sum over the cases of the median CUDA-event time of `bench.py --case` (lower is better), each case in
 its own process. A genome the library ignored (stats key "gemv_knob_ignored") scores nothing, so a fallback to
