@@ -139,7 +139,7 @@ struct b200q_ctx {
     bool         gemv_mma_sets3 = false;  // B200Q_GEMV_MMA_SETS=3: a three-stage ring for the warp-MMA GEMV even where four stages fit
     int          gemv_mma_groups = 0;     // B200Q_GEMV_MMA_GROUPS=1: blocks of one group (several blocks per SM) instead of one block per SM
     int          gemv_mma_slice = 0;      // B200Q_GEMV_MMA_SLICE=2|3|4: super-blocks per warp of the warp-MMA GEMV (0: by row length)
-    int          gemv_mma_min = 0;        // B200Q_GEMV_MMA_MIN: fewest columns at which a product takes the warp-MMA GEMV (99: never; 0: Q6_K 3, Q8_0 6, the others 4, measured)
+    int          gemv_mma_min = 0;        // B200Q_GEMV_MMA_MIN: fewest columns at which a product takes the warp-MMA GEMV (99: never; 0: Q6_K 3, Q8_0 7, the others 4, measured)
     bool         gemv_no_small = false;   // B200Q_GEMV_NO_SMALL=1: never the 128-thread, 170-register build of the wide Q6_K GEMV
     bool         moe_mins_pass = false;   // B200Q_MOE_MINS_PASS=1: Q4_K route tiles take the mins term in a separate pass
     bool         no_stream = false;       // B200Q_NO_STREAM=1: every GEMV through the per-warp ring kernel (comparisons)

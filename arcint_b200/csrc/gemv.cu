@@ -187,9 +187,9 @@ static b200q_status launch_nc(b200q_ctx *ctx, const void *w, size_t row_stride, 
     const bool want_stream = ctx->gemv_stream_mask >= 0 ? ((ctx->gemv_stream_mask >> NC) & 1) != 0 : stream_preferred<TYPE, NC>();
     if constexpr (TYPE == B200Q_TYPE_Q4_K || TYPE == B200Q_TYPE_Q5_K || TYPE == B200Q_TYPE_Q6_K || TYPE == B200Q_TYPE_IQ4_XS ||
                   TYPE == B200Q_TYPE_Q4_0 || TYPE == B200Q_TYPE_IQ4_NL || TYPE == B200Q_TYPE_Q8_0) {
-        // from how many columns the warp-MMA kernel wins (measured): Q6_K 3, Q8_0 6, the others 4
+        // from how many columns the warp-MMA kernel wins (measured): Q6_K 3, Q8_0 7, the others 4
         if (aligned && !ctx->no_stream && M <= INT32_MAX / 2 && ldd <= INT32_MAX &&
-            NC >= (ctx->gemv_mma_min ? ctx->gemv_mma_min : (TYPE == B200Q_TYPE_Q6_K ? 3 : TYPE == B200Q_TYPE_Q8_0 ? 6 : 4))) {
+            NC >= (ctx->gemv_mma_min ? ctx->gemv_mma_min : (TYPE == B200Q_TYPE_Q6_K ? 3 : TYPE == B200Q_TYPE_Q8_0 ? 7 : 4))) {
             b200q_status st = B200Q_OK;
             // the narrowest slice per warp that covers a row with sixteen warps (twelve at four super-blocks)
             const int nblk = (int)(K / 256);

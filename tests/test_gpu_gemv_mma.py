@@ -1,5 +1,5 @@
 """The decode GEMV on warp-level integer MMAs (gemv_mma.cuh: Q6_K from three columns, Q4_K, Q5_K, IQ4_XS, Q4_0 and IQ4_NL
-from four, Q8_0 from six) against the oracle.
+from four, Q8_0 from seven) against the oracle.
 
 The kernel keeps the arithmetic of the reference's mv_q45_K / mv_q6_K bodies (marfrit/arcint contrib/llama.cpp/patches/
 0000-01-kquant-integer-dpas.patch:3740-3874): exact integer dots per sub-block, integer sub-scales, float once per
@@ -52,7 +52,7 @@ def _run(ctx, t, w, k, x):
                                  (A.Q8_0, 256), (A.Q8_0, 3072), (A.Q8_0, 8448)])
 @pytest.mark.parametrize("n", [3, 4, 5, 6, 7, 8])
 def test_every_column_count_and_row_length(ctx, t, k, n):
-    if n < {A.Q6_K: 3, A.Q8_0: 6}.get(t, 4):
+    if n < {A.Q6_K: 3, A.Q8_0: 7}.get(t, 4):
         pytest.skip("the dp4a kernel is the faster one at this column count")
     m = 77                                                  # nine batches of eight rows and one of five
     w = make_weights(t, m, k, 60 + n)
